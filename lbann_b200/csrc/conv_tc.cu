@@ -1,0 +1,215 @@
+// tcgen05 implicit-GEMM convolution (1-D/2-D/3-D, stride, dilation) on channels-last
+// tensors.  Activations are [N][D][H][W][C] (2-D uses D = 1), filters are
+// [tap][Kout][C] with tap = (kd*KH + kh)*KW + kw.
+//
+// The GEMM view: rows = 128 output pixels of a (TN x TD x TH x TW) brick, columns =
+// output channels, reduction = taps x input channels.  For every (tap, channel block)
+// the producer issues ONE 5-D TMA box load whose origin is the brick origin shifted by
+// the tap offset; out-of-range coordinates are zero-filled by the TMA unit, which is
+// the convolution padding.  Strided convolutions use the tensor map's element strides.
+// The same kernel computes the data gradient of a stride-1 convolution when it is
+// given dy, the tap-flipped / channel-transposed filter and padding dil*(k-1)-pad.
+//
+// Stands in for the cuDNN calls of the reference's base_convolution layer
+// (src/layers/learning/base_convolution.cpp:462-814).
+#include "tc_pipeline.cuh"
+
+namespace lb {
+
+struct ConvGeom {
+  int N, D, H, W, C;
+  int Do, Ho, Wo, Kout;
+  int kd, kh, kw;
+  int pd, ph, pw;
+  int sd, sh, sw;
+  int dd, dh, dw;
+};
+
+template <int BN_>
+struct ConvFwdPolicy {
+  static constexpr int BN = BN_;
+  using G = StageGeom<BN>;
+
+  struct Params {
+    ConvGeom g;
+    int TW, TH, TD, TN, rows_used;
+    int tiles_w, tiles_h, tiles_d, tiles_nb, tiles_col;
+    int Cb, cblocks, slices, slices_per_stage, layout_type;
+    int num_tiles, k_iters, in_dtype;
+    long long o_sn, o_sd, o_sh, o_sw;  // output strides in elements
+    EpiParams epi;
+  };
+  struct Tile {
+    int n0, d0, h0, w0, col0;
+  };
+
+  __device__ static Tile decode(const Params& p, int t) {
+    Tile tl;
+    int r = t;
+    const int cb = r % p.tiles_col; r /= p.tiles_col;
+    const int tw = r % p.tiles_w;   r /= p.tiles_w;
+    const int th = r % p.tiles_h;   r /= p.tiles_h;
+    const int td = r % p.tiles_d;   r /= p.tiles_d;
+    tl.col0 = cb * BN;
+    tl.w0 = tw * p.TW; tl.h0 = th * p.TH; tl.d0 = td * p.TD; tl.n0 = r * p.TN;
+    return tl;
+  }
+  __device__ static int slices_in(const Params& p, int k) {
+    const int rem = p.slices - k * p.slices_per_stage;
+    return rem < p.slices_per_stage ? rem : p.slices_per_stage;
+  }
+  __device__ static uint32_t stage_bytes(const Params& p, const Tile&, int k) {
+    return (uint32_t)slices_in(p, k) * (uint32_t)((p.rows_used + BN) * p.Cb * 2);
+  }
+  __device__ static void load(const Params& p, const Tile& tl, int k, uint32_t sA, uint32_t sB,
+                              uint32_t bar, const CUtensorMap* tmA, const CUtensorMap* tmB) {
+    const ConvGeom& g = p.g;
+    const int ns = slices_in(p, k);
+    for (int j = 0; j < ns; ++j) {
+      const int sl = k * p.slices_per_stage + j;
+      const int tap = sl / p.cblocks;
+      const int c0 = (sl - tap * p.cblocks) * p.Cb;
+      const int a = tap / (g.kh * g.kw);
+      const int b = (tap / g.kw) % g.kh;
+      const int c = tap % g.kw;
+      tma_load_5d(sA + j * (kBM * p.Cb * 2), tmA, bar, c0,
+                  tl.w0 * g.sw - g.pw + c * g.dw,
+                  tl.h0 * g.sh - g.ph + b * g.dh,
+                  tl.d0 * g.sd - g.pd + a * g.dd, tl.n0);
+      tma_load_3d(sB + j * (BN * p.Cb * 2), tmB, bar, c0, tl.col0, tap);
+    }
+  }
+  __device__ static uint32_t idesc(const Params& p) {
+    return make_idesc_f16(p.in_dtype == kBF16 ? 1u : 0u, 0, 0, kBM, BN);
+  }
+  __device__ static void mma(const Params& p, int k, uint32_t sA, uint32_t sB, uint32_t tmem_acc,
+                             uint32_t idesc, bool first) {
+    const int ns = slices_in(p, k);
+    const uint32_t sbo = 8u * p.Cb * 2u;  // 8 rows of Cb elements
+    uint32_t acc = first ? 0u : 1u;
+    for (int j = 0; j < ns; ++j) {
+      const uint32_t a0 = sA + j * (kBM * p.Cb * 2);
+      const uint32_t b0 = sB + j * (BN * p.Cb * 2);
+      for (int kk = 0; kk < p.Cb / 16; ++kk) {
+        umma_f16(tmem_acc, make_smem_desc(a0 + kk * 32, 16, sbo, p.layout_type),
+                 make_smem_desc(b0 + kk * 32, 16, sbo, p.layout_type), idesc, acc);
+        acc = 1u;
+      }
+    }
+  }
+  __device__ static bool row_addr(const Params& p, const Tile& tl, int row, long long& off) {
+    int r = row;
+    const int tw = r % p.TW; r /= p.TW;
+    const int th = r % p.TH; r /= p.TH;
+    const int td = r % p.TD; r /= p.TD;
+    const int n = tl.n0 + r, d = tl.d0 + td, h = tl.h0 + th, w = tl.w0 + tw;
+    off = n * p.o_sn + d * p.o_sd + h * p.o_sh + w * p.o_sw;
+    return row < p.rows_used && n < p.g.N && d < p.g.Do && h < p.g.Ho && w < p.g.Wo;
+  }
+  __device__ static int row_index(const Params&, const Tile&, int row) { return row; }
+  __device__ static int col0(const Params&, const Tile& tl) { return tl.col0; }
+  __device__ static int ncols(const Params& p) { return p.g.Kout; }
+};
+
+static int largest_tile(int extent, int limit) {
+  // Largest tile <= limit along a dimension: the whole extent if it fits, otherwise the
+  // largest divisor of the extent unless that wastes more than half of the limit.
+  if (extent <= limit) return extent;
+  int best = 1;
+  for (int t = limit; t >= 1; --t)
+    if (extent % t == 0) { best = t; break; }
+  return best * 2 > limit ? best : limit;
+}
+
+template <int BN>
+static int launch_conv(const CUtensorMap& tmA, const CUtensorMap& tmB,
+                       typename ConvFwdPolicy<BN>::Params p, cudaStream_t stream) {
+  using P = ConvFwdPolicy<BN>;
+  using G = StageGeom<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(tc_persistent_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         G::kSmemBytes);
+    configured = true;
+  }
+  p.tiles_col = (p.g.Kout + BN - 1) / BN;
+  p.num_tiles = p.tiles_col * p.tiles_w * p.tiles_h * p.tiles_d * p.tiles_nb;
+  const int grid = p.num_tiles < lbhost::sm_count() ? p.num_tiles : lbhost::sm_count();
+  tc_persistent_kernel<P><<<grid, kTcThreads, G::kSmemBytes, stream>>>(tmA, tmB, p,
+                                                                       lbhost::status_word());
+  return (int)cudaGetLastError();
+}
+
+}  // namespace lb
+
+extern "C" {
+
+// Forward convolution / stride-1 data gradient.
+//   x: [N][D][H][W][C] with element strides (xs_n, xs_d, xs_h, xs_w), C contiguous
+//   w: [taps][Kout][C] contiguous, same dtype as x
+//   y: [N][Do][Ho][Wo][Kout] with element strides (ys_*), Kout contiguous (ldc = ys_w)
+// geom: 21 ints = N D H W C Do Ho Wo Kout kd kh kw pd ph pw sd sh sw dd dh dw
+int lb_conv_fwd_tc(const void* x, const void* w, void* y, const float* bias, const int* geom,
+                   const long long* xs, const long long* ys, int in_dtype, int out_dtype,
+                   float alpha, float beta, int act, float act_param, void* stream_) {
+  using namespace lb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  ConvGeom g;
+  static_assert(sizeof(ConvGeom) == 21 * sizeof(int), "geom layout");
+  memcpy(&g, geom, sizeof(g));
+  if (g.C % 8 != 0) return -1;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -1;
+  for (int i = 0; i < 4; ++i)
+    if (xs[i] % 8) return -1;
+
+  const int Cb = g.C >= 64 ? 64 : (g.C >= 32 ? 32 : 16);
+  const int TW = largest_tile(g.Wo, 128);
+  const int TH = largest_tile(g.Ho, 128 / TW);
+  const int TD = largest_tile(g.Do, 128 / (TW * TH));
+  const int TN = largest_tile(g.N, 128 / (TW * TH * TD));
+  const uint32_t bw = (TW - 1) * g.sw + 1, bh = (TH - 1) * g.sh + 1, bd = (TD - 1) * g.sd + 1;
+  if (bw > 256 || bh > 256 || bd > 256) return -1;
+
+  CUtensorMap tmA, tmB;
+  {
+    uint64_t dims[5] = {(uint64_t)g.C, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.D, (uint64_t)g.N};
+    uint64_t strides[4] = {(uint64_t)xs[3] * 2, (uint64_t)xs[2] * 2, (uint64_t)xs[1] * 2,
+                           (uint64_t)xs[0] * 2};
+    uint32_t box[5] = {(uint32_t)Cb, bw, bh, bd, (uint32_t)TN};
+    uint32_t es[5] = {1, (uint32_t)g.sw, (uint32_t)g.sh, (uint32_t)g.sd, 1};
+    if (!lbhost::encode_tmap(&tmA, in_dtype, 5, x, dims, strides, box, es, Cb * 2)) return -1;
+  }
+  int BN = g.Kout > 128 ? 256 : (g.Kout > 64 ? 128 : (g.Kout > 32 ? 64 : 32));
+  {
+    const int taps = g.kd * g.kh * g.kw;
+    uint64_t dims[3] = {(uint64_t)g.C, (uint64_t)g.Kout, (uint64_t)taps};
+    uint64_t strides[2] = {(uint64_t)g.C * 2, (uint64_t)g.C * g.Kout * 2};
+    uint32_t box[3] = {(uint32_t)Cb, (uint32_t)BN, 1};
+    if (!lbhost::encode_tmap(&tmB, in_dtype, 3, w, dims, strides, box, nullptr, Cb * 2)) return -1;
+  }
+
+#define LB_LAUNCH(BN_)                                                                   \
+  {                                                                                      \
+    ConvFwdPolicy<BN_>::Params p;                                                        \
+    p.g = g; p.TW = TW; p.TH = TH; p.TD = TD; p.TN = TN; p.rows_used = TW * TH * TD * TN; \
+    p.tiles_w = (g.Wo + TW - 1) / TW; p.tiles_h = (g.Ho + TH - 1) / TH;                  \
+    p.tiles_d = (g.Do + TD - 1) / TD; p.tiles_nb = (g.N + TN - 1) / TN;                  \
+    p.Cb = Cb; p.cblocks = (g.C + Cb - 1) / Cb;                                          \
+    p.slices = g.kd * g.kh * g.kw * p.cblocks; p.slices_per_stage = 64 / Cb;             \
+    p.layout_type = Cb == 64 ? kLayoutSw128 : (Cb == 32 ? kLayoutSw64 : kLayoutSw32);    \
+    p.k_iters = (p.slices + p.slices_per_stage - 1) / p.slices_per_stage;                \
+    p.in_dtype = in_dtype;                                                               \
+    p.o_sn = ys[0]; p.o_sd = ys[1]; p.o_sh = ys[2]; p.o_sw = ys[3];                      \
+    p.epi.C = y; p.epi.bias = bias; p.epi.alpha = alpha; p.epi.beta = beta;              \
+    p.epi.out_dtype = out_dtype; p.epi.bias_mode = bias ? 1 : 0; p.epi.act = act;        \
+    p.epi.act_param = act_param; p.epi.ldc = ys[3];                                      \
+    return launch_conv<BN_>(tmA, tmB, p, stream);                                        \
+  }
+  if (BN == 256) LB_LAUNCH(256)
+  if (BN == 128) LB_LAUNCH(128)
+  if (BN == 64) LB_LAUNCH(64)
+  LB_LAUNCH(32)
+#undef LB_LAUNCH
+}
+
+}  // extern "C"

@@ -1,0 +1,181 @@
+// tcgen05 GEMM for 16-bit inputs with fp32 accumulation in TMEM.
+//
+//   C[b] = act(alpha * A[b] . B[b]^T + beta * C[b] + bias)
+//
+// A is logically M x K, B logically N x K.  Each operand may be stored with K
+// contiguous ("K-major": A as [M][K], B as [N][K]) or with its M/N dimension
+// contiguous ("MN-major": A as [K][M], B as [K][N]), so all of forward
+// (x.W^T), data gradient (dy.W) and weight gradient (dy^T.x) run without a
+// transpose pass.  Replaces the cuBLAS calls behind the reference's
+// fully_connected (src/layers/learning/fully_connected.cpp:511-636),
+// channelwise_fully_connected and matmul layers
+// (src/layers/math/matmul.cpp:419-584, strided-batched).
+#include "tc_pipeline.cuh"
+
+namespace lb {
+
+template <int BN_>
+struct GemmPolicy {
+  static constexpr int BN = BN_;
+  using G = StageGeom<BN>;
+
+  struct Params {
+    int M, N, K, batch;
+    int tiles_m, tiles_n;
+    int num_tiles, k_iters;
+    int a_mn, b_mn, in_dtype;
+    long long strideC;
+    EpiParams epi;
+  };
+  struct Tile {
+    int m0, n0, b;
+  };
+
+  __device__ static Tile decode(const Params& p, int t) {
+    const int per_batch = p.tiles_m * p.tiles_n;
+    Tile tl;
+    tl.b = t / per_batch;
+    const int r = t - tl.b * per_batch;
+    const int nb = r / p.tiles_m;
+    tl.n0 = nb * BN;
+    tl.m0 = (r - nb * p.tiles_m) * kBM;
+    return tl;
+  }
+  __device__ static uint32_t stage_bytes(const Params&, const Tile&, int) {
+    return G::kStageBytes;
+  }
+  __device__ static void load(const Params& p, const Tile& tl, int k, uint32_t sA, uint32_t sB,
+                              uint32_t bar, const CUtensorMap* tmA, const CUtensorMap* tmB) {
+    const int k0 = k * kBK;
+    if (!p.a_mn) {
+      tma_load_3d(sA, tmA, bar, k0, tl.m0, tl.b);  // box {64 k, 128 rows}
+    } else {
+#pragma unroll
+      for (int j = 0; j < kBM / 64; ++j)           // box {64 m, 64 k-rows}
+        tma_load_3d(sA + j * 8192, tmA, bar, tl.m0 + j * 64, k0, tl.b);
+    }
+    if (!p.b_mn) {
+      tma_load_3d(sB, tmB, bar, k0, tl.n0, tl.b);  // box {64 k, BN rows}
+    } else {
+#pragma unroll
+      for (int j = 0; j < BN / 64; ++j)
+        tma_load_3d(sB + j * 8192, tmB, bar, tl.n0 + j * 64, k0, tl.b);
+    }
+  }
+  __device__ static uint32_t idesc(const Params& p) {
+    return make_idesc_f16(p.in_dtype == kBF16 ? 1u : 0u, p.a_mn, p.b_mn, kBM, BN);
+  }
+  __device__ static void mma(const Params& p, int, uint32_t sA, uint32_t sB, uint32_t tmem_acc,
+                             uint32_t idesc, bool first) {
+#pragma unroll
+    for (int kk = 0; kk < kBK / 16; ++kk) {
+      // K-major: 16 elements = 32 bytes along the swizzled row.
+      // MN-major: 16 k-rows of 128 bytes.
+      const uint64_t ad = p.a_mn ? make_smem_desc(sA + kk * 2048, 8192, 1024, kLayoutSw128)
+                                 : make_smem_desc(sA + kk * 32, 16, 1024, kLayoutSw128);
+      const uint64_t bd = p.b_mn ? make_smem_desc(sB + kk * 2048, 8192, 1024, kLayoutSw128)
+                                 : make_smem_desc(sB + kk * 32, 16, 1024, kLayoutSw128);
+      umma_f16(tmem_acc, ad, bd, idesc, (first && kk == 0) ? 0u : 1u);
+    }
+  }
+  __device__ static bool row_addr(const Params& p, const Tile& tl, int row, long long& off) {
+    const int m = tl.m0 + row;
+    off = (long long)tl.b * p.strideC + (long long)m * p.epi.ldc;
+    return m < p.M;
+  }
+  __device__ static int row_index(const Params&, const Tile& tl, int row) { return tl.m0 + row; }
+  __device__ static int col0(const Params&, const Tile& tl) { return tl.n0; }
+  __device__ static int ncols(const Params& p) { return p.N; }
+};
+
+template <int BN>
+static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB,
+                       typename GemmPolicy<BN>::Params p, cudaStream_t stream) {
+  using P = GemmPolicy<BN>;
+  using G = StageGeom<BN>;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(tc_persistent_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                         G::kSmemBytes);
+    configured = true;
+  }
+  p.tiles_m = (p.M + kBM - 1) / kBM;
+  p.tiles_n = (p.N + BN - 1) / BN;
+  p.num_tiles = p.tiles_m * p.tiles_n * p.batch;
+  p.k_iters = (p.K + kBK - 1) / kBK;
+  const int grid = p.num_tiles < lbhost::sm_count() ? p.num_tiles : lbhost::sm_count();
+  tc_persistent_kernel<P><<<grid, kTcThreads, G::kSmemBytes, stream>>>(tmA, tmB, p,
+                                                                       lbhost::status_word());
+  return (int)cudaGetLastError();
+}
+
+}  // namespace lb
+
+extern "C" {
+
+// Returns 0 on success, a cudaError_t (>0) on launch failure, -1 on a bad argument.
+//   a_mn = 0: A stored [M][K] with row pitch lda;  a_mn = 1: A stored [K][M] with row pitch lda
+//   b_mn = 0: B stored [N][K] with row pitch ldb;  b_mn = 1: B stored [K][N] with row pitch ldb
+//   lda/ldb (elements) must be multiples of 8 and bases 16-byte aligned (TMA).
+//   in_dtype: 0 fp16, 1 bf16.  out_dtype: 0 fp16, 1 bf16, 2 fp32.
+int lb_gemm_tc(const void* A, const void* B, void* C, const float* bias, int M, int N, int K,
+               int batch, long long lda, long long ldb, long long ldc, long long strideA,
+               long long strideB, long long strideC, int a_mn, int b_mn, int in_dtype,
+               int out_dtype, float alpha, float beta, int bias_mode, int act, float act_param,
+               int bn_hint, void* stream_) {
+  using namespace lb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -1;
+  if ((lda % 8) || (ldb % 8) || (strideA % 8) || (strideB % 8)) return -1;
+  if ((reinterpret_cast<uintptr_t>(A) & 15) || (reinterpret_cast<uintptr_t>(B) & 15)) return -1;
+
+  int BN = bn_hint;
+  if (BN != 64 && BN != 128 && BN != 256) {
+    // Heuristic: the widest tile that still gives every SM a tile.
+    const long long t256 = (long long)((M + 127) / 128) * ((N + 255) / 256) * batch;
+    const long long t128 = (long long)((M + 127) / 128) * ((N + 127) / 128) * batch;
+    if (N > 128 && t256 >= lbhost::sm_count()) BN = 256;
+    else if (N > 64 && t128 >= lbhost::sm_count() / 2) BN = 128;
+    else BN = N > 64 ? 128 : 64;
+  }
+
+  CUtensorMap tmA, tmB;
+  const uint64_t sa = strideA > 0 ? (uint64_t)strideA : (uint64_t)lda * (a_mn ? K : M);
+  const uint64_t sb = strideB > 0 ? (uint64_t)strideB : (uint64_t)ldb * (b_mn ? K : N);
+  {
+    uint64_t dims[3], strides[2];
+    uint32_t box[3];
+    if (!a_mn) { dims[0] = K; dims[1] = M; box[0] = 64; box[1] = 128; }
+    else       { dims[0] = M; dims[1] = K; box[0] = 64; box[1] = 64; }
+    dims[2] = batch; box[2] = 1;
+    strides[0] = (uint64_t)lda * 2; strides[1] = sa * 2;
+    if (!lbhost::encode_tmap(&tmA, in_dtype, 3, A, dims, strides, box, nullptr, 128)) return -1;
+  }
+  {
+    uint64_t dims[3], strides[2];
+    uint32_t box[3];
+    if (!b_mn) { dims[0] = K; dims[1] = N; box[0] = 64; box[1] = (uint32_t)BN; }
+    else       { dims[0] = N; dims[1] = K; box[0] = 64; box[1] = 64; }
+    dims[2] = batch; box[2] = 1;
+    strides[0] = (uint64_t)ldb * 2; strides[1] = sb * 2;
+    if (!lbhost::encode_tmap(&tmB, in_dtype, 3, B, dims, strides, box, nullptr, 128)) return -1;
+  }
+
+  EpiParams e;
+  e.C = C; e.bias = bias; e.alpha = alpha; e.beta = beta; e.out_dtype = out_dtype;
+  e.bias_mode = bias ? bias_mode : 0; e.act = act; e.act_param = act_param; e.ldc = ldc;
+
+#define LB_LAUNCH(BN_)                                                        \
+  {                                                                           \
+    GemmPolicy<BN_>::Params p;                                                \
+    p.M = M; p.N = N; p.K = K; p.batch = batch; p.a_mn = a_mn; p.b_mn = b_mn; \
+    p.in_dtype = in_dtype; p.strideC = strideC; p.epi = e;                    \
+    return launch_gemm<BN_>(tmA, tmB, p, stream);                             \
+  }
+  if (BN == 256) LB_LAUNCH(256)
+  if (BN == 128) LB_LAUNCH(128)
+  LB_LAUNCH(64)
+#undef LB_LAUNCH
+}
+
+}  // extern "C"

@@ -1,0 +1,268 @@
+// Persistent warp-specialised tcgen05 pipeline shared by the GEMM and the
+// implicit-GEMM convolution kernels.
+//
+//   warp 4      : TMA producer (one elected lane) - fills a ring of smem stages
+//   warp 5      : TMEM allocator + MMA issuer (one elected lane) - tcgen05.mma into
+//                 one of two TMEM accumulators, tcgen05.commit frees stages
+//   warps 0..3  : epilogue - tcgen05.ld the finished accumulator (lane quarter =
+//                 warp id), apply alpha/beta/bias/activation, store to global
+//
+// The two accumulators let the epilogue of tile i overlap the main loop of tile
+// i+1.  One CTA per SM; tiles are dealt round-robin (static persistent schedule).
+// A `Policy` supplies tile decoding, the per-stage TMA loads, the per-stage MMA
+// issue and the row -> output address map.
+#pragma once
+#include "common.cuh"
+
+namespace lb {
+
+constexpr int kBM = 128;       // accumulator rows = TMEM lanes
+constexpr int kBK = 64;        // K elements per pipeline stage (16-bit types)
+constexpr int kTcThreads = 192;
+constexpr int kMaxStages = 8;
+
+struct EpiParams {
+  void* C;            // output
+  const float* bias;  // fp32 bias or nullptr
+  float alpha;        // scale of the accumulator
+  float beta;         // scale of the existing output (0 = overwrite)
+  int out_dtype;      // DType
+  int bias_mode;      // 0 none, 1 per column, 2 per row
+  int act;            // Act
+  float act_param;
+  long long ldc;      // elements between consecutive output rows
+};
+
+template <int BN>
+struct StageGeom {
+  static constexpr int kABytes = kBM * kBK * 2;
+  static constexpr int kBBytes = BN * kBK * 2;
+  static constexpr int kStageBytes = kABytes + kBBytes;
+  static constexpr int kStages =
+      (200 * 1024 / kStageBytes) > 6 ? 6 : (200 * 1024 / kStageBytes);
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+  static constexpr int kTmemCols = (2 * BN) < 32 ? 32 : (2 * BN);  // power of two by BN choice
+};
+
+struct TcShared {
+  uint64_t full[kMaxStages];
+  uint64_t empty[kMaxStages];
+  uint64_t tmem_full[2];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+template <class Policy>
+__global__ void __launch_bounds__(kTcThreads, 1)
+tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
+                     const __grid_constant__ CUtensorMap tmB,
+                     const typename Policy::Params p, int* status) {
+  constexpr int BN = Policy::BN;
+  using G = StageGeom<BN>;
+  constexpr int S = G::kStages;
+
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ TcShared sh;
+
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  volatile int* abort_flag = &sh.abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&sh.full[s]), 1);
+      mbar_init(smem_u32(&sh.empty[s]), 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(smem_u32(&sh.tmem_full[a]), 1);
+      mbar_init(smem_u32(&sh.tmem_empty[a]), 4);  // one arrive per epilogue warp
+    }
+    sh.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tmA);
+    tma_prefetch_desc(&tmB);
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&sh.tmem_base), G::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh.tmem_base;
+
+  const int num_tiles = p.num_tiles;
+  const int k_iters = p.k_iters;
+
+  if (warp == 4) {
+    // ------------------------------ producer --------------------------------
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        const typename Policy::Tile tile = Policy::decode(p, t);
+        for (int k = 0; k < k_iters; ++k, ++it) {
+          const uint32_t s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait_bounded(smem_u32(&sh.empty[s]), ph ^ 1, abort_flag)) {
+            raise_status(status, abort_flag, kTimeoutStageEmpty);
+            ok = false;
+            break;
+          }
+          const uint32_t sA = smem_base + s * G::kStageBytes;
+          const uint32_t sB = sA + G::kABytes;
+          const uint32_t bar = smem_u32(&sh.full[s]);
+          mbar_expect_tx(bar, Policy::stage_bytes(p, tile, k));
+          Policy::load(p, tile, k, sA, sB, bar, &tmA, &tmB);
+        }
+      }
+      // Drain: every load this thread issued must have landed before the CTA's shared
+      // memory goes away.  Loads whose consumer already waited have landed; the last
+      // min(it, S) stages may still be in flight if the consumer gave up.
+      if (!ok || *abort_flag) {
+        const uint32_t pending = it < (uint32_t)S ? it : (uint32_t)S;
+        for (uint32_t j = 0; j < pending; ++j) {
+          const uint32_t q = it - 1 - j;
+          mbar_wait_budget_only(smem_u32(&sh.full[q % S]), (q / S) & 1);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      const uint32_t idesc = Policy::idesc(p);
+      uint32_t it = 0;
+      uint32_t local_tile = 0;
+      bool ok = true;
+      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
+        const uint32_t acc = local_tile & 1;
+        const uint32_t acc_ph = (local_tile >> 1) & 1;
+        if (!mbar_wait_bounded(smem_u32(&sh.tmem_empty[acc]), acc_ph ^ 1, abort_flag)) {
+          raise_status(status, abort_flag, kTimeoutTmemEmpty);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_acc = tmem_base + acc * BN;
+        for (int k = 0; k < k_iters; ++k, ++it) {
+          const uint32_t s = it % S;
+          const uint32_t ph = (it / S) & 1;
+          if (!mbar_wait_bounded(smem_u32(&sh.full[s]), ph, abort_flag)) {
+            raise_status(status, abort_flag, kTimeoutTmaFull);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sA = smem_base + s * G::kStageBytes;
+          const uint32_t sB = sA + G::kABytes;
+          Policy::mma(p, k, sA, sB, tmem_acc, idesc, /*first=*/k == 0);
+          umma_commit(smem_u32(&sh.empty[s]));  // frees the stage when the MMAs retire
+        }
+        if (ok) umma_commit(smem_u32(&sh.tmem_full[acc]));
+      }
+    }
+  } else {
+    // ------------------------------- epilogue -------------------------------
+    uint32_t local_tile = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
+      const typename Policy::Tile tile = Policy::decode(p, t);
+      const uint32_t acc = local_tile & 1;
+      const uint32_t acc_ph = (local_tile >> 1) & 1;
+      // The verdict is made warp-uniform: tcgen05.ld below is a warp-collective.
+      const bool landed = __all_sync(
+          0xffffffffu, mbar_wait_bounded(smem_u32(&sh.tmem_full[acc]), acc_ph, abort_flag));
+      if (!landed) {
+        if (lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
+        ok = false;
+        break;
+      }
+      tc_fence_after();
+      const int row = warp * 32 + lane;
+      long long row_off = 0;
+      const bool row_ok = Policy::row_addr(p, tile, row, row_off);
+      const int n0 = Policy::col0(p, tile);
+      const int n_total = Policy::ncols(p);
+      const int row_index = Policy::row_index(p, tile, row);
+      const EpiParams& e = p.epi;
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(warp * 32) << 16);
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        if (n0 + c >= n_total) break;  // warp-uniform
+        uint32_t r[32];
+        tmem_ld_32x32(taddr + c, r);
+        tmem_ld_wait();
+        if (row_ok) {
+          float v[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            float x = __uint_as_float(r[j]) * e.alpha;
+            if (e.bias_mode == 1) {
+              const int col = n0 + c + j;
+              if (col < n_total) x += e.bias[col];
+            } else if (e.bias_mode == 2) {
+              x += e.bias[row_index];
+            }
+            v[j] = x;
+          }
+          const long long off = row_off + n0 + c;
+          const int ncol = min(32, n_total - (n0 + c));
+          if (e.beta != 0.f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (j < ncol) v[j] += e.beta * load_as_f32(e.C, off + j, e.out_dtype);
+          }
+          if (e.act != kActNone) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], e.act, e.act_param);
+          }
+          if (e.out_dtype == kF32) {
+            float* dst = reinterpret_cast<float*>(e.C) + off;
+            if (ncol == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < ncol) dst[j] = v[j];
+            }
+          } else {
+            uint16_t* dst = reinterpret_cast<uint16_t*>(e.C) + off;
+            if (ncol == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8) {
+                uint4 q;
+                q.x = pack2(v[j], v[j + 1], e.out_dtype);
+                q.y = pack2(v[j + 2], v[j + 3], e.out_dtype);
+                q.z = pack2(v[j + 4], v[j + 5], e.out_dtype);
+                q.w = pack2(v[j + 6], v[j + 7], e.out_dtype);
+                *reinterpret_cast<uint4*>(dst + j) = q;
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (j < ncol) store_from_f32(e.C, off + j, v[j], e.out_dtype);
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[acc]));
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, G::kTmemCols);
+  }
+}
+
+}  // namespace lb

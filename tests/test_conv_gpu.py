@@ -1,0 +1,57 @@
+"""tcgen05 implicit-GEMM convolution against torch.nn.functional (fp32) on the same inputs."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from lbann_b200.ops import native
+from lbann_b200.ops.conv import conv_fwd, pack_filter
+
+pytestmark = pytest.mark.gpu
+
+CASES = [
+    # N, C, D, H, W, K, k, pad, stride, dil
+    (2, 16, 8, 8, 8, 32, 3, 1, 1, 1),
+    (1, 32, 16, 16, 16, 64, 3, 1, 1, 1),
+    (2, 64, 8, 8, 8, 128, 3, 1, 1, 1),
+    (1, 128, 4, 8, 8, 256, 3, 1, 1, 1),
+    (2, 16, 1, 28, 28, 48, 5, 2, 1, 1),
+    (3, 64, 1, 14, 14, 64, 1, 0, 1, 1),
+    (2, 32, 1, 30, 30, 40, 3, 1, 2, 1),
+    (1, 24, 6, 10, 12, 16, 3, 2, 1, 2),
+    (4, 8, 1, 7, 7, 24, 3, 1, 1, 1),
+]
+
+
+@pytest.mark.parametrize("case", CASES)
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_conv_fwd(case, dtype):
+    N, C, D, H, W, K, k, pad, stride, dil = case
+    torch.manual_seed(0)
+    ks = (1 if D == 1 else k, k, k)
+    pd = (0 if D == 1 else pad, pad, pad)
+    st = (1 if D == 1 else stride, stride, stride)
+    dl = (1 if D == 1 else dil, dil, dil)
+    x = torch.randn(N, C, D, H, W, device="cuda").to(dtype)
+    w = (torch.randn(K, C, *ks, device="cuda") / (C * k * k) ** 0.5).to(dtype)
+    bias = torch.randn(K, device="cuda")
+    xl = x.permute(0, 2, 3, 4, 1).contiguous()
+    y = conv_fwd(xl, pack_filter(w, dtype), ks, pad=pd, stride=st, dilation=dl, bias=bias,
+                 out_dtype=torch.float32)
+    assert native.consume_status() == 0
+    ref = F.conv3d(x.float(), w.float(), bias, st, pd, dl).permute(0, 2, 3, 4, 1)
+    torch.testing.assert_close(y, ref, rtol=2e-3, atol=2e-2)
+
+
+def test_conv_dgrad_via_flipped_filter():
+    torch.manual_seed(1)
+    N, C, K, S = 2, 32, 64, 8
+    x = torch.randn(N, C, S, S, S, device="cuda", requires_grad=True)
+    w = (torch.randn(K, C, 3, 3, 3, device="cuda") / 30).bfloat16()
+    y = F.conv3d(x, w.float(), None, 1, 1)
+    dy = torch.randn_like(y).bfloat16()
+    y.backward(dy.float())
+    dyl = dy.permute(0, 2, 3, 4, 1).contiguous()
+    dx = conv_fwd(dyl, pack_filter(w, torch.bfloat16, for_dgrad=True), 3, pad=1,
+                  out_dtype=torch.float32)
+    assert native.consume_status() == 0
+    torch.testing.assert_close(dx, x.grad.permute(0, 2, 3, 4, 1), rtol=2e-3, atol=3e-2)
