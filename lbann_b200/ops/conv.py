@@ -26,21 +26,13 @@ def _lib():
             c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_int),
             ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong),
             c_int, c_int, c_float, c_float, c_int, c_float, c_void_p]
+        lib.lb_conv_wgrad_tc.restype = c_int
+        lib.lb_conv_wgrad_tc.argtypes = [
+            c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_int),
+            ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong),
+            ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, c_int, c_float, c_void_p]
         _configured = True
     return lib
-
-
-def _triple(v):
-    if isinstance(v, int):
-        return (v, v, v)
-    v = tuple(int(i) for i in v)
-    if len(v) == 3:
-        return v
-    if len(v) == 2:
-        return (1 if False else 0, v[0], v[1])
-    if len(v) == 1:
-        return (0, 0, v[0])
-    raise ValueError(v)
 
 
 def norm3(v, fill):
@@ -129,5 +121,44 @@ def conv_fwd(x: torch.Tensor, w_taps: torch.Tensor, ksize, *, pad=0, stride=1, d
                                native.dtype_code(out.dtype), float(alpha), float(beta), int(act),
                                float(act_param), native.stream_ptr())
     native.check(rc, "lb_conv_fwd_tc")
+    native.count_launch()
+    return out
+
+
+def conv_wgrad(x: torch.Tensor, dy: torch.Tensor, ksize, *, pad=0, stride=1, dilation=1,
+               out: torch.Tensor | None = None, alpha: float = 1.0) -> torch.Tensor:
+    """Filter gradient, ADDED (times ``alpha``) into ``out``, an fp32 tensor in the
+    reference's ``Kout x C x [kd x] kh x kw`` layout (zero-initialised when omitted).
+
+    x: [N, D, H, W, C] view, dy: [N, Do, Ho, Wo, Kout] view, channels contiguous.
+    """
+    N, D, H, W, C = x.shape
+    _, Do, Ho, Wo, Kout = dy.shape
+    kd, kh, kw = norm3(ksize, 1)
+    pd, ph, pw = norm3(pad, 0)
+    sd, sh, sw = norm3(stride, 1)
+    dd, dh, dw = norm3(dilation, 1)
+    taps = kd * kh * kw
+    if out is None:
+        out = torch.zeros((Kout, C, kd, kh, kw), dtype=torch.float32, device=x.device)
+    if not x.is_cuda:
+        xin = x.float().permute(0, 4, 1, 2, 3)
+        g = dy.float().permute(0, 4, 1, 2, 3)
+        wshape = (Kout, C, kd, kh, kw)
+        gw = torch.nn.grad.conv3d_weight(xin, wshape, g, (sd, sh, sw), (pd, ph, pw), (dd, dh, dw))
+        out.view(wshape).add_(gw, alpha=alpha)
+        return out
+    if out.dtype != torch.float32 or not out.is_contiguous():
+        raise ValueError("conv_wgrad: out must be a contiguous fp32 tensor")
+    if dy.dtype != x.dtype:
+        dy = dy.to(x.dtype)
+    geom = (c_int * 21)(N, D, H, W, C, Do, Ho, Wo, Kout, kd, kh, kw, pd, ph, pw, sd, sh, sw,
+                        dd, dh, dw)
+    xs = (ctypes.c_longlong * 4)(x.stride(0), x.stride(1), x.stride(2), x.stride(3))
+    ys = (ctypes.c_longlong * 4)(dy.stride(0), dy.stride(1), dy.stride(2), dy.stride(3))
+    rc = _lib().lb_conv_wgrad_tc(x.data_ptr(), dy.data_ptr(), out.data_ptr(), geom, xs, ys,
+                                 1, C * taps, taps, native.dtype_code(x.dtype), float(alpha),
+                                 native.stream_ptr())
+    native.check(rc, "lb_conv_wgrad_tc")
     native.count_launch()
     return out

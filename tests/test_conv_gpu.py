@@ -55,3 +55,38 @@ def test_conv_dgrad_via_flipped_filter():
                   out_dtype=torch.float32)
     assert native.consume_status() == 0
     torch.testing.assert_close(dx, x.grad.permute(0, 2, 3, 4, 1), rtol=2e-3, atol=3e-2)
+
+
+WGRAD_CASES = [
+    # N, C, D, H, W, K, k, pad, stride
+    (2, 16, 8, 8, 8, 32, 3, 1, 1),
+    (2, 32, 8, 16, 16, 64, 3, 1, 1),
+    (2, 64, 8, 8, 8, 128, 3, 1, 1),
+    (1, 128, 4, 8, 8, 256, 3, 1, 1),
+    (2, 16, 1, 28, 28, 48, 5, 2, 1),
+    (3, 64, 1, 14, 14, 64, 1, 0, 1),
+    (2, 32, 1, 30, 30, 40, 3, 1, 2),
+    (4, 8, 1, 7, 7, 24, 3, 1, 1),
+]
+
+
+@pytest.mark.parametrize("case", WGRAD_CASES)
+def test_conv_wgrad(case):
+    from lbann_b200.ops.conv import conv_wgrad
+    N, C, D, H, W, K, k, pad, stride = case
+    torch.manual_seed(0)
+    ks = (1 if D == 1 else k, k, k)
+    pd = (0 if D == 1 else pad, pad, pad)
+    st = (1 if D == 1 else stride, stride, stride)
+    x = torch.randn(N, C, D, H, W, device="cuda").bfloat16()
+    w = torch.zeros(K, C, *ks, device="cuda", requires_grad=True)
+    y = F.conv3d(x.float(), w, None, st, pd)
+    dy = torch.randn_like(y).bfloat16()
+    y.backward(dy.float())
+    xl = x.permute(0, 2, 3, 4, 1).contiguous()
+    dyl = dy.permute(0, 2, 3, 4, 1).contiguous()
+    prev = torch.ones(K, C, *ks, device="cuda")
+    got = conv_wgrad(xl, dyl, ks, pad=pd, stride=st, out=prev.clone(), alpha=0.5)
+    assert native.consume_status() == 0
+    ref = prev + 0.5 * w.grad
+    torch.testing.assert_close(got, ref, rtol=2e-3, atol=2e-2 * (N * D * H * W) ** 0.5 / 8)
