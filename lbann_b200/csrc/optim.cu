@@ -1,0 +1,226 @@
+// Fused optimizer kernels over a flat parameter arena.
+//
+// All trainable weights of a model live in one fp32 "master" arena; gradients and
+// optimizer state live in parallel arenas with the same offsets.  One launch updates
+// every weight tensor: a device-resident segment table gives each tensor its offset,
+// length, learning rate and hyper-parameters, and every block looks its segment up by
+// binary search.  The same kernel refreshes the 16-bit compute copy of the weights
+// (the reference keeps typed weight proxies in sync separately,
+// include/lbann/weights/weights_proxy.hpp:77-350) and can fold in gradient
+// unscaling for mixed precision.
+//
+// Update rules follow the reference kernels exactly:
+//   SGD       src/optimizers/sgd.cu:36-108      v = mu v + g ; x -= lr v   (Nesterov: x -= lr (mu v + g))
+//   Adam      src/optimizers/adam.cu:36-96      non-finite g skipped; x -= corr*m1/(sqrt(m2)+eps) + lr*wd*x
+//   AdaGrad   src/optimizers/adagrad.cu         c += g^2 ; x -= lr g/(sqrt(c)+eps)
+//   RMSprop   src/optimizers/rmsprop.cu         c = d c + (1-d) g^2 ; x -= lr g/(sqrt(c)+eps)
+// AMP helper: unscale + finite check (src/utils/amp.cu:36-120); squared-norm reduction
+// (src/objective_functions/weight_regularization/l2.cu, src/callbacks/gradient_clipping.cpp).
+#include "common.cuh"
+
+namespace lb {
+
+enum OptKind : int { kOptSgd = 0, kOptAdam = 1, kOptAdagrad = 2, kOptRmsprop = 3 };
+
+// 64-byte segment descriptor (one per weight tensor), mirrored in lbann_b200/ops/optim.py
+struct OptSegment {
+  long long offset;   // first element in the arenas
+  long long count;    // number of elements
+  int kind;           // OptKind, -1 = frozen / no optimizer
+  int nesterov;
+  float lr;           // SGD/AdaGrad/RMSprop: learning rate.  Adam: lr (for weight decay)
+  float p0;           // SGD: momentum       Adam: beta1      RMSprop: decay
+  float p1;           //                     Adam: beta2
+  float eps;
+  float wd;           // Adam: decoupled weight decay coefficient (multiplied by lr)
+  float corr;         // Adam: lr * sqrt(1-beta2^t) / (1-beta1^t)
+  float l2;           // L2 regularisation coefficient folded into the gradient (g += l2 * x)
+  float pad[3];
+};
+static_assert(sizeof(OptSegment) == 64, "segment layout");
+
+constexpr int kOptChunk = 1024;  // elements per block iteration; tensors are padded to this
+
+__device__ __forceinline__ int find_segment(const OptSegment* segs, int nseg, long long pos) {
+  int lo = 0, hi = nseg - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (segs[mid].offset <= pos) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+// grad_dtype: dtype of the gradient arena (fp32 or 16-bit).  inv_scale multiplies g first
+// (AMP unscale / gradient averaging / clipping).  w16 (optional): 16-bit copy of the weights.
+template <typename G, typename W16>
+__global__ void fused_optimizer_kernel(float* __restrict__ w, const G* __restrict__ grad,
+                                       float* __restrict__ s0, float* __restrict__ s1,
+                                       W16* __restrict__ w16, const OptSegment* __restrict__ segs,
+                                       int nseg, long long total, float inv_scale,
+                                       const int* __restrict__ skip_flag) {
+  if (skip_flag && *skip_flag) return;  // AMP overflow: the whole step is skipped
+  const long long nchunks = (total + kOptChunk - 1) / kOptChunk;
+  for (long long ch = blockIdx.x; ch < nchunks; ch += gridDim.x) {
+    const long long base = ch * kOptChunk;
+    const int si = find_segment(segs, nseg, base);
+    const OptSegment sg = segs[si];
+    const long long end = sg.offset + sg.count;
+    for (int t = threadIdx.x; t < kOptChunk; t += blockDim.x) {
+      const long long i = base + t;
+      if (i >= end || i >= total) break;
+      float x = w[i];
+      if (sg.kind >= 0) {
+        float g = to_f32<G>(grad[i]) * inv_scale;
+        if (sg.l2 != 0.f) g += sg.l2 * x;
+        if (sg.kind == kOptSgd) {
+          if (sg.p0 != 0.f) {
+            float v = sg.p0 * s0[i] + g;
+            s0[i] = v;
+            x -= sg.lr * (sg.nesterov ? (sg.p0 * v + g) : v);
+          } else {
+            x -= sg.lr * g;
+          }
+        } else if (sg.kind == kOptAdam) {
+          if (isfinite(g)) {
+            const float m1 = sg.p0 * s0[i] + (1.f - sg.p0) * g;
+            const float m2 = sg.p1 * s1[i] + (1.f - sg.p1) * g * g;
+            s0[i] = m1; s1[i] = m2;
+            x -= sg.corr * (m1 / (sqrtf(m2) + sg.eps)) + sg.lr * sg.wd * x;
+          }
+        } else if (sg.kind == kOptAdagrad) {
+          const float c = s0[i] + g * g;
+          s0[i] = c;
+          x -= sg.lr * g / (sqrtf(c) + sg.eps);
+        } else {
+          const float c = sg.p0 * s0[i] + (1.f - sg.p0) * g * g;
+          s0[i] = c;
+          x -= sg.lr * g / (sqrtf(c) + sg.eps);
+        }
+        w[i] = x;
+      }
+      if (w16) w16[i] = from_f32<W16>(x);
+    }
+  }
+}
+
+// flag |= any non-finite; optionally g *= inv_scale in place.
+template <typename G>
+__global__ void unscale_check_kernel(G* __restrict__ grad, long long n, float inv_scale,
+                                     int write_back, int* __restrict__ flag) {
+  bool bad = false;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float g = to_f32<G>(grad[i]) * inv_scale;
+    if (!isfinite(g)) bad = true;
+    if (write_back) grad[i] = from_f32<G>(g);
+  }
+  if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(flag, 1);
+}
+
+// out[0] += sum x^2
+template <typename G>
+__global__ void sqnorm_kernel(const G* __restrict__ x, long long n, float* __restrict__ out) {
+  __shared__ float scratch[32];
+  float s = 0.f;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x) {
+    const float v = to_f32<G>(x[i]);
+    s += v * v;
+  }
+  s = warp_sum(s);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane == 0) scratch[warp] = s;
+  __syncthreads();
+  if (warp == 0) {
+    float r = lane < (blockDim.x >> 5) ? scratch[lane] : 0.f;
+    r = warp_sum(r);
+    if (lane == 0) atomicAdd(out, r);
+  }
+}
+
+// dst = cast(src) with scale (weights fp32 -> 16-bit copy, gradient casts)
+template <typename S, typename D>
+__global__ void cast_scale_kernel(const S* __restrict__ src, D* __restrict__ dst, long long n,
+                                  float scale) {
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (long long)gridDim.x * blockDim.x)
+    dst[i] = from_f32<D>(to_f32<S>(src[i]) * scale);
+}
+
+static int flat_grid(long long n, int per_block) {
+  const long long blocks = (n + per_block - 1) / per_block;
+  const long long cap = (long long)lbhost::sm_count() * 8;
+  return (int)(blocks < cap ? (blocks > 0 ? blocks : 1) : cap);
+}
+
+}  // namespace lb
+
+extern "C" {
+
+int lb_opt_segment_bytes() { return (int)sizeof(lb::OptSegment); }
+int lb_opt_chunk() { return lb::kOptChunk; }
+
+// w, s0, s1: fp32 arenas.  grad: arena of grad_dtype.  w16: optional 16-bit weight copy of
+// w16_dtype (pass null to skip).  segs: device array of nseg OptSegment sorted by offset.
+int lb_fused_optimizer(float* w, const void* grad, float* s0, float* s1, void* w16,
+                       const void* segs, int nseg, long long total, float inv_scale,
+                       const int* skip_flag, int grad_dtype, int w16_dtype, void* stream_) {
+  using namespace lb;
+  if (total <= 0 || nseg <= 0) return 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  const int grid = flat_grid(total, kOptChunk);
+  const OptSegment* sg = reinterpret_cast<const OptSegment*>(segs);
+#define LB_OPT(G, W)                                                                      \
+  fused_optimizer_kernel<G, W><<<grid, 256, 0, s>>>(w, (const G*)grad, s0, s1, (W*)w16, sg, \
+                                                    nseg, total, inv_scale, skip_flag)
+  const bool wb = (w16_dtype == kBF16);
+  if (grad_dtype == kF32) { if (wb) LB_OPT(float, __nv_bfloat16); else LB_OPT(float, __half); }
+  else if (grad_dtype == kBF16) { if (wb) LB_OPT(__nv_bfloat16, __nv_bfloat16); else LB_OPT(__nv_bfloat16, __half); }
+  else { if (wb) LB_OPT(__half, __nv_bfloat16); else LB_OPT(__half, __half); }
+#undef LB_OPT
+  return (int)cudaGetLastError();
+}
+
+int lb_unscale_check(void* grad, long long n, float inv_scale, int write_back, int* flag,
+                     int dtype, void* stream_) {
+  using namespace lb;
+  if (n <= 0) return 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  const int grid = flat_grid(n, 2048);
+  if (dtype == kF32) unscale_check_kernel<float><<<grid, 256, 0, s>>>((float*)grad, n, inv_scale, write_back, flag);
+  else if (dtype == kBF16) unscale_check_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)grad, n, inv_scale, write_back, flag);
+  else unscale_check_kernel<__half><<<grid, 256, 0, s>>>((__half*)grad, n, inv_scale, write_back, flag);
+  return (int)cudaGetLastError();
+}
+
+int lb_sqnorm(const void* x, long long n, float* out, int dtype, void* stream_) {
+  using namespace lb;
+  if (n <= 0) return 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  const int grid = flat_grid(n, 4096);
+  if (dtype == kF32) sqnorm_kernel<float><<<grid, 256, 0, s>>>((const float*)x, n, out);
+  else if (dtype == kBF16) sqnorm_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, n, out);
+  else sqnorm_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, n, out);
+  return (int)cudaGetLastError();
+}
+
+int lb_cast_scale(const void* src, void* dst, long long n, float scale, int src_dtype,
+                  int dst_dtype, void* stream_) {
+  using namespace lb;
+  if (n <= 0) return 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  const int grid = flat_grid(n, 2048);
+#define LB_CAST(S, D) cast_scale_kernel<S, D><<<grid, 256, 0, s>>>((const S*)src, (D*)dst, n, scale)
+  if (src_dtype == kF32 && dst_dtype == kBF16) LB_CAST(float, __nv_bfloat16);
+  else if (src_dtype == kF32 && dst_dtype == kF16) LB_CAST(float, __half);
+  else if (src_dtype == kF32 && dst_dtype == kF32) LB_CAST(float, float);
+  else if (src_dtype == kBF16 && dst_dtype == kF32) LB_CAST(__nv_bfloat16, float);
+  else if (src_dtype == kF16 && dst_dtype == kF32) LB_CAST(__half, float);
+  else if (src_dtype == kBF16 && dst_dtype == kBF16) LB_CAST(__nv_bfloat16, __nv_bfloat16);
+  else if (src_dtype == kF16 && dst_dtype == kF16) LB_CAST(__half, __half);
+  else return -1;
+#undef LB_CAST
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"
