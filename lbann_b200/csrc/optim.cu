@@ -33,7 +33,7 @@ struct OptSegment {
   float p1;           //                     Adam: beta2
   float eps;
   float wd;           // Adam: decoupled weight decay coefficient (multiplied by lr)
-  float corr;         // Adam: lr * sqrt(1-beta2^t) / (1-beta1^t)
+  float corr;         // unused on entry; the kernel derives it from the device step counter
   float l2;           // L2 regularisation coefficient folded into the gradient (g += l2 * x)
   float pad[3];
 };
@@ -57,13 +57,22 @@ __global__ void fused_optimizer_kernel(float* __restrict__ w, const G* __restric
                                        float* __restrict__ s0, float* __restrict__ s1,
                                        W16* __restrict__ w16, const OptSegment* __restrict__ segs,
                                        int nseg, long long total, float inv_scale,
-                                       const int* __restrict__ skip_flag) {
+                                       const int* __restrict__ skip_flag,
+                                       const int* __restrict__ step_ptr,
+                                       const float* __restrict__ lr_scale_ptr) {
   if (skip_flag && *skip_flag) return;  // AMP overflow: the whole step is skipped
+  // The step number and a global learning-rate multiplier live in device memory so that a
+  // captured CUDA graph sees fresh values on every replay.
+  const float step_t = step_ptr ? (float)(*step_ptr) : 1.f;
+  const float lr_mul = lr_scale_ptr ? *lr_scale_ptr : 1.f;
   const long long nchunks = (total + kOptChunk - 1) / kOptChunk;
   for (long long ch = blockIdx.x; ch < nchunks; ch += gridDim.x) {
     const long long base = ch * kOptChunk;
     const int si = find_segment(segs, nseg, base);
-    const OptSegment sg = segs[si];
+    OptSegment sg = segs[si];
+    sg.lr *= lr_mul;
+    if (sg.kind == kOptAdam)
+      sg.corr = sg.lr * sqrtf(1.f - powf(sg.p1, step_t)) / (1.f - powf(sg.p0, step_t));
     const long long end = sg.offset + sg.count;
     for (int t = threadIdx.x; t < kOptChunk; t += blockDim.x) {
       const long long i = base + t;
@@ -160,11 +169,14 @@ extern "C" {
 int lb_opt_segment_bytes() { return (int)sizeof(lb::OptSegment); }
 int lb_opt_chunk() { return lb::kOptChunk; }
 
+// step_ptr: device int holding the 1-based step number (Adam bias correction);
+// lr_scale_ptr: optional device float multiplied into every learning rate.
 // w, s0, s1: fp32 arenas.  grad: arena of grad_dtype.  w16: optional 16-bit weight copy of
 // w16_dtype (pass null to skip).  segs: device array of nseg OptSegment sorted by offset.
 int lb_fused_optimizer(float* w, const void* grad, float* s0, float* s1, void* w16,
                        const void* segs, int nseg, long long total, float inv_scale,
-                       const int* skip_flag, int grad_dtype, int w16_dtype, void* stream_) {
+                       const int* skip_flag, const int* step_ptr, const float* lr_scale_ptr,
+                       int grad_dtype, int w16_dtype, void* stream_) {
   using namespace lb;
   if (total <= 0 || nseg <= 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
@@ -172,7 +184,8 @@ int lb_fused_optimizer(float* w, const void* grad, float* s0, float* s1, void* w
   const OptSegment* sg = reinterpret_cast<const OptSegment*>(segs);
 #define LB_OPT(G, W)                                                                      \
   fused_optimizer_kernel<G, W><<<grid, 256, 0, s>>>(w, (const G*)grad, s0, s1, (W*)w16, sg, \
-                                                    nseg, total, inv_scale, skip_flag)
+                                                    nseg, total, inv_scale, skip_flag,     \
+                                                    step_ptr, lr_scale_ptr)
   const bool wb = (w16_dtype == kBF16);
   if (grad_dtype == kF32) { if (wb) LB_OPT(float, __nv_bfloat16); else LB_OPT(float, __half); }
   else if (grad_dtype == kBF16) { if (wb) LB_OPT(__nv_bfloat16, __nv_bfloat16); else LB_OPT(__nv_bfloat16, __half); }

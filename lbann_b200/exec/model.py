@@ -1,0 +1,468 @@
+"""Executable model: layer graph + weights arena + objective + metrics.
+
+Mirrors the responsibilities of the reference's ``model`` class (src/models/model.cpp):
+set-up order (topology check -> execution order -> layer set-up -> weights sorted by name
+-> objective / metrics), forward / backward / update, per-mode statistics.  Differences by
+design: backward is PyTorch autograd over the layers' forward functions; all weights live
+in one flat arena updated by a single fused optimizer launch; split / dummy / evaluation
+helper layers are implicit (a tensor may simply feed several children).
+"""
+from __future__ import annotations
+
+import time
+from collections import OrderedDict, defaultdict
+from typing import Callable, Dict, List, Optional
+
+import torch
+
+from ..ops import native
+from ..ops.optim import ParameterArena
+from ..proto import lbann_pb2 as pb
+from . import layers_core, layers_misc  # noqa: F401  (populate the registry)
+from .layer_base import LAYER_REGISTRY, ExecLayer
+from .weights import ExecWeights, optimizer_from_proto
+
+MODES = ("training", "validation", "testing", "prediction", "tournament")
+
+
+class LbannError(RuntimeError):
+    pass
+
+
+class ModeStats:
+    """Running sums for one execution mode, kept on the device (no per-step host sync)."""
+
+    def __init__(self, device, num_metrics):
+        self.obj_sum = torch.zeros((), dtype=torch.float64, device=device)
+        self.samples = 0
+        self.metric_sums = [torch.zeros((), dtype=torch.float64, device=device)
+                            for _ in range(num_metrics)]
+
+    def reset(self):
+        self.obj_sum.zero_()
+        self.samples = 0
+        for m in self.metric_sums:
+            m.zero_()
+
+
+class ExecMetric:
+    def __init__(self, name, layer_name, unit=""):
+        self.name, self.layer_name, self.unit = name, layer_name, unit
+
+
+class ExecModel:
+    def __init__(self, model_pb, default_optimizer_pb=None, *, device="cpu",
+                 default_dtype=torch.float32, data_dims: Optional[Callable] = None,
+                 slice_points: Optional[Callable] = None, comm=None, parallel=None,
+                 distconv=None, seed: int = 0, arena_allocator=None):
+        self.proto = model_pb
+        self.name = model_pb.name or "model"
+        self.device = torch.device(device)
+        self.default_dtype = default_dtype
+        self._data_dims = data_dims or (lambda field: (1,))
+        self._slice_points = slice_points
+        self.comm = comm
+        self.parallel = parallel
+        self.distconv = distconv
+        self.seed = int(seed)
+        self.default_optimizer = optimizer_from_proto(default_optimizer_pb) \
+            if default_optimizer_pb is not None else (None, {})
+        if self.default_optimizer[0] is None:
+            self.default_optimizer = ("none", {})
+        self.layers: List[ExecLayer] = []
+        self.layers_by_name: Dict[str, ExecLayer] = {}
+        self.weights: List[ExecWeights] = []
+        self.weights_by_name: Dict[str, ExecWeights] = {}
+        self.arena: Optional[ParameterArena] = None
+        self.arena_allocator = arena_allocator
+        self.callbacks = []
+        self.metrics: List[ExecMetric] = []
+        self.objective_terms = []      # (layer_name, scale)
+        self.l2_terms = []             # (scale, [weights names])
+        self.acts: Dict[str, List[torch.Tensor]] = {}
+        self.current_inputs: Dict[str, torch.Tensor] = {}
+        self.current_mini_batch_size = 0
+        self._global_mb = 0
+        self._mb_offset = 0
+        self.stats: Dict[str, ModeStats] = {}
+        self.last_objective = None
+        self.num_epochs = int(model_pb.num_epochs)
+        self.amp_enabled = bool(model_pb.amp.enabled) if model_pb.HasField("amp") else False
+        amp = model_pb.amp
+        self.amp_scale = float(amp.init_scale) or 65536.0
+        self.amp_growth = float(amp.growth_factor) or 2.0
+        self.amp_backoff = float(amp.backoff_factor) or 0.5
+        self.amp_interval = int(amp.growth_interval) or 2000
+        self._amp_good_steps = 0
+        self._amp_skipped = 0
+        self._gen = None
+        self.sync_layers = False       # debugging: synchronise after every layer
+        self.layer_timing = False
+        self.is_setup = False
+
+    # ------------------------------------------------------------------ helpers used by layers
+    def data_dims(self, field):
+        return tuple(int(d) for d in self._data_dims(field))
+
+    def slice_points_from_reader(self, which):
+        if self._slice_points is None:
+            raise LbannError("no data reader provides slice points")
+        return self._slice_points(which)
+
+    def layer(self, name) -> ExecLayer:
+        return self.layers_by_name[name]
+
+    def activation(self, layer_name, index=0) -> torch.Tensor:
+        return self.acts[layer_name][index]
+
+    def add_weights(self, w: ExecWeights):
+        if w.name in self.weights_by_name:
+            raise LbannError(f"duplicate weights name '{w.name}'")
+        self.weights.append(w)
+        self.weights_by_name[w.name] = w
+
+    def generator(self):
+        if self._gen is None or self._gen.device != self.device:
+            self._gen = torch.Generator(device=self.device)
+            rank = self.comm.rank_in_world if self.comm is not None else 0
+            self._gen.manual_seed(self.seed * 7919 + 17 * rank + 1)
+        return self._gen
+
+    def global_mini_batch_size(self):
+        return self._global_mb
+
+    def mini_batch_offset(self):
+        return self._mb_offset
+
+    # ------------------------------------------------------------------ set-up
+    def setup(self):
+        m = self.proto
+        for wp in m.weights:
+            self.add_weights(ExecWeights(wp.name, wp))
+        seen = set()
+        for lp in m.layer:
+            if not lp.name:
+                raise LbannError("layer without a name")
+            if lp.name in seen:
+                raise LbannError(f"duplicate layer name '{lp.name}'")
+            seen.add(lp.name)
+            t = lp.WhichOneof("layer_type")
+            if t not in LAYER_REGISTRY:
+                raise LbannError(f"layer '{lp.name}': unsupported layer type '{t}'")
+            layer = LAYER_REGISTRY[t](lp, self)
+            self.layers.append(layer)
+            self.layers_by_name[layer.name] = layer
+        self._setup_topology()
+        self._setup_execution_order()
+        if self.parallel is not None:
+            self.parallel.prepare_model(self)
+        if self.distconv is not None:
+            self.distconv.prepare_model(self)
+        for layer in self.layers:
+            in_dims = []
+            for pn in layer.parent_names:
+                parent = self.layers_by_name[pn]
+                in_dims.append(parent.out_dims[self._slot(parent, layer)])
+            layer.in_dims = [tuple(d) for d in in_dims]
+            for wn in layer.weight_names:
+                if wn and wn not in self.weights_by_name:
+                    raise LbannError(f"layer '{layer.name}' refers to unknown weights '{wn}'")
+            layer.out_dims = [tuple(int(x) for x in d) for d in layer.setup(layer.in_dims)]
+        self._setup_weights()
+        self._setup_objective()
+        self._fuse_activations()
+        for mode in MODES:
+            self.stats[mode] = ModeStats(self.device, len(self.metrics))
+        self.is_setup = True
+        return self
+
+    def _setup_topology(self):
+        by = self.layers_by_name
+        for l in self.layers:
+            for pn in l.parent_names:
+                if pn not in by:
+                    raise LbannError(f"layer '{l.name}' has unknown parent '{pn}'")
+            for cn in l.child_names:
+                if cn not in by:
+                    raise LbannError(f"layer '{l.name}' has unknown child '{cn}'")
+        # reciprocate edges: a parent listed by the child must list the child and vice versa
+        for l in self.layers:
+            for pn in l.parent_names:
+                p = by[pn]
+                if p.child_names.count(l.name) < l.parent_names.count(pn):
+                    p.child_names.append(l.name)
+            for cn in l.child_names:
+                c = by[cn]
+                if c.parent_names.count(l.name) < l.child_names.count(cn):
+                    c.parent_names.append(l.name)
+        for l in self.layers:
+            l.parents = [by[n] for n in l.parent_names]
+            l.children = [by[n] for n in l.child_names]
+            n = len(l.parents)
+            if n < l.min_parents or (l.max_parents >= 0 and n > l.max_parents):
+                raise LbannError(f"layer '{l.name}' ({l.type}) has {n} parents")
+
+    def _setup_execution_order(self):
+        indeg = {l.name: len(l.parent_names) for l in self.layers}
+        order, ready = [], [l for l in self.layers if indeg[l.name] == 0]
+        ready.sort(key=lambda l: 0 if l.type == "input" else 1)   # inputs first
+        pos = {l.name: i for i, l in enumerate(self.layers)}
+        while ready:
+            l = ready.pop(0)
+            order.append(l)
+            nxt = []
+            for c in l.children:
+                indeg[c.name] -= 1
+                if indeg[c.name] == 0:
+                    nxt.append(c)
+            ready.extend(sorted(set(nxt), key=lambda x: pos[x.name]))
+        if len(order) != len(self.layers):
+            raise LbannError("layer graph has a cycle")
+        self.layers = order
+
+    @staticmethod
+    def _slot(parent: ExecLayer, child: ExecLayer, occurrence: int = 0) -> int:
+        if parent.num_outputs == 1:
+            return 0
+        idxs = [i for i, n in enumerate(parent.child_names) if n == child.name]
+        return idxs[min(occurrence, len(idxs) - 1)]
+
+    def _setup_weights(self):
+        # deterministic order: sorted by name (src/models/model.cpp:1138-1153)
+        self.weights.sort(key=lambda w: w.name)
+        compute = self.default_dtype if (self.device.type == "cuda" and self.default_dtype in
+                                         (torch.float16, torch.bfloat16)) else None
+        self.arena = ParameterArena(self.device, compute_dtype=compute,
+                                    allocator=self.arena_allocator)
+        used = [w for w in self.weights if w.shape is not None]
+        for w in used:
+            w.bind(self.arena)
+        self.arena.materialise()
+        for w in used:
+            w.materialise(self.default_optimizer, self.seed)
+        self.weights = used
+        self.weights_by_name = {w.name: w for w in used}
+        if self.parallel is not None:
+            self.parallel.sync_initial_weights(self)
+        self.arena.refresh_compute()
+
+    def _setup_objective(self):
+        obj = self.proto.objective_function
+        for t in obj.layer_term:
+            if t.layer not in self.layers_by_name:
+                raise LbannError(f"objective refers to unknown layer '{t.layer}'")
+            self.objective_terms.append((t.layer, float(t.scale_factor) if t.scale_factor else 1.0))
+        for t in obj.l2_weight_regularization:
+            names = [n for s in t.weights for n in s.split()] or [w.name for w in self.weights]
+            scale = float(t.scale_factor) if t.scale_factor else 1.0
+            self.l2_terms.append((scale, names))
+            for n in names:
+                w = self.weights_by_name.get(n)
+                if w is not None and w.has_optimizer():
+                    w.slot.l2 += scale
+        for mp in self.proto.metric:
+            which = mp.WhichOneof("metric_type")
+            if which == "layer_metric":
+                lm = mp.layer_metric
+                if lm.layer not in self.layers_by_name:
+                    raise LbannError(f"metric refers to unknown layer '{lm.layer}'")
+                self.metrics.append(ExecMetric(lm.name or lm.layer, lm.layer, lm.unit))
+            elif which is not None:
+                from .metrics import make_external_metric
+                self.metrics.append(make_external_metric(which, getattr(mp, which)))
+
+    def _fuse_activations(self):
+        """Fold ReLU / leaky ReLU that directly follows a convolution, fully-connected or
+        batch-norm layer into that layer's kernel epilogue (CUDA 16-bit path only)."""
+        if self.device.type != "cuda" or self.default_dtype not in (torch.float16, torch.bfloat16):
+            return
+        protected = {n for n, _ in self.objective_terms} | {m.layer_name for m in self.metrics
+                                                            if getattr(m, "layer_name", None)}
+        for l in self.layers:
+            if l.type not in ("convolution", "fully_connected", "batch_normalization",
+                              "channelwise_fully_connected"):
+                continue
+            if len(l.children) != 1 or l.name in protected:
+                continue
+            c = l.children[0]
+            if c.type == "relu":
+                act = (native.ACT_RELU, 0.0)
+            elif c.type == "leaky_relu":
+                act = (native.ACT_LEAKY, c.p0())
+            else:
+                continue
+            if (l.dtype or self.default_dtype) != (c.dtype or self.default_dtype):
+                continue
+            if getattr(l, "transpose", False) or getattr(l, "groups", 1) != 1:
+                continue
+            if l.data_layout == "model_parallel":
+                continue
+            l.fused_act = act
+            c.fused_into_parent = True
+
+    # ------------------------------------------------------------------ execution
+    def forward_prop(self, inputs: Dict[str, torch.Tensor], mode: str = "training",
+                     global_mini_batch_size: Optional[int] = None, mini_batch_offset: int = 0):
+        training = mode == "training"
+        self.current_inputs = inputs
+        first = next(iter(inputs.values())) if inputs else None
+        self.current_mini_batch_size = int(first.shape[0]) if first is not None else 0
+        dp = self.parallel.dp_size if self.parallel is not None else 1
+        self._global_mb = global_mini_batch_size or self.current_mini_batch_size * dp
+        self._mb_offset = mini_batch_offset
+        acts = {}
+        cbs = self.callbacks
+        occurrence = defaultdict(int)
+        for layer in self.layers:
+            xs = []
+            occ_local = defaultdict(int)
+            for pn in layer.parent_names:
+                parent = self.layers_by_name[pn]
+                k = occ_local[pn]
+                occ_local[pn] += 1
+                xs.append(acts[pn][self._slot(parent, layer, k)])
+            for cb in cbs:
+                cb.on_layer_forward_begin(self, layer, mode)
+            if self.layer_timing:
+                if self.device.type == "cuda":
+                    torch.cuda.synchronize()
+                t0 = time.perf_counter()
+            ys = layer.forward(xs, training)
+            if self.layer_timing or self.sync_layers:
+                if self.device.type == "cuda":
+                    torch.cuda.synchronize()
+                if self.layer_timing:
+                    layer.fp_time += time.perf_counter() - t0
+            acts[layer.name] = ys
+            for cb in cbs:
+                cb.on_layer_forward_end(self, layer, mode)
+        self.acts = acts
+        return acts
+
+    def _layer_mean(self, layer_name: str) -> torch.Tensor:
+        """Sum over the local mini-batch divided by the global mini-batch size."""
+        layer = self.layers_by_name[layer_name]
+        y = self.acts[layer_name][0] if self.acts[layer_name] else self.acts[layer.parent_names[0]][0]
+        return y.float().sum() / float(self._global_mb)
+
+    def local_objective(self) -> torch.Tensor:
+        total = None
+        for name, scale in self.objective_terms:
+            v = self._layer_mean(name) * scale
+            total = v if total is None else total + v
+        if total is None:
+            total = torch.zeros((), device=self.device)
+        return total
+
+    def l2_value(self) -> torch.Tensor:
+        total = torch.zeros((), dtype=torch.float32, device=self.device)
+        for scale, names in self.l2_terms:
+            for n in names:
+                w = self.weights_by_name.get(n)
+                if w is not None:
+                    total = total + 0.5 * scale * (w.handle.master.detach().float() ** 2).sum()
+        return total
+
+    def record_statistics(self, mode: str, local_obj: torch.Tensor):
+        st = self.stats[mode]
+        n = self._global_mb
+        with torch.no_grad():
+            st.obj_sum += local_obj.detach().double() * n
+            st.samples += n
+            for i, m in enumerate(self.metrics):
+                if getattr(m, "layer_name", None):
+                    st.metric_sums[i] += self._layer_mean(m.layer_name).detach().double() * n
+
+    def clear_gradients(self):
+        self.arena.zero_grad()
+
+    def backward_prop(self, local_obj: torch.Tensor):
+        scale = self.amp_scale if self.amp_enabled else 1.0
+        for cb in self.callbacks:
+            cb.on_backward_prop_begin(self)
+        if local_obj.requires_grad:
+            (local_obj * scale if scale != 1.0 else local_obj).backward()
+        if self.parallel is not None:
+            self.parallel.sync_gradients(self)
+        for cb in self.callbacks:
+            cb.on_backward_prop_end(self)
+
+    def update_weights(self) -> bool:
+        """Returns False when the step was skipped (AMP overflow)."""
+        for cb in self.callbacks:
+            cb.on_optimize_begin(self)
+        inv = 1.0
+        if self.amp_enabled:
+            flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+            self.arena.unscale_and_check(1.0 / self.amp_scale, flag, write_back=True)
+            if self.parallel is not None:
+                self.parallel.allreduce_max_inplace(flag)
+            if int(flag.item()):
+                self.amp_scale *= self.amp_backoff
+                self._amp_good_steps = 0
+                self._amp_skipped += 1
+                if self._amp_skipped >= 10 and (self.comm is None or self.comm.am_world_master()):
+                    print(f"WARNING: {self._amp_skipped} consecutive steps skipped by automatic "
+                          f"mixed precision; loss scale is now {self.amp_scale}")
+                return False
+            self._amp_skipped = 0
+            self._amp_good_steps += 1
+            if self._amp_good_steps >= self.amp_interval:
+                self.amp_scale *= self.amp_growth
+                self._amp_good_steps = 0
+        self.arena.step(inv)
+        for w in self.weights:
+            w.handle.bump()
+        for cb in self.callbacks:
+            cb.on_optimize_end(self)
+        return True
+
+    def train_step(self, inputs, global_mini_batch_size=None, mini_batch_offset=0):
+        """clear grads -> forward -> objective -> backward (+ gradient sync) -> update."""
+        self.clear_gradients()
+        for cb in self.callbacks:
+            cb.on_forward_prop_begin(self, "training")
+        self.forward_prop(inputs, "training", global_mini_batch_size, mini_batch_offset)
+        for cb in self.callbacks:
+            cb.on_forward_prop_end(self, "training")
+        obj = self.local_objective()
+        self.last_objective = obj.detach()
+        self.record_statistics("training", obj)
+        self.backward_prop(obj)
+        self.update_weights()
+        return self.last_objective
+
+    @torch.no_grad()
+    def evaluate_step(self, inputs, mode="validation", global_mini_batch_size=None,
+                      mini_batch_offset=0):
+        for cb in self.callbacks:
+            cb.on_forward_prop_begin(self, mode)
+        self.forward_prop(inputs, mode, global_mini_batch_size, mini_batch_offset)
+        for cb in self.callbacks:
+            cb.on_forward_prop_end(self, mode)
+        obj = self.local_objective()
+        self.last_objective = obj.detach()
+        self.record_statistics(mode, obj)
+        return self.last_objective
+
+    # ------------------------------------------------------------------ reporting
+    def reduce_statistics(self, mode: str):
+        """-> (mean objective incl. L2, [metric means], samples) over the trainer."""
+        st = self.stats[mode]
+        vals = torch.stack([st.obj_sum] + st.metric_sums) if st.metric_sums else st.obj_sum.reshape(1)
+        vals = vals.clone()
+        if self.parallel is not None and self.parallel.dp_size > 1:
+            self.parallel.allreduce_sum_inplace(vals)
+        n = max(st.samples, 1)
+        vals = (vals / n).tolist()
+        obj = vals[0] + float(self.l2_value())
+        return obj, vals[1:], st.samples
+
+    def reset_statistics(self, mode: str):
+        self.stats[mode].reset()
+
+    def describe(self) -> str:
+        lines = [f"model {self.name}: {len(self.layers)} layers, {len(self.weights)} weights, "
+                 f"{sum(w.slot.count for w in self.weights)} parameters"]
+        lines += ["  " + l.describe() for l in self.layers]
+        return "\n".join(lines)

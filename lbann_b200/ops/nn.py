@@ -1,0 +1,785 @@
+"""Differentiable building blocks over the native kernels.
+
+Each function takes PyTorch tensors; CUDA 16-bit tensors run the sm_100a kernels of this
+library (forward and backward), anything else runs the equivalent PyTorch expression so
+the whole framework also works on CPU in fp32.  Weight gradients of the native paths are
+ACCUMULATED straight into the fp32 gradient buffer of the weight (``WeightHandle.grad``),
+mirroring the reference's destination-scale / gradient-scale contract
+(include/lbann/optimizers/optimizer_impl.hpp:208-290).
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Callable, Optional
+
+import torch
+import torch.nn.functional as F
+
+from . import native
+from .conv import conv_fwd, conv_wgrad, norm3, out_size, pack_filter
+from .elementwise import UNARY_CODE, unary_raw
+from .gemm import gemm
+from .native import c_float, c_int, c_ll, c_void_p
+
+_HALF = (torch.float16, torch.bfloat16)
+_ACT_UNARY = {native.ACT_RELU: "relu", native.ACT_LEAKY: "leaky_relu"}
+_configured = False
+
+
+def _lib():
+    global _configured
+    lib = native.cuda_lib()
+    if not _configured:
+        P = ctypes.POINTER
+        lib.lb_pool_fwd.restype = c_int
+        lib.lb_pool_fwd.argtypes = [c_void_p, c_void_p, P(c_int), P(c_ll), c_int, c_void_p]
+        lib.lb_pool_bwd.restype = c_int
+        lib.lb_pool_bwd.argtypes = [c_void_p, c_void_p, c_void_p, P(c_int), P(c_ll), c_int, c_void_p]
+        lib.lb_layer_norm_fwd.restype = c_int
+        lib.lb_layer_norm_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_ll, c_int, c_float, c_int, c_void_p]
+        lib.lb_layer_norm_bwd.restype = c_int
+        lib.lb_layer_norm_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p]
+        lib.lb_bn_partial_sums.restype = c_int
+        lib.lb_bn_partial_sums.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_void_p]
+        lib.lb_bn_finalize_apply.restype = c_int
+        lib.lb_bn_finalize_apply.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                             c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int,
+                                             c_float, c_float, c_float, c_float, c_int, c_float,
+                                             c_int, c_void_p]
+        lib.lb_bn_apply_fixed.restype = c_int
+        lib.lb_bn_apply_fixed.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                          c_ll, c_int, c_float, c_int, c_float, c_int, c_void_p]
+        lib.lb_bn_bwd_sums.restype = c_int
+        lib.lb_bn_bwd_sums.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                       c_ll, c_int, c_int, c_float, c_int, c_float, c_int, c_void_p]
+        lib.lb_bn_bwd_apply.restype = c_int
+        lib.lb_bn_bwd_apply.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_void_p, c_ll, c_int, c_int, c_float, c_float, c_float,
+                                        c_int, c_float, c_int, c_void_p]
+        lib.lb_softmax_fwd.restype = c_int
+        lib.lb_softmax_fwd.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_float, c_int, c_int,
+                                       c_void_p]
+        lib.lb_softmax_bwd.restype = c_int
+        lib.lb_softmax_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_float,
+                                       c_int, c_int, c_void_p]
+        lib.lb_softmax_ce_fwd.restype = c_int
+        lib.lb_softmax_ce_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int,
+                                          c_void_p]
+        lib.lb_softmax_ce_bwd.restype = c_int
+        lib.lb_softmax_ce_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_void_p,
+                                          c_ll, c_int, c_int, c_void_p]
+        lib.lb_sample_loss_fwd.restype = c_int
+        lib.lb_sample_loss_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_ll, c_int, c_int,
+                                           c_void_p]
+        lib.lb_sample_loss_bwd.restype = c_int
+        lib.lb_sample_loss_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_ll,
+                                           c_ll, c_int, c_int, c_void_p]
+        lib.lb_topk_accuracy.restype = c_int
+        lib.lb_topk_accuracy.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int,
+                                         c_void_p]
+        _configured = True
+    return lib
+
+
+def _native_ok(x: torch.Tensor) -> bool:
+    return x.is_cuda and x.dtype in _HALF
+
+
+class WeightHandle:
+    """What a native op needs from a weight: the fp32 master tensor (autograd leaf), its
+    fp32 gradient buffer, and cached 16-bit / repacked copies valid for one optimizer step."""
+
+    def __init__(self, master: torch.Tensor, grad: Optional[torch.Tensor] = None,
+                 compute16: Optional[torch.Tensor] = None):
+        self.master = master
+        self.grad = grad
+        self.compute16 = compute16      # kept in sync by the fused optimizer when present
+        self.version = 0
+        self._cache = {}
+
+    def bump(self):
+        self.version += 1
+        self._cache.clear()
+
+    def cast(self, dtype: torch.dtype) -> torch.Tensor:
+        if dtype == torch.float32:
+            return self.master.detach()
+        if self.compute16 is not None and self.compute16.dtype == dtype:
+            return self.compute16
+        key = ("cast", dtype)
+        if key not in self._cache:
+            self._cache[key] = self.master.detach().to(dtype)
+        return self._cache[key]
+
+    def packed(self, kind: str, dtype: torch.dtype, fn: Callable[[], torch.Tensor]) -> torch.Tensor:
+        key = (kind, dtype)
+        if key not in self._cache:
+            self._cache[key] = fn()
+        return self._cache[key]
+
+    def add_grad(self, g: torch.Tensor):
+        if self.grad is None:
+            return
+        self.grad.add_(g.reshape(self.grad.shape).to(self.grad.dtype))
+
+
+def column_sums(x2d: torch.Tensor) -> torch.Tensor:
+    """fp32 sum over rows of a [rows, C] 16-bit CUDA tensor (native when C % 8 == 0)."""
+    rows, C = x2d.shape
+    if _native_ok(x2d) and C % 8 == 0 and x2d.is_contiguous() and rows > 0:
+        sums = torch.zeros(2 * C, dtype=torch.float32, device=x2d.device)
+        rc = _lib().lb_bn_partial_sums(x2d.data_ptr(), sums.data_ptr(), rows, C, 1,
+                                       native.dtype_code(x2d.dtype), native.stream_ptr())
+        native.check(rc, "lb_bn_partial_sums")
+        native.count_launch()
+        return sums[:C]
+    return x2d.float().sum(0)
+
+
+def _act_grad_from_output(y: torch.Tensor, dy: torch.Tensor, act: int, p: float) -> torch.Tensor:
+    """dy * act'(.) for activations whose derivative is a function of the output sign."""
+    if act == native.ACT_NONE:
+        return dy
+    if dy.stride() != y.stride():
+        dy = torch.empty_like(y).copy_(dy)
+    return unary_raw(UNARY_CODE[_ACT_UNARY[act]], y, dy, p, 0.0, 1)
+
+
+# --------------------------------------------------------------------------- linear
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_leaf, b_leaf, wh: WeightHandle, bh: Optional[WeightHandle], act, act_p):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        w16 = wh.cast(x.dtype)
+        bias = bh.master.detach() if bh is not None else None
+        y = gemm(x2, w16, trans_b=True, bias=bias, act=act, act_param=act_p)
+        ctx.save_for_backward(x2, y if act != native.ACT_NONE else None)
+        ctx.meta = (wh, bh, act, act_p, x.shape)
+        return y.reshape(*x.shape[:-1], w16.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, y = ctx.saved_tensors
+        wh, bh, act, act_p, xshape = ctx.meta
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if not dy2.is_contiguous():
+            dy2 = dy2.contiguous()
+        dy2 = _act_grad_from_output(y, dy2, act, act_p) if y is not None else dy2
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, wh.cast(dy2.dtype)).reshape(xshape)
+        if wh.grad is not None:
+            gemm(dy2, x2, trans_a=True, out=wh.grad.view(wh.master.shape), beta=1.0)
+        if bh is not None and bh.grad is not None:
+            bh.grad.add_(column_sums(dy2))
+        return dx, None, None, None, None, None, None
+
+
+def linear(x, wh: WeightHandle, bh: Optional[WeightHandle] = None, act: int = native.ACT_NONE,
+           act_param: float = 0.0):
+    """y = act(x @ W^T + b) over the last dimension; W is [out, in]."""
+    if _native_ok(x) and act in (native.ACT_NONE, native.ACT_RELU, native.ACT_LEAKY):
+        return _Linear.apply(x, wh.master, bh.master if bh is not None else None, wh, bh, act,
+                             float(act_param))
+    w = wh.master if wh.master.dtype == x.dtype else wh.master.to(x.dtype)
+    b = None if bh is None else (bh.master if bh.master.dtype == x.dtype else bh.master.to(x.dtype))
+    y = F.linear(x, w, b)
+    from .gemm import _ACT_FN
+    return _ACT_FN[act](y, act_param)
+
+
+# --------------------------------------------------------------------------- convolution
+def _cl_view(x: torch.Tensor) -> torch.Tensor:
+    """[N, C, (D,) H, W] logical tensor -> channels-last NDHWC view (copying if needed)."""
+    if x.dim() == 4:
+        x = x.contiguous(memory_format=torch.channels_last)
+        return x.permute(0, 2, 3, 1).unsqueeze(1)
+    if x.dim() == 3:
+        x = x.unsqueeze(2)  # N, C, 1, W
+        x = x.contiguous(memory_format=torch.channels_last)
+        return x.permute(0, 2, 3, 1).unsqueeze(1)
+    x = x.contiguous(memory_format=torch.channels_last_3d)
+    return x.permute(0, 2, 3, 4, 1)
+
+
+def _from_cl(y: torch.Tensor, ndim: int) -> torch.Tensor:
+    """NDHWC tensor -> logical [N, C, ...] view with channels-last strides."""
+    if ndim == 5:
+        return y.permute(0, 4, 1, 2, 3)
+    if ndim == 4:
+        return y.squeeze(1).permute(0, 3, 1, 2)
+    return y.squeeze(1).squeeze(1).permute(0, 2, 1)
+
+
+def _pad_channels(x_cl: torch.Tensor, mult: int = 8) -> torch.Tensor:
+    C = x_cl.shape[-1]
+    if C % mult == 0:
+        return x_cl
+    return F.pad(x_cl, (0, mult - C % mult))
+
+
+def _upsample_zero(dy_cl: torch.Tensor, stride, out_dims) -> torch.Tensor:
+    """Insert zeros between the elements of dy (data gradient of a strided convolution)."""
+    N, Do, Ho, Wo, K = dy_cl.shape
+    sd, sh, sw = stride
+    up = torch.zeros((N, (Do - 1) * sd + 1, (Ho - 1) * sh + 1, (Wo - 1) * sw + 1, K),
+                     dtype=dy_cl.dtype, device=dy_cl.device)
+    up[:, ::sd, ::sh, ::sw, :] = dy_cl
+    return up
+
+
+class _Conv(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w_leaf, b_leaf, wh, bh, ksize, pad, stride, dil, act, act_p):
+        ndim = x.dim()
+        x_cl = _pad_channels(_cl_view(x))
+        Kout, Cin = wh.master.shape[0], wh.master.shape[1]
+        Kp = (Kout + 7) // 8 * 8
+        Cp = x_cl.shape[-1]
+
+        def pack_fwd():
+            w = wh.master.detach().reshape(Kout, Cin, -1)
+            if Kp != Kout or Cp != Cin:
+                w = F.pad(w, (0, 0, 0, Cp - Cin, 0, Kp - Kout))
+            return pack_filter(w.reshape(Kp, Cp, *ksize), x.dtype)
+
+        wt = wh.packed("fwd", x.dtype, pack_fwd)
+        bias = None
+        if bh is not None:
+            bias = bh.master.detach()
+            if Kp != Kout:
+                bias = F.pad(bias, (0, Kp - Kout))
+        y = conv_fwd(x_cl, wt, ksize, pad=pad, stride=stride, dilation=dil, bias=bias, act=act,
+                     act_param=act_p)
+        ctx.save_for_backward(x_cl, y if act != native.ACT_NONE else None)
+        ctx.meta = (wh, bh, ksize, pad, stride, dil, act, act_p, ndim, Kout, Cin, Kp, Cp)
+        out = y[..., :Kout] if Kp != Kout else y
+        return _from_cl(out, ndim)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_cl, y = ctx.saved_tensors
+        wh, bh, ksize, pad, stride, dil, act, act_p, ndim, Kout, Cin, Kp, Cp = ctx.meta
+        dy_cl = _cl_view(dy)
+        if Kp != Kout:
+            dy_cl = _pad_channels(dy_cl)
+        if not dy_cl.is_contiguous():
+            dy_cl = dy_cl.contiguous()
+        if y is not None:
+            dy_cl = _act_grad_from_output(y, dy_cl, act, act_p)
+        N, D, H, W, _ = x_cl.shape
+        dx = None
+        if ctx.needs_input_grad[0]:
+            def pack_bwd():
+                w = wh.master.detach().reshape(Kout, Cin, -1)
+                if Kp != Kout or Cp != Cin:
+                    w = F.pad(w, (0, 0, 0, Cp - Cin, 0, Kp - Kout))
+                return pack_filter(w.reshape(Kp, Cp, *ksize), dy.dtype, for_dgrad=True)
+
+            wt = wh.packed("dgrad", dy.dtype, pack_bwd)
+            src = dy_cl if stride == (1, 1, 1) else _upsample_zero(dy_cl, stride, (D, H, W))
+            bpad = tuple(d * (k - 1) - p for d, k, p in zip(dil, ksize, pad))
+            dx_cl = conv_fwd(src, wt, ksize, pad=bpad, stride=1, dilation=dil, out_dims=(D, H, W))
+            if Cp != Cin:
+                dx_cl = dx_cl[..., :Cin]
+            dx = _from_cl(dx_cl, ndim)
+        if wh.grad is not None:
+            if Kp == Kout and Cp == Cin:
+                conv_wgrad(x_cl, dy_cl, ksize, pad=pad, stride=stride, dilation=dil,
+                           out=wh.grad.view(Kout, Cin, *ksize))
+            else:
+                tmp = conv_wgrad(x_cl, dy_cl, ksize, pad=pad, stride=stride, dilation=dil)
+                wh.grad.add_(tmp[:Kout, :Cin].reshape(wh.grad.shape))
+        if bh is not None and bh.grad is not None:
+            bh.grad.add_(column_sums(dy_cl.reshape(-1, dy_cl.shape[-1]))[:Kout])
+        return (dx,) + (None,) * 10
+
+
+def convolution(x, wh: WeightHandle, bh: Optional[WeightHandle], ksize, pad, stride, dilation,
+                groups: int = 1, act: int = native.ACT_NONE, act_param: float = 0.0):
+    """N-d convolution on a logical [N, C, spatial...] tensor; kernel Kout x C/groups x k..."""
+    nsp = x.dim() - 2
+    if _native_ok(x) and groups == 1 and act in (native.ACT_NONE, native.ACT_RELU, native.ACT_LEAKY):
+        k3, p3, s3, d3 = norm3(ksize, 1), norm3(pad, 0), norm3(stride, 1), norm3(dilation, 1)
+        return _Conv.apply(x, wh.master, bh.master if bh is not None else None, wh, bh, k3, p3, s3,
+                           d3, act, float(act_param))
+    w = wh.master if wh.master.dtype == x.dtype else wh.master.to(x.dtype)
+    b = None if bh is None else (bh.master if bh.master.dtype == x.dtype else bh.master.to(x.dtype))
+    fn = {1: F.conv1d, 2: F.conv2d, 3: F.conv3d}[nsp]
+    y = fn(x, w, b, tuple(stride), tuple(pad), tuple(dilation), groups)
+    from .gemm import _ACT_FN
+    return _ACT_FN[act](y, act_param)
+
+
+def deconvolution(x, wh: WeightHandle, bh, ksize, pad, stride, dilation, output_padding,
+                  groups: int = 1):
+    """Transposed convolution; kernel stored Cin x Cout/groups x k... (PyTorch convention,
+    which is also the reference's: src/layers/learning/deconvolution.cpp)."""
+    nsp = x.dim() - 2
+    w = wh.master if wh.master.dtype == x.dtype else wh.master.to(x.dtype)
+    b = None if bh is None else (bh.master if bh.master.dtype == x.dtype else bh.master.to(x.dtype))
+    ks, st = tuple(ksize), tuple(stride)
+    if (_native_ok(x) and groups == 1 and ks == st and all(p == 0 for p in pad)
+            and all(d == 1 for d in dilation) and all(o == 0 for o in output_padding)):
+        # Non-overlapping up-convolution (U-Net k2 s2): a per-pixel GEMM followed by a
+        # depth-to-space rearrangement.  Both run natively (GEMM + autograd of views).
+        return _deconv_as_gemm(x, wh, bh, ks)
+    fn = {1: F.conv_transpose1d, 2: F.conv_transpose2d, 3: F.conv_transpose3d}[nsp]
+    return fn(x, w, b, st, tuple(pad), tuple(output_padding), groups, tuple(dilation))
+
+
+def _deconv_as_gemm(x, wh, bh, ks):
+    ndim = x.dim()
+    x_cl = _cl_view(x)                         # N, D, H, W, Cin
+    N, D, H, W, Cin = x_cl.shape
+    Cout = wh.master.shape[1]
+    k3 = norm3(ks, 1)
+    taps = k3[0] * k3[1] * k3[2]
+    w2d = wh.packed("deconv2d", x.dtype, lambda: wh.master.detach().reshape(Cin, Cout * taps)
+                    .t().contiguous().to(x.dtype))     # [Cout*taps, Cin]
+    y = _DeconvGemm.apply(x_cl.reshape(-1, Cin), wh.master, wh, w2d)   # [pix, Cout*taps]
+    y = y.reshape(N, D, H, W, Cout, k3[0], k3[1], k3[2])
+    y = y.permute(0, 1, 5, 2, 6, 3, 7, 4).reshape(N, D * k3[0], H * k3[1], W * k3[2], Cout)
+    if bh is not None:
+        y = y + bh.master.to(y.dtype)
+    return _from_cl(y, ndim)
+
+
+class _DeconvGemm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x2, w_leaf, wh, w2d):
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        ctx.save_for_backward(x2, w2d)
+        ctx.wh = wh
+        return gemm(x2, w2d, trans_b=True)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w2d = ctx.saved_tensors
+        wh = ctx.wh
+        if not dy.is_contiguous():
+            dy = dy.contiguous()
+        dx = gemm(dy, w2d) if ctx.needs_input_grad[0] else None
+        if wh.grad is not None:
+            # grad of W[Cin, Cout*taps] = x^T dy
+            gemm(x2, dy, trans_a=True, out=wh.grad.view(x2.shape[1], dy.shape[1]), beta=1.0)
+        return dx, None, None, None
+
+
+# --------------------------------------------------------------------------- pooling
+_POOL_MODE = {"max": 0, "average": 1, "average_no_pad": 2}
+
+
+class _Pool(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, ksize, pad, stride, mode):
+        ndim = x.dim()
+        x_cl = _cl_view(x)
+        N, D, H, W, C = x_cl.shape
+        Do, Ho, Wo = (out_size(D, ksize[0], pad[0], stride[0], 1),
+                      out_size(H, ksize[1], pad[1], stride[1], 1),
+                      out_size(W, ksize[2], pad[2], stride[2], 1))
+        y = torch.empty((N, Do, Ho, Wo, C), dtype=x.dtype, device=x.device)
+        geom = (c_int * 18)(N, D, H, W, C, Do, Ho, Wo, *ksize, *pad, *stride, mode)
+        xs = (c_ll * 4)(x_cl.stride(0), x_cl.stride(1), x_cl.stride(2), x_cl.stride(3))
+        rc = _lib().lb_pool_fwd(x_cl.data_ptr(), y.data_ptr(), geom, xs,
+                                native.dtype_code(x.dtype), native.stream_ptr())
+        native.check(rc, "lb_pool_fwd")
+        native.count_launch()
+        ctx.save_for_backward(x_cl)
+        ctx.meta = (geom, ndim)
+        return _from_cl(y, ndim)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (x_cl,) = ctx.saved_tensors
+        geom, ndim = ctx.meta
+        dy_cl = _cl_view(dy)
+        if not dy_cl.is_contiguous():
+            dy_cl = dy_cl.contiguous()
+        dx = torch.empty(x_cl.shape, dtype=x_cl.dtype, device=x_cl.device)
+        xs = (c_ll * 4)(x_cl.stride(0), x_cl.stride(1), x_cl.stride(2), x_cl.stride(3))
+        rc = _lib().lb_pool_bwd(x_cl.data_ptr(), dy_cl.data_ptr(), dx.data_ptr(), geom, xs,
+                                native.dtype_code(x_cl.dtype), native.stream_ptr())
+        native.check(rc, "lb_pool_bwd")
+        native.count_launch()
+        return _from_cl(dx, ndim), None, None, None, None
+
+
+def pooling(x, ksize, pad, stride, mode: str):
+    nsp = x.dim() - 2
+    if _native_ok(x) and x.shape[1] % 8 == 0:
+        return _Pool.apply(x, norm3(ksize, 1), norm3(pad, 0), norm3(stride, 1), _POOL_MODE[mode])
+    ks, pd, st = tuple(ksize), tuple(pad), tuple(stride)
+    if mode == "max":
+        return {1: F.max_pool1d, 2: F.max_pool2d, 3: F.max_pool3d}[nsp](x, ks, st, pd)
+    fn = {1: F.avg_pool1d, 2: F.avg_pool2d, 3: F.avg_pool3d}[nsp]
+    return fn(x, ks, st, pd, count_include_pad=(mode == "average"))
+
+
+# --------------------------------------------------------------------------- batch norm
+class _BatchNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, s_leaf, b_leaf, sh, bh, run_mean, run_var, eps, decay, correction,
+                reduce_fn, count_scale, act, act_p):
+        ndim = x.dim()
+        x_cl = _cl_view(x)
+        if not x_cl.is_contiguous():
+            x_cl = x_cl.contiguous()
+        C = x_cl.shape[-1]
+        rows = x_cl.numel() // C
+        lib = _lib()
+        dt = native.dtype_code(x.dtype)
+        sums = torch.zeros(2 * C, dtype=torch.float32, device=x.device)
+        native.check(lib.lb_bn_partial_sums(x_cl.data_ptr(), sums.data_ptr(), rows, C, 1, dt,
+                                            native.stream_ptr()), "lb_bn_partial_sums")
+        if reduce_fn is not None:
+            reduce_fn(sums)
+        count = float(rows * count_scale)
+        y = torch.empty_like(x_cl)
+        stats = torch.empty(2 * C, dtype=torch.float32, device=x.device)
+        scale = sh.master.detach() if sh is not None else None
+        bias = bh.master.detach() if bh is not None else None
+        native.check(lib.lb_bn_finalize_apply(
+            x_cl.data_ptr(), sums.data_ptr(), native.ptr(scale), native.ptr(bias), y.data_ptr(),
+            stats.data_ptr(), native.ptr(run_mean), native.ptr(run_var), rows, C, 1, count,
+            float(correction), float(eps), float(decay), act, float(act_p), dt,
+            native.stream_ptr()), "lb_bn_finalize_apply")
+        native.count_launch(2)
+        ctx.save_for_backward(x_cl, stats, y if act else None)
+        ctx.meta = (sh, bh, eps, correction, reduce_fn, count, act, act_p, ndim)
+        return _from_cl(y, ndim)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_cl, stats, y = ctx.saved_tensors
+        sh, bh, eps, correction, reduce_fn, count, act, act_p, ndim = ctx.meta
+        dy_cl = _cl_view(dy)
+        if not dy_cl.is_contiguous():
+            dy_cl = dy_cl.contiguous()
+        C = x_cl.shape[-1]
+        rows = x_cl.numel() // C
+        lib = _lib()
+        dt = native.dtype_code(x_cl.dtype)
+        bsums = torch.zeros(4 * C, dtype=torch.float32, device=x_cl.device)
+        scale = sh.master.detach() if sh is not None else None
+        native.check(lib.lb_bn_bwd_sums(x_cl.data_ptr(), dy_cl.data_ptr(), native.ptr(y),
+                                        stats.data_ptr(), native.ptr(scale), bsums.data_ptr(),
+                                        rows, C, 1, float(eps), act, float(act_p), dt,
+                                        native.stream_ptr()), "lb_bn_bwd_sums")
+        # parameter gradients use the local partial sums (the optimizer's allreduce sums ranks)
+        if sh is not None and sh.grad is not None:
+            sh.grad.add_(bsums[:C])
+        if bh is not None and bh.grad is not None:
+            bh.grad.add_(bsums[C:2 * C])
+        if reduce_fn is not None:
+            reduce_fn(bsums[2 * C:])
+        dx = torch.empty_like(x_cl)
+        native.check(lib.lb_bn_bwd_apply(x_cl.data_ptr(), dy_cl.data_ptr(), native.ptr(y),
+                                         stats.data_ptr(), native.ptr(scale), bsums.data_ptr(),
+                                         dx.data_ptr(), rows, C, 1, count, float(correction),
+                                         float(eps), act, float(act_p), dt, native.stream_ptr()),
+                     "lb_bn_bwd_apply")
+        native.count_launch(2)
+        return (_from_cl(dx, ndim),) + (None,) * 13
+
+
+def batch_norm(x, sh, bh, run_mean, run_var, training: bool, eps: float, decay: float,
+               bessel: bool = True, reduce_fn=None, count_scale: float = 1.0,
+               act: int = native.ACT_NONE, act_param: float = 0.0):
+    """Batch normalisation over (N, spatial) per channel with the reference's variance
+    definition.  ``reduce_fn(t)`` sums an fp32 tensor in place over the statistics group
+    (``count_scale`` = number of ranks in it)."""
+    C = x.shape[1]
+    correction = 1.0 if bessel else 0.0
+    if _native_ok(x) and C % 8 == 0:
+        if training:
+            return _BatchNorm.apply(x, sh.master if sh else None, bh.master if bh else None, sh, bh,
+                                    run_mean, run_var, eps, decay, correction, reduce_fn,
+                                    count_scale, act, float(act_param))
+        x_cl = _cl_view(x)
+        if not x_cl.is_contiguous():
+            x_cl = x_cl.contiguous()
+        y = torch.empty_like(x_cl)
+        rows = x_cl.numel() // C
+        native.check(_lib().lb_bn_apply_fixed(
+            x_cl.data_ptr(), run_mean.data_ptr(), run_var.data_ptr(),
+            native.ptr(sh.master.detach() if sh else None),
+            native.ptr(bh.master.detach() if bh else None), y.data_ptr(), rows, C, float(eps), act,
+            float(act_param), native.dtype_code(x.dtype), native.stream_ptr()), "lb_bn_apply_fixed")
+        native.count_launch()
+        return _from_cl(y, x.dim())
+    # reference semantics in PyTorch (fp32 statistics)
+    dims = [0] + list(range(2, x.dim()))
+    shape = [1, C] + [1] * (x.dim() - 2)
+    xf = x.float()
+    if training:
+        n = x.numel() / C
+        s = torch.stack([xf.sum(dims), (xf * xf).sum(dims)])
+        if reduce_fn is not None:
+            s = _ReduceSum.apply(s, reduce_fn)
+            n = n * count_scale
+        mean = s[0] / n
+        var = (s[1] / n - mean * mean) * (n / (n - correction))
+        var = torch.clamp(var, min=eps)
+        with torch.no_grad():
+            if run_mean is not None:
+                run_mean.mul_(decay).add_((1 - decay) * mean.detach())
+                run_var.mul_(decay).add_((1 - decay) * var.detach())
+    else:
+        mean, var = run_mean, run_var
+    y = (xf - mean.view(shape)) * torch.rsqrt(var.view(shape) + eps)
+    if sh is not None:
+        y = y * sh.master.view(shape)
+    if bh is not None:
+        y = y + bh.master.view(shape)
+    from .gemm import _ACT_FN
+    return _ACT_FN[act](y, act_param).to(x.dtype)
+
+
+class _ReduceSum(torch.autograd.Function):
+    """Differentiable in-place sum over ranks (the gradient of a sum-allreduce is a
+    sum-allreduce)."""
+
+    @staticmethod
+    def forward(ctx, t, reduce_fn):
+        ctx.reduce_fn = reduce_fn
+        out = t.clone()
+        reduce_fn(out)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        g = g.clone()
+        ctx.reduce_fn(g)
+        return g, None
+
+
+# --------------------------------------------------------------------------- layer norm
+class _LayerNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, s_leaf, b_leaf, sh, bh, cols, eps):
+        xc = x.contiguous()
+        rows = xc.numel() // cols
+        y = torch.empty_like(xc)
+        mean = torch.empty(rows, dtype=torch.float32, device=x.device)
+        rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
+        scale = sh.master.detach().reshape(-1) if sh is not None else None
+        bias = bh.master.detach().reshape(-1) if bh is not None else None
+        native.check(_lib().lb_layer_norm_fwd(xc.data_ptr(), native.ptr(scale), native.ptr(bias),
+                                              y.data_ptr(), mean.data_ptr(), rstd.data_ptr(), rows,
+                                              cols, float(eps), native.dtype_code(x.dtype),
+                                              native.stream_ptr()), "lb_layer_norm_fwd")
+        native.count_launch()
+        ctx.save_for_backward(xc, mean, rstd)
+        ctx.meta = (sh, bh, cols)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        xc, mean, rstd = ctx.saved_tensors
+        sh, bh, cols = ctx.meta
+        dyc = dy.contiguous()
+        rows = xc.numel() // cols
+        dx = torch.empty_like(xc)
+        scale = sh.master.detach().reshape(-1) if sh is not None else None
+        dscale = sh.grad.view(-1) if (sh is not None and sh.grad is not None) else None
+        dbias = bh.grad.view(-1) if (bh is not None and bh.grad is not None) else None
+        native.check(_lib().lb_layer_norm_bwd(xc.data_ptr(), dyc.data_ptr(), native.ptr(scale),
+                                              mean.data_ptr(), rstd.data_ptr(), dx.data_ptr(),
+                                              native.ptr(dscale), native.ptr(dbias), rows, cols,
+                                              native.dtype_code(xc.dtype), native.stream_ptr()),
+                     "lb_layer_norm_bwd")
+        native.count_launch(2)
+        return dx, None, None, None, None, None, None
+
+
+def layer_norm(x, normalized_size: int, sh=None, bh=None, eps: float = 1e-5):
+    """Normalise over the trailing ``normalized_size`` elements of every sample."""
+    if x.is_cuda and x.dtype in (torch.float16, torch.bfloat16, torch.float32):
+        return _LayerNorm.apply(x, sh.master if sh else None, bh.master if bh else None, sh, bh,
+                                int(normalized_size), eps)
+    shape = x.shape
+    x2 = x.reshape(-1, normalized_size).float()
+    mean = x2.mean(1, keepdim=True)
+    var = (x2 * x2).mean(1, keepdim=True) - mean * mean
+    y = (x2 - mean) * torch.rsqrt(torch.clamp(var, min=0) + eps)
+    if sh is not None:
+        y = y * sh.master.reshape(1, -1)
+    if bh is not None:
+        y = y + bh.master.reshape(1, -1)
+    return y.reshape(shape).to(x.dtype)
+
+
+# --------------------------------------------------------------------------- softmax family
+class _Softmax(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, mode, in_scale, causal_period):
+        xc = x.contiguous()
+        cols = xc.shape[-1]
+        rows = xc.numel() // cols
+        y = torch.empty_like(xc)
+        native.check(_lib().lb_softmax_fwd(xc.data_ptr(), y.data_ptr(), rows, cols, mode,
+                                           float(in_scale), int(causal_period),
+                                           native.dtype_code(x.dtype), native.stream_ptr()),
+                     "lb_softmax_fwd")
+        native.count_launch()
+        ctx.save_for_backward(y)
+        ctx.meta = (mode, in_scale, causal_period)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        (y,) = ctx.saved_tensors
+        mode, in_scale, causal_period = ctx.meta
+        dyc = dy.contiguous()
+        cols = y.shape[-1]
+        rows = y.numel() // cols
+        dx = torch.empty_like(y)
+        native.check(_lib().lb_softmax_bwd(y.data_ptr(), dyc.data_ptr(), dx.data_ptr(), rows, cols,
+                                           mode, float(in_scale), int(causal_period),
+                                           native.dtype_code(y.dtype), native.stream_ptr()),
+                     "lb_softmax_bwd")
+        native.count_launch()
+        return dx, None, None, None
+
+
+def softmax_lastdim(x, log: bool = False, in_scale: float = 1.0, causal_period: int = 0):
+    """(log-)softmax over the last dimension; optional input scale and causal masking of
+    an S x S score matrix (row r sees columns <= r mod S)."""
+    if x.is_cuda and x.dtype in (torch.float16, torch.bfloat16, torch.float32):
+        return _Softmax.apply(x, 1 if log else 0, in_scale, causal_period)
+    z = x.float() * in_scale
+    if causal_period:
+        S = causal_period
+        r = torch.arange(z.shape[-2], device=x.device) % S
+        mask = torch.arange(z.shape[-1], device=x.device)[None, :] > r[:, None]
+        z = z.masked_fill(mask, float("-inf"))
+    out = F.log_softmax(z, -1) if log else F.softmax(z, -1)
+    return out.to(x.dtype)
+
+
+class _SoftmaxCE(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, labels):
+        xc = x.contiguous()
+        cols = xc.shape[-1]
+        rows = xc.numel() // cols
+        loss = torch.empty(rows, dtype=torch.float32, device=x.device)
+        lse = torch.empty(rows, dtype=torch.float32, device=x.device)
+        lab = labels.reshape(-1).to(torch.int64).contiguous()
+        native.check(_lib().lb_softmax_ce_fwd(xc.data_ptr(), lab.data_ptr(), loss.data_ptr(),
+                                              lse.data_ptr(), rows, cols,
+                                              native.dtype_code(x.dtype), native.stream_ptr()),
+                     "lb_softmax_ce_fwd")
+        native.count_launch()
+        ctx.save_for_backward(xc, lab, lse)
+        return loss.reshape(x.shape[:-1])
+
+    @staticmethod
+    def backward(ctx, dloss):
+        xc, lab, lse = ctx.saved_tensors
+        cols = xc.shape[-1]
+        rows = xc.numel() // cols
+        dx = torch.empty_like(xc)
+        g = dloss.reshape(-1).float().contiguous()
+        native.check(_lib().lb_softmax_ce_bwd(xc.data_ptr(), lab.data_ptr(), lse.data_ptr(),
+                                              g.data_ptr(), 0.0, dx.data_ptr(), rows, cols,
+                                              native.dtype_code(xc.dtype), native.stream_ptr()),
+                     "lb_softmax_ce_bwd")
+        native.count_launch()
+        return dx, None
+
+
+def softmax_cross_entropy(logits, labels):
+    """Per-row ``-log softmax(logits)[label]`` in fp32; rows with an out-of-range label give
+    0 (value and gradient), as the reference's label-mode cross entropy does."""
+    if logits.is_cuda and logits.dtype in (torch.float16, torch.bfloat16, torch.float32):
+        return _SoftmaxCE.apply(logits, labels)
+    C = logits.shape[-1]
+    lab = labels.reshape(-1).long()
+    ok = (lab >= 0) & (lab < C)
+    lp = F.log_softmax(logits.float().reshape(-1, C), -1)
+    picked = lp.gather(1, lab.clamp(0, C - 1)[:, None])[:, 0]
+    return torch.where(ok, -picked, torch.zeros_like(picked)).reshape(logits.shape[:-1])
+
+
+_LOSS_KIND = {"cross_entropy": 0, "mean_squared_error": 1, "mean_absolute_error": 2,
+              "l1_norm": 3, "l2_norm2": 4}
+
+
+class _SampleLoss(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, a, b, kind):
+        rows = a.shape[0]
+        cols = a.numel() // max(rows, 1)
+        ac = a.contiguous()
+        bc = b.contiguous() if b is not None else None
+        out = torch.empty(rows, dtype=torch.float32, device=a.device)
+        native.check(_lib().lb_sample_loss_fwd(ac.data_ptr(), native.ptr(bc), out.data_ptr(), rows,
+                                               cols, kind, native.dtype_code(a.dtype),
+                                               native.stream_ptr()), "lb_sample_loss_fwd")
+        native.count_launch()
+        ctx.save_for_backward(ac, bc)
+        ctx.meta = (kind, rows, cols)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        ac, bc = ctx.saved_tensors
+        kind, rows, cols = ctx.meta
+        da = torch.empty_like(ac) if ctx.needs_input_grad[0] else None
+        db = torch.empty_like(bc) if (bc is not None and ctx.needs_input_grad[1]) else None
+        gc = g.float().contiguous()
+        native.check(_lib().lb_sample_loss_bwd(ac.data_ptr(), native.ptr(bc), gc.data_ptr(),
+                                               native.ptr(da), native.ptr(db), rows, cols, kind,
+                                               native.dtype_code(ac.dtype), native.stream_ptr()),
+                     "lb_sample_loss_bwd")
+        native.count_launch()
+        return da, db, None
+
+
+def sample_loss(kind: str, a, b=None):
+    """One fp32 value per sample (dim 0): cross entropy on probabilities, MSE, MAE, L1, L2^2."""
+    if a.is_cuda and a.dtype in (torch.float16, torch.bfloat16, torch.float32) and \
+            (b is None or (b.dtype == a.dtype and b.shape == a.shape)):
+        return _SampleLoss.apply(a, b, _LOSS_KIND[kind])
+    n = a.shape[0]
+    af = a.float().reshape(n, -1)
+    bf = b.float().reshape(n, -1) if b is not None else None
+    if kind == "cross_entropy":
+        return torch.where(bf > 0, -bf * torch.log(af), torch.zeros_like(af)).sum(1)
+    if kind == "mean_squared_error":
+        return ((af - bf) ** 2).mean(1)
+    if kind == "mean_absolute_error":
+        return (af - bf).abs().mean(1)
+    if kind == "l1_norm":
+        return af.abs().sum(1)
+    return (af * af).sum(1)
+
+
+def topk_accuracy(scores, labels, k: int = 1):
+    """1.0 where the label's score ranks among the k largest of its row (fp32 per row)."""
+    if scores.is_cuda and scores.dtype in (torch.float16, torch.bfloat16, torch.float32):
+        sc = scores.contiguous()
+        cols = sc.shape[-1]
+        rows = sc.numel() // cols
+        lab = labels.reshape(-1).to(torch.int64).contiguous()
+        out = torch.empty(rows, dtype=torch.float32, device=scores.device)
+        native.check(_lib().lb_topk_accuracy(sc.data_ptr(), lab.data_ptr(), out.data_ptr(), rows,
+                                             cols, int(k), native.dtype_code(sc.dtype),
+                                             native.stream_ptr()), "lb_topk_accuracy")
+        native.count_launch()
+        return out.reshape(scores.shape[:-1])
+    C = scores.shape[-1]
+    lab = labels.reshape(-1).long()
+    s = scores.float().reshape(-1, C)
+    v = s.gather(1, lab.clamp(0, C - 1)[:, None])
+    idx = torch.arange(C, device=s.device)[None, :]
+    rank = ((s > v) | ((s == v) & (idx < lab[:, None]))).sum(1)
+    return ((rank < k) & (lab >= 0) & (lab < C)).float().reshape(scores.shape[:-1])

@@ -1,0 +1,268 @@
+"""Flat parameter arena and the fused (single-launch) optimizer step.
+
+``ParameterArena`` lays every weight tensor of a model out in one fp32 buffer (each tensor
+padded to the optimizer's chunk size), with a parallel gradient arena, two optimizer-state
+arenas and an optional 16-bit compute copy.  ``step()`` updates all tensors with one
+kernel launch on CUDA; on CPU it applies the same formulas tensor by tensor.  The update
+rules are the reference's (src/optimizers/{sgd,adam,adagrad,rmsprop}.cu); its per-tensor
+launch structure (one kernel per weight tensor) is not kept.
+"""
+from __future__ import annotations
+
+import math
+import struct
+from typing import Dict, List, Optional
+
+import torch
+
+from . import native
+from .native import c_float, c_int, c_ll, c_void_p
+
+KIND = {"sgd": 0, "adam": 1, "adagrad": 2, "rmsprop": 3, "none": -1}
+_SEG_FMT = "<qqiiffffffffff"  # 64 bytes, mirrors OptSegment in csrc/optim.cu
+assert struct.calcsize(_SEG_FMT) == 64
+_configured = False
+
+
+def _lib():
+    global _configured
+    lib = native.cuda_lib()
+    if not _configured:
+        lib.lb_fused_optimizer.restype = c_int
+        lib.lb_fused_optimizer.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_int, c_ll, c_float, c_void_p, c_void_p,
+                                           c_void_p, c_int, c_int, c_void_p]
+        lib.lb_unscale_check.restype = c_int
+        lib.lb_unscale_check.argtypes = [c_void_p, c_ll, c_float, c_int, c_void_p, c_int, c_void_p]
+        lib.lb_sqnorm.restype = c_int
+        lib.lb_sqnorm.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_void_p]
+        lib.lb_cast_scale.restype = c_int
+        lib.lb_cast_scale.argtypes = [c_void_p, c_void_p, c_ll, c_float, c_int, c_int, c_void_p]
+        lib.lb_opt_chunk.restype = c_int
+        _configured = True
+    return lib
+
+
+CHUNK = 1024
+
+
+class Slot:
+    """One weight tensor's place in the arena plus its optimizer hyper-parameters."""
+
+    def __init__(self, name: str, shape, offset: int):
+        self.name = name
+        self.shape = tuple(shape)
+        self.count = int(math.prod(self.shape)) if self.shape else 1
+        self.offset = offset
+        self.kind = "none"
+        self.hp: Dict[str, float] = {}
+        self.step_count = 0
+        self.l2 = 0.0
+
+    def segment_bytes(self) -> bytes:
+        hp = self.hp
+        kind = KIND[self.kind]
+        lr = float(hp.get("learn_rate", 0.0))
+        p0 = p1 = eps = wd = corr = 0.0
+        nesterov = 0
+        if self.kind == "sgd":
+            p0 = float(hp.get("momentum", 0.0))
+            nesterov = int(bool(hp.get("nesterov", False)))
+        elif self.kind == "adam":
+            p0, p1 = float(hp.get("beta1", 0.9)), float(hp.get("beta2", 0.99))
+            eps = float(hp.get("eps", 1e-8))
+            wd = float(hp.get("adamw_weight_decay", 0.0))
+        elif self.kind == "adagrad":
+            eps = float(hp.get("eps", 1e-8))
+        elif self.kind == "rmsprop":
+            p0 = float(hp.get("decay_rate", 0.9))
+            eps = float(hp.get("eps", 1e-8))
+        return struct.pack(_SEG_FMT, self.offset, self.count, kind, nesterov, lr, p0, p1, eps, wd,
+                           corr, float(self.l2), 0.0, 0.0, 0.0)
+
+
+class ParameterArena:
+    def __init__(self, device: torch.device, compute_dtype: Optional[torch.dtype] = None,
+                 grad_dtype: torch.dtype = torch.float32, allocator=None):
+        self.device = torch.device(device)
+        self.compute_dtype = compute_dtype
+        self.grad_dtype = grad_dtype
+        self.slots: List[Slot] = []
+        self.total = 0
+        self.allocator = allocator  # callable(nelem, dtype) -> tensor (e.g. symmetric memory)
+        self.master = self.grad = self.state0 = self.state1 = self.compute = None
+        self._seg_dev = None
+        self._seg_stage = []
+        self._seg_key = None
+        self.step_dev = None      # int32[1] on the device: optimizer step number
+        self.lr_scale_dev = None  # float32[1] on the device: global learning-rate multiplier
+
+    # ---- layout
+    def reserve(self, name: str, shape) -> Slot:
+        if self.master is not None:
+            raise RuntimeError("arena already materialised")
+        slot = Slot(name, shape, self.total)
+        self.slots.append(slot)
+        self.total += (slot.count + CHUNK - 1) // CHUNK * CHUNK
+        return slot
+
+    def _alloc(self, dtype):
+        n = max(self.total, CHUNK)
+        if self.allocator is not None:
+            t = self.allocator(n, dtype)
+            t.zero_()
+            return t
+        return torch.zeros(n, dtype=dtype, device=self.device)
+
+    def materialise(self):
+        self.master = self._alloc(torch.float32)
+        self.grad = self._alloc(self.grad_dtype)
+        self.state0 = torch.zeros_like(self.master)
+        self.state1 = None
+        if self.compute_dtype in (torch.float16, torch.bfloat16):
+            self.compute = torch.zeros(self.master.numel(), dtype=self.compute_dtype,
+                                       device=self.device)
+        return self
+
+    def ensure_state1(self):
+        if self.state1 is None:
+            self.state1 = torch.zeros_like(self.master)
+
+    def view(self, buf: torch.Tensor, slot: Slot) -> torch.Tensor:
+        return buf[slot.offset:slot.offset + slot.count].view(slot.shape if slot.shape else (1,))
+
+    def refresh_compute(self):
+        """Re-derive the 16-bit compute copy from the master weights (after init / load)."""
+        if self.compute is None:
+            return
+        if self.master.is_cuda:
+            rc = _lib().lb_cast_scale(self.master.data_ptr(), self.compute.data_ptr(),
+                                      self.master.numel(), 1.0, native.DT_F32,
+                                      native.dtype_code(self.compute.dtype), native.stream_ptr())
+            native.check(rc, "lb_cast_scale")
+            native.count_launch()
+        else:
+            self.compute.copy_(self.master)
+
+    def zero_grad(self):
+        self.grad.zero_()
+
+    # ---- optimizer
+    def _segments(self):
+        blob = b"".join(s.segment_bytes() for s in self.slots)
+        if blob != self._seg_key:
+            self._seg_key = blob
+            if self._seg_dev is None or self._seg_dev.numel() != len(blob):
+                self._seg_dev = torch.empty(len(blob), dtype=torch.uint8, device=self.device)
+                self._seg_stage = []
+            # pinned staging buffers are rotated so an upload in flight is never overwritten
+            if len(self._seg_stage) < 4:
+                stage = (torch.empty(len(blob), dtype=torch.uint8).pin_memory(), torch.cuda.Event())
+                self._seg_stage.append(stage)
+            else:
+                stage = self._seg_stage.pop(0)
+                stage[1].synchronize()
+                self._seg_stage.append(stage)
+            stage[0].copy_(torch.frombuffer(bytearray(blob), dtype=torch.uint8))
+            self._seg_dev.copy_(stage[0], non_blocking=True)
+            stage[1].record()
+        return self._seg_dev
+
+    def step(self, inv_scale: float = 1.0, skip_flag: Optional[torch.Tensor] = None):
+        """Advance every slot's step counter and apply its optimizer."""
+        for s in self.slots:
+            if s.kind != "none":
+                s.step_count += 1
+        if any(s.kind == "adam" for s in self.slots):
+            self.ensure_state1()
+        if self.master.is_cuda:
+            segs = self._segments()
+            if self.step_dev is None:
+                self.step_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
+                self.lr_scale_dev = torch.ones(1, dtype=torch.float32, device=self.device)
+            self.step_dev.add_(1)
+            s1 = self.state1 if self.state1 is not None else self.state0
+            rc = _lib().lb_fused_optimizer(
+                self.master.data_ptr(), self.grad.data_ptr(), self.state0.data_ptr(),
+                s1.data_ptr(), native.ptr(self.compute), segs.data_ptr(), len(self.slots),
+                self.total, float(inv_scale), native.ptr(skip_flag), self.step_dev.data_ptr(),
+                self.lr_scale_dev.data_ptr(), native.dtype_code(self.grad.dtype),
+                native.dtype_code(self.compute.dtype) if self.compute is not None else native.DT_BF16,
+                native.stream_ptr())
+            native.check(rc, "lb_fused_optimizer")
+            native.count_launch()
+            return
+        self._step_cpu(inv_scale)
+
+    @torch.no_grad()
+    def _step_cpu(self, inv_scale: float):
+        for s in self.slots:
+            if s.kind == "none":
+                continue
+            x = self.view(self.master, s)
+            g = self.view(self.grad, s).float() * inv_scale
+            if s.l2:
+                g = g + s.l2 * x
+            hp = s.hp
+            lr = float(hp.get("learn_rate", 0.0))
+            if s.kind == "sgd":
+                mu = float(hp.get("momentum", 0.0))
+                if mu != 0.0:
+                    v = self.view(self.state0, s)
+                    v.mul_(mu).add_(g)
+                    x.sub_(lr * (mu * v + g) if hp.get("nesterov") else lr * v)
+                else:
+                    x.sub_(lr * g)
+            elif s.kind == "adam":
+                b1, b2 = float(hp.get("beta1", 0.9)), float(hp.get("beta2", 0.99))
+                eps = float(hp.get("eps", 1e-8))
+                wd = float(hp.get("adamw_weight_decay", 0.0))
+                t = s.step_count
+                corr = lr * math.sqrt(1.0 - b2 ** t) / (1.0 - b1 ** t)
+                m1, m2 = self.view(self.state0, s), self.view(self.state1, s)
+                ok = torch.isfinite(g)
+                gz = torch.where(ok, g, torch.zeros_like(g))
+                nm1 = b1 * m1 + (1 - b1) * gz
+                nm2 = b2 * m2 + (1 - b2) * gz * gz
+                m1.copy_(torch.where(ok, nm1, m1))
+                m2.copy_(torch.where(ok, nm2, m2))
+                upd = corr * (m1 / (m2.sqrt() + eps)) + lr * wd * x
+                x.sub_(torch.where(ok, upd, torch.zeros_like(upd)))
+            elif s.kind == "adagrad":
+                c = self.view(self.state0, s)
+                c.add_(g * g)
+                x.sub_(lr * g / (c.sqrt() + float(hp.get("eps", 1e-8))))
+            elif s.kind == "rmsprop":
+                d = float(hp.get("decay_rate", 0.9))
+                c = self.view(self.state0, s)
+                c.mul_(d).add_((1 - d) * g * g)
+                x.sub_(lr * g / (c.sqrt() + float(hp.get("eps", 1e-8))))
+        if self.compute is not None:
+            self.compute.copy_(self.master)
+
+    # ---- reductions used by AMP / clipping / L2 reporting
+    def grad_sqnorm(self, buf: Optional[torch.Tensor] = None) -> torch.Tensor:
+        buf = self.grad if buf is None else buf
+        if buf.is_cuda:
+            out = torch.zeros(1, dtype=torch.float32, device=buf.device)
+            rc = _lib().lb_sqnorm(buf.data_ptr(), buf.numel(), out.data_ptr(),
+                                  native.dtype_code(buf.dtype), native.stream_ptr())
+            native.check(rc, "lb_sqnorm")
+            native.count_launch()
+            return out
+        return (buf.float() ** 2).sum().reshape(1)
+
+    def unscale_and_check(self, inv_scale: float, flag: torch.Tensor, write_back: bool = True):
+        """grad *= inv_scale (optionally) and flag[0] |= any non-finite value."""
+        if self.grad.is_cuda:
+            rc = _lib().lb_unscale_check(self.grad.data_ptr(), self.grad.numel(), float(inv_scale),
+                                         1 if write_back else 0, flag.data_ptr(),
+                                         native.dtype_code(self.grad.dtype), native.stream_ptr())
+            native.check(rc, "lb_unscale_check")
+            native.count_launch()
+            return
+        g = self.grad.float() * inv_scale
+        if not torch.isfinite(g).all():
+            flag.fill_(1)
+        if write_back:
+            self.grad.copy_(g)

@@ -974,7 +974,7 @@ FILES = [
             'transforms=600 Transform *', 'hdf5_key_data=700 string', 'hdf5_key_labels=701 string',
             'hdf5_key_responses=702 string', 'hdf5_hyperslab_labels=703 bool',
             'num_responses=704 int32', 'data_schema_filename=800 string',
-            'experiment_schema_filename=801 string',
+            'experiment_schema_filename=801 string', 'synth_distribution=2001 string', 'synth_pool_size=2002 int64',
         ]),
         M('PythonDataReader', [
             'module=1 string', 'module_dir=2 string', 'sample_function=3 string',
