@@ -1,0 +1,111 @@
+// Backward of non-overlapping max pooling (window == stride, no padding, input extents
+// divisible by the window) on channels-last tensors, optionally fused with the gradient
+// of a ReLU / leaky-ReLU that produced the pooled tensor:
+//
+//   dx[p] = (p is the first maximum of its window) ? dy[window] * act'(x[p]) : 0
+//
+// One thread owns one window and 8 channels: it reads the window once, finds the arg-max
+// and writes every dx position of the window, so dx is written exactly once and x is read
+// exactly once (the general gather kernel in pool.cu re-scans windows per input element).
+// This is the shape of every pooling layer of CosmoFlow and U-Net
+// (reference: cuDNN pooling backward, src/layers/transform/pooling.cpp:129-176, followed
+// by a separate activation backward kernel).
+#include "common.cuh"
+
+namespace lb {
+
+struct TiledPoolGeom {
+  int N, D, H, W, C;     // input dims
+  int kd, kh, kw;        // window == stride
+};
+
+template <typename T>
+__global__ void pool_bwd_tiled_kernel(const T* __restrict__ x, const T* __restrict__ dy,
+                                      T* __restrict__ dx, TiledPoolGeom g, int act,
+                                      float act_param, long long total) {
+  const int cv = g.C / 8;
+  const int Do = g.D / g.kd, Ho = g.H / g.kh, Wo = g.W / g.kw;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long r = i;
+    const int c8 = r % cv; r /= cv;
+    const int ow = r % Wo; r /= Wo;
+    const int oh = r % Ho; r /= Ho;
+    const int od = r % Do; r /= Do;
+    const long long n = r;
+    float best[8], gy[8], bestx[8];
+    int arg[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { best[j] = -INFINITY; arg[j] = 0; bestx[j] = 0.f; }
+    {
+      uint4 q = *reinterpret_cast<const uint4*>(dy + i * 8);
+      const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) gy[j] = to_f32<T>(e[j]);
+    }
+    const long long base = (((n * g.D + (long long)od * g.kd) * g.H + (long long)oh * g.kh) * g.W +
+                            (long long)ow * g.kw) * g.C + c8 * 8;
+    int pos = 0;
+    for (int a = 0; a < g.kd; ++a)
+      for (int b = 0; b < g.kh; ++b)
+        for (int c = 0; c < g.kw; ++c, ++pos) {
+          const long long off = base + (((long long)a * g.H + b) * g.W + c) * g.C;
+          uint4 q = *reinterpret_cast<const uint4*>(x + off);
+          const T* e = reinterpret_cast<const T*>(&q);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            const float v = to_f32<T>(e[j]);
+            if (v > best[j]) { best[j] = v; arg[j] = pos; }
+          }
+        }
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      float f = 1.f;
+      if (act == kActRelu) f = best[j] > 0.f ? 1.f : 0.f;
+      else if (act == kActLeaky) f = best[j] > 0.f ? 1.f : act_param;
+      gy[j] *= f;
+    }
+    pos = 0;
+    for (int a = 0; a < g.kd; ++a)
+      for (int b = 0; b < g.kh; ++b)
+        for (int c = 0; c < g.kw; ++c, ++pos) {
+          const long long off = base + (((long long)a * g.H + b) * g.W + c) * g.C;
+          uint4 q;
+          T* e = reinterpret_cast<T*>(&q);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) e[j] = from_f32<T>(arg[j] == pos ? gy[j] : 0.f);
+          *reinterpret_cast<uint4*>(dx + off) = q;
+        }
+  }
+}
+
+}  // namespace lb
+
+extern "C" {
+
+// geom: N D H W C kd kh kw (8 ints); x, dx dense NDHWC, dy dense [N][D/kd][H/kh][W/kw][C].
+// act: 0 none, 1 relu, 2 leaky(act_param) - derivative taken from the sign of x.
+int lb_pool_bwd_tiled(const void* x, const void* dy, void* dx, const int* geom, int act,
+                      float act_param, int dtype, void* stream_) {
+  using namespace lb;
+  TiledPoolGeom g;
+  memcpy(&g, geom, sizeof(g));
+  if (g.C % 8 || g.D % g.kd || g.H % g.kh || g.W % g.kw) return -1;
+  const long long total = (long long)g.N * (g.D / g.kd) * (g.H / g.kh) * (g.W / g.kw) * (g.C / 8);
+  if (total <= 0) return 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  const long long blocks = (total + 255) / 256;
+  const long long cap = (long long)lbhost::sm_count() * 32;
+  const int grid = (int)(blocks < cap ? blocks : cap);
+  if (dtype == kBF16)
+    pool_bwd_tiled_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, g, act, act_param, total);
+  else if (dtype == kF16)
+    pool_bwd_tiled_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (const __half*)dy,
+                                                       (__half*)dx, g, act, act_param, total);
+  else
+    return -1;
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -159,6 +159,17 @@ class DataCoordinator:
         gidx = st.order[pos:pos + st.mb]
         mine = self._my_slice(gidx)
         fields = self.fields or list(r.fields())
+        if getattr(self, "cache_collated", False):
+            # Readers that cycle through a fixed pool of samples (synthetic data) keep their
+            # collated, pinned mini-batches; a step then costs only the host-to-device copy.
+            key = (mode, mine.tobytes())
+            cache = self.__dict__.setdefault("_collated", {})
+            if key in cache:
+                out, nbytes = cache[key]
+                st.samples_fetched += len(mine)
+                b = Batch(dict(out), len(gidx), mine, pos + st.mb >= len(st.order), pos)
+                b.h2d_bytes = nbytes if self.device.type == "cuda" else 0
+                return b
         host = r.fetch_batch(mine, fields)
         out = {}
         nbytes = 0
@@ -166,7 +177,9 @@ class DataCoordinator:
             dt = self.field_dtypes.get(f)
             if dt is not None and t.dtype != dt:
                 t = t.to(dt)
-            if self.device.type == "cuda":
+            if self.device.type == "cuda" and getattr(self, "cache_collated", False):
+                out[f] = t.contiguous().pin_memory()
+            elif self.device.type == "cuda":
                 pin = self._pinned_like((mode, f, self._pin_idx % 3), tuple(t.shape), t.dtype)
                 ev = getattr(pin, "_lb_event", None)
                 if ev is not None:
@@ -180,6 +193,8 @@ class DataCoordinator:
         st.samples_fetched += len(mine)
         st.bytes_fetched += nbytes
         st.fetch_seconds += time.perf_counter() - t0
+        if getattr(self, "cache_collated", False):
+            self.__dict__.setdefault("_collated", {})[(mode, mine.tobytes())] = (dict(out), nbytes)
         b = Batch(out, len(gidx), mine, pos + st.mb >= len(st.order), pos)
         b.h2d_bytes = nbytes if self.device.type == "cuda" else 0
         return b

@@ -116,7 +116,7 @@ class Convolution(_ConvBase):
             return [dc.convolution(self, x)]
         y = nn.convolution(x, self.w.handle, None if self.b is None else self.b.handle, self.ksize,
                            self.pad, self.stride, self.dil, self.groups, self.fused_act[0],
-                           self.fused_act[1])
+                           self.fused_act[1], getattr(self, "skip_act_grad", False))
         return [y]
 
 

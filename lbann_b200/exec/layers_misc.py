@@ -240,7 +240,8 @@ class Pooling(ExecLayer):
         dc = self.model.distconv
         if dc is not None and dc.enabled(self):
             return [dc.pooling(self, x)]
-        return [nn.pooling(x, self.k, self.pad, self.stride, self.mode)]
+        act = getattr(self, "bwd_act", (0, 0.0))
+        return [nn.pooling(x, self.k, self.pad, self.stride, self.mode, act[0], act[1])]
 
 
 @register("unpooling")

@@ -299,6 +299,13 @@ class ExecModel:
                 continue
             l.fused_act = act
             c.fused_into_parent = True
+            # conv -> (fused act) -> max pooling: the pooling backward kernel also applies the
+            # activation gradient, so the convolution's backward skips that pass
+            if (l.type == "convolution" and len(c.children) == 1 and c.name not in protected
+                    and c.children[0].type == "pooling" and c.children[0].mode == "max"
+                    and l.cout % 8 == 0 and self.distconv is None):
+                c.children[0].bwd_act = act
+                l.skip_act_grad = True
 
     # ------------------------------------------------------------------ execution
     def forward_prop(self, inputs: Dict[str, torch.Tensor], mode: str = "training",
@@ -392,25 +399,49 @@ class ExecModel:
         for cb in self.callbacks:
             cb.on_optimize_begin(self)
         inv = 1.0
+        skip_flag = None
+        skipped = False
         if self.amp_enabled:
+            # The overflow flag stays on the device: the fused optimizer reads it and skips
+            # the update by itself, so the step needs no host synchronisation.  The host looks
+            # at the flag of the PREVIOUS step (copied asynchronously) to adapt the loss scale,
+            # i.e. the reference's schedule (src/models/model.cpp:1796-1824) with one step of
+            # latency.  CPU runs read the flag directly.
             flag = torch.zeros(1, dtype=torch.int32, device=self.device)
             self.arena.unscale_and_check(1.0 / self.amp_scale, flag, write_back=True)
             if self.parallel is not None:
                 self.parallel.allreduce_max_inplace(flag)
-            if int(flag.item()):
+            skip_flag = flag
+            if self.device.type == "cuda":
+                prev = getattr(self, "_amp_prev", None)
+                overflow = False
+                if prev is not None:
+                    prev[1].synchronize()     # recorded a whole step ago: completes at once
+                    overflow = bool(prev[0].item())
+                host = torch.empty(1, dtype=torch.int32).pin_memory()
+                host.copy_(flag, non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record()
+                self._amp_prev = (host, ev)
+            else:
+                overflow = bool(int(flag.item()))
+                skipped = overflow
+            if overflow:
                 self.amp_scale *= self.amp_backoff
                 self._amp_good_steps = 0
                 self._amp_skipped += 1
                 if self._amp_skipped >= 10 and (self.comm is None or self.comm.am_world_master()):
                     print(f"WARNING: {self._amp_skipped} consecutive steps skipped by automatic "
                           f"mixed precision; loss scale is now {self.amp_scale}")
+            else:
+                self._amp_skipped = 0
+                self._amp_good_steps += 1
+                if self._amp_good_steps >= self.amp_interval:
+                    self.amp_scale *= self.amp_growth
+                    self._amp_good_steps = 0
+            if skipped:
                 return False
-            self._amp_skipped = 0
-            self._amp_good_steps += 1
-            if self._amp_good_steps >= self.amp_interval:
-                self.amp_scale *= self.amp_growth
-                self._amp_good_steps = 0
-        self.arena.step(inv)
+        self.arena.step(inv, skip_flag if self.device.type == "cuda" else None)
         for w in self.weights:
             w.handle.bump()
         for cb in self.callbacks:
@@ -456,7 +487,13 @@ class ExecModel:
         n = max(st.samples, 1)
         vals = (vals / n).tolist()
         obj = vals[0] + float(self.l2_value())
-        return obj, vals[1:], st.samples
+        mets = vals[1:]
+        for i, m in enumerate(self.metrics):
+            if not getattr(m, "layer_name", None):
+                mets[i] = m.evaluate(self, mode)
+            elif m.unit == "%":
+                mets[i] *= 100.0     # layer metrics in percent (src/metrics/layer_metric.cpp)
+        return obj, mets, st.samples
 
     def reset_statistics(self, mode: str):
         self.stats[mode].reset()

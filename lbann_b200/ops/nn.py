@@ -79,6 +79,15 @@ def _lib():
         lib.lb_topk_accuracy.restype = c_int
         lib.lb_topk_accuracy.argtypes = [c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int, c_int,
                                          c_void_p]
+        lib.lb_pool_bwd_tiled.restype = c_int
+        lib.lb_pool_bwd_tiled.argtypes = [c_void_p, c_void_p, c_void_p, P(c_int), c_int, c_float,
+                                          c_int, c_void_p]
+        lib.lb_conv_c8_fwd.restype = c_int
+        lib.lb_conv_c8_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, P(c_int), P(c_ll),
+                                       P(c_ll), c_int, c_int, c_int, c_float, c_void_p]
+        lib.lb_conv_c8_wgrad.restype = c_int
+        lib.lb_conv_c8_wgrad.argtypes = [c_void_p, c_void_p, c_void_p, P(c_int), P(c_ll), P(c_ll),
+                                         c_ll, c_ll, c_ll, c_int, c_int, c_float, c_void_p]
         _configured = True
     return lib
 
@@ -234,7 +243,7 @@ def _upsample_zero(dy_cl: torch.Tensor, stride, out_dims) -> torch.Tensor:
 
 class _Conv(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w_leaf, b_leaf, wh, bh, ksize, pad, stride, dil, act, act_p):
+    def forward(ctx, x, w_leaf, b_leaf, wh, bh, ksize, pad, stride, dil, act, act_p, skip_act_grad):
         ndim = x.dim()
         x_cl = _pad_channels(_cl_view(x))
         Kout, Cin = wh.master.shape[0], wh.master.shape[1]
@@ -255,7 +264,7 @@ class _Conv(torch.autograd.Function):
                 bias = F.pad(bias, (0, Kp - Kout))
         y = conv_fwd(x_cl, wt, ksize, pad=pad, stride=stride, dilation=dil, bias=bias, act=act,
                      act_param=act_p)
-        ctx.save_for_backward(x_cl, y if act != native.ACT_NONE else None)
+        ctx.save_for_backward(x_cl, y if (act != native.ACT_NONE and not skip_act_grad) else None)
         ctx.meta = (wh, bh, ksize, pad, stride, dil, act, act_p, ndim, Kout, Cin, Kp, Cp)
         out = y[..., :Kout] if Kp != Kout else y
         return _from_cl(out, ndim)
@@ -296,17 +305,98 @@ class _Conv(torch.autograd.Function):
                 wh.grad.add_(tmp[:Kout, :Cin].reshape(wh.grad.shape))
         if bh is not None and bh.grad is not None:
             bh.grad.add_(column_sums(dy_cl.reshape(-1, dy_cl.shape[-1]))[:Kout])
-        return (dx,) + (None,) * 10
+        return (dx,) + (None,) * 11
+
+
+class _ConvC8(torch.autograd.Function):
+    """First-layer convolution: at most 8 input channels, kernel (kd, kh, 3), stride 1, no
+    dilation, "same" padding along W.  Forward and filter gradient use the dedicated
+    16-bytes-per-pixel tcgen05 kernels (csrc/conv_c8_tc.cu); the data gradient, when one is
+    needed at all, goes through the generic path."""
+
+    @staticmethod
+    def forward(ctx, x, w_leaf, b_leaf, wh, bh, ksize, pad, act, act_p, skip_act_grad):
+        ndim = x.dim()
+        x_cl = _cl_view(x)
+        Cin = x_cl.shape[-1]
+        if Cin != 8:
+            x_cl = F.pad(x_cl, (0, 8 - Cin))
+        if not x_cl.is_contiguous():
+            x_cl = x_cl.contiguous()
+        Kout = wh.master.shape[0]
+        kd, kh, _ = ksize
+
+        def pack():
+            w = wh.master.detach().reshape(Kout, Cin, kd * kh, 3)          # K, C, tap2, kw
+            w = F.pad(w, (0, 1, 0, 0, 0, 8 - Cin))                          # K, 8, tap2, 4
+            return w.permute(2, 0, 3, 1).reshape(kd * kh, Kout, 32).contiguous().to(x.dtype)
+
+        wt = wh.packed("c8fwd", x.dtype, pack)
+        N, D, H, W, _ = x_cl.shape
+        y = torch.empty((N, D, H, W, Kout), dtype=x.dtype, device=x.device)
+        geom = (c_int * 9)(N, D, H, W, Kout, kd, kh, pad[0], pad[1])
+        xs = (c_ll * 4)(x_cl.stride(0), x_cl.stride(1), x_cl.stride(2), x_cl.stride(3))
+        ys = (c_ll * 4)(y.stride(0), y.stride(1), y.stride(2), y.stride(3))
+        bias = bh.master.detach() if bh is not None else None
+        native.check(_lib().lb_conv_c8_fwd(x_cl.data_ptr(), wt.data_ptr(), y.data_ptr(),
+                                           native.ptr(bias), geom, xs, ys,
+                                           native.dtype_code(x.dtype), native.dtype_code(x.dtype),
+                                           int(act), float(act_p), native.stream_ptr()),
+                     "lb_conv_c8_fwd")
+        native.count_launch()
+        ctx.save_for_backward(x_cl, y if (act != native.ACT_NONE and not skip_act_grad) else None)
+        ctx.meta = (wh, bh, ksize, pad, act, act_p, ndim, Kout, Cin, geom, xs)
+        return _from_cl(y, ndim)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_cl, y = ctx.saved_tensors
+        wh, bh, ksize, pad, act, act_p, ndim, Kout, Cin, geom, xs = ctx.meta
+        dy_cl = _cl_view(dy)
+        if not dy_cl.is_contiguous():
+            dy_cl = dy_cl.contiguous()
+        if y is not None:
+            dy_cl = _act_grad_from_output(y, dy_cl, act, act_p)
+        dx = None
+        if ctx.needs_input_grad[0]:
+            def pack_bwd():
+                w = F.pad(wh.master.detach().reshape(Kout, Cin, -1), (0, 0, 0, 8 - Cin))
+                return pack_filter(w.reshape(Kout, 8, *ksize), dy.dtype, for_dgrad=True)
+            wt = wh.packed("dgrad", dy.dtype, pack_bwd)
+            bpad = tuple(k - 1 - p for k, p in zip(ksize, pad))
+            N, D, H, W, _ = x_cl.shape
+            dx_cl = conv_fwd(dy_cl, wt, ksize, pad=bpad, stride=1, out_dims=(D, H, W))
+            dx = _from_cl(dx_cl[..., :Cin], ndim)
+        if wh.grad is not None:
+            taps = ksize[0] * ksize[1] * 3
+            ys = (c_ll * 4)(dy_cl.stride(0), dy_cl.stride(1), dy_cl.stride(2), dy_cl.stride(3))
+            native.check(_lib().lb_conv_c8_wgrad(x_cl.data_ptr(), dy_cl.data_ptr(),
+                                                 wh.grad.data_ptr(), geom, xs, ys, 1, Cin * taps,
+                                                 taps, Cin, native.dtype_code(x_cl.dtype), 1.0,
+                                                 native.stream_ptr()), "lb_conv_c8_wgrad")
+            native.count_launch()
+        if bh is not None and bh.grad is not None:
+            bh.grad.add_(column_sums(dy_cl.reshape(-1, Kout)))
+        return (dx,) + (None,) * 9
 
 
 def convolution(x, wh: WeightHandle, bh: Optional[WeightHandle], ksize, pad, stride, dilation,
-                groups: int = 1, act: int = native.ACT_NONE, act_param: float = 0.0):
-    """N-d convolution on a logical [N, C, spatial...] tensor; kernel Kout x C/groups x k..."""
+                groups: int = 1, act: int = native.ACT_NONE, act_param: float = 0.0,
+                skip_act_grad: bool = False):
+    """N-d convolution on a logical [N, C, spatial...] tensor; kernel Kout x C/groups x k...
+    ``skip_act_grad``: the consumer applies the fused activation's gradient itself."""
     nsp = x.dim() - 2
     if _native_ok(x) and groups == 1 and act in (native.ACT_NONE, native.ACT_RELU, native.ACT_LEAKY):
         k3, p3, s3, d3 = norm3(ksize, 1), norm3(pad, 0), norm3(stride, 1), norm3(dilation, 1)
+        Kout, Cin = wh.master.shape[0], wh.master.shape[1]
+        if (Cin <= 8 and k3[2] == 3 and p3[2] == 1 and s3 == (1, 1, 1) and d3 == (1, 1, 1)
+                and Kout <= 64 and Kout % 8 == 0 and k3[0] * k3[1] * max(32, Kout) <= 512
+                and 2 * p3[0] == k3[0] - 1 and 2 * p3[1] == k3[1] - 1
+                and wh.grad is not None and wh.grad.is_contiguous()):
+            return _ConvC8.apply(x, wh.master, bh.master if bh is not None else None, wh, bh, k3,
+                                 p3, act, float(act_param), bool(skip_act_grad))
         return _Conv.apply(x, wh.master, bh.master if bh is not None else None, wh, bh, k3, p3, s3,
-                           d3, act, float(act_param))
+                           d3, act, float(act_param), bool(skip_act_grad))
     w = wh.master if wh.master.dtype == x.dtype else wh.master.to(x.dtype)
     b = None if bh is None else (bh.master if bh.master.dtype == x.dtype else bh.master.to(x.dtype))
     fn = {1: F.conv1d, 2: F.conv2d, 3: F.conv3d}[nsp]
@@ -377,9 +467,11 @@ _POOL_MODE = {"max": 0, "average": 1, "average_no_pad": 2}
 
 class _Pool(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, ksize, pad, stride, mode):
+    def forward(ctx, x, ksize, pad, stride, mode, bwd_act, bwd_act_p):
         ndim = x.dim()
         x_cl = _cl_view(x)
+        ctx.bwd_act = (bwd_act, bwd_act_p)
+        ctx.win = (ksize, pad, stride, mode)
         N, D, H, W, C = x_cl.shape
         Do, Ho, Wo = (out_size(D, ksize[0], pad[0], stride[0], 1),
                       out_size(H, ksize[1], pad[1], stride[1], 1),
@@ -403,18 +495,38 @@ class _Pool(torch.autograd.Function):
         if not dy_cl.is_contiguous():
             dy_cl = dy_cl.contiguous()
         dx = torch.empty(x_cl.shape, dtype=x_cl.dtype, device=x_cl.device)
+        ksize, pad, stride, mode = ctx.win
+        N, D, H, W, C = x_cl.shape
+        tiled = (mode == 0 and ksize == stride and pad == (0, 0, 0) and x_cl.is_contiguous()
+                 and D % ksize[0] == 0 and H % ksize[1] == 0 and W % ksize[2] == 0)
+        if tiled:
+            tg = (c_int * 8)(N, D, H, W, C, *ksize)
+            rc = _lib().lb_pool_bwd_tiled(x_cl.data_ptr(), dy_cl.data_ptr(), dx.data_ptr(), tg,
+                                          int(ctx.bwd_act[0]), float(ctx.bwd_act[1]),
+                                          native.dtype_code(x_cl.dtype), native.stream_ptr())
+            native.check(rc, "lb_pool_bwd_tiled")
+            native.count_launch()
+            return _from_cl(dx, ndim), None, None, None, None, None, None
         xs = (c_ll * 4)(x_cl.stride(0), x_cl.stride(1), x_cl.stride(2), x_cl.stride(3))
         rc = _lib().lb_pool_bwd(x_cl.data_ptr(), dy_cl.data_ptr(), dx.data_ptr(), geom, xs,
                                 native.dtype_code(x_cl.dtype), native.stream_ptr())
         native.check(rc, "lb_pool_bwd")
         native.count_launch()
-        return _from_cl(dx, ndim), None, None, None, None
+        if ctx.bwd_act[0] != native.ACT_NONE:
+            dx = _act_grad_from_output(x_cl, dx, ctx.bwd_act[0], ctx.bwd_act[1])
+        return _from_cl(dx, ndim), None, None, None, None, None, None
 
 
-def pooling(x, ksize, pad, stride, mode: str):
+def pooling(x, ksize, pad, stride, mode: str, bwd_act: int = native.ACT_NONE,
+            bwd_act_param: float = 0.0):
+    """``bwd_act``: also apply the gradient of that activation (taken from the sign of x) in
+    the backward pass - used when the producer fused the activation into its epilogue."""
     nsp = x.dim() - 2
     if _native_ok(x) and x.shape[1] % 8 == 0:
-        return _Pool.apply(x, norm3(ksize, 1), norm3(pad, 0), norm3(stride, 1), _POOL_MODE[mode])
+        return _Pool.apply(x, norm3(ksize, 1), norm3(pad, 0), norm3(stride, 1), _POOL_MODE[mode],
+                           int(bwd_act), float(bwd_act_param))
+    if bwd_act != native.ACT_NONE:
+        raise RuntimeError("pooling: fused activation gradient needs the native path")
     ks, pd, st = tuple(ksize), tuple(pad), tuple(stride)
     if mode == "max":
         return {1: F.max_pool1d, 2: F.max_pool2d, 3: F.max_pool3d}[nsp](x, ks, st, pd)

@@ -181,6 +181,8 @@ class ParameterArena:
                 self.step_dev = torch.zeros(1, dtype=torch.int32, device=self.device)
                 self.lr_scale_dev = torch.ones(1, dtype=torch.float32, device=self.device)
             self.step_dev.add_(1)
+            if skip_flag is not None:
+                self.step_dev.sub_(skip_flag.to(torch.int32))   # a skipped step is not counted
             s1 = self.state1 if self.state1 is not None else self.state0
             rc = _lib().lb_fused_optimizer(
                 self.master.data_ptr(), self.grad.data_ptr(), self.state0.data_ptr(),

@@ -213,3 +213,7 @@ def message_class(name: str):
     for p in parts[1:]:
         cls = getattr(cls, p)
     return cls
+
+
+from . import serialize  # noqa: E402,F401
+from .serialize import save_prototext  # noqa: E402,F401

@@ -1,0 +1,147 @@
+"""Native differentiable ops (ops/nn.py) against PyTorch fp32 autograd on the same inputs."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+from lbann_b200.ops import native, nn
+
+pytestmark = pytest.mark.gpu
+
+
+def _handle(t):
+    m = t.clone().float().requires_grad_(True)
+    g = torch.zeros_like(m)
+    return nn.WeightHandle(m, g, None)
+
+
+@pytest.mark.parametrize("shape", [(2, 4, 8, 16, 64), (1, 3, 6, 10, 136), (2, 8, 4, 8, 128), (2, 4, 1, 12, 40)])
+@pytest.mark.parametrize("kout", [32, 16])
+def test_conv_c8_first_layer(shape, kout):
+    N, C, D, H, W = shape
+    torch.manual_seed(0)
+    ks = (1, 3, 3) if D == 1 else (3, 3, 3)
+    pad = (0, 1, 1) if D == 1 else (1, 1, 1)
+    x = torch.randn(N, C, D, H, W, device="cuda").half()
+    w = (torch.randn(kout, C, *ks, device="cuda") / 6).half().float()
+    wh = _handle(w)
+    y = nn.convolution(x, wh, None, ks, pad, (1, 1, 1), (1, 1, 1), act=native.ACT_LEAKY, act_param=0.3)
+    assert native.consume_status() == 0
+    wr = w.clone().requires_grad_(True)
+    ref = F.leaky_relu(F.conv3d(x.float(), wr, None, 1, pad), 0.3)
+    torch.testing.assert_close(y.float(), ref, rtol=1e-2, atol=2e-2)
+    dy = torch.randn_like(ref).half()
+    y.backward(dy)
+    ref.backward(dy.float())
+    assert native.consume_status() == 0
+    scale = (N * D * H * W) ** 0.5
+    torch.testing.assert_close(wh.grad, wr.grad, rtol=2e-2, atol=3e-2 * scale / 8)
+
+
+def test_pool_bwd_tiled_with_fused_activation():
+    torch.manual_seed(1)
+    x = torch.randn(2, 16, 8, 8, 8, device="cuda").half()
+    xr = x.float().requires_grad_(True)
+    xa = x.clone().requires_grad_(True)
+    # x plays the role of an already-activated tensor: derivative from its sign
+    y = nn.pooling(xa, (2, 2, 2), (0, 0, 0), (2, 2, 2), "max", native.ACT_LEAKY, 0.3)
+    ref = F.max_pool3d(xr, 2, 2)
+    torch.testing.assert_close(y.float(), ref)
+    dy = torch.randn_like(ref)
+    y.backward(dy.half())
+    ref.backward(dy.half().float())
+    expect = xr.grad * torch.where(x.float() > 0, 1.0, 0.3)
+    torch.testing.assert_close(xa.grad.float(), expect, rtol=2e-3, atol=2e-3)
+
+
+def test_linear_and_layer_norm_softmax_ce():
+    torch.manual_seed(2)
+    x = torch.randn(64, 256, device="cuda").bfloat16().requires_grad_(True)
+    w = torch.randn(128, 256, device="cuda") / 16
+    b = torch.randn(128, device="cuda")
+    wh, bh = _handle(w.bfloat16().float()), _handle(b)
+    y = nn.linear(x, wh, bh, native.ACT_RELU)
+    xr = x.detach().float().requires_grad_(True)
+    wr = wh.master.detach().clone().requires_grad_(True)
+    br = b.clone().requires_grad_(True)
+    ref = torch.relu(F.linear(xr, wr, br))
+    torch.testing.assert_close(y.float(), ref, rtol=2e-2, atol=3e-2)
+    g = torch.randn_like(ref).bfloat16()
+    y.backward(g)
+    ref.backward(g.float())
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=3e-2, atol=5e-2)
+    torch.testing.assert_close(wh.grad, wr.grad, rtol=3e-2, atol=1e-1)
+    torch.testing.assert_close(bh.grad, br.grad, rtol=3e-2, atol=1e-1)
+
+    z = torch.randn(32, 512, device="cuda").bfloat16().requires_grad_(True)
+    sh, bh2 = _handle(torch.rand(512, device="cuda") + 0.5), _handle(torch.randn(512, device="cuda"))
+    out = nn.layer_norm(z, 512, sh, bh2, 1e-5)
+    zr = z.detach().float().requires_grad_(True)
+    sr, b2r = sh.master.detach().clone().requires_grad_(True), bh2.master.detach().clone().requires_grad_(True)
+    refn = F.layer_norm(zr, (512,), sr, b2r, 1e-5)
+    torch.testing.assert_close(out.float(), refn, rtol=2e-2, atol=3e-2)
+    gn = torch.randn_like(refn).bfloat16()
+    out.backward(gn)
+    refn.backward(gn.float())
+    torch.testing.assert_close(z.grad.float(), zr.grad, rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(sh.grad, sr.grad, rtol=3e-2, atol=1e-1)
+    torch.testing.assert_close(bh2.grad, b2r.grad, rtol=3e-2, atol=1e-1)
+
+    logits = torch.randn(40, 1000, device="cuda").bfloat16().requires_grad_(True)
+    labels = torch.randint(0, 1000, (40,), device="cuda")
+    labels[3] = 5000
+    loss = nn.softmax_cross_entropy(logits, labels)
+    lr = logits.detach().float().requires_grad_(True)
+    ok = labels < 1000
+    refl = F.cross_entropy(lr, labels.clamp(max=999), reduction="none") * ok
+    torch.testing.assert_close(loss, refl, rtol=1e-3, atol=1e-3)
+    loss.sum().backward()
+    refl.sum().backward()
+    torch.testing.assert_close(logits.grad.float(), lr.grad, rtol=2e-2, atol=2e-3)
+
+
+def test_batch_norm_matches_reference_formula():
+    torch.manual_seed(3)
+    x = torch.randn(4, 32, 6, 6, 6, device="cuda").half().requires_grad_(True)
+    sh, bh = _handle(torch.rand(32, device="cuda") + 0.5), _handle(torch.randn(32, device="cuda"))
+    rm, rv = torch.zeros(32, device="cuda"), torch.ones(32, device="cuda")
+    y = nn.batch_norm(x, sh, bh, rm, rv, True, 1e-5, 0.9, True)
+    xr = x.detach().float().requires_grad_(True)
+    s2, b2 = _handle(sh.master.detach()), _handle(bh.master.detach())
+    rm2, rv2 = torch.zeros(32, device="cuda"), torch.ones(32, device="cuda")
+    ref = nn.batch_norm(xr, s2, b2, rm2, rv2, True, 1e-5, 0.9, True)   # PyTorch-composed path (fp32)
+    torch.testing.assert_close(y.float(), ref, rtol=1e-2, atol=2e-2)
+    torch.testing.assert_close(rm, rm2, rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(rv, rv2, rtol=1e-3, atol=1e-3)
+    g = torch.randn_like(ref).half()
+    y.backward(g)
+    ref.backward(g.float())
+    torch.testing.assert_close(x.grad.float(), xr.grad, rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(sh.grad, s2.master.grad, rtol=3e-2, atol=2e-1)
+    torch.testing.assert_close(bh.grad, b2.master.grad, rtol=3e-2, atol=2e-1)
+
+
+def test_fused_optimizer_matches_cpu_formulas():
+    from lbann_b200.ops.optim import ParameterArena
+    torch.manual_seed(4)
+    arenas = []
+    for dev in ("cuda", "cpu"):
+        a = ParameterArena(dev)
+        s1 = a.reserve("a", (300,)); s2 = a.reserve("b", (17, 9)); s3 = a.reserve("c", (5,))
+        a.materialise()
+        s1.kind, s1.hp = "adam", {"learn_rate": 1e-2, "beta1": 0.9, "beta2": 0.95, "eps": 1e-8, "adamw_weight_decay": 0.1}
+        s2.kind, s2.hp = "sgd", {"learn_rate": 0.1, "momentum": 0.9, "nesterov": True}
+        s3.kind, s3.hp = "rmsprop", {"learn_rate": 0.01, "decay_rate": 0.9, "eps": 1e-8}
+        arenas.append(a)
+    g = torch.Generator().manual_seed(0)
+    init = torch.randn(arenas[0].master.numel(), generator=g)
+    for a in arenas:
+        a.master.copy_(init)
+    for step in range(3):
+        grad = torch.randn(arenas[0].master.numel(), generator=g)
+        if step == 1:
+            grad[7] = float("inf")
+        for a in arenas:
+            a.grad.copy_(grad)
+            a.step()
+    torch.cuda.synchronize()
+    torch.testing.assert_close(arenas[0].master.cpu(), arenas[1].master, rtol=1e-5, atol=1e-6)
