@@ -42,6 +42,7 @@ struct ConvC8FwdPolicy {
   struct Params {
     C8Geom g;
     int TW, tiles_w;
+    int half_px;   // pixels per slab box: a multiple of 8 (128 B) so both boxes land aligned
     int num_tiles, k_iters, in_dtype;
     long long o_sn, o_sd, o_sh, o_sw;
     EpiParams epi;
@@ -59,14 +60,21 @@ struct ConvC8FwdPolicy {
     return tl;
   }
   __device__ static uint32_t stage_bytes(const Params& p, const Tile&, int) {
-    return (uint32_t)((p.TW + 8) * 16 + BN * 64);
+    return (uint32_t)(2 * p.half_px * 16 + BN * 64);
   }
   __device__ static void load(const Params& p, const Tile& tl, int k, uint32_t sA, uint32_t sB,
                               uint32_t bar, const CUtensorMap* tmA, const CUtensorMap* tmB) {
     const int a = k / p.g.kh, b = k - a * p.g.kh;
-    // slab of TW + 8 pixels starting one pixel left of the tile (padding by TMA zero fill)
-    tma_load_5d(sA, tmA, bar, 0, tl.w0 - 1, tl.h - p.g.ph + b, tl.d - p.g.pd + a, tl.n);
-    tma_load_3d(sB, tmB, bar, 0, 0, k);   // [32 k-elements][BN rows] of tap-row k
+    // Slab of 2 * half_px >= TW + 3 pixels starting one pixel left of the tile (TMA zero fill
+    // supplies the padding).
+    // The tensor map views the 16-byte pixels as pairs of 8-byte units so that a row of
+    // pixels is ONE long TMA row instead of one 16-byte request per pixel; the slab comes
+    // as two boxes of half_px pixels each; TMA destinations must be 128-byte aligned.
+    const int half = p.half_px;
+    const int h = tl.h - p.g.ph + b, d = tl.d - p.g.pd + a;
+    tma_load_4d(sA, tmA, bar, (tl.w0 - 1) * 2, h, d, tl.n);
+    tma_load_4d(sA + half * 16, tmA, bar, (tl.w0 - 1 + half) * 2, h, d, tl.n);
+    tma_load_2d(sB, tmB, bar, 0, k);      // packed filter of tap-row k: one 2 KB row
   }
   __device__ static uint32_t idesc(const Params& p) {
     return make_idesc_f16(p.in_dtype == kBF16 ? 1u : 0u, 0, 0, kBM, BN);
@@ -77,8 +85,9 @@ struct ConvC8FwdPolicy {
     for (int kk = 0; kk < 2; ++kk) {
       // A: rows 16 B apart (SBO = 8 rows = 128 B), the two 8-element K chunks 16 B apart.
       const uint64_t ad = make_smem_desc(sA + kk * 32, 16, 128, kLayoutNone);
-      // B: [BN][32] K-major rows of 64 B, 64-byte swizzle (as written by TMA)
-      const uint64_t bd = make_smem_desc(sB + kk * 32, 16, 512, kLayoutSw64);
+      // B: un-swizzled core-matrix order [k-chunk(4)][BN rows][8 elements]: rows 16 B apart,
+      // 8-row groups 128 B apart (SBO), K chunks BN*16 B apart (LBO); 2 chunks per UMMA
+      const uint64_t bd = make_smem_desc(sB + kk * 2 * BN * 16, BN * 16, 128, kLayoutNone);
       umma_f16(tmem_acc, ad, bd, idesc, (first && kk == 0) ? 0u : 1u);
     }
   }
@@ -186,7 +195,7 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         const uint32_t bar = smem_u32(&sh.full[s]);
         mbar_expect_tx(bar, (uint32_t)(p.taps2 * kC8SlabPix * 16 + kC8Brick * p.BN * 2));
         // x slab: [kd][kh][80 pixels][8 ch]; dy brick: [64 pixels][BN]
-        tma_load_5d(sA, &tmX, bar, 0, w0 - 1, h - g.ph, d - g.pd, n);
+        tma_load_4d(sA, &tmX, bar, (w0 - 1) * 2, h - g.ph, d - g.pd, n);   // 8-byte units
         tma_load_5d(sB, &tmDy, bar, 0, w0, h, d, n);
       }
       if (!ok || *abort_flag) {
@@ -267,8 +276,8 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
 
 extern "C" {
 
-// x: [N][D][H][W][8] (strides xs in elements, 8 channels contiguous); w: [kd*kh][Kout][32]
-// with element (kw, c) at kw*8 + c and kw = 3 zero; y: [N][D][H][W][Kout] (strides ys).
+// x: [N][D][H][W][8] (strides xs in elements, pixels dense); w: [kd*kh][4 (kw, kw = 3 zero)]
+// [32 (output channel, zero rows beyond Kout)][8 (input channel)]; y: [N][D][H][W][Kout].
 // geom: N D H W Kout kd kh pd ph (9 ints).  kw = 3, pad_w = 1, stride 1.
 int lb_conv_c8_fwd(const void* x, const void* w, void* y, const float* bias, const int* geom,
                    const long long* xs, const long long* ys, int in_dtype, int out_dtype,
@@ -277,28 +286,31 @@ int lb_conv_c8_fwd(const void* x, const void* w, void* y, const float* bias, con
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   C8Geom g;
   memcpy(&g, geom, sizeof(g));
-  if (g.Kout > 64 || g.Kout % 8) return -1;
+  if (g.Kout > 32 || g.Kout % 8) return -1;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -1;
+  if (xs[3] != 8 || (g.W & 1)) return -1;   // dense 8-channel pixels, even width
   const int TW = g.W < 128 ? g.W : 128;
+  const int half_px = (((TW + 3 + 1) / 2) + 7) / 8 * 8;
   CUtensorMap tmA, tmB;
   {
-    uint64_t dims[5] = {8, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.D, (uint64_t)g.N};
-    uint64_t strides[4] = {(uint64_t)xs[3] * 2, (uint64_t)xs[2] * 2, (uint64_t)xs[1] * 2,
-                           (uint64_t)xs[0] * 2};
-    uint32_t box[5] = {8, (uint32_t)(TW + 8), 1, 1, 1};
-    if (!lbhost::encode_tmap(&tmA, in_dtype, 5, x, dims, strides, box, nullptr, 0)) return -1;
+    // pixels viewed as pairs of 8-byte units: one image row = one TMA row of 2 W units
+    uint64_t dims[4] = {(uint64_t)g.W * 2, (uint64_t)g.H, (uint64_t)g.D, (uint64_t)g.N};
+    uint64_t strides[3] = {(uint64_t)xs[2] * 2, (uint64_t)xs[1] * 2, (uint64_t)xs[0] * 2};
+    uint32_t box[4] = {(uint32_t)(half_px * 2), 1, 1, 1};
+    if (!lbhost::encode_tmap(&tmA, kI64, 4, x, dims, strides, box, nullptr, 0)) return -1;
   }
-  const int BN = g.Kout > 32 ? 64 : 32;
+  const int BN = 32;
   {
-    uint64_t dims[3] = {32, (uint64_t)g.Kout, (uint64_t)(g.kd * g.kh)};
-    uint64_t strides[2] = {64, (uint64_t)g.Kout * 64};
-    uint32_t box[3] = {32, (uint32_t)BN, 1};
-    if (!lbhost::encode_tmap(&tmB, in_dtype, 3, w, dims, strides, box, nullptr, 64)) return -1;
+    // packed filter: [kd*kh][4 k-chunks][32 rows][8 elements] = 2 KB per tap-row
+    uint64_t dims[2] = {256, (uint64_t)(g.kd * g.kh)};
+    uint64_t strides[1] = {2048};
+    uint32_t box[2] = {256, 1};
+    if (!lbhost::encode_tmap(&tmB, kI64, 2, w, dims, strides, box, nullptr, 0)) return -1;
   }
 #define LB_LAUNCH(BN_)                                                                 \
   {                                                                                    \
     ConvC8FwdPolicy<BN_>::Params p;                                                    \
-    p.g = g; p.TW = TW; p.tiles_w = (g.W + TW - 1) / TW;                               \
+    p.g = g; p.TW = TW; p.half_px = half_px; p.tiles_w = (g.W + TW - 1) / TW;                             \
     p.num_tiles = p.tiles_w * g.H * g.D * g.N; p.k_iters = g.kd * g.kh;                \
     p.in_dtype = in_dtype;                                                             \
     p.o_sn = ys[0]; p.o_sd = ys[1]; p.o_sh = ys[2]; p.o_sw = ys[3];                    \
@@ -307,7 +319,7 @@ int lb_conv_c8_fwd(const void* x, const void* w, void* y, const float* bias, con
     p.epi.act_param = act_param; p.epi.ldc = ys[3];                                    \
     return launch_c8_fwd<BN_>(tmA, tmB, p, stream);                                    \
   }
-  if (BN == 64) LB_LAUNCH(64)
+  (void)BN;
   LB_LAUNCH(32)
 #undef LB_LAUNCH
 }
@@ -345,11 +357,11 @@ int lb_conv_c8_wgrad(const void* x, const void* dy, float* dW, const int* geom,
   p.s_tap = s_tap; p.s_k = s_k; p.s_c = s_c;
   CUtensorMap tmX, tmDy;
   {
-    uint64_t dims[5] = {8, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.D, (uint64_t)g.N};
-    uint64_t strides[4] = {(uint64_t)xs[3] * 2, (uint64_t)xs[2] * 2, (uint64_t)xs[1] * 2,
-                           (uint64_t)xs[0] * 2};
-    uint32_t box[5] = {8, (uint32_t)kC8SlabPix, (uint32_t)g.kh, (uint32_t)g.kd, 1};
-    if (!lbhost::encode_tmap(&tmX, in_dtype, 5, x, dims, strides, box, nullptr, 0)) return -1;
+    if (xs[3] != 8) return -1;
+    uint64_t dims[4] = {(uint64_t)g.W * 2, (uint64_t)g.H, (uint64_t)g.D, (uint64_t)g.N};
+    uint64_t strides[3] = {(uint64_t)xs[2] * 2, (uint64_t)xs[1] * 2, (uint64_t)xs[0] * 2};
+    uint32_t box[4] = {(uint32_t)kC8SlabPix * 2, (uint32_t)g.kh, (uint32_t)g.kd, 1};
+    if (!lbhost::encode_tmap(&tmX, kI64, 4, x, dims, strides, box, nullptr, 0)) return -1;
   }
   {
     uint64_t dims[5] = {(uint64_t)g.Kout, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.D, (uint64_t)g.N};

@@ -70,6 +70,7 @@ bool encode_tmap(CUtensorMap* out, int dtype, int rank, const void* base, const 
   CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   if (dtype == lb::kF16) dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   if (dtype == lb::kF32) dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;
+  if (dtype == lb::kI64) dt = CU_TENSOR_MAP_DATA_TYPE_INT64;
   CUtensorMapSwizzle sw = CU_TENSOR_MAP_SWIZZLE_NONE;
   if (swizzle_bytes == 32) sw = CU_TENSOR_MAP_SWIZZLE_32B;
   if (swizzle_bytes == 64) sw = CU_TENSOR_MAP_SWIZZLE_64B;

@@ -318,6 +318,7 @@ class ExecModel:
         self._global_mb = global_mini_batch_size or self.current_mini_batch_size * dp
         self._mb_offset = mini_batch_offset
         acts = {}
+        self.acts = acts          # visible to callbacks while it fills up
         cbs = self.callbacks
         occurrence = defaultdict(int)
         for layer in self.layers:

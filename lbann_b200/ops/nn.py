@@ -328,8 +328,9 @@ class _ConvC8(torch.autograd.Function):
 
         def pack():
             w = wh.master.detach().reshape(Kout, Cin, kd * kh, 3)          # K, C, tap2, kw
-            w = F.pad(w, (0, 1, 0, 0, 0, 8 - Cin))                          # K, 8, tap2, 4
-            return w.permute(2, 0, 3, 1).reshape(kd * kh, Kout, 32).contiguous().to(x.dtype)
+            w = F.pad(w, (0, 1, 0, 0, 0, 8 - Cin, 0, 32 - Kout))            # 32, 8, tap2, 4
+            # core-matrix order of the un-swizzled B operand: [tap2][kw][row][channel]
+            return w.permute(2, 3, 0, 1).contiguous().to(x.dtype)
 
         wt = wh.packed("c8fwd", x.dtype, pack)
         N, D, H, W, _ = x_cl.shape
@@ -390,7 +391,8 @@ def convolution(x, wh: WeightHandle, bh: Optional[WeightHandle], ksize, pad, str
         k3, p3, s3, d3 = norm3(ksize, 1), norm3(pad, 0), norm3(stride, 1), norm3(dilation, 1)
         Kout, Cin = wh.master.shape[0], wh.master.shape[1]
         if (Cin <= 8 and k3[2] == 3 and p3[2] == 1 and s3 == (1, 1, 1) and d3 == (1, 1, 1)
-                and Kout <= 64 and Kout % 8 == 0 and k3[0] * k3[1] * max(32, Kout) <= 512
+                and Kout <= 32 and Kout % 8 == 0 and k3[0] * k3[1] * 32 <= 512
+                and x.shape[-1] % 2 == 0
                 and 2 * p3[0] == k3[0] - 1 and 2 * p3[1] == k3[1] - 1
                 and wh.grad is not None and wh.grad.is_contiguous()):
             return _ConvC8.apply(x, wh.master, bh.master if bh is not None else None, wh, bh, k3,
