@@ -32,13 +32,27 @@ struct C8Geom {
   int Kout;
   int kd, kh;           // kw is 3
   int pd, ph;           // pw is 1
+  int Do;               // output depth = D + 2 pd - kd + 1 (pd = 0 when halos carry the padding)
 };
 
 // ------------------------------------------------------------------------- forward
+// A stage holds one (kd, kh) slab (<= 144 pixels = 2304 B) and its 2 KB filter slice.  The
+// stages are tiny, so the ring is made deep: with ~1 us of load latency it is the number
+// of bytes in flight, not the copy engine, that bounds this kernel.
+template <int BN>
+struct C8StageGeom {
+  static constexpr int kABytes = 2304;
+  static constexpr int kBBytes = BN * 64;
+  static constexpr int kStageBytes = kABytes + kBBytes;     // multiple of 128
+  static constexpr int kStages = 32;
+  static constexpr int kSmemBytes = kStages * kStageBytes + 1024;
+  static constexpr int kTmemCols = 2 * BN < 32 ? 32 : 2 * BN;
+};
+
 template <int BN_>
 struct ConvC8FwdPolicy {
   static constexpr int BN = BN_;
-  using G = StageGeom<BN>;
+  using G = C8StageGeom<BN>;
   struct Params {
     C8Geom g;
     int TW, tiles_w;
@@ -54,7 +68,7 @@ struct ConvC8FwdPolicy {
     int r = t;
     const int tw = r % p.tiles_w; r /= p.tiles_w;
     tl.h = r % p.g.H; r /= p.g.H;
-    tl.d = r % p.g.D; r /= p.g.D;
+    tl.d = r % p.g.Do; r /= p.g.Do;
     tl.n = r;
     tl.w0 = tw * p.TW;
     return tl;
@@ -105,7 +119,7 @@ template <int BN>
 static int launch_c8_fwd(const CUtensorMap& tmA, const CUtensorMap& tmB,
                          typename ConvC8FwdPolicy<BN>::Params p, cudaStream_t stream) {
   using P = ConvC8FwdPolicy<BN>;
-  using G = StageGeom<BN>;
+  using G = typename P::G;
   static bool configured = false;
   if (!configured) {
     cudaFuncSetAttribute(tc_persistent_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize,
@@ -181,7 +195,7 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         int r = b;
         const int bw = r % p.bricks_w; r /= p.bricks_w;
         const int h = r % g.H; r /= g.H;
-        const int d = r % g.D; r /= g.D;
+        const int d = r % g.Do; r /= g.Do;
         const int n = r;
         const int w0 = bw * kC8Brick;
         const uint32_t s = it % S, ph = (it / S) & 1;
@@ -278,7 +292,7 @@ extern "C" {
 
 // x: [N][D][H][W][8] (strides xs in elements, pixels dense); w: [kd*kh][4 (kw, kw = 3 zero)]
 // [32 (output channel, zero rows beyond Kout)][8 (input channel)]; y: [N][D][H][W][Kout].
-// geom: N D H W Kout kd kh pd ph (9 ints).  kw = 3, pad_w = 1, stride 1.
+// geom: N D H W Kout kd kh pd ph Do (10 ints).  kw = 3, pad_w = 1, stride 1.
 int lb_conv_c8_fwd(const void* x, const void* w, void* y, const float* bias, const int* geom,
                    const long long* xs, const long long* ys, int in_dtype, int out_dtype,
                    int act, float act_param, void* stream_) {
@@ -311,7 +325,7 @@ int lb_conv_c8_fwd(const void* x, const void* w, void* y, const float* bias, con
   {                                                                                    \
     ConvC8FwdPolicy<BN_>::Params p;                                                    \
     p.g = g; p.TW = TW; p.half_px = half_px; p.tiles_w = (g.W + TW - 1) / TW;                             \
-    p.num_tiles = p.tiles_w * g.H * g.D * g.N; p.k_iters = g.kd * g.kh;                \
+    p.num_tiles = p.tiles_w * g.H * g.Do * g.N; p.k_iters = g.kd * g.kh;                \
     p.in_dtype = in_dtype;                                                             \
     p.o_sn = ys[0]; p.o_sd = ys[1]; p.o_sh = ys[2]; p.o_sw = ys[3];                    \
     p.epi.C = y; p.epi.bias = bias; p.epi.alpha = 1.f; p.epi.beta = 0.f;               \
@@ -347,7 +361,7 @@ int lb_conv_c8_wgrad(const void* x, const void* dy, float* dW, const int* geom,
   p.stages = 200 * 1024 / p.stage_bytes;
   if (p.stages > 6) p.stages = 6;
   p.bricks_w = (g.W + kC8Brick - 1) / kC8Brick;
-  p.bricks_total = p.bricks_w * g.H * g.D * g.N;
+  p.bricks_total = p.bricks_w * g.H * g.Do * g.N;
   int splits = lbhost::sm_count();
   if (splits > p.bricks_total) splits = p.bricks_total;
   p.splits = splits;
@@ -364,7 +378,7 @@ int lb_conv_c8_wgrad(const void* x, const void* dy, float* dW, const int* geom,
     if (!lbhost::encode_tmap(&tmX, kI64, 4, x, dims, strides, box, nullptr, 0)) return -1;
   }
   {
-    uint64_t dims[5] = {(uint64_t)g.Kout, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.D, (uint64_t)g.N};
+    uint64_t dims[5] = {(uint64_t)g.Kout, (uint64_t)g.W, (uint64_t)g.H, (uint64_t)g.Do, (uint64_t)g.N};
     uint64_t strides[4] = {(uint64_t)ys[3] * 2, (uint64_t)ys[2] * 2, (uint64_t)ys[1] * 2,
                            (uint64_t)ys[0] * 2};
     uint32_t box[5] = {(uint32_t)p.BN, (uint32_t)kC8Brick, 1, 1, 1};

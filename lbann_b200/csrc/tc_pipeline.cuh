@@ -19,7 +19,7 @@ namespace lb {
 constexpr int kBM = 128;       // accumulator rows = TMEM lanes
 constexpr int kBK = 64;        // K elements per pipeline stage (16-bit types)
 constexpr int kTcThreads = 192;
-constexpr int kMaxStages = 8;
+constexpr int kMaxStages = 32;
 
 struct EpiParams {
   void* C;            // output
@@ -59,7 +59,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB,
                      const typename Policy::Params p, int* status) {
   constexpr int BN = Policy::BN;
-  using G = StageGeom<BN>;
+  using G = typename Policy::G;
   constexpr int S = G::kStages;
 
   extern __shared__ uint8_t smem_raw[];

@@ -174,6 +174,9 @@ class DataCoordinator:
         out = {}
         nbytes = 0
         for f, t in host.items():
+            sl = getattr(self, "field_slices", {}).get(f)
+            if sl is not None:      # this rank only needs a slab of the sample (distconv)
+                t = t.narrow(sl[0], sl[1], sl[2] - sl[1])
             dt = self.field_dtypes.get(f)
             if dt is not None and t.dtype != dt:
                 t = t.to(dt)

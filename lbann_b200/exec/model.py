@@ -303,7 +303,7 @@ class ExecModel:
             # activation gradient, so the convolution's backward skips that pass
             if (l.type == "convolution" and len(c.children) == 1 and c.name not in protected
                     and c.children[0].type == "pooling" and c.children[0].mode == "max"
-                    and l.cout % 8 == 0 and self.distconv is None):
+                    and l.cout % 8 == 0):
                 c.children[0].bwd_act = act
                 l.skip_act_grad = True
 
@@ -329,6 +329,8 @@ class ExecModel:
                 k = occ_local[pn]
                 occ_local[pn] += 1
                 xs.append(acts[pn][self._slot(parent, layer, k)])
+            if self.distconv is not None:
+                xs = self.distconv.adapt_inputs(self, layer, xs)
             for cb in cbs:
                 cb.on_layer_forward_begin(self, layer, mode)
             if self.layer_timing:
@@ -342,6 +344,8 @@ class ExecModel:
                 if self.layer_timing:
                     layer.fp_time += time.perf_counter() - t0
             acts[layer.name] = ys
+            if self.distconv is not None:
+                self.distconv.note_outputs(self, layer)
             for cb in cbs:
                 cb.on_layer_forward_end(self, layer, mode)
         self.acts = acts

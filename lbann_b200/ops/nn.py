@@ -334,8 +334,9 @@ class _ConvC8(torch.autograd.Function):
 
         wt = wh.packed("c8fwd", x.dtype, pack)
         N, D, H, W, _ = x_cl.shape
-        y = torch.empty((N, D, H, W, Kout), dtype=x.dtype, device=x.device)
-        geom = (c_int * 9)(N, D, H, W, Kout, kd, kh, pad[0], pad[1])
+        Do = D + 2 * pad[0] - kd + 1
+        y = torch.empty((N, Do, H, W, Kout), dtype=x.dtype, device=x.device)
+        geom = (c_int * 10)(N, D, H, W, Kout, kd, kh, pad[0], pad[1], Do)
         xs = (c_ll * 4)(x_cl.stride(0), x_cl.stride(1), x_cl.stride(2), x_cl.stride(3))
         ys = (c_ll * 4)(y.stride(0), y.stride(1), y.stride(2), y.stride(3))
         bias = bh.master.detach() if bh is not None else None
@@ -393,7 +394,7 @@ def convolution(x, wh: WeightHandle, bh: Optional[WeightHandle], ksize, pad, str
         if (Cin <= 8 and k3[2] == 3 and p3[2] == 1 and s3 == (1, 1, 1) and d3 == (1, 1, 1)
                 and Kout <= 32 and Kout % 8 == 0 and k3[0] * k3[1] * 32 <= 512
                 and x.shape[-1] % 2 == 0
-                and 2 * p3[0] == k3[0] - 1 and 2 * p3[1] == k3[1] - 1
+                and p3[0] in (0, (k3[0] - 1) // 2) and k3[0] % 2 == 1 and 2 * p3[1] == k3[1] - 1
                 and wh.grad is not None and wh.grad.is_contiguous()):
             return _ConvC8.apply(x, wh.master, bh.master if bh is not None else None, wh, bh, k3,
                                  p3, act, float(act_param), bool(skip_act_grad))

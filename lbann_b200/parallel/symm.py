@@ -1,0 +1,217 @@
+"""Symmetric (peer-mapped) buffers and the device-side collectives built on them.
+
+``SymmetricGroup`` covers a set of ranks on one NVSwitch domain.  ``alloc`` gives every
+rank a buffer of the same size and the peer-mapped addresses of all the others; the
+collectives (two-shot / one-shot all-reduce, row puts for halos and shuffles, group
+barrier) are this library's kernels (``csrc/comm_kernels.cu``) working on those addresses
+with peer loads and stores.  On CPU ranks (gloo) and single-rank groups the same methods
+fall back to ``torch.distributed`` / local copies so host-side logic can be tested
+without GPUs.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import List, Optional, Sequence
+
+import torch
+import torch.distributed as dist
+
+from ..ops import native
+from ..ops.native import c_float, c_int, c_ll, c_void_p
+
+_configured = False
+
+
+def _lib():
+    global _configured
+    lib = native.cuda_lib()
+    if not _configured:
+        vpp = ctypes.POINTER(c_void_p)
+        lib.lb_symm_alloc.restype = c_void_p
+        lib.lb_symm_alloc.argtypes = [c_ll]
+        lib.lb_symm_free.argtypes = [c_void_p]
+        lib.lb_ipc_handle_bytes.restype = c_int
+        lib.lb_ipc_get_handle.restype = c_int
+        lib.lb_ipc_get_handle.argtypes = [c_void_p, c_void_p]
+        lib.lb_ipc_open.restype = c_void_p
+        lib.lb_ipc_open.argtypes = [c_void_p]
+        lib.lb_ipc_close.argtypes = [c_void_p]
+        lib.lb_comm_pad_bytes.restype = c_int
+        lib.lb_allreduce_two_shot.restype = c_int
+        lib.lb_allreduce_two_shot.argtypes = [vpp, vpp, c_int, c_int, c_ll, c_float, ctypes.c_uint,
+                                              c_int, c_int, c_void_p]
+        lib.lb_allreduce_one_shot.restype = c_int
+        lib.lb_allreduce_one_shot.argtypes = [vpp, vpp, c_int, c_int, c_void_p, c_void_p, c_int,
+                                              c_int, c_ll, ctypes.c_uint, c_void_p]
+        lib.lb_put_rows.restype = c_int
+        lib.lb_put_rows.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_ll, c_ll, c_void_p]
+        lib.lb_group_barrier.restype = c_int
+        lib.lb_group_barrier.argtypes = [vpp, vpp, c_int, c_int, c_int, ctypes.c_uint, c_void_p]
+        _configured = True
+    return lib
+
+
+class _DevMem:
+    """Exposes a raw device allocation to PyTorch through ``__cuda_array_interface__``."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.ptr, self.nbytes = ptr, nbytes
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1",
+                                         "data": (ptr, False), "version": 3, "strides": None}
+
+
+def tensor_from_ptr(ptr: int, nbytes: int, device) -> torch.Tensor:
+    t = torch.as_tensor(_DevMem(ptr, nbytes), device=device)
+    t._lb_keepalive = True
+    return t
+
+
+class SymmetricBuffer:
+    """One allocation per rank; ``local`` is this rank's bytes, ``peer_ptrs[r]`` the address
+    of rank r's bytes as mapped into this process."""
+
+    def __init__(self, group: "SymmetricGroup", nbytes: int):
+        self.group = group
+        self.nbytes = int(nbytes)
+        dev = group.device
+        if group.native:
+            lib = _lib()
+            ptr = lib.lb_symm_alloc(self.nbytes)
+            if not ptr:
+                raise native.NativeError(f"symmetric allocation of {nbytes} bytes failed")
+            self.ptr = ptr
+            hb = lib.lb_ipc_handle_bytes()
+            handle = ctypes.create_string_buffer(hb)
+            native.check(lib.lb_ipc_get_handle(ptr, handle), "lb_ipc_get_handle")
+            handles = group.gather_object(bytes(handle.raw))
+            self.peer_ptrs: List[int] = []
+            for r, h in enumerate(handles):
+                if r == group.rank:
+                    self.peer_ptrs.append(ptr)
+                else:
+                    p = lib.lb_ipc_open(ctypes.create_string_buffer(h, hb))
+                    if not p:
+                        raise native.NativeError(f"cannot map the symmetric buffer of rank {r}")
+                    self.peer_ptrs.append(p)
+            self.local = tensor_from_ptr(ptr, self.nbytes, dev)
+        else:
+            self.local = torch.zeros(self.nbytes, dtype=torch.uint8, device=dev)
+            self.ptr = self.local.data_ptr()
+            self.peer_ptrs = [self.ptr] * group.world
+        self._c_ptrs = (c_void_p * group.world)(*self.peer_ptrs)
+
+    def view(self, dtype: torch.dtype, numel: Optional[int] = None, offset_bytes: int = 0) -> torch.Tensor:
+        es = torch.empty((), dtype=dtype).element_size()
+        n = (self.nbytes - offset_bytes) // es if numel is None else numel
+        return self.local[offset_bytes:offset_bytes + n * es].view(dtype)
+
+    def peer_ptr(self, r: int, offset_bytes: int = 0) -> int:
+        return self.peer_ptrs[r] + offset_bytes
+
+
+class SymmetricGroup:
+    def __init__(self, device, ranks: Optional[Sequence[int]] = None, pg=None):
+        self.device = torch.device(device)
+        self.pg = pg
+        self.distributed = dist.is_initialized() and (pg is not None or ranks is None or len(ranks) > 1)
+        if self.distributed:
+            self.world = dist.get_world_size(pg) if pg is not None else dist.get_world_size()
+            self.rank = dist.get_rank(pg) if pg is not None else dist.get_rank()
+        else:
+            self.world, self.rank = 1, 0
+        self.native = self.device.type == "cuda" and self.world > 1
+        self.epoch = 0
+        self.pad = None
+        self.staging = None
+        self.bytes_moved = 0
+        if self.native:
+            self.pad = SymmetricBuffer(self, _lib().lb_comm_pad_bytes())
+            self.staging = SymmetricBuffer(self, self.world * 4096 * 4)   # one-shot slots
+            self.barrier_host()
+
+    def gather_object(self, obj):
+        if not self.distributed:
+            return [obj]
+        out = [None] * self.world
+        dist.all_gather_object(out, obj, group=self.pg)
+        return out
+
+    def barrier_host(self):
+        if self.distributed:
+            if self.device.type == "cuda":
+                torch.cuda.synchronize(self.device)
+            dist.barrier(group=self.pg)
+
+    def alloc(self, nbytes: int) -> SymmetricBuffer:
+        b = SymmetricBuffer(self, nbytes)
+        self.barrier_host()
+        return b
+
+    def _next_epoch(self) -> int:
+        self.epoch = (self.epoch + 1) & 0x7FFFFFFF or 1
+        return self.epoch
+
+    # ------------------------------------------------------------------ collectives
+    def allreduce_(self, buf: SymmetricBuffer, dtype: torch.dtype, numel: int, scale: float = 1.0,
+                   offset_bytes: int = 0, blocks: int = 32):
+        """In-place sum over the group of ``numel`` elements at ``offset_bytes`` of ``buf``."""
+        if self.world == 1:
+            if scale != 1.0:
+                buf.view(dtype, numel, offset_bytes).mul_(scale)
+            return
+        if not self.native:
+            t = buf.view(dtype, numel, offset_bytes)
+            dist.all_reduce(t, group=self.pg)
+            if scale != 1.0:
+                t.mul_(scale)
+            return
+        ptrs = (c_void_p * self.world)(*[p + offset_bytes for p in buf.peer_ptrs])
+        rc = _lib().lb_allreduce_two_shot(ptrs, self.pad._c_ptrs, self.rank, self.world, numel,
+                                          float(scale), self._next_epoch(),
+                                          native.dtype_code(dtype), blocks, native.stream_ptr())
+        native.check(rc, "lb_allreduce_two_shot")
+        native.count_launch()
+        es = torch.empty((), dtype=dtype).element_size()
+        self.bytes_moved += 2 * numel * es * (self.world - 1) // self.world
+
+    def allreduce_small_(self, t: torch.Tensor, op: str = "sum"):
+        """In-place all-reduce of a short fp32 tensor (<= 4096 elements) in one kernel."""
+        if self.world == 1:
+            return
+        if not self.native or t.dtype != torch.float32 or t.numel() > 4096 or not t.is_contiguous():
+            o = dist.ReduceOp.SUM if op == "sum" else dist.ReduceOp.MAX
+            if t.dtype in (torch.float32, torch.float64, torch.int32, torch.int64):
+                dist.all_reduce(t, o, group=self.pg)
+            else:
+                f = t.float()
+                dist.all_reduce(f, o, group=self.pg)
+                t.copy_(f)
+            return
+        rc = _lib().lb_allreduce_one_shot(self.staging._c_ptrs, self.pad._c_ptrs, self.rank, self.world,
+                                          t.data_ptr(), t.data_ptr(), t.numel(),
+                                          0 if op == "sum" else 1, 4096, self._next_epoch(),
+                                          native.stream_ptr())
+        native.check(rc, "lb_allreduce_one_shot")
+        native.count_launch()
+        self.bytes_moved += t.numel() * 4 * (self.world - 1)
+
+    def put_rows(self, src: torch.Tensor, dst_buf: SymmetricBuffer, dst_rank: int, dst_offset_bytes: int,
+                 rows: int, row_bytes: int, src_pitch: int, dst_pitch: int):
+        """Copy ``rows`` rows from a local tensor into rank ``dst_rank``'s buffer."""
+        rc = _lib().lb_put_rows(src.data_ptr(), src_pitch, dst_buf.peer_ptr(dst_rank, dst_offset_bytes),
+                                dst_pitch, rows, row_bytes, native.stream_ptr())
+        native.check(rc, "lb_put_rows")
+        native.count_launch()
+        self.bytes_moved += rows * row_bytes
+
+    def barrier_device(self, phase: int = 3):
+        """Stream-ordered rendezvous of the group (no host synchronisation)."""
+        if self.world == 1:
+            return
+        if not self.native:
+            dist.barrier(group=self.pg)
+            return
+        rc = _lib().lb_group_barrier(self.pad._c_ptrs, self.pad._c_ptrs, self.rank, self.world, phase,
+                                     self._next_epoch(), native.stream_ptr())
+        native.check(rc, "lb_group_barrier")
+        native.count_launch()

@@ -1,0 +1,36 @@
+"""Depth-partitioned CosmoFlow on two gloo ranks reproduces the single-process run."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+WORKER = os.path.join(HERE, "_dist_worker.py")
+
+
+def _run(nproc, args, out, env_extra=None, timeout=300):
+    env = dict(os.environ)
+    env.update(env_extra or {})
+    env.setdefault("LBANN_TEST_DEVICE", "cpu")
+    if nproc == 1:
+        cmd = [sys.executable, WORKER] + args[:1] + [out] + args[1:]
+    else:
+        port = 29600 + os.getpid() % 300
+        cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+               "--master-addr", "127.0.0.1", "--master-port", str(port), WORKER] + args[:1] + [out] + args[1:]
+    r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=timeout)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-4000:]
+    with open(out) as f:
+        return json.load(f)
+
+
+def test_distconv_two_ranks_matches_single(tmp_path):
+    single = _run(1, ["cosmoflow", "1", "3"], str(tmp_path / "a.json"))
+    dist = _run(2, ["cosmoflow", "2", "3"], str(tmp_path / "b.json"))
+    assert dist["world"] == 2
+    for a, b in zip(single["losses"], dist["losses"]):
+        assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], dist["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - dist["weight_norms"][k]) <= 1e-3 * max(1.0, abs(v)), k

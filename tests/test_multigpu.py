@@ -1,0 +1,28 @@
+"""Multi-GPU tests (one process per GPU over NCCL + this library's peer-memory kernels)."""
+import os
+
+import pytest
+import torch
+
+from test_distconv_cpu import _run
+
+pytestmark = pytest.mark.gpu
+
+needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+ENV = {"LBANN_TEST_DEVICE": "cuda", "NCCL_NVLS_ENABLE": "0"}
+
+
+@needs2
+def test_symmetric_memory_collectives(tmp_path):
+    n = min(torch.cuda.device_count(), 4)
+    res = _run(n, ["comm"], str(tmp_path / "c.json"), ENV)
+    assert res["native"] and res["world"] == n
+    assert res["all_ranks_ok"], res
+
+
+@needs2
+def test_distconv_two_gpus_matches_one(tmp_path):
+    single = _run(1, ["cosmoflow", "1", "3", "fp16"], str(tmp_path / "a.json"), ENV)
+    dist = _run(2, ["cosmoflow", "2", "3", "fp16"], str(tmp_path / "b.json"), ENV)
+    for a, b in zip(single["losses"], dist["losses"]):
+        assert abs(a - b) <= 3e-2 * max(1.0, abs(a)), (single["losses"], dist["losses"])
