@@ -77,7 +77,9 @@ struct ConvC8FwdPolicy {
     return (uint32_t)(2 * p.half_px * 16 + BN * 64);
   }
   __device__ static void load(const Params& p, const Tile& tl, int k, uint32_t sA, uint32_t sB,
-                              uint32_t bar, const CUtensorMap* tmA, const CUtensorMap* tmB) {
+                              uint32_t bar, const CUtensorMap* tmA, const CUtensorMap* tmB,
+                              int lane) {
+    if (lane > 2) return;
     const int a = k / p.g.kh, b = k - a * p.g.kh;
     // Slab of 2 * half_px >= TW + 3 pixels starting one pixel left of the tile (TMA zero fill
     // supplies the padding).
@@ -86,9 +88,9 @@ struct ConvC8FwdPolicy {
     // as two boxes of half_px pixels each; TMA destinations must be 128-byte aligned.
     const int half = p.half_px;
     const int h = tl.h - p.g.ph + b, d = tl.d - p.g.pd + a;
-    tma_load_4d(sA, tmA, bar, (tl.w0 - 1) * 2, h, d, tl.n);
-    tma_load_4d(sA + half * 16, tmA, bar, (tl.w0 - 1 + half) * 2, h, d, tl.n);
-    tma_load_2d(sB, tmB, bar, 0, k);      // packed filter of tap-row k: one 2 KB row
+    if (lane == 0) tma_load_4d(sA, tmA, bar, (tl.w0 - 1) * 2, h, d, tl.n);
+    if (lane == 1) tma_load_4d(sA + half * 16, tmA, bar, (tl.w0 - 1 + half) * 2, h, d, tl.n);
+    if (lane == 2) tma_load_2d(sB, tmB, bar, 0, k);   // packed filter of tap-row k: one 2 KB row
   }
   __device__ static uint32_t idesc(const Params& p) {
     return make_idesc_f16(p.in_dtype == kBF16 ? 1u : 0u, 0, 0, kBM, BN);

@@ -62,13 +62,17 @@ struct ConvFwdPolicy {
     return (uint32_t)slices_in(p, k) * (uint32_t)((p.rows_used + BN) * p.Cb * 2);
   }
   __device__ static void load(const Params& p, const Tile& tl, int k, uint32_t sA, uint32_t sB,
-                              uint32_t bar, const CUtensorMap* tmA, const CUtensorMap* tmB) {
+                              uint32_t bar, const CUtensorMap* tmA, const CUtensorMap* tmB,
+                              int lane) {
     const ConvGeom& g = p.g;
     const int ns = slices_in(p, k);
-    for (int j = 0; j < ns; ++j) {
-      const int sl = k * p.slices_per_stage + j;
-      const int tap = sl / p.cblocks;
-      const int c0 = (sl - tap * p.cblocks) * p.Cb;
+    // lane 2j issues the activation box of slice j, lane 2j+1 its filter box
+    const int j = lane >> 1;
+    if (j >= ns) return;
+    const int sl = k * p.slices_per_stage + j;
+    const int tap = sl / p.cblocks;
+    const int c0 = (sl - tap * p.cblocks) * p.Cb;
+    if ((lane & 1) == 0) {
       const int a = tap / (g.kh * g.kw);
       const int b = (tap / g.kw) % g.kh;
       const int c = tap % g.kw;
@@ -76,6 +80,7 @@ struct ConvFwdPolicy {
                   tl.w0 * g.sw - g.pw + c * g.dw,
                   tl.h0 * g.sh - g.ph + b * g.dh,
                   tl.d0 * g.sd - g.pd + a * g.dd, tl.n0);
+    } else {
       tma_load_3d(sB + j * (BN * p.Cb * 2), tmB, bar, c0, tl.col0, tap);
     }
   }

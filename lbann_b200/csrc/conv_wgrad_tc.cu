@@ -97,50 +97,60 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   const WgradGeom& g = p.g;
 
   if (warp == 4) {
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int b = split; b < p.bricks_total && ok; b += p.splits, ++it) {
-        int r = b;
-        const int bw = r % p.bricks_w; r /= p.bricks_w;
-        const int bh = r % p.bricks_h; r /= p.bricks_h;
-        const int bd = r % p.bricks_d; r /= p.bricks_d;
-        const int w0 = bw * p.TW, h0 = bh * p.TH, d0 = bd * p.TD, nn0 = r * p.TN;
-        const uint32_t s = it % S, ph = (it / S) & 1;
+    // The whole warp walks the bricks: lane 0 owns the barrier protocol, and the
+    // boxes of one stage go out from different lanes so that they enter the
+    // copy engine side by side instead of one after another.
+    uint32_t it = 0;
+    bool ok = true;
+    // slices this CTA loads per brick (the same for every brick)
+    int nsl = 0;
+    for (int gi = 0; gi < g_count; ++gi)
+      nsl += min(p.spg, p.slices_total - (g_first + gi) * p.spg);
+    const int ndy = p.BN == 32 ? 1 : p.BN / 64;
+    for (int b = split; b < p.bricks_total && ok; b += p.splits, ++it) {
+      int r = b;
+      const int bw = r % p.bricks_w; r /= p.bricks_w;
+      const int bh = r % p.bricks_h; r /= p.bricks_h;
+      const int bd = r % p.bricks_d; r /= p.bricks_d;
+      const int w0 = bw * p.TW, h0 = bh * p.TH, d0 = bd * p.TD, nn0 = r * p.TN;
+      const uint32_t s = it % S, ph = (it / S) & 1;
+      const uint32_t sA = smem_base + s * p.stage_bytes;
+      const uint32_t sB = sA + p.a_bytes;
+      const uint32_t bar = smem_u32(&sh.full[s]);
+      int go = 1;
+      if (lane == 0) {
         if (!mbar_wait_bounded(smem_u32(&sh.empty[s]), ph ^ 1, abort_flag)) {
           raise_status(status, abort_flag, kTimeoutStageEmpty);
-          ok = false;
-          break;
-        }
-        const uint32_t sA = smem_base + s * p.stage_bytes;
-        const uint32_t sB = sA + p.a_bytes;
-        const uint32_t bar = smem_u32(&sh.full[s]);
-        // bytes: every loaded slice brings rows_used * Cb * 2, dy brings rows_used * BN * 2
-        int nsl = 0;
-        for (int gi = 0; gi < g_count; ++gi) {
-          const int first = (g_first + gi) * p.spg;
-          nsl += min(p.spg, p.slices_total - first);
-        }
-        mbar_expect_tx(bar, (uint32_t)(p.rows_used * 2 * (nsl * p.Cb + p.BN)));
-        if (p.BN == 32) {
-          tma_load_5d(sB, &tmDy, bar, n0, w0, h0, d0, nn0);
+          go = 0;
         } else {
-          for (int j = 0; j < p.BN / 64; ++j)
-            tma_load_5d(sB + j * 8192, &tmDy, bar, n0 + j * 64, w0, h0, d0, nn0);
-        }
-        for (int gi = 0; gi < g_count; ++gi) {
-          for (int j = 0; j < p.spg; ++j) {
-            const int sl = (g_first + gi) * p.spg + j;
-            if (sl >= p.slices_total) break;
-            const int tap = sl / p.cblocks;
-            const int c0 = (sl - tap * p.cblocks) * p.Cb;
-            const int ta = tap / (g.kh * g.kw), tb = (tap / g.kw) % g.kh, tc = tap % g.kw;
-            tma_load_5d(sA + gi * 16384 + j * (64 * p.Cb * 2), &tmX, bar, c0,
-                        w0 * g.sw - g.pw + tc * g.dw, h0 * g.sh - g.ph + tb * g.dh,
-                        d0 * g.sd - g.pd + ta * g.dd, nn0);
-          }
+          // every slice brings rows_used * Cb * 2 bytes, dy brings rows_used * BN * 2
+          mbar_expect_tx(bar, (uint32_t)(p.rows_used * 2 * (nsl * p.Cb + p.BN)));
         }
       }
+      go = __shfl_sync(0xffffffffu, go, 0);
+      if (!go) {
+        ok = false;
+        break;
+      }
+      // job q < ndy: a box of dy; job q >= ndy: slice (q - ndy) of this CTA's groups
+      for (int q = lane; q < ndy + g_count * p.spg; q += 32) {
+        if (q < ndy) {
+          tma_load_5d(sB + q * 8192, &tmDy, bar, n0 + q * 64, w0, h0, d0, nn0);
+          continue;
+        }
+        const int gi = (q - ndy) / p.spg, j = (q - ndy) - gi * p.spg;
+        const int sl = (g_first + gi) * p.spg + j;
+        if (sl >= p.slices_total) continue;
+        const int tap = sl / p.cblocks;
+        const int c0 = (sl - tap * p.cblocks) * p.Cb;
+        const int ta = tap / (g.kh * g.kw), tb = (tap / g.kw) % g.kh, tc = tap % g.kw;
+        tma_load_5d(sA + gi * 16384 + j * (64 * p.Cb * 2), &tmX, bar, c0,
+                    w0 * g.sw - g.pw + tc * g.dw, h0 * g.sh - g.ph + tb * g.dh,
+                    d0 * g.sd - g.pd + ta * g.dd, nn0);
+      }
+      __syncwarp();
+    }
+    if (lane == 0) {
       if (!ok || *abort_flag) {
         const uint32_t pending = it < (uint32_t)S ? it : (uint32_t)S;
         for (uint32_t j = 0; j < pending; ++j) {

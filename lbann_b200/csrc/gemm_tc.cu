@@ -45,21 +45,20 @@ struct GemmPolicy {
     return G::kStageBytes;
   }
   __device__ static void load(const Params& p, const Tile& tl, int k, uint32_t sA, uint32_t sB,
-                              uint32_t bar, const CUtensorMap* tmA, const CUtensorMap* tmB) {
+                              uint32_t bar, const CUtensorMap* tmA, const CUtensorMap* tmB,
+                              int lane) {
     const int k0 = k * kBK;
+    // boxes of the A operand go out from lanes 0.., boxes of B from lanes 8..
     if (!p.a_mn) {
-      tma_load_3d(sA, tmA, bar, k0, tl.m0, tl.b);  // box {64 k, 128 rows}
-    } else {
-#pragma unroll
-      for (int j = 0; j < kBM / 64; ++j)           // box {64 m, 64 k-rows}
-        tma_load_3d(sA + j * 8192, tmA, bar, tl.m0 + j * 64, k0, tl.b);
+      if (lane == 0) tma_load_3d(sA, tmA, bar, k0, tl.m0, tl.b);  // box {64 k, 128 rows}
+    } else if (lane < kBM / 64) {                                 // box {64 m, 64 k-rows}
+      tma_load_3d(sA + lane * 8192, tmA, bar, tl.m0 + lane * 64, k0, tl.b);
     }
     if (!p.b_mn) {
-      tma_load_3d(sB, tmB, bar, k0, tl.n0, tl.b);  // box {64 k, BN rows}
-    } else {
-#pragma unroll
-      for (int j = 0; j < BN / 64; ++j)
-        tma_load_3d(sB + j * 8192, tmB, bar, tl.n0 + j * 64, k0, tl.b);
+      if (lane == 8) tma_load_3d(sB, tmB, bar, k0, tl.n0, tl.b);  // box {64 k, BN rows}
+    } else if (lane >= 8 && lane < 8 + BN / 64) {
+      const int j = lane - 8;
+      tma_load_3d(sB + j * 8192, tmB, bar, tl.n0 + j * 64, k0, tl.b);
     }
   }
   __device__ static uint32_t idesc(const Params& p) {

@@ -53,6 +53,19 @@ struct TcShared {
   int abort_flag;
 };
 
+// Per-role timestamps of CTA 0 (development aid, compiled in with -DLB_TRACE):
+// row 0 producer after issuing stage i, row 1 MMA warp after the stage landed, row 2 after
+// its MMAs were issued, row 3 epilogue begin / end per tile.
+#ifdef LB_TRACE
+static __device__ long long lb_trace[4][512];
+#define LB_TRACE_AT(row, idx)                                                        \
+  do {                                                                               \
+    if (blockIdx.x == 0 && (idx) < 512u) lb_trace[row][idx] = clock64();             \
+  } while (0)
+#else
+#define LB_TRACE_AT(row, idx) do {} while (0)
+#endif
+
 template <class Policy>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -100,35 +113,45 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
 
   if (warp == 4) {
     // ------------------------------ producer --------------------------------
-    if (lane == 0) {
-      uint32_t it = 0;
-      bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
-        const typename Policy::Tile tile = Policy::decode(p, t);
-        for (int k = 0; k < k_iters; ++k, ++it) {
-          const uint32_t s = it % S;
-          const uint32_t ph = (it / S) & 1;
-          if (!mbar_wait_bounded(smem_u32(&sh.empty[s]), ph ^ 1, abort_flag)) {
-            raise_status(status, abort_flag, kTimeoutStageEmpty);
-            ok = false;
-            break;
-          }
-          const uint32_t sA = smem_base + s * G::kStageBytes;
-          const uint32_t sB = sA + G::kABytes;
-          const uint32_t bar = smem_u32(&sh.full[s]);
-          mbar_expect_tx(bar, Policy::stage_bytes(p, tile, k));
-          Policy::load(p, tile, k, sA, sB, bar, &tmA, &tmB);
+    // The whole warp runs the loop: lane 0 waits for the stage and arms its barrier, then
+    // every lane may issue one of the stage's TMA boxes (Policy::load picks by lane), so
+    // the boxes of a stage enter the copy engine side by side instead of one after another.
+    uint32_t it = 0;
+    bool ok = true;
+    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+      const typename Policy::Tile tile = Policy::decode(p, t);
+      for (int k = 0; k < k_iters; ++k, ++it) {
+        const uint32_t s = it % S;
+        const uint32_t ph = (it / S) & 1;
+        int good = 1;
+        const uint32_t bar = smem_u32(&sh.full[s]);
+        if (lane == 0) {
+          LB_TRACE_AT(0, 4 * it);
+          good = mbar_wait_bounded(smem_u32(&sh.empty[s]), ph ^ 1, abort_flag) ? 1 : 0;
+          LB_TRACE_AT(0, 4 * it + 1);
+          if (good) mbar_expect_tx(bar, Policy::stage_bytes(p, tile, k));
+          else raise_status(status, abort_flag, kTimeoutStageEmpty);
         }
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) {
+          ok = false;
+          break;
+        }
+        const uint32_t sA = smem_base + s * G::kStageBytes;
+        const uint32_t sB = sA + G::kABytes;
+        if (lane == 0) LB_TRACE_AT(0, 4 * it + 2);
+        Policy::load(p, tile, k, sA, sB, bar, &tmA, &tmB, lane);
+        if (lane == 0) LB_TRACE_AT(0, 4 * it + 3);
       }
-      // Drain: every load this thread issued must have landed before the CTA's shared
-      // memory goes away.  Loads whose consumer already waited have landed; the last
-      // min(it, S) stages may still be in flight if the consumer gave up.
-      if (!ok || *abort_flag) {
-        const uint32_t pending = it < (uint32_t)S ? it : (uint32_t)S;
-        for (uint32_t j = 0; j < pending; ++j) {
-          const uint32_t q = it - 1 - j;
-          mbar_wait_budget_only(smem_u32(&sh.full[q % S]), (q / S) & 1);
-        }
+    }
+    // Drain: every load issued must have landed before the CTA's shared memory goes away.
+    // Loads whose consumer already waited have landed; the last min(it, S) stages may
+    // still be in flight if the consumer gave up.
+    if (lane == 0 && (!ok || *abort_flag)) {
+      const uint32_t pending = it < (uint32_t)S ? it : (uint32_t)S;
+      for (uint32_t j = 0; j < pending; ++j) {
+        const uint32_t q = it - 1 - j;
+        mbar_wait_budget_only(smem_u32(&sh.full[q % S]), (q / S) & 1);
       }
     }
   } else if (warp == 5) {
@@ -157,10 +180,12 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
             break;
           }
           tc_fence_after();
+          LB_TRACE_AT(1, it);
           const uint32_t sA = smem_base + s * G::kStageBytes;
           const uint32_t sB = sA + G::kABytes;
           Policy::mma(p, k, sA, sB, tmem_acc, idesc, /*first=*/k == 0);
           umma_commit(smem_u32(&sh.empty[s]));  // frees the stage when the MMAs retire
+          LB_TRACE_AT(2, it);
         }
         if (ok) umma_commit(smem_u32(&sh.tmem_full[acc]));
       }
@@ -182,6 +207,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         break;
       }
       tc_fence_after();
+      if (threadIdx.x == 0) LB_TRACE_AT(3, 2 * local_tile);
       const int row = warp * 32 + lane;
       long long row_off = 0;
       const bool row_ok = Policy::row_addr(p, tile, row, row_off);
@@ -253,6 +279,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       }
       tc_fence_before();
       __syncwarp();
+      if (threadIdx.x == 0) LB_TRACE_AT(3, 2 * local_tile + 1);
       if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[acc]));
     }
   }

@@ -1,0 +1,179 @@
+"""Single-kernel timing harness: ``python -m lbann_b200.ops.microbench <case> [options]``.
+
+Each case runs one native kernel (or one layer's forward / backward pair) on a
+stated shape, times it with CUDA events on the launching stream after warm-up,
+writes a buffer larger than L2 between timed iterations, and prints one JSON
+line with the algorithmic FLOPs and bytes, the achieved rates and -- when a
+``MEASURED_PEAKS.json`` sits in the working directory -- the fractions of the
+measured copy bandwidth and cuBLAS bf16 throughput.  The same command line is
+what a profiler capture of that kernel wraps.
+
+Cases: ``gemm``, ``conv`` (forward and, with ``--bwd``, data and filter
+gradients; the first-layer kernels are chosen automatically for <= 8 input
+channels), ``pool``, ``optimizer``.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+
+import torch
+
+from . import native
+
+
+def _peaks():
+    try:
+        with open(os.path.join(os.getcwd(), "MEASURED_PEAKS.json")) as f:
+            d = json.load(f)
+        return float(d.get("hbm_gbs", 0.0)), float(d.get("bf16_tflops", 0.0))
+    except (OSError, ValueError):
+        return 0.0, 0.0
+
+
+class _Timer:
+    def __init__(self, iters: int, warmup: int, flush: bool = True):
+        self.iters, self.warmup = iters, warmup
+        self.scratch = torch.empty(192 << 20, dtype=torch.uint8, device="cuda") if flush else None
+
+    def run(self, fn):
+        for _ in range(self.warmup):
+            fn()
+        torch.cuda.synchronize()
+        times = []
+        for _ in range(self.iters):
+            if self.scratch is not None:
+                self.scratch.fill_(1)
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            fn()
+            e1.record()
+            torch.cuda.synchronize()
+            times.append(e0.elapsed_time(e1))
+        times.sort()
+        return times[len(times) // 2], times[0]
+
+
+def _report(name, shape, ms, ms_min, flops, nbytes):
+    hbm, tf = _peaks()
+    out = {"case": name, "shape": shape, "ms_median": round(ms, 4), "ms_min": round(ms_min, 4),
+           "tflops": round(flops / ms / 1e9, 2), "gbs": round(nbytes / ms / 1e6, 1)}
+    if hbm > 0:
+        out["frac_hbm_of_measured"] = round(out["gbs"] / hbm, 3)
+    if tf > 0:
+        out["frac_bf16_of_measured"] = round(out["tflops"] / tf, 3)
+    print(json.dumps(out))
+    return out
+
+
+def _dtype(name):
+    return {"fp16": torch.float16, "bf16": torch.bfloat16}[name]
+
+
+def case_gemm(a, timer):
+    from .gemm import gemm
+    dt = _dtype(a.dtype)
+    A = torch.randn(a.m, a.k, device="cuda", dtype=dt)
+    B = torch.randn(a.n, a.k, device="cuda", dtype=dt)
+    C = torch.empty(a.m, a.n, device="cuda", dtype=dt)
+    ms, mn = timer.run(lambda: gemm(A, B, trans_b=True, out=C))
+    return _report("gemm", [a.m, a.n, a.k], ms, mn, 2.0 * a.m * a.n * a.k,
+                   2.0 * (a.m * a.k + a.n * a.k + a.m * a.n))
+
+
+def case_conv(a, timer):
+    from . import nn
+    dt = _dtype(a.dtype)
+    N, C, K, S, ks = a.batch, a.cin, a.cout, a.size, a.ksize
+    x = torch.randn(N, S, S, S, C, device="cuda", dtype=dt).permute(0, 4, 1, 2, 3)
+    x.requires_grad_(a.bwd and C > 8)
+    w = torch.randn(K, C, ks, ks, ks, device="cuda") * 0.05
+    wh = nn.WeightHandle(w.requires_grad_(True), torch.zeros_like(w))
+    pad = (ks - 1) // 2
+    px = float(N) * S ** 3
+    flops = 2.0 * px * K * C * ks ** 3
+    fwd_bytes = 2.0 * px * (max(C, 8) + K)
+    out = []
+
+    def fwd():
+        return nn.convolution(x, wh, None, (ks,) * 3, (pad,) * 3, (1,) * 3, (1,) * 3,
+                              act=native.ACT_LEAKY if a.act else native.ACT_NONE, act_param=0.3)
+
+    ms, mn = timer.run(fwd)
+    out.append(_report("conv_fwd", [N, C, K, S, ks], ms, mn, flops, fwd_bytes))
+    if a.bwd:
+        y = fwd()
+        dy = torch.randn_like(y)
+
+        def bwd():
+            y.backward(dy, retain_graph=True)
+
+        ms, mn = timer.run(bwd)
+        nmm = 2 if x.requires_grad else 1
+        out.append(_report("conv_bwd(dgrad+wgrad)" if nmm == 2 else "conv_bwd(wgrad)",
+                           [N, C, K, S, ks], ms, mn, nmm * flops, nmm * fwd_bytes))
+    return out
+
+
+def case_pool(a, timer):
+    from . import nn
+    dt = _dtype(a.dtype)
+    N, C, S = a.batch, a.cin, a.size
+    x = torch.randn(N, S, S, S, C, device="cuda", dtype=dt).permute(0, 4, 1, 2, 3)
+    x.requires_grad_(True)
+    px = float(N) * S ** 3 * C
+    ms, mn = timer.run(lambda: nn.pooling(x, 2, 0, 2, "max"))
+    out = [_report("pool_fwd", [N, C, S], ms, mn, 0.0, 2.0 * px * (1 + 1 / 8))]
+    if a.bwd:
+        y = nn.pooling(x, 2, 0, 2, "max")
+        dy = torch.randn_like(y)
+        ms, mn = timer.run(lambda: y.backward(dy, retain_graph=True))
+        out.append(_report("pool_bwd", [N, C, S], ms, mn, 0.0, 2.0 * px * (2 + 1 / 8)))
+    return out
+
+
+def case_optimizer(a, timer):
+    from .optim import ParameterArena
+    arena = ParameterArena(torch.device("cuda"), _dtype(a.dtype))
+    n = a.m * a.k
+    slot = arena.reserve("w", (a.m, a.k))
+    arena.materialise()
+    slot.kind = a.opt
+    slot.hp = {"learn_rate": 1e-3, "beta1": 0.9, "beta2": 0.999, "eps": 1e-8, "momentum": 0.9}
+    arena.grad.normal_()
+    ms, mn = timer.run(lambda: arena.step())
+    states = {"sgd": 1, "adam": 2}.get(a.opt, 2)
+    return _report(f"optimizer_{a.opt}", [n], ms, mn, 0.0,
+                   4.0 * n * (2 + 2 * states + 1) + 2.0 * n)
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("case", choices=["gemm", "conv", "pool", "optimizer"])
+    ap.add_argument("--dtype", default="bf16", choices=["fp16", "bf16"])
+    ap.add_argument("--m", type=int, default=8192)
+    ap.add_argument("--n", type=int, default=8192)
+    ap.add_argument("--k", type=int, default=8192)
+    ap.add_argument("--batch", type=int, default=1)
+    ap.add_argument("--cin", type=int, default=32)
+    ap.add_argument("--cout", type=int, default=64)
+    ap.add_argument("--size", type=int, default=64)
+    ap.add_argument("--ksize", type=int, default=3)
+    ap.add_argument("--act", action="store_true")
+    ap.add_argument("--bwd", action="store_true")
+    ap.add_argument("--opt", default="adam")
+    ap.add_argument("--iters", type=int, default=10)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--no-flush", action="store_true")
+    a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("microbench needs a GPU")
+    timer = _Timer(a.iters, a.warmup, flush=not a.no_flush)
+    {"gemm": case_gemm, "conv": case_conv, "pool": case_pool, "optimizer": case_optimizer}[a.case](
+        a, timer)
+    native.consume_status()
+
+
+if __name__ == "__main__":
+    main()
