@@ -12,18 +12,10 @@
 //
 // Stands in for the cuDNN calls of the reference's base_convolution layer
 // (src/layers/learning/base_convolution.cpp:462-814).
+#include "conv_geom.cuh"
 #include "tc_pipeline.cuh"
 
 namespace lb {
-
-struct ConvGeom {
-  int N, D, H, W, C;
-  int Do, Ho, Wo, Kout;
-  int kd, kh, kw;
-  int pd, ph, pw;
-  int sd, sh, sw;
-  int dd, dh, dw;
-};
 
 template <int BN_>
 struct ConvFwdPolicy {
@@ -166,6 +158,14 @@ int lb_conv_fwd_tc(const void* x, const void* w, void* y, const float* bias, con
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -1;
   for (int i = 0; i < 4; ++i)
     if (xs[i] % 8) return -1;
+
+  // Stride-1 convolutions whose whole filter fits in shared memory take the halo-slab
+  // kernel: one TMA box per (tile, filter plane) instead of one per tap.
+  {
+    const int rc = lb_conv_slab_fwd(x, w, y, bias, geom, xs, ys, in_dtype, out_dtype, alpha, beta,
+                                    act, act_param, stream_);
+    if (rc != -2) return rc;
+  }
 
   const int Cb = g.C >= 64 ? 64 : (g.C >= 32 ? 32 : 16);
   const int TW = largest_tile(g.Wo, 128);

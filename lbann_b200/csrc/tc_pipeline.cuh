@@ -66,6 +66,108 @@ static __device__ long long lb_trace[4][512];
 #define LB_TRACE_AT(row, idx) do {} while (0)
 #endif
 
+// Epilogue of one accumulator tile for one warp: reads this warp's 32 TMEM lanes in
+// chunks of 32 columns, applies alpha / bias / beta / activation and stores the row.
+// The activation kind is switched on ONCE per chunk, outside the element loops: a switch
+// inside a 32-way unrolled loop made 32 copies of every activation's code, and walking
+// that much code (instruction-cache misses, 32 indirect branches) cost ~200 cycles per
+// element.
+__device__ __forceinline__ void tc_apply_act32(float (&v)[32], int act, float prm) {
+  switch (act) {
+    case kActNone:
+      break;
+    case kActRelu:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+      break;
+    case kActLeaky:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = v[j] > 0.f ? v[j] : prm * v[j];
+      break;
+    default:
+#pragma unroll
+      for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], act, prm);
+      break;
+  }
+}
+
+template <int BN>
+__device__ __forceinline__ void tc_epilogue_rows(uint32_t taddr, bool row_ok, long long row_off,
+                                                 int n0, int n_total, int row_index,
+                                                 const EpiParams& e, unsigned lb_trace_tile = 0) {
+  const float alpha = e.alpha, beta = e.beta;
+  const int bias_mode = e.bias_mode, act = e.act, out_dtype = e.out_dtype;
+  const float row_bias = bias_mode == 2 ? e.bias[row_index] : 0.f;
+#pragma unroll 1
+  for (int c = 0; c < BN; c += 32) {
+    if (n0 + c >= n_total) break;  // warp-uniform
+    uint32_t r[32];
+    __syncwarp();  // tcgen05.ld is warp-collective: rejoin lanes that skipped a masked row
+    if (threadIdx.x == 0) LB_TRACE_AT(0, 256 + 4 * lb_trace_tile + 0);
+    tmem_ld_32x32(taddr + c, r);
+    tmem_ld_wait();
+    if (threadIdx.x == 0) LB_TRACE_AT(0, 256 + 4 * lb_trace_tile + 1);
+    if (!row_ok) continue;
+    float v[32];
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha + row_bias;
+    const long long off = row_off + n0 + c;
+    const int ncol = min(32, n_total - (n0 + c));
+    const bool full = ncol == 32;
+    if (bias_mode == 1) {
+      const float* bp = e.bias + n0 + c;
+      if (full) {
+#pragma unroll
+        for (int j = 0; j < 32; ++j) v[j] += __ldg(bp + j);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncol) v[j] += __ldg(bp + j);
+      }
+    }
+    if (beta != 0.f) {
+#pragma unroll
+      for (int j = 0; j < 32; ++j)
+        if (j < ncol) v[j] += beta * load_as_f32(e.C, off + j, out_dtype);
+    }
+    tc_apply_act32(v, act, e.act_param);
+    if (threadIdx.x == 0) LB_TRACE_AT(0, 256 + 4 * lb_trace_tile + 2);
+    if (out_dtype == kF32) {
+      float* dst = reinterpret_cast<float*>(e.C) + off;
+      if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncol) dst[j] = v[j];
+      }
+    } else {
+      uint16_t* dst = reinterpret_cast<uint16_t*>(e.C) + off;
+      uint32_t q[16];
+      if (out_dtype == kBF16) {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) q[j] = pack2(v[2 * j], v[2 * j + 1], kBF16);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 16; ++j) q[j] = pack2(v[2 * j], v[2 * j + 1], kF16);
+      }
+      if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4*>(dst + 8 * j) =
+              make_uint4(q[4 * j], q[4 * j + 1], q[4 * j + 2], q[4 * j + 3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncol) dst[j] = static_cast<uint16_t>(j & 1 ? q[j >> 1] >> 16 : q[j >> 1] & 0xffffu);
+      }
+    }
+    if (threadIdx.x == 0) LB_TRACE_AT(0, 256 + 4 * lb_trace_tile + 3);
+  }
+}
+
 template <class Policy>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -216,67 +318,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       const int row_index = Policy::row_index(p, tile, row);
       const EpiParams& e = p.epi;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(warp * 32) << 16);
-#pragma unroll 1
-      for (int c = 0; c < BN; c += 32) {
-        if (n0 + c >= n_total) break;  // warp-uniform
-        uint32_t r[32];
-        tmem_ld_32x32(taddr + c, r);
-        tmem_ld_wait();
-        if (row_ok) {
-          float v[32];
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            float x = __uint_as_float(r[j]) * e.alpha;
-            if (e.bias_mode == 1) {
-              const int col = n0 + c + j;
-              if (col < n_total) x += e.bias[col];
-            } else if (e.bias_mode == 2) {
-              x += e.bias[row_index];
-            }
-            v[j] = x;
-          }
-          const long long off = row_off + n0 + c;
-          const int ncol = min(32, n_total - (n0 + c));
-          if (e.beta != 0.f) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (j < ncol) v[j] += e.beta * load_as_f32(e.C, off + j, e.out_dtype);
-          }
-          if (e.act != kActNone) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = apply_act(v[j], e.act, e.act_param);
-          }
-          if (e.out_dtype == kF32) {
-            float* dst = reinterpret_cast<float*>(e.C) + off;
-            if (ncol == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 4)
-                *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < ncol) dst[j] = v[j];
-            }
-          } else {
-            uint16_t* dst = reinterpret_cast<uint16_t*>(e.C) + off;
-            if (ncol == 32 && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
-#pragma unroll
-              for (int j = 0; j < 32; j += 8) {
-                uint4 q;
-                q.x = pack2(v[j], v[j + 1], e.out_dtype);
-                q.y = pack2(v[j + 2], v[j + 3], e.out_dtype);
-                q.z = pack2(v[j + 4], v[j + 5], e.out_dtype);
-                q.w = pack2(v[j + 6], v[j + 7], e.out_dtype);
-                *reinterpret_cast<uint4*>(dst + j) = q;
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 32; ++j)
-                if (j < ncol) store_from_f32(e.C, off + j, v[j], e.out_dtype);
-            }
-          }
-        }
-      }
+      tc_epilogue_rows<BN>(taddr, row_ok, row_off, n0, n_total, row_index, e);
       tc_fence_before();
       __syncwarp();
       if (threadIdx.x == 0) LB_TRACE_AT(3, 2 * local_tile + 1);

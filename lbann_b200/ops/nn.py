@@ -317,12 +317,18 @@ class _ConvC8(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w_leaf, b_leaf, wh, bh, ksize, pad, act, act_p, skip_act_grad):
         ndim = x.dim()
-        x_cl = _cl_view(x)
-        Cin = x_cl.shape[-1]
-        if Cin != 8:
-            x_cl = F.pad(x_cl, (0, 8 - Cin))
+        x_in = _cl_view(x)
+        Cin = x_in.shape[-1]
+        x_cl = F.pad(x_in, (0, 8 - Cin)) if Cin != 8 else x_in
         if not x_cl.is_contiguous():
             x_cl = x_cl.contiguous()
+        # The filter-gradient kernel also takes 4-channel (8-byte) pixels: keep the input as
+        # it came instead of the padded copy whenever that is possible.
+        x_bwd = x_cl
+        if Cin <= 4 and x_in.shape[-2] % 16 == 0:
+            x_bwd = F.pad(x_in, (0, 4 - Cin)) if Cin != 4 else x_in
+            if not x_bwd.is_contiguous():
+                x_bwd = x_bwd.contiguous()
         Kout = wh.master.shape[0]
         kd, kh, _ = ksize
 
@@ -346,7 +352,8 @@ class _ConvC8(torch.autograd.Function):
                                            int(act), float(act_p), native.stream_ptr()),
                      "lb_conv_c8_fwd")
         native.count_launch()
-        ctx.save_for_backward(x_cl, y if (act != native.ACT_NONE and not skip_act_grad) else None)
+        ctx.save_for_backward(x_bwd, y if (act != native.ACT_NONE and not skip_act_grad) else None)
+        xs = (c_ll * 4)(x_bwd.stride(0), x_bwd.stride(1), x_bwd.stride(2), x_bwd.stride(3))
         ctx.meta = (wh, bh, ksize, pad, act, act_p, ndim, Kout, Cin, geom, xs)
         return _from_cl(y, ndim)
 
@@ -393,7 +400,7 @@ def convolution(x, wh: WeightHandle, bh: Optional[WeightHandle], ksize, pad, str
         Kout, Cin = wh.master.shape[0], wh.master.shape[1]
         if (Cin <= 8 and k3[2] == 3 and p3[2] == 1 and s3 == (1, 1, 1) and d3 == (1, 1, 1)
                 and Kout <= 32 and Kout % 8 == 0 and k3[0] * k3[1] * 32 <= 512
-                and x.shape[-1] % 2 == 0
+                and x.shape[-1] % 8 == 0
                 and p3[0] in (0, (k3[0] - 1) // 2) and k3[0] % 2 == 1 and 2 * p3[1] == k3[1] - 1
                 and wh.grad is not None and wh.grad.is_contiguous()):
             return _ConvC8.apply(x, wh.master, bh.master if bh is not None else None, wh, bh, k3,

@@ -72,7 +72,7 @@ def comm_kernels():
     m = torch.full((5,), float(rank), device=dev)
     g.allreduce_small_(m, "max")
     torch.cuda.synchronize()
-    res["one_shot_sum"] = bool(torch.allclose(v, P * torch.arange(100, device=dev) + sum(range(P))))
+    res["one_shot_sum"] = bool(torch.allclose(v, P * torch.arange(100, device=dev, dtype=torch.float32) + sum(range(P))))
     res["one_shot_max"] = bool((m == P - 1).all())
     # neighbour put + barrier
     rows, rb = 4, 256

@@ -19,6 +19,12 @@ CASES = [
     (2, 32, 1, 30, 30, 40, 3, 1, 2, 1),
     (1, 24, 6, 10, 12, 16, 3, 2, 1, 2),
     (4, 8, 1, 7, 7, 24, 3, 1, 1, 1),
+    # shapes the halo-slab kernel takes (stride 1, filter resident in shared memory)
+    (1, 32, 6, 40, 64, 64, 3, 1, 1, 1),
+    (2, 64, 4, 24, 32, 32, 3, 1, 1, 1),
+    (1, 16, 1, 33, 50, 24, 3, 1, 1, 1),
+    (1, 48, 3, 20, 28, 96, 3, 1, 1, 1),
+    (1, 32, 3, 9, 130, 64, 3, 0, 1, 1),
 ]
 
 

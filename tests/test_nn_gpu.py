@@ -14,7 +14,8 @@ def _handle(t):
     return nn.WeightHandle(m, g, None)
 
 
-@pytest.mark.parametrize("shape", [(2, 4, 8, 16, 64), (1, 3, 6, 10, 136), (2, 8, 4, 8, 128), (2, 4, 1, 12, 40)])
+@pytest.mark.parametrize("shape", [(2, 4, 8, 16, 64), (1, 3, 6, 10, 136), (2, 8, 4, 8, 128), (2, 4, 1, 12, 40),
+                                   (2, 4, 4, 6, 160), (1, 2, 3, 5, 48), (1, 4, 3, 4, 256)])
 @pytest.mark.parametrize("kout", [32, 16])
 def test_conv_c8_first_layer(shape, kout):
     N, C, D, H, W = shape
