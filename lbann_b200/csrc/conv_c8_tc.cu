@@ -1,25 +1,19 @@
-// First-layer convolution kernels for inputs with at most 8 channels (stored as exactly
-// 8 = one 16-byte vector per pixel), 3x3x3 / 1x3x3 filters, stride 1, dilation 1.
+// First-layer convolution kernels for inputs with at most 8 channels (4 or 8 channels per
+// pixel in memory, i.e. 8- or 16-byte pixels), kd x kh x 3 filters, stride 1, dilation 1.
 //
-// With 16 bytes per pixel a row of W consecutive pixels is a dense array of 16-byte
-// vectors, which is exactly the core-matrix row pitch of the un-swizzled tcgen05 operand
-// layouts.  The kernels exploit that to apply the kw taps WITHOUT re-loading or
-// re-arranging data:
+// With so few channels the reduction per tap is tiny, and a tcgen05.mma costs ~104
+// cycles however little of it is used, so the generic implicit-GEMM path (one operand
+// slice per tap) wastes almost all of every instruction here.  Both kernels therefore
+// bring ONE halo slab per tile with TMA and let the four epilogue warps unfold it in
+// shared memory into a dense operand whose rows / columns are (tap, channel):
 //
-//  forward:  A is K-major, un-swizzled, row pitch 16 B, K-chunk pitch (LBO) 16 B, so
-//            A[m][k] = slab[8 m + k]: row m sees pixels m, m+1 (one UMMA, K = 16) and
-//            m+2, m+3 (second UMMA); the filter is laid out [kd*kh][Kout][kw(4) x c(8)] with
-//            the kw = 3 column zero.  One TMA box of (W+2) pixels per (kd, kh) feeds 128
-//            output pixels; there is no im2col and no per-tap reload.
+//  forward:  A = [pixel][(tap, channel)] K-major, 7 UMMAs per 128 pixels for a 3x3x3
+//            filter on 4-channel pixels; the packed filter stays in shared memory.
+//  wgrad:    A = the same bytes read MN-major (M = (tap, channel), K = pixel), B = the dy
+//            brick as TMA delivers it; 8 UMMAs per 128 pixels, one accumulator tile per
+//            CTA, partial dW added with fp32 atomics at the end.
 //
-//  wgrad:    A is MN-major, un-swizzled, with the M-block pitch (SBO) equal to one pixel
-//            (16 B): M = 16 shifts x 8 channels, of which shifts 0..2 are the kw taps.  One
-//            accumulator per (kd, kh) (9 x 32 TMEM columns for 32 output channels); a CTA
-//            streams 64-pixel bricks (one x slab + one dy brick per stage) and finally adds
-//            its partial dW with fp32 atomics.
-//
-// These replace the generic implicit-GEMM path for the layer where it is weakest (tiny
-// reduction per tap, 27 reloads of the same pixels); the reference relies on cuDNN here
+// The reference relies on cuDNN for this layer
 // (src/layers/learning/base_convolution.cpp:462-814).
 #include "tc_pipeline.cuh"
 
@@ -28,33 +22,108 @@ namespace lb {
 constexpr uint32_t kLayoutNone = 0;
 
 struct C8Geom {
-  int N, D, H, W;       // input spatial dims (C is 8)
+  int N, D, H, W;       // input spatial dims
   int Kout;
   int kd, kh;           // kw is 3
   int pd, ph;           // pw is 1
   int Do;               // output depth = D + 2 pd - kd + 1 (pd = 0 when halos carry the padding)
 };
 
+// Unfold one pixel: gather its taps from the halo slab (3 kw taps from each of the
+// kd * kh slab rows) and store them as 16-byte K chunks, 128 B apart, of the operand row.
+// All loads of a pixel are issued before the first store so that their latencies overlap;
+// TAPS2 > 0 fixes kd * kh at compile time (full unrolling), TAPS2 = 0 is the generic loop.
+template <int CR, int TAPS2>
+__device__ __forceinline__ void c8_unfold_pixel(uint32_t src_px, uint32_t dst, int taps2,
+                                                int row_bytes) {
+  if constexpr (TAPS2 > 0 && CR == 4) {
+    uint2 v[TAPS2 * 3 + 1];
+#pragma unroll
+    for (int r = 0; r < TAPS2; ++r) {
+#pragma unroll
+      for (int c = 0; c < 3; ++c) v[r * 3 + c] = lds64(src_px + r * row_bytes + c * 8);
+    }
+    v[TAPS2 * 3] = make_uint2(0u, 0u);
+#pragma unroll
+    for (int mb = 0; mb < (TAPS2 * 3 + 1) / 2; ++mb)
+      sts128(dst + mb * 128, make_uint4(v[2 * mb].x, v[2 * mb].y, v[2 * mb + 1].x, v[2 * mb + 1].y));
+  } else if constexpr (TAPS2 > 0) {
+#pragma unroll
+    for (int r = 0; r < TAPS2; ++r) {
+      uint4 v[3];
+#pragma unroll
+      for (int c = 0; c < 3; ++c) v[c] = lds128(src_px + r * row_bytes + c * 16);
+#pragma unroll
+      for (int c = 0; c < 3; ++c) sts128(dst + (r * 3 + c) * 128, v[c]);
+    }
+  } else if constexpr (CR == 4) {
+    const int taps = taps2 * 3;
+    for (int mb = 0; mb < (taps + 1) / 2; ++mb) {
+      const int t0 = 2 * mb, t1 = 2 * mb + 1;
+      const int r0 = t0 / 3, c0 = t0 - r0 * 3;
+      const int r1 = t1 / 3, c1 = t1 - r1 * 3;
+      uint2 lo = lds64(src_px + r0 * row_bytes + c0 * 8);
+      uint2 hi = make_uint2(0u, 0u);
+      if (t1 < taps) hi = lds64(src_px + r1 * row_bytes + c1 * 8);
+      sts128(dst + mb * 128, make_uint4(lo.x, lo.y, hi.x, hi.y));
+    }
+  } else {
+    for (int r = 0; r < taps2; ++r) {
+#pragma unroll
+      for (int c = 0; c < 3; ++c)
+        sts128(dst + (r * 3 + c) * 128, lds128(src_px + r * row_bytes + c * 16));
+    }
+  }
+}
+
+__device__ __forceinline__ void c8_unfold(int cr, int taps2, uint32_t slab, int slab_lead, int px,
+                                          uint32_t dst, int row_bytes) {
+  if (cr == 4) {
+    const uint32_t src_px = slab + (slab_lead + px) * 8;
+    if (taps2 == 9) c8_unfold_pixel<4, 9>(src_px, dst, taps2, row_bytes);
+    else if (taps2 == 3) c8_unfold_pixel<4, 3>(src_px, dst, taps2, row_bytes);
+    else c8_unfold_pixel<4, 0>(src_px, dst, taps2, row_bytes);
+  } else {
+    const uint32_t src_px = slab + (slab_lead + px) * 16;
+    if (taps2 == 9) c8_unfold_pixel<8, 9>(src_px, dst, taps2, row_bytes);
+    else if (taps2 == 3) c8_unfold_pixel<8, 3>(src_px, dst, taps2, row_bytes);
+    else c8_unfold_pixel<8, 0>(src_px, dst, taps2, row_bytes);
+  }
+}
+
 // ------------------------------------------------------------------------- forward
-// One CTA per SM walks tiles of 128 pixels along W.  Per tile a SINGLE 5-D TMA box brings
-// the whole input neighbourhood: kd x kh rows of 144 pixels (8 left of the tile start to
-// 136 right of it), and the packed filter (2 KB per (kd, kh) row) stays in shared memory
-// for the life of the CTA.  A kw tap is a 16-byte shift of the operand start address, so
-// a tile costs one copy instruction and 2 * kd * kh UMMAs; the copy engine's per-box
-// set-up time (a few hundred cycles, whatever the box size) is paid once per tile
-// instead of once per tap row.
+// y[pixel][k] = sum over (tap, channel) of x[pixel + tap][channel] * w[k][tap][channel], as a
+// GEMM with M = 128 pixels of one image row, N = Kout, K = (tap, channel).  A tcgen05.mma
+// costs ~104 cycles whatever N <= 128 is, so the tile time is the number of UMMAs: the
+// four epilogue warps first unfold the tile's halo slab into the canonical un-swizzled
+// K-major operand [pixel][(tap, channel)] in shared memory, which makes every K element
+// useful: 27 taps x 4 channels = 108 -> 7 UMMAs per tile (14 with 8-channel pixels)
+// against 18 when each (kd, kh) slab row is fed through shifted descriptors.
 //
-// The tensor map splits W into 8-pixel chunks (dim 0: 16 units of 8 bytes, dim 1: chunk
-// index, stride 128 B), which lifts the 256-element limit of a box dimension while the
-// rows still land back to back: [kd][kh][18 chunks][128 B].  Chunk -1 and chunks beyond
-// W / 8 are zero-filled and supply the padding along W; rows outside H / D likewise.
-constexpr int kC8SlabChunks = 18;                       // 144 pixels
-constexpr int kC8RowBytes = kC8SlabChunks * 128;        // 2304
+// Per tile ONE 5-D TMA box brings the slab [kd][kh][chunks][128 B].  The tensor map
+// splits W into 128-byte chunks (dim 0: 16 units of 8 bytes, dim 1: chunk index), which
+// lifts the 256-element limit of a box dimension while the rows still land back to
+// back; the chunk left of the tile and chunks beyond W are zero-filled and supply the
+// padding along W, rows outside H / D likewise.  Pixels are 8 bytes (4 channels) or 16.
+// The filter, packed on the host as [K chunk of 8][32 rows][8], stays in shared memory.
 constexpr int kC8MaxStages = 12;
+// Worker groups of four warps.  A group unfolds a tile and later runs its epilogue; with a
+// single warp per scheduler every dependent instruction shows its full latency, so the
+// groups take tiles in turn (tile i belongs to group i % G, with its own operand buffer
+// and accumulator) and overlap one another's latencies.
+constexpr int kC8Groups = 3;
+constexpr int kC8Threads = 64 + 128 * kC8Groups;
 
 struct C8FwdParams {
   C8Geom g;
-  int tiles_w, num_tiles, taps2, stages, stage_bytes, in_dtype;
+  int tiles_w, num_tiles, taps2, taps;
+  int cr;                      // channels per pixel in memory: 4 or 8
+  int mb_pad;                  // 16-byte K chunks per pixel in the unfolded operand (16 or 32)
+  int ksteps;                  // UMMAs per tile
+  int groups;                  // worker groups (<= kC8Groups)
+  int slab_row_bytes, slab_lead, stage_bytes, stages, filter_bytes;
+  int in_dtype;
+  const void* w;               // packed filter in global memory
   long long o_sn, o_sd, o_sh, o_sw;
   EpiParams epi;
 };
@@ -62,22 +131,27 @@ struct C8FwdParams {
 struct C8FwdShared {
   uint64_t full[kC8MaxStages];
   uint64_t empty[kC8MaxStages];
-  uint64_t tmem_full[2];
-  uint64_t tmem_empty[2];
-  uint64_t filter_ready;
+  uint64_t a_ready[kC8Groups];
+  uint64_t a_free[kC8Groups];
+  uint64_t tmem_full[kC8Groups];
+  uint64_t tmem_empty[kC8Groups];
   uint32_t tmem_base;
   int abort_flag;
 };
 
-__global__ void __launch_bounds__(192, 1)
-conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
-                   const C8FwdParams p, int* status) {
+__global__ void __launch_bounds__(kC8Threads, 1)
+conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const C8FwdParams p, int* status) {
   constexpr int BN = 32;
+  const int G = p.groups;                        // worker groups in this launch: 2 or 3
+  const int kProducerWarp = 4 * G, kMmaWarp = 4 * G + 1;
+  constexpr int kTmemCols = 128;
   extern __shared__ uint8_t smem_raw[];
   __shared__ C8FwdShared sh;
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-  const uint32_t s_filter = smem_base;                           // taps2 * 2048 bytes
-  const uint32_t s_stage0 = smem_base + p.taps2 * 2048;
+  const uint32_t a_bytes = 16u * p.mb_pad * 128u;
+  const uint32_t s_a0 = smem_base;                               // G unfolded operands
+  const uint32_t s_filter = smem_base + G * a_bytes;
+  const uint32_t s_stage0 = s_filter + p.filter_bytes;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int* abort_flag = &sh.abort_flag;
   const int S = p.stages;
@@ -86,34 +160,40 @@ conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
       mbar_init(smem_u32(&sh.full[s]), 1);
-      mbar_init(smem_u32(&sh.empty[s]), 1);
+      mbar_init(smem_u32(&sh.empty[s]), 4);      // one arrive per unfolding warp
     }
-    for (int a = 0; a < 2; ++a) {
+    for (int a = 0; a < kC8Groups; ++a) {
+      mbar_init(smem_u32(&sh.a_ready[a]), 4);
+      mbar_init(smem_u32(&sh.a_free[a]), 1);
       mbar_init(smem_u32(&sh.tmem_full[a]), 1);
       mbar_init(smem_u32(&sh.tmem_empty[a]), 4);
     }
-    mbar_init(smem_u32(&sh.filter_ready), 1);
     sh.abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 4 && lane == 0) {
-    tma_prefetch_desc(&tmX);
-    tma_prefetch_desc(&tmW);
-  }
-  if (warp == 5) {
-    tmem_alloc(smem_u32(&sh.tmem_base), 2 * BN);
+  if (warp == kProducerWarp && lane == 0) tma_prefetch_desc(&tmX);
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&sh.tmem_base), kTmemCols);
     tmem_relinquish();
+  }
+  if (warp < 4 * G) {
+    // zero the operand buffers (K chunks that no tap fills must read as zero) and bring
+    // the filter in with plain loads; both are then published to the tensor core's proxy
+    uint4* az = reinterpret_cast<uint4*>(smem_raw + (s_a0 - smem_u32(smem_raw)));
+    for (uint32_t i = threadIdx.x; i < G * a_bytes / 16; i += 128 * G) az[i] = make_uint4(0, 0, 0, 0);
+    uint4* fz = reinterpret_cast<uint4*>(smem_raw + (s_filter - smem_u32(smem_raw)));
+    const uint4* fw = reinterpret_cast<const uint4*>(p.w);
+    for (uint32_t i = threadIdx.x; i < (uint32_t)p.filter_bytes / 16; i += 128 * G) fz[i] = fw[i];
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
   }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sh.tmem_base;
+  const int chunk_px = p.cr == 4 ? 16 : 8;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     if (lane == 0) {
-      // filter: one box of taps2 rows x 2 KB, once
-      mbar_expect_tx(smem_u32(&sh.filter_ready), (uint32_t)p.taps2 * 2048u);
-      tma_load_2d(s_filter, &tmW, smem_u32(&sh.filter_ready), 0, 0);
       uint32_t it = 0;
       bool ok = true;
       // tile index -> (tw, h, d, n), advanced incrementally: no divisions in the loop
@@ -132,11 +212,9 @@ conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           break;
         }
         const uint32_t bar = smem_u32(&sh.full[s]);
-        LB_TRACE_AT(0, 2 * it);
-        mbar_expect_tx(bar, (uint32_t)p.stage_bytes);
-        tma_load_5d(s_stage0 + s * p.stage_bytes, &tmX, bar, 0, tw * 16 - 1, h - g.ph,
-                    d - g.pd, n);
-        LB_TRACE_AT(0, 2 * it + 1);
+        mbar_expect_tx(bar, (uint32_t)(p.taps2 * p.slab_row_bytes));
+        tma_load_5d(s_stage0 + s * p.stage_bytes, &tmX, bar, 0, tw * (128 / chunk_px) - 1,
+                    h - g.ph, d - g.pd, n);
         // mixed-radix add of the grid stride
         tw += step_tw;
         int c = 0;
@@ -153,84 +231,109 @@ conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constan
           const uint32_t q = it - 1 - j;
           mbar_wait_budget_only(smem_u32(&sh.full[q % S]), (q / S) & 1);
         }
-        mbar_wait_budget_only(smem_u32(&sh.filter_ready), 0);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc_f16(p.in_dtype == kBF16 ? 1u : 0u, 0, 0, 128, BN);
-      // A: rows (pixels) 16 B apart, 8-row groups 128 B apart (SBO), the two 8-element K
-      // chunks of one UMMA 16 B apart (LBO): K = 16 spans pixels m and m + 1.
-      // B: [k-chunk(4)][BN rows][8 elements]: rows 16 B apart, 8-row groups 128 B (SBO),
-      // K chunks BN * 16 B apart (LBO).
-      const uint64_t a_desc0 = make_smem_desc(0, 16, 128, kLayoutNone);
-      const uint64_t b_desc0 = make_smem_desc(0, BN * 16, 128, kLayoutNone);
-      bool ok = mbar_wait_bounded(smem_u32(&sh.filter_ready), 0, abort_flag);
-      if (!ok) raise_status(status, abort_flag, kTimeoutTmaFull);
+      // A (K-major, un-swizzled): core matrix = 8 pixels x 16 B; K chunks 128 B apart (LBO),
+      // 8-pixel groups mb_pad * 128 B apart (SBO).  B: [K chunk][BN rows][16 B]: K chunks
+      // BN * 16 B apart (LBO), 8-row groups 128 B apart (SBO).  One UMMA = 2 K chunks.
+      const uint64_t a_desc0 = make_smem_desc(0, 128, p.mb_pad * 128, kLayoutNone);
+      const uint64_t b_desc0 = make_smem_desc(s_filter, BN * 16, 128, kLayoutNone);
       uint32_t it = 0;
+      bool ok = true;
       for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, ++it) {
-        const uint32_t acc = it & 1, acc_ph = (it >> 1) & 1;
-        if (!mbar_wait_bounded(smem_u32(&sh.tmem_empty[acc]), acc_ph ^ 1, abort_flag)) {
+        const uint32_t j = it % G, jph = (it / G) & 1;
+        if (!mbar_wait_bounded(smem_u32(&sh.tmem_empty[j]), jph ^ 1, abort_flag)) {
           raise_status(status, abort_flag, kTimeoutTmemEmpty);
           ok = false;
           break;
         }
-        const uint32_t s = it % S, ph = (it / S) & 1;
-        if (!mbar_wait_bounded(smem_u32(&sh.full[s]), ph, abort_flag)) {
+        if (!mbar_wait_bounded(smem_u32(&sh.a_ready[j]), jph, abort_flag)) {
           raise_status(status, abort_flag, kTimeoutTmaFull);
           ok = false;
           break;
         }
         tc_fence_after();
-        LB_TRACE_AT(1, it);
-        // pixel w0 - 1 sits 7 pixels into the slab row
-        uint64_t ad = a_desc0 + ((s_stage0 + s * p.stage_bytes + 7 * 16) >> 4);
-        uint64_t bd = b_desc0 + (s_filter >> 4);
-        const uint32_t tmem_acc = tmem_base + acc * BN;
-        for (int t2 = 0; t2 < p.taps2; ++t2) {
-          umma_f16(tmem_acc, ad, bd, idesc, t2 == 0 ? 0u : 1u);
-          umma_f16(tmem_acc, ad + 2, bd + (2 * BN * 16 >> 4), idesc, 1u);
-          ad += kC8RowBytes >> 4;
-          bd += 2048 >> 4;
+        uint64_t ad = a_desc0 + ((s_a0 + j * a_bytes) >> 4);
+        uint64_t bd = b_desc0;
+        const uint32_t tmem_acc = tmem_base + j * BN;
+        for (int kk = 0; kk < p.ksteps; ++kk) {
+          umma_f16(tmem_acc, ad, bd, idesc, kk == 0 ? 0u : 1u);
+          ad += (2 * 128) >> 4;
+          bd += (2 * BN * 16) >> 4;
         }
-        umma_commit(smem_u32(&sh.empty[s]));
-        umma_commit(smem_u32(&sh.tmem_full[acc]));
-        LB_TRACE_AT(2, it);
+        umma_commit(smem_u32(&sh.a_free[j]));
+        umma_commit(smem_u32(&sh.tmem_full[j]));
       }
     }
   } else {
-    uint32_t it = 0;
+    const int group = warp >> 2;                    // tiles group, group + G, ... of this CTA
+    const int wq = warp & 3;                        // TMEM lane quarter of this warp
+    const int px = wq * 32 + lane;                  // pixel of the tile this thread unfolds
+    const uint32_t dst_px = (px >> 3) * (p.mb_pad * 128) + (px & 7) * 16;
     const EpiParams& e = p.epi;
-    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++it) {
-      int r = t;
-      const int tw = r % p.tiles_w; r /= p.tiles_w;
-      const int h = r % g.H; r /= g.H;
-      const int d = r % g.Do, n = r / g.Do;
-      const uint32_t acc = it & 1, acc_ph = (it >> 1) & 1;
-      const bool landed = __all_sync(
-          0xffffffffu, mbar_wait_bounded(smem_u32(&sh.tmem_full[acc]), acc_ph, abort_flag));
-      if (!landed) {
-        if (lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
-        break;
+    const uint32_t j = group;
+    int t_prev = -1;
+    uint32_t use = 0;                               // how often this group used its buffers
+    for (uint32_t it = group;; it += G, ++use) {
+      const long long tl = (long long)blockIdx.x + (long long)it * gridDim.x;
+      const bool have = tl < p.num_tiles;
+      const int t = (int)tl;
+      if (have) {
+        // ---- unfold tile `it` ---------------------------------------------------------
+        const uint32_t s = it % S, ph = (it / S) & 1;
+        const uint32_t jph = use & 1;
+        bool good = mbar_wait_bounded(smem_u32(&sh.full[s]), ph, abort_flag);
+        good = good && mbar_wait_bounded(smem_u32(&sh.a_free[j]), jph ^ 1, abort_flag);
+        if (!__all_sync(0xffffffffu, good)) {
+          if (lane == 0) raise_status(status, abort_flag, kTimeoutTmaFull);
+          break;
+        }
+        const uint32_t sX = s_stage0 + s * p.stage_bytes;
+        const uint32_t dst = s_a0 + j * a_bytes + dst_px;
+        c8_unfold(p.cr, p.taps2, sX, p.slab_lead, px, dst, p.slab_row_bytes);
+        // publish the generic-proxy writes to the tensor core's proxy, then signal
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&sh.a_ready[j]));
+          mbar_arrive(smem_u32(&sh.empty[s]));       // the slab is no longer needed
+        }
       }
-      tc_fence_after();
-      if (threadIdx.x == 0) LB_TRACE_AT(3, 2 * it);
-      const int row = warp * 32 + lane;
-      const int w = tw * 128 + row;
-      const long long row_off = n * p.o_sn + d * p.o_sd + h * p.o_sh + (long long)w * p.o_sw;
-      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(warp * 32) << 16);
-      tc_epilogue_rows<BN>(taddr, w < g.W, row_off, 0, g.Kout, row, e, it);
-      tc_fence_before();
-      __syncwarp();
-      if (threadIdx.x == 0) LB_TRACE_AT(3, 2 * it + 1);
-      if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[acc]));
+      // ---- epilogue of this group's previous tile (its UMMAs ran meanwhile) ------------
+      if (t_prev >= 0) {
+        const uint32_t acc_ph = (use - 1) & 1;
+        int r = t_prev;
+        const int tw = r % p.tiles_w; r /= p.tiles_w;
+        const int h = r % g.H; r /= g.H;
+        const int d = r % g.Do, n = r / g.Do;
+        const bool landed = __all_sync(
+            0xffffffffu, mbar_wait_bounded(smem_u32(&sh.tmem_full[j]), acc_ph, abort_flag));
+        if (!landed) {
+          if (lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
+          break;
+        }
+        tc_fence_after();
+        const int row = wq * 32 + lane;
+        const int w = tw * 128 + row;
+        const long long row_off = n * p.o_sn + d * p.o_sd + h * p.o_sh + (long long)w * p.o_sw;
+        const uint32_t taddr = tmem_base + j * BN + (static_cast<uint32_t>(wq * 32) << 16);
+        tc_epilogue_rows<BN>(taddr, w < g.W, row_off, 0, g.Kout, row, e);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[j]));
+      }
+      if (!have) break;
+      t_prev = t;
     }
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 2 * BN);
+    tmem_dealloc(tmem_base, kTmemCols);
   }
 }
 
@@ -260,6 +363,7 @@ struct C8WgradParams {
   int mb_pad;           // 16-byte row blocks per pixel in the unfolded operand (16 or 32)
   int slab_row_bytes, slab_bytes, slab_lead;   // slab_lead: slab index of pixel w0 - 1
   int stage_bytes, stages;
+  int groups;           // worker groups unfolding bricks in turn (<= kC8Groups)
   float alpha;
   float* dW;
   long long s_tap, s_k, s_c;   // tap = (a*kh + b)*3 + kw
@@ -269,14 +373,14 @@ constexpr int kWgMaxStages = 8;
 struct C8WgShared {
   uint64_t full[kWgMaxStages];
   uint64_t empty[kWgMaxStages];
-  uint64_t a_ready[2];
-  uint64_t a_free[2];
+  uint64_t a_ready[kC8Groups];
+  uint64_t a_free[kC8Groups];
   uint64_t done;
   uint32_t tmem_base;
   int abort_flag;
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kC8Threads, 1)
 conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmDy,
                      const C8WgradParams p, int* status) {
   extern __shared__ uint8_t smem_raw[];
@@ -287,8 +391,10 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   const int S = p.stages;
   const C8Geom& g = p.g;
   const uint32_t a_bytes = 16u * p.mb_pad * 128u;          // 16 pixel groups x row blocks x 128 B
-  const uint32_t s_a0 = smem_base;                          // two unfolded operands
-  const uint32_t s_stage0 = smem_base + 2 * a_bytes;
+  const int G = p.groups;
+  const int kProducerWarp = 4 * G, kMmaWarp = 4 * G + 1;
+  const uint32_t s_a0 = smem_base;                          // G unfolded operands
+  const uint32_t s_stage0 = smem_base + G * a_bytes;
   const int tmem_cols = p.m_tiles * p.BN < 32 ? 32 : p.m_tiles * p.BN;
 
   if (threadIdx.x == 0) {
@@ -296,7 +402,7 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       mbar_init(smem_u32(&sh.full[s]), 1);
       mbar_init(smem_u32(&sh.empty[s]), 1);
     }
-    for (int j = 0; j < 2; ++j) {
+    for (int j = 0; j < kC8Groups; ++j) {
       mbar_init(smem_u32(&sh.a_ready[j]), 4);   // one arrive per unfolding warp
       mbar_init(smem_u32(&sh.a_free[j]), 1);
     }
@@ -304,11 +410,11 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     sh.abort_flag = 0;
     mbar_fence_init();
   }
-  if (warp == 4 && lane == 0) {
+  if (warp == kProducerWarp && lane == 0) {
     tma_prefetch_desc(&tmX);
     tma_prefetch_desc(&tmDy);
   }
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tmem_alloc(smem_u32(&sh.tmem_base), tmem_cols);
     tmem_relinquish();
   }
@@ -321,7 +427,7 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   const int bw_px = g.W < kWgBrick ? g.W : kWgBrick;        // pixels per brick
   const int k_steps = (bw_px + 15) / 16;
 
-  if (warp == 4) {
+  if (warp == kProducerWarp) {
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
@@ -354,7 +460,7 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         }
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == kMmaWarp) {
     if (lane == 0) {
       const uint32_t idesc = make_idesc_f16(p.in_dtype == kBF16 ? 1u : 0u, 1, 1, 128, (uint32_t)p.BN);
       // A (MN-major, un-swizzled): core matrix = 8 pixels x 16 B; row blocks 128 B apart
@@ -367,7 +473,7 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       bool ok = true;
       for (int b = split; b < p.bricks_total && ok; b += p.splits, ++it) {
         const uint32_t s = it % S, ph = (it / S) & 1;
-        const uint32_t j = it & 1, jph = (it >> 1) & 1;
+        const uint32_t j = it % G, jph = (it / G) & 1;
         if (!mbar_wait_bounded(smem_u32(&sh.full[s]), ph, abort_flag) ||
             !mbar_wait_bounded(smem_u32(&sh.a_ready[j]), jph, abort_flag)) {
           raise_status(status, abort_flag, kTimeoutTmaFull);
@@ -393,14 +499,17 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       if (ok) umma_commit(smem_u32(&sh.done));
     }
   } else {
-    // ---- unfold: thread t owns pixel t of the brick -------------------------------
-    const int px = threadIdx.x;                     // 0..127
+    // ---- unfold: group `warp / 4` takes bricks group, group + G, ...; a thread owns a pixel
+    const int group = warp >> 2, wq = warp & 3;
+    const int px = wq * 32 + lane;                  // 0..127
     const uint32_t dst_px = (px >> 3) * (p.mb_pad * 128) + (px & 7) * 16;
-    uint32_t it = 0;
+    const uint32_t j = group;
     bool ok = true;
-    for (int b = split; b < p.bricks_total && ok; b += p.splits, ++it) {
+    uint32_t use = 0;
+    for (uint32_t it = group; (long long)split + (long long)it * p.splits < p.bricks_total;
+         it += G, ++use) {
       const uint32_t s = it % S, ph = (it / S) & 1;
-      const uint32_t j = it & 1, jph = (it >> 1) & 1;
+      const uint32_t jph = use & 1;
       bool good = mbar_wait_bounded(smem_u32(&sh.full[s]), ph, abort_flag);
       good = good && mbar_wait_bounded(smem_u32(&sh.a_free[j]), jph ^ 1, abort_flag);
       if (!__all_sync(0xffffffffu, good)) {
@@ -410,25 +519,7 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       }
       const uint32_t sX = s_stage0 + s * p.stage_bytes;
       const uint32_t dst = s_a0 + j * a_bytes + dst_px;
-      if (p.cr == 4) {
-        // 8-byte pixels: a 16-byte row block holds two taps
-        const uint32_t src_px = sX + (p.slab_lead + px) * 8;
-        for (int mb = 0; mb < (p.taps + 1) / 2; ++mb) {
-          const int t0 = 2 * mb, t1 = 2 * mb + 1;
-          const int r0 = t0 / 3, c0 = t0 - r0 * 3;
-          const int r1 = t1 / 3, c1 = t1 - r1 * 3;
-          uint2 lo = lds64(src_px + r0 * p.slab_row_bytes + c0 * 8);
-          uint2 hi = make_uint2(0u, 0u);
-          if (t1 < p.taps) hi = lds64(src_px + r1 * p.slab_row_bytes + c1 * 8);
-          sts128(dst + mb * 128, make_uint4(lo.x, lo.y, hi.x, hi.y));
-        }
-      } else {
-        const uint32_t src_px = sX + (p.slab_lead + px) * 16;
-        for (int t = 0; t < p.taps; ++t) {
-          const int r0 = t / 3, c0 = t - r0 * 3;
-          sts128(dst + t * 128, lds128(src_px + r0 * p.slab_row_bytes + c0 * 16));
-        }
-      }
+      c8_unfold(p.cr, p.taps2, sX, p.slab_lead, px, dst, p.slab_row_bytes);
       // make the generic-proxy writes visible to the tensor core (async proxy), then signal
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
       __syncwarp();
@@ -436,9 +527,10 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     }
     // ---- epilogue: D row m = tap * cr + channel ----------------------------------------
     const bool landed =
-        ok && my_bricks > 0 &&
+        group == 0 && ok && my_bricks > 0 &&
         __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&sh.done), 0, abort_flag));
-    if (ok && my_bricks > 0 && !landed && lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
+    if (group == 0 && ok && my_bricks > 0 && !landed && lane == 0)
+      raise_status(status, abort_flag, kTimeoutTmemFull);
     if (landed) {
       tc_fence_after();
       for (int mt = 0; mt < p.m_tiles; ++mt) {
@@ -465,7 +557,7 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == kMmaWarp) {
     tc_fence_after();
     tmem_dealloc(tmem_base, tmem_cols);
   }
@@ -475,59 +567,70 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
 
 extern "C" {
 
-// x: [N][D][H][W][8] (strides xs in elements, pixels dense); w: [kd*kh][4 (kw, kw = 3 zero)]
-// [32 (output channel, zero rows beyond Kout)][8 (input channel)]; y: [N][D][H][W][Kout].
-// geom: N D H W Kout kd kh pd ph Do (10 ints).  kw = 3, pad_w = 1, stride 1.
+// x: [N][D][H][W][cr] with cr = xs[3] = 4 or 8 channels per pixel (dense); W a multiple of
+// 16 (cr = 4) or 8.  w: filter packed as [K chunk][32 rows (output channel, zero beyond
+// Kout)][8], K = tap * cr + channel with tap = (a*kh + b)*3 + kw, zero-padded to a multiple
+// of 16.  y: [N][Do][H][W][Kout].  geom: N D H W Kout kd kh pd ph Do.  kw = 3, pad_w = 1.
 int lb_conv_c8_fwd(const void* x, const void* w, void* y, const float* bias, const int* geom,
                    const long long* xs, const long long* ys, int in_dtype, int out_dtype,
                    int act, float act_param, void* stream_) {
   using namespace lb;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
-  C8Geom g;
-  memcpy(&g, geom, sizeof(g));
+  C8FwdParams p;
+  memcpy(&p.g, geom, sizeof(C8Geom));
+  const C8Geom& g = p.g;
   if (g.Kout > 32 || g.Kout % 8) return -1;
   if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15)) return -1;
-  if (xs[3] != 8 || (g.W & 1)) return -1;   // dense 8-channel pixels, even width
-  if (g.W % 8) return -1;                    // the W axis is cut into 8-pixel chunks
-  const int taps2 = g.kd * g.kh;
-  if (taps2 < 1 || taps2 > 16) return -1;
-  CUtensorMap tmX, tmW;
-  {
-    // dims: 8-byte unit within an 8-pixel chunk, chunk, H, D, N
-    uint64_t dims[5] = {16, (uint64_t)g.W / 8, (uint64_t)g.H, (uint64_t)g.D, (uint64_t)g.N};
-    uint64_t strides[4] = {128, (uint64_t)xs[2] * 2, (uint64_t)xs[1] * 2, (uint64_t)xs[0] * 2};
-    uint32_t box[5] = {16, (uint32_t)kC8SlabChunks, (uint32_t)g.kh, (uint32_t)g.kd, 1};
-    if (!lbhost::encode_tmap(&tmX, kI64, 5, x, dims, strides, box, nullptr, 0)) return -1;
+  p.cr = (int)xs[3];
+  if (p.cr != 4 && p.cr != 8) return -1;
+  const int chunk_px = p.cr == 4 ? 16 : 8;
+  if (g.W % chunk_px) return -1;
+  p.taps2 = g.kd * g.kh;
+  p.taps = p.taps2 * 3;
+  const int kchunks = (p.taps * p.cr + 7) / 8;
+  p.ksteps = (kchunks + 1) / 2;
+  if (p.ksteps > 16) return -1;
+  p.mb_pad = p.ksteps > 8 ? 32 : 16;
+  p.filter_bytes = (2 * p.ksteps * 32 * 16 + 1023) & ~1023;
+  p.slab_lead = chunk_px - 1;
+  const int nchunks = (p.slab_lead + 128 + 2 + chunk_px - 1) / chunk_px;
+  p.slab_row_bytes = nchunks * 128;
+  p.stage_bytes = p.taps2 * p.slab_row_bytes;
+  // three worker groups when their operand buffers leave room for a few slab stages
+  p.groups = kC8Groups;
+  int fixed = p.groups * 16 * p.mb_pad * 128 + p.filter_bytes;
+  if ((224 * 1024 - fixed) / p.stage_bytes < 3) {
+    p.groups = 2;
+    fixed = p.groups * 16 * p.mb_pad * 128 + p.filter_bytes;
   }
-  {
-    // packed filter: [kd*kh][4 k-chunks][32 rows][8 elements] = 2 KB per tap-row
-    uint64_t dims[2] = {256, (uint64_t)taps2};
-    uint64_t strides[1] = {2048};
-    uint32_t box[2] = {256, (uint32_t)taps2};
-    if (!lbhost::encode_tmap(&tmW, kI64, 2, w, dims, strides, box, nullptr, 0)) return -1;
-  }
-  C8FwdParams p;
-  p.g = g;
-  p.taps2 = taps2;
-  p.tiles_w = (g.W + 127) / 128;
-  p.num_tiles = p.tiles_w * g.H * g.Do * g.N;
-  p.stage_bytes = taps2 * kC8RowBytes;
-  p.stages = (200 * 1024 - taps2 * 2048) / p.stage_bytes;
+  p.stages = (224 * 1024 - fixed) / p.stage_bytes;
   if (p.stages > kC8MaxStages) p.stages = kC8MaxStages;
   if (p.stages < 2) return -1;
+  p.tiles_w = (g.W + 127) / 128;
+  p.num_tiles = p.tiles_w * g.H * g.Do * g.N;
   p.in_dtype = in_dtype;
+  p.w = w;
   p.o_sn = ys[0]; p.o_sd = ys[1]; p.o_sh = ys[2]; p.o_sw = ys[3];
   p.epi.C = y; p.epi.bias = bias; p.epi.alpha = 1.f; p.epi.beta = 0.f;
   p.epi.out_dtype = out_dtype; p.epi.bias_mode = bias ? 1 : 0; p.epi.act = act;
   p.epi.act_param = act_param; p.epi.ldc = ys[3];
-  const int smem = taps2 * 2048 + p.stages * p.stage_bytes + 1024;
+  CUtensorMap tmX;
+  {
+    // dims: 8-byte unit within a 128-byte chunk, chunk, H, D, N
+    uint64_t dims[5] = {16, (uint64_t)(g.W / chunk_px), (uint64_t)g.H, (uint64_t)g.D,
+                        (uint64_t)g.N};
+    uint64_t strides[4] = {128, (uint64_t)xs[2] * 2, (uint64_t)xs[1] * 2, (uint64_t)xs[0] * 2};
+    uint32_t box[5] = {16, (uint32_t)nchunks, (uint32_t)g.kh, (uint32_t)g.kd, 1};
+    if (!lbhost::encode_tmap(&tmX, kI64, 5, x, dims, strides, box, nullptr, 0)) return -1;
+  }
+  const int smem = fixed + p.stages * p.stage_bytes + 1024;
   static int configured = 0;
   if (configured < smem) {
     cudaFuncSetAttribute(conv_c8_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     configured = smem;
   }
   const int grid = p.num_tiles < lbhost::sm_count() ? p.num_tiles : lbhost::sm_count();
-  conv_c8_fwd_kernel<<<grid, 192, smem, stream>>>(tmX, tmW, p, lbhost::status_word());
+  conv_c8_fwd_kernel<<<grid, 64 + 128 * p.groups, smem, stream>>>(tmX, p, lbhost::status_word());
   return (int)cudaGetLastError();
 }
 
@@ -561,7 +664,12 @@ int lb_conv_c8_wgrad(const void* x, const void* dy, float* dW, const int* geom,
   p.slab_row_bytes = nchunks * 128;
   p.slab_bytes = (p.taps2 * p.slab_row_bytes + 1023) & ~1023;
   p.stage_bytes = p.slab_bytes + kWgBrick * p.BN * 2;
-  const int a_total = 2 * 16 * p.mb_pad * 128;
+  p.groups = kC8Groups;
+  int a_total = p.groups * 16 * p.mb_pad * 128;
+  if ((224 * 1024 - a_total) / p.stage_bytes < 3) {
+    p.groups = 2;
+    a_total = p.groups * 16 * p.mb_pad * 128;
+  }
   p.stages = (224 * 1024 - a_total) / p.stage_bytes;
   if (p.stages > kWgMaxStages) p.stages = kWgMaxStages;
   if (p.stages < 2) return -1;
@@ -596,7 +704,7 @@ int lb_conv_c8_wgrad(const void* x, const void* dy, float* dW, const int* geom,
     cudaFuncSetAttribute(conv_c8_wgrad_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     configured_smem = smem;
   }
-  conv_c8_wgrad_kernel<<<p.splits, 192, smem, stream>>>(tmX, tmDy, p, lbhost::status_word());
+  conv_c8_wgrad_kernel<<<p.splits, 64 + 128 * p.groups, smem, stream>>>(tmX, tmDy, p, lbhost::status_word());
   return (int)cudaGetLastError();
 }
 

@@ -319,24 +319,24 @@ class _ConvC8(torch.autograd.Function):
         ndim = x.dim()
         x_in = _cl_view(x)
         Cin = x_in.shape[-1]
-        x_cl = F.pad(x_in, (0, 8 - Cin)) if Cin != 8 else x_in
+        # pixels are 8 bytes (<= 4 channels, W a multiple of 16) or 16 bytes; an input that
+        # already has 4 or 8 channels is used as it is
+        cr = 4 if (Cin <= 4 and x_in.shape[-2] % 16 == 0) else 8
+        x_cl = F.pad(x_in, (0, cr - Cin)) if Cin != cr else x_in
         if not x_cl.is_contiguous():
             x_cl = x_cl.contiguous()
-        # The filter-gradient kernel also takes 4-channel (8-byte) pixels: keep the input as
-        # it came instead of the padded copy whenever that is possible.
         x_bwd = x_cl
-        if Cin <= 4 and x_in.shape[-2] % 16 == 0:
-            x_bwd = F.pad(x_in, (0, 4 - Cin)) if Cin != 4 else x_in
-            if not x_bwd.is_contiguous():
-                x_bwd = x_bwd.contiguous()
         Kout = wh.master.shape[0]
         kd, kh, _ = ksize
 
         def pack():
-            w = wh.master.detach().reshape(Kout, Cin, kd * kh, 3)          # K, C, tap2, kw
-            w = F.pad(w, (0, 1, 0, 0, 0, 8 - Cin, 0, 32 - Kout))            # 32, 8, tap2, 4
-            # core-matrix order of the un-swizzled B operand: [tap2][kw][row][channel]
-            return w.permute(2, 3, 0, 1).contiguous().to(x.dtype)
+            # K index = tap * cr + channel, padded to a multiple of 16; rows padded to 32
+            w = wh.master.detach().reshape(Kout, Cin, kd * kh * 3).permute(0, 2, 1)   # K, tap, C
+            w = F.pad(w, (0, cr - Cin)).reshape(Kout, -1)
+            kpad = (w.shape[1] + 15) // 16 * 16
+            w = F.pad(w, (0, kpad - w.shape[1], 0, 32 - Kout))
+            # [K chunk][32 rows][8 elements]
+            return w.reshape(32, kpad // 8, 8).permute(1, 0, 2).contiguous().to(x.dtype)
 
         wt = wh.packed("c8fwd", x.dtype, pack)
         N, D, H, W, _ = x_cl.shape
