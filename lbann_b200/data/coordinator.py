@@ -125,6 +125,12 @@ class DataCoordinator:
         st = self.modes[mode]
         if st.reader is None:
             return
+        if getattr(st, "primed", False):
+            # the end of the previous epoch already drew this epoch's order and started
+            # fetching its first mini-batch
+            st.primed = False
+            st.pos = 0
+            return
         if st.inflight is not None:
             st.inflight.cancel()
             try:
@@ -221,7 +227,14 @@ class DataCoordinator:
         if pos >= len(st.order):
             st.inflight = None
             return
-        st.inflight = self.pool.submit(self._collate, mode, pos) if self.pool is not None else None
+        st.inflight = self.pool.submit(self._prefetch, mode, pos) if self.pool is not None else None
+
+    def _prefetch(self, mode: str, pos: int) -> Batch:
+        """Background job: build the batch on the host AND enqueue its host-to-device copy on
+        the copy stream, so that the transfer of batch k+1 runs under the compute of batch k."""
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        return self._to_device(self._collate(mode, pos))
 
     def next_batch(self, mode: str) -> Optional[Batch]:
         """The next mini-batch of this rank on the device (None when the epoch is over);
@@ -230,19 +243,28 @@ class DataCoordinator:
         if st.reader is None or st.pos >= len(st.order):
             return None
         if st.inflight is not None:
-            b = st.inflight.result()
+            b = st.inflight.result()          # already on its way to the device
             st.inflight = None
         else:
-            b = self._collate(mode, st.pos)
+            b = self._to_device(self._collate(mode, st.pos))
         st.pos += st.mb
         st.last_indices = b.indices
         if self.background:
             self._submit(mode, st.pos)
-        b = self._to_device(b)
         if b.event is not None:
-            torch.cuda.current_stream(self.device).wait_event(b.event)
+            cur = torch.cuda.current_stream(self.device)
+            cur.wait_event(b.event)
+            for t in b.tensors.values():      # allocated on the copy stream, used on this one
+                t.record_stream(cur)
         if b.end_of_epoch:
             st.epoch += 1
+            if self.background and self.pool is not None:
+                # draw the next epoch's order now and start on its first mini-batch, so the
+                # epoch boundary does not expose a host fetch and a host-to-device copy
+                self._reshuffle(st, mode)
+                st.pos = len(st.order)
+                st.inflight = self.pool.submit(self._prefetch, mode, 0)
+                st.primed = True
         return b
 
     def peek_batch(self, mode: str):
@@ -265,6 +287,10 @@ class DataCoordinator:
         for m, s in state.items():
             st = self.modes[m]
             st.pos, st.epoch, st.mb = int(s["pos"]), int(s["epoch"]), int(s["mb"])
+            if st.inflight is not None:
+                st.inflight.cancel()
+                st.inflight = None
+            st.primed = False
             st.order = np.asarray(s["order"], dtype=np.int64)
             if st.reader is not None and s.get("reader") is not None:
                 st.reader.load_state(s["reader"])
