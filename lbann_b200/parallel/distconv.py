@@ -118,7 +118,26 @@ class DistconvContext:
     def enabled(self, layer) -> bool:
         st = self.strategies.get(layer.name)
         return bool(st is not None and st.is_spatial() and layer.supports_distconv
-                    and self.depth_groups > 1)
+                    and self.depth_groups > 1 and self._feasible(layer))
+
+    def _feasible(self, layer) -> bool:
+        """Can this layer still be computed on depth slabs?  Deep in a network the depth
+        extent falls below what the partition needs (a 2x pooling wants an even number of
+        planes per rank, a convolution at least its halo); such layers are computed
+        sample-parallel instead and the tensor is redistributed in front of them."""
+        dims = layer.in_dims[0] if getattr(layer, "in_dims", None) else None
+        if not dims or len(dims) != 4:
+            return True
+        D, P = int(dims[1]), self.depth_groups
+        if D % P:
+            return False
+        local = D // P
+        if layer.type in ("convolution", "deconvolution"):
+            k, s, d = layer.ksize[0], layer.stride[0], layer.dil[0]
+            return local % s == 0 and local >= (k - 1) // 2 * d and local >= 1
+        if layer.type == "pooling":
+            return local % layer.stride[0] == 0 and local >= layer.k[0] // 2
+        return local >= 1
 
     # ------------------------------------------------------------------ distribution bookkeeping
     def adapt_inputs(self, model, layer, xs):

@@ -14,18 +14,18 @@ from lbann_b200.models.cosmoflow import construct_cosmoflow_model, synthetic_rea
 from lbann_b200.utils import options as opts  # noqa: E402
 
 
-def cosmoflow(depth_groups, steps, dtype):
+def cosmoflow(depth_groups, steps, dtype, width=32):
     o = opts.reset()
     o.set("default_dtype", dtype)
     if os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cpu":
         o.set("disable_cuda", True)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     ps = lbann.get_parallel_strategy_args(depth_groups=depth_groups) if depth_groups > 1 else None
-    model = construct_cosmoflow_model(32, 4, 4, num_epochs=1, channels=(8, 16, 16), pool_mode="max",
+    model = construct_cosmoflow_model(width, 4, 4, num_epochs=1, channels=(8, 16, 16), pool_mode="max",
                                       conv_bias=False, fc_sizes=(32, 16), parallel_strategy=ps)
     exp = lbann.proto.serialize.build_experiment(
         trainer=lbann.Trainer(mini_batch_size=4, random_seed=5), model=model,
-        data_reader=synthetic_reader(16, 32, 4, 4),
+        data_reader=synthetic_reader(16, width, 4, 4),
         optimizer=lbann.SGD(learn_rate=0.01, momentum=0.9))
     tr = ExecTrainer(exp)
     m = tr.build_model(exp.model)
@@ -95,7 +95,8 @@ if __name__ == "__main__":
     if what == "comm":
         res = comm_kernels()
     elif what == "cosmoflow":
-        res = cosmoflow(int(sys.argv[3]), int(sys.argv[4]), sys.argv[5] if len(sys.argv) > 5 else "float")
+        res = cosmoflow(int(sys.argv[3]), int(sys.argv[4]), sys.argv[5] if len(sys.argv) > 5 else "float",
+                        int(sys.argv[6]) if len(sys.argv) > 6 else 32)
     else:
         raise SystemExit(f"unknown job {what}")
     if int(os.environ.get("RANK", "0")) == 0:

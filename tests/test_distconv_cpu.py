@@ -34,3 +34,16 @@ def test_distconv_two_ranks_matches_single(tmp_path):
         assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], dist["losses"])
     for k, v in single["weight_norms"].items():
         assert abs(v - dist["weight_norms"][k]) <= 1e-3 * max(1.0, abs(v)), k
+
+
+def test_distconv_falls_back_to_sample_parallel_when_depth_runs_out(tmp_path):
+    """Four ranks on a 16^3 volume with three conv/pool blocks: the last pooling would see
+    one plane per rank, so it (and what follows) is computed sample-parallel after a
+    redistribution; the result still matches the single-process run."""
+    single = _run(1, ["cosmoflow", "1", "2", "float", "16"], str(tmp_path / "a.json"))
+    dist = _run(4, ["cosmoflow", "4", "2", "float", "16"], str(tmp_path / "b.json"), timeout=600)
+    assert dist["world"] == 4
+    for a, b in zip(single["losses"], dist["losses"]):
+        assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], dist["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - dist["weight_norms"][k]) <= 1e-3 * max(1.0, abs(v)), k
