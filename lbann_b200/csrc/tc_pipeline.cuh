@@ -31,6 +31,13 @@ struct EpiParams {
   int act;            // Act
   float act_param;
   long long ldc;      // elements between consecutive output rows
+  // Reduce-scatter epilogue (fused GEMM -> reduce-scatter): when rs_ranks > 0 the tile is
+  // not stored but ADDED (fp32 atomics, over NVLink for remote owners) into the output
+  // shard of the rank that owns the row: owner = row / rs_rows, buffer rs_ptr[owner] with
+  // row pitch ldc.  alpha applies; bias, beta and activation do not.
+  int rs_ranks = 0;
+  int rs_rows = 0;
+  float* rs_ptr[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
 template <int BN>
@@ -114,6 +121,20 @@ __device__ __forceinline__ void tc_epilogue_rows(uint32_t taddr, bool row_ok, lo
     const long long off = row_off + n0 + c;
     const int ncol = min(32, n_total - (n0 + c));
     const bool full = ncol == 32;
+    if (e.rs_ranks > 0) {
+      const int owner = row_index / e.rs_rows;
+      float* dst = e.rs_ptr[owner] + (long long)(row_index - owner * e.rs_rows) * e.ldc + n0 + c;
+      if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+        for (int j = 0; j < 32; j += 4)
+          atomicAdd(reinterpret_cast<float4*>(dst + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (j < ncol) atomicAdd(dst + j, v[j]);
+      }
+      continue;
+    }
     if (bias_mode == 1) {
       const float* bp = e.bias + n0 + c;
       if (full) {
@@ -168,6 +189,23 @@ __device__ __forceinline__ void tc_epilogue_rows(uint32_t taddr, bool row_ok, lo
   }
 }
 
+// A policy may reserve the LAST `Policy::helpers(p)` CTAs of the grid for work of its own
+// (e.g. copying a peer's operand shard into local memory while the other CTAs multiply):
+// such a CTA runs Policy::helper_cta and leaves before any tile machinery is set up.
+template <class Policy, class = void>
+struct TcHelpers {
+  __device__ static int count(const typename Policy::Params&) { return 0; }
+  __device__ static void run(const typename Policy::Params&, int, int, uint8_t*, int*) {}
+};
+template <class Policy>
+struct TcHelpers<Policy, typename Policy::HasHelpers> {
+  __device__ static int count(const typename Policy::Params& p) { return Policy::helpers(p); }
+  __device__ static void run(const typename Policy::Params& p, int index, int n, uint8_t* smem,
+                             int* status) {
+    Policy::helper_cta(p, index, n, smem, status);
+  }
+};
+
 template <class Policy>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
@@ -179,6 +217,13 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
 
   extern __shared__ uint8_t smem_raw[];
   __shared__ TcShared sh;
+
+  const int n_helpers = TcHelpers<Policy>::count(p);
+  const int n_workers = (int)gridDim.x - n_helpers;      // CTAs that walk tiles
+  if ((int)blockIdx.x >= n_workers) {
+    TcHelpers<Policy>::run(p, (int)blockIdx.x - n_workers, n_helpers, smem_raw, status);
+    return;
+  }
 
   const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
   const int warp = threadIdx.x >> 5;
@@ -220,7 +265,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     // the boxes of a stage enter the copy engine side by side instead of one after another.
     uint32_t it = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+    for (int t = blockIdx.x; t < num_tiles && ok; t += n_workers) {
       const typename Policy::Tile tile = Policy::decode(p, t);
       for (int k = 0; k < k_iters; ++k, ++it) {
         const uint32_t s = it % S;
@@ -263,7 +308,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t it = 0;
       uint32_t local_tile = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
+      for (int t = blockIdx.x; t < num_tiles && ok; t += n_workers, ++local_tile) {
         const uint32_t acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
         if (!mbar_wait_bounded(smem_u32(&sh.tmem_empty[acc]), acc_ph ^ 1, abort_flag)) {
@@ -296,7 +341,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     // ------------------------------- epilogue -------------------------------
     uint32_t local_tile = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x, ++local_tile) {
+    for (int t = blockIdx.x; t < num_tiles && ok; t += n_workers, ++local_tile) {
       const typename Policy::Tile tile = Policy::decode(p, t);
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;

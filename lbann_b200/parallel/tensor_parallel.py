@@ -1,0 +1,228 @@
+"""Sharded fully-connected layers on the fused GEMM + collective kernels.
+
+Three differentiable building blocks (``x`` is ``[tokens, features]``, weights are
+``[out_features, in_features]`` like the reference's fully-connected layer):
+
+``ColumnParallelLinear``  weights split by OUTPUT rows, activations split by tokens on
+    entry (sequence-parallel): forward all-gather -> GEMM, the result ``[tokens, out/P]``
+    stays split by features.
+``RowParallelLinear``     weights split by INPUT columns, activations split by features on
+    entry: forward GEMM -> reduce-scatter, the result ``[tokens/P, out]`` is split by tokens
+    again.  A column-parallel layer followed by a row-parallel one is the transformer
+    FFN / attention projection pair; it reproduces what the reference obtains from a
+    model-parallel (MC,MR-distributed) fully connected layer
+    (src/layers/learning/fully_connected.cpp:638-808) without ever materialising a
+    gathered activation or an unreduced output.
+``ShardedLinear``         FSDP-style weights (split by output rows, optimizer state only for
+    the local rows; src/weights/data_type_weights.cpp:244-266,456-462): forward gathers
+    the weight tile by tile inside the GEMM, backward multiplies by the staged copy and
+    reduce-scatters the weight gradient straight into the local fp32 gradient shard
+    (include/lbann/optimizers/optimizer_impl.hpp:113-169 does all-reduce + copy).
+
+All of them run on the symmetric-memory kernels on GPUs and on torch.distributed
+collectives on CPU (gloo), so the same code is covered by the CPU tests.
+"""
+from __future__ import annotations
+
+from typing import Optional
+
+import torch
+
+from .fused import FusedGemm
+from .symm import SymmetricBuffer, SymmetricGroup
+
+
+class _Workspace:
+    """Symmetric buffers of one layer, allocated collectively on first use."""
+
+    def __init__(self, group: SymmetricGroup):
+        self.group = group
+        self.bufs = {}
+
+    def get(self, key, nbytes) -> SymmetricBuffer:
+        b = self.bufs.get(key)
+        if b is None or b.nbytes < nbytes:
+            b = self.group.alloc(nbytes)
+            self.bufs[key] = b
+        return b
+
+
+def _esize(dtype) -> int:
+    return torch.empty((), dtype=dtype).element_size()
+
+
+def _mm_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a^T @ b in fp32 (weight-gradient form) on the tcgen05 GEMM when on a GPU."""
+    if a.is_cuda and a.dtype in (torch.float16, torch.bfloat16):
+        from ..ops.gemm import gemm
+        return gemm(a.contiguous(), b.contiguous(), trans_a=True, out_dtype=torch.float32)
+    return a.float().t() @ b.float()
+
+
+class _ColumnParallel(torch.autograd.Function):
+    """y[:, rank's features] = gather(x) . w_local^T."""
+
+    @staticmethod
+    def forward(ctx, x_local, w_local, layer):
+        g, fg, ws = layer.group, layer.fused, layer.ws
+        rows, k = x_local.shape
+        dt = x_local.dtype
+        xbuf = ws.get(("x", rows, k, dt), rows * k * _esize(dt))
+        xbuf.view(dt, rows * k).view(rows, k).copy_(x_local)
+        y = fg.allgather_gemm(xbuf, rows, k, w_local.to(dt), sharded="a", dtype=dt)
+        ctx.layer, ctx.shape = layer, (rows, k)
+        ctx.save_for_backward(w_local)
+        ctx.xbuf = xbuf
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        layer = ctx.layer
+        g, fg, ws = layer.group, layer.fused, layer.ws
+        (w_local,) = ctx.saved_tensors
+        rows, k = ctx.shape
+        dt = dy.dtype
+        P = g.world
+        dy = dy.contiguous()
+        # dx[tokens, k] = sum over ranks of dy[:, f_r] . w_r, scattered by tokens
+        obuf = ws.get(("dx", rows, k), rows * k * 4)
+        dx = fg.gemm_reduce_scatter(dy, w_local.to(dt), obuf, rows, trans_b=True).to(dt)
+        # dw_r[f_r, k] = dy[:, f_r]^T . gather(x): the gathered operand is split along the
+        # reduction dimension here, which the fused kernel does not take: gather, then GEMM
+        full = layer.gather_rows(ctx.xbuf, rows, k, dt)
+        dw = _mm_tn(dy, full)
+        return dx, dw.to(w_local.dtype), None
+
+
+class ColumnParallelLinear:
+    def __init__(self, group: SymmetricGroup, fused: Optional[FusedGemm] = None):
+        self.group = group
+        self.fused = fused or FusedGemm(group)
+        self.ws = _Workspace(group)
+
+    def gather_rows(self, buf: SymmetricBuffer, rows: int, k: int, dtype) -> torch.Tensor:
+        """All ranks' ``[rows, k]`` blocks of a symmetric buffer as one local tensor."""
+        g = self.group
+        local = buf.view(dtype, rows * k).view(rows, k)
+        if g.world == 1:
+            return local
+        import torch.distributed as dist
+        full = torch.empty((g.world * rows, k), dtype=dtype, device=local.device)
+        dist.all_gather_into_tensor(full, local.contiguous(), group=g.pg)
+        return full
+
+    def __call__(self, x_local: torch.Tensor, w_local: torch.Tensor) -> torch.Tensor:
+        return _ColumnParallel.apply(x_local, w_local, self)
+
+
+class _RowParallel(torch.autograd.Function):
+    """y[rank's tokens] = sum over ranks of x[:, f_r] . w[:, f_r]^T."""
+
+    @staticmethod
+    def forward(ctx, x_feat, w_local, layer):
+        g, fg, ws = layer.group, layer.fused, layer.ws
+        tokens, kl = x_feat.shape
+        n = w_local.shape[0]
+        P = g.world
+        rows = tokens // P
+        dt = x_feat.dtype
+        obuf = ws.get(("y", rows, n), rows * n * 4)
+        y = fg.gemm_reduce_scatter(x_feat.contiguous(), w_local.to(dt), obuf, rows).to(dt)
+        ctx.layer, ctx.dims = layer, (tokens, kl, n, rows)
+        ctx.save_for_backward(x_feat, w_local)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy_local):
+        layer = ctx.layer
+        g, fg, ws = layer.group, layer.fused, layer.ws
+        x_feat, w_local = ctx.saved_tensors
+        tokens, kl, n, rows = ctx.dims
+        dt = dy_local.dtype
+        # dx[:, f_r] = gather(dy)[tokens, n] . w[:, f_r]   (all-gather -> GEMM)
+        dbuf = ws.get(("dy", rows, n, dt), rows * n * _esize(dt))
+        dbuf.view(dt, rows * n).view(rows, n).copy_(dy_local)
+        dx = fg.allgather_gemm(dbuf, rows, n, w_local.to(dt).t().contiguous(), sharded="a", dtype=dt)
+        # dw[:, f_r] = gather(dy)^T . x[:, f_r]
+        full = layer.gather_rows(dbuf, rows, n, dt)
+        dw = _mm_tn(full, x_feat)
+        return dx, dw.to(w_local.dtype), None
+
+
+class RowParallelLinear(ColumnParallelLinear):
+    def __call__(self, x_feat: torch.Tensor, w_local: torch.Tensor) -> torch.Tensor:
+        return _RowParallel.apply(x_feat, w_local, self)
+
+
+class _Sharded(torch.autograd.Function):
+    """y = x . gather(w_shards)^T with the gather inside the GEMM; dW reduce-scattered."""
+
+    @staticmethod
+    def forward(ctx, x, w_shard_leaf, layer):
+        g, fg = layer.group, layer.fused
+        rows, k = layer.shard_rows, layer.k
+        dt = x.dtype
+        wbuf = layer.compute_shard(dt)
+        y = fg.allgather_gemm(wbuf, rows, k, x.contiguous(), sharded="b", dtype=dt)
+        ctx.layer = layer
+        ctx.save_for_backward(x)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        layer = ctx.layer
+        g, fg = layer.group, layer.fused
+        (x,) = ctx.saved_tensors
+        rows, k = layer.shard_rows, layer.k
+        dt = dy.dtype
+        dy = dy.contiguous()
+        w_full = layer.gathered_weight(dt)
+        if x.is_cuda:
+            from ..ops.gemm import gemm
+            dx = gemm(dy, w_full)
+        else:
+            dx = (dy.float() @ w_full.float()).to(dt)
+        # dW[n, k] = dy^T . x summed over the data-parallel ranks, rows scattered to their owners
+        gbuf = layer.grad_buffer()
+        dw = fg.gemm_reduce_scatter(dy, x.contiguous(), gbuf, rows, trans_a=True, trans_b=True,
+                                    zero=True)
+        return dx, dw.to(layer.w_shard.dtype), None
+
+
+class ShardedLinear:
+    """Weights ``[P * shard_rows, k]`` of which this rank owns rows
+    ``[rank * shard_rows, (rank + 1) * shard_rows)`` (fp32 master ``w_shard``)."""
+
+    def __init__(self, group: SymmetricGroup, w_shard: torch.Tensor, fused: Optional[FusedGemm] = None):
+        self.group = group
+        self.fused = fused or FusedGemm(group)
+        self.ws = _Workspace(group)
+        self.w_shard = w_shard
+        self.shard_rows, self.k = w_shard.shape
+
+    def compute_shard(self, dtype) -> SymmetricBuffer:
+        """This rank's rows in the compute dtype, in symmetric memory (refreshed per call)."""
+        n = self.shard_rows * self.k
+        buf = self.ws.get(("w", dtype), n * _esize(dtype))
+        buf.view(dtype, n).view(self.shard_rows, self.k).copy_(self.w_shard.detach())
+        return buf
+
+    def gathered_weight(self, dtype) -> torch.Tensor:
+        """The full weight matrix for the data-gradient product: the staged copy that the
+        forward kernel left in local memory when it staged, else a plain gather."""
+        key = (self.shard_rows, self.k, dtype)
+        st = self.fused._stage.get(key)
+        g = self.group
+        if st is not None and g.native:
+            full = st[0]
+            # the local rows are read from the shard itself in the forward kernel: fill them in
+            full[g.rank * self.shard_rows:(g.rank + 1) * self.shard_rows].copy_(self.w_shard.detach())
+            return full
+        buf = self.ws.get(("w", dtype), self.shard_rows * self.k * _esize(dtype))
+        return ColumnParallelLinear.gather_rows(self, buf, self.shard_rows, self.k, dtype)
+
+    def grad_buffer(self) -> SymmetricBuffer:
+        return self.ws.get(("dw",), self.shard_rows * self.k * 4)
+
+    def __call__(self, x: torch.Tensor) -> torch.Tensor:
+        return _Sharded.apply(x, self.w_shard, self)

@@ -90,10 +90,147 @@ def comm_kernels():
     return res
 
 
+def fused_gemm():
+    """All-gather -> GEMM and GEMM -> reduce-scatter against fp32 references."""
+    from lbann_b200.ops import native
+    from lbann_b200.parallel.comm import LbannComm
+    from lbann_b200.parallel.fused import FusedGemm
+    from lbann_b200.parallel.symm import SymmetricGroup
+    rank = int(os.environ.get("RANK", "0"))
+    use_cuda = os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cuda"
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_cuda else torch.device("cpu")
+    if use_cuda:
+        torch.cuda.set_device(dev)
+    comm = LbannComm(device=dev)
+    g = SymmetricGroup(dev, pg=comm.trainer_group)
+    P = g.world
+    fg = FusedGemm(g)
+    dt = torch.bfloat16
+    res = {"world": P, "native": g.native}
+    gen = torch.Generator().manual_seed(1234)
+    rows, K, N = (256, 512, 384) if use_cuda else (16, 32, 24)
+    X = torch.randn(P * rows, K, generator=gen).to(dt)         # the same on every rank
+    W = torch.randn(N, K, generator=gen).to(dt)
+    # --- left operand sharded by rows
+    buf = g.alloc(rows * K * 2)
+    buf.view(dt, rows * K).view(rows, K).copy_(X[rank * rows:(rank + 1) * rows])
+    y = fg.allgather_gemm(buf, rows, K, W.to(dev), sharded="a", dtype=dt, out_dtype=torch.float32)
+    ref = X.float() @ W.float().t()
+    res["ag_a"] = bool(torch.allclose(y.cpu(), ref, rtol=2e-2, atol=2e-1))
+    for rep in range(2):     # staged through copying CTAs; twice: the flags carry epochs
+        y = fg.allgather_gemm(buf, rows, K, W.to(dev), sharded="a", dtype=dt, out_dtype=torch.float32,
+                              staged=True)
+        res[f"ag_a_staged{rep}"] = bool(torch.allclose(y.cpu(), ref, rtol=2e-2, atol=2e-1))
+    # --- right operand (weights) sharded by rows
+    wrows = N // P if (N // P) % (64 if use_cuda else 1) == 0 else N
+    if use_cuda:
+        wrows = 128
+    Wf = torch.randn(P * wrows, K, generator=gen).to(dt)
+    wbuf = g.alloc(wrows * K * 2)
+    wbuf.view(dt, wrows * K).view(wrows, K).copy_(Wf[rank * wrows:(rank + 1) * wrows])
+    xin = torch.randn(160 if use_cuda else 8, K, generator=gen).to(dt)
+    y2 = fg.allgather_gemm(wbuf, wrows, K, xin.to(dev), sharded="b", dtype=dt, out_dtype=torch.float32)
+    res["ag_b"] = bool(torch.allclose(y2.cpu(), xin.float() @ Wf.float().t(), rtol=2e-2, atol=2e-1))
+    y2 = fg.allgather_gemm(wbuf, wrows, K, xin.to(dev), sharded="b", dtype=dt, out_dtype=torch.float32,
+                           staged=True)
+    res["ag_b_staged"] = bool(torch.allclose(y2.cpu(), xin.float() @ Wf.float().t(), rtol=2e-2, atol=2e-1))
+    # --- K-sliced product, result scattered by rows
+    M2, N2, Kl = (P * 128, 320, 256) if use_cuda else (P * 4, 12, 16)
+    A = torch.randn(M2, P * Kl, generator=gen).to(dt)
+    B = torch.randn(N2, P * Kl, generator=gen).to(dt)
+    obuf = g.alloc((M2 // P) * N2 * 4)
+    a_loc = A[:, rank * Kl:(rank + 1) * Kl].contiguous().to(dev)
+    b_loc = B[:, rank * Kl:(rank + 1) * Kl].contiguous().to(dev)
+    mine = fg.gemm_reduce_scatter(a_loc, b_loc, obuf, M2 // P)
+    full = A.float() @ B.float().t()
+    want = full[rank * (M2 // P):(rank + 1) * (M2 // P)]
+    res["rs"] = bool(torch.allclose(mine.cpu(), want, rtol=2e-2, atol=5e-1))
+    # transposed operands (weight-gradient form: dW = dY^T . X over the sample slices)
+    mine2 = fg.gemm_reduce_scatter(a_loc.t().contiguous(), b_loc.t().contiguous(), obuf, M2 // P,
+                                   trans_a=True, trans_b=True)
+    res["rs_t"] = bool(torch.allclose(mine2.cpu(), want, rtol=2e-2, atol=5e-1))
+    if use_cuda:
+        torch.cuda.synchronize()
+        res["status"] = native.consume_status(False)
+    oks = comm.world_gather_object({k: v for k, v in res.items() if k not in ("world", "native")})
+    res["all_ranks_ok"] = all(all(bool(x) if k != "status" else x == 0 for k, x in o.items()) for o in oks)
+    return res
+
+
+def tensor_parallel():
+    """Column/row-parallel and sharded (FSDP) linear layers against dense autograd."""
+    from lbann_b200.parallel.comm import LbannComm
+    from lbann_b200.parallel.symm import SymmetricGroup
+    from lbann_b200.parallel.tensor_parallel import (ColumnParallelLinear, RowParallelLinear,
+                                                     ShardedLinear)
+    rank = int(os.environ.get("RANK", "0"))
+    use_cuda = os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cuda"
+    dev = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0"))) if use_cuda else torch.device("cpu")
+    if use_cuda:
+        torch.cuda.set_device(dev)
+    comm = LbannComm(device=dev)
+    g = SymmetricGroup(dev, pg=comm.trainer_group)
+    P = g.world
+    dt = torch.bfloat16 if use_cuda else torch.float32
+    tol = dict(rtol=3e-2, atol=3e-1) if use_cuda else dict(rtol=1e-4, atol=1e-4)
+    gen = torch.Generator().manual_seed(7)
+    T, D, F = (P * 128, 256, P * 256) if use_cuda else (P * 4, 8, P * 6)
+    X = torch.randn(T, D, generator=gen).to(dt)
+    W1 = (torch.randn(F, D, generator=gen) / D ** 0.5).to(dt)
+    W2 = (torch.randn(D, F, generator=gen) / F ** 0.5).to(dt)
+    DY = torch.randn(T, D, generator=gen).to(dt)
+    # dense reference (fp32 autograd)
+    xr, w1r, w2r = (t.float().clone().detach().requires_grad_(True) for t in (X, W1, W2))
+    yr = (xr @ w1r.t()) @ w2r.t()
+    yr.backward(DY.float())
+    res = {"world": P}
+    rows, fl = T // P, F // P
+    x = X[rank * rows:(rank + 1) * rows].to(dev).clone().detach().requires_grad_(True)
+    w1 = W1[rank * fl:(rank + 1) * fl].to(dev).clone().detach().requires_grad_(True)   # output rows
+    w2 = W2[:, rank * fl:(rank + 1) * fl].contiguous().to(dev).clone().detach().requires_grad_(True)   # input columns
+    col, row = ColumnParallelLinear(g), RowParallelLinear(g)
+    h = col(x, w1)                    # [T, F/P]
+    y = row(h, w2)                    # [T/P, D]
+    y.backward(DY[rank * rows:(rank + 1) * rows].to(dev))
+    sl = slice(rank * rows, (rank + 1) * rows)
+    res["tp_fwd"] = bool(torch.allclose(y.detach().float().cpu(), yr[sl].detach(), **tol))
+    res["tp_dx"] = bool(torch.allclose(x.grad.float().cpu(), xr.grad[sl], **tol))
+    res["tp_dw1"] = bool(torch.allclose(w1.grad.float().cpu(), w1r.grad[rank * fl:(rank + 1) * fl], **tol))
+    res["tp_dw2"] = bool(torch.allclose(w2.grad.float().cpu(), w2r.grad[:, rank * fl:(rank + 1) * fl], **tol))
+    # sharded weights, data-parallel activations: every rank has its own tokens
+    Xs = torch.randn(P, rows, D, generator=gen).to(dt)
+    DYs = torch.randn(P, rows, F, generator=gen).to(dt)
+    w_master = W1[rank * fl:(rank + 1) * fl].float().to(dev).clone().detach().requires_grad_(True)
+    lin = ShardedLinear(g, w_master)
+    xs = Xs[rank].to(dev).clone().detach().requires_grad_(True)
+    ys = lin(xs)
+    ys.backward(DYs[rank].to(dev))
+    wd = W1.float().clone().detach().requires_grad_(True)
+    xd = Xs.float().clone().detach().requires_grad_(True)
+    yd = xd @ wd.t()
+    yd.backward(DYs.float())
+    res["fsdp_fwd"] = bool(torch.allclose(ys.detach().float().cpu(), yd[rank].detach(), **tol))
+    res["fsdp_dx"] = bool(torch.allclose(xs.grad.float().cpu(), xd.grad[rank], **tol))
+    res["fsdp_dw"] = bool(torch.allclose(w_master.grad.float().cpu(), wd.grad[rank * fl:(rank + 1) * fl], **tol))
+    res["fsdp_dw_err"] = float((w_master.grad.float().cpu() - wd.grad[rank * fl:(rank + 1) * fl]).abs().max())
+    if use_cuda:
+        from lbann_b200.ops import native
+        torch.cuda.synchronize()
+        res["status"] = native.consume_status(False)
+    oks = comm.world_gather_object({k: v for k, v in res.items() if k != "world"})
+    res["all_ranks_ok"] = all(all((bool(x) if k != "status" else x == 0) for k, x in o.items() if not k.endswith("_err")) for o in oks)
+    res["detail"] = oks
+    return res
+
+
 if __name__ == "__main__":
     what, out = sys.argv[1], sys.argv[2]
     if what == "comm":
         res = comm_kernels()
+    elif what == "fused":
+        res = fused_gemm()
+    elif what == "tp":
+        res = tensor_parallel()
     elif what == "cosmoflow":
         res = cosmoflow(int(sys.argv[3]), int(sys.argv[4]), sys.argv[5] if len(sys.argv) > 5 else "float",
                         int(sys.argv[6]) if len(sys.argv) > 6 else 32)

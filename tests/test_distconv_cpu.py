@@ -47,3 +47,17 @@ def test_distconv_falls_back_to_sample_parallel_when_depth_runs_out(tmp_path):
         assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], dist["losses"])
     for k, v in single["weight_norms"].items():
         assert abs(v - dist["weight_norms"][k]) <= 1e-3 * max(1.0, abs(v)), k
+
+
+def test_fused_gemm_collectives_gloo(tmp_path):
+    """all-gather -> GEMM and GEMM -> reduce-scatter entry points on two CPU ranks (the
+    torch.distributed fall-back path; the kernels themselves are covered on GPUs)."""
+    res = _run(2, ["fused"], str(tmp_path / "f.json"))
+    assert res["world"] == 2 and res["all_ranks_ok"], res
+
+
+def test_tensor_parallel_and_sharded_linear_gloo(tmp_path):
+    """Column-/row-parallel FFN pair and FSDP-style sharded linear layer on two CPU ranks
+    reproduce the dense fp32 forward values and all gradients."""
+    res = _run(2, ["tp"], str(tmp_path / "t.json"))
+    assert res["world"] == 2 and res["all_ranks_ok"], res

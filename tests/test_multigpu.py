@@ -26,3 +26,17 @@ def test_distconv_two_gpus_matches_one(tmp_path):
     dist = _run(2, ["cosmoflow", "2", "3", "fp16"], str(tmp_path / "b.json"), ENV)
     for a, b in zip(single["losses"], dist["losses"]):
         assert abs(a - b) <= 3e-2 * max(1.0, abs(a)), (single["losses"], dist["losses"])
+
+
+@needs2
+def test_fused_gemm_collectives(tmp_path):
+    n = 2
+    res = _run(n, ["fused"], str(tmp_path / "f.json"), ENV)
+    assert res["native"] and res["world"] == n
+    assert res["all_ranks_ok"], res
+
+
+@needs2
+def test_tensor_parallel_and_sharded_linear(tmp_path):
+    res = _run(2, ["tp"], str(tmp_path / "t.json"), ENV)
+    assert res["world"] == 2 and res["all_ranks_ok"], res
