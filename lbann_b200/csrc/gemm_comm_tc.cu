@@ -49,6 +49,7 @@ struct GemmCommPolicy {
   static constexpr int BN = BN_;
   using G = StageGeom<BN>;
   using HasHelpers = void;
+  using HasEpilogue = void;
 
   struct Params {
     int M, N, K;
@@ -70,6 +71,43 @@ struct GemmCommPolicy {
   };
 
   __device__ static int helpers(const Params& p) { return p.staged ? p.st.helpers : 0; }
+
+  // Reduce-scatter epilogue: the 32 x 32 block a warp reads from TMEM (one row per lane) is
+  // turned through shared memory so that every store / reduction instruction of the warp
+  // covers 128 contiguous bytes of ONE output row.  Over NVLink that is one transaction
+  // where a row-per-lane float4 store makes thirty-two of 16 bytes.
+  __device__ static void epilogue(uint32_t taddr, bool row_ok, long long row_off, int n0,
+                                  int n_total, int row_index, const EpiParams& e, const Params& p) {
+    if (e.rs_ranks == 0) {
+      tc_epilogue_rows<BN>(taddr, row_ok, row_off, n0, n_total, row_index, e);
+      return;
+    }
+    __shared__ float stg[4][32][33];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row_first = row_index - lane;           // first row of this warp's block
+#pragma unroll 1
+    for (int c = 0; c < BN; c += 32) {
+      if (n0 + c >= n_total) break;
+      uint32_t r[32];
+      __syncwarp();
+      tmem_ld_32x32(taddr + c, r);
+      tmem_ld_wait();
+#pragma unroll
+      for (int j = 0; j < 32; ++j) stg[warp][lane][j] = __uint_as_float(r[j]) * e.alpha;
+      __syncwarp();
+      const int col = n0 + c + lane;
+#pragma unroll 4
+      for (int rr = 0; rr < 32; ++rr) {
+        const int m = row_first + rr;
+        if (m >= p.M || col >= n_total) continue;
+        const int owner = m / e.rs_rows;
+        float* dst = e.rs_ptr[owner] + (long long)(m - owner * e.rs_rows) * e.ldc + col;
+        const float v = stg[warp][rr][lane];
+        if (e.rs_store) *dst = v;
+        else atomicAdd(dst, v);
+      }
+    }
+  }
 
   // ---- copying CTA: one thread drives a ring of bulk copies -----------------------------
   __device__ static void helper_cta(const Params& p, int index, int n, uint8_t* smem, int* status) {
@@ -279,6 +317,18 @@ static bool encode_operand(CUtensorMap* tm, const void* base, int rows, int K, l
 }  // namespace lb
 
 namespace lb {
+__global__ void rs_reduce_kernel(float4* __restrict__ out, const float4* __restrict__ slots,
+                                 int nslots, long long slot4, long long n4) {
+  for (long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x; i < n4;
+       i += (long long)gridDim.x * blockDim.x) {
+    float4 a = out[i];
+    for (int s = 0; s < nslots; ++s) {
+      const float4 b = slots[s * slot4 + i];
+      a.x += b.x; a.y += b.y; a.z += b.z; a.w += b.w;
+    }
+    out[i] = a;
+  }
+}
 struct MapCacheEntry { void* dev; CUtensorMap maps[32]; };
 static MapCacheEntry g_map_cache[8];
 static int g_map_cache_next = 0;
@@ -303,14 +353,18 @@ void lb_gemm_comm_forget(void* maps_dev) {
 //       one uint32 per 128 rows of it (never equal to `epoch` before the call), `helpers`
 //       the number of copying CTAs.  gathered == nullptr: TMA reads the peers directly.
 //   rs_ptrs: nullptr, or `ranks` fp32 output shards of rs_rows rows each, pitch ldc: the
-//       result is ADDED there instead of being stored to C (which may then be nullptr).
+//       result is ADDED there (fp32 atomics) instead of being stored to C (which may then be
+//       nullptr).  rs_store = 1: plain stores instead - rs_ptrs[r] is then the slot that rank
+//       r keeps for THIS rank's partial result (its own output shard for r == rank), and
+//       lb_rs_reduce sums the slots after a rendezvous.
 // Returns 0, a cudaError_t (> 0), or -1 for a bad argument.
 int lb_gemm_comm_tc(const void* A, const void* B, void* C, int M, int N, int K, long long lda,
                     long long ldb, long long ldc, int a_mn, int b_mn, int in_dtype, int out_dtype,
                     float alpha, const void* const* a_shard_ptrs, int a_rows,
                     const void* const* b_shard_ptrs, int b_rows, int ranks, int rank,
                     void* maps_dev, void* gathered, unsigned int* flags, unsigned int epoch,
-                    int helpers, float* const* rs_ptrs, int rs_rows, void* stream_) {
+                    int helpers, float* const* rs_ptrs, int rs_rows, int rs_store,
+                    void* stream_) {
   using namespace lb;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0 || ranks < 1 || ranks > 8 || rank < 0 || rank >= ranks) return -1;
@@ -389,7 +443,7 @@ int lb_gemm_comm_tc(const void* A, const void* B, void* C, int M, int N, int K, 
     p.epi.out_dtype = out_dtype; p.epi.bias_mode = 0; p.epi.act = 0;                  \
     p.epi.act_param = 0.f; p.epi.ldc = ldc;                                           \
     if (rs_ptrs) {                                                                    \
-      p.epi.rs_ranks = ranks; p.epi.rs_rows = rs_rows;                                \
+      p.epi.rs_ranks = ranks; p.epi.rs_rows = rs_rows; p.epi.rs_store = rs_store;     \
       for (int r = 0; r < ranks; ++r) p.epi.rs_ptr[r] = rs_ptrs[r];                   \
     }                                                                                 \
     return launch_gemm_comm<BN_>(tmA, tmB, p, stream);                                \
@@ -398,6 +452,21 @@ int lb_gemm_comm_tc(const void* A, const void* B, void* C, int M, int N, int K, 
   if (BN == 128) LB_LAUNCH(128)
   LB_LAUNCH(64)
 #undef LB_LAUNCH
+}
+
+// out[i] += sum over s < nslots of slots[s * slot_elems + i]   (fp32, n elements, n % 4 == 0)
+int lb_rs_reduce(float* out, const float* slots, int nslots, long long slot_elems, long long n,
+                 void* stream_) {
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  if (n <= 0 || (n % 4) || nslots < 0) return -1;
+  const long long n4 = n / 4;
+  int blocks = (int)((n4 + 255) / 256);
+  const int cap = 8 * lbhost::sm_count();
+  if (blocks > cap) blocks = cap;
+  lb::rs_reduce_kernel<<<blocks, 256, 0, stream>>>(reinterpret_cast<float4*>(out),
+                                                   reinterpret_cast<const float4*>(slots), nslots,
+                                                   slot_elems / 4, n4);
+  return (int)cudaGetLastError();
 }
 
 }  // extern "C"

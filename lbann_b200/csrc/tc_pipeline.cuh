@@ -37,6 +37,7 @@ struct EpiParams {
   // row pitch ldc.  alpha applies; bias, beta and activation do not.
   int rs_ranks = 0;
   int rs_rows = 0;
+  int rs_store = 0;   // 1: plain stores (every source rank has its own slot at the owner)
   float* rs_ptr[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
@@ -124,7 +125,17 @@ __device__ __forceinline__ void tc_epilogue_rows(uint32_t taddr, bool row_ok, lo
     if (e.rs_ranks > 0) {
       const int owner = row_index / e.rs_rows;
       float* dst = e.rs_ptr[owner] + (long long)(row_index - owner * e.rs_rows) * e.ldc + n0 + c;
-      if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+      if (e.rs_store) {
+        if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j)
+            if (j < ncol) dst[j] = v[j];
+        }
+      } else if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
         for (int j = 0; j < 32; j += 4)
           atomicAdd(reinterpret_cast<float4*>(dst + j), make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
@@ -203,6 +214,23 @@ struct TcHelpers<Policy, typename Policy::HasHelpers> {
   __device__ static void run(const typename Policy::Params& p, int index, int n, uint8_t* smem,
                              int* status) {
     Policy::helper_cta(p, index, n, smem, status);
+  }
+};
+
+// A policy may bring its own epilogue (`using HasEpilogue = void;` plus a static
+// `epilogue(...)`); the default is tc_epilogue_rows.
+template <class Policy, class = void>
+struct TcEpilogue {
+  __device__ static void run(uint32_t taddr, bool row_ok, long long row_off, int n0, int n_total,
+                             int row_index, const EpiParams& e, const typename Policy::Params&) {
+    tc_epilogue_rows<Policy::BN>(taddr, row_ok, row_off, n0, n_total, row_index, e);
+  }
+};
+template <class Policy>
+struct TcEpilogue<Policy, typename Policy::HasEpilogue> {
+  __device__ static void run(uint32_t taddr, bool row_ok, long long row_off, int n0, int n_total,
+                             int row_index, const EpiParams& e, const typename Policy::Params& p) {
+    Policy::epilogue(taddr, row_ok, row_off, n0, n_total, row_index, e, p);
   }
 };
 
@@ -363,7 +391,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       const int row_index = Policy::row_index(p, tile, row);
       const EpiParams& e = p.epi;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(warp * 32) << 16);
-      tc_epilogue_rows<BN>(taddr, row_ok, row_off, n0, n_total, row_index, e);
+      TcEpilogue<Policy>::run(taddr, row_ok, row_off, n0, n_total, row_index, e, p);
       tc_fence_before();
       __syncwarp();
       if (threadIdx.x == 0) LB_TRACE_AT(3, 2 * local_tile + 1);

@@ -40,7 +40,7 @@ def _lib():
         lib.lb_gemm_comm_tc.argtypes = [
             c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_ll, c_ll, c_ll, c_int, c_int, c_int,
             c_int, c_float, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
-            ctypes.c_uint, c_int, c_void_p, c_int, c_void_p]
+            ctypes.c_uint, c_int, c_void_p, c_int, c_int, c_void_p]
         _configured = True
     return lib
 
@@ -53,7 +53,7 @@ class FusedGemm:
         self._maps = None
         self._stage = {}            # (rows, k, dtype) -> (gathered, flags)
         self._epoch = 0
-        self.helpers = 12           # copying CTAs of the staged all-gather -> GEMM
+        self.helpers = 6            # copying CTAs of the staged all-gather -> GEMM
         self.bytes_over_nvlink = 0
 
     # ------------------------------------------------------------------ helpers
@@ -133,7 +133,7 @@ class FusedGemm:
             out.data_ptr(), M, N, k, k, k, out.stride(0), 0, 0, native.dtype_code(dtype),
             native.dtype_code(out.dtype), float(alpha), a_ptrs, shard_rows if sharded == "a" else 0,
             b_ptrs, shard_rows if sharded == "b" else 0, P, g.rank, self._maps_dev(),
-            native.ptr(gathered), native.ptr(flags), epoch, self.helpers, None, 0,
+            native.ptr(gathered), native.ptr(flags), epoch, self.helpers, None, 0, 0,
             native.stream_ptr())
         native.check(rc, "lb_gemm_comm_tc (all-gather -> GEMM)")
         native.count_launch()
@@ -175,19 +175,48 @@ class FusedGemm:
             else:
                 mine.add_(res)
             return mine
-        if zero:
-            mine.zero_()
-        g.barrier_device(2)           # every destination block is cleared / ready
         a = a.contiguous()
         b = b.contiguous()
-        ptrs = self._ptr_array(out, offset_bytes)
+        shard_elems = rows_per_rank * N
+        use_slots = zero and P > 1 and shard_elems % 4 == 0
+        if use_slots:
+            # Every source rank owns a slot at every other rank: the epilogue writes partial
+            # tiles there with plain (posted, coalesced) stores - own rows go straight into
+            # the output shard - and a short kernel adds the P - 1 slots after the rendezvous.
+            # Remote fp32 atomics would need one NVLink transaction per 16 bytes.
+            key = ("rs", shard_elems)
+            slots = self._stage.get(key)
+            if slots is None:
+                slots = g.alloc((P - 1) * shard_elems * 4)
+                self._stage[key] = slots
+            ptr_list = []
+            for r in range(P):
+                if r == g.rank:
+                    ptr_list.append(out.peer_ptr(r, offset_bytes))
+                else:
+                    slot = (g.rank - r - 1) % P
+                    ptr_list.append(slots.peer_ptr(r, slot * shard_elems * 4))
+            ptrs = (c_void_p * P)(*ptr_list)
+        else:
+            if zero:
+                mine.zero_()
+            ptrs = self._ptr_array(out, offset_bytes)
+        g.barrier_device(2)           # destinations are ready (cleared / no longer being read)
         rc = _lib().lb_gemm_comm_tc(
             a.data_ptr(), b.data_ptr(), None, M, N, K, a.stride(0), b.stride(0), N,
             1 if trans_a else 0, 1 if trans_b else 0, native.dtype_code(a.dtype), native.DT_F32,
             float(alpha), None, 0, None, 0, P, g.rank, None, None, None, 0, 0, ptrs, rows_per_rank,
-            native.stream_ptr())
+            1 if use_slots else 0, native.stream_ptr())
         native.check(rc, "lb_gemm_comm_tc (GEMM -> reduce-scatter)")
         native.count_launch()
         g.barrier_device(3)           # every rank's contributions have landed
+        if use_slots:
+            lib = _lib()
+            lib.lb_rs_reduce.restype = c_int
+            lib.lb_rs_reduce.argtypes = [c_void_p, c_void_p, c_int, c_ll, c_ll, c_void_p]
+            rc = lib.lb_rs_reduce(mine.data_ptr(), slots.ptr, P - 1, shard_elems, shard_elems,
+                                  native.stream_ptr())
+            native.check(rc, "lb_rs_reduce")
+            native.count_launch()
         self.bytes_over_nvlink += (P - 1) * rows_per_rank * N * 4
         return mine
