@@ -400,6 +400,8 @@ class Softmax(ExecLayer):
 
     def forward(self, xs, training):
         x = self.cast_in(xs[0])
+        if getattr(self, "fused_into_child", False):
+            return [x]          # the cross-entropy child consumes the logits
         mode = (self.params.softmax_mode or "instance") if hasattr(self.params, "softmax_mode") else "instance"
         if mode == "channel" and x.dim() > 2:
             xm = x.movedim(1, -1)
@@ -741,7 +743,16 @@ class OperatorLayer(ExecLayer):
         if short in ew.BINARY_CODE:
             a, b = xs[0], xs[1]
             if b.shape != a.shape:
-                b = b.reshape(a.shape)
+                if b.numel() == a.numel():
+                    b = b.reshape(a.shape)
+                else:
+                    # operands with unit dims (a mask shared by all heads, a per-row scale):
+                    # broadcast instead of asking the graph to tessellate them
+                    if a.numel() < b.numel():
+                        a = a.expand(torch.broadcast_shapes(a.shape, b.shape))
+                    else:
+                        b = b.expand(torch.broadcast_shapes(a.shape, b.shape))
+                    a, b = a.contiguous(), b.to(a.dtype).contiguous()
             return ew.binary(short, a, b.to(a.dtype))
         if short == "clamp":
             return ew.unary("clamp", xs[0], float(msg.min), float(msg.max))

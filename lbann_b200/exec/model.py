@@ -171,6 +171,7 @@ class ExecModel:
         self._setup_weights()
         self._setup_objective()
         self._fuse_activations()
+        self._fuse_softmax_cross_entropy()
         for mode in MODES:
             self.stats[mode] = ModeStats(self.device, len(self.metrics))
         self.is_setup = True
@@ -306,6 +307,26 @@ class ExecModel:
                     and l.cout % 8 == 0):
                 c.children[0].bwd_act = act
                 l.skip_act_grad = True
+
+    def _fuse_softmax_cross_entropy(self):
+        """softmax over channels -> cross-entropy with integer labels: the softmax layer
+        passes its input through and the loss layer runs the fused softmax-cross-entropy
+        kernel on the logits (one pass, no probability tensor)."""
+        protected = {n for n, _ in self.objective_terms} | {m.layer_name for m in self.metrics
+                                                            if getattr(m, "layer_name", None)}
+        for l in self.layers:
+            if l.type != "cross_entropy" or not l.params.use_labels or not l.parents:
+                continue
+            sm = l.parents[0]
+            if sm.type != "softmax" or len(sm.children) != 1 or sm.name in protected:
+                continue
+            mode = (getattr(sm.params, "softmax_mode", "") or "instance")
+            if mode != "channel" or len(sm.in_dims[0]) < 2:
+                continue
+            if self.distconv is not None and self.distconv.enabled(l):
+                continue
+            sm.fused_into_child = True
+            l.fused_logits = True
 
     # ------------------------------------------------------------------ execution
     def forward_prop(self, inputs: Dict[str, torch.Tensor], mode: str = "training",

@@ -651,8 +651,10 @@ def batch_norm(x, sh, bh, run_mean, run_var, training: bool, eps: float, decay: 
         var = torch.clamp(var, min=eps)
         with torch.no_grad():
             if run_mean is not None:
-                run_mean.mul_(decay).add_((1 - decay) * mean.detach())
-                run_var.mul_(decay).add_((1 - decay) * var.detach())
+                # .data: the running statistics are views of the parameter arena, whose version
+                # counter is shared with every weight saved for the backward pass
+                run_mean.data.mul_(decay).add_((1 - decay) * mean.detach())
+                run_var.data.mul_(decay).add_((1 - decay) * var.detach())
     else:
         mean, var = run_mean, run_var
     y = (xf - mean.view(shape)) * torch.rsqrt(var.view(shape) + eps)

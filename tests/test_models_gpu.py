@@ -1,0 +1,66 @@
+"""Model zoo on a GPU in 16-bit precision: the native kernels (tcgen05 GEMM / convolution,
+layer norm, softmax, fused softmax-cross-entropy, batch norm, fused optimizer) carry a few
+training steps of every model family."""
+import math
+
+import pytest
+import torch
+
+import lbann_b200 as lbann
+from lbann_b200.exec.trainer import ExecTrainer
+from lbann_b200.ops import native
+from lbann_b200.utils import options as opts
+from test_models_cpu import _reader
+
+pytestmark = pytest.mark.gpu
+
+
+def _train_gpu(model, reader, steps, mb, dtype, optimizer=None):
+    o = opts.reset()
+    o.set("default_dtype", dtype)
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=mb, random_seed=3), model=model, data_reader=reader,
+        optimizer=optimizer or lbann.Adam(learn_rate=2e-3, beta1=0.9, beta2=0.99, eps=1e-8))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    b = dc.next_batch("training")
+    n0 = native.launches()
+    losses = []
+    for _ in range(steps):
+        m.train_step(b.tensors, b.global_size)
+        losses.append(float(m.last_objective))
+    assert native.consume_status() == 0
+    assert native.launches() > n0, "no native kernel ran"
+    tr.shutdown()
+    assert all(math.isfinite(v) for v in losses), losses
+    return losses
+
+
+def test_gpt_bf16():
+    from lbann_b200.models.transformer import construct_gpt_model
+    torch.manual_seed(0)
+    model = construct_gpt_model(vocab_size=256, seq_len=64, d_model=128, num_heads=4, num_layers=2,
+                                ffn_dim=512)
+    losses = _train_gpu(model, _reader(8, [65], "randint:256"), steps=20, mb=8, dtype="bf16")
+    assert losses[0] == pytest.approx(math.log(256), rel=0.25)
+    assert losses[-1] < 0.9 * losses[0], losses
+
+
+def test_resnet18_bf16():
+    from lbann_b200.models import ResNet18, construct_classifier
+    torch.manual_seed(0)
+    model = construct_classifier(ResNet18(16, width=0.5), 16)
+    losses = _train_gpu(model, _reader(16, [3, 64, 64], "normal", label_classes=16), steps=10, mb=16,
+                        dtype="bf16", optimizer=lbann.SGD(learn_rate=0.05, momentum=0.9))
+    assert losses[-1] < losses[0], losses
+
+
+def test_unet3d_fp16():
+    from lbann_b200.models import construct_unet3d_model
+    torch.manual_seed(0)
+    model = construct_unet3d_model(num_classes=3, base_channels=8, levels=2)
+    r = _reader(2, [1, 32, 32, 32], "samples:normal responses:randint:3", response_dims=[32, 32, 32])
+    losses = _train_gpu(model, r, steps=8, mb=2, dtype="fp16")
+    assert losses[-1] < losses[0], losses
