@@ -733,6 +733,8 @@ class OperatorLayer(ExecLayer):
         return [tuple(in_dims[0])]
 
     def forward(self, xs, training):
+        if getattr(self, "fused_into_child", False):
+            return [self.cast_in(xs[0])]      # the consumer applies this operator itself
         xs = [self.cast_in(x) for x in xs]
         cur = xs
         for short, msg in self.ops:

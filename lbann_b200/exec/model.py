@@ -9,6 +9,7 @@ helper layers are implicit (a tensor may simply feed several children).
 """
 from __future__ import annotations
 
+import os
 import time
 from collections import OrderedDict, defaultdict
 from typing import Callable, Dict, List, Optional
@@ -172,6 +173,7 @@ class ExecModel:
         self._setup_objective()
         self._fuse_activations()
         self._fuse_softmax_cross_entropy()
+        self._fuse_attention_scores()
         for mode in MODES:
             self.stats[mode] = ModeStats(self.device, len(self.metrics))
         self.is_setup = True
@@ -327,6 +329,52 @@ class ExecModel:
                 continue
             sm.fused_into_child = True
             l.fused_logits = True
+
+    def _fuse_attention_scores(self):
+        """QK^T -> scale -> (+ causal mask) -> softmax: fold the scaling and the causal mask
+        into the softmax kernel, which then reads the raw scores once instead of three
+        element-wise passes over the [heads, S, S] tensor.  A mask qualifies when it is a
+        constant (optimizer-less) weights layer holding 0 on and below the diagonal and a
+        large negative number above it."""
+        if self.device.type != "cuda" or os.environ.get("LBANN_DISABLE_ATTENTION_FUSION"):
+            return
+        protected = {n for n, _ in self.objective_terms} | {m.layer_name for m in self.metrics
+                                                            if getattr(m, "layer_name", None)}
+
+        def single_op(l, short):
+            return (l.type == "operator_layer" and len(getattr(l, "ops", [])) == 1
+                    and l.ops[0][0] == short and len(l.children) == 1 and l.name not in protected)
+
+        for sm in self.layers:
+            if sm.type != "channelwise_softmax" or not sm.parents:
+                continue
+            nd = len(sm.in_dims[0])
+            dim = int(sm.params.dim)
+            if not sm.params.single_dim_mode or (dim + nd) % nd != nd - 1 or nd < 2:
+                continue
+            S = sm.in_dims[0][-1]
+            cur = sm.parents[0]
+            mask_layer = None
+            if single_op(cur, "add") and len(cur.parents) == 2 and cur.parents[1].type == "weights_layer":
+                wl = cur.parents[1]
+                w = wl.w.handle.master.detach().float().reshape(-1, S, S) if wl.out_dims[0][-2:] == (S, S) \
+                    and sm.in_dims[0][-2] == S else None
+                if w is not None and not wl.w.has_optimizer():
+                    tri = torch.triu(torch.ones(S, S, dtype=torch.bool, device=w.device), 1)
+                    if bool((w[:, ~tri] == 0).all()) and bool((w[:, tri] <= -1e4).all()):
+                        mask_layer = cur
+                        cur = cur.parents[0]
+            scale = None
+            if single_op(cur, "scale"):
+                scale = float(cur.ops[0][1].constant)
+            if mask_layer is None and scale is None:
+                continue
+            if mask_layer is not None:
+                mask_layer.fused_into_child = True
+                sm.fused_causal = S
+            if scale is not None:
+                cur.fused_into_child = True
+                sm.fused_scale = scale
 
     # ------------------------------------------------------------------ execution
     def forward_prop(self, inputs: Dict[str, torch.Tensor], mode: str = "training",

@@ -64,3 +64,21 @@ def test_unet3d_fp16():
     r = _reader(2, [1, 32, 32, 32], "samples:normal responses:randint:3", response_dims=[32, 32, 32])
     losses = _train_gpu(model, r, steps=8, mb=2, dtype="fp16")
     assert losses[-1] < losses[0], losses
+
+
+def test_attention_score_fusion_matches_unfused(monkeypatch):
+    """Folding 1/sqrt(d) and the causal mask into the softmax kernel does not change the
+    training trajectory beyond 16-bit rounding."""
+    from lbann_b200.models.transformer import construct_gpt_model
+
+    def run():
+        torch.manual_seed(0)
+        model = construct_gpt_model(vocab_size=128, seq_len=32, d_model=64, num_heads=4, num_layers=2,
+                                    ffn_dim=128, name="gptf")
+        return _train_gpu(model, _reader(8, [33], "randint:128"), steps=6, mb=8, dtype="bf16")
+
+    fused = run()
+    monkeypatch.setenv("LBANN_DISABLE_ATTENTION_FUSION", "1")
+    plain = run()
+    for a, b in zip(fused, plain):
+        assert abs(a - b) < 3e-2 * max(1.0, abs(b)), (fused, plain)
