@@ -126,8 +126,14 @@ class ParallelContext:
         arena = model.arena
         buf = self._buffers.get(arena.grad.data_ptr())
         n = arena.total
+        # The ranks of a process-grid column see the same samples: replicated layers compute
+        # the same gradient tp_size times (model-parallel layers pre-multiply theirs).
+        scale = 1.0 / self.tp_size
         if buf is None or not self.group.native:
-            self.comm.allreduce(arena.grad[:max(n, 1)], "trainer", "sum")
+            g = arena.grad[:max(n, 1)]
+            self.comm.allreduce(g, "trainer", "sum")
+            if scale != 1.0:
+                g.mul_(scale)
             return
         es = arena.grad.element_size()
         per = max(self.bucket_bytes // es, 1 << 16)
@@ -137,7 +143,7 @@ class ParallelContext:
         with torch.cuda.stream(self.comm_stream):
             for off in range(0, n, per):
                 cnt = min(per, n - off)
-                self.group.allreduce_(buf, arena.grad.dtype, cnt, 1.0, off * es,
+                self.group.allreduce_(buf, arena.grad.dtype, cnt, scale, off * es,
                                       blocks=32 if cnt * es >= (4 << 20) else 8)
         cur.wait_stream(self.comm_stream)
 

@@ -32,6 +32,94 @@ from .fused import FusedGemm
 from .symm import SymmetricBuffer, SymmetricGroup
 
 
+class _ModelParallelLinear(torch.autograd.Function):
+    """y = x W^T with the OUTPUT rows of W dealt to the ranks of a process-grid column:
+    every rank multiplies by its row block and the blocks are all-gathered; backward
+    all-reduces the partial input gradient and leaves the weight gradient of the other
+    ranks' rows at zero (the data-parallel gradient all-reduce completes it)."""
+
+    @staticmethod
+    def forward(ctx, x, w, b, tp):
+        P, r = tp.size, tp.rank
+        n = w.shape[0]
+        lo, hi = tp.bounds(n)
+        ctx.tp, ctx.bounds, ctx.has_bias = tp, (lo, hi, n), b is not None
+        ctx.save_for_backward(x, w)
+        y_loc = torch.nn.functional.linear(x, w[lo:hi].to(x.dtype),
+                                           None if b is None else b[lo:hi].to(x.dtype))
+        return tp.all_gather_cols(y_loc, n)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x, w = ctx.saved_tensors
+        tp = ctx.tp
+        lo, hi, n = ctx.bounds
+        dy_loc = dy[:, lo:hi]
+        dx = dy_loc.float() @ w[lo:hi].float()
+        tp.all_reduce(dx)
+        dw = torch.zeros_like(w, dtype=torch.float32)
+        dw[lo:hi] = dy_loc.float().t() @ x.float()
+        db = None
+        if ctx.has_bias:
+            db = torch.zeros(n, dtype=torch.float32, device=dy.device)
+            db[lo:hi] = dy_loc.float().sum(0)
+        # Only this rank produces these rows while replicated layers are produced by every
+        # rank of the column; the trainer-wide gradient sum is divided by the column size,
+        # so the row block is pre-multiplied by it.
+        dw.mul_(tp.size)
+        if db is not None:
+            db.mul_(tp.size)
+        return dx.to(x.dtype), dw.to(w.dtype), db, None
+
+
+class TensorParallel:
+    """Model-parallel fully-connected layers on a trainer's process grid (the reference's
+    ``data_layout='model_parallel'`` over an MC,MR grid, src/layers/learning/
+    fully_connected.cpp:638-808).  The ranks of one grid column share the mini-batch and
+    split the output neurons."""
+
+    def __init__(self, ctx):
+        import torch.distributed as dist
+        self.ctx = ctx
+        self.comm = ctx.comm
+        self.group = self.comm.grid_col_group
+        self.size = self.comm.grid_height
+        self.rank = dist.get_rank(self.group) if self.size > 1 else 0
+
+    def bounds(self, n: int):
+        per = (n + self.size - 1) // self.size
+        lo = min(n, self.rank * per)
+        return lo, min(n, lo + per)
+
+    def all_gather_cols(self, y_loc: torch.Tensor, n: int) -> torch.Tensor:
+        import torch.distributed as dist
+        if self.size == 1:
+            return y_loc
+        per = (n + self.size - 1) // self.size
+        pad = torch.zeros((y_loc.shape[0], per), dtype=y_loc.dtype, device=y_loc.device)
+        pad[:, :y_loc.shape[1]] = y_loc
+        parts = [torch.empty_like(pad) for _ in range(self.size)]
+        dist.all_gather(parts, pad, group=self.group)
+        return torch.cat(parts, 1)[:, :n].contiguous()
+
+    def all_reduce(self, t: torch.Tensor):
+        import torch.distributed as dist
+        if self.size > 1:
+            dist.all_reduce(t, group=self.group)
+
+    def linear(self, layer, x: torch.Tensor) -> torch.Tensor:
+        w = layer.w.handle.master
+        if layer.transpose:
+            w = w.t()
+        b = layer.b.handle.master if layer.b is not None else None
+        return _ModelParallelLinear.apply(x, w, b, self)
+
+    def softmax(self, x: torch.Tensor, log: bool) -> torch.Tensor:
+        """Activations are whole on every rank after the gather: a local softmax."""
+        fn = torch.log_softmax if log else torch.softmax
+        return fn(x.float(), dim=-1).to(x.dtype)
+
+
 class _Workspace:
     """Symmetric buffers of one layer, allocated collectively on first use."""
 

@@ -223,6 +223,44 @@ def tensor_parallel():
     return res
 
 
+def model_parallel_fc(grid_height, steps):
+    """MLP whose hidden layers are model-parallel over a process-grid column."""
+    o = opts.reset()
+    o.set("disable_cuda", True)
+    if grid_height > 1:
+        o.set("trainer_grid_height", grid_height)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    x = lbann.Input(data_field="samples")
+    t = lbann.Input(data_field="responses")
+    layout = "model_parallel"
+    h = lbann.Relu(lbann.FullyConnected(x, num_neurons=24, has_bias=True, data_layout=layout, name="fc1"))
+    h = lbann.Relu(lbann.FullyConnected(h, num_neurons=10, has_bias=True, name="fc2"))
+    y = lbann.FullyConnected(h, num_neurons=3, has_bias=False, data_layout=layout, name="fc3")
+    loss = lbann.MeanSquaredError(y, t, name="mse")
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph([x, t])),
+                        objective_function=lbann.ObjectiveFunction([loss]))
+    from test_models_cpu import _reader
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=8, random_seed=11), model=model,
+        data_reader=_reader(16, [12], "normal", response_dims=[3]),
+        optimizer=lbann.SGD(learn_rate=0.05, momentum=0.9))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    losses = []
+    for _ in range(steps):
+        b = dc.next_batch("training")
+        if b is None:
+            dc.start_epoch("training")
+            b = dc.next_batch("training")
+        m.train_step(b.tensors, b.global_size)
+        losses.append(float(m.last_objective))
+    w = {x.name: float(x.values.detach().float().norm()) for x in m.weights}
+    tr.shutdown()
+    return {"losses": losses, "weight_norms": w, "world": world}
+
+
 if __name__ == "__main__":
     what, out = sys.argv[1], sys.argv[2]
     if what == "comm":
@@ -231,6 +269,8 @@ if __name__ == "__main__":
         res = fused_gemm()
     elif what == "tp":
         res = tensor_parallel()
+    elif what == "mpfc":
+        res = model_parallel_fc(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "cosmoflow":
         res = cosmoflow(int(sys.argv[3]), int(sys.argv[4]), sys.argv[5] if len(sys.argv) > 5 else "float",
                         int(sys.argv[6]) if len(sys.argv) > 6 else 32)

@@ -61,3 +61,15 @@ def test_tensor_parallel_and_sharded_linear_gloo(tmp_path):
     reproduce the dense fp32 forward values and all gradients."""
     res = _run(2, ["tp"], str(tmp_path / "t.json"))
     assert res["world"] == 2 and res["all_ranks_ok"], res
+
+
+def test_model_parallel_fully_connected_matches_single(tmp_path):
+    """FullyConnected layers with data_layout='model_parallel' on a 2 x 1 process grid give
+    the losses and weights of the single-process run."""
+    single = _run(1, ["mpfc", "1", "4"], str(tmp_path / "a.json"))
+    grid = _run(2, ["mpfc", "2", "4"], str(tmp_path / "b.json"))
+    assert grid["world"] == 2
+    for a, b in zip(single["losses"], grid["losses"]):
+        assert abs(a - b) <= 1e-4 * max(1.0, abs(a)), (single["losses"], grid["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - grid["weight_norms"][k]) <= 1e-4 * max(1.0, abs(v)), k
