@@ -1,0 +1,187 @@
+"""K-FAC: Kronecker-factored approximate curvature preconditioning around SGD.
+
+For every fully-connected, channelwise fully-connected and convolution layer with an
+optimizer the algorithm keeps running averages of the two Kronecker factors
+
+    A = E[a a^T]  (layer inputs; unfolded patches for convolutions)
+    G = E[g g^T]  (gradients w.r.t. the layer outputs, rescaled to per-sample values)
+
+and replaces the weight gradient dW by  (G + pi^-1 sqrt(damping_err) I)^-1 dW
+(A + pi sqrt(damping_act) I)^-1  before the first-order optimizer step (Martens and
+Grosse 2015; the reference: src/execution_algorithms/kfac.cpp:122-860 and
+src/execution_algorithms/kfac/kfac_block_fc_conv.cpp).  Factors are averaged over the
+data-parallel ranks; inverses are recomputed every ``update_interval`` steps with a
+Cholesky solve (``torch.linalg``; not a hot path).  Batch-norm and GRU blocks of the
+reference are not preconditioned here.
+"""
+from __future__ import annotations
+
+from typing import Dict, List
+
+import torch
+import torch.nn.functional as F
+
+from .algorithms import SGDTrainingAlgorithm, Termination
+
+
+def _floats(s, default):
+    vals = [float(v) for v in str(s).split()] if s else []
+    return vals or [default]
+
+
+class _Block:
+    """Factor state of one layer."""
+
+    def __init__(self, layer):
+        self.layer = layer
+        self.A = self.G = self.Ainv = self.Ginv = None
+        self.inp = self.out = self.grad_out = None
+        self.hook = None
+
+    # inputs as a [rows, features] matrix (bias handled by an appended column of ones)
+    def activations(self) -> torch.Tensor:
+        l, x = self.layer, self.inp.detach().float()
+        if l.type == "convolution":
+            nd = l.nd
+            if nd == 2:
+                cols = F.unfold(x, l.ksize, dilation=l.dil, padding=l.pad, stride=l.stride)
+                a = cols.transpose(1, 2).reshape(-1, cols.shape[1])
+            else:       # 3-D: patches through a direct gather (small problems only)
+                xp = F.pad(self.inp.detach().float(), [p for q in reversed(l.pad) for p in (q, q)])
+                u = xp.unfold(2, l.ksize[0], l.stride[0]).unfold(3, l.ksize[1], l.stride[1])
+                u = u.unfold(4, l.ksize[2], l.stride[2])
+                a = u.permute(0, 2, 3, 4, 1, 5, 6, 7).reshape(-1, l.cin * l.ksize[0] * l.ksize[1] * l.ksize[2])
+        elif l.type == "channelwise_fully_connected":
+            a = x.reshape(-1, l.in_size)
+        else:
+            a = x.reshape(x.shape[0], -1)
+        if l.b is not None:
+            a = torch.cat([a, torch.ones(a.shape[0], 1, device=a.device)], 1)
+        return a
+
+    def errors(self, batch: int) -> torch.Tensor:
+        l, g = self.layer, self.grad_out.detach().float()
+        if l.type == "convolution":
+            g = g.reshape(g.shape[0], g.shape[1], -1).transpose(1, 2).reshape(-1, g.shape[1])
+        elif l.type == "channelwise_fully_connected":
+            g = g.reshape(-1, l.out_size)
+        else:
+            g = g.reshape(g.shape[0], -1)
+        return g * batch       # the objective is a mean over the mini-batch
+
+
+class KFAC(SGDTrainingAlgorithm):
+    def __init__(self, name, sgd: SGDTrainingAlgorithm, msg):
+        super().__init__(name, sgd.termination, sgd.suppress_timer)
+        self.damping_act = _floats(msg.damping_act, 1e-2)
+        self.damping_err = _floats(msg.damping_err, 1e-2)
+        self.damping_warmup_steps = int(msg.damping_warmup_steps) or 0
+        self.decay = float(msg.kronecker_decay) or 0.99
+        self.use_pi = bool(msg.use_pi)
+        iv = [int(v) for v in str(msg.update_intervals).split()] if msg.update_intervals else [1]
+        self.update_intervals = iv
+        self.update_interval_steps = int(msg.update_interval_steps) or 1
+        self.compute_interval = int(msg.compute_interval) or 1
+        self.disable_layers = set(str(msg.disable_layers).split()) if msg.disable_layers else set()
+        self.lr_factor = float(msg.learning_rate_factor) or 1.0
+        self.blocks: Dict[str, _Block] = {}
+
+    # ---------------------------------------------------------------- schedules
+    def _damping(self, vals: List[float], step: int) -> float:
+        if len(vals) == 1 or self.damping_warmup_steps <= 0:
+            return vals[0]
+        t = min(1.0, step / self.damping_warmup_steps)
+        return vals[0] * (1 - t) + vals[1] * t
+
+    def _update_interval(self, step: int) -> int:
+        if len(self.update_intervals) == 1:
+            return max(1, self.update_intervals[0])
+        t = min(1.0, step / max(1, self.update_interval_steps))
+        return max(1, int(round(self.update_intervals[0] * (1 - t) + self.update_intervals[1] * t)))
+
+    # ---------------------------------------------------------------- set-up
+    def _setup(self, model):
+        for l in model.layers:
+            if l.type not in ("fully_connected", "channelwise_fully_connected", "convolution"):
+                continue
+            if l.name in self.disable_layers or not l.w.has_optimizer():
+                continue
+            if getattr(l, "transpose", False) or getattr(l, "groups", 1) != 1:
+                continue
+            self.blocks[l.name] = _Block(l)
+
+    def _capture(self, model):
+        """Remember every block's input and hook its output for the error signal."""
+        for name, blk in self.blocks.items():
+            l = blk.layer
+            parent = l.parents[0]
+            blk.inp = model.acts[parent.name][model._slot(parent, l)]
+            out = model.acts[name][0]
+            blk.out = out
+            if out.requires_grad:
+                out.register_hook(lambda g, b=blk: setattr(b, "grad_out", g))
+
+    # ---------------------------------------------------------------- the step
+    def train_mini_batch(self, trainer, model, ctx, batch, cbs):
+        if not self.blocks and not getattr(self, "_ready", False):
+            self._ready = True
+            self._setup(model)
+        for cb in cbs:
+            if ctx.step % cb.batch_interval == 0:
+                cb.on_batch_begin(model)
+        model.clear_gradients()
+        model.forward_prop(batch.tensors, "training", batch.global_size, batch.offset)
+        self._capture(model)
+        obj = model.local_objective()
+        model.last_objective = obj.detach()
+        model.record_statistics("training", obj)
+        model.backward_prop(obj)
+        if ctx.step % self.compute_interval == 0:
+            self._precondition(model, ctx.step, batch.global_size)
+        model.update_weights()
+        ctx.step += 1
+        ctx.step_in_epoch += 1
+        for cb in cbs:
+            if (ctx.step - 1) % cb.batch_interval == 0:
+                cb.on_batch_end(model)
+
+    @torch.no_grad()
+    def _precondition(self, model, step: int, global_batch: int):
+        d_act = self._damping(self.damping_act, step)
+        d_err = self._damping(self.damping_err, step)
+        refresh = step % self._update_interval(step) == 0
+        par = model.parallel
+        for blk in self.blocks.values():
+            if blk.grad_out is None or blk.layer.w.handle.grad is None:
+                continue
+            a = blk.activations()
+            g = blk.errors(global_batch)
+            A = a.t() @ a / a.shape[0]
+            G = g.t() @ g / g.shape[0]
+            if par is not None and par.dp_size > 1:
+                par.allreduce_sum_inplace(A)
+                par.allreduce_sum_inplace(G)
+                A /= par.dp_size
+                G /= par.dp_size
+            blk.A = A if blk.A is None else self.decay * blk.A + (1 - self.decay) * A
+            blk.G = G if blk.G is None else self.decay * blk.G + (1 - self.decay) * G
+            if refresh or blk.Ainv is None:
+                pi = 1.0
+                if self.use_pi:
+                    pi = float(torch.sqrt((blk.A.trace() / blk.A.shape[0]) /
+                                          (blk.G.trace() / blk.G.shape[0]).clamp_min(1e-30)).clamp(1e-3, 1e3))
+                eye_a = torch.eye(blk.A.shape[0], device=A.device)
+                eye_g = torch.eye(blk.G.shape[0], device=G.device)
+                blk.Ainv = torch.cholesky_inverse(torch.linalg.cholesky(blk.A + pi * d_act ** 0.5 * eye_a))
+                blk.Ginv = torch.cholesky_inverse(torch.linalg.cholesky(blk.G + d_err ** 0.5 / pi * eye_g))
+            l = blk.layer
+            gw = l.w.handle.grad.float().reshape(blk.G.shape[0], -1)
+            if l.b is not None and l.b.handle.grad is not None:
+                gw = torch.cat([gw, l.b.handle.grad.float().reshape(-1, 1)], 1)
+            # (the patch matrix is ordered (channel, kernel...) like the kernel's trailing dims)
+            nat = blk.Ginv @ gw @ blk.Ainv * self.lr_factor
+            if l.b is not None and l.b.handle.grad is not None:
+                l.b.handle.grad.copy_(nat[:, -1].reshape(l.b.handle.grad.shape))
+                nat = nat[:, :-1]
+            l.w.handle.grad.copy_(nat.reshape(l.w.handle.grad.shape))
+            blk.grad_out = None
