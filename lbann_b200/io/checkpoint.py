@@ -233,7 +233,10 @@ def restore_checkpoint(trainer, model, base: str, per_rank_base: Optional[str] =
         trainer.data_coordinator.load_state(state)
     _load_rng(d, comm.rank_in_world, model)
     ctx = trainer.context(model, "training")
-    ctx._resume_mid_epoch = trainer.data_coordinator.modes["training"].pos > 0
+    st = trainer.data_coordinator.modes["training"]
+    # resume inside an epoch only when the checkpoint was taken inside one (a position at
+    # the end of the sample order means the epoch had finished)
+    ctx._resume_mid_epoch = 0 < st.pos < len(st.order)
     if comm.am_trainer_master():
         print(f"[{trainer.name}] Restart from {kind} checkpoint: hook {hook} epoch {epoch} step {step}",
               flush=True)
