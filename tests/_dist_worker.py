@@ -261,6 +261,45 @@ def model_parallel_fc(grid_height, steps):
     return {"losses": losses, "weight_norms": w, "world": world}
 
 
+def ltfb(strategy):
+    """Two trainers of one rank each run LTFB tournaments on an MLP regression."""
+    o = opts.reset()
+    o.set("disable_cuda", True)
+    o.set("procs_per_trainer", 1)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    x = lbann.Input(data_field="samples")
+    t = lbann.Input(data_field="responses")
+    h = lbann.Tanh(lbann.FullyConnected(x, num_neurons=12, has_bias=True, name="fc1"))
+    y = lbann.FullyConnected(h, num_neurons=2, has_bias=True, name="fc2")
+    loss = lbann.MeanSquaredError(y, t, name="mse")
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph([x, t])),
+                        objective_function=lbann.ObjectiveFunction([loss]),
+                        metrics=[lbann.Metric(loss, name="mse")])
+    RPE = lbann.RandomPairwiseExchange
+    if strategy == "truncation":
+        meta = lbann.TruncationSelectionExchange({"mse": RPE.MetricStrategy.LOWER_IS_BETTER}, truncation_k=1)
+    else:
+        meta = RPE({"mse": RPE.MetricStrategy.LOWER_IS_BETTER}, RPE.ExchangeStrategy(strategy))
+    algo = lbann.LTFB("ltfb", lbann.BatchedIterativeOptimizer("local", num_iterations=3), meta,
+                      metalearning_steps=3)
+    from test_models_cpu import _reader
+    rd = _reader(32, [6], "normal", response_dims=[2])
+    r2 = rd.reader.add()
+    r2.CopyFrom(rd.reader[0])
+    r2.role = "tournament"
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=8, random_seed=3, training_algo=algo), model=model,
+        data_reader=rd, optimizer=lbann.SGD(learn_rate=0.05 if rank == 0 else 0.0))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    tr.train(m, num_epochs=1)
+    w = {x.name: float(x.values.detach().float().norm()) for x in m.weights}
+    allw = tr.comm.world_gather_object(w)
+    tr.shutdown()
+    return {"world": world, "weights": allw, "num_trainers": tr.comm.num_trainers}
+
+
 if __name__ == "__main__":
     what, out = sys.argv[1], sys.argv[2]
     if what == "comm":
@@ -269,6 +308,8 @@ if __name__ == "__main__":
         res = fused_gemm()
     elif what == "tp":
         res = tensor_parallel()
+    elif what == "ltfb":
+        res = ltfb(sys.argv[3])
     elif what == "mpfc":
         res = model_parallel_fc(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "cosmoflow":

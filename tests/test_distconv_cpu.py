@@ -73,3 +73,14 @@ def test_model_parallel_fully_connected_matches_single(tmp_path):
         assert abs(a - b) <= 1e-4 * max(1.0, abs(a)), (single["losses"], grid["losses"])
     for k, v in single["weight_norms"].items():
         assert abs(v - grid["weight_norms"][k]) <= 1e-4 * max(1.0, abs(v)), k
+
+
+@pytest.mark.parametrize("strategy", ["checkpoint_binary", "sendrecv_weights", "truncation"])
+def test_ltfb_two_trainers(tmp_path, strategy):
+    """Two single-rank trainers, one of which cannot learn (zero learning rate): after the
+    tournaments both hold the learner's weights."""
+    res = _run(2, ["ltfb", strategy], str(tmp_path / "l.json"))
+    assert res["num_trainers"] == 2
+    a, b = res["weights"]
+    for k in a:
+        assert abs(a[k] - b[k]) <= 1e-5 * max(1.0, abs(a[k])), (strategy, k, a, b)
