@@ -75,3 +75,16 @@ def test_prototext_round_trip(tmp_path):
     text_format.Parse(open(tmp_path / "exp.prototext").read(), back)
     assert back == msg
     assert [l.name for l in back.model.layer if l.HasField("fully_connected")] == ["fc1", "fc2"]
+
+
+def test_torch_module_lowering_matches_pytorch():
+    import torch.nn as nn
+    import lbann_b200.torch as lt
+    opts.reset().set("disable_cuda", True)
+    torch.manual_seed(0)
+    net = nn.Sequential(nn.Conv2d(2, 4, 3, padding=1), nn.ReLU(), nn.MaxPool2d(2), nn.Flatten(),
+                        nn.Linear(4 * 4 * 4, 5), nn.Tanh())
+    x = torch.randn(3, 2, 8, 8)
+    outs = lt.compile(net, input=x)
+    got = lbann.evaluate(outs[0], x.numpy())
+    torch.testing.assert_close(torch.from_numpy(got), net(x).detach(), rtol=1e-4, atol=1e-5)
