@@ -238,7 +238,7 @@ template <class Policy>
 __global__ void __launch_bounds__(kTcThreads, 1)
 tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB,
-                     const typename Policy::Params p, int* status) {
+                     const __grid_constant__ typename Policy::Params p, int* status) {
   constexpr int BN = Policy::BN;
   using G = typename Policy::G;
   constexpr int S = G::kStages;

@@ -8,7 +8,7 @@ line with the algorithmic FLOPs and bytes, the achieved rates and -- when a
 measured copy bandwidth and cuBLAS bf16 throughput.  The same command line is
 what a profiler capture of that kernel wraps.
 
-Cases: ``gemm``, ``conv`` (forward and, with ``--bwd``, data and filter
+Cases: ``gemm``, ``gemm_comm`` (fused GEMM + collective kernel in a one-GPU layout), ``conv`` (forward and, with ``--bwd``, data and filter
 gradients; the first-layer kernels are chosen automatically for <= 8 input
 channels), ``pool``, ``optimizer``.
 """
@@ -133,6 +133,66 @@ def case_pool(a, timer):
     return out
 
 
+def case_gemm_comm(a, timer):
+    """The fused GEMM + collective kernel on ONE GPU: both "ranks" of a two-rank layout are
+    buffers of this device, so the copying CTAs, the per-block flags and the reduce-scatter
+    epilogue all run (their traffic stays in local memory instead of crossing NVLink).
+    This is the form a profiler can capture; multi-GPU timings come from
+    ``python -m lbann_b200.parallel.fused_bench``."""
+    import ctypes
+    from ..parallel import fused
+    lib = fused._lib()
+    dt = _dtype(a.dtype)
+    P = 2
+    M, N, K = a.m, a.n, a.k
+    rows = M // P
+    c_void_p = ctypes.c_void_p
+    out = []
+    # all-gather -> GEMM with in-kernel staging: A = two row shards
+    shards = [torch.randn(rows, K, device="cuda", dtype=dt) for _ in range(P)]
+    W = torch.randn(N, K, device="cuda", dtype=dt)
+    Y = torch.empty(M, N, device="cuda", dtype=dt)
+    gathered = torch.empty(M, K, device="cuda", dtype=dt)
+    flags = torch.zeros(M // 128, dtype=torch.int32, device="cuda")
+    maps = torch.empty(32 * 128, dtype=torch.uint8, device="cuda")
+    ptrs = (c_void_p * P)(*[s.data_ptr() for s in shards])
+    epoch = [0]
+
+    def ag():
+        epoch[0] += 1
+        rc = lib.lb_gemm_comm_tc(None, W.data_ptr(), Y.data_ptr(), M, N, K, K, K, N, 0, 0,
+                                 native.dtype_code(dt), native.dtype_code(dt), 1.0, ptrs, rows, None, 0,
+                                 P, 0, maps.data_ptr(), gathered.data_ptr() if a.helpers > 0 else None,
+                                 flags.data_ptr(), epoch[0], a.helpers, None, 0, 0, native.stream_ptr())
+        native.check(rc, "lb_gemm_comm_tc")
+
+    ms, mn = timer.run(ag)
+    out.append(_report("allgather_gemm_staged(1-GPU layout)", [M, N, K], ms, mn, 2.0 * M * N * K,
+                       2.0 * (M * K + N * K + M * N)))
+    ref = torch.cat(shards).float() @ W.float().t()
+    err = float((Y.float() - ref).abs().max() / ref.abs().max())
+    # GEMM -> reduce-scatter: K slice of this "rank", rows of the result owned half / half
+    A = torch.randn(M, K, device="cuda", dtype=dt)
+    B = torch.randn(N, K, device="cuda", dtype=dt)
+    own = torch.zeros(rows, N, device="cuda", dtype=torch.float32)
+    slot = torch.zeros(rows, N, device="cuda", dtype=torch.float32)
+    rs = (c_void_p * P)(own.data_ptr(), slot.data_ptr())
+
+    def rsf():
+        rc = lib.lb_gemm_comm_tc(A.data_ptr(), B.data_ptr(), None, M, N, K, K, K, N, 0, 0,
+                                 native.dtype_code(dt), native.DT_F32, 1.0, None, 0, None, 0, P, 0, None,
+                                 None, None, 0, 0, rs, rows, 1, native.stream_ptr())
+        native.check(rc, "lb_gemm_comm_tc")
+
+    ms, mn = timer.run(rsf)
+    out.append(_report("gemm_reduce_scatter(1-GPU layout)", [M, N, K], ms, mn, 2.0 * M * N * K,
+                       2.0 * (M * K + N * K) + 4.0 * M * N))
+    ref2 = A.float() @ B.float().t()
+    err2 = float((torch.cat([own, slot]) - ref2).abs().max() / ref2.abs().max())
+    print(json.dumps({"max_rel_err_allgather_gemm": err, "max_rel_err_reduce_scatter": err2}))
+    return out
+
+
 def case_optimizer(a, timer):
     from .optim import ParameterArena
     arena = ParameterArena(torch.device("cuda"), _dtype(a.dtype))
@@ -150,7 +210,7 @@ def case_optimizer(a, timer):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("case", choices=["gemm", "conv", "pool", "optimizer"])
+    ap.add_argument("case", choices=["gemm", "gemm_comm", "conv", "pool", "optimizer"])
     ap.add_argument("--dtype", default="bf16", choices=["fp16", "bf16"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -163,6 +223,7 @@ def main(argv=None):
     ap.add_argument("--act", action="store_true")
     ap.add_argument("--bwd", action="store_true")
     ap.add_argument("--opt", default="adam")
+    ap.add_argument("--helpers", type=int, default=6, help="copying CTAs of the staged all-gather")
     ap.add_argument("--iters", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--no-flush", action="store_true")
@@ -170,7 +231,8 @@ def main(argv=None):
     if not torch.cuda.is_available():
         raise SystemExit("microbench needs a GPU")
     timer = _Timer(a.iters, a.warmup, flush=not a.no_flush)
-    {"gemm": case_gemm, "conv": case_conv, "pool": case_pool, "optimizer": case_optimizer}[a.case](
+    {"gemm": case_gemm, "gemm_comm": case_gemm_comm, "conv": case_conv, "pool": case_pool,
+     "optimizer": case_optimizer}[a.case](
         a, timer)
     native.consume_status()
 
