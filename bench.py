@@ -228,6 +228,9 @@ def ours(args):
             "clocks": clocks,
         }
         print(json.dumps(out))
+    if getattr(model, "_phase_timer", None) is not None and rank == 0:
+        # LBANN_PHASE_TIMING=1: (device ms, host ms) per phase of the step, on stderr
+        print("phase timing:", model._phase_timer.report(), file=sys.stderr)
     trainer.shutdown()
     comm.finalize()
     return 0

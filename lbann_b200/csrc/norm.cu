@@ -164,7 +164,9 @@ __global__ void bn_partial_sums_kernel(const T* __restrict__ x, float* __restric
   for (int j = 0; j < 8; ++j) { s[j] = 0.f; ss[j] = 0.f; }
   const T* base = x + ((long long)grp * rows) * C + v * 8;
   if (valid)
-    for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
+#pragma unroll 4
+  #pragma unroll 4
+  for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
       float f[8];
       ld8n<T>(base + r * C, f);
 #pragma unroll
@@ -222,6 +224,7 @@ __global__ void bn_finalize_apply_kernel(const T* __restrict__ x, const float* _
   const long long r0 = (long long)blockIdx.y * rows_per_block;
   const long long r1 = min(rows, r0 + rows_per_block);
   const long long base = ((long long)grp * rows) * C + v * 8;
+#pragma unroll 4
   for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
     float f[8];
     ld8n<T>(x + base + r * C, f);
@@ -257,6 +260,7 @@ __global__ void bn_apply_fixed_kernel(const T* __restrict__ x, const float* __re
   }
   const long long r0 = (long long)blockIdx.y * rows_per_block;
   const long long r1 = min(rows, r0 + rows_per_block);
+#pragma unroll 4
   for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
     float f[8];
     ld8n<T>(x + r * C + v * 8, f);
@@ -297,7 +301,9 @@ __global__ void bn_bwd_sums_kernel(const T* __restrict__ x, const T* __restrict_
   const long long r1 = min(rows, r0 + rows_per_block);
   const long long base = ((long long)grp * rows) * C + v * 8;
   if (valid)
-    for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
+#pragma unroll 4
+  #pragma unroll 4
+  for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
       float fx[8], fg[8], fy[8];
       ld8n<T>(x + base + r * C, fx);
       ld8n<T>(dy + base + r * C, fg);
@@ -357,6 +363,7 @@ __global__ void bn_bwd_apply_kernel(const T* __restrict__ x, const T* __restrict
   const long long r0 = (long long)blockIdx.y * rows_per_block;
   const long long r1 = min(rows, r0 + rows_per_block);
   const long long base = ((long long)grp * rows) * C + v * 8;
+#pragma unroll 4
   for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
     float fx[8], fg[8], fy[8];
     ld8n<T>(x + base + r * C, fx);

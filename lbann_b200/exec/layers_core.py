@@ -264,9 +264,11 @@ class EntrywiseScaleBias(ExecLayer):
 
 @register("embedding")
 class Embedding(ExecLayer):
-    """Lookup table; weights ``<name>_weights`` stored embedding_dim x num_embeddings
-    (transpose of PyTorch), out-of-range indices give zeros, ``padding_idx`` row gets no
-    gradient (src/layers/learning/embedding.cpp, src/proto/layers.proto:1271-1276)."""
+    """Lookup table; weights ``<name>_weights`` hold one embedding vector per row
+    (num_embeddings x embedding_dim, row-major: the same memory order as the reference's
+    column-major embedding_dim x num_embeddings matrix, so value lists and checkpoints
+    agree), out-of-range indices give zeros, ``padding_idx`` row gets no gradient
+    (src/layers/learning/embedding.cpp, src/proto/layers.proto:1271-1276)."""
 
     def setup(self, in_dims):
         p = self.params
@@ -276,7 +278,7 @@ class Embedding(ExecLayer):
 
         def init(shape, gen, fi, fo):
             return torch.randn(self.dim * self.num, generator=gen)
-        self.w = self.get_weights(0, "weights", (self.dim, self.num), init)
+        self.w = self.get_weights(0, "weights", (self.num, self.dim), init)
         return [tuple(in_dims[0]) + (self.dim,)]
 
     def forward(self, xs, training):
@@ -285,7 +287,7 @@ class Embedding(ExecLayer):
         if self.padding_idx >= 0:
             ok = ok & (idx != self.padding_idx)
         dt = self.dtype or self.model.default_dtype
-        table = self.w.handle.master.t()
+        table = self.w.handle.master
         out = F.embedding(idx.clamp(0, self.num - 1), table)
         out = out * ok.unsqueeze(-1).to(out.dtype)
         return [out.to(dt)]

@@ -176,6 +176,7 @@ class ExecModel:
         self._fuse_attention_scores()
         for mode in MODES:
             self.stats[mode] = ModeStats(self.device, len(self.metrics))
+        self._phase_timer = ExecModel._PhaseTimer(self.device) if os.environ.get("LBANN_PHASE_TIMING") else None
         self.is_setup = True
         return self
 
@@ -524,6 +525,9 @@ class ExecModel:
 
     def train_step(self, inputs, global_mini_batch_size=None, mini_batch_offset=0):
         """clear grads -> forward -> objective -> backward (+ gradient sync) -> update."""
+        pt = self._phase_timer
+        if pt is not None:
+            pt.mark("start")
         self.clear_gradients()
         for cb in self.callbacks:
             cb.on_forward_prop_begin(self, "training")
@@ -533,9 +537,51 @@ class ExecModel:
         obj = self.local_objective()
         self.last_objective = obj.detach()
         self.record_statistics("training", obj)
+        if pt is not None:
+            pt.mark("forward")
         self.backward_prop(obj)
+        if pt is not None:
+            pt.mark("backward+sync")
         self.update_weights()
+        if pt is not None:
+            pt.mark("update")
         return self.last_objective
+
+    class _PhaseTimer:
+        """Per-phase device and host times of the training step (LBANN_PHASE_TIMING=1):
+        CUDA events between the phases plus host timestamps, summarised by ``report``."""
+
+        def __init__(self, device):
+            self.device, self.events, self.host, self.steps = device, [], [], 0
+            self.dev_ms, self.host_ms = defaultdict(float), defaultdict(float)
+
+        def mark(self, name):
+            ev = None
+            if self.device.type == "cuda":
+                ev = torch.cuda.Event(enable_timing=True)
+                ev.record()
+            self.events.append((name, ev, time.perf_counter()))
+            if name == "update":
+                self.steps += 1
+                if self.steps % 16 == 0:
+                    self.flush()
+
+        def flush(self):
+            if self.device.type == "cuda":
+                torch.cuda.synchronize()
+            prev = None
+            for name, ev, t in self.events:
+                if name != "start" and prev is not None:
+                    if ev is not None:
+                        self.dev_ms[name] += prev[1].elapsed_time(ev)
+                    self.host_ms[name] += (t - prev[2]) * 1e3
+                prev = (name, ev, t)
+            self.events = []
+
+        def report(self):
+            self.flush()
+            n = max(self.steps, 1)
+            return {k: (round(self.dev_ms[k] / n, 3), round(self.host_ms[k] / n, 3)) for k in self.host_ms}
 
     @torch.no_grad()
     def evaluate_step(self, inputs, mode="validation", global_mini_batch_size=None,

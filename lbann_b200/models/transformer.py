@@ -203,7 +203,7 @@ class GPT(Module):
         self.final_norm = LayerNorm(d_model, name=f"{name}_final_norm")
         self.tie = tie_embeddings
         self.head = ChannelwiseFullyConnectedModule(
-            vocab_size, bias=False, transpose=tie_embeddings,
+            vocab_size, bias=False, transpose=False,   # the table is [vocab, d_model] = [out, in]
             weights=[self.embed_weights] if tie_embeddings else
             [L.Weights(initializer=L.NormalInitializer(standard_deviation=0.02), name=f"{name}_lm_head")],
             name=f"{name}_head")

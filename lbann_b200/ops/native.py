@@ -90,7 +90,14 @@ def have_cuda_lib() -> bool:
     return os.path.exists(os.path.join(_NATIVE, "liblbann_b200.so"))
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr() -> int:
+    """The current CUDA stream's handle (the raw getter avoids building a Stream object on
+    every kernel launch: ~17 us -> <1 us)."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
 
 
