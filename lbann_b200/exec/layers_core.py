@@ -64,6 +64,9 @@ class FullyConnected(ExecLayer):
         par = self.model.parallel
         if par is not None and self.data_layout == "model_parallel" and par.tp_size > 1:
             y = par.tp_linear(self, x)
+        elif (par is not None and self.w.sharded and par.world_size > 1 and not self.transpose
+              and self.out_size % (128 * par.world_size) == 0 and self.in_size % 8 == 0):
+            y = self._sharded_forward(par, x)
         elif self.transpose:
             w = self.w.handle.master.to(x.dtype).t()
             y = F.linear(x, w, None if self.b is None else self.b.handle.master.to(x.dtype))
@@ -71,6 +74,27 @@ class FullyConnected(ExecLayer):
             y = nn.linear(x, self.w.handle, None if self.b is None else self.b.handle,
                           self.fused_act[0], self.fused_act[1])
         return [y.reshape(x.shape[0], *self.out_dims[0])]
+
+    def _sharded_forward(self, par, x):
+        """Weights flagged ``sharded``: every rank multiplies by its own block of output rows
+        gathered tile by tile inside the GEMM (all-gather -> GEMM) and the weight gradient is
+        reduce-scattered by the GEMM epilogue into the owner's rows (parallel/
+        tensor_parallel.py::ShardedLinear).  The row block is a view of the arena's master
+        copy, so optimizer and checkpoints see ordinary weights."""
+        from ..parallel.tensor_parallel import ShardedLinear
+        P, r = par.world_size, par.comm.rank_in_trainer
+        rows = self.out_size // P
+        lin = getattr(self, "_sharded", None)
+        if lin is None:
+            lin = self._sharded = ShardedLinear(par.group, self.w.handle.master[r * rows:(r + 1) * rows])
+        lin.w_shard = self.w.handle.master[r * rows:(r + 1) * rows]
+        y = lin(x)
+        if self.b is not None:
+            y = y + self.b.handle.master.to(y.dtype)
+        if self.fused_act[0] != native.ACT_NONE:
+            from ..ops.gemm import _ACT_FN
+            y = _ACT_FN[self.fused_act[0]](y, self.fused_act[1])
+        return y
 
 
 class _ConvBase(ExecLayer):

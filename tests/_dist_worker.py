@@ -223,8 +223,9 @@ def tensor_parallel():
     return res
 
 
-def model_parallel_fc(grid_height, steps):
-    """MLP whose hidden layers are model-parallel over a process-grid column."""
+def model_parallel_fc(grid_height, steps, sharded=False):
+    """MLP whose hidden layers are model-parallel over a process-grid column (or, with
+    ``sharded``, whose first layer has weights flagged sharded on a data-parallel trainer)."""
     o = opts.reset()
     o.set("disable_cuda", True)
     if grid_height > 1:
@@ -232,8 +233,12 @@ def model_parallel_fc(grid_height, steps):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     x = lbann.Input(data_field="samples")
     t = lbann.Input(data_field="responses")
-    layout = "model_parallel"
-    h = lbann.Relu(lbann.FullyConnected(x, num_neurons=24, has_bias=True, data_layout=layout, name="fc1"))
+    layout = "model_parallel" if not sharded else "data_parallel"
+    if sharded:
+        w = lbann.Weights(initializer=lbann.HeNormalInitializer(), sharded=True, name="fc1_w")
+        h = lbann.Relu(lbann.FullyConnected(x, num_neurons=256, has_bias=True, weights=[w], name="fc1"))
+    else:
+        h = lbann.Relu(lbann.FullyConnected(x, num_neurons=24, has_bias=True, data_layout=layout, name="fc1"))
     h = lbann.Relu(lbann.FullyConnected(h, num_neurons=10, has_bias=True, name="fc2"))
     y = lbann.FullyConnected(h, num_neurons=3, has_bias=False, data_layout=layout, name="fc3")
     loss = lbann.MeanSquaredError(y, t, name="mse")
@@ -255,7 +260,10 @@ def model_parallel_fc(grid_height, steps):
             dc.start_epoch("training")
             b = dc.next_batch("training")
         m.train_step(b.tensors, b.global_size)
-        losses.append(float(m.last_objective))
+        v = m.last_objective.detach().float().reshape(1).clone()
+        if tr.parallel is not None and tr.parallel.dp_size > 1:
+            tr.comm.allreduce(v, "trainer", "sum")       # local objectives are partial sums
+        losses.append(float(v))
     w = {x.name: float(x.values.detach().float().norm()) for x in m.weights}
     tr.shutdown()
     return {"losses": losses, "weight_norms": w, "world": world}
@@ -311,7 +319,7 @@ if __name__ == "__main__":
     elif what == "ltfb":
         res = ltfb(sys.argv[3])
     elif what == "mpfc":
-        res = model_parallel_fc(int(sys.argv[3]), int(sys.argv[4]))
+        res = model_parallel_fc(int(sys.argv[3]), int(sys.argv[4]), len(sys.argv) > 5 and sys.argv[5] == "sharded")
     elif what == "cosmoflow":
         res = cosmoflow(int(sys.argv[3]), int(sys.argv[4]), sys.argv[5] if len(sys.argv) > 5 else "float",
                         int(sys.argv[6]) if len(sys.argv) > 6 else 32)

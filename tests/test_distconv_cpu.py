@@ -84,3 +84,16 @@ def test_ltfb_two_trainers(tmp_path, strategy):
     a, b = res["weights"]
     for k in a:
         assert abs(a[k] - b[k]) <= 1e-5 * max(1.0, abs(a[k])), (strategy, k, a, b)
+
+
+def test_sharded_weights_fully_connected_matches_single(tmp_path):
+    """A fully-connected layer whose weights carry the ``sharded`` flag, on two data-parallel
+    ranks (all-gather -> GEMM forward, reduce-scattered weight gradient), follows the
+    single-process trajectory."""
+    single = _run(1, ["mpfc", "1", "4", "sharded"], str(tmp_path / "a.json"))
+    two = _run(2, ["mpfc", "1", "4", "sharded"], str(tmp_path / "b.json"))
+    assert two["world"] == 2
+    for a, b in zip(single["losses"], two["losses"]):
+        assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], two["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - two["weight_norms"][k]) <= 2e-4 * max(1.0, abs(v)), k
