@@ -85,8 +85,8 @@ class ClockSampler:
 def reference_arm(args):
     # The reference is a CMake superbuild whose distributed linear algebra, collectives and
     # distconv kernels (Hydrogen, Aluminum, DiHydrogen) are fetched from the network; the one
-    # permitted offline install answered: "Directory '/root/reference' is not installable.
-    # Neither 'setup.py' nor 'pyproject.toml' found."
+    # offline pip install of the reference tree answers that the directory is not installable:
+    # neither setup.py nor pyproject.toml is found.
     print(json.dumps({"impl": "reference",
                       "unavailable": "reference is a CMake superbuild (no setup.py/pyproject.toml; "
                                      "Hydrogen/Aluminum/DiHydrogen must be fetched from the network), "

@@ -493,7 +493,11 @@ class ExecModel:
                 if prev is not None:
                     prev[1].synchronize()     # recorded a whole step ago: completes at once
                     overflow = bool(prev[0].item())
-                host = torch.empty(1, dtype=torch.int32).pin_memory()
+                ring = getattr(self, "_amp_pinned", None)
+                if ring is None:       # two pinned words, used alternately (no per-step pinning)
+                    ring = self._amp_pinned = [torch.empty(1, dtype=torch.int32).pin_memory()
+                                               for _ in range(2)]
+                host = ring[self._amp_good_steps & 1 if prev is None else (0 if prev[0] is ring[1] else 1)]
                 host.copy_(flag, non_blocking=True)
                 ev = torch.cuda.Event()
                 ev.record()
