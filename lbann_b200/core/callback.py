@@ -1,0 +1,8 @@
+"""Callback classes."""
+from ..frontend import core as _C
+
+for _n in dir(_C):
+    _o = getattr(_C, _n)
+    if not _n.startswith('_') and (lambda n, o: n.startswith('Callback'))(_n, _o):
+        globals()[_n] = _o
+del _n, _o

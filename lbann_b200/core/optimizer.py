@@ -1,0 +1,8 @@
+"""Optimizer classes."""
+from ..frontend import core as _C
+
+for _n in dir(_C):
+    _o = getattr(_C, _n)
+    if not _n.startswith('_') and (lambda n, o: isinstance(o, type) and issubclass(o, _C.Optimizer))(_n, _o):
+        globals()[_n] = _o
+del _n, _o
