@@ -12,7 +12,8 @@ import numpy as np
 
 from ..frontend import core as L
 from ..modules.base import ChannelwiseFullyConnectedModule, Module
-from ..modules.transformer import LearnedInputEncoding, MultiheadAttention, PositionalEncoding
+from ..modules.transformer import (LearnedInputEncoding, MultiheadAttention, PositionalEncoding,
+                                   RotaryPositionalEmbedding)
 
 
 class LayerNorm(Module):
@@ -190,15 +191,28 @@ class GPT(Module):
     final LayerNorm + LM head; ``forward(tokens)`` returns ``[S, vocab]`` logits."""
 
     def __init__(self, vocab_size=50304, seq_len=2048, d_model=2048, num_heads=16, num_layers=24,
-                 ffn_dim=8192, dropout=0.0, tie_embeddings=False, name="gpt"):
+                 ffn_dim=8192, dropout=0.0, tie_embeddings=False, positional_encoding="learned",
+                 name="gpt"):
         super().__init__()
         self.name, self.vocab, self.seq_len, self.d_model = name, vocab_size, seq_len, d_model
+        if positional_encoding not in ("learned", "sinusoidal", "rope"):
+            raise ValueError(f"unknown positional encoding {positional_encoding!r}")
         self.embed_weights = L.Weights(initializer=L.NormalInitializer(standard_deviation=0.02),
                                        name=f"{name}_token_embeddings")
-        self.positions = LearnedInputEncoding(d_model, seq_len, dropout=dropout, name=f"{name}_positions")
+        # learned / sinusoidal encodings act on the embedded input, rotary embedding on every
+        # layer's queries and keys (applications/nlp/transformer/modeling.py:132-200)
+        layer_enc = None
+        if positional_encoding == "learned":
+            self.positions = LearnedInputEncoding(d_model, seq_len, dropout=dropout, name=f"{name}_positions")
+        elif positional_encoding == "sinusoidal":
+            self.positions = PositionalEncoding(d_model, dropout=dropout, name=f"{name}_positions")
+        else:
+            self.positions = None
+            layer_enc = RotaryPositionalEmbedding(d_model // num_heads, seq_len, num_heads, name=f"{name}_rope")
         self.blocks = [TransformerEncoderLayer(embed_dim=d_model, num_heads=num_heads,
                                                feedforward_dim=ffn_dim, dropout=dropout,
                                                pre_layernorm=True, activation=L.Gelu,
+                                               positional_encoding=layer_enc,
                                                name=f"{name}_block{i}") for i in range(num_layers)]
         self.final_norm = LayerNorm(d_model, name=f"{name}_final_norm")
         self.tie = tie_embeddings
@@ -211,7 +225,8 @@ class GPT(Module):
     def forward(self, tokens):
         x = L.Embedding(tokens, num_embeddings=self.vocab, embedding_dim=self.d_model,
                         weights=self.embed_weights, name=f"{self.name}_embed")
-        x = self.positions.apply_input(x, self.seq_len)
+        if self.positions is not None:
+            x = self.positions.apply_input(x, self.seq_len)
         mask = causal_mask(self.seq_len, f"{self.name}_causal")
         for blk in self.blocks:
             x = blk(x, mask=mask)

@@ -7,4 +7,4 @@ from .rnn import GRU, ChannelwiseGRU, LSTMCell  # noqa: F401
 from .transformations import Cumsum, PeriodicPadding2D, PeriodicPadding3D, Permute  # noqa: F401
 from . import transformer  # noqa: F401
 from .transformer import (LearnedInputEncoding, MultiheadAttention, PositionalEncoding,  # noqa: F401
-                          SequenceEncoding)
+                          RotaryPositionalEmbedding, SequenceEncoding)

@@ -51,7 +51,7 @@ class MultiheadAttention(Module):
         self.output_weights = pair("output")
 
     # ------------------------------------------------------------------ projections
-    def _project(self, queries, keys, values, name):
+    def _project(self, queries, keys, values, name, seqlen=None):
         E = self.embed_dim
         if self.self_attention:
             qkv = L.ChannelwiseFullyConnected(queries, weights=self.qkv_weights, output_channel_dims=[3 * E],
@@ -66,7 +66,7 @@ class MultiheadAttention(Module):
             v = L.ChannelwiseFullyConnected(values, weights=self.value_weights, output_channel_dims=[E],
                                             name=f"{name}_values_fc")
         if self.positional_encoding is not None:
-            q, k, v = self.positional_encoding.apply_layer(q, k, v)
+            q, k, v = self.positional_encoding.apply_layer(q, k, v, seqlen)
         return q, k, v
 
     def forward(self, queries, keys, values, mask=None, seqlen=None):
@@ -74,7 +74,7 @@ class MultiheadAttention(Module):
         softmax (e.g. -1e9 above the diagonal for causal attention)."""
         self.instance += 1
         name = f"{self.name}_instance{self.instance}"
-        q, k, v = self._project(queries, keys, values, name)
+        q, k, v = self._project(queries, keys, values, name, seqlen)
         H, D = self.num_heads, self.head_dim
         if self.separate_heads:
             ctx = self._separate(q, k, v, mask, name)
@@ -129,7 +129,7 @@ class SequenceEncoding:
     def apply_input(self, x, length):
         return x
 
-    def apply_layer(self, q, k, v):
+    def apply_layer(self, q, k, v, length=None):
         return q, k, v
 
 
@@ -192,3 +192,56 @@ class LearnedInputEncoding(SequenceEncoding):
         if self.dropout > 0:
             y = L.Dropout(y, keep_prob=1 - self.dropout, name=f"{name}_drop")
         return y
+
+
+class RotaryPositionalEmbedding(SequenceEncoding):
+    """Rotary position embedding (Su et al., arXiv:2104.09864) applied to the per-layer
+    queries and keys (and, with ``embed_values``, the values): each head's vector is rotated
+    pairwise by position-dependent angles, ``x cos + rotate_half(x) sin``.  The cos / sin
+    tables are constant weights of shape ``[sequence, heads * freq_dim]``
+    (python/lbann/modules/transformer/encoding.py:226-357)."""
+
+    global_count = 0
+
+    def __init__(self, freq_dim, max_sequence_length, num_heads, embed_values=False, theta=10000.0,
+                 name=None):
+        RotaryPositionalEmbedding.global_count += 1
+        if freq_dim % 2:
+            raise ValueError(f"rotary embedding needs an even number of frequencies, got {freq_dim}")
+        self.name = name or f"rope{RotaryPositionalEmbedding.global_count}"
+        self.dim, self.max_len, self.num_heads = freq_dim, max_sequence_length, num_heads
+        self.embed_values, self.theta = embed_values, theta
+        self.instance = 0
+        inv_freq = 1.0 / theta ** (np.arange(0, freq_dim, 2) / freq_dim)
+        ang = np.outer(np.arange(max_sequence_length), inv_freq)
+        ang = np.concatenate([ang, ang], axis=-1)
+        self.cos = _constant_table(np.tile(np.cos(ang), num_heads), f"{self.name}_cos")
+        self.sin = _constant_table(np.tile(np.sin(ang), num_heads), f"{self.name}_sin")
+
+    def _rotate_half(self, x, length, name):
+        H, P = self.num_heads, self.dim
+        r = L.Reshape(x, dims=[length, H, P], name=f"{name}_split")
+        s = L.Slice(r, axis=2, slice_points=[0, P // 2, P], name=f"{name}_halves")
+        x1 = L.Identity(s, name=f"{name}_lo")
+        x2 = L.Identity(s, name=f"{name}_hi")
+        cat = L.Concatenation([L.Scale(x2, constant=-1.0, name=f"{name}_neg"), x1], axis=2,
+                              name=f"{name}_cat")
+        return L.Reshape(cat, dims=[length, H * P], name=f"{name}_merge")
+
+    def _embed(self, x, length, cos, sin, name):
+        rot = self._rotate_half(x, length, name)
+        return L.Add(L.Multiply(x, cos, name=f"{name}_cos"), L.Multiply(rot, sin, name=f"{name}_sin"),
+                     name=f"{name}_out")
+
+    def apply_layer(self, q, k, v, length=None):
+        length = length or self.max_len
+        self.instance += 1
+        base = f"{self.name}_instance{self.instance}"
+        cos, sin = self.cos, self.sin
+        if length != self.max_len:
+            cos = L.Identity(L.Slice(cos, axis=0, slice_points=[0, length], name=f"{base}_cos_slice"))
+            sin = L.Identity(L.Slice(sin, axis=0, slice_points=[0, length], name=f"{base}_sin_slice"))
+        eq = self._embed(q, length, cos, sin, f"{base}_q")
+        ek = self._embed(k, length, cos, sin, f"{base}_k")
+        ev = self._embed(v, length, cos, sin, f"{base}_v") if self.embed_values else v
+        return eq, ek, ev

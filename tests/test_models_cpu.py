@@ -2,6 +2,7 @@
 steps in the in-process executor and lowers the loss on a fixed synthetic batch."""
 import math
 
+import numpy as np
 import pytest
 import torch
 
@@ -115,3 +116,65 @@ def test_recurrent_and_graph_modules_build_and_run():
     losses = _train(model, _reader(4, [24], "normal"), steps=5, mb=4,
                     optimizer=lbann.SGD(learn_rate=0.05))
     assert losses[-1] < losses[0], losses
+
+
+def test_rotary_embedding_matches_the_rotation_formula():
+    """q cos + rotate_half(q) sin per head, against the same written in numpy."""
+    from lbann_b200.modules import RotaryPositionalEmbedding
+    opts.reset().set("disable_cuda", True)
+    S, H, P = 6, 2, 8
+    rope = RotaryPositionalEmbedding(P, S, H)
+    x = lbann.Reshape(lbann.Input(data_field="samples"), dims=[S, H * P])
+    q, k, v = rope.apply_layer(x, x, x, S)
+    data = np.random.RandomState(3).randn(3, S * H * P).astype(np.float32)
+    out = lbann.evaluate([q, k], data, outputs=[q.name]).reshape(3, S, H, P)
+    xs = data.reshape(3, S, H, P)
+    inv = 1.0 / 10000.0 ** (np.arange(0, P, 2) / P)
+    ang = np.outer(np.arange(S), inv)
+    ang = np.concatenate([ang, ang], -1)[None, :, None, :]
+    rot = np.concatenate([-xs[..., P // 2:], xs[..., :P // 2]], -1)
+    want = xs * np.cos(ang) + rot * np.sin(ang)
+    np.testing.assert_allclose(out, want, rtol=1e-4, atol=1e-5)
+    assert v is x          # values are left alone unless embed_values is set
+
+
+def test_gpt_with_rotary_positions_trains():
+    from lbann_b200.models.transformer import construct_gpt_model
+    torch.manual_seed(0)
+    model = construct_gpt_model(vocab_size=48, seq_len=12, d_model=32, num_heads=4, num_layers=1,
+                                ffn_dim=64, positional_encoding="rope")
+    losses = _train(model, _reader(8, [13], "randint:48"), steps=20, mb=8)
+    assert losses[-1] < 0.9 * losses[0], losses
+
+
+def test_transformer_parallelism_switches_mark_the_graph():
+    """--fsdp-mlp, --ffn-parallel, --lm-head-parallel and --layer-parallel act on the model
+    by layer and weight names; the flags reach the serialised protobuf."""
+    import argparse
+    from lbann_b200.models import parallelism as par
+    from lbann_b200.models.transformer import construct_gpt_model
+    ap = argparse.ArgumentParser()
+    par.add_transformer_parallelism_arguments(ap)
+
+    model = construct_gpt_model(vocab_size=32, seq_len=8, d_model=16, num_heads=2, num_layers=4, ffn_dim=32)
+    assert par.apply_fsdp_mlp(model, ap.parse_args(["--fsdp-mlp"])) == 8      # 4 blocks x (fc1, fc2)
+    sharded = [w.name for l in model.layers for w in l.weights if w.sharded]
+    assert sharded and all(n.endswith(("_fc1_matrix", "_fc2_matrix")) for n in sharded)
+    with pytest.raises(ValueError):
+        par.apply_fsdp_mlp(model, ap.parse_args(["--fsdp-mlp", "--ffn-parallel"]))
+
+    model = construct_gpt_model(vocab_size=32, seq_len=8, d_model=16, num_heads=2, num_layers=4, ffn_dim=32)
+    changed = par.apply_ffn_model_parallelism(model, ap.parse_args(["--ffn-parallel"]), blocks=[1, 3])
+    assert len(changed) == 4 and all("_block1_" in n or "_block3_" in n for n in changed)
+    head = next(l for l in model.layers if l.name.startswith("gpt_head"))
+    tail = par.apply_lm_head_model_parallelism(model, head, ap.parse_args(["--lm-head-parallel"]))
+    assert head.name in tail and "loss" in tail and "gpt_embed" not in tail
+    grids = par.apply_layer_parallelism(model, ap.parse_args(["--layer-parallel", "--lp-count", "2"]))
+    assert grids == 2
+    tags = {l.name: (l.grid_tag or {}).get("value", 0) for l in model.layers}
+    assert tags[next(n for n in tags if "_block0_" in n)] == 1
+    assert tags[next(n for n in tags if "_block3_" in n)] == 2
+    msg = model.export_proto()
+    layouts = {l.name: l.data_layout for l in msg.layer}
+    assert layouts[head.name] == "model_parallel"
+    assert any(l.grid_tag.value == 2 for l in msg.layer)
