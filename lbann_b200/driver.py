@@ -146,6 +146,14 @@ def main(argv: Optional[List[str]] = None) -> int:
         for p in parts:
             msg.MergeFrom(load_prototext(p))
     else:
+        rank = int(os.environ.get("RANK", "0"))
+        ppt = o.get_int("procs_per_trainer")
+        if o.get_bool("generate_multi_proto") and ppt > 0 and "trainer0" in path:
+            # one experiment file per trainer: <prefix>trainer0<suffix> names trainer 0's and
+            # trainer i reads <prefix>trainer<i><suffix> (src/proto/proto_common.cpp, used by
+            # python/lbann/contrib/hyperparameter.py:80-88)
+            head, _, tail = path.rpartition("trainer0")
+            path = f"{head}trainer{rank // ppt}{tail}"
         msg = load_prototext(path)
     apply_overrides(msg, o)
     rank = int(os.environ.get("RANK", "0"))
