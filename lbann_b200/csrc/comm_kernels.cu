@@ -161,6 +161,107 @@ __global__ void group_barrier_kernel(PeerPtrs pp, int rank, int world, int phase
   block_rendezvous(pp, rank, world, phase, epoch, status);
 }
 
+// ---------------------------------------------------------------------------------
+// Halo exchange of a depth-partitioned activation as ONE kernel.
+//
+// Forward: the local tensor x [N][Dl][plane] is copied into the interior of this rank's
+// extended buffer [N][Dl + 2h][plane] (a symmetric buffer), the planes beyond the global
+// boundary are filled, and - after the neighbours signalled that they no longer read the
+// previous contents of their halo planes - the first / last h planes are stored into the
+// halo planes of the rank above / below.  A second rendezvous makes the stores visible
+// before the consumer (the convolution that follows in the stream) starts.
+// `up` / `down`: group ranks of the neighbours, -1 at the global boundary.  `pv`: 16-byte
+// vectors per plane.  Every rank has the same Dl.
+__global__ void __launch_bounds__(512)
+halo_fwd_kernel(PeerPtrs pp, int rank, int world, int up, int down, const uint4* __restrict__ x,
+                long long N, long long Dl, long long h, long long pv, uint32_t fill_bits,
+                uint32_t epoch, int* status) {
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  const long long ext_pitch = (Dl + 2 * h) * pv;
+  uint4* mine = reinterpret_cast<uint4*>(pp.buf[rank]);
+  const long long inner = Dl * pv, edge = h * pv;
+  for (long long i = tid; i < N * inner; i += nthreads) {
+    const long long n = i / inner, rem = i - n * inner;
+    mine[n * ext_pitch + edge + rem] = x[i];
+  }
+  const uint4 fv = make_uint4(fill_bits, fill_bits, fill_bits, fill_bits);
+  if (up < 0 || down < 0) {
+    for (long long i = tid; i < N * edge; i += nthreads) {
+      const long long n = i / edge, rem = i - n * edge;
+      if (up < 0) mine[n * ext_pitch + rem] = fv;
+      if (down < 0) mine[n * ext_pitch + edge + inner + rem] = fv;
+    }
+  }
+  if (!block_rendezvous(pp, rank, world, 2, epoch, status)) return;
+  uint4* above = up >= 0 ? reinterpret_cast<uint4*>(pp.buf[up]) : nullptr;
+  uint4* below = down >= 0 ? reinterpret_cast<uint4*>(pp.buf[down]) : nullptr;
+  for (long long i = tid; i < N * edge; i += nthreads) {
+    const long long n = i / edge, rem = i - n * edge;
+    if (above) above[n * ext_pitch + edge + inner + rem] = x[n * inner + rem];
+    if (below) below[n * ext_pitch + rem] = x[n * inner + inner - edge + rem];
+  }
+  block_rendezvous(pp, rank, world, 3, epoch, status);
+}
+
+// Backward: g [N][Dl + 2h][plane] is the gradient of the extended tensor.  The gradients of
+// the halo planes belong to the neighbours: they are stored into the neighbours' receive
+// areas ([2][N][h][plane]: slot 0 from the rank above, slot 1 from the rank below), the
+// planes that receive nothing are copied meanwhile, and after the rendezvous the boundary
+// planes are written as own gradient + received gradient.  The closing rendezvous keeps the
+// neighbours from overwriting the receive area before it was read.
+template <typename T>
+__global__ void __launch_bounds__(512)
+halo_bwd_kernel(PeerPtrs pp, int rank, int world, int up, int down, const uint4* __restrict__ g,
+                uint4* __restrict__ dx, long long N, long long Dl, long long h, long long pv,
+                uint32_t epoch, int* status) {
+  constexpr int V = 16 / sizeof(T);
+  const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  const long long nthreads = (long long)gridDim.x * blockDim.x;
+  const long long ext_pitch = (Dl + 2 * h) * pv;
+  const long long inner = Dl * pv, edge = h * pv;
+  uint4* above = up >= 0 ? reinterpret_cast<uint4*>(pp.buf[up]) : nullptr;
+  uint4* below = down >= 0 ? reinterpret_cast<uint4*>(pp.buf[down]) : nullptr;
+  for (long long i = tid; i < N * edge; i += nthreads) {
+    const long long n = i / edge, rem = i - n * edge;
+    if (above) above[(N + n) * edge + rem] = g[n * ext_pitch + rem];                  // their slot 1
+    if (below) below[n * edge + rem] = g[n * ext_pitch + edge + inner + rem];         // their slot 0
+  }
+  // planes [lo, hi) receive nothing
+  const long long lo = up >= 0 ? (h < Dl ? h : Dl) : 0;
+  long long hi = down >= 0 ? Dl - h : Dl;
+  if (hi < lo) hi = lo;
+  const long long mid = (hi - lo) * pv;
+  for (long long i = tid; i < N * mid; i += nthreads) {
+    const long long n = i / mid, rem = i - n * mid;
+    dx[n * inner + lo * pv + rem] = g[n * ext_pitch + edge + lo * pv + rem];
+  }
+  if (!block_rendezvous(pp, rank, world, 3, epoch, status)) return;
+  const uint4* recv = reinterpret_cast<const uint4*>(pp.buf[rank]);
+  const long long nb = lo + (Dl - hi);          // boundary planes
+  for (long long i = tid; i < N * nb * pv; i += nthreads) {
+    const long long n = i / (nb * pv), r2 = i - n * nb * pv;
+    const long long j = r2 / pv, v = r2 - j * pv;
+    const long long d = j < lo ? j : hi + (j - lo);
+    uint4 acc = g[n * ext_pitch + edge + d * pv + v];
+    T* a = reinterpret_cast<T*>(&acc);
+    if (up >= 0 && d < h) {
+      const uint4 r = __ldcg(recv + n * edge + d * pv + v);
+      const T* e = reinterpret_cast<const T*>(&r);
+#pragma unroll
+      for (int k = 0; k < V; ++k) a[k] = from_f32<T>(to_f32<T>(a[k]) + to_f32<T>(e[k]));
+    }
+    if (down >= 0 && d >= Dl - h) {
+      const uint4 r = __ldcg(recv + (N + n) * edge + (d - (Dl - h)) * pv + v);
+      const T* e = reinterpret_cast<const T*>(&r);
+#pragma unroll
+      for (int k = 0; k < V; ++k) a[k] = from_f32<T>(to_f32<T>(a[k]) + to_f32<T>(e[k]));
+    }
+    dx[n * inner + d * pv + v] = acc;
+  }
+  block_rendezvous(pp, rank, world, 2, epoch, status);
+}
+
 static PeerPtrs make_ptrs(void* const* bufs, void* const* pads, int world) {
   PeerPtrs pp;
   for (int i = 0; i < kMaxRanks; ++i) {
@@ -221,6 +322,72 @@ int lb_put_rows(const void* src, long long src_pitch, void* dst, long long dst_p
   if (blocks > cap) blocks = cap;
   put_rows_kernel<<<(int)blocks, 256, 0, s>>>((const uint8_t*)src, src_pitch, (uint8_t*)dst,
                                                dst_pitch, rows, row_bytes);
+  return (int)cudaGetLastError();
+}
+
+static int halo_blocks(long long vectors) {
+  long long b = (vectors + 512 * 8 - 1) / (512 * 8);      // >= 8 vectors per thread
+  if (b < 1) b = 1;
+  if (b > lb::kCommBlocks) b = lb::kCommBlocks;
+  return (int)b;
+}
+
+// ext_bufs: the extended buffers of the group's ranks ([N][Dl + 2h][plane_bytes]); x: this
+// rank's [N][Dl][plane_bytes].  fill: value of the planes beyond the global boundary.
+// Returns -2 when the shape is not covered (plane not a multiple of 16 bytes, Dl < h).
+int lb_halo_exchange_fwd(void* const* ext_bufs, void* const* pads, int rank, int world, int up,
+                         int down, const void* x, long long N, long long Dl, long long h,
+                         long long plane_bytes, float fill, int dtype, unsigned epoch,
+                         void* stream_) {
+  using namespace lb;
+  if (world < 2 || world > kMaxRanks || up >= world || down >= world) return -1;
+  if (plane_bytes % 16 || Dl < h || h < 1 || N < 1) return -2;
+  if (reinterpret_cast<uintptr_t>(x) & 15) return -2;
+  uint32_t bits;
+  if (dtype == kF32) {
+    memcpy(&bits, &fill, 4);
+  } else {
+    uint16_t hb;
+    if (dtype == kF16) {
+      const __half v = __float2half(fill);
+      memcpy(&hb, &v, 2);
+    } else {
+      const __nv_bfloat16 v = __float2bfloat16(fill);
+      memcpy(&hb, &v, 2);
+    }
+    bits = (uint32_t)hb | ((uint32_t)hb << 16);
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  PeerPtrs pp = make_ptrs(ext_bufs, pads, world);
+  const long long pv = plane_bytes / 16;
+  halo_fwd_kernel<<<halo_blocks(N * Dl * pv), 512, 0, s>>>(
+      pp, rank, world, up, down, reinterpret_cast<const uint4*>(x), N, Dl, h, pv, bits, epoch,
+      lbhost::status_word());
+  return (int)cudaGetLastError();
+}
+
+// recv_bufs: the receive areas of the group's ranks ([2][N][h][plane_bytes]); g: gradient of
+// the extended tensor; dx: [N][Dl][plane_bytes].
+int lb_halo_exchange_bwd(void* const* recv_bufs, void* const* pads, int rank, int world, int up,
+                         int down, const void* g, void* dx, long long N, long long Dl,
+                         long long h, long long plane_bytes, int dtype, unsigned epoch,
+                         void* stream_) {
+  using namespace lb;
+  if (world < 2 || world > kMaxRanks || up >= world || down >= world) return -1;
+  if (plane_bytes % 16 || Dl < h || h < 1 || N < 1) return -2;
+  if ((reinterpret_cast<uintptr_t>(g) & 15) || (reinterpret_cast<uintptr_t>(dx) & 15)) return -2;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  PeerPtrs pp = make_ptrs(recv_bufs, pads, world);
+  const long long pv = plane_bytes / 16;
+  const int blocks = halo_blocks(N * Dl * pv);
+  const uint4* gv = reinterpret_cast<const uint4*>(g);
+  uint4* dv = reinterpret_cast<uint4*>(dx);
+  if (dtype == kF32)
+    halo_bwd_kernel<float><<<blocks, 512, 0, s>>>(pp, rank, world, up, down, gv, dv, N, Dl, h, pv, epoch, lbhost::status_word());
+  else if (dtype == kBF16)
+    halo_bwd_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(pp, rank, world, up, down, gv, dv, N, Dl, h, pv, epoch, lbhost::status_word());
+  else
+    halo_bwd_kernel<__half><<<blocks, 512, 0, s>>>(pp, rank, world, up, down, gv, dv, N, Dl, h, pv, epoch, lbhost::status_word());
   return (int)cudaGetLastError();
 }
 

@@ -43,6 +43,9 @@ def _lib():
                                           c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p]
         lib.lb_bn_partial_sums.restype = c_int
         lib.lb_bn_partial_sums.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_void_p]
+        lib.lb_outer_accum.restype = c_int
+        lib.lb_outer_accum.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_ll, c_float,
+                                       c_float, c_int, c_void_p]
         lib.lb_bn_finalize_apply.restype = c_int
         lib.lb_bn_finalize_apply.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                              c_void_p, c_void_p, c_void_p, c_ll, c_int, c_int,
@@ -182,10 +185,27 @@ class _Linear(torch.autograd.Function):
         if ctx.needs_input_grad[0]:
             dx = gemm(dy2, wh.cast(dy2.dtype)).reshape(xshape)
         if wh.grad is not None:
-            gemm(dy2, x2, trans_a=True, out=wh.grad.view(wh.master.shape), beta=1.0)
+            _weight_grad(dy2, x2, wh.grad.view(wh.master.shape))
         if bh is not None and bh.grad is not None:
             bh.grad.add_(column_sums(dy2))
         return dx, None, None, None, None, None, None
+
+
+def _weight_grad(dy2: torch.Tensor, x2: torch.Tensor, grad: torch.Tensor) -> None:
+    """grad[out, in] += dy2^T x2.  Mini-batches of at most 16 rows make this a rank-K update
+    bound by the fp32 read-modify-write of ``grad``; a plain kernel does it at memory speed,
+    everything else goes to the tensor-core GEMM."""
+    K = dy2.shape[0]
+    if (K in (1, 2, 4, 8, 16) and grad.dtype == torch.float32 and grad.is_contiguous()
+            and x2.shape[1] % 4 == 0 and dy2.dtype == x2.dtype and _native_ok(x2)):
+        rc = _lib().lb_outer_accum(dy2.data_ptr(), x2.data_ptr(), grad.data_ptr(), K, dy2.shape[1],
+                                   x2.shape[1], 1.0, 1.0, native.dtype_code(x2.dtype),
+                                   native.stream_ptr())
+        if rc != -2:
+            native.check(rc, "lb_outer_accum")
+            native.count_launch()
+            return
+    gemm(dy2, x2, trans_a=True, out=grad, beta=1.0)
 
 
 def linear(x, wh: WeightHandle, bh: Optional[WeightHandle] = None, act: int = native.ACT_NONE,

@@ -45,6 +45,12 @@ def _lib():
                                               c_int, c_ll, ctypes.c_uint, c_void_p]
         lib.lb_put_rows.restype = c_int
         lib.lb_put_rows.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_ll, c_ll, c_void_p]
+        lib.lb_halo_exchange_fwd.restype = c_int
+        lib.lb_halo_exchange_fwd.argtypes = [vpp, vpp, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_ll,
+                                             c_ll, c_ll, c_float, c_int, ctypes.c_uint, c_void_p]
+        lib.lb_halo_exchange_bwd.restype = c_int
+        lib.lb_halo_exchange_bwd.argtypes = [vpp, vpp, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                                             c_ll, c_ll, c_ll, c_ll, c_int, ctypes.c_uint, c_void_p]
         lib.lb_group_barrier.restype = c_int
         lib.lb_group_barrier.argtypes = [vpp, vpp, c_int, c_int, c_int, ctypes.c_uint, c_void_p]
         _configured = True
@@ -203,6 +209,41 @@ class SymmetricGroup:
         native.check(rc, "lb_put_rows")
         native.count_launch()
         self.bytes_moved += rows * row_bytes
+
+    def halo_forward(self, x: torch.Tensor, ext: SymmetricBuffer, n: int, dl: int, h: int,
+                     plane_bytes: int, fill: float) -> bool:
+        """One kernel: ``x`` [n, dl, plane] -> interior of this rank's extended buffer, boundary
+        planes -> the neighbours' halo planes, with the two rendezvous inside.  Returns False
+        when the shape is not covered (the caller then uses separate puts and barriers)."""
+        up = self.rank - 1 if self.rank > 0 else -1
+        down = self.rank + 1 if self.rank < self.world - 1 else -1
+        rc = _lib().lb_halo_exchange_fwd(ext._c_ptrs, self.pad._c_ptrs, self.rank, self.world, up, down,
+                                         x.data_ptr(), n, dl, h, plane_bytes, float(fill),
+                                         native.dtype_code(x.dtype), self._next_epoch(),
+                                         native.stream_ptr())
+        if rc == -2:
+            return False
+        native.check(rc, "lb_halo_exchange_fwd")
+        native.count_launch()
+        self.bytes_moved += n * h * plane_bytes * ((up >= 0) + (down >= 0))
+        return True
+
+    def halo_backward(self, g: torch.Tensor, recv: SymmetricBuffer, dx: torch.Tensor, n: int, dl: int,
+                      h: int, plane_bytes: int) -> bool:
+        """One kernel: halo-plane gradients -> the neighbours' receive areas, and
+        ``dx`` = interior of ``g`` + what the neighbours sent."""
+        up = self.rank - 1 if self.rank > 0 else -1
+        down = self.rank + 1 if self.rank < self.world - 1 else -1
+        rc = _lib().lb_halo_exchange_bwd(recv._c_ptrs, self.pad._c_ptrs, self.rank, self.world, up, down,
+                                         g.data_ptr(), dx.data_ptr(), n, dl, h, plane_bytes,
+                                         native.dtype_code(g.dtype), self._next_epoch(),
+                                         native.stream_ptr())
+        if rc == -2:
+            return False
+        native.check(rc, "lb_halo_exchange_bwd")
+        native.count_launch()
+        self.bytes_moved += n * h * plane_bytes * ((up >= 0) + (down >= 0))
+        return True
 
     def barrier_device(self, phase: int = 3):
         """Stream-ordered rendezvous of the group (no host synchronisation)."""

@@ -146,3 +146,18 @@ def test_fused_optimizer_matches_cpu_formulas():
             a.step()
     torch.cuda.synchronize()
     torch.testing.assert_close(arenas[0].master.cpu(), arenas[1].master, rtol=1e-5, atol=1e-6)
+
+
+@pytest.mark.parametrize("rows,out_f,in_f,dt", [(8, 256, 2048, torch.float16), (4, 100, 36, torch.bfloat16),
+                                                (16, 64, 520, torch.float16), (3, 64, 128, torch.float16)])
+def test_short_batch_weight_gradient(rows, out_f, in_f, dt):
+    """grad += dy^T x for mini-batches of a few rows (rank-K update kernel; 3 rows falls back
+    to the tensor-core GEMM) against fp32 matmul, accumulating onto a non-zero gradient."""
+    torch.manual_seed(1)
+    dy = torch.randn(rows, out_f, device="cuda").to(dt)
+    x = torch.randn(rows, in_f, device="cuda").to(dt)
+    grad = torch.randn(out_f, in_f, device="cuda")
+    want = grad + dy.float().t() @ x.float()
+    nn._weight_grad(dy, x, grad)
+    assert native.consume_status() == 0
+    torch.testing.assert_close(grad, want, rtol=2e-3, atol=2e-3)
