@@ -176,7 +176,12 @@ class DataCoordinator:
                 b = Batch(dict(out), len(gidx), mine, pos + st.mb >= len(st.order), pos)
                 b.h2d_bytes = nbytes if self.device.type == "cuda" else 0
                 return b
-        host = r.fetch_batch(mine, fields)
+        if getattr(r, "owner_of", None) is not None and r.world == self.dp_size and self.dp_size > 1:
+            # data store: owners send the samples this rank needs (no file reads after the
+            # first epoch)
+            host = r.fetch_batch_global(gidx, self.dp_rank, self.dp_size, fields)
+        else:
+            host = r.fetch_batch(mine, fields)
         out = {}
         nbytes = 0
         for f, t in host.items():

@@ -614,6 +614,56 @@ class ArrayReader(DataReader):
         return self.arrays[field][index].reshape(self._fields[field])
 
 
+@register("numpy_npz_conduit", "npz_bundle")
+class SampleListReader(DataReader):
+    """Bundle files selected through a sample list (``sample_list`` of the reader message).
+    A bundle is an ``.npz`` archive whose arrays are called ``<sample>/<field>``; the fields
+    of the first sample define the data fields.  A bounded set of bundles stays open, as in
+    the reference's open-file sample lists
+    (include/lbann/data_ingestion/readers/sample_list_open_files.hpp, used by
+    data_reader_npz_ras_lipid.cpp / data_reader_jag_conduit.cpp)."""
+
+    max_open_files = 16
+
+    def load(self):
+        from .sample_list import SampleList
+        p = self.proto
+        path = p.sample_list if os.path.isabs(p.sample_list) or not p.data_filedir \
+            else os.path.join(p.data_filedir, p.sample_list)
+        self.sample_list = SampleList.load(path)
+        if not len(self.sample_list):
+            raise ValueError(f"sample list {path} selects no samples")
+        self._open_files: Dict[str, object] = {}
+        first = self._bundle(0)
+        name = self.sample_list.samples[0][1]
+        self._fields = {}
+        for key in first.files:
+            s, _, f = key.partition("/")
+            if s == name and f:
+                self._fields[f] = tuple(first[key].shape) or (1,)
+        if self.num_labels and "labels" in self._fields:
+            self._fields["labels"] = (self.num_labels,)
+
+    def _bundle(self, index):
+        path = self.sample_list.path_of(index)
+        z = self._open_files.get(path)
+        if z is None:
+            if len(self._open_files) >= self.max_open_files:
+                old = next(iter(self._open_files))
+                self._open_files.pop(old).close()
+            z = self._open_files[path] = np.load(path)
+        return z
+
+    def total_samples(self):
+        return len(self.sample_list)
+
+    def fetch_field(self, field, index):
+        a = self._bundle(index)[f"{self.sample_list.samples[index][1]}/{field}"]
+        if field == "labels" and self.num_labels:
+            return self.one_hot(int(np.asarray(a).reshape(-1)[0]))
+        return np.asarray(a, dtype=np.float32).reshape(self._fields[field])
+
+
 _UNAVAILABLE = {
     "jag_conduit": "needs the Conduit library",
     "ras_lipid": "needs the Conduit library",

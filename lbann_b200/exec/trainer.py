@@ -124,6 +124,14 @@ class ExecTrainer:
             dp_rank, dp_size = 0, 1
             if self.parallel is not None:
                 dp_rank, dp_size = self.parallel.data_rank(self.distconv), self.parallel.data_size(self.distconv)
+            o = opts.current()
+            if o.get_bool("use_data_store") or o.get_bool("preload_data_store"):
+                from ..data.store import DataStore
+                pg = DataStore.make_group() if dp_size == self.comm.world_size and dp_size > 1 else None
+                world = dp_size if (pg is not None or dp_size == 1) else 1
+                for k, role in enumerate(sorted(readers)):
+                    readers[role] = DataStore(readers[role], dp_rank if world > 1 else 0, world, pg,
+                                              preload=o.get_bool("preload_data_store"), tag=k)
             self.data_coordinator = DataCoordinator(
                 readers, self.max_mini_batch_size, device=self.device, dp_rank=dp_rank,
                 dp_size=dp_size, seed=self.data_seed, io_threads=self.io_threads,

@@ -269,6 +269,34 @@ def model_parallel_fc(grid_height, steps, sharded=False):
     return {"losses": losses, "weight_norms": w, "world": world}
 
 
+def data_store(preload):
+    """Ranks of one trainer draw differently shuffled epochs through the data store: every
+    sample is read from the reader once, later epochs are served by owner -> consumer sends."""
+    import numpy as np
+    import torch.distributed as dist
+    from lbann_b200.data.readers import ArrayReader
+    from lbann_b200.data.store import DataStore
+    dist.init_process_group("gloo")
+    rank, world = dist.get_rank(), dist.get_world_size()
+    n = 24
+    arrays = {"samples": np.arange(n * 6, dtype=np.float32).reshape(n, 2, 3),
+              "responses": -np.arange(n, dtype=np.float32).reshape(n, 1)}
+    reader = ArrayReader(arrays).setup(0)
+    store = DataStore(reader, rank, world, DataStore.make_group(), preload=preload)
+    ok = True
+    for epoch in range(3):
+        order = np.random.RandomState(epoch).permutation(n)
+        for pos in range(0, n, 8):
+            gidx = order[pos:pos + 8]
+            mine = gidx[rank::world]
+            got = store.fetch_batch_global(gidx, rank, world, ["samples", "responses"])
+            ok = ok and np.array_equal(got["samples"].numpy(), arrays["samples"][mine])
+            ok = ok and np.array_equal(got["responses"].numpy(), arrays["responses"][mine])
+    stats = [None] * world
+    dist.all_gather_object(stats, dict(store.stats, ok=bool(ok), cached=len(store.cache)))
+    return {"world": world, "stats": stats, "samples": n}
+
+
 def ltfb(strategy):
     """Two trainers of one rank each run LTFB tournaments on an MLP regression."""
     o = opts.reset()
@@ -318,6 +346,8 @@ if __name__ == "__main__":
         res = tensor_parallel()
     elif what == "ltfb":
         res = ltfb(sys.argv[3])
+    elif what == "store":
+        res = data_store(sys.argv[3] == "preload")
     elif what == "mpfc":
         res = model_parallel_fc(int(sys.argv[3]), int(sys.argv[4]), len(sys.argv) > 5 and sys.argv[5] == "sharded")
     elif what == "cosmoflow":

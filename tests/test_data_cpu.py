@@ -98,3 +98,103 @@ def test_coordinator_deals_every_sample_once_per_epoch_across_ranks():
                 break
         dc.shutdown()
     assert sorted(seen) == list(range(20))
+
+
+# ---------------------------------------------------------------------------- sample lists / data store
+def _write_bundles(tmp_path, files=3, per_file=4):
+    names = {}
+    for b in range(files):
+        arrays = {}
+        for s in range(per_file):
+            name = f"s{b}_{s}"
+            arrays[f"{name}/samples"] = np.full((2, 2), 10 * b + s, dtype=np.float32)
+            arrays[f"{name}/responses"] = np.asarray([b - s], dtype=np.float32)
+        np.savez(tmp_path / f"bundle{b}.npz", **arrays)
+        names[f"bundle{b}.npz"] = [f"s{b}_{s}" for s in range(per_file)]
+    return names
+
+
+def test_sample_list_inclusion_exclusion_striding_and_round_trip(tmp_path):
+    from lbann_b200.data.sample_list import SampleList
+    _write_bundles(tmp_path)
+    inc = (f"MULTI-SAMPLE_INCLUSION\n5 7 3\n{tmp_path}\n"
+           "bundle0.npz 2 2 s0_0 s0_3\nbundle1.npz 1 3 s1_2\nbundle2.npz 2 2 s2_1 s2_2\n")
+    sl = SampleList.load_from_string(inc)
+    assert sl.samples == [("bundle0.npz", "s0_0"), ("bundle0.npz", "s0_3"), ("bundle1.npz", "s1_2"),
+                          ("bundle2.npz", "s2_1"), ("bundle2.npz", "s2_2")]
+    exc = (f"MULTI-SAMPLE_EXCLUSION\n9 3 3\n{tmp_path}\n"
+           "bundle0.npz 3 1 s0_1\nbundle1.npz 4 0\nbundle2.npz 2 2 s2_0 s2_3\n")
+    se = SampleList.load_from_string(exc)
+    assert len(se) == 9 and ("bundle0.npz", "s0_1") not in se.samples and ("bundle1.npz", "s1_3") in se.samples
+    # every second line for rank 1 of 2
+    assert SampleList.load_from_string(inc, stride=2, offset=1).files() == ["bundle1.npz"]
+    v2 = SampleList.load_from_string(f"MULTI-SAMPLE_INCLUSION_V2\n2 1\n{tmp_path}\nbundle1.npz 2 s1_0 s1_1\n")
+    assert [s for _, s in v2.samples] == ["s1_0", "s1_1"]
+    single = SampleList.load_from_string(f"SINGLE-SAMPLE\n2\n{tmp_path}\na.npy 3\nb.npy 5\n")
+    assert single.samples == [("a.npy", ""), ("b.npy", "")] and single.labels == ["3", "5"]
+    # written lists read back the same; partitions cover the list
+    se.write(tmp_path / "again.txt")
+    assert SampleList.load(str(tmp_path / "again.txt")).samples == se.samples
+    parts = se.partition(2)
+    assert sorted(parts[0].samples + parts[1].samples) == sorted(se.samples)
+    with pytest.raises(ValueError):
+        SampleList.load_from_string(f"MULTI-SAMPLE_INCLUSION\n1 0 1\n{tmp_path}\nbundle0.npz 2 0 s0_0\n")
+
+
+def test_sample_list_reader_and_single_rank_store(tmp_path):
+    from lbann_b200.data.readers import build_reader
+    from lbann_b200.data.store import DataStore
+    _write_bundles(tmp_path)
+    (tmp_path / "list.txt").write_text(
+        f"MULTI-SAMPLE_INCLUSION\n4 8 2\n{tmp_path}\nbundle0.npz 2 2 s0_1 s0_2\nbundle2.npz 2 2 s2_0 s2_3\n")
+    rp = lbann.reader_pb2.Reader(name="npz_bundle", role="train", sample_list=str(tmp_path / "list.txt"),
+                                 fraction_of_data_to_use=1.0)
+    r = build_reader(rp).setup(0)
+    assert r.num_samples() == 4 and r.dims("samples") == (2, 2)
+    b = r.fetch_batch([0, 3], ["samples", "responses"])
+    assert b["samples"][:, 0, 0].tolist() == [1.0, 23.0] and b["responses"].reshape(-1).tolist() == [-1.0, -1.0]
+    store = DataStore(r)
+    for _ in range(3):
+        got = store.fetch_batch([3, 1, 0, 2], ["samples"])
+        assert got["samples"][:, 0, 0].tolist() == [23.0, 2.0, 1.0, 20.0]
+    assert store.stats["file_reads"] == 4 and store.stats["cache_hits"] == 8
+
+
+@pytest.mark.parametrize("mode", ["dynamic", "preload"])
+def test_data_store_exchanges_samples_between_two_ranks(tmp_path, mode):
+    from test_distconv_cpu import _run
+    res = _run(2, ["store", mode], str(tmp_path / "s.json"))
+    stats = res["stats"]
+    assert all(s["ok"] for s in stats)
+    # every sample was read from the reader exactly once over both ranks and three epochs
+    assert sum(s["file_reads"] for s in stats) == res["samples"]
+    assert sum(s["cached"] for s in stats) == res["samples"]
+    assert sum(s["sent"] for s in stats) == sum(s["received"] for s in stats) > 0
+
+
+def test_trainer_runs_with_the_data_store_option():
+    """--use_data_store puts the cache in front of every reader: two epochs read each sample
+    once."""
+    from lbann_b200.exec.trainer import ExecTrainer
+    from lbann_b200.utils import options as opts
+    o = opts.reset()
+    o.set("disable_cuda", True)
+    o.set("use_data_store", True)
+    x = lbann.Input(data_field="samples")
+    y = lbann.FullyConnected(x, num_neurons=3)
+    loss = lbann.MeanSquaredError(y, lbann.Input(data_field="responses"))
+    model = lbann.Model(2, layers=list(lbann.traverse_layer_graph([x])),
+                        objective_function=lbann.ObjectiveFunction([loss]))
+    r = reader_pb2.Reader(name="synthetic", role="train", num_samples=12, synth_dimensions="5",
+                          synth_response_dimensions="3", fraction_of_data_to_use=1.0, shuffle=True)
+    dr = reader_pb2.DataReader()
+    dr.reader.append(r)
+    exp = lbann.proto.serialize.build_experiment(trainer=lbann.Trainer(mini_batch_size=4), model=model,
+                                                 data_reader=dr, optimizer=lbann.SGD(learn_rate=0.01))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    tr.train(m)
+    store = tr.data_coordinator.reader("training")
+    tr.shutdown()
+    opts.reset()
+    assert store.stats["file_reads"] == 12 and store.stats["cache_hits"] >= 12
