@@ -262,6 +262,68 @@ halo_bwd_kernel(PeerPtrs pp, int rank, int world, int up, int down, const uint4*
   block_rendezvous(pp, rank, world, 2, epoch, status);
 }
 
+// ---------------------------------------------------------------------------------
+// Embedding table partitioned over the ranks of a group (row i lives on rank i % world as
+// local row i / world of that rank's fp32 shard in symmetric memory).
+//
+// Gather (forward): one warp per looked-up index reads the row from its owner with plain
+// peer loads and writes it, converted, into the local output.  Scatter (backward): one warp
+// per index adds scale * dy to the owner's row with fp32 reductions sent over NVLink; with
+// scale = -learning_rate that IS the sparse SGD step, applied where the row lives.  Both
+// kernels open with a rendezvous: a peer that has started this kernel has finished whatever
+// preceded it in its stream (the previous scatter before a gather, the gather before a
+// scatter), so rows are never read half-updated.
+// Takes the place of the reference's NVSHMEM kernels (src/layers/misc/dist_embedding.cu:221-360,
+// 479-640).
+template <typename T>
+__global__ void __launch_bounds__(256)
+dist_embed_gather_kernel(PeerPtrs pp, int rank, int world, const long long* __restrict__ idx,
+                         T* __restrict__ out, long long n, int dim, long long num_embeddings,
+                         uint32_t epoch, int* status) {
+  if (!block_rendezvous(pp, rank, world, 2, epoch, status)) return;
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long s = warp; s < n; s += nwarps) {
+    const long long i = idx[s];
+    T* o = out + s * dim;
+    if (i < 0 || i >= num_embeddings) {
+      for (int k = lane; k < dim; k += 32) o[k] = from_f32<T>(0.f);
+      continue;
+    }
+    const float* row = reinterpret_cast<const float*>(pp.buf[i % world]) + (i / world) * dim;
+    if ((dim & 3) == 0) {
+      for (int k = lane * 4; k < dim; k += 128) {
+        const float4 v = *reinterpret_cast<const float4*>(row + k);
+        o[k] = from_f32<T>(v.x);
+        o[k + 1] = from_f32<T>(v.y);
+        o[k + 2] = from_f32<T>(v.z);
+        o[k + 3] = from_f32<T>(v.w);
+      }
+    } else {
+      for (int k = lane; k < dim; k += 32) o[k] = from_f32<T>(row[k]);
+    }
+  }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+dist_embed_scatter_kernel(PeerPtrs pp, int rank, int world, const long long* __restrict__ idx,
+                          const T* __restrict__ dy, long long n, int dim, long long num_embeddings,
+                          float scale, uint32_t epoch, int* status) {
+  if (!block_rendezvous(pp, rank, world, 3, epoch, status)) return;
+  const int lane = threadIdx.x & 31;
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
+  for (long long s = warp; s < n; s += nwarps) {
+    const long long i = idx[s];
+    if (i < 0 || i >= num_embeddings) continue;
+    float* row = reinterpret_cast<float*>(pp.buf[i % world]) + (i / world) * dim;
+    const T* g = dy + s * dim;
+    for (int k = lane; k < dim; k += 32) atomicAdd(row + k, scale * to_f32<T>(g[k]));
+  }
+}
+
 static PeerPtrs make_ptrs(void* const* bufs, void* const* pads, int world) {
   PeerPtrs pp;
   for (int i = 0; i < kMaxRanks; ++i) {
@@ -388,6 +450,45 @@ int lb_halo_exchange_bwd(void* const* recv_bufs, void* const* pads, int rank, in
     halo_bwd_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(pp, rank, world, up, down, gv, dv, N, Dl, h, pv, epoch, lbhost::status_word());
   else
     halo_bwd_kernel<__half><<<blocks, 512, 0, s>>>(pp, rank, world, up, down, gv, dv, N, Dl, h, pv, epoch, lbhost::status_word());
+  return (int)cudaGetLastError();
+}
+
+// tables: the fp32 shards of the group's ranks.  idx: n int64 indices; out: [n][dim] of dtype.
+// Every rank launches the same number of blocks whatever its n (the blocks rendezvous
+// pairwise), so ranks with different local batch sizes still meet.
+int lb_dist_embed_gather(void* const* tables, void* const* pads, int rank, int world,
+                         const long long* idx, void* out, long long n, int dim,
+                         long long num_embeddings, int dtype, unsigned epoch, void* stream_) {
+  using namespace lb;
+  if (world < 2 || world > kMaxRanks || dim < 1 || n < 0) return -1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  PeerPtrs pp = make_ptrs(tables, pads, world);
+  const int blocks = 32;
+  if (dtype == kF32)
+    dist_embed_gather_kernel<float><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (float*)out, n, dim, num_embeddings, epoch, lbhost::status_word());
+  else if (dtype == kBF16)
+    dist_embed_gather_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (__nv_bfloat16*)out, n, dim, num_embeddings, epoch, lbhost::status_word());
+  else
+    dist_embed_gather_kernel<__half><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (__half*)out, n, dim, num_embeddings, epoch, lbhost::status_word());
+  return (int)cudaGetLastError();
+}
+
+// table[owner(idx[s])][row(idx[s])] += scale * dy[s] for every s < n.
+int lb_dist_embed_scatter(void* const* tables, void* const* pads, int rank, int world,
+                          const long long* idx, const void* dy, long long n, int dim,
+                          long long num_embeddings, float scale, int dtype, unsigned epoch,
+                          void* stream_) {
+  using namespace lb;
+  if (world < 2 || world > kMaxRanks || dim < 1 || n < 0) return -1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  PeerPtrs pp = make_ptrs(tables, pads, world);
+  const int blocks = 32;
+  if (dtype == kF32)
+    dist_embed_scatter_kernel<float><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (const float*)dy, n, dim, num_embeddings, scale, epoch, lbhost::status_word());
+  else if (dtype == kBF16)
+    dist_embed_scatter_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (const __nv_bfloat16*)dy, n, dim, num_embeddings, scale, epoch, lbhost::status_word());
+  else
+    dist_embed_scatter_kernel<__half><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (const __half*)dy, n, dim, num_embeddings, scale, epoch, lbhost::status_word());
   return (int)cudaGetLastError();
 }
 

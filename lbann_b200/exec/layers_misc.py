@@ -777,31 +777,15 @@ class DistEmbedding(ExecLayer):
     def forward(self, xs, training):
         idx = xs[0].long()
         par = self.model.parallel
-        if par is not None and par.world_size > 1 and hasattr(par, "dist_embedding"):
-            return [par.dist_embedding(self, idx, training)]
+        if self.params.sparse_sgd:
+            # built-in sparse SGD; with several ranks the table is partitioned and rows are
+            # accessed one-sidedly (replicated on host-side ranks)
+            from ..parallel.dist_embedding import dist_embedding
+            return [dist_embedding(par, self, idx, training)]
         ok = (idx >= 0) & (idx < self.num)
         table = self.w.handle.master
         out = F.embedding(idx.clamp(0, self.num - 1), table) * ok.unsqueeze(-1)
-        if self.params.sparse_sgd and training:
-            out = _SparseSgd.apply(out, table, idx.clamp(0, self.num - 1), float(self.params.learning_rate))
         return [out.to(self.dtype or self.model.default_dtype)]
-
-
-class _SparseSgd(torch.autograd.Function):
-    """Applies the embedding update in backward (rows touched only), like the reference's
-    sparse SGD path."""
-
-    @staticmethod
-    def forward(ctx, out, table, idx, lr):
-        ctx.table, ctx.idx, ctx.lr = table, idx, lr
-        return out.clone()
-
-    @staticmethod
-    def backward(ctx, g):
-        with torch.no_grad():
-            flat = ctx.idx.reshape(-1)
-            ctx.table.index_add_(0, flat, g.reshape(flat.numel(), -1).to(ctx.table.dtype), alpha=-ctx.lr)
-        return g, None, None, None
 
 
 @register("external")

@@ -70,7 +70,9 @@ def model_state(model, gather_sharded: bool = True):
     tensors, meta = {}, {"name": model.name, "weights": {}, "amp_scale": model.amp_scale}
     for w in model.weights:
         vals = w.values.detach()
-        if gather_sharded and model.parallel is not None and getattr(w, "shard", None) is not None:
+        if getattr(w, "export_values", None) is not None:
+            vals = w.export_values()         # the layer keeps the live copy elsewhere
+        elif gather_sharded and model.parallel is not None and getattr(w, "shard", None) is not None:
             vals = model.parallel.gather_sharded_weights(w)
         tensors[f"weights/{w.name}/values"] = vals.float().cpu()
         for k, t in w.optimizer_state().items():
@@ -92,6 +94,8 @@ def load_model_state(model, tensors, meta, strict: bool = True):
                 raise KeyError(f"checkpoint has no weights '{w.name}'")
             continue
         w.set_values(tensors[key].to(model.device))
+        if getattr(w, "after_load", None) is not None:
+            w.after_load()
         info = meta.get("weights", {}).get(w.name, {})
         if info:
             w.slot.hp.update(info.get("hyperparameters", {}))

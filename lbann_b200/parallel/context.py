@@ -169,6 +169,10 @@ class ParallelContext:
     def tp_softmax(self, x, log):
         return self.tp.softmax(x, log)
 
+    def dist_embedding(self, layer, idx, training):
+        from .dist_embedding import dist_embedding
+        return dist_embedding(self, layer, idx, training)
+
     def gather_sharded_weights(self, w):
         return self.fsdp.gather(w) if self.fsdp is not None else w.values.detach()
 

@@ -269,6 +269,53 @@ def model_parallel_fc(grid_height, steps, sharded=False):
     return {"losses": losses, "weight_norms": w, "world": world}
 
 
+def dist_embedding(steps):
+    """Embedding layer with its own sparse SGD: on several ranks the table is partitioned
+    (GPU ranks: one-sided row gather / gradient scatter; CPU ranks: replicated with gathered
+    gradients).  Returns the losses and the trained table."""
+    o = opts.reset()
+    if os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cpu":
+        o.set("disable_cuda", True)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    x = lbann.Input(data_field="samples")
+    t = lbann.Input(data_field="responses")
+    e = lbann.DistEmbedding(x, num_embeddings=21, embedding_dim=8, sparse_sgd=True, learning_rate=0.01,
+                            name="table")
+    y = lbann.Reduction(lbann.Reshape(e, dims=[6, 8]), mode="sum")
+    loss = lbann.MeanSquaredError(lbann.Reshape(y, dims=[1]), t, name="mse")
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph([x, t])),
+                        objective_function=lbann.ObjectiveFunction([loss]))
+    from test_models_cpu import _reader
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=8, random_seed=11), model=model,
+        data_reader=_reader(16, [6], "samples:randint:23 responses:normal", response_dims=[1]),
+        optimizer=lbann.SGD(learn_rate=0.05))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    losses = []
+    for _ in range(steps):
+        b = dc.next_batch("training")
+        if b is None:
+            dc.start_epoch("training")
+            b = dc.next_batch("training")
+        m.train_step(b.tensors, b.global_size)
+        v = m.last_objective.detach().float().reshape(1).clone()
+        if tr.parallel is not None and tr.parallel.dp_size > 1:
+            tr.comm.allreduce(v, "trainer", "sum")
+        losses.append(float(v))
+    if torch.cuda.is_available() and not o.get_bool("disable_cuda"):
+        torch.cuda.synchronize()
+    from lbann_b200.io.checkpoint import model_state
+    tensors, _ = model_state(m)
+    table = next(v for k, v in tensors.items() if k.endswith("/values") and v.numel() == 21 * 8)
+    from lbann_b200.ops import native
+    status = native.consume_status(False) if torch.cuda.is_available() and not o.get_bool("disable_cuda") else 0
+    tr.shutdown()
+    return {"losses": losses, "table": table.reshape(-1).tolist(), "world": world, "status": int(status)}
+
+
 def data_store(preload):
     """Ranks of one trainer draw differently shuffled epochs through the data store: every
     sample is read from the reader once, later epochs are served by owner -> consumer sends."""
@@ -346,6 +393,8 @@ if __name__ == "__main__":
         res = tensor_parallel()
     elif what == "ltfb":
         res = ltfb(sys.argv[3])
+    elif what == "distembed":
+        res = dist_embedding(int(sys.argv[3]))
     elif what == "store":
         res = data_store(sys.argv[3] == "preload")
     elif what == "mpfc":

@@ -97,3 +97,15 @@ def test_sharded_weights_fully_connected_matches_single(tmp_path):
         assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], two["losses"])
     for k, v in single["weight_norms"].items():
         assert abs(v - two["weight_norms"][k]) <= 2e-4 * max(1.0, abs(v)), k
+
+
+def test_partitioned_embedding_with_sparse_sgd_matches_single_rank(tmp_path):
+    """dist_embedding with its own sparse SGD: two ranks (replicated table, gathered
+    gradients on CPU) train the same table as one rank; indices beyond the table give zeros."""
+    single = _run(1, ["distembed", "5"], str(tmp_path / "a.json"))
+    two = _run(2, ["distembed", "5"], str(tmp_path / "b.json"))
+    assert two["world"] == 2
+    for a, b in zip(single["losses"], two["losses"]):
+        assert abs(a - b) <= 1e-4 * max(1.0, abs(a)), (single["losses"], two["losses"])
+    assert max(abs(a - b) for a, b in zip(single["table"], two["table"])) < 1e-4
+    assert single["losses"][-1] < single["losses"][0]

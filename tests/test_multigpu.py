@@ -40,3 +40,16 @@ def test_fused_gemm_collectives(tmp_path):
 def test_tensor_parallel_and_sharded_linear(tmp_path):
     res = _run(2, ["tp"], str(tmp_path / "t.json"), ENV)
     assert res["world"] == 2 and res["all_ranks_ok"], res
+
+
+@needs2
+def test_partitioned_embedding_two_gpus(tmp_path):
+    """The embedding table is split over two GPUs; rows are gathered from and gradients are
+    added to their owners through peer memory.  Same losses and same trained table as the
+    single-process run."""
+    single = _run(1, ["distembed", "5"], str(tmp_path / "a.json"), {"LBANN_TEST_DEVICE": "cpu"})
+    two = _run(2, ["distembed", "5"], str(tmp_path / "b.json"), ENV)
+    assert two["world"] == 2 and two["status"] == 0
+    for a, b in zip(single["losses"], two["losses"]):
+        assert abs(a - b) <= 1e-3 * max(1.0, abs(a)), (single["losses"], two["losses"])
+    assert max(abs(a - b) for a, b in zip(single["table"], two["table"])) < 1e-3
