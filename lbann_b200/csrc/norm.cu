@@ -163,15 +163,15 @@ __global__ void bn_partial_sums_kernel(const T* __restrict__ x, float* __restric
 #pragma unroll
   for (int j = 0; j < 8; ++j) { s[j] = 0.f; ss[j] = 0.f; }
   const T* base = x + ((long long)grp * rows) * C + v * 8;
-  if (valid)
+  if (valid) {
 #pragma unroll 4
-  #pragma unroll 4
-  for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
+    for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
       float f[8];
       ld8n<T>(base + r * C, f);
 #pragma unroll
       for (int j = 0; j < 8; ++j) { s[j] += f[j]; ss[j] += f[j] * f[j]; }
     }
+  }
   reduce_over_y(s, sm);
   reduce_over_y(ss, sm);
   if (valid && threadIdx.y == 0) {

@@ -737,7 +737,6 @@ def _snake(name: str) -> str:
     return "".join(out)
 
 
-_OP_ALIASES = {"logical_not": "logical_not", "log_sigmoid": "log_sigmoid", "safe_reciprocal": "safe_reciprocal"}
 
 
 @register("operator_layer")

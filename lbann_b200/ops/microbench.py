@@ -10,7 +10,8 @@ what a profiler capture of that kernel wraps.
 
 Cases: ``gemm``, ``gemm_comm`` (fused GEMM + collective kernel in a one-GPU layout), ``conv`` (forward and, with ``--bwd``, data and filter
 gradients; the first-layer kernels are chosen automatically for <= 8 input
-channels), ``pool``, ``optimizer``.
+channels), ``pool``, ``optimizer``, ``linear_wgrad`` (weight gradient of a fully-connected
+layer; ``--m`` rows of mini-batch, ``--n`` outputs, ``--k`` inputs), ``bn`` (batch norm + ReLU, ``--batch --cin --size``).
 """
 from __future__ import annotations
 
@@ -193,6 +194,43 @@ def case_gemm_comm(a, timer):
     return out
 
 
+def case_linear_wgrad(a, timer):
+    """grad[n, k] += dy[m, n]^T x[m, k] for a short mini-batch of m rows (rank-m update)."""
+    from . import nn
+    dt = _dtype(a.dtype)
+    dy = torch.randn(a.m, a.n, device="cuda", dtype=dt)
+    x = torch.randn(a.m, a.k, device="cuda", dtype=dt)
+    grad = torch.zeros(a.n, a.k, device="cuda")
+    ms, mn = timer.run(lambda: nn._weight_grad(dy, x, grad))
+    return _report("linear_wgrad", [a.m, a.n, a.k], ms, mn, 2.0 * a.m * a.n * a.k,
+                   8.0 * a.n * a.k + 2.0 * a.m * (a.n + a.k))
+
+
+def case_bn(a, timer):
+    """Batch normalisation + ReLU over a 2-D activation [batch, cin, size, size]: forward
+    (statistics pass + apply pass) and, with ``--bwd``, backward (reduction pass + apply pass)."""
+    from . import nn
+    dt = _dtype(a.dtype)
+    N, C, S = a.batch, a.cin, a.size
+    x = torch.randn(N, S, S, C, device="cuda", dtype=dt).permute(0, 3, 1, 2).requires_grad_(True)
+    sh = nn.WeightHandle(torch.ones(C, device="cuda").requires_grad_(True), torch.zeros(C, device="cuda"))
+    bh = nn.WeightHandle(torch.zeros(C, device="cuda").requires_grad_(True), torch.zeros(C, device="cuda"))
+    rm, rv = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda")
+    elems = float(N) * S * S * C
+
+    def fwd():
+        return nn.batch_norm(x, sh, bh, rm, rv, True, 1e-5, 0.9, act=native.ACT_RELU)
+
+    ms, mn = timer.run(fwd)
+    out = [_report("bn_relu_fwd", [N, C, S], ms, mn, 0.0, 2.0 * elems * 3)]
+    if a.bwd:
+        y = fwd()
+        dy = torch.randn_like(y)
+        ms, mn = timer.run(lambda: y.backward(dy, retain_graph=True))
+        out.append(_report("bn_relu_bwd", [N, C, S], ms, mn, 0.0, 2.0 * elems * 6))
+    return out
+
+
 def case_optimizer(a, timer):
     from .optim import ParameterArena
     arena = ParameterArena(torch.device("cuda"), _dtype(a.dtype))
@@ -210,7 +248,7 @@ def case_optimizer(a, timer):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("case", choices=["gemm", "gemm_comm", "conv", "pool", "optimizer"])
+    ap.add_argument("case", choices=["gemm", "gemm_comm", "conv", "pool", "optimizer", "linear_wgrad", "bn"])
     ap.add_argument("--dtype", default="bf16", choices=["fp16", "bf16"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -232,7 +270,7 @@ def main(argv=None):
         raise SystemExit("microbench needs a GPU")
     timer = _Timer(a.iters, a.warmup, flush=not a.no_flush)
     {"gemm": case_gemm, "gemm_comm": case_gemm_comm, "conv": case_conv, "pool": case_pool,
-     "optimizer": case_optimizer}[a.case](
+     "optimizer": case_optimizer, "linear_wgrad": case_linear_wgrad, "bn": case_bn}[a.case](
         a, timer)
     native.consume_status()
 

@@ -186,6 +186,9 @@ class _Linear(torch.autograd.Function):
             dx = gemm(dy2, wh.cast(dy2.dtype)).reshape(xshape)
         if wh.grad is not None:
             _weight_grad(dy2, x2, wh.grad.view(wh.master.shape))
+            ready = getattr(wh, "on_grad_ready", None)
+            if ready is not None:
+                ready()         # data-parallel runs start reducing this gradient right away
         if bh is not None and bh.grad is not None:
             bh.grad.add_(column_sums(dy2))
         return dx, None, None, None, None, None, None

@@ -10,6 +10,7 @@ with the remaining backward computation.
 """
 from __future__ import annotations
 
+import os
 from typing import Dict, List, Optional
 
 import numpy as np
@@ -138,14 +139,63 @@ class ParallelContext:
         es = arena.grad.element_size()
         per = max(self.bucket_bytes // es, 1 << 16)
         cur = torch.cuda.current_stream(self.device)
-        # reduce on the communication stream, bucket by bucket, and join afterwards
+        if not getattr(self, "_early_hooks", False):
+            self._install_early_reduce(model)
+        # ranges already handed to the communication stream during backward
+        done = sorted(getattr(self, "_early_ranges", []))
+        self._early_ranges = []
+        todo, pos = [], 0
+        for off, cnt in done:
+            if off > pos:
+                todo.append((pos, off - pos))
+            pos = max(pos, off + cnt)
+        if pos < n:
+            todo.append((pos, n - pos))
+        # reduce the rest on the communication stream, bucket by bucket, and join afterwards
         self.comm_stream.wait_stream(cur)
         with torch.cuda.stream(self.comm_stream):
-            for off in range(0, n, per):
-                cnt = min(per, n - off)
-                self.group.allreduce_(buf, arena.grad.dtype, cnt, scale, off * es,
-                                      blocks=32 if cnt * es >= (4 << 20) else 8)
+            for start, length in todo:
+                for off in range(start, start + length, per):
+                    cnt = min(per, start + length - off)
+                    self.group.allreduce_(buf, arena.grad.dtype, cnt, scale, off * es,
+                                          blocks=32 if cnt * es >= (4 << 20) else 8)
         cur.wait_stream(self.comm_stream)
+
+    def _install_early_reduce(self, model):
+        """Large fully-connected weights that only one layer uses get a callback that starts
+        their gradient all-reduce on the communication stream as soon as the layer's backward
+        has written the gradient, so the transfer runs under the rest of backward (the
+        reference starts one non-blocking all-reduce per weight the same way,
+        include/lbann/optimizers/optimizer_impl.hpp:101-143).  The first step installs the
+        callbacks and reduces everything at the end."""
+        import functools
+        self._early_hooks = True
+        self._early_ranges = []
+        if os.environ.get("LBANN_DISABLE_EARLY_GRAD_REDUCE"):
+            return
+        for w in model.weights:
+            handle = getattr(w, "handle", None)
+            if (handle is None or len(getattr(w, "users", [])) != 1 or w.slot.count < (1 << 20)
+                    or handle.grad is None):
+                continue
+            handle.on_grad_ready = functools.partial(self._early_reduce, model, w)
+
+    def _early_reduce(self, model, w):
+        arena = model.arena
+        buf = self._buffers.get(arena.grad.data_ptr())
+        if buf is None or not self.group.native:
+            return
+        es = arena.grad.element_size()
+        off = (w.slot.offset + 3) // 4 * 4
+        end = (w.slot.offset + w.slot.count) // 4 * 4
+        if end <= off:
+            return
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self.comm_stream.wait_event(ev)
+        with torch.cuda.stream(self.comm_stream):
+            self.group.allreduce_(buf, arena.grad.dtype, end - off, 1.0 / self.tp_size, off * es, blocks=32)
+        self._early_ranges.append((off, end - off))
 
     # ------------------------------------------------------------------ sub-graph parallelism
     def subgrids_active(self) -> bool:
