@@ -389,6 +389,7 @@ class ExecModel:
         self._mb_offset = mini_batch_offset
         acts = {}
         self.acts = acts          # visible to callbacks while it fills up
+        self._mean_cache = {}
         cbs = self.callbacks
         occurrence = defaultdict(int)
         for layer in self.layers:
@@ -407,7 +408,12 @@ class ExecModel:
                 if self.device.type == "cuda":
                     torch.cuda.synchronize()
                 t0 = time.perf_counter()
+            pt = self._phase_timer
+            if pt is not None:
+                th = time.perf_counter()
             ys = layer.forward(xs, training)
+            if pt is not None:          # host time of the layer's forward (no synchronisation)
+                pt.layer_host[layer.name] += time.perf_counter() - th
             if self.layer_timing or self.sync_layers:
                 if self.device.type == "cuda":
                     torch.cuda.synchronize()
@@ -423,9 +429,14 @@ class ExecModel:
 
     def _layer_mean(self, layer_name: str) -> torch.Tensor:
         """Sum over the local mini-batch divided by the global mini-batch size."""
+        hit = self._mean_cache.get(layer_name)      # objective term and metric often coincide
+        if hit is not None:
+            return hit
         layer = self.layers_by_name[layer_name]
         y = self.acts[layer_name][0] if self.acts[layer_name] else self.acts[layer.parent_names[0]][0]
-        return y.float().sum() / float(self._global_mb)
+        val = y.float().sum() / float(self._global_mb)
+        self._mean_cache[layer_name] = val
+        return val
 
     def local_objective(self) -> torch.Tensor:
         total = None
@@ -449,11 +460,11 @@ class ExecModel:
         st = self.stats[mode]
         n = self._global_mb
         with torch.no_grad():
-            st.obj_sum += local_obj.detach().double() * n
+            st.obj_sum.add_(local_obj.detach(), alpha=n)
             st.samples += n
             for i, m in enumerate(self.metrics):
                 if getattr(m, "layer_name", None):
-                    st.metric_sums[i] += self._layer_mean(m.layer_name).detach().double() * n
+                    st.metric_sums[i].add_(self._layer_mean(m.layer_name).detach(), alpha=n)
 
     def clear_gradients(self):
         self.arena.zero_grad()
@@ -557,6 +568,7 @@ class ExecModel:
 
         def __init__(self, device):
             self.device, self.events, self.host, self.steps = device, [], [], 0
+            self.layer_host = defaultdict(float)
             self.dev_ms, self.host_ms = defaultdict(float), defaultdict(float)
 
         def mark(self, name):
@@ -585,7 +597,10 @@ class ExecModel:
         def report(self):
             self.flush()
             n = max(self.steps, 1)
-            return {k: (round(self.dev_ms[k] / n, 3), round(self.host_ms[k] / n, 3)) for k in self.host_ms}
+            out = {k: (round(self.dev_ms[k] / n, 3), round(self.host_ms[k] / n, 3)) for k in self.host_ms}
+            top = sorted(self.layer_host.items(), key=lambda kv: -kv[1])[:12]
+            out["forward host ms by layer"] = {k: round(v * 1e3 / n, 3) for k, v in top}
+            return out
 
     @torch.no_grad()
     def evaluate_step(self, inputs, mode="validation", global_mini_batch_size=None,

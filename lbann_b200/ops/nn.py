@@ -43,6 +43,9 @@ def _lib():
                                           c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p]
         lib.lb_bn_partial_sums.restype = c_int
         lib.lb_bn_partial_sums.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_void_p]
+        lib.lb_pack_filter.restype = c_int
+        lib.lb_pack_filter.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                       c_int, c_void_p]
         lib.lb_outer_accum.restype = c_int
         lib.lb_outer_accum.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_ll, c_float,
                                        c_float, c_int, c_void_p]
@@ -194,6 +197,27 @@ class _Linear(torch.autograd.Function):
         return dx, None, None, None, None, None, None
 
 
+def _pack_both(wh: WeightHandle, dtype: torch.dtype, Kout, Cin, Kp, Cp, ksize) -> None:
+    """Fill the handle's cache with the forward and the data-gradient filter layouts in one
+    launch (they are valid until the optimizer changes the weights)."""
+    if ("fwd", dtype) in wh._cache or not wh.master.is_cuda or wh.master.dtype != torch.float32:
+        return
+    m = wh.master.detach()
+    if not m.is_contiguous():
+        return
+    taps = 1
+    for k in ksize:
+        taps *= int(k)
+    fwd = torch.empty((taps, Kp, Cp), dtype=dtype, device=m.device)
+    dgrad = torch.empty((taps, Cp, Kp), dtype=dtype, device=m.device)
+    rc = _lib().lb_pack_filter(m.data_ptr(), fwd.data_ptr(), dgrad.data_ptr(), Kout, Cin, taps, Kp, Cp,
+                               native.dtype_code(dtype), native.stream_ptr())
+    native.check(rc, "lb_pack_filter")
+    native.count_launch()
+    wh._cache[("fwd", dtype)] = fwd
+    wh._cache[("dgrad", dtype)] = dgrad
+
+
 def _weight_grad(dy2: torch.Tensor, x2: torch.Tensor, grad: torch.Tensor) -> None:
     """grad[out, in] += dy2^T x2.  Mini-batches of at most 16 rows make this a rank-K update
     bound by the fp32 read-modify-write of ``grad``; a plain kernel does it at memory speed,
@@ -279,6 +303,7 @@ class _Conv(torch.autograd.Function):
                 w = F.pad(w, (0, 0, 0, Cp - Cin, 0, Kp - Kout))
             return pack_filter(w.reshape(Kp, Cp, *ksize), x.dtype)
 
+        _pack_both(wh, x.dtype, Kout, Cin, Kp, Cp, ksize)
         wt = wh.packed("fwd", x.dtype, pack_fwd)
         bias = None
         if bh is not None:

@@ -8,9 +8,11 @@ src/layers/learning/base_convolution.cpp:1326-1445) is done here with three diff
 primitives over symmetric memory:
 
   HaloExchange   local slab [N, C, Dl, H, W] -> slab with `h` halo planes on both sides.
-                 Boundary planes are STORED straight into the neighbours' halo planes by a
-                 peer-store kernel; a device-side group barrier orders them before the
-                 consumer.  Backward sends the halo gradients back and adds them.
+                 One kernel copies the slab into the extended buffer, STORES the boundary
+                 planes straight into the neighbours' halo planes and runs the two group
+                 rendezvous that order the stores against the neighbours' consumers.
+                 Backward is one kernel too: halo gradients go back to their owners and are
+                 added to the boundary planes.
   to_sample_parallel / to_spatial   redistribution between "every rank holds a depth slab
                  of all samples" and "every rank holds all of some samples" (an all-to-all
                  by peer stores), used where distconv layers meet ordinary layers.
@@ -23,6 +25,8 @@ unspecified groups are 1, channel / filter parallelism of convolutions is reject
 left-over ranks multiply the sample groups.
 """
 from __future__ import annotations
+
+import os
 
 from typing import Dict, Optional, Tuple
 
@@ -66,11 +70,13 @@ class DistconvContext:
         self.sample_group_index = 0
         self.depth_rank = 0
         self.dist: Dict[Tuple[str, int], str] = {}
+        self._enabled: Dict[str, bool] = {}
         self._bufs: Dict[tuple, SymmetricBuffer] = {}
         self.halo_bytes = 0
 
     # ------------------------------------------------------------------ set-up
     def prepare_model(self, model):
+        self._enabled.clear()
         depth = 1
         for l in model.layers:
             if l.parallel_strategy is None:
@@ -116,9 +122,15 @@ class DistconvContext:
             self.sliced_fields = set()
 
     def enabled(self, layer) -> bool:
+        hit = self._enabled.get(layer.name)       # static per layer once its dims are known
+        if hit is not None:
+            return hit
         st = self.strategies.get(layer.name)
-        return bool(st is not None and st.is_spatial() and layer.supports_distconv
-                    and self.depth_groups > 1 and self._feasible(layer))
+        val = bool(st is not None and st.is_spatial() and layer.supports_distconv
+                   and self.depth_groups > 1 and self._feasible(layer))
+        if getattr(layer, "in_dims", None):
+            self._enabled[layer.name] = val
+        return val
 
     def _feasible(self, layer) -> bool:
         """Can this layer still be computed on depth slabs?  Deep in a network the depth
@@ -274,7 +286,7 @@ class HaloExchange(torch.autograd.Function):
         x_cl = x.permute(0, 2, 3, 4, 1)
         g = dc.group
         ctx.meta = (dc, h, tag, (N, C, Dl, H, W))
-        if g.native and P == g.world and r == g.rank:
+        if g.native and P == g.world and r == g.rank and not os.environ.get("LBANN_DISABLE_FUSED_HALO"):
             # interior copy, boundary fill, peer stores and both rendezvous in one launch
             xs = x_cl if x_cl.is_contiguous() else x_cl.contiguous()
             if g.halo_forward(xs, buf, N, Dl, h, plane, fill):
@@ -330,7 +342,7 @@ class HaloExchange(torch.autograd.Function):
         buf = dc.buffer(("halo_bwd", tag), 2 * N * h * plane)
         pitch = (Dl + 2 * h) * plane
         grp = dc.group
-        if P == grp.world and r == grp.rank:
+        if P == grp.world and r == grp.rank and not os.environ.get("LBANN_DISABLE_FUSED_HALO"):
             dx = torch.empty((N, Dl, H, W, C), dtype=g_cl.dtype, device=g_cl.device)
             if grp.halo_backward(g_cl, buf, dx, N, Dl, h, plane):
                 return dx.permute(0, 4, 1, 2, 3), None, None, None, None
