@@ -4,7 +4,7 @@
 // addresses of all the others (CUDA IPC / VMM mappings set up by parallel/symm.py), plus
 // a small signal pad per rank.  The kernels below move data with plain peer loads and
 // stores over NVLink - no TMA is ever issued on another GPU's memory - and synchronise
-// with epoch flags in the signal pads.  Every wait is bounded: when the budget runs out
+// with epoch flags in the signal pads (epochs counted on the device).  Every wait is bounded: when the budget runs out
 // the kernel records kTimeoutPeerFlag in the library status word and returns.
 //
 // They take the place of the reference's Aluminum / NCCL calls (src/comm.cpp:440-625),
@@ -35,17 +35,29 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 
 // Block-level rendezvous with the same block index on every rank of the group.
 // Threads 0..world-1 each handle one peer.  Returns false after the wait budget ran out.
+//
+// The epoch that the flags are compared with is not a launch argument: every flag row
+// (phase, block) has a use counter `ctr` in this rank's own memory, read at the start of the
+// rendezvous and advanced at its end.  All ranks run the same sequence of kernels, so their
+// counters agree, and a launch carries no per-step value - which is what lets a training
+// step be captured once as a CUDA graph and replayed.
 __device__ __forceinline__ bool block_rendezvous(const PeerPtrs& pp, int rank, int world,
-                                                 int phase, uint32_t epoch, int* status) {
+                                                 int phase, uint32_t* ctr, int* status) {
   __shared__ int ok_flag;
-  if (threadIdx.x == 0) ok_flag = 1;
+  __shared__ uint32_t epoch_sh;
+  const int row = phase * kCommBlocks + blockIdx.x;
+  if (threadIdx.x == 0) {
+    ok_flag = 1;
+    epoch_sh = ctr[row] + 1;
+  }
   __syncthreads();          // all of this block's earlier writes are issued
+  const uint32_t epoch = epoch_sh;
   if ((int)threadIdx.x < world) {
     const int peer = threadIdx.x;
     __threadfence_system();
-    uint32_t* remote = pp.pad[peer] + ((size_t)phase * kCommBlocks + blockIdx.x) * kMaxRanks + rank;
+    uint32_t* remote = pp.pad[peer] + (size_t)row * kMaxRanks + rank;
     st_release_sys(remote, epoch);
-    const uint32_t* mine = pp.pad[rank] + ((size_t)phase * kCommBlocks + blockIdx.x) * kMaxRanks + peer;
+    const uint32_t* mine = pp.pad[rank] + (size_t)row * kMaxRanks + peer;
     const uint64_t t0 = globaltimer_ns();
     uint32_t spins = 0;
     while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
@@ -57,6 +69,7 @@ __device__ __forceinline__ bool block_rendezvous(const PeerPtrs& pp, int rank, i
     }
   }
   __syncthreads();
+  if (threadIdx.x == 0) ctr[row] = epoch;
   return ok_flag != 0;
 }
 
@@ -68,9 +81,9 @@ __device__ __forceinline__ bool block_rendezvous(const PeerPtrs& pp, int rank, i
 template <typename T>
 __global__ void __launch_bounds__(512)
 allreduce_two_shot_kernel(PeerPtrs pp, int rank, int world, long long n, float scale,
-                          uint32_t epoch, int* status) {
+                          uint32_t* ctr, int* status) {
   constexpr int V = 16 / sizeof(T);
-  if (!block_rendezvous(pp, rank, world, 0, epoch, status)) return;
+  if (!block_rendezvous(pp, rank, world, 0, ctr, status)) return;
   const long long shard = ((n + world - 1) / world + V - 1) / V * V;
   const long long s0 = (long long)rank * shard;
   const long long s1 = s0 + shard < n ? s0 + shard : n;
@@ -105,7 +118,7 @@ allreduce_two_shot_kernel(PeerPtrs pp, int rank, int world, long long n, float s
       }
     }
   }
-  block_rendezvous(pp, rank, world, 1, epoch, status);
+  block_rendezvous(pp, rank, world, 1, ctr, status);
 }
 
 // ---------------------------------------------------------------------------------
@@ -116,13 +129,13 @@ allreduce_two_shot_kernel(PeerPtrs pp, int rank, int world, long long n, float s
 __global__ void __launch_bounds__(256)
 allreduce_one_shot_kernel(PeerPtrs pp, int rank, int world, const float* __restrict__ in,
                           float* __restrict__ out, int n, int op, long long slot_stride,
-                          uint32_t epoch, int* status) {
+                          uint32_t* ctr, int* status) {
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     const float v = in[i];
     for (int q = 0; q < world; ++q)
       reinterpret_cast<float*>(pp.buf[q])[(long long)rank * slot_stride + i] = v;
   }
-  if (!block_rendezvous(pp, rank, world, 2, epoch, status)) return;
+  if (!block_rendezvous(pp, rank, world, 2, ctr, status)) return;
   const float* mine = reinterpret_cast<const float*>(pp.buf[rank]);
   for (int i = threadIdx.x; i < n; i += blockDim.x) {
     float a = op == 0 ? 0.f : -INFINITY;
@@ -133,7 +146,7 @@ allreduce_one_shot_kernel(PeerPtrs pp, int rank, int world, const float* __restr
     out[i] = a;
   }
   // peers may overwrite the staging slots on their next call only after everybody read
-  block_rendezvous(pp, rank, world, 3, epoch, status);
+  block_rendezvous(pp, rank, world, 3, ctr, status);
 }
 
 // ---------------------------------------------------------------------------------
@@ -156,9 +169,9 @@ put_rows_kernel(const uint8_t* __restrict__ src, long long src_pitch, uint8_t* _
 
 // Group barrier as its own (single block) kernel: orders "my puts are visible" with the
 // peers' consumers.  phase selects an independent flag row.
-__global__ void group_barrier_kernel(PeerPtrs pp, int rank, int world, int phase, uint32_t epoch,
+__global__ void group_barrier_kernel(PeerPtrs pp, int rank, int world, int phase, uint32_t* ctr,
                                      int* status) {
-  block_rendezvous(pp, rank, world, phase, epoch, status);
+  block_rendezvous(pp, rank, world, phase, ctr, status);
 }
 
 // ---------------------------------------------------------------------------------
@@ -175,7 +188,7 @@ __global__ void group_barrier_kernel(PeerPtrs pp, int rank, int world, int phase
 __global__ void __launch_bounds__(512)
 halo_fwd_kernel(PeerPtrs pp, int rank, int world, int up, int down, const uint4* __restrict__ x,
                 long long N, long long Dl, long long h, long long pv, uint32_t fill_bits,
-                uint32_t epoch, int* status) {
+                uint32_t* ctr, int* status) {
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
   const long long ext_pitch = (Dl + 2 * h) * pv;
@@ -193,7 +206,7 @@ halo_fwd_kernel(PeerPtrs pp, int rank, int world, int up, int down, const uint4*
       if (down < 0) mine[n * ext_pitch + edge + inner + rem] = fv;
     }
   }
-  if (!block_rendezvous(pp, rank, world, 2, epoch, status)) return;
+  if (!block_rendezvous(pp, rank, world, 2, ctr, status)) return;
   uint4* above = up >= 0 ? reinterpret_cast<uint4*>(pp.buf[up]) : nullptr;
   uint4* below = down >= 0 ? reinterpret_cast<uint4*>(pp.buf[down]) : nullptr;
   for (long long i = tid; i < N * edge; i += nthreads) {
@@ -201,7 +214,7 @@ halo_fwd_kernel(PeerPtrs pp, int rank, int world, int up, int down, const uint4*
     if (above) above[n * ext_pitch + edge + inner + rem] = x[n * inner + rem];
     if (below) below[n * ext_pitch + rem] = x[n * inner + inner - edge + rem];
   }
-  block_rendezvous(pp, rank, world, 3, epoch, status);
+  block_rendezvous(pp, rank, world, 3, ctr, status);
 }
 
 // Backward: g [N][Dl + 2h][plane] is the gradient of the extended tensor.  The gradients of
@@ -214,7 +227,7 @@ template <typename T>
 __global__ void __launch_bounds__(512)
 halo_bwd_kernel(PeerPtrs pp, int rank, int world, int up, int down, const uint4* __restrict__ g,
                 uint4* __restrict__ dx, long long N, long long Dl, long long h, long long pv,
-                uint32_t epoch, int* status) {
+                uint32_t* ctr, int* status) {
   constexpr int V = 16 / sizeof(T);
   const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   const long long nthreads = (long long)gridDim.x * blockDim.x;
@@ -236,7 +249,7 @@ halo_bwd_kernel(PeerPtrs pp, int rank, int world, int up, int down, const uint4*
     const long long n = i / mid, rem = i - n * mid;
     dx[n * inner + lo * pv + rem] = g[n * ext_pitch + edge + lo * pv + rem];
   }
-  if (!block_rendezvous(pp, rank, world, 3, epoch, status)) return;
+  if (!block_rendezvous(pp, rank, world, 3, ctr, status)) return;
   const uint4* recv = reinterpret_cast<const uint4*>(pp.buf[rank]);
   const long long nb = lo + (Dl - hi);          // boundary planes
   for (long long i = tid; i < N * nb * pv; i += nthreads) {
@@ -259,7 +272,7 @@ halo_bwd_kernel(PeerPtrs pp, int rank, int world, int up, int down, const uint4*
     }
     dx[n * inner + d * pv + v] = acc;
   }
-  block_rendezvous(pp, rank, world, 2, epoch, status);
+  block_rendezvous(pp, rank, world, 2, ctr, status);
 }
 
 // ---------------------------------------------------------------------------------
@@ -279,8 +292,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 dist_embed_gather_kernel(PeerPtrs pp, int rank, int world, const long long* __restrict__ idx,
                          T* __restrict__ out, long long n, int dim, long long num_embeddings,
-                         uint32_t epoch, int* status) {
-  if (!block_rendezvous(pp, rank, world, 2, epoch, status)) return;
+                         uint32_t* ctr, int* status) {
+  if (!block_rendezvous(pp, rank, world, 2, ctr, status)) return;
   const int lane = threadIdx.x & 31;
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -310,8 +323,8 @@ template <typename T>
 __global__ void __launch_bounds__(256)
 dist_embed_scatter_kernel(PeerPtrs pp, int rank, int world, const long long* __restrict__ idx,
                           const T* __restrict__ dy, long long n, int dim, long long num_embeddings,
-                          float scale, uint32_t epoch, int* status) {
-  if (!block_rendezvous(pp, rank, world, 3, epoch, status)) return;
+                          float scale, uint32_t* ctr, int* status) {
+  if (!block_rendezvous(pp, rank, world, 3, ctr, status)) return;
   const int lane = threadIdx.x & 31;
   const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
   const long long nwarps = ((long long)gridDim.x * blockDim.x) >> 5;
@@ -343,7 +356,7 @@ int lb_comm_max_ranks() { return lb::kMaxRanks; }
 // bufs / pads: host arrays of `world` device pointers (index = rank in group).
 // dtype: 0 fp16, 1 bf16, 2 fp32.  In place on the symmetric buffers; n elements.
 int lb_allreduce_two_shot(void* const* bufs, void* const* pads, int rank, int world, long long n,
-                          float scale, unsigned epoch, int dtype, int blocks, void* stream_) {
+                          float scale, unsigned* ctr, int dtype, int blocks, void* stream_) {
   using namespace lb;
   if (world < 1 || world > kMaxRanks || n <= 0) return -1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
@@ -351,22 +364,22 @@ int lb_allreduce_two_shot(void* const* bufs, void* const* pads, int rank, int wo
   if (blocks < 1) blocks = 1;
   if (blocks > kCommBlocks) blocks = kCommBlocks;
   if (dtype == kF32)
-    allreduce_two_shot_kernel<float><<<blocks, 512, 0, s>>>(pp, rank, world, n, scale, epoch, lbhost::status_word());
+    allreduce_two_shot_kernel<float><<<blocks, 512, 0, s>>>(pp, rank, world, n, scale, ctr, lbhost::status_word());
   else if (dtype == kBF16)
-    allreduce_two_shot_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(pp, rank, world, n, scale, epoch, lbhost::status_word());
+    allreduce_two_shot_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(pp, rank, world, n, scale, ctr, lbhost::status_word());
   else
-    allreduce_two_shot_kernel<__half><<<blocks, 512, 0, s>>>(pp, rank, world, n, scale, epoch, lbhost::status_word());
+    allreduce_two_shot_kernel<__half><<<blocks, 512, 0, s>>>(pp, rank, world, n, scale, ctr, lbhost::status_word());
   return (int)cudaGetLastError();
 }
 
 int lb_allreduce_one_shot(void* const* bufs, void* const* pads, int rank, int world,
                           const float* in, float* out, int n, int op, long long slot_stride,
-                          unsigned epoch, void* stream_) {
+                          unsigned* ctr, void* stream_) {
   using namespace lb;
   if (world < 1 || world > kMaxRanks || n <= 0) return -1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   PeerPtrs pp = make_ptrs(bufs, pads, world);
-  allreduce_one_shot_kernel<<<1, 256, 0, s>>>(pp, rank, world, in, out, n, op, slot_stride, epoch,
+  allreduce_one_shot_kernel<<<1, 256, 0, s>>>(pp, rank, world, in, out, n, op, slot_stride, ctr,
                                               lbhost::status_word());
   return (int)cudaGetLastError();
 }
@@ -399,7 +412,7 @@ static int halo_blocks(long long vectors) {
 // Returns -2 when the shape is not covered (plane not a multiple of 16 bytes, Dl < h).
 int lb_halo_exchange_fwd(void* const* ext_bufs, void* const* pads, int rank, int world, int up,
                          int down, const void* x, long long N, long long Dl, long long h,
-                         long long plane_bytes, float fill, int dtype, unsigned epoch,
+                         long long plane_bytes, float fill, int dtype, unsigned* ctr,
                          void* stream_) {
   using namespace lb;
   if (world < 2 || world > kMaxRanks || up >= world || down >= world) return -1;
@@ -423,7 +436,7 @@ int lb_halo_exchange_fwd(void* const* ext_bufs, void* const* pads, int rank, int
   PeerPtrs pp = make_ptrs(ext_bufs, pads, world);
   const long long pv = plane_bytes / 16;
   halo_fwd_kernel<<<halo_blocks(N * Dl * pv), 512, 0, s>>>(
-      pp, rank, world, up, down, reinterpret_cast<const uint4*>(x), N, Dl, h, pv, bits, epoch,
+      pp, rank, world, up, down, reinterpret_cast<const uint4*>(x), N, Dl, h, pv, bits, ctr,
       lbhost::status_word());
   return (int)cudaGetLastError();
 }
@@ -432,7 +445,7 @@ int lb_halo_exchange_fwd(void* const* ext_bufs, void* const* pads, int rank, int
 // the extended tensor; dx: [N][Dl][plane_bytes].
 int lb_halo_exchange_bwd(void* const* recv_bufs, void* const* pads, int rank, int world, int up,
                          int down, const void* g, void* dx, long long N, long long Dl,
-                         long long h, long long plane_bytes, int dtype, unsigned epoch,
+                         long long h, long long plane_bytes, int dtype, unsigned* ctr,
                          void* stream_) {
   using namespace lb;
   if (world < 2 || world > kMaxRanks || up >= world || down >= world) return -1;
@@ -445,11 +458,11 @@ int lb_halo_exchange_bwd(void* const* recv_bufs, void* const* pads, int rank, in
   const uint4* gv = reinterpret_cast<const uint4*>(g);
   uint4* dv = reinterpret_cast<uint4*>(dx);
   if (dtype == kF32)
-    halo_bwd_kernel<float><<<blocks, 512, 0, s>>>(pp, rank, world, up, down, gv, dv, N, Dl, h, pv, epoch, lbhost::status_word());
+    halo_bwd_kernel<float><<<blocks, 512, 0, s>>>(pp, rank, world, up, down, gv, dv, N, Dl, h, pv, ctr, lbhost::status_word());
   else if (dtype == kBF16)
-    halo_bwd_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(pp, rank, world, up, down, gv, dv, N, Dl, h, pv, epoch, lbhost::status_word());
+    halo_bwd_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(pp, rank, world, up, down, gv, dv, N, Dl, h, pv, ctr, lbhost::status_word());
   else
-    halo_bwd_kernel<__half><<<blocks, 512, 0, s>>>(pp, rank, world, up, down, gv, dv, N, Dl, h, pv, epoch, lbhost::status_word());
+    halo_bwd_kernel<__half><<<blocks, 512, 0, s>>>(pp, rank, world, up, down, gv, dv, N, Dl, h, pv, ctr, lbhost::status_word());
   return (int)cudaGetLastError();
 }
 
@@ -458,25 +471,25 @@ int lb_halo_exchange_bwd(void* const* recv_bufs, void* const* pads, int rank, in
 // pairwise), so ranks with different local batch sizes still meet.
 int lb_dist_embed_gather(void* const* tables, void* const* pads, int rank, int world,
                          const long long* idx, void* out, long long n, int dim,
-                         long long num_embeddings, int dtype, unsigned epoch, void* stream_) {
+                         long long num_embeddings, int dtype, unsigned* ctr, void* stream_) {
   using namespace lb;
   if (world < 2 || world > kMaxRanks || dim < 1 || n < 0) return -1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   PeerPtrs pp = make_ptrs(tables, pads, world);
   const int blocks = 32;
   if (dtype == kF32)
-    dist_embed_gather_kernel<float><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (float*)out, n, dim, num_embeddings, epoch, lbhost::status_word());
+    dist_embed_gather_kernel<float><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (float*)out, n, dim, num_embeddings, ctr, lbhost::status_word());
   else if (dtype == kBF16)
-    dist_embed_gather_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (__nv_bfloat16*)out, n, dim, num_embeddings, epoch, lbhost::status_word());
+    dist_embed_gather_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (__nv_bfloat16*)out, n, dim, num_embeddings, ctr, lbhost::status_word());
   else
-    dist_embed_gather_kernel<__half><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (__half*)out, n, dim, num_embeddings, epoch, lbhost::status_word());
+    dist_embed_gather_kernel<__half><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (__half*)out, n, dim, num_embeddings, ctr, lbhost::status_word());
   return (int)cudaGetLastError();
 }
 
 // table[owner(idx[s])][row(idx[s])] += scale * dy[s] for every s < n.
 int lb_dist_embed_scatter(void* const* tables, void* const* pads, int rank, int world,
                           const long long* idx, const void* dy, long long n, int dim,
-                          long long num_embeddings, float scale, int dtype, unsigned epoch,
+                          long long num_embeddings, float scale, int dtype, unsigned* ctr,
                           void* stream_) {
   using namespace lb;
   if (world < 2 || world > kMaxRanks || dim < 1 || n < 0) return -1;
@@ -484,21 +497,21 @@ int lb_dist_embed_scatter(void* const* tables, void* const* pads, int rank, int 
   PeerPtrs pp = make_ptrs(tables, pads, world);
   const int blocks = 32;
   if (dtype == kF32)
-    dist_embed_scatter_kernel<float><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (const float*)dy, n, dim, num_embeddings, scale, epoch, lbhost::status_word());
+    dist_embed_scatter_kernel<float><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (const float*)dy, n, dim, num_embeddings, scale, ctr, lbhost::status_word());
   else if (dtype == kBF16)
-    dist_embed_scatter_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (const __nv_bfloat16*)dy, n, dim, num_embeddings, scale, epoch, lbhost::status_word());
+    dist_embed_scatter_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (const __nv_bfloat16*)dy, n, dim, num_embeddings, scale, ctr, lbhost::status_word());
   else
-    dist_embed_scatter_kernel<__half><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (const __half*)dy, n, dim, num_embeddings, scale, epoch, lbhost::status_word());
+    dist_embed_scatter_kernel<__half><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (const __half*)dy, n, dim, num_embeddings, scale, ctr, lbhost::status_word());
   return (int)cudaGetLastError();
 }
 
 int lb_group_barrier(void* const* bufs, void* const* pads, int rank, int world, int phase,
-                     unsigned epoch, void* stream_) {
+                     unsigned* ctr, void* stream_) {
   using namespace lb;
   if (world < 1 || world > kMaxRanks || phase < 0 || phase > 3) return -1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   PeerPtrs pp = make_ptrs(bufs, pads, world);
-  group_barrier_kernel<<<1, 32, 0, s>>>(pp, rank, world, phase, epoch, lbhost::status_word());
+  group_barrier_kernel<<<1, 32, 0, s>>>(pp, rank, world, phase, ctr, lbhost::status_word());
   return (int)cudaGetLastError();
 }
 

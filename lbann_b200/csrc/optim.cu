@@ -115,7 +115,9 @@ __global__ void fused_optimizer_kernel(float* __restrict__ w, const G* __restric
 // flag |= any non-finite; optionally g *= inv_scale in place.
 template <typename G>
 __global__ void unscale_check_kernel(G* __restrict__ grad, long long n, float inv_scale,
-                                     int write_back, int* __restrict__ flag) {
+                                     const float* __restrict__ inv_scale_dev, int write_back,
+                                     int* __restrict__ flag) {
+  if (inv_scale_dev) inv_scale = *inv_scale_dev;     // loss scale kept on the device
   bool bad = false;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x) {
@@ -124,6 +126,37 @@ __global__ void unscale_check_kernel(G* __restrict__ grad, long long n, float in
     if (write_back) grad[i] = from_f32<G>(g);
   }
   if (__any_sync(0xffffffffu, bad) && (threadIdx.x & 31) == 0) atomicOr(flag, 1);
+}
+
+// Loss-scale schedule of automatic mixed precision, on the device so that a training step
+// needs no host decision (src/models/model.cpp:1796-1824 is the schedule): after an overflow
+// the scale shrinks and the step is skipped, after `interval` clean steps it grows.
+// state = {scale, 1 / scale, clean steps, consecutive skipped steps}; reduced: the overflow
+// flag after the max-reduction over the ranks (nullptr on one rank); flag: this rank's flag
+// on entry, the decision the optimizer reads on exit.
+__global__ void amp_update_kernel(float* __restrict__ state, const float* __restrict__ reduced,
+                                  int* __restrict__ flag, float growth, float backoff,
+                                  float interval) {
+  if (threadIdx.x != 0 || blockIdx.x != 0) return;
+  const bool bad = reduced ? (*reduced > 0.f) : (*flag != 0);
+  *flag = bad ? 1 : 0;
+  float scale = state[0], good = state[2], skipped = state[3];
+  if (bad) {
+    scale *= backoff;
+    good = 0.f;
+    skipped += 1.f;
+  } else {
+    skipped = 0.f;
+    good += 1.f;
+    if (good >= interval) {
+      scale *= growth;
+      good = 0.f;
+    }
+  }
+  state[0] = scale;
+  state[1] = 1.f / scale;
+  state[2] = good;
+  state[3] = skipped;
 }
 
 // out[0] += sum x^2
@@ -194,15 +227,23 @@ int lb_fused_optimizer(float* w, const void* grad, float* s0, float* s1, void* w
   return (int)cudaGetLastError();
 }
 
-int lb_unscale_check(void* grad, long long n, float inv_scale, int write_back, int* flag,
-                     int dtype, void* stream_) {
+int lb_amp_update(float* state, const float* reduced, int* flag, float growth, float backoff,
+                  float interval, void* stream_) {
+  lb::amp_update_kernel<<<1, 32, 0, reinterpret_cast<cudaStream_t>(stream_)>>>(
+      state, reduced, flag, growth, backoff, interval);
+  return (int)cudaGetLastError();
+}
+
+// inv_scale_dev: when not null the factor is read from device memory instead of `inv_scale`.
+int lb_unscale_check(void* grad, long long n, float inv_scale, const float* inv_scale_dev,
+                     int write_back, int* flag, int dtype, void* stream_) {
   using namespace lb;
   if (n <= 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   const int grid = flat_grid(n, 2048);
-  if (dtype == kF32) unscale_check_kernel<float><<<grid, 256, 0, s>>>((float*)grad, n, inv_scale, write_back, flag);
-  else if (dtype == kBF16) unscale_check_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)grad, n, inv_scale, write_back, flag);
-  else unscale_check_kernel<__half><<<grid, 256, 0, s>>>((__half*)grad, n, inv_scale, write_back, flag);
+  if (dtype == kF32) unscale_check_kernel<float><<<grid, 256, 0, s>>>((float*)grad, n, inv_scale, inv_scale_dev, write_back, flag);
+  else if (dtype == kBF16) unscale_check_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)grad, n, inv_scale, inv_scale_dev, write_back, flag);
+  else unscale_check_kernel<__half><<<grid, 256, 0, s>>>((__half*)grad, n, inv_scale, inv_scale_dev, write_back, flag);
   return (int)cudaGetLastError();
 }
 

@@ -90,7 +90,8 @@ class ExecModel:
         self.num_epochs = int(model_pb.num_epochs)
         self.amp_enabled = bool(model_pb.amp.enabled) if model_pb.HasField("amp") else False
         amp = model_pb.amp
-        self.amp_scale = float(amp.init_scale) or 65536.0
+        self._amp_scale_host = float(amp.init_scale) or 65536.0
+        self._amp_state = None      # CUDA: [scale, 1 / scale, clean steps, skipped steps] on the device
         self.amp_growth = float(amp.growth_factor) or 2.0
         self.amp_backoff = float(amp.backoff_factor) or 0.5
         self.amp_interval = int(amp.growth_interval) or 2000
@@ -470,15 +471,39 @@ class ExecModel:
         self.arena.zero_grad()
 
     def backward_prop(self, local_obj: torch.Tensor):
-        scale = self.amp_scale if self.amp_enabled else 1.0
         for cb in self.callbacks:
             cb.on_backward_prop_begin(self)
         if local_obj.requires_grad:
-            (local_obj * scale if scale != 1.0 else local_obj).backward()
+            if not self.amp_enabled:
+                local_obj.backward()
+            elif self.device.type == "cuda":
+                (local_obj * self._amp_device_state()[0]).backward()     # no host read of the scale
+            else:
+                (local_obj * self._amp_scale_host).backward()
         if self.parallel is not None:
             self.parallel.sync_gradients(self)
         for cb in self.callbacks:
             cb.on_backward_prop_end(self)
+
+    @property
+    def amp_scale(self) -> float:
+        """Current loss scale (reads the device copy when the schedule runs there)."""
+        if self._amp_state is not None:
+            return float(self._amp_state[0].item())
+        return self._amp_scale_host
+
+    @amp_scale.setter
+    def amp_scale(self, value: float):
+        self._amp_scale_host = float(value)
+        if self._amp_state is not None:
+            self._amp_state[0] = float(value)
+            self._amp_state[1] = 1.0 / float(value)
+
+    def _amp_device_state(self) -> torch.Tensor:
+        if self._amp_state is None:
+            s = self._amp_scale_host
+            self._amp_state = torch.tensor([s, 1.0 / s, 0.0, 0.0], dtype=torch.float32, device=self.device)
+        return self._amp_state
 
     def update_weights(self) -> bool:
         """Returns False when the step was skipped (AMP overflow)."""
@@ -488,47 +513,40 @@ class ExecModel:
         skip_flag = None
         skipped = False
         if self.amp_enabled:
-            # The overflow flag stays on the device: the fused optimizer reads it and skips
-            # the update by itself, so the step needs no host synchronisation.  The host looks
-            # at the flag of the PREVIOUS step (copied asynchronously) to adapt the loss scale,
-            # i.e. the reference's schedule (src/models/model.cpp:1796-1824) with one step of
-            # latency.  CPU runs read the flag directly.
+            # the reference's schedule: src/models/model.cpp:1796-1824
             flag = torch.zeros(1, dtype=torch.int32, device=self.device)
-            self.arena.unscale_and_check(1.0 / self.amp_scale, flag, write_back=True)
-            if self.parallel is not None:
-                self.parallel.allreduce_max_inplace(flag)
-            skip_flag = flag
             if self.device.type == "cuda":
-                prev = getattr(self, "_amp_prev", None)
-                overflow = False
-                if prev is not None:
-                    prev[1].synchronize()     # recorded a whole step ago: completes at once
-                    overflow = bool(prev[0].item())
-                ring = getattr(self, "_amp_pinned", None)
-                if ring is None:       # two pinned words, used alternately (no per-step pinning)
-                    ring = self._amp_pinned = [torch.empty(1, dtype=torch.int32).pin_memory()
-                                               for _ in range(2)]
-                host = ring[self._amp_good_steps & 1 if prev is None else (0 if prev[0] is ring[1] else 1)]
-                host.copy_(flag, non_blocking=True)
-                ev = torch.cuda.Event()
-                ev.record()
-                self._amp_prev = (host, ev)
+                # Overflow flag, loss scale and its schedule all stay on the device: the fused
+                # optimizer reads the flag and skips the update by itself, so a step needs no
+                # host synchronisation (and can be captured as a graph).
+                st = self._amp_device_state()
+                self.arena.unscale_and_check(1.0, flag, write_back=True, inv_scale_dev=st[1:2])
+                reduced = None
+                if self.parallel is not None and self.parallel.world_size > 1:
+                    reduced = flag.float()
+                    self.parallel.allreduce_max_inplace(reduced)
+                from ..ops import optim as _optim
+                _optim.amp_update(st, reduced, flag, self.amp_growth, self.amp_backoff, self.amp_interval)
+                skip_flag = flag
             else:
+                self.arena.unscale_and_check(1.0 / self._amp_scale_host, flag, write_back=True)
+                if self.parallel is not None:
+                    self.parallel.allreduce_max_inplace(flag)
                 overflow = bool(int(flag.item()))
                 skipped = overflow
-            if overflow:
-                self.amp_scale *= self.amp_backoff
-                self._amp_good_steps = 0
-                self._amp_skipped += 1
-                if self._amp_skipped >= 10 and (self.comm is None or self.comm.am_world_master()):
-                    print(f"WARNING: {self._amp_skipped} consecutive steps skipped by automatic "
-                          f"mixed precision; loss scale is now {self.amp_scale}")
-            else:
-                self._amp_skipped = 0
-                self._amp_good_steps += 1
-                if self._amp_good_steps >= self.amp_interval:
-                    self.amp_scale *= self.amp_growth
+                if overflow:
+                    self._amp_scale_host *= self.amp_backoff
                     self._amp_good_steps = 0
+                    self._amp_skipped += 1
+                    if self._amp_skipped >= 10 and (self.comm is None or self.comm.am_world_master()):
+                        print(f"WARNING: {self._amp_skipped} consecutive steps skipped by automatic "
+                              f"mixed precision; loss scale is now {self._amp_scale_host}")
+                else:
+                    self._amp_skipped = 0
+                    self._amp_good_steps += 1
+                    if self._amp_good_steps >= self.amp_interval:
+                        self._amp_scale_host *= self.amp_growth
+                        self._amp_good_steps = 0
             if skipped:
                 return False
         self.arena.step(inv, skip_flag if self.device.type == "cuda" else None)

@@ -33,7 +33,9 @@ def _lib():
                                            c_void_p, c_int, c_ll, c_float, c_void_p, c_void_p,
                                            c_void_p, c_int, c_int, c_void_p]
         lib.lb_unscale_check.restype = c_int
-        lib.lb_unscale_check.argtypes = [c_void_p, c_ll, c_float, c_int, c_void_p, c_int, c_void_p]
+        lib.lb_unscale_check.argtypes = [c_void_p, c_ll, c_float, c_void_p, c_int, c_void_p, c_int, c_void_p]
+        lib.lb_amp_update.restype = c_int
+        lib.lb_amp_update.argtypes = [c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_void_p]
         lib.lb_sqnorm.restype = c_int
         lib.lb_sqnorm.argtypes = [c_void_p, c_ll, c_void_p, c_int, c_void_p]
         lib.lb_cast_scale.restype = c_int
@@ -254,12 +256,15 @@ class ParameterArena:
             return out
         return (buf.float() ** 2).sum().reshape(1)
 
-    def unscale_and_check(self, inv_scale: float, flag: torch.Tensor, write_back: bool = True):
-        """grad *= inv_scale (optionally) and flag[0] |= any non-finite value."""
+    def unscale_and_check(self, inv_scale: float, flag: torch.Tensor, write_back: bool = True,
+                          inv_scale_dev: Optional[torch.Tensor] = None):
+        """grad *= inv_scale (optionally) and flag[0] |= any non-finite value.  With
+        ``inv_scale_dev`` (a one-element fp32 CUDA tensor) the factor is read on the device."""
         if self.grad.is_cuda:
             rc = _lib().lb_unscale_check(self.grad.data_ptr(), self.grad.numel(), float(inv_scale),
-                                         1 if write_back else 0, flag.data_ptr(),
-                                         native.dtype_code(self.grad.dtype), native.stream_ptr())
+                                         native.ptr(inv_scale_dev), 1 if write_back else 0,
+                                         flag.data_ptr(), native.dtype_code(self.grad.dtype),
+                                         native.stream_ptr())
             native.check(rc, "lb_unscale_check")
             native.count_launch()
             return
@@ -268,3 +273,14 @@ class ParameterArena:
             flag.fill_(1)
         if write_back:
             self.grad.copy_(g)
+
+
+def amp_update(state: torch.Tensor, reduced, flag: torch.Tensor, growth: float, backoff: float,
+               interval: int) -> None:
+    """One step of the loss-scale schedule on the device (``state``: scale, 1 / scale, clean
+    steps, consecutive skipped steps; ``reduced``: overflow flag after the reduction over the
+    ranks or None; ``flag``: int32 flag that the fused optimizer reads)."""
+    rc = _lib().lb_amp_update(state.data_ptr(), native.ptr(reduced), flag.data_ptr(), float(growth),
+                              float(backoff), float(interval), native.stream_ptr())
+    native.check(rc, "lb_amp_update")
+    native.count_launch()

@@ -93,7 +93,10 @@ class ParallelContext:
     def allreduce_max_inplace(self, t: torch.Tensor):
         if self.world_size == 1:
             return
-        self.comm.allreduce(t, "trainer", "max")
+        if t.dtype == torch.float32 and t.is_contiguous() and t.numel() <= 4096 and t.is_cuda:
+            self.group.allreduce_small_(t, "max")
+        else:
+            self.comm.allreduce(t, "trainer", "max")
 
     def bn_reduction(self, stats_group: int):
         """(in-place sum over the statistics group, number of ranks in it) for batch norm:

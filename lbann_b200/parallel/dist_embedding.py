@@ -33,10 +33,10 @@ def _lib():
         vpp = ctypes.POINTER(c_void_p)
         lib.lb_dist_embed_gather.restype = c_int
         lib.lb_dist_embed_gather.argtypes = [vpp, vpp, c_int, c_int, c_void_p, c_void_p, c_ll, c_int, c_ll,
-                                             c_int, ctypes.c_uint, c_void_p]
+                                             c_int, c_void_p, c_void_p]
         lib.lb_dist_embed_scatter.restype = c_int
         lib.lb_dist_embed_scatter.argtypes = [vpp, vpp, c_int, c_int, c_void_p, c_void_p, c_ll, c_int, c_ll,
-                                              c_float, c_int, ctypes.c_uint, c_void_p]
+                                              c_float, c_int, c_void_p, c_void_p]
         _configured = True
     return lib
 
@@ -92,7 +92,7 @@ class DistEmbeddingTable:
         out = torch.empty(flat.numel(), self.dim, dtype=dtype, device=flat.device)
         rc = _lib().lb_dist_embed_gather(self.buf._c_ptrs, self.group.pad._c_ptrs, self.rank, self.world,
                                          flat.data_ptr(), out.data_ptr(), flat.numel(), self.dim, self.num,
-                                         native.dtype_code(dtype), self.group._next_epoch(),
+                                         native.dtype_code(dtype), self.group.ctr_ptr,
                                          native.stream_ptr())
         native.check(rc, "lb_dist_embed_gather")
         native.count_launch()
@@ -106,7 +106,7 @@ class DistEmbeddingTable:
         rc = _lib().lb_dist_embed_scatter(self.buf._c_ptrs, self.group.pad._c_ptrs, self.rank, self.world,
                                           flat.data_ptr(), g.data_ptr(), flat.numel(), self.dim, self.num,
                                           float(scale), native.dtype_code(g.dtype),
-                                          self.group._next_epoch(), native.stream_ptr())
+                                          self.group.ctr_ptr, native.stream_ptr())
         native.check(rc, "lb_dist_embed_scatter")
         native.count_launch()
 

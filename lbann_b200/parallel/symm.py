@@ -38,21 +38,21 @@ def _lib():
         lib.lb_ipc_close.argtypes = [c_void_p]
         lib.lb_comm_pad_bytes.restype = c_int
         lib.lb_allreduce_two_shot.restype = c_int
-        lib.lb_allreduce_two_shot.argtypes = [vpp, vpp, c_int, c_int, c_ll, c_float, ctypes.c_uint,
+        lib.lb_allreduce_two_shot.argtypes = [vpp, vpp, c_int, c_int, c_ll, c_float, c_void_p,
                                               c_int, c_int, c_void_p]
         lib.lb_allreduce_one_shot.restype = c_int
         lib.lb_allreduce_one_shot.argtypes = [vpp, vpp, c_int, c_int, c_void_p, c_void_p, c_int,
-                                              c_int, c_ll, ctypes.c_uint, c_void_p]
+                                              c_int, c_ll, c_void_p, c_void_p]
         lib.lb_put_rows.restype = c_int
         lib.lb_put_rows.argtypes = [c_void_p, c_ll, c_void_p, c_ll, c_ll, c_ll, c_void_p]
         lib.lb_halo_exchange_fwd.restype = c_int
         lib.lb_halo_exchange_fwd.argtypes = [vpp, vpp, c_int, c_int, c_int, c_int, c_void_p, c_ll, c_ll,
-                                             c_ll, c_ll, c_float, c_int, ctypes.c_uint, c_void_p]
+                                             c_ll, c_ll, c_float, c_int, c_void_p, c_void_p]
         lib.lb_halo_exchange_bwd.restype = c_int
         lib.lb_halo_exchange_bwd.argtypes = [vpp, vpp, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
-                                             c_ll, c_ll, c_ll, c_ll, c_int, ctypes.c_uint, c_void_p]
+                                             c_ll, c_ll, c_ll, c_ll, c_int, c_void_p, c_void_p]
         lib.lb_group_barrier.restype = c_int
-        lib.lb_group_barrier.argtypes = [vpp, vpp, c_int, c_int, c_int, ctypes.c_uint, c_void_p]
+        lib.lb_group_barrier.argtypes = [vpp, vpp, c_int, c_int, c_int, c_void_p, c_void_p]
         _configured = True
     return lib
 
@@ -127,11 +127,15 @@ class SymmetricGroup:
             self.world, self.rank = 1, 0
         self.native = self.device.type == "cuda" and self.world > 1
         self.epoch = 0
+        self.ctr = None          # use counters of the flag rows (this rank's own memory)
+        self.ctr_ptr = None
         self.pad = None
         self.staging = None
         self.bytes_moved = 0
         if self.native:
             self.pad = SymmetricBuffer(self, _lib().lb_comm_pad_bytes())
+            self.ctr = torch.zeros(_lib().lb_comm_pad_bytes() // 4, dtype=torch.int32, device=self.device)
+            self.ctr_ptr = self.ctr.data_ptr()
             self.staging = SymmetricBuffer(self, self.world * 4096 * 4)   # one-shot slots
             self.barrier_host()
 
@@ -173,7 +177,7 @@ class SymmetricGroup:
             return
         ptrs = (c_void_p * self.world)(*[p + offset_bytes for p in buf.peer_ptrs])
         rc = _lib().lb_allreduce_two_shot(ptrs, self.pad._c_ptrs, self.rank, self.world, numel,
-                                          float(scale), self._next_epoch(),
+                                          float(scale), self.ctr_ptr,
                                           native.dtype_code(dtype), blocks, native.stream_ptr())
         native.check(rc, "lb_allreduce_two_shot")
         native.count_launch()
@@ -195,7 +199,7 @@ class SymmetricGroup:
             return
         rc = _lib().lb_allreduce_one_shot(self.staging._c_ptrs, self.pad._c_ptrs, self.rank, self.world,
                                           t.data_ptr(), t.data_ptr(), t.numel(),
-                                          0 if op == "sum" else 1, 4096, self._next_epoch(),
+                                          0 if op == "sum" else 1, 4096, self.ctr_ptr,
                                           native.stream_ptr())
         native.check(rc, "lb_allreduce_one_shot")
         native.count_launch()
@@ -219,7 +223,7 @@ class SymmetricGroup:
         down = self.rank + 1 if self.rank < self.world - 1 else -1
         rc = _lib().lb_halo_exchange_fwd(ext._c_ptrs, self.pad._c_ptrs, self.rank, self.world, up, down,
                                          x.data_ptr(), n, dl, h, plane_bytes, float(fill),
-                                         native.dtype_code(x.dtype), self._next_epoch(),
+                                         native.dtype_code(x.dtype), self.ctr_ptr,
                                          native.stream_ptr())
         if rc == -2:
             return False
@@ -236,7 +240,7 @@ class SymmetricGroup:
         down = self.rank + 1 if self.rank < self.world - 1 else -1
         rc = _lib().lb_halo_exchange_bwd(recv._c_ptrs, self.pad._c_ptrs, self.rank, self.world, up, down,
                                          g.data_ptr(), dx.data_ptr(), n, dl, h, plane_bytes,
-                                         native.dtype_code(g.dtype), self._next_epoch(),
+                                         native.dtype_code(g.dtype), self.ctr_ptr,
                                          native.stream_ptr())
         if rc == -2:
             return False
@@ -253,6 +257,6 @@ class SymmetricGroup:
             dist.barrier(group=self.pg)
             return
         rc = _lib().lb_group_barrier(self.pad._c_ptrs, self.pad._c_ptrs, self.rank, self.world, phase,
-                                     self._next_epoch(), native.stream_ptr())
+                                     self.ctr_ptr, native.stream_ptr())
         native.check(rc, "lb_group_barrier")
         native.count_launch()
