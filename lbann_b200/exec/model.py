@@ -99,6 +99,8 @@ class ExecModel:
         self._amp_skipped = 0
         self._gen = None
         self.sync_layers = False       # debugging: synchronise after every layer
+        self._graph_mode = None        # decided at the first training step
+        self._graphs = {}
         self.layer_timing = False
         self.is_setup = False
 
@@ -557,7 +559,86 @@ class ExecModel:
         return True
 
     def train_step(self, inputs, global_mini_batch_size=None, mini_batch_offset=0):
-        """clear grads -> forward -> objective -> backward (+ gradient sync) -> update."""
+        """clear grads -> forward -> objective -> backward (+ gradient sync) -> update.
+        With the ``use_cuda_graph`` option the step is captured once per input signature as
+        a CUDA graph and replayed afterwards."""
+        if self._graph_mode is None:
+            self._graph_mode = self._graph_capable()
+        if self._graph_mode:
+            return self._train_step_graph(inputs, global_mini_batch_size, mini_batch_offset)
+        return self._train_step_eager(inputs, global_mini_batch_size, mini_batch_offset)
+
+    # ------------------------------------------------------------------ CUDA-graph replay
+    _IN_STEP_HOOKS = ("on_forward_prop_begin", "on_forward_prop_end", "on_layer_forward_begin",
+                      "on_layer_forward_end", "on_backward_prop_begin", "on_backward_prop_end",
+                      "on_optimize_begin", "on_optimize_end")
+
+    def _graph_capable(self) -> bool:
+        """Graph replay is used when asked for, on a GPU, and when nothing needs the host
+        inside a step: no callback overrides an in-step hook, no per-layer timing."""
+        from ..callbacks.base import ExecCallback
+        from ..utils import options as _opts
+        if self.device.type != "cuda" or not (_opts.current().get_bool("use_cuda_graph")
+                                              or os.environ.get("LBANN_CUDA_GRAPH") == "1"):
+            return False
+        if self.layer_timing or self.sync_layers or self._phase_timer is not None:
+            return False
+        for cb in self.callbacks:
+            for h in self._IN_STEP_HOOKS:
+                if getattr(type(cb), h, None) is not getattr(ExecCallback, h):
+                    return False
+        # layers whose output depends on a host-side value that changes from step to step
+        # (position in the epoch, host random streams, user code)
+        if any(l.type in self._HOST_STATE_LAYERS for l in self.layers):
+            return False
+        return True
+
+    _HOST_STATE_LAYERS = frozenset({"mini_batch_index", "dropout", "selu_dropout", "bernoulli", "gaussian",
+                                    "uniform", "dist_embedding", "external", "python"})
+
+    def _train_step_graph(self, inputs, gmb, offset):
+        key = (tuple((k, tuple(v.shape), v.dtype) for k, v in sorted(inputs.items())), gmb)
+        entry = self._graphs.get(key)
+        if entry is None:
+            entry = self._graphs[key] = {"warm": 0}
+        if "graph" not in entry:
+            if entry["warm"] < 3:
+                # lazy allocations, symmetric buffers, tensor maps and optimizer tables are
+                # created by ordinary steps first
+                entry["warm"] += 1
+                return self._train_step_eager(inputs, gmb, offset)
+            static = {k: torch.empty_like(v) for k, v in inputs.items()}
+            for k, v in inputs.items():
+                static[k].copy_(v)
+            samples0 = self.stats["training"].samples
+            counts0 = [s.step_count for s in self.arena.slots]
+            launches0 = native.launches()
+            graph = torch.cuda.CUDAGraph()
+            torch.cuda.synchronize(self.device)
+            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                out = self._train_step_eager(static, gmb, offset)
+            # capture executes nothing: undo the host-side bookkeeping it did, replay does it
+            self.stats["training"].samples = samples0
+            for s, c in zip(self.arena.slots, counts0):
+                s.step_count = c
+            entry.update(graph=graph, static=static, out=out, acts=self.acts,
+                         launches=native.launches() - launches0, samples=self._global_mb)
+            native.count_launch(-entry["launches"])
+        else:
+            for k, v in inputs.items():
+                entry["static"][k].copy_(v)
+        entry["graph"].replay()
+        self.stats["training"].samples += entry["samples"]
+        for s in self.arena.slots:
+            if s.kind != "none":
+                s.step_count += 1
+        native.count_launch(entry["launches"])
+        self.acts = entry["acts"]
+        self.current_inputs = entry["static"]
+        self.last_objective = entry["out"]
+        return self.last_objective
+
+    def _train_step_eager(self, inputs, global_mini_batch_size=None, mini_batch_offset=0):
         pt = self._phase_timer
         if pt is not None:
             pt.mark("start")

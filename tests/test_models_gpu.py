@@ -15,9 +15,11 @@ from test_models_cpu import _reader
 pytestmark = pytest.mark.gpu
 
 
-def _train_gpu(model, reader, steps, mb, dtype, optimizer=None):
+def _train_gpu(model, reader, steps, mb, dtype, optimizer=None, graph=False):
     o = opts.reset()
     o.set("default_dtype", dtype)
+    if graph:
+        o.set("use_cuda_graph", True)
     exp = lbann.proto.serialize.build_experiment(
         trainer=lbann.Trainer(mini_batch_size=mb, random_seed=3), model=model, data_reader=reader,
         optimizer=optimizer or lbann.Adam(learn_rate=2e-3, beta1=0.9, beta2=0.99, eps=1e-8))
@@ -33,6 +35,8 @@ def _train_gpu(model, reader, steps, mb, dtype, optimizer=None):
         losses.append(float(m.last_objective))
     assert native.consume_status() == 0
     assert native.launches() > n0, "no native kernel ran"
+    if graph:
+        assert m._graph_mode and any("graph" in e for e in m._graphs.values()), "step was not captured"
     tr.shutdown()
     assert all(math.isfinite(v) for v in losses), losses
     return losses
@@ -82,3 +86,35 @@ def test_attention_score_fusion_matches_unfused(monkeypatch):
     plain = run()
     for a, b in zip(fused, plain):
         assert abs(a - b) < 3e-2 * max(1.0, abs(b)), (fused, plain)
+
+
+
+@pytest.mark.parametrize("family", ["cosmoflow_amp", "gpt"])
+def test_cuda_graph_replay_matches_eager_steps(family):
+    """The training step captured as a CUDA graph (after three ordinary steps) and replayed
+    gives the losses of the step-by-step run: same kernels, same order, device-side
+    optimizer step counter and loss-scale schedule."""
+    def build():
+        torch.manual_seed(0)
+        if family == "gpt":
+            from lbann_b200.models.transformer import construct_gpt_model
+            m = construct_gpt_model(vocab_size=256, seq_len=64, d_model=128, num_heads=4, num_layers=2,
+                                    ffn_dim=512)
+            return m, _reader(8, [65], "randint:256"), "bf16"
+        from lbann_b200.models.cosmoflow import construct_cosmoflow_model, synthetic_reader
+        m = construct_cosmoflow_model(32, 4, 4, num_epochs=1, channels=(16, 32, 32), pool_mode="max",
+                                      conv_bias=False, fc_sizes=(64, 32))
+        m.amp = lbann.AmpOptions(enabled=True, init_scale=1024.0)
+        return m, synthetic_reader(8, 32, 4, 4), "fp16"
+
+    model, reader, dt = build()
+    sgd = lambda: lbann.Adam(learn_rate=1e-4, beta1=0.9, beta2=0.99, eps=1e-8)      # noqa: E731
+    eager = _train_gpu(model, reader, steps=10, mb=8, dtype=dt, optimizer=sgd())
+    model, reader, dt = build()
+    again = _train_gpu(model, reader, steps=10, mb=8, dtype=dt, optimizer=sgd())
+    model, reader, dt = build()
+    replay = _train_gpu(model, reader, steps=10, mb=8, dtype=dt, optimizer=sgd(), graph=True)
+    # tolerance: what two step-by-step runs differ by (fp32 atomics in the filter gradients)
+    noise = max(abs(a - b) for a, b in zip(eager, again))
+    for a, b in zip(eager, replay):
+        assert abs(a - b) <= max(5.0 * noise, 2e-3 * max(1.0, abs(a))), (eager, again, replay)
