@@ -63,6 +63,8 @@ def ours(args):
     rank = int(os.environ.get("RANK", "0"))
     o = opts.reset()
     o.set("default_dtype", "bf16")
+    if args.graph:
+        o.set("use_cuda_graph", True)
     exp = _build(lbann, args, world)
     tr = ExecTrainer(exp)
     m = tr.build_model(exp.model)
@@ -70,7 +72,7 @@ def ours(args):
     dc = tr.data_coordinator
     dc.start_epoch("training")
     batches = [dc.next_batch("training"), dc.next_batch("training")]
-    for i in range(max(args.warmup, 3)):
+    for i in range(max(args.warmup, 3) + (4 if args.graph else 0)):     # + ordinary steps and capture
         b = batches[i % 2]
         m.train_step(b.tensors, b.global_size)
     torch.cuda.synchronize()
@@ -94,7 +96,8 @@ def ours(args):
         gb = args.batch * world
         out = {"model": args.model, "impl": "lbann_b200", "n_gpus": world, "global_batch": gb,
                "ms_per_step": round(ms, 3), "samples_per_s": round(gb / ms * 1e3, 2), "dtype": "bf16",
-               "gpu_launches": native.launches() - n0, "loss": loss, "device_status": status}
+               "gpu_launches": native.launches() - n0, "loss": loss, "device_status": status,
+               "cuda_graph": bool(getattr(m, "_graph_mode", False))}
         if args.model == "gpt":
             out["tokens_per_s"] = round(gb * args.seq / ms * 1e3, 1)
             out["config"] = {"layers": args.layers, "d_model": args.d_model, "heads": args.heads,
@@ -213,6 +216,7 @@ def main():
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--seq", type=int, default=2048)
     ap.add_argument("--vocab", type=int, default=50304)
+    ap.add_argument("--graph", action="store_true", help="capture the step as a CUDA graph and replay it")
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     args = ap.parse_args()

@@ -61,3 +61,34 @@ def test_lenet_trains_on_cpu(tmp_path):
     assert "test objective function" in out
     assert "mini-batch time statistics" in out
     assert (tmp_path / "experiment.prototext").exists()
+
+
+def test_cuda_graph_option_is_ignored_without_a_gpu():
+    """use_cuda_graph on a CPU run: the model decides against capturing and trains step by
+    step; a callback that hooks into the step also switches capturing off."""
+    from lbann_b200.exec.trainer import ExecTrainer
+    from lbann_b200.utils import options as opts
+    from test_models_cpu import _reader
+    o = opts.reset()
+    o.set("disable_cuda", True)
+    o.set("use_cuda_graph", True)
+    x = lbann.Input(data_field="samples")
+    y = lbann.FullyConnected(x, num_neurons=3)
+    loss = lbann.MeanSquaredError(y, lbann.Input(data_field="responses"))
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph([x])),
+                        objective_function=lbann.ObjectiveFunction([loss]))
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=4), model=model,
+        data_reader=_reader(8, [5], "normal", response_dims=[3]), optimizer=lbann.SGD(learn_rate=0.05))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    b = dc.next_batch("training")
+    first = float(m.train_step(b.tensors, b.global_size))
+    for _ in range(5):
+        last = float(m.train_step(b.tensors, b.global_size))
+    tr.shutdown()
+    opts.reset()
+    assert m._graph_mode is False and not m._graphs
+    assert last < first
