@@ -627,6 +627,9 @@ class ExecModel:
         else:
             for k, v in inputs.items():
                 entry["static"][k].copy_(v)
+        # hyper-parameters changed by callbacks (learning-rate schedules) reach the captured
+        # optimizer kernel through its device-side table, refreshed here when they change
+        self.arena._segments()
         entry["graph"].replay()
         self.stats["training"].samples += entry["samples"]
         for s in self.arena.slots:

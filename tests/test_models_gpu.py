@@ -118,3 +118,36 @@ def test_cuda_graph_replay_matches_eager_steps(family):
     noise = max(abs(a - b) for a, b in zip(eager, again))
     for a, b in zip(eager, replay):
         assert abs(a - b) <= max(5.0 * noise, 2e-3 * max(1.0, abs(a))), (eager, again, replay)
+
+
+def test_learning_rate_change_reaches_a_captured_step():
+    """A learning-rate schedule keeps working under graph replay: the optimizer kernel reads
+    its hyper-parameters from a device table that is refreshed before a replay."""
+    from lbann_b200.models.transformer import construct_gpt_model
+    torch.manual_seed(0)
+    o = opts.reset()
+    o.set("default_dtype", "bf16")
+    o.set("use_cuda_graph", True)
+    model = construct_gpt_model(vocab_size=128, seq_len=32, d_model=64, num_heads=2, num_layers=1, ffn_dim=128)
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=4, random_seed=3), model=model,
+        data_reader=_reader(4, [33], "randint:128"), optimizer=lbann.SGD(learn_rate=0.05))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    b = dc.next_batch("training")
+    for _ in range(6):
+        m.train_step(b.tensors, b.global_size)
+    assert any("graph" in e for e in m._graphs.values())
+    before = m.arena.master.detach().clone()
+    m.train_step(b.tensors, b.global_size)
+    moved = float((m.arena.master - before).abs().max())
+    for s in m.arena.slots:
+        s.hp["learn_rate"] = 0.0
+    before = m.arena.master.detach().clone()
+    m.train_step(b.tensors, b.global_size)
+    frozen = float((m.arena.master - before).abs().max())
+    tr.shutdown()
+    assert native.consume_status() == 0
+    assert moved > 0.0 and frozen == 0.0, (moved, frozen)
