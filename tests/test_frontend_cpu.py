@@ -47,3 +47,26 @@ def test_grid_search_writes_one_file_per_point_and_runs(tmp_path, capsys):
         os.chdir(cwd)
     assert rc == 0
     assert "training epoch 0 objective function" in capsys.readouterr().out
+
+
+def test_profiling_regions_and_hierarchical_timers():
+    import time
+    import pytest
+    from lbann_b200.utils import profiling as prof
+    timers = prof.TimerMap("train")
+    for _ in range(2):
+        with timers.scope("epoch"):
+            with timers.scope("forward"), prof.ProfRegion("forward"):
+                time.sleep(0.002)
+            with timers.scope("backward"):
+                time.sleep(0.001)
+    epoch = timers.children["epoch"]
+    assert len(epoch.times) == 2 and set(epoch.children) == {"forward", "backward"}
+    assert epoch.total() >= epoch.children["forward"].total() + epoch.children["backward"].total()
+    text = timers.report()
+    assert "epoch: total" in text and "    forward: total" in text
+    prof.prof_region_begin("a")
+    with pytest.raises(RuntimeError):
+        prof.prof_region_end("b")
+    info = prof.system_info()
+    assert info["cpus"] >= 1 and "torch" in info
