@@ -13,7 +13,7 @@
 namespace lb {
 
 constexpr int kOuterMaxK = 32;
-constexpr int kOuterRows = 64;      // rows of `out` per block
+constexpr int kOuterRows = 32;      // rows of `out` per block (power of two)
 
 template <typename T, int K>
 __global__ void __launch_bounds__(256)
@@ -37,23 +37,33 @@ outer_accum_kernel(const T* __restrict__ a, const T* __restrict__ b, float* __re
     for (int j = 0; j < 4; ++j) bv[k][j] = to_f32<T>(e[j]);
   }
   const int rows = M - m0 < kOuterRows ? M - m0 : kOuterRows;
-#pragma unroll 4
-  for (int m = 0; m < rows; ++m) {
-    float4* o = reinterpret_cast<float4*>(out + (long long)(m0 + m) * N + n);
-    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    if (beta != 0.f) {
-      acc = *o;
-      acc.x *= beta; acc.y *= beta; acc.z *= beta; acc.w *= beta;
+  // eight rows at a time: their read-modify-write loads are all issued before the first is
+  // used, which is what keeps enough bytes in flight for a memory-bound kernel
+  constexpr int G = 8;
+  for (int mb = 0; mb < rows; mb += G) {
+    float4 acc[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      acc[g] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (beta != 0.f && mb + g < rows)
+        acc[g] = *reinterpret_cast<const float4*>(out + (long long)(m0 + mb + g) * N + n);
     }
 #pragma unroll
-    for (int k = 0; k < K; ++k) {
-      const float av = sa[k][m];
-      acc.x = fmaf(av, bv[k][0], acc.x);
-      acc.y = fmaf(av, bv[k][1], acc.y);
-      acc.z = fmaf(av, bv[k][2], acc.z);
-      acc.w = fmaf(av, bv[k][3], acc.w);
+    for (int g = 0; g < G; ++g) {
+      acc[g].x *= beta; acc[g].y *= beta; acc[g].z *= beta; acc[g].w *= beta;
+#pragma unroll
+      for (int k = 0; k < K; ++k) {
+        const float av = sa[k][(mb + g) & (kOuterRows - 1)];
+        acc[g].x = fmaf(av, bv[k][0], acc[g].x);
+        acc[g].y = fmaf(av, bv[k][1], acc[g].y);
+        acc[g].z = fmaf(av, bv[k][2], acc[g].z);
+        acc[g].w = fmaf(av, bv[k][3], acc[g].w);
+      }
     }
-    *o = acc;
+#pragma unroll
+    for (int g = 0; g < G; ++g)
+      if (mb + g < rows)
+        *reinterpret_cast<float4*>(out + (long long)(m0 + mb + g) * N + n) = acc[g];
   }
 }
 

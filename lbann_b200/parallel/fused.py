@@ -67,16 +67,18 @@ class FusedGemm:
         return self._maps.data_ptr()
 
     def _staging(self, rows: int, k: int, dtype: torch.dtype):
-        """Local gathered buffer and per-block flags for one operand shape (flags hold the
-        epoch of the launch that filled the block, so they never need clearing)."""
+        """Local gathered buffer and per-block flags for one operand shape.  The flags are
+        cleared in the stream before every launch and the "block present" value is constant,
+        so a launch carries no per-call value and can be replayed from a CUDA graph."""
         key = (rows, k, dtype)
         if key not in self._stage:
             P = self.group.world
             gathered = torch.empty((P * rows, k), dtype=dtype, device=self.group.device)
             flags = torch.zeros(P * rows // 128, dtype=torch.int32, device=self.group.device)
             self._stage[key] = (gathered, flags)
-        self._epoch = (self._epoch + 1) & 0x7FFFFFFF or 1
-        return self._stage[key] + (self._epoch,)
+        gathered, flags = self._stage[key]
+        flags.zero_()
+        return gathered, flags, 1
 
     def _ptr_array(self, buf: SymmetricBuffer, offset_bytes: int = 0):
         return (c_void_p * self.group.world)(*[p + offset_bytes for p in buf.peer_ptrs])
