@@ -70,3 +70,49 @@ def test_profiling_regions_and_hierarchical_timers():
         prof.prof_region_end("b")
     info = prof.system_info()
     assert info["cpus"] >= 1 and "torch" in info
+
+
+def test_saved_model_is_loaded_for_inference(tmp_path):
+    """Train with the save-model callback, then rebuild the model through the embedding API
+    with another mini-batch size and reproduce the trained model's outputs."""
+    import numpy as np
+    from lbann_b200 import inference
+    from lbann_b200.exec.trainer import ExecTrainer
+    from lbann_b200.utils import options as opts
+    o = opts.reset()
+    o.set("disable_cuda", True)
+    x = lbann.Input(data_field="samples")
+    h = lbann.Relu(lbann.FullyConnected(x, num_neurons=7, has_bias=True, name="fc1"))
+    y = lbann.FullyConnected(h, num_neurons=3, has_bias=True, name="fc2")
+    probs = lbann.Softmax(y, name="probs")
+    loss = lbann.CrossEntropy(probs, lbann.Input(data_field="labels"))
+    model = lbann.Model(2, layers=list(lbann.traverse_layer_graph([x])),
+                        objective_function=lbann.ObjectiveFunction([loss]),
+                        callbacks=[lbann.CallbackSaveModel(dir=str(tmp_path / "saved"))])
+    r = lbann.reader_pb2.Reader(name="synthetic", role="train", num_samples=16, synth_dimensions="5",
+                                num_labels=3, fraction_of_data_to_use=1.0)
+    dr = lbann.reader_pb2.DataReader()
+    dr.reader.append(r)
+    exp = lbann.proto.serialize.build_experiment(trainer=lbann.Trainer(mini_batch_size=8), model=model,
+                                                 data_reader=dr, optimizer=lbann.SGD(learn_rate=0.1))
+    os.makedirs(tmp_path / "saved", exist_ok=True)
+    with open(tmp_path / "saved" / "experiment.prototext", "w") as f:
+        from google.protobuf import text_format
+        f.write(text_format.MessageToString(exp))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    tr.train(m)
+    data = np.random.RandomState(1).randn(6, 5).astype(np.float32)
+    import torch
+    with torch.no_grad():
+        m.forward_prop({"samples": torch.from_numpy(data), "labels": torch.zeros(6, 3)}, "prediction")
+        want = m.acts["probs"][0].numpy().copy()
+    tr.shutdown()
+    inference.initialize_lbann(["--disable_cuda"])
+    h = inference.load_inference_model(str(tmp_path / "saved"), 4, {"samples": (5,), "labels": (3,)})
+    got = h.infer(data, output_layer="probs")
+    labels = h.infer(data, output_layer="probs", labels=True)
+    inference.finalize_lbann(h)
+    opts.reset()
+    np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
+    assert labels.tolist() == want.argmax(1).tolist()
