@@ -615,8 +615,21 @@ class ExecModel:
             launches0 = native.launches()
             graph = torch.cuda.CUDAGraph()
             torch.cuda.synchronize(self.device)
-            with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                out = self._train_step_eager(static, gmb, offset)
+            try:
+                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                    out = self._train_step_eager(static, gmb, offset)
+            except Exception as e:      # something in this model cannot be captured
+                self._graph_mode = False
+                self._graphs.clear()
+                self.stats["training"].samples = samples0
+                for s, c in zip(self.arena.slots, counts0):
+                    s.step_count = c
+                native.count_launch(launches0 - native.launches())
+                if self.comm is None or self.comm.am_world_master():
+                    print(f"WARNING: the training step could not be captured as a CUDA graph ({e}); "
+                          "kernels are launched from the host", flush=True)
+                torch.cuda.synchronize(self.device)
+                return self._train_step_eager(inputs, gmb, offset)
             # capture executes nothing: undo the host-side bookkeeping it did, replay does it
             self.stats["training"].samples = samples0
             for s, c in zip(self.arena.slots, counts0):
