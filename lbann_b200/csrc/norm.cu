@@ -130,17 +130,30 @@ __global__ void layer_norm_param_grad_kernel(const T* __restrict__ x, const T* _
 }
 
 // Sum an 8-wide register array over threadIdx.y; the result is valid where threadIdx.y == 0.
-// `sm` holds blockDim.x * blockDim.y * 8 floats.  Every thread of the block must call it.
+// blockDim.x is a power of two <= 32 and the block has 256 threads.  Lanes of a warp that
+// share threadIdx.x are combined with shuffles first, so shared memory only carries one
+// partial per warp and the closing serial sum is 8 terms long (it used to be blockDim.y
+// terms, which left the memory system idle for microseconds at the end of every block).
+// `sm` holds 8 warps x 8 values x blockDim.x floats.  Every thread of the block must call it.
 __device__ __forceinline__ void reduce_over_y(float (&a)[8], float* sm) {
-  __syncthreads();
+  const int bx = blockDim.x;
+  for (int off = bx; off < 32; off <<= 1) {
 #pragma unroll
-  for (int j = 0; j < 8; ++j) sm[(j * blockDim.y + threadIdx.y) * blockDim.x + threadIdx.x] = a[j];
+    for (int j = 0; j < 8; ++j) a[j] += __shfl_xor_sync(0xffffffffu, a[j], off);
+  }
+  const int tid = threadIdx.y * bx + threadIdx.x;
+  const int warp = tid >> 5, lane = tid & 31, nw = (bx * blockDim.y) >> 5;
+  __syncthreads();
+  if (lane < bx) {
+#pragma unroll
+    for (int j = 0; j < 8; ++j) sm[(warp * 8 + j) * bx + lane] = a[j];
+  }
   __syncthreads();
   if (threadIdx.y == 0) {
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       float t = 0.f;
-      for (int yy = 0; yy < (int)blockDim.y; ++yy) t += sm[(j * blockDim.y + yy) * blockDim.x + threadIdx.x];
+      for (int w = 0; w < nw; ++w) t += sm[(w * 8 + j) * bx + threadIdx.x];
       a[j] = t;
     }
   }
@@ -288,22 +301,22 @@ __global__ void bn_bwd_sums_kernel(const T* __restrict__ x, const T* __restrict_
   const int v = blockIdx.x * blockDim.x + threadIdx.x;
   const int grp = blockIdx.z;
   const bool valid = v < cv;
-  float mean[8], rstd[8], sc[8], a0[8], a1[8], a2[8], a3[8];
+  // Two running sums per channel are enough: S1 = sum g and S2 = sum g (x - mean); the four
+  // outputs are linear in them (dscale = S2 rstd, dbias = S1, dmean = -scale rstd S1,
+  // dvar = -scale rstd^3 S2 / 2), which halves the registers and the block reductions.
+  float mean[8], s1[8], s2[8];
 #pragma unroll
   for (int j = 0; j < 8; ++j) {
     const int c = valid ? v * 8 + j : 0;
     mean[j] = stats[(long long)grp * 2 * C + c];
-    rstd[j] = rsqrtf(stats[(long long)grp * 2 * C + C + c] + eps);
-    sc[j] = scale ? scale[c] : 1.f;
-    a0[j] = a1[j] = a2[j] = a3[j] = 0.f;
+    s1[j] = s2[j] = 0.f;
   }
   const long long r0 = (long long)blockIdx.y * rows_per_block;
   const long long r1 = min(rows, r0 + rows_per_block);
   const long long base = ((long long)grp * rows) * C + v * 8;
-  if (valid)
+  if (valid) {
 #pragma unroll 4
-  #pragma unroll 4
-  for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
+    for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
       float fx[8], fg[8], fy[8];
       ld8n<T>(x + base + r * C, fx);
       ld8n<T>(dy + base + r * C, fg);
@@ -313,27 +326,24 @@ __global__ void bn_bwd_sums_kernel(const T* __restrict__ x, const T* __restrict_
         float g = fg[j];
         if (act == 1) g = fy[j] > 0.f ? g : 0.f;
         else if (act == 2) g = fy[j] > 0.f ? g : act_param * g;
-        const float xc = fx[j] - mean[j];
-        a0[j] += g * xc * rstd[j];
-        a1[j] += g;
-        const float dxh = g * sc[j];
-        a2[j] -= dxh * rstd[j];
-        a3[j] -= dxh * xc * rstd[j] * rstd[j] * rstd[j] * 0.5f;
+        s1[j] += g;
+        s2[j] += g * (fx[j] - mean[j]);
       }
     }
-  reduce_over_y(a0, sm);
-  reduce_over_y(a1, sm);
-  reduce_over_y(a2, sm);
-  reduce_over_y(a3, sm);
+  }
+  reduce_over_y(s1, sm);
+  reduce_over_y(s2, sm);
   if (valid && threadIdx.y == 0) {
     float* out = bsums + (long long)grp * 4 * C;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int c = v * 8 + j;
-      atomicAdd(out + c, a0[j]);
-      atomicAdd(out + C + c, a1[j]);
-      atomicAdd(out + 2 * C + c, a2[j]);
-      atomicAdd(out + 3 * C + c, a3[j]);
+      const float rstd = rsqrtf(stats[(long long)grp * 2 * C + C + c] + eps);
+      const float sc = scale ? scale[c] : 1.f;
+      atomicAdd(out + c, s2[j] * rstd);
+      atomicAdd(out + C + c, s1[j]);
+      atomicAdd(out + 2 * C + c, -sc * rstd * s1[j]);
+      atomicAdd(out + 3 * C + c, -0.5f * sc * rstd * rstd * rstd * s2[j]);
     }
   }
 }
