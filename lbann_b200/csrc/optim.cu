@@ -59,8 +59,12 @@ __global__ void fused_optimizer_kernel(float* __restrict__ w, const G* __restric
                                        int nseg, long long total, float inv_scale,
                                        const int* __restrict__ skip_flag,
                                        const int* __restrict__ step_ptr,
-                                       const float* __restrict__ lr_scale_ptr) {
+                                       const float* __restrict__ lr_scale_ptr,
+                                       const float* __restrict__ inv_scale_dev) {
   if (skip_flag && *skip_flag) return;  // AMP overflow: the whole step is skipped
+  // AMP: the inverse loss scale of this step's gradients, kept on the device; the gradients
+  // are then unscaled here, in registers, instead of by a pass of their own
+  if (inv_scale_dev) inv_scale *= *inv_scale_dev;
   // The step number and a global learning-rate multiplier live in device memory so that a
   // captured CUDA graph sees fresh values on every replay.
   const float step_t = step_ptr ? (float)(*step_ptr) : 1.f;
@@ -131,7 +135,8 @@ __global__ void unscale_check_kernel(G* __restrict__ grad, long long n, float in
 // Loss-scale schedule of automatic mixed precision, on the device so that a training step
 // needs no host decision (src/models/model.cpp:1796-1824 is the schedule): after an overflow
 // the scale shrinks and the step is skipped, after `interval` clean steps it grows.
-// state = {scale, 1 / scale, clean steps, consecutive skipped steps}; reduced: the overflow
+// state = {scale, 1 / scale, clean steps, consecutive skipped steps, 1 / scale of the step
+// that just ran (what the optimizer unscales this step's gradients with)}; reduced: the overflow
 // flag after the max-reduction over the ranks (nullptr on one rank); flag: this rank's flag
 // on entry, the decision the optimizer reads on exit.
 __global__ void amp_update_kernel(float* __restrict__ state, const float* __restrict__ reduced,
@@ -141,6 +146,7 @@ __global__ void amp_update_kernel(float* __restrict__ state, const float* __rest
   const bool bad = reduced ? (*reduced > 0.f) : (*flag != 0);
   *flag = bad ? 1 : 0;
   float scale = state[0], good = state[2], skipped = state[3];
+  state[4] = state[1];
   if (bad) {
     scale *= backoff;
     good = 0.f;
@@ -209,7 +215,7 @@ int lb_opt_chunk() { return lb::kOptChunk; }
 int lb_fused_optimizer(float* w, const void* grad, float* s0, float* s1, void* w16,
                        const void* segs, int nseg, long long total, float inv_scale,
                        const int* skip_flag, const int* step_ptr, const float* lr_scale_ptr,
-                       int grad_dtype, int w16_dtype, void* stream_) {
+                       const float* inv_scale_dev, int grad_dtype, int w16_dtype, void* stream_) {
   using namespace lb;
   if (total <= 0 || nseg <= 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
@@ -218,7 +224,7 @@ int lb_fused_optimizer(float* w, const void* grad, float* s0, float* s1, void* w
 #define LB_OPT(G, W)                                                                      \
   fused_optimizer_kernel<G, W><<<grid, 256, 0, s>>>(w, (const G*)grad, s0, s1, (W*)w16, sg, \
                                                     nseg, total, inv_scale, skip_flag,     \
-                                                    step_ptr, lr_scale_ptr)
+                                                    step_ptr, lr_scale_ptr, inv_scale_dev)
   const bool wb = (w16_dtype == kBF16);
   if (grad_dtype == kF32) { if (wb) LB_OPT(float, __nv_bfloat16); else LB_OPT(float, __half); }
   else if (grad_dtype == kBF16) { if (wb) LB_OPT(__nv_bfloat16, __nv_bfloat16); else LB_OPT(__nv_bfloat16, __half); }

@@ -504,7 +504,8 @@ class ExecModel:
     def _amp_device_state(self) -> torch.Tensor:
         if self._amp_state is None:
             s = self._amp_scale_host
-            self._amp_state = torch.tensor([s, 1.0 / s, 0.0, 0.0], dtype=torch.float32, device=self.device)
+            self._amp_state = torch.tensor([s, 1.0 / s, 0.0, 0.0, 1.0 / s], dtype=torch.float32,
+                                           device=self.device)
         return self._amp_state
 
     def update_weights(self) -> bool:
@@ -514,6 +515,7 @@ class ExecModel:
         inv = 1.0
         skip_flag = None
         skipped = False
+        amp_inv = None
         if self.amp_enabled:
             # the reference's schedule: src/models/model.cpp:1796-1824
             flag = torch.zeros(1, dtype=torch.int32, device=self.device)
@@ -522,7 +524,10 @@ class ExecModel:
                 # optimizer reads the flag and skips the update by itself, so a step needs no
                 # host synchronisation (and can be captured as a graph).
                 st = self._amp_device_state()
-                self.arena.unscale_and_check(1.0, flag, write_back=True, inv_scale_dev=st[1:2])
+                # the check only reads; the optimizer unscales in registers (st[4] = inverse of
+                # the scale that this step's gradients carry)
+                self.arena.unscale_and_check(1.0, flag, write_back=False, inv_scale_dev=st[1:2])
+                amp_inv = st[4:5]
                 reduced = None
                 if self.parallel is not None and self.parallel.world_size > 1:
                     reduced = flag.float()
@@ -551,7 +556,7 @@ class ExecModel:
                         self._amp_good_steps = 0
             if skipped:
                 return False
-        self.arena.step(inv, skip_flag if self.device.type == "cuda" else None)
+        self.arena.step(inv, skip_flag if self.device.type == "cuda" else None, inv_scale_dev=amp_inv)
         for w in self.weights:
             w.handle.bump()
         for cb in self.callbacks:

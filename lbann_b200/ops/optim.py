@@ -31,7 +31,7 @@ def _lib():
         lib.lb_fused_optimizer.restype = c_int
         lib.lb_fused_optimizer.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                            c_void_p, c_int, c_ll, c_float, c_void_p, c_void_p,
-                                           c_void_p, c_int, c_int, c_void_p]
+                                           c_void_p, c_void_p, c_int, c_int, c_void_p]
         lib.lb_unscale_check.restype = c_int
         lib.lb_unscale_check.argtypes = [c_void_p, c_ll, c_float, c_void_p, c_int, c_void_p, c_int, c_void_p]
         lib.lb_amp_update.restype = c_int
@@ -170,8 +170,10 @@ class ParameterArena:
             stage[1].record()
         return self._seg_dev
 
-    def step(self, inv_scale: float = 1.0, skip_flag: Optional[torch.Tensor] = None):
-        """Advance every slot's step counter and apply its optimizer."""
+    def step(self, inv_scale: float = 1.0, skip_flag: Optional[torch.Tensor] = None,
+             inv_scale_dev: Optional[torch.Tensor] = None):
+        """Advance every slot's step counter and apply its optimizer.  ``inv_scale_dev``: a
+        one-element fp32 CUDA tensor multiplied into the gradients as they are read."""
         for s in self.slots:
             if s.kind != "none":
                 s.step_count += 1
@@ -190,7 +192,7 @@ class ParameterArena:
                 self.master.data_ptr(), self.grad.data_ptr(), self.state0.data_ptr(),
                 s1.data_ptr(), native.ptr(self.compute), segs.data_ptr(), len(self.slots),
                 self.total, float(inv_scale), native.ptr(skip_flag), self.step_dev.data_ptr(),
-                self.lr_scale_dev.data_ptr(), native.dtype_code(self.grad.dtype),
+                self.lr_scale_dev.data_ptr(), native.ptr(inv_scale_dev), native.dtype_code(self.grad.dtype),
                 native.dtype_code(self.compute.dtype) if self.compute is not None else native.DT_BF16,
                 native.stream_ptr())
             native.check(rc, "lb_fused_optimizer")
