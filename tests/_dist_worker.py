@@ -347,7 +347,8 @@ def data_store(preload):
 def ltfb(strategy):
     """Two trainers of one rank each run LTFB tournaments on an MLP regression."""
     o = opts.reset()
-    o.set("disable_cuda", True)
+    if os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cpu":
+        o.set("disable_cuda", True)
     o.set("procs_per_trainer", 1)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))

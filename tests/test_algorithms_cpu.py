@@ -40,8 +40,10 @@ def _mlp():
                        objective_function=lbann.ObjectiveFunction([loss]))
 
 
-def _fit(algo, epochs=3):
-    opts.reset().set("disable_cuda", True)
+def _fit(algo, epochs=3, cuda=False):
+    o = opts.reset()
+    if not cuda:
+        o.set("disable_cuda", True)
     torch.manual_seed(0)
     exp = lbann.proto.serialize.build_experiment(
         trainer=lbann.Trainer(mini_batch_size=16, random_seed=9, training_algo=algo), model=_mlp(),

@@ -53,3 +53,15 @@ def test_partitioned_embedding_two_gpus(tmp_path):
     for a, b in zip(single["losses"], two["losses"]):
         assert abs(a - b) <= 1e-3 * max(1.0, abs(a)), (single["losses"], two["losses"])
     assert max(abs(a - b) for a, b in zip(single["table"], two["table"])) < 1e-3
+
+
+@needs2
+@pytest.mark.parametrize("strategy", ["sendrecv_weights", "checkpoint_binary"])
+def test_ltfb_two_trainers_on_gpus(tmp_path, strategy):
+    """Two single-GPU trainers run tournaments; the one that cannot learn ends up with the
+    learner's weights (weights travel GPU to GPU through the inter-trainer group)."""
+    res = _run(2, ["ltfb", strategy], str(tmp_path / "l.json"), ENV)
+    assert res["num_trainers"] == 2
+    a, b = res["weights"]
+    for k in a:
+        assert abs(a[k] - b[k]) <= 1e-4 * max(1.0, abs(a[k])), (strategy, k, a, b)
