@@ -36,6 +36,26 @@ def _build(lbann, args, world):
         opt = lbann.SGD(learn_rate=0.1, momentum=0.9)
         for w in []:
             pass
+    elif args.model == "unet3d":
+        # 3D U-Net with batch norm, per-voxel 3-class cross-entropy; with several ranks the
+        # depth dimension is split over them (strong scaling of one global mini-batch)
+        from lbann_b200.models import construct_unet3d_model
+        ps = lbann.get_parallel_strategy_args(depth_groups=world) if world > 1 else None
+        model = construct_unet3d_model(num_classes=3, base_channels=32, levels=4, parallel_strategy=ps)
+        v = args.volume
+        r = lbann.reader_pb2.Reader()
+        r.name, r.role, r.shuffle, r.fraction_of_data_to_use = "synthetic", "train", False, 1.0
+        r.synth_dimensions = f"1 {v} {v} {v}"
+        r.synth_response_dimensions = f"{v} {v} {v}"
+        r.synth_distribution = "samples:normal responses:randint:3"
+        r.num_samples = 2 * args.batch
+        r.synth_pool_size = 2 * args.batch
+        opt = lbann.Adam(learn_rate=1e-3, beta1=0.9, beta2=0.99, eps=1e-8)
+        dr = lbann.reader_pb2.DataReader()
+        dr.reader.append(r)
+        return lbann.proto.serialize.build_experiment(
+            trainer=lbann.Trainer(mini_batch_size=args.batch, random_seed=1), model=model,
+            data_reader=dr, optimizer=opt)
     else:
         from lbann_b200.models.transformer import construct_gpt_model
         model = construct_gpt_model(vocab_size=args.vocab, seq_len=args.seq, d_model=args.d_model,
@@ -93,7 +113,7 @@ def ours(args):
     status = native.consume_status(False)
     loss = float(m.last_objective)
     if rank == 0:
-        gb = args.batch * world
+        gb = args.batch if args.model == "unet3d" else args.batch * world
         out = {"model": args.model, "impl": "lbann_b200", "n_gpus": world, "global_batch": gb,
                "ms_per_step": round(ms, 3), "samples_per_s": round(gb / ms * 1e3, 2), "dtype": "bf16",
                "gpu_launches": native.launches() - n0, "loss": loss, "device_status": status,
@@ -207,10 +227,11 @@ def torch_arm(args):
 
 def main():
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--model", default="resnet50", choices=["resnet50", "gpt"])
+    ap.add_argument("--model", default="resnet50", choices=["resnet50", "gpt", "unet3d"])
     ap.add_argument("--impl", default="ours", choices=["ours", "torch"])
     ap.add_argument("--batch", type=int, default=64, help="per-GPU mini-batch")
     ap.add_argument("--image", type=int, default=224)
+    ap.add_argument("--volume", type=int, default=128, help="edge of the U-Net input volume")
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--d-model", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=16)
