@@ -138,6 +138,57 @@ __global__ void softmax_ce_bwd_kernel(const T* __restrict__ x, const long long* 
   }
 }
 
+// Short rows (a handful of classes per voxel, as in segmentation): one THREAD per row, so a
+// warp covers 32 consecutive rows and its loads are contiguous; the block-per-row kernels
+// above spend their time in two block reductions over three values.
+template <typename T>
+__global__ void softmax_ce_fwd_short_kernel(const T* __restrict__ x,
+                                            const long long* __restrict__ labels,
+                                            float* __restrict__ loss, float* __restrict__ lse_out,
+                                            long long rows, int cols) {
+  for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows;
+       r += (long long)gridDim.x * blockDim.x) {
+    const T* xr = x + r * cols;
+    float m = -INFINITY;
+    for (int c = 0; c < cols; ++c) m = fmaxf(m, to_f32<T>(xr[c]));
+    float s = 0.f;
+    for (int c = 0; c < cols; ++c) s += __expf(to_f32<T>(xr[c]) - m);
+    const float lse = m + logf(s);
+    lse_out[r] = lse;
+    const long long lab = labels[r];
+    loss[r] = (lab >= 0 && lab < cols) ? lse - to_f32<T>(xr[lab]) : 0.f;
+  }
+}
+
+template <typename T>
+__global__ void softmax_ce_bwd_short_kernel(const T* __restrict__ x,
+                                            const long long* __restrict__ labels,
+                                            const float* __restrict__ lse,
+                                            const float* __restrict__ dloss, float dloss_scalar,
+                                            T* __restrict__ dx, long long rows, int cols) {
+  for (long long r = (long long)blockIdx.x * blockDim.x + threadIdx.x; r < rows;
+       r += (long long)gridDim.x * blockDim.x) {
+    const T* xr = x + r * cols;
+    T* dr = dx + r * cols;
+    const long long lab = labels[r];
+    const bool ok = lab >= 0 && lab < cols;
+    const float g = ok ? (dloss ? dloss[r] : dloss_scalar) : 0.f;
+    const float l = lse[r];
+    for (int c = 0; c < cols; ++c) {
+      const float p = __expf(to_f32<T>(xr[c]) - l);
+      dr[c] = from_f32<T>(g * (p - (c == lab ? 1.f : 0.f)));
+    }
+  }
+}
+
+constexpr int kShortRowCols = 32;
+static int short_row_grid(long long rows) {
+  long long b = (rows + 255) / 256;
+  const long long cap = (long long)lbhost::sm_count() * 16;
+  if (b > cap) b = cap;
+  return (int)(b > 0 ? b : 1);
+}
+
 // Per-sample reductions of two inputs.  kind: 0 = CE on probabilities (-sum t*log(p), t>0),
 // 1 = MSE (mean of squared diff), 2 = MAE (mean abs diff), 3 = L1 norm of a, 4 = L2^2 of a.
 template <typename T>
@@ -248,6 +299,11 @@ int lb_softmax_ce_fwd(const void* x, const long long* labels, float* loss, float
                       long long rows, int cols, int dtype, void* stream_) {
   using namespace lb;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  if (cols <= kShortRowCols && rows >= 4096) {
+    LB_DISPATCH_ALL(dtype, (softmax_ce_fwd_short_kernel<T><<<short_row_grid(rows), 256, 0, s>>>(
+                               (const T*)x, labels, loss, lse, rows, cols)));
+    return (int)cudaGetLastError();
+  }
   LB_DISPATCH_ALL(dtype, (softmax_ce_fwd_kernel<T><<<row_grid(rows), row_threads(cols), 0, s>>>(
                              (const T*)x, labels, loss, lse, rows, cols)));
   return (int)cudaGetLastError();
@@ -257,6 +313,11 @@ int lb_softmax_ce_bwd(const void* x, const long long* labels, const float* lse, 
                       void* stream_) {
   using namespace lb;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  if (cols <= kShortRowCols && rows >= 4096) {
+    LB_DISPATCH_ALL(dtype, (softmax_ce_bwd_short_kernel<T><<<short_row_grid(rows), 256, 0, s>>>(
+                               (const T*)x, labels, lse, dloss, dloss_scalar, (T*)dx, rows, cols)));
+    return (int)cudaGetLastError();
+  }
   LB_DISPATCH_ALL(dtype, (softmax_ce_bwd_kernel<T><<<row_grid(rows), row_threads(cols), 0, s>>>(
                              (const T*)x, labels, lse, dloss, dloss_scalar, (T*)dx, rows, cols)));
   return (int)cudaGetLastError();

@@ -161,3 +161,25 @@ def test_short_batch_weight_gradient(rows, out_f, in_f, dt):
     nn._weight_grad(dy, x, grad)
     assert native.consume_status() == 0
     torch.testing.assert_close(grad, want, rtol=2e-3, atol=2e-3)
+
+
+@pytest.mark.parametrize("classes", [3, 7, 32])
+def test_softmax_cross_entropy_with_few_classes(classes):
+    """Per-voxel cross-entropy over a handful of classes (thread-per-row kernels) against
+    PyTorch fp32, with an out-of-range label giving a zero loss and a zero gradient row."""
+    torch.manual_seed(2)
+    rows = 8200
+    logits = torch.randn(rows, classes, device="cuda").bfloat16().requires_grad_(True)
+    labels = torch.randint(0, classes, (rows,), device="cuda")
+    labels[11] = classes + 4
+    loss = nn.softmax_cross_entropy(logits, labels)
+    assert native.consume_status() == 0
+    lr = logits.detach().float().requires_grad_(True)
+    ok = labels < classes
+    ref = F.cross_entropy(lr, labels.clamp(max=classes - 1), reduction="none") * ok
+    torch.testing.assert_close(loss, ref, rtol=1e-3, atol=1e-3)
+    w = torch.rand(rows, device="cuda")
+    (loss * w).sum().backward()
+    (ref * w).sum().backward()
+    torch.testing.assert_close(logits.grad.float(), lr.grad, rtol=2e-2, atol=2e-3)
+    assert float(logits.grad[11].abs().max()) == 0.0
