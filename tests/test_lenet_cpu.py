@@ -65,7 +65,7 @@ def test_lenet_trains_on_cpu(tmp_path):
 
 def test_cuda_graph_option_is_ignored_without_a_gpu():
     """use_cuda_graph on a CPU run: the model decides against capturing and trains step by
-    step; a callback that hooks into the step also switches capturing off."""
+    step."""
     from lbann_b200.exec.trainer import ExecTrainer
     from lbann_b200.utils import options as opts
     from test_models_cpu import _reader
