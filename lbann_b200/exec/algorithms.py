@@ -84,7 +84,16 @@ class SGDTrainingAlgorithm(TrainingAlgorithm):
         ctx.start_time = time.time()
         for cb in cbs:
             cb.on_train_begin(model)
+        # hierarchical wall-clock timers, printed at the end of the run with --verbose
+        # (src/execution_algorithms/sgd_training_algorithm.cpp:75-96)
+        from ..utils.profiling import TimerMap
+        timers = self.timers = TimerMap(self.name or "sgd")
+        epoch_scope = None
         while not term(ctx):
+            if epoch_scope is not None:
+                epoch_scope.__exit__(None, None, None)
+            epoch_scope = timers.scope("epoch")
+            epoch_scope.__enter__()
             model.reset_statistics("training")
             if not getattr(ctx, "_resume_mid_epoch", False):
                 dc.start_epoch("training")
@@ -98,7 +107,8 @@ class SGDTrainingAlgorithm(TrainingAlgorithm):
                 if batch is None:
                     finished_epoch = True
                     break
-                self.train_mini_batch(trainer, model, ctx, batch, cbs)
+                with timers.scope("mini-batch"):
+                    self.train_mini_batch(trainer, model, ctx, batch, cbs)
                 if batch.end_of_epoch:
                     finished_epoch = True
                     break
@@ -113,6 +123,11 @@ class SGDTrainingAlgorithm(TrainingAlgorithm):
             ctx.epoch += 1
             if dc.num_samples("validation"):
                 self.evaluate(trainer, model, "validation")
+        if epoch_scope is not None:
+            epoch_scope.__exit__(None, None, None)
+        from ..utils import options as _opts
+        if _opts.current().get_bool("verbose") and trainer.comm.am_world_master():
+            print(timers.report(), flush=True)
         for cb in cbs:
             cb.on_train_end(model)
 
