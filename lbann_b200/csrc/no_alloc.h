@@ -16,7 +16,7 @@ extern "C" {
 
 // Per-column sum and sum of squares of a row-major [rows][cols] matrix of 16-bit floats:
 //   out[c] = sum_r x[r][c],  out[cols + c] = sum_r x[r][c]^2      (fp32, OVERWRITTEN)
-// Same numbers as lb_bn_partial_sums(x, sums, rows, cols, 1, dtype, stream) writes into a
+// Same numbers as lb_bn_partial_sums(x, sums, rows, cols, 1, dtype, 1, stream) writes into a
 // zero-filled `sums`, but with no workspace argument and no allocation of any kind: the
 // partial sums accumulate in a file-scope __device__ array of
 // 2 * LB_COLUMN_SUMS_NOALLOC_MAX_COLS floats, which every call first clears on `stream`

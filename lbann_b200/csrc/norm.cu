@@ -164,7 +164,8 @@ __device__ __forceinline__ void reduce_over_y(float (&a)[8], float* sm) {
 // batch norm, = N for instance norm).  Threads: x -> 8-channel vectors, y -> row lanes.
 template <typename T>
 __global__ void bn_partial_sums_kernel(const T* __restrict__ x, float* __restrict__ sums,
-                                       long long rows, int C, long long rows_per_block) {
+                                       long long rows, int C, long long rows_per_block,
+                                       int replicas) {
   __shared__ float sm[256 * 8];
   const int cv = C / 8;
   const int v = blockIdx.x * blockDim.x + threadIdx.x;
@@ -177,8 +178,26 @@ __global__ void bn_partial_sums_kernel(const T* __restrict__ x, float* __restric
   for (int j = 0; j < 8; ++j) { s[j] = 0.f; ss[j] = 0.f; }
   const T* base = x + ((long long)grp * rows) * C + v * 8;
   if (valid) {
-#pragma unroll 4
-    for (long long r = r0 + threadIdx.y; r < r1; r += blockDim.y) {
+    // four rows' loads are issued before the first is used (the pass is a pure streaming
+    // read, so bytes in flight per thread are what sets its bandwidth)
+    const long long step = blockDim.y;
+    long long r = r0 + threadIdx.y;
+    for (; r + 3 * step < r1; r += 4 * step) {
+      uint4 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) q[u] = *reinterpret_cast<const uint4*>(base + (r + u * step) * C);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const T* e = reinterpret_cast<const T*>(&q[u]);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const float f = to_f32<T>(e[j]);
+          s[j] += f;
+          ss[j] += f * f;
+        }
+      }
+    }
+    for (; r < r1; r += step) {
       float f[8];
       ld8n<T>(base + r * C, f);
 #pragma unroll
@@ -188,7 +207,10 @@ __global__ void bn_partial_sums_kernel(const T* __restrict__ x, float* __restric
   reduce_over_y(s, sm);
   reduce_over_y(ss, sm);
   if (valid && threadIdx.y == 0) {
-    float* out = sums + (long long)grp * 2 * C;
+    // Hundreds of blocks add into the same few cache lines, and the L2 serialises atomics on
+    // a line (592 blocks x 32 floats per line cost 37 us on a 51 MB activation, four times the
+    // read itself): the blocks are spread over `replicas` copies that the caller sums.
+    float* out = sums + ((long long)(blockIdx.y % replicas) * gridDim.z + grp) * 2 * C;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       atomicAdd(out + v * 8 + j, s[j]);
@@ -295,7 +317,7 @@ __global__ void bn_bwd_sums_kernel(const T* __restrict__ x, const T* __restrict_
                                    const T* __restrict__ y, const float* __restrict__ stats,
                                    const float* __restrict__ scale, float* __restrict__ bsums,
                                    long long rows, int C, long long rows_per_block, float eps,
-                                   int act, float act_param) {
+                                   int act, float act_param, int replicas) {
   __shared__ float sm[256 * 8];
   const int cv = C / 8;
   const int v = blockIdx.x * blockDim.x + threadIdx.x;
@@ -334,7 +356,7 @@ __global__ void bn_bwd_sums_kernel(const T* __restrict__ x, const T* __restrict_
   reduce_over_y(s1, sm);
   reduce_over_y(s2, sm);
   if (valid && threadIdx.y == 0) {
-    float* out = bsums + (long long)grp * 4 * C;
+    float* out = bsums + ((long long)(blockIdx.y % replicas) * gridDim.z + grp) * 4 * C;
 #pragma unroll
     for (int j = 0; j < 8; ++j) {
       const int c = v * 8 + j;
@@ -462,14 +484,15 @@ int lb_layer_norm_bwd(const void* x, const void* dy, const float* scale, const f
 }
 
 // sums: fp32 [groups][2][C], must be zero on entry.  C % 8 == 0.
+// sums: fp32 [replicas][groups][2][C], zero on entry; the caller adds the replicas up.
 int lb_bn_partial_sums(const void* x, float* sums, long long rows, int C, int groups, int dtype,
-                       void* stream_) {
+                       int replicas, void* stream_) {
   using namespace lb;
   if (C % 8) return -1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   BnLaunch l = bn_shape(rows, C, groups);
   LB_DISPATCH_16(dtype, (bn_partial_sums_kernel<T><<<l.grid, l.block, 0, s>>>(
-                            (const T*)x, sums, rows, C, l.rows_per_block)));
+                            (const T*)x, sums, rows, C, l.rows_per_block, replicas < 1 ? 1 : replicas)));
   return (int)cudaGetLastError();
 }
 
@@ -500,17 +523,17 @@ int lb_bn_apply_fixed(const void* x, const float* mean, const float* var, const 
   return (int)cudaGetLastError();
 }
 
-// bsums: fp32 [groups][4][C], zero on entry.
+// bsums: fp32 [replicas][groups][4][C], zero on entry; the caller adds the replicas up.
 int lb_bn_bwd_sums(const void* x, const void* dy, const void* y, const float* stats,
                    const float* scale, float* bsums, long long rows, int C, int groups, float eps,
-                   int act, float act_param, int dtype, void* stream_) {
+                   int act, float act_param, int dtype, int replicas, void* stream_) {
   using namespace lb;
   if (C % 8) return -1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   BnLaunch l = bn_shape(rows, C, groups);
   LB_DISPATCH_16(dtype, (bn_bwd_sums_kernel<T><<<l.grid, l.block, 0, s>>>(
                             (const T*)x, (const T*)dy, (const T*)y, stats, scale, bsums, rows, C,
-                            l.rows_per_block, eps, act, act_param)));
+                            l.rows_per_block, eps, act, act_param, replicas < 1 ? 1 : replicas)));
   return (int)cudaGetLastError();
 }
 

@@ -42,7 +42,7 @@ def _lib():
         lib.lb_layer_norm_bwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                           c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p]
         lib.lb_bn_partial_sums.restype = c_int
-        lib.lb_bn_partial_sums.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_void_p]
+        lib.lb_bn_partial_sums.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p]
         lib.lb_pack_filter.restype = c_int
         lib.lb_pack_filter.argtypes = [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                        c_int, c_void_p]
@@ -59,7 +59,7 @@ def _lib():
                                           c_ll, c_int, c_float, c_int, c_float, c_int, c_void_p]
         lib.lb_bn_bwd_sums.restype = c_int
         lib.lb_bn_bwd_sums.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                       c_ll, c_int, c_int, c_float, c_int, c_float, c_int, c_void_p]
+                                       c_ll, c_int, c_int, c_float, c_int, c_float, c_int, c_int, c_void_p]
         lib.lb_bn_bwd_apply.restype = c_int
         lib.lb_bn_bwd_apply.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                         c_void_p, c_ll, c_int, c_int, c_float, c_float, c_float,
@@ -144,13 +144,20 @@ def column_sums(x2d: torch.Tensor) -> torch.Tensor:
     """fp32 sum over rows of a [rows, C] 16-bit CUDA tensor (native when C % 8 == 0)."""
     rows, C = x2d.shape
     if _native_ok(x2d) and C % 8 == 0 and x2d.is_contiguous() and rows > 0:
-        sums = torch.zeros(2 * C, dtype=torch.float32, device=x2d.device)
+        reps = _bn_replicas(rows)
+        sums = torch.zeros(reps, 2 * C, dtype=torch.float32, device=x2d.device)
         rc = _lib().lb_bn_partial_sums(x2d.data_ptr(), sums.data_ptr(), rows, C, 1,
-                                       native.dtype_code(x2d.dtype), native.stream_ptr())
+                                       native.dtype_code(x2d.dtype), reps, native.stream_ptr())
         native.check(rc, "lb_bn_partial_sums")
         native.count_launch()
-        return sums[:C]
+        return (sums.sum(0) if reps > 1 else sums[0])[:C]
     return x2d.float().sum(0)
+
+
+def _bn_replicas(rows: int) -> int:
+    """Copies of the partial-sum buffer that the reduction kernels spread their atomics over
+    (the caller adds them up): the L2 serialises atomics on one cache line."""
+    return 16 if rows >= 8192 else 1
 
 
 def _act_grad_from_output(y: torch.Tensor, dy: torch.Tensor, act: int, p: float) -> torch.Tensor:
@@ -605,9 +612,11 @@ class _BatchNorm(torch.autograd.Function):
         rows = x_cl.numel() // C
         lib = _lib()
         dt = native.dtype_code(x.dtype)
-        sums = torch.zeros(2 * C, dtype=torch.float32, device=x.device)
-        native.check(lib.lb_bn_partial_sums(x_cl.data_ptr(), sums.data_ptr(), rows, C, 1, dt,
+        reps = _bn_replicas(rows)
+        sums = torch.zeros(reps, 2 * C, dtype=torch.float32, device=x.device)
+        native.check(lib.lb_bn_partial_sums(x_cl.data_ptr(), sums.data_ptr(), rows, C, 1, dt, reps,
                                             native.stream_ptr()), "lb_bn_partial_sums")
+        sums = sums.sum(0) if reps > 1 else sums[0]
         if reduce_fn is not None:
             reduce_fn(sums)
         count = float(rows * count_scale)
@@ -636,12 +645,14 @@ class _BatchNorm(torch.autograd.Function):
         rows = x_cl.numel() // C
         lib = _lib()
         dt = native.dtype_code(x_cl.dtype)
-        bsums = torch.zeros(4 * C, dtype=torch.float32, device=x_cl.device)
+        reps = _bn_replicas(rows)
+        bsums = torch.zeros(reps, 4 * C, dtype=torch.float32, device=x_cl.device)
         scale = sh.master.detach() if sh is not None else None
         native.check(lib.lb_bn_bwd_sums(x_cl.data_ptr(), dy_cl.data_ptr(), native.ptr(y),
                                         stats.data_ptr(), native.ptr(scale), bsums.data_ptr(),
-                                        rows, C, 1, float(eps), act, float(act_p), dt,
+                                        rows, C, 1, float(eps), act, float(act_p), dt, reps,
                                         native.stream_ptr()), "lb_bn_bwd_sums")
+        bsums = bsums.sum(0) if reps > 1 else bsums[0]
         # parameter gradients use the local partial sums (the optimizer's allreduce sums ranks)
         if sh is not None and sh.grad is not None:
             sh.grad.add_(bsums[:C])

@@ -19,7 +19,7 @@ def _symbols():
     fn.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_void_p]
     ref = lib.lb_bn_partial_sums
     ref.restype = c_int
-    ref.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_void_p]
+    ref.argtypes = [c_void_p, c_void_p, c_ll, c_int, c_int, c_int, c_int, c_void_p]
     return fn, ref
 
 
@@ -35,7 +35,7 @@ def test_two_calls_in_a_row_match_existing_entry_point(dtype):
         out = torch.full((2 * cols,), float("nan"), dtype=torch.float32, device="cuda")
         assert fn(x.data_ptr(), out.data_ptr(), rows, cols, code, stream) == 0
         want = torch.zeros(2 * cols, dtype=torch.float32, device="cuda")
-        assert ref(x.data_ptr(), want.data_ptr(), rows, cols, 1, code, stream) == 0
+        assert ref(x.data_ptr(), want.data_ptr(), rows, cols, 1, code, 1, stream) == 0
         torch.cuda.synchronize()
         torch.testing.assert_close(out, want, rtol=1e-4, atol=1e-2)
         xf = x.float()
