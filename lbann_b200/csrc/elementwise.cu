@@ -21,7 +21,7 @@ enum UnaryOp : int {
 enum BinaryOp : int {
   B_ADD = 0, B_SUB, B_MUL, B_DIV, B_MOD, B_POW, B_SAFE_DIV, B_SQ_DIFF, B_MAX, B_MIN, B_EQ, B_NE,
   B_LT, B_LE, B_GT, B_GE, B_AND, B_OR, B_XOR, B_BCE, B_SIGMOID_BCE, B_BOOL_ACC, B_BOOL_FN,
-  B_BOOL_FP, B_COUNT
+  B_BOOL_FP, B_ADD_RELU, B_COUNT
 };
 
 __device__ __forceinline__ float unary_fwd(int op, float x, float p0, float p1) {
@@ -186,6 +186,7 @@ __device__ __forceinline__ float binary_fwd(int op, float a, float b) {
     case B_BOOL_ACC: return ((a >= 0.5f) == (b >= 0.5f)) ? 1.f : 0.f;
     case B_BOOL_FN: return (!(a >= 0.5f) && (b >= 0.5f)) ? 1.f : 0.f;
     case B_BOOL_FP: return ((a >= 0.5f) && !(b >= 0.5f)) ? 1.f : 0.f;
+    case B_ADD_RELU: return fmaxf(a + b, 0.f);      // residual addition + ReLU in one pass
     default: return 0.f;
   }
 }
@@ -195,6 +196,7 @@ __device__ __forceinline__ void binary_bwd(int op, float a, float b, float dy, f
   da = 0.f; db = 0.f;
   switch (op) {
     case B_ADD: da = dy; db = dy; break;
+    case B_ADD_RELU: da = (a + b) > 0.f ? dy : 0.f; db = da; break;
     case B_SUB: da = dy; db = -dy; break;
     case B_MUL: da = dy * b; db = dy * a; break;
     case B_DIV: da = dy / b; db = -dy * a / (b * b); break;

@@ -780,6 +780,9 @@ class OperatorLayer(ExecLayer):
                     else:
                         b = b.expand(torch.broadcast_shapes(a.shape, b.shape))
                     a, b = a.contiguous(), b.to(a.dtype).contiguous()
+            if (short == "add" and len(self.ops) == 1
+                    and getattr(self, "fused_act", (native.ACT_NONE, 0.0))[0] == native.ACT_RELU):
+                return ew.add_relu(a, b.to(a.dtype))      # the ReLU that follows is folded in
             return ew.binary(short, a, b.to(a.dtype))
         if short == "clamp":
             return ew.unary("clamp", xs[0], float(msg.min), float(msg.max))

@@ -15,7 +15,7 @@ from typing import List
 import torch
 import torch.nn.functional as F
 
-from ..ops import nn
+from ..ops import native, nn
 from ..ops import elementwise as ew
 from ..ops.gemm import gemm
 from .layer_base import ExecLayer, broadcast_list, prod, register
@@ -64,8 +64,15 @@ class Sum(ExecLayer):
     def forward(self, xs, training):
         xs = [self.cast_in(x) for x in xs]
         out = xs[0]
-        for x in xs[1:]:
-            out = ew.binary("add", out, x.reshape(out.shape))
+        relu = getattr(self, "fused_act", (native.ACT_NONE, 0.0))[0] == native.ACT_RELU
+        for k, x in enumerate(xs[1:]):
+            if relu and k == len(xs) - 2:        # the ReLU that follows rides on the last addition
+                out = ew.add_relu(out, x.reshape(out.shape))
+                relu = False
+            else:
+                out = ew.binary("add", out, x.reshape(out.shape))
+        if relu:
+            out = torch.relu(out)
         return [out]
 
 

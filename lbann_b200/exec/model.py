@@ -287,11 +287,15 @@ class ExecModel:
                                                             if getattr(m, "layer_name", None)}
         for l in self.layers:
             if l.type not in ("convolution", "fully_connected", "batch_normalization",
-                              "channelwise_fully_connected"):
+                              "channelwise_fully_connected", "sum", "operator_layer"):
+                continue
+            if l.type == "operator_layer" and [o for o, _ in getattr(l, "ops", [])] != ["add"]:
                 continue
             if len(l.children) != 1 or l.name in protected:
                 continue
             c = l.children[0]
+            if l.type in ("sum", "operator_layer") and (c.type != "relu" or len(l.parent_names) < 2):
+                continue          # residual addition: only a plain ReLU is folded in
             if c.type == "relu":
                 act = (native.ACT_RELU, 0.0)
             elif c.type == "leaky_relu":

@@ -26,7 +26,7 @@ BINARY = ["add", "subtract", "multiply", "divide", "mod", "pow", "safe_divide",
           "squared_difference", "max", "min", "equal", "not_equal", "less", "less_equal",
           "greater", "greater_equal", "logical_and", "logical_or", "logical_xor",
           "binary_cross_entropy", "sigmoid_binary_cross_entropy", "boolean_accuracy",
-          "boolean_false_negative", "boolean_false_positive"]
+          "boolean_false_negative", "boolean_false_positive", "add_relu"]
 UNARY_CODE = {n: i for i, n in enumerate(UNARY)}
 BINARY_CODE = {n: i for i, n in enumerate(BINARY)}
 
@@ -199,6 +199,8 @@ class _Binary(torch.autograd.Function):
     @staticmethod
     def backward(ctx, dy):
         a, b = ctx.saved_tensors
+        if ctx.code == BINARY_CODE["add"]:
+            return dy, dy, None          # no kernel, no copies
         if dy.stride() != a.stride():
             dy = torch.empty_like(a).copy_(dy)
         da, db = torch.empty_like(a), torch.empty_like(a)
@@ -208,6 +210,37 @@ class _Binary(torch.autograd.Function):
         native.check(rc, "lb_binary")
         native.count_launch()
         return da, db, None
+
+
+class _AddRelu(torch.autograd.Function):
+    """relu(a + b) in one kernel; backward is one masking pass on the saved output and both
+    inputs receive the same gradient tensor."""
+
+    @staticmethod
+    def forward(ctx, a, b):
+        out = torch.empty_like(a)
+        rc = _lib().lb_binary(a.data_ptr(), b.data_ptr(), 0, out.data_ptr(), 0, a.numel(),
+                              BINARY_CODE["add_relu"], 0, native.dtype_code(a.dtype), native.stream_ptr())
+        native.check(rc, "lb_binary")
+        native.count_launch()
+        ctx.save_for_backward(out)
+        return out
+
+    @staticmethod
+    def backward(ctx, dy):
+        (out,) = ctx.saved_tensors
+        if dy.stride() != out.stride():
+            dy = torch.empty_like(out).copy_(dy)
+        g = unary_raw(UNARY_CODE["relu"], out, dy, 0.0, 0.0, 1)
+        return g, g
+
+
+def add_relu(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """relu(a + b); one native kernel each way for dense same-layout CUDA tensors."""
+    if (a.is_cuda and a.dtype in _NATIVE_DTYPES and a.dtype == b.dtype and a.shape == b.shape
+            and a.stride() == b.stride() and _dense(a) and a.numel() > 0):
+        return _AddRelu.apply(a, b)
+    return torch.relu(a + b)
 
 
 _NATIVE_DTYPES = (torch.float32, torch.bfloat16, torch.float16)

@@ -183,3 +183,30 @@ def test_softmax_cross_entropy_with_few_classes(classes):
     (ref * w).sum().backward()
     torch.testing.assert_close(logits.grad.float(), lr.grad, rtol=2e-2, atol=2e-3)
     assert float(logits.grad[11].abs().max()) == 0.0
+
+
+def test_add_relu_fused_kernel():
+    """relu(a + b) in one kernel, gradient masked by the saved output and shared by both
+    inputs; plain add passes its gradient through without a kernel."""
+    from lbann_b200.ops import elementwise as ew
+    torch.manual_seed(4)
+    a = torch.randn(4, 16, 8, 8, device="cuda").bfloat16().requires_grad_(True)
+    b = torch.randn(4, 16, 8, 8, device="cuda").bfloat16().requires_grad_(True)
+    ar, br = a.detach().float().requires_grad_(True), b.detach().float().requires_grad_(True)
+    y = ew.add_relu(a, b)
+    ref = torch.relu((ar + br).bfloat16().float())
+    torch.testing.assert_close(y.float(), ref, rtol=1e-2, atol=1e-2)
+    g = torch.randn_like(y)
+    y.backward(g)
+    torch.relu(ar + br).backward(g.float())
+    torch.testing.assert_close(a.grad.float(), ar.grad, rtol=1e-2, atol=1e-2)
+    torch.testing.assert_close(b.grad.float(), br.grad, rtol=1e-2, atol=1e-2)
+    n0 = native.launches()
+    c = torch.randn_like(a).requires_grad_(True)
+    d = torch.randn_like(a).requires_grad_(True)
+    s = ew.binary("add", c, d)
+    n1 = native.launches()
+    s.backward(g)
+    assert native.launches() == n1 and n1 == n0 + 1
+    torch.testing.assert_close(c.grad, g)
+    assert native.consume_status() == 0
