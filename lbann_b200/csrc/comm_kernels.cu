@@ -122,6 +122,60 @@ allreduce_two_shot_kernel(PeerPtrs pp, int rank, int world, long long n, float s
 }
 
 // ---------------------------------------------------------------------------------
+// Reduce-scatter (sum) of a range of an arena whose chunks are OWNED block-cyclically:
+// blocks of `own_elems` elements are dealt round-robin, block b belongs to rank b % world
+// (the layout of the sharded optimizer, csrc/optim.cu).  Rank r sums, for every block it owns
+// inside [e0, e1), the values of all ranks (peer loads over NVLink) and keeps the scaled sum
+// in its own buffer; nothing is written to a peer.  The opening rendezvous tells that every
+// rank's gradients of the range are complete; the kernel has no closing one - the caller
+// keeps the ranks from overwriting their gradients until a later rendezvous of the step
+// (the one before the updated weights are used).
+template <typename T>
+__global__ void __launch_bounds__(512)
+reduce_scatter_owned_kernel(PeerPtrs pp, int rank, int world, long long e0, long long e1,
+                            long long own_elems, float scale, uint32_t* ctr, int* status) {
+  constexpr int V = 16 / sizeof(T);
+  __shared__ const T* src[kMaxRanks];      // peers in staggered order (dynamic index: shared, not local)
+  if ((int)threadIdx.x < world)
+    src[threadIdx.x] = reinterpret_cast<const T*>(pp.buf[(rank + threadIdx.x) % world]);
+  if (!block_rendezvous(pp, rank, world, 0, ctr, status)) return;
+  const long long b_first = e0 / own_elems, b_end = (e1 + own_elems - 1) / own_elems;
+  long long ob = b_first + (((long long)rank - b_first % world) + world) % world;  // first owned block
+  if (ob >= b_end) return;
+  const long long nob = (b_end - ob + world - 1) / world;
+  const long long vpb = own_elems / V;
+  const long long total = nob * vpb;
+  T* mine = const_cast<T*>(src[0]);
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long k = idx / vpb, v = idx - k * vpb;
+    const long long i = (ob + k * world) * own_elems + v * V;
+    if (i < e0 || i + V > e1) continue;
+    uint4 part[kMaxRanks];
+#pragma unroll
+    for (int p = 0; p < kMaxRanks; ++p) {
+      if (p >= world) break;
+      part[p] = *reinterpret_cast<const uint4*>(src[p] + i);   // src[0] is this rank's own buffer
+    }
+    float acc[V];
+#pragma unroll
+    for (int j = 0; j < V; ++j) acc[j] = 0.f;
+#pragma unroll
+    for (int p = 0; p < kMaxRanks; ++p) {
+      if (p >= world) break;
+      const T* e = reinterpret_cast<const T*>(&part[p]);
+#pragma unroll
+      for (int j = 0; j < V; ++j) acc[j] += to_f32<T>(e[j]);
+    }
+    uint4 o;
+    T* e = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < V; ++j) e[j] = from_f32<T>(acc[j] * scale);
+    *reinterpret_cast<uint4*>(mine + i) = o;
+  }
+}
+
+// ---------------------------------------------------------------------------------
 // One-shot all-reduce for short vectors (batch-norm statistics, scalars, flags):
 // every rank pushes its vector into slot[rank] of every peer's staging buffer, then sums
 // the `world` slots locally into `out`.  staging: [world][n] fp32 in the symmetric buffer.
@@ -359,6 +413,9 @@ int lb_allreduce_two_shot(void* const* bufs, void* const* pads, int rank, int wo
                           float scale, unsigned* ctr, int dtype, int blocks, void* stream_) {
   using namespace lb;
   if (world < 1 || world > kMaxRanks || n <= 0) return -1;
+  // the kernel moves 16-byte vectors at bufs[r] + i: a misaligned base would fault on the device
+  for (int r = 0; r < world; ++r)
+    if (reinterpret_cast<uintptr_t>(bufs[r]) & 15) return -1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   PeerPtrs pp = make_ptrs(bufs, pads, world);
   if (blocks < 1) blocks = 1;
@@ -369,6 +426,31 @@ int lb_allreduce_two_shot(void* const* bufs, void* const* pads, int rank, int wo
     allreduce_two_shot_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(pp, rank, world, n, scale, ctr, lbhost::status_word());
   else
     allreduce_two_shot_kernel<__half><<<blocks, 512, 0, s>>>(pp, rank, world, n, scale, ctr, lbhost::status_word());
+  return (int)cudaGetLastError();
+}
+
+// Reduce-scatter of elements [e0, e1) of the symmetric buffers `bufs` with block-cyclic
+// ownership (see reduce_scatter_owned_kernel).  e0, e1 and own_elems are element counts and
+// multiples of one 16-byte vector; every base address is 16-byte aligned.
+int lb_reduce_scatter_owned(void* const* bufs, void* const* pads, int rank, int world,
+                            long long e0, long long e1, long long own_elems, float scale,
+                            unsigned* ctr, int dtype, int blocks, void* stream_) {
+  using namespace lb;
+  if (world < 2 || world > kMaxRanks || e1 <= e0 || own_elems <= 0) return -1;
+  const int v = dtype == kF32 ? 4 : 8;
+  if (e0 % v || e1 % v || own_elems % v) return -1;
+  for (int r = 0; r < world; ++r)
+    if (reinterpret_cast<uintptr_t>(bufs[r]) & 15) return -1;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  PeerPtrs pp = make_ptrs(bufs, pads, world);
+  if (blocks < 1) blocks = 1;
+  if (blocks > kCommBlocks) blocks = kCommBlocks;
+  if (dtype == kF32)
+    reduce_scatter_owned_kernel<float><<<blocks, 512, 0, s>>>(pp, rank, world, e0, e1, own_elems, scale, ctr, lbhost::status_word());
+  else if (dtype == kBF16)
+    reduce_scatter_owned_kernel<__nv_bfloat16><<<blocks, 512, 0, s>>>(pp, rank, world, e0, e1, own_elems, scale, ctr, lbhost::status_word());
+  else
+    reduce_scatter_owned_kernel<__half><<<blocks, 512, 0, s>>>(pp, rank, world, e0, e1, own_elems, scale, ctr, lbhost::status_word());
   return (int)cudaGetLastError();
 }
 

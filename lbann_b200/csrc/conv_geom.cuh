@@ -19,4 +19,4 @@ struct ConvGeom {
 extern "C" int lb_conv_slab_fwd(const void* x, const void* w, void* y, const float* bias,
                                 const int* geom, const long long* xs, const long long* ys,
                                 int in_dtype, int out_dtype, float alpha, float beta, int act,
-                                float act_param, void* stream_);
+                                float act_param, const void* halo, void* stream_);

@@ -19,6 +19,7 @@
 // transposed filter and padding k - 1 - pad), like the kernel it stands in for.
 // Reference counterpart: the cuDNN calls of src/layers/learning/base_convolution.cpp:462-814.
 #include "conv_geom.cuh"
+#include "halo_sync.cuh"
 #include "tc_pipeline.cuh"
 
 namespace lb {
@@ -34,6 +35,7 @@ struct SlabParams {
   int in_dtype;
   long long o_sn, o_sd, o_sh, o_sw;
   EpiParams epi;
+  HaloSync hs;                // halo exchange with the depth neighbours inside this kernel
 };
 
 struct SlabShared {
@@ -86,6 +88,15 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = sh.tmem_base;
+  const HaloSync& hs = p.hs;
+
+  if (hs.enabled && warp < 4) {
+    // the epilogue warps have nothing to do until the first accumulator is complete: they
+    // send this rank's boundary planes to the neighbours meanwhile
+    halo_push(hs, threadIdx.x, 128, blockIdx.x, gridDim.x);
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (threadIdx.x == 0) halo_signal(hs);
+  }
 
   if (warp == 4) {
     if (lane == 0) {
@@ -96,12 +107,26 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         tma_load_3d(s_filter + j * (p.filter_bytes / p.cblocks), &tmW, fbar, j * p.Cb, 0, 0);
       uint32_t it = 0;
       bool ok = true;
+      // halo planes: input planes [0, h) come from the rank above, [h + dl, dl + 2h) from below
+      const uint32_t halo_target =
+          hs.enabled ? (*reinterpret_cast<volatile uint32_t*>(hs.local) + 1u) * gridDim.x : 0u;
+      bool top_ok = !hs.enabled || hs.top_flag == nullptr;
+      bool bot_ok = !hs.enabled || hs.bot_flag == nullptr;
       for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
         int r = t;
         const int ti = r % p.tiles_plane; r /= p.tiles_plane;
-        const int d = r % g.Do, n = r / g.Do;
+        const int d = hs.enabled ? halo_rotate(r % g.Do, g.Do) : r % g.Do, n = r / g.Do;
         const int l0 = (ti * 128) / p.Wp;
         for (int a = 0; a < g.kd && ok; ++a) {
+          const int plane_in = d - g.pd + a;
+          if (!top_ok && plane_in < hs.h) {
+            top_ok = halo_wait(hs.top_flag, halo_target, status, abort_flag);
+            if (!top_ok) { ok = false; break; }
+          }
+          if (!bot_ok && plane_in >= hs.h + hs.dl) {
+            bot_ok = halo_wait(hs.bot_flag, halo_target, status, abort_flag);
+            if (!bot_ok) { ok = false; break; }
+          }
           for (int j = 0; j < p.cblocks; ++j, ++it) {
             const uint32_t s = it % S, ph = (it / S) & 1;
             if (!mbar_wait_bounded(smem_u32(&sh.empty[s]), ph ^ 1, abort_flag)) {
@@ -182,7 +207,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++lt) {
       int r = t;
       const int ti = r % p.tiles_plane; r /= p.tiles_plane;
-      const int d = r % g.Do, n = r / g.Do;
+      const int d = hs.enabled ? halo_rotate(r % g.Do, g.Do) : r % g.Do, n = r / g.Do;
       const uint32_t acc = lt & 1, acc_ph = (lt >> 1) & 1;
       const bool landed = __all_sync(
           0xffffffffu, mbar_wait_bounded(smem_u32(&sh.tmem_full[acc]), acc_ph, abort_flag));
@@ -204,6 +229,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   }
   tc_fence_before();
   __syncthreads();
+  if (hs.enabled && threadIdx.x == 0) halo_finish(hs, gridDim.x);
   if (warp == 5) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 2 * BN < 32 ? 32 : 2 * BN);
@@ -228,7 +254,7 @@ static int launch_slab(const CUtensorMap& tmX, const CUtensorMap& tmW, const Sla
 extern "C" int lb_conv_slab_fwd(const void* x, const void* w, void* y, const float* bias,
                                 const int* geom, const long long* xs, const long long* ys,
                                 int in_dtype, int out_dtype, float alpha, float beta, int act,
-                                float act_param, void* stream_) {
+                                float act_param, const void* halo, void* stream_) {
   using namespace lb;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   SlabParams p;
@@ -263,6 +289,10 @@ extern "C" int lb_conv_slab_fwd(const void* x, const void* w, void* y, const flo
   p.epi.C = y; p.epi.bias = bias; p.epi.alpha = alpha; p.epi.beta = beta;
   p.epi.out_dtype = out_dtype; p.epi.bias_mode = bias ? 1 : 0; p.epi.act = act;
   p.epi.act_param = act_param; p.epi.ldc = ys[3];
+  if (halo && (g.pd != 0 || xs[2] != (long long)g.W * g.C || xs[3] != g.C)) return -1;
+  if (!make_halo_sync(p.hs, reinterpret_cast<const HaloSyncArgs*>(halo), x, g.N, g.D,
+                      (long long)g.H * g.W * g.C * 2, xs[0] * 2)) return -1;
+  if (halo && xs[1] != (long long)g.H * g.W * g.C) return -1;
 
   CUtensorMap tmX, tmW;
   {

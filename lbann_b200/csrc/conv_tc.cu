@@ -30,10 +30,19 @@ struct ConvFwdPolicy {
     int num_tiles, k_iters, in_dtype;
     long long o_sn, o_sd, o_sh, o_sw;  // output strides in elements
     EpiParams epi;
+    HaloSync hs;                       // halo exchange with the depth neighbours (distconv)
   };
   struct Tile {
     int n0, d0, h0, w0, col0;
   };
+  using HasHalo = void;
+  __device__ static const HaloSync& halo(const Params& p) { return p.hs; }
+  __device__ static int tile_halo(const Params& p, const Tile& tl) {
+    // input planes of the brick: [d0 * sd - pd, (d0 + TD - 1) * sd - pd + (kd - 1) * dd]
+    const int lo = tl.d0 * p.g.sd - p.g.pd;
+    const int hi = (tl.d0 + p.TD - 1) * p.g.sd - p.g.pd + (p.g.kd - 1) * p.g.dd;
+    return (lo < (int)p.hs.h ? 1 : 0) | (hi >= (int)(p.hs.h + p.hs.dl) ? 2 : 0);
+  }
 
   __device__ static Tile decode(const Params& p, int t) {
     Tile tl;
@@ -41,7 +50,8 @@ struct ConvFwdPolicy {
     const int cb = r % p.tiles_col; r /= p.tiles_col;
     const int tw = r % p.tiles_w;   r /= p.tiles_w;
     const int th = r % p.tiles_h;   r /= p.tiles_h;
-    const int td = r % p.tiles_d;   r /= p.tiles_d;
+    int td = r % p.tiles_d;         r /= p.tiles_d;
+    if (p.hs.enabled) td = halo_rotate(td, p.tiles_d);   // the brick that needs the top halo goes last
     tl.col0 = cb * BN;
     tl.w0 = tw * p.TW; tl.h0 = th * p.TH; tl.d0 = td * p.TD; tl.n0 = r * p.TN;
     return tl;
@@ -146,9 +156,26 @@ extern "C" {
 //   w: [taps][Kout][C] contiguous, same dtype as x
 //   y: [N][Do][Ho][Wo][Kout] with element strides (ys_*), Kout contiguous (ldc = ys_w)
 // geom: 21 ints = N D H W C Do Ho Wo Kout kd kh kw pd ph pw sd sh sw dd dh dw
+int lb_conv_fwd_halo_tc(const void* x, const void* w, void* y, const float* bias, const int* geom,
+                        const long long* xs, const long long* ys, int in_dtype, int out_dtype,
+                        float alpha, float beta, int act, float act_param, const void* halo,
+                        void* stream_);
+
 int lb_conv_fwd_tc(const void* x, const void* w, void* y, const float* bias, const int* geom,
                    const long long* xs, const long long* ys, int in_dtype, int out_dtype,
                    float alpha, float beta, int act, float act_param, void* stream_) {
+  return lb_conv_fwd_halo_tc(x, w, y, bias, geom, xs, ys, in_dtype, out_dtype, alpha, beta, act,
+                             act_param, nullptr, stream_);
+}
+
+// `halo` (optional): a HaloSyncArgs.  x is then this rank's extended tensor
+// [N][Dl + 2h][H][W][C] in symmetric memory (dense planes, pd == 0): the kernel sends the
+// boundary planes to the depth neighbours itself and waits for theirs before the first tile
+// that reads a halo plane.
+int lb_conv_fwd_halo_tc(const void* x, const void* w, void* y, const float* bias, const int* geom,
+                        const long long* xs, const long long* ys, int in_dtype, int out_dtype,
+                        float alpha, float beta, int act, float act_param, const void* halo,
+                        void* stream_) {
   using namespace lb;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   ConvGeom g;
@@ -163,7 +190,7 @@ int lb_conv_fwd_tc(const void* x, const void* w, void* y, const float* bias, con
   // kernel: one TMA box per (tile, filter plane) instead of one per tap.
   {
     const int rc = lb_conv_slab_fwd(x, w, y, bias, geom, xs, ys, in_dtype, out_dtype, alpha, beta,
-                                    act, act_param, stream_);
+                                    act, act_param, halo, stream_);
     if (rc != -2) return rc;
   }
 
@@ -174,6 +201,12 @@ int lb_conv_fwd_tc(const void* x, const void* w, void* y, const float* bias, con
   const int TN = largest_tile(g.N, 128 / (TW * TH * TD));
   const uint32_t bw = (TW - 1) * g.sw + 1, bh = (TH - 1) * g.sh + 1, bd = (TD - 1) * g.sd + 1;
   if (bw > 256 || bh > 256 || bd > 256) return -1;
+
+  HaloSync hsync;
+  if (halo && (g.pd != 0 || xs[3] != g.C || xs[2] != (long long)g.W * g.C ||
+               xs[1] != (long long)g.H * g.W * g.C)) return -1;
+  if (!make_halo_sync(hsync, reinterpret_cast<const HaloSyncArgs*>(halo), x, g.N, g.D,
+                      (long long)g.H * g.W * g.C * 2, xs[0] * 2)) return -1;
 
   CUtensorMap tmA, tmB;
   {
@@ -208,6 +241,7 @@ int lb_conv_fwd_tc(const void* x, const void* w, void* y, const float* bias, con
     p.epi.C = y; p.epi.bias = bias; p.epi.alpha = alpha; p.epi.beta = beta;              \
     p.epi.out_dtype = out_dtype; p.epi.bias_mode = bias ? 1 : 0; p.epi.act = act;        \
     p.epi.act_param = act_param; p.epi.ldc = ys[3];                                      \
+    p.hs = hsync;                                                                        \
     return launch_conv<BN_>(tmA, tmB, p, stream);                                        \
   }
   if (BN == 256) LB_LAUNCH(256)

@@ -116,15 +116,182 @@ __global__ void fused_optimizer_kernel(float* __restrict__ w, const G* __restric
   }
 }
 
+
+// ---------------------------------------------------------------------------------
+// One element of any of the update rules above; s0 / s1 are updated in place.
+__device__ __forceinline__ float opt_update_one(const OptSegment& sg, float x, float g, float& s0,
+                                                float& s1) {
+  if (sg.l2 != 0.f) g += sg.l2 * x;
+  if (sg.kind == kOptSgd) {
+    if (sg.p0 != 0.f) {
+      const float v = sg.p0 * s0 + g;
+      s0 = v;
+      x -= sg.lr * (sg.nesterov ? (sg.p0 * v + g) : v);
+    } else {
+      x -= sg.lr * g;
+    }
+  } else if (sg.kind == kOptAdam) {
+    if (isfinite(g)) {
+      const float m1 = sg.p0 * s0 + (1.f - sg.p0) * g;
+      const float m2 = sg.p1 * s1 + (1.f - sg.p1) * g * g;
+      s0 = m1; s1 = m2;
+      x -= sg.corr * (m1 / (sqrtf(m2) + sg.eps)) + sg.lr * sg.wd * x;
+    }
+  } else if (sg.kind == kOptAdagrad) {
+    const float c = s0 + g * g;
+    s0 = c;
+    x -= sg.lr * g / (sqrtf(c) + sg.eps);
+  } else {
+    const float c = sg.p0 * s0 + (1.f - sg.p0) * g * g;
+    s0 = c;
+    x -= sg.lr * g / (sqrtf(c) + sg.eps);
+  }
+  return x;
+}
+
+// Peers of a sharded update: the fp32 master arenas of the ranks of the group (index = rank).
+struct OptPeers {
+  float* w[8];
+};
+
+// Ownership of the arena when the optimizer is sharded over `world` ranks: blocks of
+// `own_chunks` chunks are dealt round-robin, block b belongs to rank b % world.  Any long
+// range of the arena is then spread evenly over the ranks, whichever weight tensors it holds.
+__device__ __forceinline__ bool chunk_owned(long long ch, int rank, int world, int own_chunks) {
+  return world <= 1 || (int)((ch / own_chunks) % world) == rank;
+}
+
+// Vectorised update of the chunks this rank owns (all chunks when world == 1): four
+// elements per thread and 16-byte accesses.  With peers, the new fp32 values of an owned
+// chunk are also STORED into every other rank's master arena over NVLink, which is the
+// all-gather that follows a sharded update (rank q then only casts its arena to 16 bits);
+// gradients and optimizer state are touched on the owner alone.
+template <typename G, typename W16>
+__global__ void __launch_bounds__(256)
+fused_optimizer_vec_kernel(float* __restrict__ w, const G* __restrict__ grad,
+                           float* __restrict__ s0, float* __restrict__ s1, W16* __restrict__ w16,
+                           const OptSegment* __restrict__ segs, int nseg, long long total,
+                           float inv_scale, const int* __restrict__ skip_flag,
+                           const int* __restrict__ step_ptr,
+                           const float* __restrict__ lr_scale_ptr,
+                           const float* __restrict__ inv_scale_dev, int rank, int world,
+                           int own_chunks, OptPeers peers) {
+  if (skip_flag && *skip_flag) return;
+  if (inv_scale_dev) inv_scale *= *inv_scale_dev;
+  const float step_t = step_ptr ? (float)(*step_ptr) : 1.f;
+  const float lr_mul = lr_scale_ptr ? *lr_scale_ptr : 1.f;
+  const long long nchunks = (total + kOptChunk - 1) / kOptChunk;
+  // owned chunks are enumerated densely so that every block of the grid has work
+  const long long nblocks = (nchunks + own_chunks - 1) / own_chunks;
+  const long long mine = world <= 1 ? nblocks : (nblocks - rank + world - 1) / world;
+  const long long nowned = mine * own_chunks;
+  const bool has_s1 = s1 != s0;
+  for (long long k = blockIdx.x; k < nowned; k += gridDim.x) {
+    const long long ch = world <= 1 ? k
+                                    : ((k / own_chunks) * world + rank) * own_chunks + k % own_chunks;
+    if (ch >= nchunks) continue;
+    const long long base = ch * kOptChunk;
+    const int si = find_segment(segs, nseg, base);
+    OptSegment sg = segs[si];
+    sg.lr *= lr_mul;
+    if (sg.kind == kOptAdam)
+      sg.corr = sg.lr * sqrtf(1.f - powf(sg.p1, step_t)) / (1.f - powf(sg.p0, step_t));
+    long long end = sg.offset + sg.count;
+    if (end > total) end = total;
+    const long long i = base + 4 * (long long)threadIdx.x;
+    if (i >= end) continue;
+    const int nv = end - i >= 4 ? 4 : (int)(end - i);
+    float x[4], g[4], a0[4], a1[4];
+    if (nv == 4) {
+      const float4 xv = *reinterpret_cast<const float4*>(w + i);
+      x[0] = xv.x; x[1] = xv.y; x[2] = xv.z; x[3] = xv.w;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) x[j] = j < nv ? w[i + j] : 0.f;
+    }
+    if (sg.kind >= 0) {
+      if (nv == 4) {
+        if (sizeof(G) == 4) {
+          const float4 gv = *reinterpret_cast<const float4*>(grad + i);
+          g[0] = gv.x; g[1] = gv.y; g[2] = gv.z; g[3] = gv.w;
+        } else {
+          const uint2 gv = *reinterpret_cast<const uint2*>(grad + i);
+          const G* e = reinterpret_cast<const G*>(&gv);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) g[j] = to_f32<G>(e[j]);
+        }
+        const float4 v0 = *reinterpret_cast<const float4*>(s0 + i);
+        a0[0] = v0.x; a0[1] = v0.y; a0[2] = v0.z; a0[3] = v0.w;
+        if (has_s1) {
+          const float4 v1 = *reinterpret_cast<const float4*>(s1 + i);
+          a1[0] = v1.x; a1[1] = v1.y; a1[2] = v1.z; a1[3] = v1.w;
+        }
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          g[j] = j < nv ? to_f32<G>(grad[i + j]) : 0.f;
+          a0[j] = j < nv ? s0[i + j] : 0.f;
+          a1[j] = (j < nv && has_s1) ? s1[i + j] : 0.f;
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) x[j] = opt_update_one(sg, x[j], g[j] * inv_scale, a0[j], a1[j]);
+      if (nv == 4) {
+        *reinterpret_cast<float4*>(s0 + i) = make_float4(a0[0], a0[1], a0[2], a0[3]);
+        if (has_s1 && sg.kind == kOptAdam)
+          *reinterpret_cast<float4*>(s1 + i) = make_float4(a1[0], a1[1], a1[2], a1[3]);
+        *reinterpret_cast<float4*>(w + i) = make_float4(x[0], x[1], x[2], x[3]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (j >= nv) continue;
+          s0[i + j] = a0[j];
+          if (has_s1 && sg.kind == kOptAdam) s1[i + j] = a1[j];
+          w[i + j] = x[j];
+        }
+      }
+    }
+    if (world > 1 && sg.kind >= 0) {   // frozen tensors are not the optimizer's to publish
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        float* dst = peers.w[q];
+        if (!dst) continue;
+        if (nv == 4) {
+          *reinterpret_cast<float4*>(dst + i) = make_float4(x[0], x[1], x[2], x[3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            if (j < nv) dst[i + j] = x[j];
+        }
+      }
+    }
+    if (w16 && world <= 1) {
+      if (nv == 4) {
+        uint2 o;
+        W16* e = reinterpret_cast<W16*>(&o);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) e[j] = from_f32<W16>(x[j]);
+        *reinterpret_cast<uint2*>(w16 + i) = o;
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (j < nv) w16[i + j] = from_f32<W16>(x[j]);
+      }
+    }
+  }
+}
+
 // flag |= any non-finite; optionally g *= inv_scale in place.
 template <typename G>
 __global__ void unscale_check_kernel(G* __restrict__ grad, long long n, float inv_scale,
                                      const float* __restrict__ inv_scale_dev, int write_back,
-                                     int* __restrict__ flag) {
+                                     int* __restrict__ flag, int rank, int world, int own_chunks) {
   if (inv_scale_dev) inv_scale = *inv_scale_dev;     // loss scale kept on the device
   bool bad = false;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (long long)gridDim.x * blockDim.x) {
+    // sharded update: only the owner holds the reduced gradient of a chunk
+    if (!chunk_owned(i / kOptChunk, rank, world, own_chunks)) continue;
     const float g = to_f32<G>(grad[i]) * inv_scale;
     if (!isfinite(g)) bad = true;
     if (write_back) grad[i] = from_f32<G>(g);
@@ -241,15 +408,61 @@ int lb_amp_update(float* state, const float* reduced, int* flag, float growth, f
 }
 
 // inv_scale_dev: when not null the factor is read from device memory instead of `inv_scale`.
-int lb_unscale_check(void* grad, long long n, float inv_scale, const float* inv_scale_dev,
-                     int write_back, int* flag, int dtype, void* stream_) {
+int lb_unscale_check_owned(void* grad, long long n, float inv_scale, const float* inv_scale_dev,
+                           int write_back, int* flag, int dtype, int rank, int world,
+                           int own_chunks, void* stream_) {
   using namespace lb;
   if (n <= 0) return 0;
+  if (world < 1 || rank < 0 || rank >= world || own_chunks < 1) return -1;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   const int grid = flat_grid(n, 2048);
-  if (dtype == kF32) unscale_check_kernel<float><<<grid, 256, 0, s>>>((float*)grad, n, inv_scale, inv_scale_dev, write_back, flag);
-  else if (dtype == kBF16) unscale_check_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)grad, n, inv_scale, inv_scale_dev, write_back, flag);
-  else unscale_check_kernel<__half><<<grid, 256, 0, s>>>((__half*)grad, n, inv_scale, inv_scale_dev, write_back, flag);
+  if (dtype == kF32) unscale_check_kernel<float><<<grid, 256, 0, s>>>((float*)grad, n, inv_scale, inv_scale_dev, write_back, flag, rank, world, own_chunks);
+  else if (dtype == kBF16) unscale_check_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>((__nv_bfloat16*)grad, n, inv_scale, inv_scale_dev, write_back, flag, rank, world, own_chunks);
+  else unscale_check_kernel<__half><<<grid, 256, 0, s>>>((__half*)grad, n, inv_scale, inv_scale_dev, write_back, flag, rank, world, own_chunks);
+  return (int)cudaGetLastError();
+}
+
+int lb_unscale_check(void* grad, long long n, float inv_scale, const float* inv_scale_dev,
+                     int write_back, int* flag, int dtype, void* stream_) {
+  return lb_unscale_check_owned(grad, n, inv_scale, inv_scale_dev, write_back, flag, dtype, 0, 1, 1,
+                                stream_);
+}
+
+// Sharded form of lb_fused_optimizer: updates the chunks that `rank` owns (blocks of
+// own_chunks chunks dealt round-robin over `world` ranks) and stores their new fp32 values
+// into the master arenas of the other ranks (peer_w: host array of `world` device pointers,
+// peer-mapped; entry `rank` is ignored).  With world == 1 it is the whole update and also
+// refreshes the 16-bit copy; with world > 1 the 16-bit copy is left to a cast of the arena
+// once every rank's stores have landed.
+int lb_fused_optimizer_sharded(float* w, const void* grad, float* s0, float* s1, void* w16,
+                               const void* segs, int nseg, long long total, float inv_scale,
+                               const int* skip_flag, const int* step_ptr,
+                               const float* lr_scale_ptr, const float* inv_scale_dev,
+                               int grad_dtype, int w16_dtype, int rank, int world, int own_chunks,
+                               void* const* peer_w, void* stream_) {
+  using namespace lb;
+  if (total <= 0 || nseg <= 0) return 0;
+  if (world < 1 || world > 8 || rank < 0 || rank >= world || own_chunks < 1) return -1;
+  if ((reinterpret_cast<uintptr_t>(w) | reinterpret_cast<uintptr_t>(grad) |
+       reinterpret_cast<uintptr_t>(s0) | reinterpret_cast<uintptr_t>(s1)) & 15) return -1;
+  OptPeers peers;
+  for (int r = 0; r < 8; ++r) {
+    peers.w[r] = (world > 1 && r < world && r != rank && peer_w) ? (float*)peer_w[r] : nullptr;
+    if (reinterpret_cast<uintptr_t>(peers.w[r]) & 15) return -1;
+  }
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  const long long nchunks = (total + kOptChunk - 1) / kOptChunk;
+  const int grid = flat_grid((nchunks + world - 1) / world * kOptChunk, kOptChunk);
+  const OptSegment* sg = reinterpret_cast<const OptSegment*>(segs);
+#define LB_OPTV(G, W)                                                                        \
+  fused_optimizer_vec_kernel<G, W><<<grid, 256, 0, s>>>(                                     \
+      w, (const G*)grad, s0, s1, (W*)w16, sg, nseg, total, inv_scale, skip_flag, step_ptr,   \
+      lr_scale_ptr, inv_scale_dev, rank, world, own_chunks, peers)
+  const bool wb = (w16_dtype == kBF16);
+  if (grad_dtype == kF32) { if (wb) LB_OPTV(float, __nv_bfloat16); else LB_OPTV(float, __half); }
+  else if (grad_dtype == kBF16) { if (wb) LB_OPTV(__nv_bfloat16, __nv_bfloat16); else LB_OPTV(__nv_bfloat16, __half); }
+  else { if (wb) LB_OPTV(__half, __nv_bfloat16); else LB_OPTV(__half, __half); }
+#undef LB_OPTV
   return (int)cudaGetLastError();
 }
 

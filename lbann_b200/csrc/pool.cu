@@ -37,8 +37,9 @@ __device__ __forceinline__ void st8(T* p, const float (&f)[8]) {
 template <typename T>
 __global__ void pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, PoolGeom g,
                                 long long xs_n, long long xs_d, long long xs_h, long long xs_w,
-                                long long total) {
+                                long long y_sn, long long total) {
   const int cv = g.C / 8;
+  const long long per_sample = (long long)g.Do * g.Ho * g.Wo * g.C;   // dense part of a sample
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
        i += (long long)gridDim.x * blockDim.x) {
     long long r = i;
@@ -77,7 +78,7 @@ __global__ void pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, Pool
 #pragma unroll
       for (int j = 0; j < 8; ++j) acc[j] *= inv;
     }
-    st8<T>(y + i * 8, acc);
+    st8<T>(y + n * y_sn + (i * 8 - n * per_sample), acc);
   }
 }
 
@@ -166,20 +167,30 @@ extern "C" {
 
 // geom: 18 ints = N D H W C Do Ho Wo kd kh kw pd ph pw sd sh sw mode.  C % 8 == 0.
 // y and dx are dense NDHWC; x may be strided (xs = n, d, h, w strides in elements).
+int lb_pool_fwd_strided(const void* x, void* y, const int* geom, const long long* xs,
+                        long long y_sn, int dtype, void* stream_);
 int lb_pool_fwd(const void* x, void* y, const int* geom, const long long* xs, int dtype,
                 void* stream_) {
+  return lb_pool_fwd_strided(x, y, geom, xs, 0, dtype, stream_);
+}
+
+// y_sn: elements between consecutive samples of y (0 = dense); a sample itself is dense.
+int lb_pool_fwd_strided(const void* x, void* y, const int* geom, const long long* xs,
+                        long long y_sn, int dtype, void* stream_) {
   using namespace lb;
   PoolGeom g;
   memcpy(&g, geom, sizeof(g));
   if (g.C % 8) return -1;
+  if (y_sn == 0) y_sn = (long long)g.Do * g.Ho * g.Wo * g.C;
+  if (y_sn % 8 || (reinterpret_cast<uintptr_t>(y) & 15)) return -1;
   const long long total = (long long)g.N * g.Do * g.Ho * g.Wo * (g.C / 8);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   if (dtype == kBF16)
     pool_fwd_kernel<__nv_bfloat16><<<pool_grid(total), 256, 0, s>>>(
-        (const __nv_bfloat16*)x, (__nv_bfloat16*)y, g, xs[0], xs[1], xs[2], xs[3], total);
+        (const __nv_bfloat16*)x, (__nv_bfloat16*)y, g, xs[0], xs[1], xs[2], xs[3], y_sn, total);
   else if (dtype == kF16)
     pool_fwd_kernel<__half><<<pool_grid(total), 256, 0, s>>>((const __half*)x, (__half*)y, g,
-                                                             xs[0], xs[1], xs[2], xs[3], total);
+                                                             xs[0], xs[1], xs[2], xs[3], y_sn, total);
   else
     return -1;
   return (int)cudaGetLastError();

@@ -22,7 +22,7 @@ struct TiledPoolGeom {
 template <typename T>
 __global__ void pool_bwd_tiled_kernel(const T* __restrict__ x, const T* __restrict__ dy,
                                       T* __restrict__ dx, TiledPoolGeom g, int act,
-                                      float act_param, long long total) {
+                                      float act_param, long long dx_sn, long long total) {
   const int cv = g.C / 8;
   const int Do = g.D / g.kd, Ho = g.H / g.kh, Wo = g.W / g.kw;
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -45,6 +45,8 @@ __global__ void pool_bwd_tiled_kernel(const T* __restrict__ x, const T* __restri
     }
     const long long base = (((n * g.D + (long long)od * g.kd) * g.H + (long long)oh * g.kh) * g.W +
                             (long long)ow * g.kw) * g.C + c8 * 8;
+    // dx may leave a gap between samples (it is then the inside of a tensor with halo planes)
+    const long long dbase = base + n * (dx_sn - (long long)g.D * g.H * g.W * g.C);
     int pos = 0;
     for (int a = 0; a < g.kd; ++a)
       for (int b = 0; b < g.kh; ++b)
@@ -74,7 +76,7 @@ __global__ void pool_bwd_tiled_kernel(const T* __restrict__ x, const T* __restri
           T* e = reinterpret_cast<T*>(&q);
 #pragma unroll
           for (int j = 0; j < 8; ++j) e[j] = from_f32<T>(arg[j] == pos ? gy[j] : 0.f);
-          *reinterpret_cast<uint4*>(dx + off) = q;
+          *reinterpret_cast<uint4*>(dx + off + (dbase - base)) = q;
         }
   }
 }
@@ -85,12 +87,22 @@ extern "C" {
 
 // geom: N D H W C kd kh kw (8 ints); x, dx dense NDHWC, dy dense [N][D/kd][H/kh][W/kw][C].
 // act: 0 none, 1 relu, 2 leaky(act_param) - derivative taken from the sign of x.
+int lb_pool_bwd_tiled_strided(const void* x, const void* dy, void* dx, const int* geom, int act,
+                              float act_param, long long dx_sn, int dtype, void* stream_);
 int lb_pool_bwd_tiled(const void* x, const void* dy, void* dx, const int* geom, int act,
                       float act_param, int dtype, void* stream_) {
+  return lb_pool_bwd_tiled_strided(x, dy, dx, geom, act, act_param, 0, dtype, stream_);
+}
+
+// dx_sn: elements between consecutive samples of dx (0 = dense).
+int lb_pool_bwd_tiled_strided(const void* x, const void* dy, void* dx, const int* geom, int act,
+                              float act_param, long long dx_sn, int dtype, void* stream_) {
   using namespace lb;
   TiledPoolGeom g;
   memcpy(&g, geom, sizeof(g));
   if (g.C % 8 || g.D % g.kd || g.H % g.kh || g.W % g.kw) return -1;
+  if (dx_sn == 0) dx_sn = (long long)g.D * g.H * g.W * g.C;
+  if (dx_sn % 8 || (reinterpret_cast<uintptr_t>(dx) & 15)) return -1;
   const long long total = (long long)g.N * (g.D / g.kd) * (g.H / g.kh) * (g.W / g.kw) * (g.C / 8);
   if (total <= 0) return 0;
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
@@ -99,10 +111,10 @@ int lb_pool_bwd_tiled(const void* x, const void* dy, void* dx, const int* geom, 
   const int grid = (int)(blocks < cap ? blocks : cap);
   if (dtype == kBF16)
     pool_bwd_tiled_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
-        (const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, g, act, act_param, total);
+        (const __nv_bfloat16*)x, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, g, act, act_param, dx_sn, total);
   else if (dtype == kF16)
     pool_bwd_tiled_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (const __half*)dy,
-                                                       (__half*)dx, g, act, act_param, total);
+                                                       (__half*)dx, g, act, act_param, dx_sn, total);
   else
     return -1;
   return (int)cudaGetLastError();

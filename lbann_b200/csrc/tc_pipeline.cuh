@@ -13,6 +13,7 @@
 // issue and the row -> output address map.
 #pragma once
 #include "common.cuh"
+#include "halo_sync.cuh"
 
 namespace lb {
 
@@ -61,19 +62,6 @@ struct TcShared {
   int abort_flag;
 };
 
-// Per-role timestamps of CTA 0 (development aid, compiled in with -DLB_TRACE):
-// row 0 producer after issuing stage i, row 1 MMA warp after the stage landed, row 2 after
-// its MMAs were issued, row 3 epilogue begin / end per tile.
-#ifdef LB_TRACE
-static __device__ long long lb_trace[4][512];
-#define LB_TRACE_AT(row, idx)                                                        \
-  do {                                                                               \
-    if (blockIdx.x == 0 && (idx) < 512u) lb_trace[row][idx] = clock64();             \
-  } while (0)
-#else
-#define LB_TRACE_AT(row, idx) do {} while (0)
-#endif
-
 // Epilogue of one accumulator tile for one warp: reads this warp's 32 TMEM lanes in
 // chunks of 32 columns, applies alpha / bias / beta / activation and stores the row.
 // The activation kind is switched on ONCE per chunk, outside the element loops: a switch
@@ -102,7 +90,7 @@ __device__ __forceinline__ void tc_apply_act32(float (&v)[32], int act, float pr
 template <int BN>
 __device__ __forceinline__ void tc_epilogue_rows(uint32_t taddr, bool row_ok, long long row_off,
                                                  int n0, int n_total, int row_index,
-                                                 const EpiParams& e, unsigned lb_trace_tile = 0) {
+                                                 const EpiParams& e) {
   const float alpha = e.alpha, beta = e.beta;
   const int bias_mode = e.bias_mode, act = e.act, out_dtype = e.out_dtype;
   const float row_bias = bias_mode == 2 ? e.bias[row_index] : 0.f;
@@ -111,10 +99,8 @@ __device__ __forceinline__ void tc_epilogue_rows(uint32_t taddr, bool row_ok, lo
     if (n0 + c >= n_total) break;  // warp-uniform
     uint32_t r[32];
     __syncwarp();  // tcgen05.ld is warp-collective: rejoin lanes that skipped a masked row
-    if (threadIdx.x == 0) LB_TRACE_AT(0, 256 + 4 * lb_trace_tile + 0);
     tmem_ld_32x32(taddr + c, r);
     tmem_ld_wait();
-    if (threadIdx.x == 0) LB_TRACE_AT(0, 256 + 4 * lb_trace_tile + 1);
     if (!row_ok) continue;
     float v[32];
 #pragma unroll
@@ -163,7 +149,6 @@ __device__ __forceinline__ void tc_epilogue_rows(uint32_t taddr, bool row_ok, lo
         if (j < ncol) v[j] += beta * load_as_f32(e.C, off + j, out_dtype);
     }
     tc_apply_act32(v, act, e.act_param);
-    if (threadIdx.x == 0) LB_TRACE_AT(0, 256 + 4 * lb_trace_tile + 2);
     if (out_dtype == kF32) {
       float* dst = reinterpret_cast<float*>(e.C) + off;
       if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
@@ -196,7 +181,6 @@ __device__ __forceinline__ void tc_epilogue_rows(uint32_t taddr, bool row_ok, lo
           if (j < ncol) dst[j] = static_cast<uint16_t>(j & 1 ? q[j >> 1] >> 16 : q[j >> 1] & 0xffffu);
       }
     }
-    if (threadIdx.x == 0) LB_TRACE_AT(0, 256 + 4 * lb_trace_tile + 3);
   }
 }
 
@@ -214,6 +198,26 @@ struct TcHelpers<Policy, typename Policy::HasHelpers> {
   __device__ static void run(const typename Policy::Params& p, int index, int n, uint8_t* smem,
                              int* status) {
     Policy::helper_cta(p, index, n, smem, status);
+  }
+};
+
+// A policy whose operand A is a depth-partitioned tensor with halo planes (`using HasHalo =
+// void;`) exposes the exchange state (`halo(p)`) and tells which halos a tile reads
+// (`tile_halo(p, tile)`: bit 0 = planes from the rank above, bit 1 = from the rank below).
+template <class Policy, class = void>
+struct TcHalo {
+  static constexpr bool kHas = false;
+  __device__ static const HaloSync* get(const typename Policy::Params&) { return nullptr; }
+  __device__ static int touches(const typename Policy::Params&, const typename Policy::Tile&) {
+    return 0;
+  }
+};
+template <class Policy>
+struct TcHalo<Policy, typename Policy::HasHalo> {
+  static constexpr bool kHas = true;
+  __device__ static const HaloSync* get(const typename Policy::Params& p) { return &Policy::halo(p); }
+  __device__ static int touches(const typename Policy::Params& p, const typename Policy::Tile& t) {
+    return Policy::tile_halo(p, t);
   }
 };
 
@@ -285,6 +289,15 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
 
   const int num_tiles = p.num_tiles;
   const int k_iters = p.k_iters;
+  const HaloSync* hs = TcHalo<Policy>::get(p);
+  const bool halo_on = TcHalo<Policy>::kHas && hs->enabled;
+
+  if (halo_on && warp < 4) {
+    // idle until the first accumulator completes: send the boundary planes to the neighbours
+    halo_push(*hs, threadIdx.x, 128, blockIdx.x, n_workers);
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (threadIdx.x == 0) halo_signal(*hs);
+  }
 
   if (warp == 4) {
     // ------------------------------ producer --------------------------------
@@ -293,17 +306,33 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     // the boxes of a stage enter the copy engine side by side instead of one after another.
     uint32_t it = 0;
     bool ok = true;
+    const uint32_t halo_target =
+        halo_on ? (*reinterpret_cast<volatile uint32_t*>(hs->local) + 1u) * (uint32_t)n_workers : 0u;
+    int halo_need = halo_on ? ((hs->top_flag ? 1 : 0) | (hs->bot_flag ? 2 : 0)) : 0;
     for (int t = blockIdx.x; t < num_tiles && ok; t += n_workers) {
       const typename Policy::Tile tile = Policy::decode(p, t);
+      if (halo_need) {
+        // first tile of this CTA that reads planes a neighbour sends: wait for them (bounded)
+        const int touch = TcHalo<Policy>::touches(p, tile) & halo_need;
+        int good = 1;
+        if (touch && lane == 0) {
+          if ((touch & 1) && !halo_wait(hs->top_flag, halo_target, status, abort_flag)) good = 0;
+          if (good && (touch & 2) && !halo_wait(hs->bot_flag, halo_target, status, abort_flag)) good = 0;
+        }
+        good = __shfl_sync(0xffffffffu, good, 0);
+        if (!good) {
+          ok = false;
+          break;
+        }
+        halo_need &= ~touch;
+      }
       for (int k = 0; k < k_iters; ++k, ++it) {
         const uint32_t s = it % S;
         const uint32_t ph = (it / S) & 1;
         int good = 1;
         const uint32_t bar = smem_u32(&sh.full[s]);
         if (lane == 0) {
-          LB_TRACE_AT(0, 4 * it);
           good = mbar_wait_bounded(smem_u32(&sh.empty[s]), ph ^ 1, abort_flag) ? 1 : 0;
-          LB_TRACE_AT(0, 4 * it + 1);
           if (good) mbar_expect_tx(bar, Policy::stage_bytes(p, tile, k));
           else raise_status(status, abort_flag, kTimeoutStageEmpty);
         }
@@ -314,9 +343,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         }
         const uint32_t sA = smem_base + s * G::kStageBytes;
         const uint32_t sB = sA + G::kABytes;
-        if (lane == 0) LB_TRACE_AT(0, 4 * it + 2);
         Policy::load(p, tile, k, sA, sB, bar, &tmA, &tmB, lane);
-        if (lane == 0) LB_TRACE_AT(0, 4 * it + 3);
       }
     }
     // Drain: every load issued must have landed before the CTA's shared memory goes away.
@@ -355,12 +382,10 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
             break;
           }
           tc_fence_after();
-          LB_TRACE_AT(1, it);
           const uint32_t sA = smem_base + s * G::kStageBytes;
           const uint32_t sB = sA + G::kABytes;
           Policy::mma(p, k, sA, sB, tmem_acc, idesc, /*first=*/k == 0);
           umma_commit(smem_u32(&sh.empty[s]));  // frees the stage when the MMAs retire
-          LB_TRACE_AT(2, it);
         }
         if (ok) umma_commit(smem_u32(&sh.tmem_full[acc]));
       }
@@ -382,7 +407,6 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         break;
       }
       tc_fence_after();
-      if (threadIdx.x == 0) LB_TRACE_AT(3, 2 * local_tile);
       const int row = warp * 32 + lane;
       long long row_off = 0;
       const bool row_ok = Policy::row_addr(p, tile, row, row_off);
@@ -394,13 +418,13 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       TcEpilogue<Policy>::run(taddr, row_ok, row_off, n0, n_total, row_index, e, p);
       tc_fence_before();
       __syncwarp();
-      if (threadIdx.x == 0) LB_TRACE_AT(3, 2 * local_tile + 1);
       if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[acc]));
     }
   }
 
   tc_fence_before();
   __syncthreads();
+  if (halo_on && threadIdx.x == 0) halo_finish(*hs, n_workers);
   if (warp == 5) {
     tc_fence_after();
     tmem_dealloc(tmem_base, G::kTmemCols);

@@ -39,6 +39,24 @@ class _ModeState:
         self.fetch_seconds = 0.0
 
 
+def slice_with_halo(t: torch.Tensor, dim: int, start: int, stop: int, halo: int = 0) -> torch.Tensor:
+    """``t[start - halo : stop + halo]`` along ``dim``, with zeros where that leaves the tensor
+    (a rank's slab of a partitioned sample together with the planes its first convolution
+    reads from the neighbouring slabs)."""
+    if halo <= 0:
+        return t.narrow(dim, start, stop - start)
+    lo, hi = start - halo, stop + halo
+    a, b = max(lo, 0), min(hi, t.shape[dim])
+    core = t.narrow(dim, a, b - a)
+    if a == lo and b == hi:
+        return core
+    shape = list(t.shape)
+    shape[dim] = hi - lo
+    out = torch.zeros(shape, dtype=t.dtype)
+    out.narrow(dim, a - lo, b - a).copy_(core)
+    return out
+
+
 class Batch:
     def __init__(self, tensors, global_size, indices, end_of_epoch, offset):
         self.tensors: Dict[str, torch.Tensor] = tensors
@@ -187,7 +205,7 @@ class DataCoordinator:
         for f, t in host.items():
             sl = getattr(self, "field_slices", {}).get(f)
             if sl is not None:      # this rank only needs a slab of the sample (distconv)
-                t = t.narrow(sl[0], sl[1], sl[2] - sl[1])
+                t = slice_with_halo(t, sl[0], sl[1], sl[2], sl[3] if len(sl) > 3 else 0)
             dt = self.field_dtypes.get(f)
             if dt is not None and t.dtype != dt:
                 t = t.to(dt)

@@ -240,6 +240,7 @@ class _TransposedLinear(torch.autograd.Function):
         dx = gemm(dy2, wh.cast(dy2.dtype), trans_b=True).reshape(xshape)
         if wh.grad is not None:
             gemm(x2, dy2, trans_a=True, out=wh.grad.view(wh.master.shape), beta=1.0)
+            wh.mark_ready()
         return dx, None, None
 
 

@@ -32,6 +32,8 @@ LOWER_IS_BETTER, HIGHER_IS_BETTER = 0, 1
 def pack_model(model, weights_names=None, with_optimizer=True) -> Dict[str, torch.Tensor]:
     out = {}
     names = set(weights_names) if weights_names else None
+    if with_optimizer and hasattr(model, "sync_optimizer_state"):
+        model.sync_optimizer_state()     # collective over the trainer when the state is sharded
     for w in model.weights:
         if names is not None and w.name not in names:
             continue

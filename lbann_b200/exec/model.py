@@ -476,6 +476,12 @@ class ExecModel:
     def clear_gradients(self):
         self.arena.zero_grad()
 
+    def sync_optimizer_state(self):
+        """Collective over the trainer: optimizer state that the ranks hold in shards (the
+        sharded update of data-parallel GPU runs) becomes whole on every rank."""
+        if self.parallel is not None and self.arena is not None:
+            self.parallel.sync_optimizer_state(self)
+
     def backward_prop(self, local_obj: torch.Tensor):
         for cb in self.callbacks:
             cb.on_backward_prop_begin(self)
@@ -739,6 +745,10 @@ class ExecModel:
                       mini_batch_offset=0):
         for cb in self.callbacks:
             cb.on_forward_prop_begin(self, mode)
+        if self.distconv is not None:
+            # forward-only steps have no gradient reduction between them: the ranks meet here,
+            # so that no rank sends halo planes into a tensor a neighbour still reads
+            self.distconv.step_barrier()
         self.forward_prop(inputs, mode, global_mini_batch_size, mini_batch_offset)
         for cb in self.callbacks:
             cb.on_forward_prop_end(self, mode)

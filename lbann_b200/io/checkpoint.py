@@ -67,7 +67,16 @@ def read_latest(base, trainer_name, kind="shared") -> Optional[Tuple[str, int, i
 
 # ------------------------------------------------------------------ model / trainer payloads
 def model_state(model, gather_sharded: bool = True):
+    # optimizer state that is sharded over the trainer's ranks is made whole first (collective)
+    if hasattr(model, "sync_optimizer_state"):
+        model.sync_optimizer_state()
     tensors, meta = {}, {"name": model.name, "weights": {}, "amp_scale": model.amp_scale}
+    if getattr(model, "_amp_state", None) is not None:
+        # loss scale, its inverse, clean steps, consecutive skipped steps, last step's inverse
+        meta["amp_state"] = [float(v) for v in model._amp_state.tolist()]
+    else:
+        meta["amp_counters"] = [int(getattr(model, "_amp_good_steps", 0)),
+                                int(getattr(model, "_amp_skipped", 0))]
     for w in model.weights:
         vals = w.values.detach()
         if getattr(w, "export_values", None) is not None:
@@ -111,6 +120,14 @@ def load_model_state(model, tensors, meta, strict: bool = True):
             a.lr_scale_dev = torch.ones(1, dtype=torch.float32, device=model.device)
         a.step_dev.fill_(int(meta["optimizer_step"]))
     model.amp_scale = float(meta.get("amp_scale", model.amp_scale))
+    if "amp_state" in meta and model.device.type == "cuda" and model.amp_enabled:
+        st = model._amp_device_state()
+        st.copy_(torch.tensor(meta["amp_state"], dtype=torch.float32))
+    elif "amp_state" in meta:
+        model._amp_good_steps = int(meta["amp_state"][2])
+        model._amp_skipped = int(meta["amp_state"][3])
+    elif "amp_counters" in meta:
+        model._amp_good_steps, model._amp_skipped = (int(v) for v in meta["amp_counters"])
     model.arena.refresh_compute()
 
 
@@ -138,6 +155,9 @@ def _save_rng(dirpath: str, rank: int, model):
 def _load_rng(dirpath: str, rank: int, model):
     path = os.path.join(dirpath, "rng_state", f"rng_generator_{rank}")
     if not os.path.exists(path):
+        import warnings
+        warnings.warn(f"checkpoint {dirpath} has no random-generator state for rank {rank}: this "
+                      "rank continues with fresh random streams, the restart is not reproducible")
         return
     t, meta = container.load(path)
     torch.set_rng_state(t["torch_cpu"])
@@ -182,7 +202,10 @@ def save_checkpoint(trainer, model, base: str, hook: str, distributed: bool = Fa
                        for m, s in dc.items() if s["reader"] is not None})
         container.save(os.path.join(d, "data_coordinator.bin"), arrays,
                        {m: {"pos": s["pos"], "epoch": s["epoch"], "mb": s["mb"]} for m, s in dc.items()})
-        _save_rng(d, comm.rank_in_world, model)
+    # every rank keeps its own generators (src/utils/random.cpp save_rng_to_checkpoint writes
+    # one file per rank in shared checkpoints too): the master has made the directory by now
+    comm.trainer_barrier()
+    _save_rng(d, rank, model)
     comm.trainer_barrier()
     if comm.am_trainer_master():
         write_latest(per_rank_base or base if distributed else base, trainer.name,
@@ -235,7 +258,7 @@ def restore_checkpoint(trainer, model, base: str, per_rank_base: Optional[str] =
                            "reader": ({"indices": arrays[f"{mode}/reader_indices"].numpy()}
                                       if f"{mode}/reader_indices" in arrays else None)}
         trainer.data_coordinator.load_state(state)
-    _load_rng(d, comm.rank_in_world, model)
+    _load_rng(d, comm.rank_in_trainer, model)
     ctx = trainer.context(model, "training")
     st = trainer.data_coordinator.modes["training"]
     # resume inside an epoch only when the checkpoint was taken inside one (a position at

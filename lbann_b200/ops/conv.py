@@ -26,6 +26,11 @@ def _lib():
             c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_int),
             ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong),
             c_int, c_int, c_float, c_float, c_int, c_float, c_void_p]
+        lib.lb_conv_fwd_halo_tc.restype = c_int
+        lib.lb_conv_fwd_halo_tc.argtypes = [
+            c_void_p, c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_int),
+            ctypes.POINTER(ctypes.c_longlong), ctypes.POINTER(ctypes.c_longlong),
+            c_int, c_int, c_float, c_float, c_int, c_float, c_void_p, c_void_p]
         lib.lb_conv_wgrad_tc.restype = c_int
         lib.lb_conv_wgrad_tc.argtypes = [
             c_void_p, c_void_p, c_void_p, ctypes.POINTER(c_int),
@@ -33,6 +38,13 @@ def _lib():
             ctypes.c_longlong, ctypes.c_longlong, ctypes.c_longlong, c_int, c_float, c_void_p]
         _configured = True
     return lib
+
+
+class HaloSyncArgs(ctypes.Structure):
+    """Mirror of ``lb::HaloSyncArgs`` (csrc/halo_sync.cuh)."""
+    _fields_ = [("up_dst", c_void_p), ("down_dst", c_void_p), ("up_flag", c_void_p),
+                ("down_flag", c_void_p), ("top_flag", c_void_p), ("bot_flag", c_void_p),
+                ("local", c_void_p), ("h", ctypes.c_longlong)]
 
 
 def norm3(v, fill):
@@ -62,8 +74,11 @@ def conv_fwd(x: torch.Tensor, w_taps: torch.Tensor, ksize, *, pad=0, stride=1, d
              bias: torch.Tensor | None = None, act: int = native.ACT_NONE,
              act_param: float = 0.0, out: torch.Tensor | None = None,
              out_dtype: torch.dtype | None = None, alpha: float = 1.0, beta: float = 0.0,
-             out_dims=None) -> torch.Tensor:
-    """x: [N, D, H, W, C] view (C contiguous).  w_taps: [taps, Kout, C].  Returns NDHWC."""
+             out_dims=None, halo=None) -> torch.Tensor:
+    """x: [N, D, H, W, C] view (C contiguous).  w_taps: [taps, Kout, C].  Returns NDHWC.
+    ``halo``: a ``HaloSyncArgs`` structure (csrc/halo_sync.cuh) when ``x`` is a rank's
+    depth-extended tensor in symmetric memory: the kernel then exchanges the halo planes with
+    the depth neighbours itself (CUDA only, depth padding 0)."""
     N, D, H, W, C = x.shape
     kd, kh, kw = norm3(ksize, 1)
     pd, ph, pw = norm3(pad, 0)
@@ -116,11 +131,13 @@ def conv_fwd(x: torch.Tensor, w_taps: torch.Tensor, ksize, *, pad=0, stride=1, d
     ys = (ctypes.c_longlong * 4)(out.stride(0), out.stride(1), out.stride(2), out.stride(3))
     if bias is not None and bias.dtype != torch.float32:
         bias = bias.float()
-    rc = _lib().lb_conv_fwd_tc(x.data_ptr(), w_taps.data_ptr(), out.data_ptr(), native.ptr(bias),
-                               geom, xs, ys, native.dtype_code(x.dtype),
-                               native.dtype_code(out.dtype), float(alpha), float(beta), int(act),
-                               float(act_param), native.stream_ptr())
-    native.check(rc, "lb_conv_fwd_tc")
+    rc = _lib().lb_conv_fwd_halo_tc(x.data_ptr(), w_taps.data_ptr(), out.data_ptr(), native.ptr(bias),
+                                    geom, xs, ys, native.dtype_code(x.dtype),
+                                    native.dtype_code(out.dtype), float(alpha), float(beta), int(act),
+                                    float(act_param),
+                                    ctypes.cast(ctypes.pointer(halo), c_void_p) if halo is not None else None,
+                                    native.stream_ptr())
+    native.check(rc, "lb_conv_fwd_halo_tc")
     native.count_launch()
     return out
 

@@ -33,6 +33,11 @@ def _lib():
         P = ctypes.POINTER
         lib.lb_pool_fwd.restype = c_int
         lib.lb_pool_fwd.argtypes = [c_void_p, c_void_p, P(c_int), P(c_ll), c_int, c_void_p]
+        lib.lb_pool_fwd_strided.restype = c_int
+        lib.lb_pool_fwd_strided.argtypes = [c_void_p, c_void_p, P(c_int), P(c_ll), c_ll, c_int, c_void_p]
+        lib.lb_pool_bwd_tiled_strided.restype = c_int
+        lib.lb_pool_bwd_tiled_strided.argtypes = [c_void_p, c_void_p, c_void_p, P(c_int), c_int, c_float,
+                                                  c_ll, c_int, c_void_p]
         lib.lb_pool_bwd.restype = c_int
         lib.lb_pool_bwd.argtypes = [c_void_p, c_void_p, c_void_p, P(c_int), P(c_ll), c_int, c_void_p]
         lib.lb_layer_norm_fwd.restype = c_int
@@ -139,6 +144,17 @@ class WeightHandle:
             return
         self.grad.add_(g.reshape(self.grad.shape).to(self.grad.dtype))
 
+    def mark_ready(self):
+        """One user's backward has written its contribution to ``grad``.  When all users of
+        this step have, ``on_grad_ready`` (set by a data-parallel context) starts reducing the
+        gradient while the rest of backward still runs."""
+        cb = getattr(self, "on_grad_ready", None)
+        if cb is None:
+            return
+        self.pending_uses = getattr(self, "pending_uses", 1) - 1
+        if self.pending_uses == 0:
+            cb()
+
 
 def column_sums(x2d: torch.Tensor) -> torch.Tensor:
     """fp32 sum over rows of a [rows, C] 16-bit CUDA tensor (native when C % 8 == 0)."""
@@ -196,11 +212,10 @@ class _Linear(torch.autograd.Function):
             dx = gemm(dy2, wh.cast(dy2.dtype)).reshape(xshape)
         if wh.grad is not None:
             _weight_grad(dy2, x2, wh.grad.view(wh.master.shape))
-            ready = getattr(wh, "on_grad_ready", None)
-            if ready is not None:
-                ready()         # data-parallel runs start reducing this gradient right away
+            wh.mark_ready()     # data-parallel runs start reducing this gradient right away
         if bh is not None and bh.grad is not None:
             bh.grad.add_(column_sums(dy2))
+            bh.mark_ready()
         return dx, None, None, None, None, None, None
 
 
@@ -256,6 +271,13 @@ def linear(x, wh: WeightHandle, bh: Optional[WeightHandle] = None, act: int = na
 
 
 # --------------------------------------------------------------------------- convolution
+def _sample_dense(t: torch.Tensor) -> bool:
+    """NDHWC tensor whose samples are dense (only the sample stride may leave a gap)."""
+    N, D, H, W, C = t.shape
+    return (t.stride(4) == 1 and t.stride(3) == C and t.stride(2) == W * C
+            and t.stride(1) == H * W * C and t.stride(0) >= D * H * W * C)
+
+
 def _cl_view(x: torch.Tensor) -> torch.Tensor:
     """[N, C, (D,) H, W] logical tensor -> channels-last NDHWC view (copying if needed)."""
     if x.dim() == 4:
@@ -265,6 +287,9 @@ def _cl_view(x: torch.Tensor) -> torch.Tensor:
         x = x.unsqueeze(2)  # N, C, 1, W
         x = x.contiguous(memory_format=torch.channels_last)
         return x.permute(0, 2, 3, 1).unsqueeze(1)
+    v = x.permute(0, 2, 3, 4, 1)
+    if _sample_dense(v):      # dense samples, possibly with a gap between them (halo planes)
+        return v
     x = x.contiguous(memory_format=torch.channels_last_3d)
     return x.permute(0, 2, 3, 4, 1)
 
@@ -358,8 +383,10 @@ class _Conv(torch.autograd.Function):
             else:
                 tmp = conv_wgrad(x_cl, dy_cl, ksize, pad=pad, stride=stride, dilation=dil)
                 wh.grad.add_(tmp[:Kout, :Cin].reshape(wh.grad.shape))
+            wh.mark_ready()
         if bh is not None and bh.grad is not None:
             bh.grad.add_(column_sums(dy_cl.reshape(-1, dy_cl.shape[-1]))[:Kout])
+            bh.mark_ready()
         return (dx,) + (None,) * 11
 
 
@@ -439,8 +466,10 @@ class _ConvC8(torch.autograd.Function):
                                                  taps, Cin, native.dtype_code(x_cl.dtype), 1.0,
                                                  native.stream_ptr()), "lb_conv_c8_wgrad")
             native.count_launch()
+            wh.mark_ready()
         if bh is not None and bh.grad is not None:
             bh.grad.add_(column_sums(dy_cl.reshape(-1, Kout)))
+            bh.mark_ready()
         return (dx,) + (None,) * 9
 
 
@@ -523,6 +552,7 @@ class _DeconvGemm(torch.autograd.Function):
         if wh.grad is not None:
             # grad of W[Cin, Cout*taps] = x^T dy
             gemm(x2, dy, trans_a=True, out=wh.grad.view(x2.shape[1], dy.shape[1]), beta=1.0)
+            wh.mark_ready()
         return dx, None, None, None
 
 
@@ -531,22 +561,29 @@ _POOL_MODE = {"max": 0, "average": 1, "average_no_pad": 2}
 
 
 class _Pool(torch.autograd.Function):
+    """``out_alloc`` / ``dx_alloc``: optional callables (shape, dtype) -> NDHWC tensor (or
+    None) that place the output / the input gradient, e.g. inside a consumer's buffer with
+    halo planes; samples must be dense, the sample stride may leave a gap."""
+
     @staticmethod
-    def forward(ctx, x, ksize, pad, stride, mode, bwd_act, bwd_act_p):
+    def forward(ctx, x, ksize, pad, stride, mode, bwd_act, bwd_act_p, out_alloc=None, dx_alloc=None):
         ndim = x.dim()
         x_cl = _cl_view(x)
         ctx.bwd_act = (bwd_act, bwd_act_p)
         ctx.win = (ksize, pad, stride, mode)
+        ctx.dx_alloc = dx_alloc
         N, D, H, W, C = x_cl.shape
         Do, Ho, Wo = (out_size(D, ksize[0], pad[0], stride[0], 1),
                       out_size(H, ksize[1], pad[1], stride[1], 1),
                       out_size(W, ksize[2], pad[2], stride[2], 1))
-        y = torch.empty((N, Do, Ho, Wo, C), dtype=x.dtype, device=x.device)
+        y = out_alloc((N, Do, Ho, Wo, C), x.dtype) if out_alloc is not None else None
+        if y is None or not _sample_dense(y):
+            y = torch.empty((N, Do, Ho, Wo, C), dtype=x.dtype, device=x.device)
         geom = (c_int * 18)(N, D, H, W, C, Do, Ho, Wo, *ksize, *pad, *stride, mode)
         xs = (c_ll * 4)(x_cl.stride(0), x_cl.stride(1), x_cl.stride(2), x_cl.stride(3))
-        rc = _lib().lb_pool_fwd(x_cl.data_ptr(), y.data_ptr(), geom, xs,
-                                native.dtype_code(x.dtype), native.stream_ptr())
-        native.check(rc, "lb_pool_fwd")
+        rc = _lib().lb_pool_fwd_strided(x_cl.data_ptr(), y.data_ptr(), geom, xs, y.stride(0),
+                                        native.dtype_code(x.dtype), native.stream_ptr())
+        native.check(rc, "lb_pool_fwd_strided")
         native.count_launch()
         ctx.save_for_backward(x_cl)
         ctx.meta = (geom, ndim)
@@ -559,19 +596,24 @@ class _Pool(torch.autograd.Function):
         dy_cl = _cl_view(dy)
         if not dy_cl.is_contiguous():
             dy_cl = dy_cl.contiguous()
-        dx = torch.empty(x_cl.shape, dtype=x_cl.dtype, device=x_cl.device)
         ksize, pad, stride, mode = ctx.win
         N, D, H, W, C = x_cl.shape
         tiled = (mode == 0 and ksize == stride and pad == (0, 0, 0) and x_cl.is_contiguous()
                  and D % ksize[0] == 0 and H % ksize[1] == 0 and W % ksize[2] == 0)
+        nothing = (None,) * 8
         if tiled:
+            dx = ctx.dx_alloc(tuple(x_cl.shape), x_cl.dtype) if ctx.dx_alloc is not None else None
+            if dx is None or not _sample_dense(dx):
+                dx = torch.empty(x_cl.shape, dtype=x_cl.dtype, device=x_cl.device)
             tg = (c_int * 8)(N, D, H, W, C, *ksize)
-            rc = _lib().lb_pool_bwd_tiled(x_cl.data_ptr(), dy_cl.data_ptr(), dx.data_ptr(), tg,
-                                          int(ctx.bwd_act[0]), float(ctx.bwd_act[1]),
-                                          native.dtype_code(x_cl.dtype), native.stream_ptr())
-            native.check(rc, "lb_pool_bwd_tiled")
+            rc = _lib().lb_pool_bwd_tiled_strided(x_cl.data_ptr(), dy_cl.data_ptr(), dx.data_ptr(), tg,
+                                                  int(ctx.bwd_act[0]), float(ctx.bwd_act[1]),
+                                                  dx.stride(0), native.dtype_code(x_cl.dtype),
+                                                  native.stream_ptr())
+            native.check(rc, "lb_pool_bwd_tiled_strided")
             native.count_launch()
-            return _from_cl(dx, ndim), None, None, None, None, None, None
+            return (_from_cl(dx, ndim),) + nothing
+        dx = torch.empty(x_cl.shape, dtype=x_cl.dtype, device=x_cl.device)
         xs = (c_ll * 4)(x_cl.stride(0), x_cl.stride(1), x_cl.stride(2), x_cl.stride(3))
         rc = _lib().lb_pool_bwd(x_cl.data_ptr(), dy_cl.data_ptr(), dx.data_ptr(), geom, xs,
                                 native.dtype_code(x_cl.dtype), native.stream_ptr())
@@ -579,17 +621,18 @@ class _Pool(torch.autograd.Function):
         native.count_launch()
         if ctx.bwd_act[0] != native.ACT_NONE:
             dx = _act_grad_from_output(x_cl, dx, ctx.bwd_act[0], ctx.bwd_act[1])
-        return _from_cl(dx, ndim), None, None, None, None, None, None
+        return (_from_cl(dx, ndim),) + nothing
 
 
 def pooling(x, ksize, pad, stride, mode: str, bwd_act: int = native.ACT_NONE,
-            bwd_act_param: float = 0.0):
+            bwd_act_param: float = 0.0, out_alloc=None, dx_alloc=None):
     """``bwd_act``: also apply the gradient of that activation (taken from the sign of x) in
-    the backward pass - used when the producer fused the activation into its epilogue."""
+    the backward pass - used when the producer fused the activation into its epilogue.
+    ``out_alloc`` / ``dx_alloc``: see ``_Pool``."""
     nsp = x.dim() - 2
     if _native_ok(x) and x.shape[1] % 8 == 0:
         return _Pool.apply(x, norm3(ksize, 1), norm3(pad, 0), norm3(stride, 1), _POOL_MODE[mode],
-                           int(bwd_act), float(bwd_act_param))
+                           int(bwd_act), float(bwd_act_param), out_alloc, dx_alloc)
     if bwd_act != native.ACT_NONE:
         raise RuntimeError("pooling: fused activation gradient needs the native path")
     ks, pd, st = tuple(ksize), tuple(pad), tuple(stride)
@@ -656,8 +699,10 @@ class _BatchNorm(torch.autograd.Function):
         # parameter gradients use the local partial sums (the optimizer's allreduce sums ranks)
         if sh is not None and sh.grad is not None:
             sh.grad.add_(bsums[:C])
+            sh.mark_ready()
         if bh is not None and bh.grad is not None:
             bh.grad.add_(bsums[C:2 * C])
+            bh.mark_ready()
         if reduce_fn is not None:
             reduce_fn(bsums[2 * C:])
         dx = torch.empty_like(x_cl)
@@ -779,6 +824,10 @@ class _LayerNorm(torch.autograd.Function):
                                               native.dtype_code(xc.dtype), native.stream_ptr()),
                      "lb_layer_norm_bwd")
         native.count_launch(2)
+        if dscale is not None:
+            sh.mark_ready()
+        if dbias is not None:
+            bh.mark_ready()
         return dx, None, None, None, None, None, None
 
 

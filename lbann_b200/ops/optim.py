@@ -34,6 +34,14 @@ def _lib():
                                            c_void_p, c_void_p, c_int, c_int, c_void_p]
         lib.lb_unscale_check.restype = c_int
         lib.lb_unscale_check.argtypes = [c_void_p, c_ll, c_float, c_void_p, c_int, c_void_p, c_int, c_void_p]
+        lib.lb_unscale_check_owned.restype = c_int
+        lib.lb_unscale_check_owned.argtypes = [c_void_p, c_ll, c_float, c_void_p, c_int, c_void_p, c_int,
+                                               c_int, c_int, c_int, c_void_p]
+        lib.lb_fused_optimizer_sharded.restype = c_int
+        lib.lb_fused_optimizer_sharded.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                   c_void_p, c_int, c_ll, c_float, c_void_p, c_void_p,
+                                                   c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                   c_void_p, c_void_p]
         lib.lb_amp_update.restype = c_int
         lib.lb_amp_update.argtypes = [c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_void_p]
         lib.lb_sqnorm.restype = c_int
@@ -46,6 +54,30 @@ def _lib():
 
 
 CHUNK = 1024
+OWN_CHUNKS = 16        # chunks per ownership block of a sharded update (64 KiB of fp32)
+
+
+class ArenaShard:
+    """Ownership of an arena whose optimizer update is sharded over the ranks of a group:
+    blocks of ``OWN_CHUNKS`` chunks are dealt round-robin, block b belongs to rank b % world.
+    Gradients of a block are reduced onto its owner, only the owner keeps optimizer state for
+    it and updates it, and the new values are stored into every rank's master arena
+    (``peer_master``: the peer-mapped addresses of the master arenas).  ``after_step`` runs
+    once the update has been launched (a rendezvous of the group)."""
+
+    def __init__(self, rank: int, world: int, peer_master, after_step=None):
+        self.rank, self.world = int(rank), int(world)
+        self.own_chunks = OWN_CHUNKS
+        self.own_elems = OWN_CHUNKS * CHUNK
+        self.peer_master = peer_master
+        self.after_step = after_step
+        self.state_whole = True      # False once a sharded step has run since the last gather
+
+    def owner_mask(self, numel: int, device) -> torch.Tensor:
+        """bool[numel]: elements whose block this rank owns."""
+        nb = (numel + self.own_elems - 1) // self.own_elems
+        own = (torch.arange(nb, device=device) % self.world) == self.rank
+        return own.repeat_interleave(self.own_elems)[:numel]
 
 
 class Slot:
@@ -98,6 +130,7 @@ class ParameterArena:
         self._seg_key = None
         self.step_dev = None      # int32[1] on the device: optimizer step number
         self.lr_scale_dev = None  # float32[1] on the device: global learning-rate multiplier
+        self.shard: Optional[ArenaShard] = None   # set when the update is sharded over ranks
 
     # ---- layout
     def reserve(self, name: str, shape) -> Slot:
@@ -149,6 +182,21 @@ class ParameterArena:
     def zero_grad(self):
         self.grad.zero_()
 
+    def gather_sharded_state(self, allreduce_sum) -> None:
+        """Make the optimizer state whole on every rank after sharded steps (checkpoints,
+        model exchange): each rank clears the blocks it does not own and the ranks sum.
+        ``allreduce_sum(tensor)`` sums in place over the group.  Collective."""
+        sh = self.shard
+        if sh is None or sh.state_whole:
+            return
+        mask = sh.owner_mask(self.state0.numel(), self.state0.device)
+        for st in (self.state0, self.state1):
+            if st is None:
+                continue
+            st.mul_(mask)
+            allreduce_sum(st)
+        sh.state_whole = True
+
     # ---- optimizer
     def _segments(self):
         blob = b"".join(s.segment_bytes() for s in self.slots)
@@ -188,15 +236,24 @@ class ParameterArena:
             if skip_flag is not None:
                 self.step_dev.sub_(skip_flag.to(torch.int32))   # a skipped step is not counted
             s1 = self.state1 if self.state1 is not None else self.state0
-            rc = _lib().lb_fused_optimizer(
+            sh = self.shard
+            rc = _lib().lb_fused_optimizer_sharded(
                 self.master.data_ptr(), self.grad.data_ptr(), self.state0.data_ptr(),
                 s1.data_ptr(), native.ptr(self.compute), segs.data_ptr(), len(self.slots),
                 self.total, float(inv_scale), native.ptr(skip_flag), self.step_dev.data_ptr(),
                 self.lr_scale_dev.data_ptr(), native.ptr(inv_scale_dev), native.dtype_code(self.grad.dtype),
                 native.dtype_code(self.compute.dtype) if self.compute is not None else native.DT_BF16,
-                native.stream_ptr())
-            native.check(rc, "lb_fused_optimizer")
+                sh.rank if sh else 0, sh.world if sh else 1, sh.own_chunks if sh else 1,
+                sh.peer_master if sh else None, native.stream_ptr())
+            native.check(rc, "lb_fused_optimizer_sharded")
             native.count_launch()
+            if sh is not None:
+                # every rank's stores must have landed before anybody reads the new weights;
+                # the 16-bit copy is then cast from the (whole) master arena
+                sh.state_whole = False
+                if sh.after_step is not None:
+                    sh.after_step()
+                self.refresh_compute()
             return
         self._step_cpu(inv_scale)
 
@@ -263,11 +320,13 @@ class ParameterArena:
         """grad *= inv_scale (optionally) and flag[0] |= any non-finite value.  With
         ``inv_scale_dev`` (a one-element fp32 CUDA tensor) the factor is read on the device."""
         if self.grad.is_cuda:
-            rc = _lib().lb_unscale_check(self.grad.data_ptr(), self.grad.numel(), float(inv_scale),
-                                         native.ptr(inv_scale_dev), 1 if write_back else 0,
-                                         flag.data_ptr(), native.dtype_code(self.grad.dtype),
-                                         native.stream_ptr())
-            native.check(rc, "lb_unscale_check")
+            sh = self.shard     # sharded update: every rank checks the chunks it owns
+            rc = _lib().lb_unscale_check_owned(self.grad.data_ptr(), self.grad.numel(), float(inv_scale),
+                                               native.ptr(inv_scale_dev), 1 if write_back else 0,
+                                               flag.data_ptr(), native.dtype_code(self.grad.dtype),
+                                               sh.rank if sh else 0, sh.world if sh else 1,
+                                               sh.own_chunks if sh else 1, native.stream_ptr())
+            native.check(rc, "lb_unscale_check_owned")
             native.count_launch()
             return
         g = self.grad.float() * inv_scale

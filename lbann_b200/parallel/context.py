@@ -19,6 +19,43 @@ import torch
 from .symm import SymmetricBuffer, SymmetricGroup
 
 
+def aligned_range(offset: int, count: int, element_size: int):
+    """Largest sub-range [off, end) of [offset, offset + count) whose two ends sit on 16-byte
+    boundaries of the arena (the all-reduce kernel moves 16-byte vectors)."""
+    v = max(16 // element_size, 1)
+    off = (offset + v - 1) // v * v
+    end = (offset + count) // v * v
+    return off, end
+
+
+def bucket_elements(bucket_bytes: int, element_size: int) -> int:
+    """Elements per gradient bucket: a whole number of 16-byte vectors."""
+    v = max(16 // element_size, 1)
+    return max(bucket_bytes // element_size, 1 << 16) // v * v
+
+
+class Bucket:
+    """A range [start, end) of the gradient arena reduced by one kernel launch."""
+
+    def __init__(self, start: int, end: int):
+        self.start, self.end = start, end
+        self.slots: List[int] = []     # trainable weights that overlap the range
+        self.pending = 0               # of those, how many have not reported their gradient
+        self.done = False
+
+
+def plan_buckets(slots, numel: int, per: int) -> List[Bucket]:
+    """Buckets of ``per`` elements covering the part of the arena that holds trainable
+    weights (``slots``: (offset, count) pairs).  Ranges without a trainable weight are left
+    out: nothing is reduced there."""
+    out = []
+    for start in range(0, numel, per):
+        end = min(start + per, numel)
+        if any(o < end and start < o + c for o, c in slots):
+            out.append(Bucket(start, end))
+    return out
+
+
 class ParallelContext:
     def __init__(self, comm, device):
         self.comm = comm
@@ -76,11 +113,6 @@ class ParallelContext:
             return t
         return alloc
 
-    def sync_initial_weights(self, model):
-        """All ranks of a trainer start from the trainer master's values."""
-        if self.world_size > 1:
-            self.comm.broadcast(model.arena.master, 0, "trainer")
-
     # ------------------------------------------------------------------ small reductions
     def allreduce_sum_inplace(self, t: torch.Tensor):
         if self.world_size == 1:
@@ -122,9 +154,41 @@ class ParallelContext:
         return reduce_fn, float(n)
 
     # ------------------------------------------------------------------ gradient sync
+    def sync_initial_weights(self, model):
+        """All ranks of a trainer start from the trainer master's values; on GPUs with more
+        than one rank the optimizer update is then sharded over the ranks."""
+        if self.world_size > 1:
+            self.comm.broadcast(model.arena.master, 0, "trainer")
+        self._setup_sharded_update(model)
+
+    def _setup_sharded_update(self, model):
+        """Reduce-scatter -> update the owned blocks -> store the new values into every rank's
+        master arena, instead of all-reduce -> the same update on every rank.  Needs the
+        master and gradient arenas in symmetric memory (``arena_allocator``)."""
+        from ..ops.optim import ArenaShard
+        from ..ops.native import c_void_p
+        arena = model.arena
+        if (self.world_size == 1 or not self.group.native or self.tp_size > 1
+                or os.environ.get("LBANN_REPLICATED_OPTIMIZER")):
+            return
+        mbuf = self._buffers.get(arena.master.data_ptr())
+        gbuf = self._buffers.get(arena.grad.data_ptr())
+        if mbuf is None or gbuf is None:
+            return
+        peers = (c_void_p * self.world_size)(*mbuf.peer_ptrs)
+        arena.shard = ArenaShard(self.rank, self.world_size, peers,
+                                 after_step=lambda: self.group.barrier_device(3))
+
+    def sync_optimizer_state(self, model):
+        """Collective: optimizer state sharded by ``_setup_sharded_update`` becomes whole on
+        every rank (before checkpoints and model exchanges)."""
+        model.arena.gather_sharded_state(lambda t: self.comm.allreduce(t, "trainer", "sum"))
+
     def sync_gradients(self, model):
         """Sum the gradient arena over the data-parallel ranks (loss terms are already
-        divided by the global mini-batch size, so the sum is the mean gradient)."""
+        divided by the global mini-batch size, so the sum is the mean gradient).  Buckets
+        whose gradients were complete during backward have been reduced on the communication
+        stream already (``_install_early_reduce``); the rest follows here."""
         if self.world_size == 1:
             return
         arena = model.arena
@@ -139,66 +203,79 @@ class ParallelContext:
             if scale != 1.0:
                 g.mul_(scale)
             return
-        es = arena.grad.element_size()
-        per = max(self.bucket_bytes // es, 1 << 16)
-        cur = torch.cuda.current_stream(self.device)
-        if not getattr(self, "_early_hooks", False):
+        if getattr(self, "_buckets", None) is None:
             self._install_early_reduce(model)
-        # ranges already handed to the communication stream during backward
-        done = sorted(getattr(self, "_early_ranges", []))
-        self._early_ranges = []
-        todo, pos = [], 0
-        for off, cnt in done:
-            if off > pos:
-                todo.append((pos, off - pos))
-            pos = max(pos, off + cnt)
-        if pos < n:
-            todo.append((pos, n - pos))
-        # reduce the rest on the communication stream, bucket by bucket, and join afterwards
+        cur = torch.cuda.current_stream(self.device)
         self.comm_stream.wait_stream(cur)
         with torch.cuda.stream(self.comm_stream):
-            for start, length in todo:
-                for off in range(start, start + length, per):
-                    cnt = min(per, start + length - off)
-                    self.group.allreduce_(buf, arena.grad.dtype, cnt, scale, off * es,
-                                          blocks=32 if cnt * es >= (4 << 20) else 8)
+            for b in self._buckets:
+                if not b.done:
+                    self._reduce_bucket(model, b)
         cur.wait_stream(self.comm_stream)
+        for b in self._buckets:            # next step
+            b.done, b.pending = False, len(b.slots)
+        for w in self._hooked:
+            w.handle.pending_uses = max(len(w.users), 1)
+
+    def _reduce_bucket(self, model, b):
+        arena = model.arena
+        buf = self._buffers[arena.grad.data_ptr()]
+        es = arena.grad.element_size()
+        scale = 1.0 / self.tp_size
+        big = (b.end - b.start) * es >= (4 << 20)
+        if arena.shard is not None:
+            self.group.reduce_scatter_owned_(buf, arena.grad.dtype, b.start, b.end,
+                                             arena.shard.own_elems, scale, blocks=48 if big else 8)
+        else:
+            self.group.allreduce_(buf, arena.grad.dtype, b.end - b.start, scale, b.start * es,
+                                  blocks=32 if big else 8)
+        b.done = True
 
     def _install_early_reduce(self, model):
-        """Large fully-connected weights that only one layer uses get a callback that starts
-        their gradient all-reduce on the communication stream as soon as the layer's backward
-        has written the gradient, so the transfer runs under the rest of backward (the
-        reference starts one non-blocking all-reduce per weight the same way,
-        include/lbann/optimizers/optimizer_impl.hpp:101-143).  The first step installs the
-        callbacks and reduces everything at the end."""
+        """Cuts the gradient arena into buckets and gives every trainable weight a callback:
+        when the last weight of a bucket reports its gradient complete (its layer's backward
+        has run), the bucket's reduction starts on the communication stream, under the rest of
+        backward.  The reference starts one non-blocking all-reduce per weight the same way
+        (include/lbann/optimizers/optimizer_impl.hpp:101-143); buckets keep the launches few."""
         import functools
-        self._early_hooks = True
-        self._early_ranges = []
-        if os.environ.get("LBANN_DISABLE_EARLY_GRAD_REDUCE"):
-            return
-        for w in model.weights:
-            handle = getattr(w, "handle", None)
-            if (handle is None or len(getattr(w, "users", [])) != 1 or w.slot.count < (1 << 20)
-                    or handle.grad is None):
-                continue
-            handle.on_grad_ready = functools.partial(self._early_reduce, model, w)
-
-    def _early_reduce(self, model, w):
+        from ..ops.optim import OWN_CHUNKS, CHUNK
         arena = model.arena
-        buf = self._buffers.get(arena.grad.data_ptr())
-        if buf is None or not self.group.native:
-            return
         es = arena.grad.element_size()
-        off = (w.slot.offset + 3) // 4 * 4
-        end = (w.slot.offset + w.slot.count) // 4 * 4
-        if end <= off:
-            return
-        ev = torch.cuda.Event()
-        ev.record(torch.cuda.current_stream(self.device))
-        self.comm_stream.wait_event(ev)
-        with torch.cuda.stream(self.comm_stream):
-            self.group.allreduce_(buf, arena.grad.dtype, end - off, 1.0 / self.tp_size, off * es, blocks=32)
-        self._early_ranges.append((off, end - off))
+        # bucket borders sit on ownership-block borders (and therefore on 16-byte borders)
+        blk = OWN_CHUNKS * CHUNK
+        per = max(bucket_elements(self.bucket_bytes, es) // blk, 1) * blk
+        self._buckets = plan_buckets([(w.slot.offset, w.slot.count) for w in model.weights
+                                      if getattr(w, "handle", None) is not None
+                                      and w.handle.grad is not None], arena.master.numel(), per)
+        self._hooked = []
+        early = not os.environ.get("LBANN_DISABLE_EARLY_GRAD_REDUCE")
+        trainable = [w for w in model.weights if getattr(w, "handle", None) is not None
+                     and w.handle.grad is not None]
+        for i, w in enumerate(trainable):
+            mine = [b for b in self._buckets if b.start < w.slot.offset + w.slot.count
+                    and w.slot.offset < b.end]
+            for b in mine:
+                b.slots.append(i)
+            if early:
+                w.handle.pending_uses = max(len(w.users), 1)
+                w.handle.on_grad_ready = functools.partial(self._grad_ready, model, mine)
+                # weights that a layer uses through PyTorch autograd (not through a native
+                # op that writes the arena itself) report when autograd has accumulated
+                w.handle.master.register_post_accumulate_grad_hook(
+                    lambda _p, h=w.handle: h.mark_ready())
+                self._hooked.append(w)
+        for b in self._buckets:
+            b.pending = len(b.slots)
+
+    def _grad_ready(self, model, buckets):
+        for b in buckets:
+            b.pending -= 1
+            if b.pending == 0 and not b.done and b.slots:
+                ev = torch.cuda.Event()
+                ev.record(torch.cuda.current_stream(self.device))
+                self.comm_stream.wait_event(ev)
+                with torch.cuda.stream(self.comm_stream):
+                    self._reduce_bucket(model, b)
 
     # ------------------------------------------------------------------ sub-graph parallelism
     def subgrids_active(self) -> bool:

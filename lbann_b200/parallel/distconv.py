@@ -7,12 +7,16 @@ distconv::Convolution's halo exchange, TensorMPICUDAShuffler) through its distco
 src/layers/learning/base_convolution.cpp:1326-1445) is done here with three differentiable
 primitives over symmetric memory:
 
-  HaloExchange   local slab [N, C, Dl, H, W] -> slab with `h` halo planes on both sides.
-                 One kernel copies the slab into the extended buffer, STORES the boundary
-                 planes straight into the neighbours' halo planes and runs the two group
-                 rendezvous that order the stores against the neighbours' consumers.
-                 Backward is one kernel too: halo gradients go back to their owners and are
-                 added to the boundary planes.
+  fused convolution  (GPUs) the activation lives in a symmetric buffer [N, Dl + 2h, H, W, C]
+                 whose inside the producing layer writes directly; the convolution kernel
+                 itself stores the boundary planes into the neighbours' halo planes, computes
+                 interior tiles meanwhile and waits on per-side arrival counters only before
+                 the first tile that reads a halo plane (csrc/halo_sync.cuh).  The data
+                 gradient is the same kernel on the extended output gradient; the filter
+                 gradient reads the extended input that forward left behind.
+  HaloExchange   (CPU ranks, overlapping pooling, odd channel counts) local slab
+                 [N, C, Dl, H, W] -> slab with `h` halo planes on both sides as one kernel
+                 beside the consumer; backward sends halo gradients back to their owners.
   to_sample_parallel / to_spatial   redistribution between "every rank holds a depth slab
                  of all samples" and "every rank holds all of some samples" (an all-to-all
                  by peer stores), used where distconv layers meet ordinary layers.
@@ -66,6 +70,7 @@ class DistconvContext:
             SymmetricGroup(self.device, pg=comm.trainer_group)
         self.strategies: Dict[str, Strategy] = {}
         self.depth_groups = 1
+        self.input_halo: Dict[str, int] = {}      # input layer -> halo planes uploaded with it
         self.num_sample_groups = 1
         self.sample_group_index = 0
         self.depth_rank = 0
@@ -73,6 +78,11 @@ class DistconvContext:
         self._enabled: Dict[str, bool] = {}
         self._bufs: Dict[tuple, SymmetricBuffer] = {}
         self.halo_bytes = 0
+        self._halo_tensors: Dict[tuple, "HaloTensor"] = {}
+        self._flags: Optional[SymmetricBuffer] = None     # arrival counters of all halo tensors
+        self._local_ctr: Optional[torch.Tensor] = None
+        self.interior_copies = 0          # forward / backward copies into a halo tensor (0 when
+                                          # the producing layer wrote there directly)
 
     # ------------------------------------------------------------------ set-up
     def prepare_model(self, model):
@@ -114,12 +124,23 @@ class DistconvContext:
                     dims = tr.data_coordinator.dims(l.params.data_field or "samples")
                     if len(dims) == 4 and dims[1] % depth == 0:
                         dl = dims[1] // depth
+                        # an input read by one convolution only is uploaded WITH its halo
+                        # planes (zeros beyond the volume): the first layer then needs no
+                        # exchange at all
+                        h = self._input_halo(kids) if self.group.native else 0
                         slicers[l.params.data_field or "samples"] = (2, self.depth_rank * dl,
-                                                                     (self.depth_rank + 1) * dl)
+                                                                     (self.depth_rank + 1) * dl, h)
+                        self.input_halo[l.name] = h
             tr.data_coordinator.field_slices = slicers
             self.sliced_fields = set(slicers)
         else:
             self.sliced_fields = set()
+
+    def _input_halo(self, kids) -> int:
+        if len(kids) != 1 or kids[0].type != "convolution" or kids[0].nd != 3:
+            return 0
+        k = kids[0]
+        return (k.ksize[0] - 1) // 2 * k.dil[0] if k.stride[0] == 1 and k.pad[0] == (k.ksize[0] - 1) // 2 * k.dil[0] else 0
 
     def enabled(self, layer) -> bool:
         hit = self._enabled.get(layer.name)       # static per layer once its dims are known
@@ -195,10 +216,55 @@ class DistconvContext:
         return b
 
     # ------------------------------------------------------------------ layer entry points
+    def step_barrier(self):
+        """Stream-ordered rendezvous of the trainer's ranks (needed between two steps that
+        have no other collective between them, see csrc/halo_sync.cuh)."""
+        if self.depth_groups > 1 and self.group.native:
+            self.group.barrier_device(3)
+
+    def halo_tensor(self, key: tuple, N, Dl, h, H, W, C, dtype) -> "HaloTensor":
+        """The symmetric tensor with halo planes of one use site (collective on first use:
+        every rank runs the same graph and asks in the same order)."""
+        full_key = key + (N, Dl, h, H, W, C, dtype)
+        t = self._halo_tensors.get(full_key)
+        if t is None:
+            if self._flags is None:
+                self._flags = self.group.alloc(4096 * 4)
+                self._flags.local.zero_()
+                self._local_ctr = torch.zeros(4096, dtype=torch.int32, device=self.device)
+                self.group.barrier_host()
+            t = HaloTensor(self, len(self._halo_tensors), full_key, N, Dl, h, H, W, C, dtype)
+            self._halo_tensors[full_key] = t
+        return t
+
+    def _fused_halo_ok(self, layer, x, hd: int) -> bool:
+        if not (self.group.native and hd > 0 and x.is_cuda and layer.nd == 3 and layer.groups == 1):
+            return False
+        if os.environ.get("LBANN_DISTCONV_HALO_EXCHANGE", "").upper() == "SEPARATE":
+            return False
+        Kout, Cin = layer.w.handle.master.shape[0], layer.w.handle.master.shape[1]
+        return (Kout % 8 == 0 and Cin % 8 == 0 and tuple(layer.stride) == (1, 1, 1)
+                and layer.pad[0] == hd and x.shape[2] > 2 * hd - 1 and x.shape[2] >= hd
+                and x.dtype in (torch.float16, torch.bfloat16)
+                and (x.shape[3] * x.shape[4] * Cin * 2) % 16 == 0
+                and self.depth_groups == self.group.world)
+
     def convolution(self, layer, x):
         from ..ops import nn
         halo = tuple((k - 1) // 2 * d for k, d in zip(layer.ksize, layer.dil))
         hd = halo[0] if layer.nd == 3 else 0
+        parent = layer.parent_names[0] if layer.parent_names else None
+        pre = self.input_halo.get(parent, 0)
+        if hd > 0 and pre == hd:
+            # the input was uploaded with its halo planes: an ordinary convolution, no exchange
+            pad = (0,) + tuple(layer.pad[1:])
+            return nn.convolution(x, layer.w.handle, None if layer.b is None else layer.b.handle,
+                                  layer.ksize, pad, layer.stride, layer.dil, layer.groups,
+                                  layer.fused_act[0], layer.fused_act[1],
+                                  getattr(layer, "skip_act_grad", False))
+        if self._fused_halo_ok(layer, x, hd):
+            return _DistConv.apply(x, layer.w.handle.master,
+                                   None if layer.b is None else layer.b.handle.master, self, layer, hd)
         xe = HaloExchange.apply(x, self, hd, layer.name) if hd > 0 else x
         pad = (0,) + tuple(layer.pad[1:]) if layer.nd == 3 and hd > 0 else layer.pad
         return nn.convolution(xe, layer.w.handle, None if layer.b is None else layer.b.handle,
@@ -225,7 +291,34 @@ class DistconvContext:
             pad = (0,) + tuple(layer.pad[1:])
             return nn.pooling(x, layer.k, pad, layer.stride, layer.mode)
         act = getattr(layer, "bwd_act", (0, 0.0))
-        return nn.pooling(x, layer.k, layer.pad, layer.stride, layer.mode, act[0], act[1])
+        out_alloc = dx_alloc = None
+        if self.group.native and x.is_cuda:
+            # write the output straight into the next convolution's tensor with halo planes,
+            # and the input gradient into the producing convolution's (no interior copies)
+            model = getattr(layer, "model", None)
+            kids = [model.layers_by_name[c] for c in layer.child_names] if model is not None else []
+            if len(kids) == 1 and kids[0].type == "convolution" and self.enabled(kids[0]):
+                k = kids[0]
+                hk = (k.ksize[0] - 1) // 2 * k.dil[0] if k.nd == 3 else 0
+
+                def out_alloc(shape, dtype, k=k, hk=hk):
+                    N, Do, Ho, Wo, C = shape
+                    probe = torch.empty((N, C, Do, Ho, Wo), dtype=dtype, device="meta")
+                    if not self._fused_halo_ok(k, _Shape(probe, self.device), hk):
+                        return None
+                    return self.halo_tensor(("x", k.name), N, Do, hk, Ho, Wo, C, dtype).interior
+            par = model.layers_by_name.get(layer.parent_names[0]) if model is not None else None
+            if (par is not None and par.type == "convolution" and self.enabled(par)
+                    and getattr(par, "skip_act_grad", False)):
+                hp = (par.ksize[0] - 1) // 2 * par.dil[0] if par.nd == 3 else 0
+
+                def dx_alloc(shape, dtype, par=par, hp=hp):
+                    N, D, H, W, C = shape
+                    if not getattr(par, "_fused_halo", False) or not getattr(par, "_needs_dx", False):
+                        return None
+                    return self.halo_tensor(("dy", par.name), N, D, hp, H, W, C, dtype).interior
+        return nn.pooling(x, layer.k, layer.pad, layer.stride, layer.mode, act[0], act[1],
+                          out_alloc, dx_alloc)
 
     def bn_reduction(self, layer):
         return self.parallel.allreduce_sum_inplace, float(self.world)
@@ -251,6 +344,131 @@ class DistconvContext:
             from ..ops import nn
             part = nn.sample_loss("cross_entropy", p, labels.to(p.dtype).reshape(p.shape)).reshape(-1, 1)
         return _AllReduceSum.apply(part, self)
+
+
+class _Shape:
+    """Stand-in for a tensor of which only shape / dtype / device matter."""
+
+    def __init__(self, meta: torch.Tensor, device):
+        self.shape, self.dtype = meta.shape, meta.dtype
+        self.is_cuda = torch.device(device).type == "cuda"
+
+
+class HaloTensor:
+    """A rank's [N, Dl + 2h, H, W, C] activation in symmetric memory plus what the fused
+    kernels need to exchange its halo planes: the neighbours' peer-mapped copies and the
+    arrival counters (two 32-bit words per tensor in a symmetric flag buffer; the launch
+    counters are local).  Planes beyond the global boundary stay zero: nobody writes them."""
+
+    def __init__(self, dc: "DistconvContext", slot: int, key, N, Dl, h, H, W, C, dtype):
+        from ..ops.conv import HaloSyncArgs
+        if slot >= 2048:
+            raise RuntimeError("too many tensors with halo planes")
+        es = torch.empty((), dtype=dtype).element_size()
+        n = N * (Dl + 2 * h) * H * W * C
+        self.buf = dc.buffer(("halo",) + tuple(key), n * es)
+        self.full = self.buf.view(dtype, n).view(N, Dl + 2 * h, H, W, C)
+        self.full.zero_()
+        dc.group.barrier_host()          # nobody sends before every rank has cleared
+        self.interior = self.full[:, h:h + Dl]
+        self.h, self.dl = h, Dl
+        r, P = dc.depth_rank, dc.depth_groups
+        up, down = (r - 1 if r > 0 else None), (r + 1 if r < P - 1 else None)
+        fl = dc._flags
+        a = HaloSyncArgs()
+        a.up_dst = self.buf.peer_ptr(up) if up is not None else None
+        a.down_dst = self.buf.peer_ptr(down) if down is not None else None
+        # my first planes land in the BOTTOM halo of the rank above, my last in the TOP halo below
+        a.up_flag = fl.peer_ptr(up, (2 * slot + 1) * 4) if up is not None else None
+        a.down_flag = fl.peer_ptr(down, (2 * slot) * 4) if down is not None else None
+        a.top_flag = fl.ptr + (2 * slot) * 4 if up is not None else None
+        a.bot_flag = fl.ptr + (2 * slot + 1) * 4 if down is not None else None
+        a.local = dc._local_ctr.data_ptr() + 2 * slot * 4
+        a.h = h
+        self.args = a
+        self.sent_bytes = N * h * H * W * C * es * ((up is not None) + (down is not None))
+
+    def holds(self, t: torch.Tensor) -> bool:
+        return (t.data_ptr() == self.interior.data_ptr() and t.shape == self.interior.shape
+                and t.stride() == self.interior.stride())
+
+
+class _DistConv(torch.autograd.Function):
+    """Convolution of a depth-partitioned activation with the halo exchange inside the
+    convolution kernels (forward and data gradient); see the module docstring.  Stands in
+    for src/layers/learning/base_convolution.cpp:1355-1445."""
+
+    @staticmethod
+    def forward(ctx, x, w_leaf, b_leaf, dc: "DistconvContext", layer, h: int):
+        from ..ops import native, nn
+        from ..ops.conv import conv_fwd
+        wh = layer.w.handle
+        bh = layer.b.handle if layer.b is not None else None
+        ksize, dil = tuple(layer.ksize), tuple(layer.dil)
+        pad = (0,) + tuple(layer.pad[1:])
+        act, act_p = layer.fused_act
+        skip_act_grad = bool(getattr(layer, "skip_act_grad", False))
+        x_cl = nn._cl_view(x)
+        N, Dl, H, W, C = x_cl.shape
+        Kout = wh.master.shape[0]
+        ext = dc.halo_tensor(("x", layer.name), N, Dl, h, H, W, C, x.dtype)
+        if not ext.holds(x_cl):
+            ext.interior.copy_(x_cl)
+            dc.interior_copies += 1
+        nn._pack_both(wh, x.dtype, Kout, C, Kout, C, ksize)
+        wt = wh.packed("fwd", x.dtype, lambda: nn.pack_filter(wh.master.detach(), x.dtype))
+        bias = bh.master.detach() if bh is not None else None
+        y = conv_fwd(ext.full, wt, ksize, pad=pad, stride=1, dilation=dil, bias=bias, act=act,
+                     act_param=act_p, halo=ext.args)
+        dc.halo_bytes += ext.sent_bytes
+        layer._fused_halo = True
+        layer._needs_dx = bool(ctx.needs_input_grad[0])
+        ctx.save_for_backward(y if (act != native.ACT_NONE and not skip_act_grad) else None)
+        ctx.meta = (dc, layer, h, ext, (N, Dl, H, W, C), Kout, act, act_p)
+        return nn._from_cl(y, 5)
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops import nn
+        from ..ops.conv import conv_fwd, conv_wgrad
+        (y,) = ctx.saved_tensors
+        dc, layer, h, ext, (N, Dl, H, W, C), Kout, act, act_p = ctx.meta
+        wh = layer.w.handle
+        bh = layer.b.handle if layer.b is not None else None
+        ksize, dil = tuple(layer.ksize), tuple(layer.dil)
+        pad = (0,) + tuple(layer.pad[1:])
+        dy_cl = nn._cl_view(dy)
+        Do, Ho, Wo = dy_cl.shape[1:4]
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dye = dc.halo_tensor(("dy", layer.name), N, Do, h, Ho, Wo, Kout, dy.dtype)
+            if y is not None:
+                dy_cl = nn._act_grad_from_output(y, dy_cl if dy_cl.is_contiguous() else dy_cl.contiguous(),
+                                                 act, act_p)
+            if not dye.holds(dy_cl):
+                dye.interior.copy_(dy_cl)
+                dc.interior_copies += 1
+            dy_cl = dye.interior
+            wt = wh.packed("dgrad", dy.dtype,
+                           lambda: nn.pack_filter(wh.master.detach(), dy.dtype, for_dgrad=True))
+            bpad = (0,) + tuple(d * (k - 1) - p for d, k, p in zip(dil[1:], ksize[1:], layer.pad[1:]))
+            dx_cl = conv_fwd(dye.full, wt, ksize, pad=bpad, stride=1, dilation=dil,
+                             out_dims=(Dl, H, W), halo=dye.args)
+            dc.halo_bytes += dye.sent_bytes
+            dx = nn._from_cl(dx_cl, 5)
+        elif y is not None:
+            dy_cl = nn._act_grad_from_output(y, dy_cl if dy_cl.is_contiguous() else dy_cl.contiguous(),
+                                             act, act_p)
+        if wh.grad is not None:
+            # the extended input still holds the halo planes that forward received
+            conv_wgrad(ext.full, dy_cl, ksize, pad=pad, stride=1, dilation=dil,
+                       out=wh.grad.view(Kout, C, *ksize))
+            wh.mark_ready()
+        if bh is not None and bh.grad is not None:
+            d2 = dy_cl if dy_cl.is_contiguous() else dy_cl.contiguous()
+            bh.grad.add_(nn.column_sums(d2.reshape(-1, Kout)))
+            bh.mark_ready()
+        return dx, None, None, None, None, None
 
 
 class _AllReduceSum(torch.autograd.Function):
@@ -286,40 +504,28 @@ class HaloExchange(torch.autograd.Function):
         x_cl = x.permute(0, 2, 3, 4, 1)
         g = dc.group
         ctx.meta = (dc, h, tag, (N, C, Dl, H, W))
-        if g.native and P == g.world and r == g.rank and not os.environ.get("LBANN_DISABLE_FUSED_HALO"):
+        if g.native and P == g.world and r == g.rank:
             # interior copy, boundary fill, peer stores and both rendezvous in one launch
             xs = x_cl if x_cl.is_contiguous() else x_cl.contiguous()
             if g.halo_forward(xs, buf, N, Dl, h, plane, fill):
                 dc.halo_bytes += 2 * N * h * plane
                 return xe.permute(0, 4, 1, 2, 3)
+        if g.native:
+            raise native.NativeError("halo exchange: the tensor's planes are not multiples of "
+                                     "16 bytes or it has fewer planes than the halo is wide")
+        # host-side ranks (gloo): same data movement with a library all-gather
         xe[:, h:h + Dl].copy_(x_cl)
         if r == 0:
             xe[:, :h].fill_(fill)
         if r == P - 1:
             xe[:, h + Dl:].fill_(fill)
-        src = xe  # boundary planes are read from the interior just written
-        pitch = (Dl + 2 * h) * plane
-        g = dc.group
-        ctx.meta = (dc, h, tag, (N, C, Dl, H, W))
-        if not g.native:
-            # host-side ranks (gloo): same data movement with a library all-gather
-            edges = torch.stack([xe[:, h:2 * h], xe[:, Dl:Dl + h]]).contiguous()
-            allp = dc.comm.all_gather(edges, "trainer")
-            if r > 0:
-                xe[:, :h].copy_(allp[r - 1][1])
-            if r < P - 1:
-                xe[:, h + Dl:].copy_(allp[r + 1][0])
-            return xe.permute(0, 4, 1, 2, 3).clone()
-        # neighbours must be done with the previous contents of their halo planes
-        g.barrier_device(2)
-        if r > 0:       # my first h planes -> upper halo of the rank above
-            g.put_rows(src[:, h:2 * h], buf, r - 1, (h + Dl) * plane, N, h * plane, pitch, pitch)
-        if r < P - 1:   # my last h planes -> lower halo of the rank below
-            g.put_rows(src[:, Dl:Dl + h], buf, r + 1, 0, N, h * plane, pitch, pitch)
-        g.barrier_device(3)
-        dc.halo_bytes += 2 * N * h * plane
-        ctx.meta = (dc, h, tag, (N, C, Dl, H, W))
-        return xe.permute(0, 4, 1, 2, 3)
+        edges = torch.stack([xe[:, h:2 * h], xe[:, Dl:Dl + h]]).contiguous()
+        allp = dc.comm.all_gather(edges, "trainer")
+        if r > 0:
+            xe[:, :h].copy_(allp[r - 1][1])
+        if r < P - 1:
+            xe[:, h + Dl:].copy_(allp[r + 1][0])
+        return xe.permute(0, 4, 1, 2, 3).clone()
 
     @staticmethod
     def backward(ctx, gxe):
@@ -342,22 +548,10 @@ class HaloExchange(torch.autograd.Function):
         buf = dc.buffer(("halo_bwd", tag), 2 * N * h * plane)
         pitch = (Dl + 2 * h) * plane
         grp = dc.group
-        if P == grp.world and r == grp.rank and not os.environ.get("LBANN_DISABLE_FUSED_HALO"):
-            dx = torch.empty((N, Dl, H, W, C), dtype=g_cl.dtype, device=g_cl.device)
-            if grp.halo_backward(g_cl, buf, dx, N, Dl, h, plane):
-                return dx.permute(0, 4, 1, 2, 3), None, None, None, None
-        if r > 0:       # gradient of the halo I received from above goes back up
-            grp.put_rows(g_cl[:, :h], buf, r - 1, N * h * plane, N, h * plane, pitch, h * plane)
-        if r < P - 1:
-            grp.put_rows(g_cl[:, h + Dl:], buf, r + 1, 0, N, h * plane, pitch, h * plane)
-        grp.barrier_device(3)
-        dx = g_cl[:, h:h + Dl].clone()
-        recv = buf.view(g_cl.dtype, 2 * N * h * H * W * C).view(2, N, h, H, W, C)
-        if r > 0:
-            dx[:, :h] += recv[0]       # written by the rank above (its lower halo gradient)
-        if r < P - 1:
-            dx[:, Dl - h:] += recv[1]  # written by the rank below
-        grp.barrier_device(2)          # receive area may be overwritten only after this
+        dx = torch.empty((N, Dl, H, W, C), dtype=g_cl.dtype, device=g_cl.device)
+        if not (P == grp.world and r == grp.rank and grp.halo_backward(g_cl, buf, dx, N, Dl, h, plane)):
+            raise native.NativeError("halo exchange (backward): the tensor's planes are not "
+                                     "multiples of 16 bytes or it has fewer planes than the halo is wide")
         return dx.permute(0, 4, 1, 2, 3), None, None, None, None
 
 

@@ -52,6 +52,9 @@ class FusedGemm:
         self.group = group
         self._maps = None
         self._stage = {}            # (rows, k, dtype) -> (gathered, flags)
+        self._stage_token = {}      # (rows, k, dtype) -> serial number of the call that staged last
+        self._calls = 0
+        self.last_stage_token = None
         self._epoch = 0
         self.helpers = 6            # copying CTAs of the staged all-gather -> GEMM
         self.bytes_over_nvlink = 0
@@ -128,8 +131,15 @@ class FusedGemm:
         staged = bool(staged) and shard_rows % 128 == 0 and P > 1
         gathered = flags = None
         epoch = 0
+        # Callers that want to reuse the gathered copy later (the data-gradient product of a
+        # sharded layer) keep the token of THEIR call: the copy is theirs only while no other
+        # call with the same operand shape has staged since, and only if this call staged.
+        self._calls += 1
+        self.last_stage_token = None
         if staged:
             gathered, flags, epoch = self._staging(shard_rows, k, dtype)
+            self._stage_token[(shard_rows, k, dtype)] = self._calls
+            self.last_stage_token = self._calls
         rc = _lib().lb_gemm_comm_tc(
             other.data_ptr() if sharded == "b" else None, other.data_ptr() if sharded == "a" else None,
             out.data_ptr(), M, N, k, k, k, out.stride(0), 0, 0, native.dtype_code(dtype),

@@ -40,6 +40,9 @@ def _lib():
         lib.lb_allreduce_two_shot.restype = c_int
         lib.lb_allreduce_two_shot.argtypes = [vpp, vpp, c_int, c_int, c_ll, c_float, c_void_p,
                                               c_int, c_int, c_void_p]
+        lib.lb_reduce_scatter_owned.restype = c_int
+        lib.lb_reduce_scatter_owned.argtypes = [vpp, vpp, c_int, c_int, c_ll, c_ll, c_ll, c_float,
+                                                c_void_p, c_int, c_int, c_void_p]
         lib.lb_allreduce_one_shot.restype = c_int
         lib.lb_allreduce_one_shot.argtypes = [vpp, vpp, c_int, c_int, c_void_p, c_void_p, c_int,
                                               c_int, c_ll, c_void_p, c_void_p]
@@ -183,6 +186,30 @@ class SymmetricGroup:
         native.count_launch()
         es = torch.empty((), dtype=dtype).element_size()
         self.bytes_moved += 2 * numel * es * (self.world - 1) // self.world
+
+    def reduce_scatter_owned_(self, buf: SymmetricBuffer, dtype: torch.dtype, e0: int, e1: int,
+                              own_elems: int, scale: float = 1.0, blocks: int = 48):
+        """Elements [e0, e1) of ``buf``: every ownership block (``own_elems`` elements, block b
+        owned by rank b % world) ends up summed over the group, times ``scale``, in its
+        owner's buffer.  The other ranks' copies of the block keep their own contribution.
+        No closing rendezvous: call a later collective before the buffers are overwritten."""
+        if self.world == 1:
+            if scale != 1.0:
+                buf.view(dtype)[e0:e1].mul_(scale)
+            return
+        if not self.native:
+            t = buf.view(dtype)[e0:e1]
+            dist.all_reduce(t, group=self.pg)
+            if scale != 1.0:
+                t.mul_(scale)
+            return
+        rc = _lib().lb_reduce_scatter_owned(buf._c_ptrs, self.pad._c_ptrs, self.rank, self.world,
+                                            e0, e1, own_elems, float(scale), self.ctr_ptr,
+                                            native.dtype_code(dtype), blocks, native.stream_ptr())
+        native.check(rc, "lb_reduce_scatter_owned")
+        native.count_launch()
+        es = torch.empty((), dtype=dtype).element_size()
+        self.bytes_moved += (e1 - e0) * es * (self.world - 1) // self.world
 
     def allreduce_small_(self, t: torch.Tensor, op: str = "sum"):
         """In-place all-reduce of a short fp32 tensor (<= 4096 elements) in one kernel."""

@@ -253,6 +253,7 @@ class _Sharded(torch.autograd.Function):
         wbuf = layer.compute_shard(dt)
         y = fg.allgather_gemm(wbuf, rows, k, x.contiguous(), sharded="b", dtype=dt)
         ctx.layer = layer
+        ctx.stage_token = fg.last_stage_token    # None when this forward did not stage
         ctx.save_for_backward(x)
         return y
 
@@ -264,7 +265,7 @@ class _Sharded(torch.autograd.Function):
         rows, k = layer.shard_rows, layer.k
         dt = dy.dtype
         dy = dy.contiguous()
-        w_full = layer.gathered_weight(dt)
+        w_full = layer.gathered_weight(dt, ctx.stage_token)
         if x.is_cuda:
             from ..ops.gemm import gemm
             dx = gemm(dy, w_full)
@@ -295,13 +296,17 @@ class ShardedLinear:
         buf.view(dtype, n).view(self.shard_rows, self.k).copy_(self.w_shard.detach())
         return buf
 
-    def gathered_weight(self, dtype) -> torch.Tensor:
-        """The full weight matrix for the data-gradient product: the staged copy that the
-        forward kernel left in local memory when it staged, else a plain gather."""
+    def gathered_weight(self, dtype, stage_token=None) -> torch.Tensor:
+        """The full weight matrix for the data-gradient product.  ``stage_token`` is what the
+        matching forward call left in ``FusedGemm.last_stage_token``: the staged copy in local
+        memory is used only when that forward staged (small mini-batches do not) and no other
+        call of the same operand shape has overwritten the copy since; otherwise the shards
+        are gathered again."""
         key = (self.shard_rows, self.k, dtype)
         st = self.fused._stage.get(key)
         g = self.group
-        if st is not None and g.native:
+        if (st is not None and g.native and stage_token is not None
+                and self.fused._stage_token.get(key) == stage_token):
             full = st[0]
             # the local rows are read from the shard itself in the forward kernel: fill them in
             full[g.rank * self.shard_rows:(g.rank + 1) * self.shard_rows].copy_(self.w_shard.detach())

@@ -14,14 +14,16 @@ from lbann_b200.models.cosmoflow import construct_cosmoflow_model, synthetic_rea
 from lbann_b200.utils import options as opts  # noqa: E402
 
 
-def cosmoflow(depth_groups, steps, dtype, width=32):
+def cosmoflow(depth_groups, steps, dtype, width=32, channels=(8, 16, 16), graph=False):
     o = opts.reset()
     o.set("default_dtype", dtype)
     if os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cpu":
         o.set("disable_cuda", True)
+    if graph:
+        o.set("use_cuda_graph", True)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     ps = lbann.get_parallel_strategy_args(depth_groups=depth_groups) if depth_groups > 1 else None
-    model = construct_cosmoflow_model(width, 4, 4, num_epochs=1, channels=(8, 16, 16), pool_mode="max",
+    model = construct_cosmoflow_model(width, 4, 4, num_epochs=1, channels=tuple(channels), pool_mode="max",
                                       conv_bias=False, fc_sizes=(32, 16), parallel_strategy=ps)
     exp = lbann.proto.serialize.build_experiment(
         trainer=lbann.Trainer(mini_batch_size=4, random_seed=5), model=model,
@@ -40,8 +42,19 @@ def cosmoflow(depth_groups, steps, dtype, width=32):
             tr.comm.allreduce(v, "trainer", "sum")
         losses.append(float(v))
     w = {x.name: float(x.values.detach().float().norm()) for x in m.weights}
+    res = {"losses": losses, "weight_norms": w, "world": world}
+    if tr.distconv is not None:
+        res["interior_copies"] = tr.distconv.interior_copies
+        res["halo_bytes"] = tr.distconv.halo_bytes
+        res["halo_tensors"] = len(tr.distconv._halo_tensors)
+    if torch.cuda.is_available() and os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cuda":
+        from lbann_b200.ops import native
+        torch.cuda.synchronize()
+        res["status"] = native.consume_status(False)
+        res["sharded_update"] = m.arena.shard is not None
+        res["graph"] = bool(getattr(m, "_graph_mode", False))
     tr.shutdown()
-    return {"losses": losses, "weight_norms": w, "world": world}
+    return res
 
 
 def comm_kernels():
@@ -265,8 +278,19 @@ def model_parallel_fc(grid_height, steps, sharded=False):
             tr.comm.allreduce(v, "trainer", "sum")       # local objectives are partial sums
         losses.append(float(v))
     w = {x.name: float(x.values.detach().float().norm()) for x in m.weights}
+    res = {"losses": losses, "weight_norms": w, "world": world}
+    if tr.distconv is not None:
+        res["interior_copies"] = tr.distconv.interior_copies
+        res["halo_bytes"] = tr.distconv.halo_bytes
+        res["halo_tensors"] = len(tr.distconv._halo_tensors)
+    if torch.cuda.is_available() and os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cuda":
+        from lbann_b200.ops import native
+        torch.cuda.synchronize()
+        res["status"] = native.consume_status(False)
+        res["sharded_update"] = m.arena.shard is not None
+        res["graph"] = bool(getattr(m, "_graph_mode", False))
     tr.shutdown()
-    return {"losses": losses, "weight_norms": w, "world": world}
+    return res
 
 
 def dist_embedding(steps):
@@ -402,7 +426,9 @@ if __name__ == "__main__":
         res = model_parallel_fc(int(sys.argv[3]), int(sys.argv[4]), len(sys.argv) > 5 and sys.argv[5] == "sharded")
     elif what == "cosmoflow":
         res = cosmoflow(int(sys.argv[3]), int(sys.argv[4]), sys.argv[5] if len(sys.argv) > 5 else "float",
-                        int(sys.argv[6]) if len(sys.argv) > 6 else 32)
+                        int(sys.argv[6]) if len(sys.argv) > 6 else 32,
+                        tuple(int(c) for c in sys.argv[7].split(",")) if len(sys.argv) > 7 else (8, 16, 16),
+                        len(sys.argv) > 8 and sys.argv[8] == "graph")
     else:
         raise SystemExit(f"unknown job {what}")
     if int(os.environ.get("RANK", "0")) == 0:
