@@ -221,6 +221,29 @@ put_rows_kernel(const uint8_t* __restrict__ src, long long src_pitch, uint8_t* _
   }
 }
 
+// All-to-all of equal slabs as ONE kernel (tensor shuffles between "every rank holds a depth
+// slab of all samples" and "every rank holds all of some samples", either direction): slab i
+// of the local source goes to rank i % world, slot (i / world) * world + rank of that rank's
+// buffer.  Peer stores, then one rendezvous that makes them visible to the consumers that
+// follow in the stream.  Nothing here keeps a destination from being overwritten while it
+// is still read: the caller separates two uses of a buffer by another rendezvous of the
+// group (one per training step suffices).
+__global__ void __launch_bounds__(512)
+alltoall_slabs_kernel(PeerPtrs pp, int rank, int world, const uint4* __restrict__ src,
+                      long long count, long long slab_vec, uint32_t* ctr, int* status) {
+  __shared__ uint4* dst[kMaxRanks];
+  if ((int)threadIdx.x < world) dst[threadIdx.x] = reinterpret_cast<uint4*>(pp.buf[threadIdx.x]);
+  __syncthreads();
+  const long long total = count * slab_vec;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long i = idx / slab_vec, v = idx - i * slab_vec;
+    const int q = (int)(i % world);
+    dst[q][((i / world) * world + rank) * slab_vec + v] = src[idx];
+  }
+  block_rendezvous(pp, rank, world, 3, ctr, status);
+}
+
 // Group barrier as its own (single block) kernel: orders "my puts are visible" with the
 // peers' consumers.  phase selects an independent flag row.
 __global__ void group_barrier_kernel(PeerPtrs pp, int rank, int world, int phase, uint32_t* ctr,
@@ -584,6 +607,22 @@ int lb_dist_embed_scatter(void* const* tables, void* const* pads, int rank, int 
     dist_embed_scatter_kernel<__nv_bfloat16><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (const __nv_bfloat16*)dy, n, dim, num_embeddings, scale, ctr, lbhost::status_word());
   else
     dist_embed_scatter_kernel<__half><<<blocks, 256, 0, s>>>(pp, rank, world, idx, (const __half*)dy, n, dim, num_embeddings, scale, ctr, lbhost::status_word());
+  return (int)cudaGetLastError();
+}
+
+// bufs: the receive buffers of the group's ranks; src: `count` slabs of slab_bytes bytes.
+int lb_alltoall_slabs(void* const* bufs, void* const* pads, int rank, int world, const void* src,
+                      long long count, long long slab_bytes, unsigned* ctr, void* stream_) {
+  using namespace lb;
+  if (world < 2 || world > kMaxRanks || count < 0 || slab_bytes <= 0) return -1;
+  if (slab_bytes % 16 || (reinterpret_cast<uintptr_t>(src) & 15)) return -2;
+  for (int r = 0; r < world; ++r)
+    if (reinterpret_cast<uintptr_t>(bufs[r]) & 15) return -2;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  PeerPtrs pp = make_ptrs(bufs, pads, world);
+  // every rank launches the same number of blocks (they meet pairwise), whatever its count
+  alltoall_slabs_kernel<<<kCommBlocks, 512, 0, s>>>(pp, rank, world, reinterpret_cast<const uint4*>(src),
+                                                     count, slab_bytes / 16, ctr, lbhost::status_word());
   return (int)cudaGetLastError();
 }
 

@@ -137,10 +137,22 @@ class DistconvContext:
             self.sliced_fields = set()
 
     def _input_halo(self, kids) -> int:
-        if len(kids) != 1 or kids[0].type != "convolution" or kids[0].nd != 3:
+        """Halo planes to upload with an input: what its only consumer, a stride-1 3-D
+        convolution with "same" padding along depth, reads from the neighbouring slabs
+        (layers are not set up yet at this point: the numbers come from the prototext)."""
+        if len(kids) != 1 or kids[0].type != "convolution":
             return 0
-        k = kids[0]
-        return (k.ksize[0] - 1) // 2 * k.dil[0] if k.stride[0] == 1 and k.pad[0] == (k.ksize[0] - 1) // 2 * k.dil[0] else 0
+        from ..exec.layer_base import broadcast_list
+        p = kids[0].params
+        nd = int(p.num_dims) or 3
+        if nd != 3:
+            return 0
+        k = broadcast_list(p.kernel_size, nd, 1)[0]
+        s = broadcast_list(p.stride, nd, 1)[0]
+        pad = broadcast_list(p.padding, nd, 0)[0]
+        d = broadcast_list(p.dilation, nd, 1)[0]
+        h = (k - 1) // 2 * d
+        return h if (s == 1 and pad == h) else 0
 
     def enabled(self, layer) -> bool:
         hit = self._enabled.get(layer.name)       # static per layer once its dims are known
@@ -308,6 +320,8 @@ class DistconvContext:
                         return None
                     return self.halo_tensor(("x", k.name), N, Do, hk, Ho, Wo, C, dtype).interior
             par = model.layers_by_name.get(layer.parent_names[0]) if model is not None else None
+            while par is not None and getattr(par, "fused_into_parent", False) and par.parent_names:
+                par = model.layers_by_name.get(par.parent_names[0])   # an activation folded into its producer
             if (par is not None and par.type == "convolution" and self.enabled(par)
                     and getattr(par, "skip_act_grad", False)):
                 hp = (par.ksize[0] - 1) // 2 * par.dil[0] if par.nd == 3 else 0
@@ -591,15 +605,19 @@ def _redistribute(x, dc: DistconvContext, to_sample: bool, tag: str):
         ns = (N + P - 1) // P                           # samples per rank (round-robin owner)
         slab = Dl * H * W * C * es
         buf = dc.buffer(("redist", tag), ns * P * slab)
+        mine = len(range(r, N, P))
+        view = buf.view(x_cl.dtype, ns * P * Dl * H * W * C).view(ns, P * Dl, H, W, C)
+        # sample n, depth slab r -> slot [n // P][r] of owner n % P: one kernel, one rendezvous;
+        # the result is read where it landed (two uses of the buffer are a training step apart)
+        if grp.alltoall_slabs(x_cl, buf, N, slab):
+            return view[:mine].permute(0, 4, 1, 2, 3)
         for q in range(P):
             rows = x_cl[q::P]
             if rows.shape[0] == 0:
                 continue
-            # sample j of owner q, depth slab r -> [j][r] in q's buffer
             grp.put_rows(rows, buf, q, r * slab, rows.shape[0], slab, P * slab, P * slab)
         grp.barrier_device(3)
-        mine = len(range(r, N, P))
-        out = buf.view(x_cl.dtype, ns * P * Dl * H * W * C).view(ns, P * Dl, H, W, C)[:mine].clone()
+        out = view[:mine].clone()
         grp.barrier_device(2)
         return out.permute(0, 4, 1, 2, 3)
     ns, D, H, W, C = x_cl.shape
@@ -608,11 +626,14 @@ def _redistribute(x, dc: DistconvContext, to_sample: bool, tag: str):
     # every rank owns ns samples (equal counts are required for the inverse map)
     N = ns * P
     buf = dc.buffer(("redist", tag), N * slab)
+    view = buf.view(x_cl.dtype, N * Dl * H * W * C).view(N, Dl, H, W, C)
+    # my sample j (global index j * P + r), depth slab q -> row j * P + r of rank q's buffer
+    if grp.alltoall_slabs(x_cl, buf, ns * P, slab):
+        return view.permute(0, 4, 1, 2, 3)
     for q in range(P):
-        # my sample j (global index j*P + r), depth slab q -> row (j*P + r) of q's buffer
         src = x_cl[:, q * Dl:(q + 1) * Dl]
         grp.put_rows(src, buf, q, r * slab, ns, slab, D * H * W * C * es, P * slab)
     grp.barrier_device(3)
-    out = buf.view(x_cl.dtype, N * Dl * H * W * C).view(N, Dl, H, W, C).clone()
+    out = view.clone()
     grp.barrier_device(2)
     return out.permute(0, 4, 1, 2, 3)

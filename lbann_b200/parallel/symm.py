@@ -54,6 +54,8 @@ def _lib():
         lib.lb_halo_exchange_bwd.restype = c_int
         lib.lb_halo_exchange_bwd.argtypes = [vpp, vpp, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                              c_ll, c_ll, c_ll, c_ll, c_int, c_void_p, c_void_p]
+        lib.lb_alltoall_slabs.restype = c_int
+        lib.lb_alltoall_slabs.argtypes = [vpp, vpp, c_int, c_int, c_void_p, c_ll, c_ll, c_void_p, c_void_p]
         lib.lb_group_barrier.restype = c_int
         lib.lb_group_barrier.argtypes = [vpp, vpp, c_int, c_int, c_int, c_void_p, c_void_p]
         _configured = True
@@ -274,6 +276,20 @@ class SymmetricGroup:
         native.check(rc, "lb_halo_exchange_bwd")
         native.count_launch()
         self.bytes_moved += n * h * plane_bytes * ((up >= 0) + (down >= 0))
+        return True
+
+    def alltoall_slabs(self, src: torch.Tensor, dst: SymmetricBuffer, count: int, slab_bytes: int) -> bool:
+        """One kernel: slab i of ``src`` (``count`` contiguous slabs) -> rank i % world, slot
+        (i // world) * world + rank of ``dst``; ends with a rendezvous of the group.  Returns
+        False when the slabs are not multiples of 16 bytes (the caller falls back to puts)."""
+        rc = _lib().lb_alltoall_slabs(dst._c_ptrs, self.pad._c_ptrs, self.rank, self.world,
+                                      src.data_ptr(), count, slab_bytes, self.ctr_ptr,
+                                      native.stream_ptr())
+        if rc == -2:
+            return False
+        native.check(rc, "lb_alltoall_slabs")
+        native.count_launch()
+        self.bytes_moved += count * slab_bytes * (self.world - 1) // self.world
         return True
 
     def barrier_device(self, phase: int = 3):

@@ -28,7 +28,7 @@ def cosmoflow(depth_groups, steps, dtype, width=32, channels=(8, 16, 16), graph=
     exp = lbann.proto.serialize.build_experiment(
         trainer=lbann.Trainer(mini_batch_size=4, random_seed=5), model=model,
         data_reader=synthetic_reader(16, width, 4, 4),
-        optimizer=lbann.SGD(learn_rate=0.01, momentum=0.9))
+        optimizer=lbann.SGD(learn_rate=float(os.environ.get("LBANN_TEST_LR", "0.01")), momentum=0.9))
     tr = ExecTrainer(exp)
     m = tr.build_model(exp.model)
     losses = []
@@ -36,6 +36,9 @@ def cosmoflow(depth_groups, steps, dtype, width=32, channels=(8, 16, 16), graph=
     dc.start_epoch("training")
     for _ in range(steps):
         b = dc.next_batch("training")
+        if b is None:                       # end of the epoch: the next one reshuffles nothing
+            dc.start_epoch("training")
+            b = dc.next_batch("training")
         m.train_step(b.tensors, b.global_size)
         v = m.last_objective.detach().float().reshape(1).clone()
         if tr.parallel is not None:

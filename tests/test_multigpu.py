@@ -10,6 +10,9 @@ pytestmark = pytest.mark.gpu
 
 needs2 = pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
 ENV = {"LBANN_TEST_DEVICE": "cuda", "NCCL_NVLS_ENABLE": "0"}
+# a learning rate at which the small CosmoFlow stays a contraction, so that runs can be compared
+# over more than a couple of steps
+STABLE = dict(ENV, LBANN_TEST_LR="0.0005")
 
 
 @needs2
@@ -30,8 +33,8 @@ def test_distconv_two_gpus_matches_one(tmp_path, width, channels, graph):
     producer wrote straight into its consumer's tensor with halo planes), clean status."""
     steps = "8" if graph else "5"
     tail = [width, channels] + ([graph] if graph else [])
-    single = _run(1, ["cosmoflow", "1", steps, "fp16"] + tail, str(tmp_path / "a.json"), ENV)
-    dist = _run(2, ["cosmoflow", "2", steps, "fp16"] + tail, str(tmp_path / "b.json"), ENV)
+    single = _run(1, ["cosmoflow", "1", steps, "fp16"] + tail, str(tmp_path / "a.json"), STABLE)
+    dist = _run(2, ["cosmoflow", "2", steps, "fp16"] + tail, str(tmp_path / "b.json"), STABLE)
     assert dist["status"] == 0 and dist["sharded_update"]
     assert dist["halo_tensors"] >= 4 and dist["halo_bytes"] > 0
     assert dist["interior_copies"] == 0, dist
@@ -44,12 +47,26 @@ def test_distconv_two_gpus_matches_one(tmp_path, width, channels, graph):
 
 
 @needs2
+def test_distconv_shuffle_to_sample_parallel_on_gpus(tmp_path):
+    """An 8^3 volume on two GPUs: the last pooling would see one plane per rank, so the
+    tensor is redistributed to sample-parallel in front of it (one all-to-all kernel each
+    way) and the rest of the network runs data-parallel; same results as one GPU."""
+    single = _run(1, ["cosmoflow", "1", "4", "fp16", "8"], str(tmp_path / "a.json"), STABLE)
+    dist = _run(2, ["cosmoflow", "2", "4", "fp16", "8"], str(tmp_path / "b.json"), STABLE)
+    assert dist["status"] == 0
+    for a, b in zip(single["losses"], dist["losses"]):
+        assert abs(a - b) <= 1e-2 * max(1.0, abs(a)), (single["losses"], dist["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - dist["weight_norms"][k]) <= 5e-3 * max(1.0, abs(v)), k
+
+
+@needs2
 def test_sharded_update_matches_replicated(tmp_path):
     """Reduce-scatter -> update of the owned blocks -> peer stores of the new values gives
     the same trajectory as all-reduce -> the same update on every rank."""
-    a = _run(2, ["cosmoflow", "2", "5", "fp16"], str(tmp_path / "a.json"), ENV)
+    a = _run(2, ["cosmoflow", "2", "5", "fp16"], str(tmp_path / "a.json"), STABLE)
     b = _run(2, ["cosmoflow", "2", "5", "fp16"], str(tmp_path / "b.json"),
-             dict(ENV, LBANN_REPLICATED_OPTIMIZER="1"))
+             dict(STABLE, LBANN_REPLICATED_OPTIMIZER="1"))
     assert a["sharded_update"] and not b["sharded_update"]
     for x, y in zip(a["losses"], b["losses"]):
         assert abs(x - y) <= 1e-3 * max(1.0, abs(x)), (a["losses"], b["losses"])
