@@ -25,6 +25,77 @@ def build(width):
     return nn.Sequential(*layers)
 
 
+def measure_torch(steps, warm, global_batch, width):
+    """The comparison arm inside an already initialised process group (called by bench.py
+    after its own measurement): same model, cuDNN autotuning on, DistributedDataParallel over
+    NCCL when there are several ranks.  Returns a dict (device-timed and end to end)."""
+    import torch.distributed as dist
+    world = dist.get_world_size() if dist.is_initialized() else 1
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dev = torch.device("cuda", local)
+    torch.backends.cudnn.benchmark = True           # the reference autotunes (cudnnFind*Ex)
+    torch.manual_seed(1)
+    model = build(width).to(dev).to(memory_format=torch.channels_last_3d)
+    if world > 1:
+        model = nn.parallel.DistributedDataParallel(model, device_ids=[local])
+    opt = torch.optim.Adam(model.parameters(), lr=1e-3, betas=(0.9, 0.99), eps=1e-8, fused=True)
+    scaler = torch.amp.GradScaler("cuda", init_scale=128.0)
+    nb = max(global_batch // world, 1)
+    batches = []
+    for i in range(2):
+        x = torch.randn(nb, 4, width, width, width, device=dev).exp().half().contiguous(
+            memory_format=torch.channels_last_3d)
+        batches.append((x, torch.rand(nb, 4, device=dev) * 2 - 1))
+
+    def step(x, y):
+        opt.zero_grad(set_to_none=True)
+        with torch.autocast("cuda", dtype=torch.float16):
+            out = model(x)
+        loss = nn.functional.mse_loss(out.float(), y)
+        scaler.scale(loss).backward()
+        scaler.step(opt)
+        scaler.update()
+        return loss
+
+    for i in range(max(warm, 3) + 2):
+        step(*batches[i % 2])
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(steps):
+        loss = step(*batches[i % 2])
+    e1.record()
+    torch.cuda.synchronize()
+    ms = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    hx = [b[0].cpu().pin_memory() for b in batches]
+    hy = [b[1].cpu().pin_memory() for b in batches]
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    t0 = time.perf_counter()
+    for i in range(steps):
+        x = hx[i % 2].to(dev, non_blocking=True)
+        y = hy[i % 2].to(dev, non_blocking=True)
+        float(step(x, y))
+    torch.cuda.synchronize()
+    e2e = torch.tensor([(time.perf_counter() - t0) * 1e3], device=dev)
+    if world > 1:
+        dist.all_reduce(ms, dist.ReduceOp.MAX)
+        dist.all_reduce(e2e, dist.ReduceOp.MAX)
+    ms, e2e = float(ms), float(e2e)
+    out = {"impl": "torch + cuDNN (benchmark mode) + NCCL DDP", "n_gpus": world,
+           "global_batch": nb * world, "ms_per_step": round(ms / steps, 4),
+           "value": round(nb * world * steps / (ms / 1e3), 3), "unit": "samples/s",
+           "e2e": {"value": round(nb * world * steps / (e2e / 1e3), 3), "unit": "samples/s"},
+           "final_loss": float(loss), "loss_scale": float(scaler.get_scale()),
+           "parallelism": f"ddp x{world} (sample parallel)" if world > 1 else "single GPU"}
+    del model, opt, batches, hx, hy
+    torch.cuda.empty_cache()
+    return out
+
+
 def run(args, global_batch, width, baseline, ClockSampler):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
@@ -34,11 +105,12 @@ def run(args, global_batch, width, baseline, ClockSampler):
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=dev)
     torch.manual_seed(1)
+    torch.backends.cudnn.benchmark = True           # the reference autotunes (cudnnFind*Ex)
     model = build(width).to(dev).to(memory_format=torch.channels_last_3d)
     if world > 1:
         model = nn.parallel.DistributedDataParallel(model, device_ids=[local])
     opt = torch.optim.Adam(model.parameters(), lr=1e-3, betas=(0.9, 0.99), eps=1e-8, fused=True)
-    scaler = torch.amp.GradScaler("cuda", init_scale=1024.0)
+    scaler = torch.amp.GradScaler("cuda", init_scale=128.0)
     nb = max(global_batch // world, 1)
     batches = []
     for i in range(2):

@@ -34,8 +34,6 @@ def _build(lbann, args, world):
         r.num_labels = 1000
         r.synth_pool_size = 2 * args.batch * world
         opt = lbann.SGD(learn_rate=0.1, momentum=0.9)
-        for w in []:
-            pass
     elif args.model == "unet3d":
         # 3D U-Net with batch norm, per-voxel 3-class cross-entropy; with several ranks the
         # depth dimension is split over them (strong scaling of one global mini-batch)

@@ -1,7 +1,7 @@
 """Timing of the fused GEMM + collective kernels against their NCCL + GEMM baselines.
 
     python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 \\
-        -m lbann_b200.parallel.fused_bench [--tokens 8192 --d-model 2048 --ffn 8192]
+        -m benchmarks.fused_bench [--tokens 8192 --d-model 2048 --ffn 8192]
 
 Shapes follow one transformer FFN: the activations ``[tokens, d_model]`` are sharded by
 rows over the ranks (all-gather -> GEMM against a ``[ffn, d_model]`` weight), and the
@@ -20,11 +20,11 @@ import os
 import torch
 import torch.distributed as dist
 
-from ..ops import native
-from ..ops.gemm import gemm
-from .comm import LbannComm
-from .fused import FusedGemm
-from .symm import SymmetricGroup
+from lbann_b200.ops import native
+from lbann_b200.ops.gemm import gemm
+from lbann_b200.parallel.comm import LbannComm
+from lbann_b200.parallel.fused import FusedGemm
+from lbann_b200.parallel.symm import SymmetricGroup
 
 NVLINK_GBS = 770.0
 

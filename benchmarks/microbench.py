@@ -1,4 +1,4 @@
-"""Single-kernel timing harness: ``python -m lbann_b200.ops.microbench <case> [options]``.
+"""Single-kernel timing harness: ``python -m benchmarks.microbench <case> [options]``.
 
 Each case runs one native kernel (or one layer's forward / backward pair) on a
 stated shape, times it with CUDA events on the launching stream after warm-up,
@@ -21,7 +21,7 @@ import os
 
 import torch
 
-from . import native
+from lbann_b200.ops import native
 
 
 def _peaks():
@@ -73,7 +73,7 @@ def _dtype(name):
 
 
 def case_gemm(a, timer):
-    from .gemm import gemm
+    from lbann_b200.ops.gemm import gemm
     dt = _dtype(a.dtype)
     A = torch.randn(a.m, a.k, device="cuda", dtype=dt)
     B = torch.randn(a.n, a.k, device="cuda", dtype=dt)
@@ -84,7 +84,7 @@ def case_gemm(a, timer):
 
 
 def case_conv(a, timer):
-    from . import nn
+    from lbann_b200.ops import nn
     dt = _dtype(a.dtype)
     N, C, K, S, ks = a.batch, a.cin, a.cout, a.size, a.ksize
     x = torch.randn(N, S, S, S, C, device="cuda", dtype=dt).permute(0, 4, 1, 2, 3)
@@ -118,7 +118,7 @@ def case_conv(a, timer):
 
 
 def case_pool(a, timer):
-    from . import nn
+    from lbann_b200.ops import nn
     dt = _dtype(a.dtype)
     N, C, S = a.batch, a.cin, a.size
     x = torch.randn(N, S, S, S, C, device="cuda", dtype=dt).permute(0, 4, 1, 2, 3)
@@ -139,9 +139,9 @@ def case_gemm_comm(a, timer):
     buffers of this device, so the copying CTAs, the per-block flags and the reduce-scatter
     epilogue all run (their traffic stays in local memory instead of crossing NVLink).
     This is the form a profiler can capture; multi-GPU timings come from
-    ``python -m lbann_b200.parallel.fused_bench``."""
+    ``python -m benchmarks.fused_bench``."""
     import ctypes
-    from ..parallel import fused
+    from lbann_b200.parallel import fused
     lib = fused._lib()
     dt = _dtype(a.dtype)
     P = 2
@@ -196,7 +196,7 @@ def case_gemm_comm(a, timer):
 
 def case_linear_wgrad(a, timer):
     """grad[n, k] += dy[m, n]^T x[m, k] for a short mini-batch of m rows (rank-m update)."""
-    from . import nn
+    from lbann_b200.ops import nn
     dt = _dtype(a.dtype)
     dy = torch.randn(a.m, a.n, device="cuda", dtype=dt)
     x = torch.randn(a.m, a.k, device="cuda", dtype=dt)
@@ -209,7 +209,7 @@ def case_linear_wgrad(a, timer):
 def case_bn(a, timer):
     """Batch normalisation + ReLU over a 2-D activation [batch, cin, size, size]: forward
     (statistics pass + apply pass) and, with ``--bwd``, backward (reduction pass + apply pass)."""
-    from . import nn
+    from lbann_b200.ops import nn
     dt = _dtype(a.dtype)
     N, C, S = a.batch, a.cin, a.size
     x = torch.randn(N, S, S, C, device="cuda", dtype=dt).permute(0, 3, 1, 2).requires_grad_(True)
@@ -232,7 +232,7 @@ def case_bn(a, timer):
 
 
 def case_optimizer(a, timer):
-    from .optim import ParameterArena
+    from lbann_b200.ops.optim import ParameterArena
     arena = ParameterArena(torch.device("cuda"), _dtype(a.dtype))
     n = a.m * a.k
     slot = arena.reserve("w", (a.m, a.k))

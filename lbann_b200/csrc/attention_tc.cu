@@ -1,0 +1,857 @@
+// Fused scaled-dot-product attention for head dimension 128 on tcgen05 / TMEM.
+//
+//   O = softmax(scale * Q K^T  [+ causal mask]) V        per (batch, head)
+//
+// The reference composes attention from eight layers (python/lbann/modules/transformer/
+// attention.py:215-299: two batched MatMuls, a scale, a mask addition, ChannelwiseSoftmax,
+// dropout and two permutes) and materialises the [heads, S, S] score tensor twice.  Here
+// the scores never leave the SM: S = Q K^T is accumulated in TMEM, four warps turn it into
+// probabilities (online softmax, fp32), write them as a 16-bit A operand into shared
+// memory and the tensor core adds P V to the output accumulator, also in TMEM.
+//
+// Tensors are token-major: q, k, v, o are [B][S][H][128] views with arbitrary batch / token /
+// head strides (so the three slices of a packed [B][S][3 H 128] projection are used in
+// place, and the output needs no permute).  Sequence lengths are multiples of 128.
+//
+// Warp roles (192 threads, one CTA per (batch, head, 128 query rows)):
+//   warp 4  TMA producer (Q once, then a two-stage ring of K and V tiles)
+//   warp 5  TMEM allocation + MMA issue (one lane)
+//   warps 0-3  one query row per thread: softmax, rescaling of O, epilogue
+//
+// Backward is two kernels of the same shape, both recomputing P from Q, K and the saved
+// log-sum-exp: attn_bwd_kv_kernel (one CTA per 128 keys, loop over query blocks:
+// dV += P^T dO, dK += dS^T Q) and attn_bwd_q_kernel (one CTA per 128 queries, loop over key
+// blocks: dQ += dS K), with dS = P * (dP - rowsum(dO * O)) * scale.
+//
+// Every wait is bounded; a wait that runs out records a status code and all roles leave.
+#include "common.cuh"
+
+namespace lb {
+
+constexpr int kAttD = 128;                 // head dimension
+constexpr int kAttTile = 128 * kAttD * 2;  // one [128][128] 16-bit tile: 32 KiB
+constexpr int kAttHalf = kAttTile / 2;     // its two [128][64] halves (128-byte swizzled rows)
+
+struct AttnParams {
+  int B, H, Sq, Sk;
+  int causal;
+  int in_dtype;
+  float scale;           // multiplies Q K^T
+  float scale_log2;      // scale * log2(e)
+  // outputs / side inputs (element strides: batch, token, head; head dim contiguous)
+  void* o; long long o_sb, o_ss, o_sh;
+  float* lse;            // [B][H][Sq], log2 domain: max + log2(sum)
+  const float* delta;    // [B][H][Sq] rowsum(dO * O) (backward)
+  void* dq; long long dq_sb, dq_ss, dq_sh;
+  void* dk; long long dk_sb, dk_ss, dk_sh;
+  void* dv; long long dv_sb, dv_ss, dv_sh;
+};
+
+struct AttnShared {
+  uint64_t q_full;
+  uint64_t k_full[2], v_full[2], k_empty[2], v_empty[2];
+  uint64_t s_full[2], s_empty[2];
+  uint64_t p_full, pv_done;
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};" ::"r"(taddr),
+      "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+      "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+      "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+      "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() {
+  asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void fence_async_smem() {
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+}
+
+// acc (+)= A . B^T over K = 128 with both operands K-major tiles [2][128 rows][64 k].
+__device__ __forceinline__ void att_mma_kk(uint32_t acc, uint32_t a, uint32_t b, uint32_t idesc,
+                                           bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < 8; ++kk) {
+    const uint32_t off = (kk >> 2) * kAttHalf + (kk & 3) * 32;
+    umma_f16(acc, make_smem_desc(a + off, 16, 1024, kLayoutSw128),
+             make_smem_desc(b + off, 16, 1024, kLayoutSw128), idesc, (accumulate || kk) ? 1u : 0u);
+  }
+}
+// acc (+)= A . B with A a K-major tile [2][128 rows][64 k] and B given as rows of K:
+// [2 halves of N][128 k rows][64 n] ("MN-major"; the layout of a token-major tile as loaded).
+__device__ __forceinline__ void att_mma_kn(uint32_t acc, uint32_t a, uint32_t b, uint32_t idesc,
+                                           bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < 8; ++kk) {
+    const uint32_t aoff = (kk >> 2) * kAttHalf + (kk & 3) * 32;
+    umma_f16(acc, make_smem_desc(a + aoff, 16, 1024, kLayoutSw128),
+             make_smem_desc(b + kk * 2048, kAttHalf, 1024, kLayoutSw128), idesc,
+             (accumulate || kk) ? 1u : 0u);
+  }
+}
+
+// Byte offset of element (row, col) in a K-major tile [2][128 rows][64 cols], 128-byte swizzle.
+__device__ __forceinline__ uint32_t att_tile_off(int row, int col) {
+  const int half = col >> 6, c = col & 63;
+  return half * kAttHalf + row * 128 + (((c >> 3) ^ (row & 7)) << 4) + ((c & 7) << 1);
+}
+
+// Loads one [128 tokens][128] tile of head h: two boxes {64, 1, 128, 1}.
+__device__ __forceinline__ void att_load_tile(uint32_t dst, const CUtensorMap* tm, uint32_t bar,
+                                              int h, int s0, int b) {
+  tma_load_4d(dst, tm, bar, 0, h, s0, b);
+  tma_load_4d(dst + kAttHalf, tm, bar, 64, h, s0, b);
+}
+
+// Packs 32 fp32 values to 16-bit and stores them as columns [c0, c0 + 32) of row `row`.
+__device__ __forceinline__ void att_store_row32(uint32_t tile, int row, int c0, const float (&v)[32],
+                                                int dtype) {
+#pragma unroll
+  for (int j = 0; j < 32; j += 8) {
+    uint4 q;
+    q.x = pack2(v[j], v[j + 1], dtype);
+    q.y = pack2(v[j + 2], v[j + 3], dtype);
+    q.z = pack2(v[j + 4], v[j + 5], dtype);
+    q.w = pack2(v[j + 6], v[j + 7], dtype);
+    sts128(tile + att_tile_off(row, c0 + j), q);
+  }
+}
+
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// ------------------------------------------------------------------------------------
+// Forward
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(192, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                const __grid_constant__ CUtensorMap tmV, const AttnParams p, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ AttnShared sh;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = base, sK = base + kAttTile, sV = base + 3 * kAttTile, sP = base + 5 * kAttTile;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &sh.abort_flag;
+
+  const int nqb = p.Sq / 128;
+  const int qb = nqb - 1 - (int)blockIdx.x;            // long (late) query blocks first
+  const int h = blockIdx.y, b = blockIdx.z;
+  const int nkv = p.causal ? qb + 1 : p.Sk / 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&sh.q_full), 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(smem_u32(&sh.k_full[s]), 1);
+      mbar_init(smem_u32(&sh.v_full[s]), 1);
+      mbar_init(smem_u32(&sh.k_empty[s]), 1);
+      mbar_init(smem_u32(&sh.v_empty[s]), 1);
+      mbar_init(smem_u32(&sh.s_full[s]), 1);
+      mbar_init(smem_u32(&sh.s_empty[s]), 128);
+    }
+    mbar_init(smem_u32(&sh.p_full), 128);
+    mbar_init(smem_u32(&sh.pv_done), 1);
+    sh.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 4 && lane == 0) {
+    tma_prefetch_desc(&tmQ);
+    tma_prefetch_desc(&tmK);
+    tma_prefetch_desc(&tmV);
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&sh.tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh.tmem_base;
+  const uint32_t tS0 = tmem, tO = tmem + 256;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(smem_u32(&sh.q_full), kAttTile);
+      att_load_tile(sQ, &tmQ, smem_u32(&sh.q_full), h, qb * 128, b);
+      int j = 0;
+      bool ok = true;
+      for (; j < nkv && ok; ++j) {
+        const int s = j & 1;
+        if (j >= 2) {
+          const uint32_t par = ((j >> 1) - 1) & 1;
+          if (!mbar_wait_bounded(smem_u32(&sh.k_empty[s]), par, abort_flag) ||
+              !mbar_wait_bounded(smem_u32(&sh.v_empty[s]), par, abort_flag)) {
+            raise_status(status, abort_flag, kTimeoutStageEmpty);
+            ok = false;
+            break;
+          }
+        }
+        mbar_expect_tx(smem_u32(&sh.k_full[s]), kAttTile);
+        att_load_tile(sK + s * kAttTile, &tmK, smem_u32(&sh.k_full[s]), h, j * 128, b);
+        mbar_expect_tx(smem_u32(&sh.v_full[s]), kAttTile);
+        att_load_tile(sV + s * kAttTile, &tmV, smem_u32(&sh.v_full[s]), h, j * 128, b);
+      }
+      if (!ok || *abort_flag) {
+        // let the copies in flight land before shared memory is released
+        mbar_wait_budget_only(smem_u32(&sh.q_full), 0);
+        for (int i = (j >= 2 ? j - 2 : 0); i < j; ++i) {
+          mbar_wait_budget_only(smem_u32(&sh.k_full[i & 1]), (i >> 1) & 1);
+          mbar_wait_budget_only(smem_u32(&sh.v_full[i & 1]), (i >> 1) & 1);
+        }
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t fmt = p.in_dtype == kBF16 ? 1u : 0u;
+      const uint32_t idesc_qk = make_idesc_f16(fmt, 0, 0, 128, 128);
+      const uint32_t idesc_pv = make_idesc_f16(fmt, 0, 1, 128, 128);
+      bool ok = mbar_wait_bounded(smem_u32(&sh.q_full), 0, abort_flag);
+      if (!ok) raise_status(status, abort_flag, kTimeoutTmaFull);
+      for (int j = 0; j <= nkv && ok; ++j) {
+        if (j < nkv) {
+          const int s = j & 1;
+          if (!mbar_wait_bounded(smem_u32(&sh.k_full[s]), (j >> 1) & 1, abort_flag)) {
+            raise_status(status, abort_flag, kTimeoutTmaFull);
+            ok = false;
+            break;
+          }
+          if (j >= 2 && !mbar_wait_bounded(smem_u32(&sh.s_empty[s]), ((j >> 1) - 1) & 1, abort_flag)) {
+            raise_status(status, abort_flag, kTimeoutTmemEmpty);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          att_mma_kk(tS0 + s * 128, sQ, sK + s * kAttTile, idesc_qk, false);
+          umma_commit(smem_u32(&sh.k_empty[s]));
+          umma_commit(smem_u32(&sh.s_full[s]));
+        }
+        if (j >= 1) {
+          const int jj = j - 1, s = jj & 1;
+          if (!mbar_wait_bounded(smem_u32(&sh.p_full), jj & 1, abort_flag) ||
+              !mbar_wait_bounded(smem_u32(&sh.v_full[s]), (jj >> 1) & 1, abort_flag)) {
+            raise_status(status, abort_flag, kTimeoutTmaFull);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          att_mma_kn(tO, sP, sV + s * kAttTile, idesc_pv, jj > 0);
+          umma_commit(smem_u32(&sh.v_empty[s]));
+          umma_commit(smem_u32(&sh.pv_done));
+        }
+      }
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax / epilogue
+    const int row = threadIdx.x;                       // query row of this thread
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    float m = -1e30f, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < nkv && ok; ++j) {
+      const int s = j & 1;
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&sh.s_full[s]), (j >> 1) & 1, abort_flag));
+      if (!ok) {
+        if (lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
+        break;
+      }
+      tc_fence_after();
+      const uint32_t tS = tS0 + s * 128 + lane_off;
+      const int limit = (p.causal && j == qb) ? row : 127;        // last visible key column
+      // pass 1: row maximum
+      float mx = -1e30f;
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tS + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (c + i <= limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+      }
+      mx *= p.scale_log2;
+      // the running maximum is only moved when it would grow by more than 2^8: until then
+      // the probabilities stay below 256 and O needs no rescaling
+      float alpha = 1.f;
+      float m_use = m;
+      if (mx > m + 8.f) {
+        m_use = mx;
+        alpha = fast_exp2(m - mx);
+      }
+      if (j >= 1) {
+        ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&sh.pv_done), (j - 1) & 1, abort_flag));
+        if (!ok) {
+          if (lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
+          break;
+        }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.f)) {
+#pragma unroll 1
+          for (int c = 0; c < 128; c += 32) {
+            uint32_t r[32];
+            tmem_ld_32x32(tO + lane_off + c, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
+            tmem_st_32x32(tO + lane_off + c, r);
+          }
+          tmem_st_wait();
+        }
+      }
+      l *= alpha;
+      m = m_use;
+      // pass 2: probabilities -> shared memory (A operand of P V)
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tS + c, r);
+        tmem_ld_wait();
+        float v[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) {
+          const float e = fast_exp2(__uint_as_float(r[i]) * p.scale_log2 - m);
+          v[i] = (c + i <= limit) ? e : 0.f;
+          l += v[i];
+        }
+        att_store_row32(sP, row, c, v, p.in_dtype);
+      }
+      tc_fence_before();
+      fence_async_smem();
+      mbar_arrive(smem_u32(&sh.s_empty[s]));
+      mbar_arrive(smem_u32(&sh.p_full));
+    }
+    if (ok) {
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&sh.pv_done), (nkv - 1) & 1, abort_flag));
+      if (!ok && lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = 1.f / l;
+      const long long q = (long long)qb * 128 + row;
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + b * p.o_sb + q * p.o_ss + h * p.o_sh;
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tO + lane_off + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int i = 0; i < 32; i += 8) {
+          uint4 w;
+          w.x = pack2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv, p.in_dtype);
+          w.y = pack2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv, p.in_dtype);
+          w.z = pack2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv, p.in_dtype);
+          w.w = pack2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv, p.in_dtype);
+          *reinterpret_cast<uint4*>(orow + c + i) = w;
+        }
+      }
+      if (p.lse) p.lse[((long long)b * p.H + h) * p.Sq + q] = m + log2f(l);
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// delta[b][h][q] = sum_d dO[b][q][h][d] * O[b][q][h][d]     (one warp per row)
+// ------------------------------------------------------------------------------------
+template <typename T>
+__global__ void attn_delta_kernel(const T* __restrict__ o, const T* __restrict__ dout,
+                                  float* __restrict__ delta, int B, int H, int S, long long o_sb,
+                                  long long o_ss, long long o_sh, long long d_sb, long long d_ss,
+                                  long long d_sh) {
+  const long long warp = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long long total = (long long)B * H * S;
+  if (warp >= total) return;
+  const int q = (int)(warp % S);
+  const int h = (int)((warp / S) % H);
+  const int b = (int)(warp / ((long long)S * H));
+  const T* po = o + b * o_sb + (long long)q * o_ss + h * o_sh + lane * 4;
+  const T* pd = dout + b * d_sb + (long long)q * d_ss + h * d_sh + lane * 4;
+  const uint2 a = *reinterpret_cast<const uint2*>(po);
+  const uint2 g = *reinterpret_cast<const uint2*>(pd);
+  const T* ea = reinterpret_cast<const T*>(&a);
+  const T* eg = reinterpret_cast<const T*>(&g);
+  float sacc = 0.f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) sacc += to_f32<T>(ea[i]) * to_f32<T>(eg[i]);
+  sacc = warp_sum(sacc);
+  if (lane == 0) delta[((long long)b * H + h) * S + q] = sacc;
+}
+
+// ------------------------------------------------------------------------------------
+// Backward, key / value side: one CTA per (batch, head, 128 keys); rows = keys.
+//   per query block i:  S^T = K Q_i^T, dP^T = V dO_i^T   (TMEM)
+//                       P^T = exp2(S^T * c - lse_i), dS^T = P^T * (dP^T - delta_i) * scale
+//                       dV += P^T dO_i,  dK += dS^T Q_i
+// ------------------------------------------------------------------------------------
+struct __align__(128) AttnBwdShared {
+  uint64_t kv_full;        // resident operands loaded
+  uint64_t st_full;        // stage (per-iteration operands) loaded
+  uint64_t st_empty;       // the MMAs that read the stage, P and dS have retired
+  uint64_t s_full;         // score and dP accumulators complete
+  uint64_t p_full;         // P and dS written to shared memory (128 arrivals)
+  uint32_t tmem_base;
+  int abort_flag;
+  float lse[128];
+  float delta[128];
+};
+
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                   const AttnParams p, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ AttnBwdShared sh;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sK = base, sV = base + kAttTile, sQ = base + 2 * kAttTile, sDO = base + 3 * kAttTile;
+  const uint32_t sP = base + 4 * kAttTile, sDS = base + 5 * kAttTile;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &sh.abort_flag;
+  const int kb = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int nqb = p.Sq / 128;
+  const int i0 = p.causal ? kb : 0;                    // first query block that sees these keys
+  const int iters = nqb - i0;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&sh.kv_full), 1);
+    mbar_init(smem_u32(&sh.st_full), 1);
+    mbar_init(smem_u32(&sh.st_empty), 1);
+    mbar_init(smem_u32(&sh.s_full), 1);
+    mbar_init(smem_u32(&sh.p_full), 128);
+    sh.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&sh.tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh.tmem_base;
+  const uint32_t tS = tmem, tDP = tmem + 128, tDV = tmem + 256, tDK = tmem + 384;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      mbar_expect_tx(smem_u32(&sh.kv_full), 2 * kAttTile);
+      att_load_tile(sK, &tmK, smem_u32(&sh.kv_full), h, kb * 128, b);
+      att_load_tile(sV, &tmV, smem_u32(&sh.kv_full), h, kb * 128, b);
+      int it = 0;
+      bool ok = true;
+      for (; it < iters && ok; ++it) {
+        if (it >= 1 && !mbar_wait_bounded(smem_u32(&sh.st_empty), (it - 1) & 1, abort_flag)) {
+          raise_status(status, abort_flag, kTimeoutStageEmpty);
+          ok = false;
+          break;
+        }
+        const int i = i0 + it;
+        const float* lse = p.lse + ((long long)b * p.H + h) * p.Sq + i * 128;
+        const float* dl = p.delta + ((long long)b * p.H + h) * p.Sq + i * 128;
+        mbar_expect_tx(smem_u32(&sh.st_full), 2 * kAttTile + 1024);
+        att_load_tile(sQ, &tmQ, smem_u32(&sh.st_full), h, i * 128, b);
+        att_load_tile(sDO, &tmDO, smem_u32(&sh.st_full), h, i * 128, b);
+        bulk_load_1d(smem_u32(sh.lse), lse, 512, smem_u32(&sh.st_full));
+        bulk_load_1d(smem_u32(sh.delta), dl, 512, smem_u32(&sh.st_full));
+      }
+      if (!ok || *abort_flag) {
+        mbar_wait_budget_only(smem_u32(&sh.kv_full), 0);
+        if (it >= 1) mbar_wait_budget_only(smem_u32(&sh.st_full), (it - 1) & 1);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t fmt = p.in_dtype == kBF16 ? 1u : 0u;
+      const uint32_t idesc_kk = make_idesc_f16(fmt, 0, 0, 128, 128);
+      const uint32_t idesc_kn = make_idesc_f16(fmt, 0, 1, 128, 128);
+      bool ok = mbar_wait_bounded(smem_u32(&sh.kv_full), 0, abort_flag);
+      if (!ok) raise_status(status, abort_flag, kTimeoutTmaFull);
+      for (int it = 0; it < iters && ok; ++it) {
+        if (!mbar_wait_bounded(smem_u32(&sh.st_full), it & 1, abort_flag)) {
+          raise_status(status, abort_flag, kTimeoutTmaFull);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        att_mma_kk(tS, sK, sQ, idesc_kk, false);       // S^T[key][q]
+        att_mma_kk(tDP, sV, sDO, idesc_kk, false);     // dP^T[key][q]
+        umma_commit(smem_u32(&sh.s_full));
+        if (!mbar_wait_bounded(smem_u32(&sh.p_full), it & 1, abort_flag)) {
+          raise_status(status, abort_flag, kTimeoutTmemEmpty);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        att_mma_kn(tDV, sP, sDO, idesc_kn, it > 0);    // dV[key][d] += P^T dO
+        att_mma_kn(tDK, sDS, sQ, idesc_kn, it > 0);    // dK[key][d] += dS^T Q
+        umma_commit(smem_u32(&sh.st_empty));
+      }
+    }
+  } else {
+    const int row = threadIdx.x;                       // key row of this thread
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    bool ok = true;
+    for (int it = 0; it < iters && ok; ++it) {
+      const int i = i0 + it;
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&sh.s_full), it & 1, abort_flag));
+      if (!ok) {
+        if (lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
+        break;
+      }
+      // lse / delta of this query block came with the stage (same barrier as Q and dO)
+      mbar_wait_bounded(smem_u32(&sh.st_full), it & 1, abort_flag);
+      tc_fence_after();
+      // causal, diagonal block: query column c sees key `row` only when c >= row
+      const int first = (p.causal && i == kb) ? row : 0;
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32(tS + lane_off + c, rs);
+        tmem_ld_32x32(tDP + lane_off + c, rd);
+        tmem_ld_wait();
+        float pv[32], dsv[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const float e = fast_exp2(__uint_as_float(rs[k]) * p.scale_log2 - sh.lse[c + k]);
+          const float pr = (c + k >= first) ? e : 0.f;
+          pv[k] = pr;
+          dsv[k] = pr * (__uint_as_float(rd[k]) - sh.delta[c + k]) * p.scale;
+        }
+        att_store_row32(sP, row, c, pv, p.in_dtype);
+        att_store_row32(sDS, row, c, dsv, p.in_dtype);
+      }
+      tc_fence_before();
+      fence_async_smem();
+      mbar_arrive(smem_u32(&sh.p_full));
+    }
+    if (ok && iters > 0) {
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&sh.st_empty), (iters - 1) & 1, abort_flag));
+      if (!ok && lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
+    }
+    if (ok) {
+      tc_fence_after();
+      const long long key = (long long)kb * 128 + row;
+      uint16_t* dvrow = reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_sb + key * p.dv_ss + h * p.dv_sh;
+      uint16_t* dkrow = reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_sb + key * p.dk_ss + h * p.dk_sh;
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t r[32];
+        if (iters > 0) {
+          tmem_ld_32x32(tDV + lane_off + c, r);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int k = 0; k < 32; ++k) r[k] = 0u;
+        }
+#pragma unroll
+        for (int k = 0; k < 32; k += 8) {
+          uint4 w;
+          w.x = pack2(__uint_as_float(r[k]), __uint_as_float(r[k + 1]), p.in_dtype);
+          w.y = pack2(__uint_as_float(r[k + 2]), __uint_as_float(r[k + 3]), p.in_dtype);
+          w.z = pack2(__uint_as_float(r[k + 4]), __uint_as_float(r[k + 5]), p.in_dtype);
+          w.w = pack2(__uint_as_float(r[k + 6]), __uint_as_float(r[k + 7]), p.in_dtype);
+          *reinterpret_cast<uint4*>(dvrow + c + k) = w;
+        }
+        if (iters > 0) {
+          tmem_ld_32x32(tDK + lane_off + c, r);
+          tmem_ld_wait();
+        }
+#pragma unroll
+        for (int k = 0; k < 32; k += 8) {
+          uint4 w;
+          w.x = pack2(__uint_as_float(r[k]), __uint_as_float(r[k + 1]), p.in_dtype);
+          w.y = pack2(__uint_as_float(r[k + 2]), __uint_as_float(r[k + 3]), p.in_dtype);
+          w.z = pack2(__uint_as_float(r[k + 4]), __uint_as_float(r[k + 5]), p.in_dtype);
+          w.w = pack2(__uint_as_float(r[k + 6]), __uint_as_float(r[k + 7]), p.in_dtype);
+          *reinterpret_cast<uint4*>(dkrow + c + k) = w;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// ------------------------------------------------------------------------------------
+// Backward, query side: one CTA per (batch, head, 128 queries); rows = queries.
+//   per key block n:  S = Q K_n^T, dP = dO V_n^T  (TMEM);  dS = P * (dP - delta) * scale;
+//                     dQ += dS K_n
+// ------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(192, 1)
+attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
+                  const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
+                  const AttnParams p, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ AttnBwdShared sh;
+  const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t sQ = base, sDO = base + kAttTile, sK = base + 2 * kAttTile, sV = base + 3 * kAttTile;
+  const uint32_t sDS = base + 4 * kAttTile;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &sh.abort_flag;
+  const int nqb = p.Sq / 128;
+  const int qb = nqb - 1 - (int)blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  const int iters = p.causal ? qb + 1 : p.Sk / 128;
+
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&sh.kv_full), 1);
+    mbar_init(smem_u32(&sh.st_full), 1);
+    mbar_init(smem_u32(&sh.st_empty), 1);
+    mbar_init(smem_u32(&sh.s_full), 1);
+    mbar_init(smem_u32(&sh.p_full), 128);
+    sh.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == 5) {
+    tmem_alloc(smem_u32(&sh.tmem_base), 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = sh.tmem_base;
+  const uint32_t tS = tmem, tDP = tmem + 128, tDQ = tmem + 256;
+
+  if (warp == 4) {
+    if (lane == 0) {
+      const float* lse = p.lse + ((long long)b * p.H + h) * p.Sq + qb * 128;
+      const float* dl = p.delta + ((long long)b * p.H + h) * p.Sq + qb * 128;
+      mbar_expect_tx(smem_u32(&sh.kv_full), 2 * kAttTile + 1024);
+      att_load_tile(sQ, &tmQ, smem_u32(&sh.kv_full), h, qb * 128, b);
+      att_load_tile(sDO, &tmDO, smem_u32(&sh.kv_full), h, qb * 128, b);
+      bulk_load_1d(smem_u32(sh.lse), lse, 512, smem_u32(&sh.kv_full));
+      bulk_load_1d(smem_u32(sh.delta), dl, 512, smem_u32(&sh.kv_full));
+      int it = 0;
+      bool ok = true;
+      for (; it < iters && ok; ++it) {
+        if (it >= 1 && !mbar_wait_bounded(smem_u32(&sh.st_empty), (it - 1) & 1, abort_flag)) {
+          raise_status(status, abort_flag, kTimeoutStageEmpty);
+          ok = false;
+          break;
+        }
+        mbar_expect_tx(smem_u32(&sh.st_full), 2 * kAttTile);
+        att_load_tile(sK, &tmK, smem_u32(&sh.st_full), h, it * 128, b);
+        att_load_tile(sV, &tmV, smem_u32(&sh.st_full), h, it * 128, b);
+      }
+      if (!ok || *abort_flag) {
+        mbar_wait_budget_only(smem_u32(&sh.kv_full), 0);
+        if (it >= 1) mbar_wait_budget_only(smem_u32(&sh.st_full), (it - 1) & 1);
+      }
+    }
+  } else if (warp == 5) {
+    if (lane == 0) {
+      const uint32_t fmt = p.in_dtype == kBF16 ? 1u : 0u;
+      const uint32_t idesc_kk = make_idesc_f16(fmt, 0, 0, 128, 128);
+      const uint32_t idesc_kn = make_idesc_f16(fmt, 0, 1, 128, 128);
+      bool ok = mbar_wait_bounded(smem_u32(&sh.kv_full), 0, abort_flag);
+      if (!ok) raise_status(status, abort_flag, kTimeoutTmaFull);
+      for (int it = 0; it < iters && ok; ++it) {
+        if (!mbar_wait_bounded(smem_u32(&sh.st_full), it & 1, abort_flag)) {
+          raise_status(status, abort_flag, kTimeoutTmaFull);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        att_mma_kk(tS, sQ, sK, idesc_kk, false);       // S[q][key]
+        att_mma_kk(tDP, sDO, sV, idesc_kk, false);     // dP[q][key]
+        umma_commit(smem_u32(&sh.s_full));
+        if (!mbar_wait_bounded(smem_u32(&sh.p_full), it & 1, abort_flag)) {
+          raise_status(status, abort_flag, kTimeoutTmemEmpty);
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        att_mma_kn(tDQ, sDS, sK, idesc_kn, it > 0);    // dQ[q][d] += dS K
+        umma_commit(smem_u32(&sh.st_empty));
+      }
+    }
+  } else {
+    const int row = threadIdx.x;                       // query row of this thread
+    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&sh.kv_full), 0, abort_flag));
+    if (!ok && lane == 0) raise_status(status, abort_flag, kTimeoutTmaFull);
+    const float my_lse = ok ? sh.lse[row] : 0.f, my_delta = ok ? sh.delta[row] : 0.f;
+    for (int it = 0; it < iters && ok; ++it) {
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&sh.s_full), it & 1, abort_flag));
+      if (!ok) {
+        if (lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
+        break;
+      }
+      tc_fence_after();
+      const int limit = (p.causal && it == qb) ? row : 127;
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t rs[32], rd[32];
+        tmem_ld_32x32(tS + lane_off + c, rs);
+        tmem_ld_32x32(tDP + lane_off + c, rd);
+        tmem_ld_wait();
+        float dsv[32];
+#pragma unroll
+        for (int k = 0; k < 32; ++k) {
+          const float e = fast_exp2(__uint_as_float(rs[k]) * p.scale_log2 - my_lse);
+          const float pr = (c + k <= limit) ? e : 0.f;
+          dsv[k] = pr * (__uint_as_float(rd[k]) - my_delta) * p.scale;
+        }
+        att_store_row32(sDS, row, c, dsv, p.in_dtype);
+      }
+      tc_fence_before();
+      fence_async_smem();
+      mbar_arrive(smem_u32(&sh.p_full));
+    }
+    if (ok) {
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&sh.st_empty), (iters - 1) & 1, abort_flag));
+      if (!ok && lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
+    }
+    if (ok) {
+      tc_fence_after();
+      const long long q = (long long)qb * 128 + row;
+      uint16_t* dqrow = reinterpret_cast<uint16_t*>(p.dq) + b * p.dq_sb + q * p.dq_ss + h * p.dq_sh;
+#pragma unroll 1
+      for (int c = 0; c < 128; c += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(tDQ + lane_off + c, r);
+        tmem_ld_wait();
+#pragma unroll
+        for (int k = 0; k < 32; k += 8) {
+          uint4 w;
+          w.x = pack2(__uint_as_float(r[k]), __uint_as_float(r[k + 1]), p.in_dtype);
+          w.y = pack2(__uint_as_float(r[k + 2]), __uint_as_float(r[k + 3]), p.in_dtype);
+          w.z = pack2(__uint_as_float(r[k + 4]), __uint_as_float(r[k + 5]), p.in_dtype);
+          w.w = pack2(__uint_as_float(r[k + 6]), __uint_as_float(r[k + 7]), p.in_dtype);
+          *reinterpret_cast<uint4*>(dqrow + c + k) = w;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 5) {
+    tc_fence_after();
+    tmem_dealloc(tmem, 512);
+  }
+}
+
+// Tensor map of a token-major tensor [B][S][H][128] with element strides (sb, ss, sh).
+static bool att_tmap(CUtensorMap* tm, const void* ptr, int dtype, int B, int S, int H, long long sb,
+                     long long ss, long long sh) {
+  uint64_t dims[4] = {(uint64_t)kAttD, (uint64_t)H, (uint64_t)S, (uint64_t)B};
+  uint64_t strides[3] = {(uint64_t)sh * 2, (uint64_t)ss * 2, (uint64_t)sb * 2};
+  uint32_t box[4] = {64, 1, 128, 1};
+  return lbhost::encode_tmap(tm, dtype, 4, ptr, dims, strides, box, nullptr, 128);
+}
+
+static bool att_layout_ok(const void* ptr, long long sb, long long ss, long long sh) {
+  return (reinterpret_cast<uintptr_t>(ptr) & 15) == 0 && sb % 8 == 0 && ss % 8 == 0 && sh % 8 == 0;
+}
+
+}  // namespace lb
+
+extern "C" {
+
+// q, k, v, o: [B][S][H][128] views, strides in elements (batch, token, head); head dim dense.
+// lse: fp32 [B][H][Sq] (log2 domain), written when not null.  dtype: 0 fp16, 1 bf16.
+// Returns -2 when the shape is not covered (head dim != 128 is the caller's check; sequence
+// lengths must be multiples of 128, causal needs Sq == Sk).
+int lb_attention_fwd(const void* q, const void* k, const void* v, void* o, float* lse, int B, int H,
+                     int Sq, int Sk, const long long* qs, const long long* ks, const long long* vs,
+                     const long long* os, float scale, int causal, int dtype, void* stream_) {
+  using namespace lb;
+  if (B < 1 || H < 1 || Sq < 128 || Sk < 128 || Sq % 128 || Sk % 128) return -2;
+  if (causal && Sq != Sk) return -2;
+  if (dtype != kF16 && dtype != kBF16) return -2;
+  if (!att_layout_ok(q, qs[0], qs[1], qs[2]) || !att_layout_ok(k, ks[0], ks[1], ks[2]) ||
+      !att_layout_ok(v, vs[0], vs[1], vs[2]) || !att_layout_ok(o, os[0], os[1], os[2])) return -1;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  CUtensorMap tq, tk, tv;
+  if (!att_tmap(&tq, q, dtype, B, Sq, H, qs[0], qs[1], qs[2]) ||
+      !att_tmap(&tk, k, dtype, B, Sk, H, ks[0], ks[1], ks[2]) ||
+      !att_tmap(&tv, v, dtype, B, Sk, H, vs[0], vs[1], vs[2])) return -1;
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.causal = causal; p.in_dtype = dtype;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.o = o; p.o_sb = os[0]; p.o_ss = os[1]; p.o_sh = os[2]; p.lse = lse;
+  const int smem = 6 * kAttTile + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(attn_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    configured = true;
+  }
+  dim3 grid(Sq / 128, H, B);
+  attn_fwd_kernel<<<grid, 192, smem, stream>>>(tq, tk, tv, p, lbhost::status_word());
+  return (int)cudaGetLastError();
+}
+
+// Gradients of lb_attention_fwd.  o, dout: [B][Sq][H][128]; lse from the forward call; delta:
+// fp32 workspace [B][H][Sq].  dq, dk, dv are written (not accumulated).
+int lb_attention_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                     const float* lse, float* delta, void* dq, void* dk, void* dv, int B, int H, int Sq,
+                     int Sk, const long long* qs, const long long* ks, const long long* vs,
+                     const long long* os, const long long* dos, const long long* dqs,
+                     const long long* dks, const long long* dvs, float scale, int causal, int dtype,
+                     void* stream_) {
+  using namespace lb;
+  if (B < 1 || H < 1 || Sq < 128 || Sk < 128 || Sq % 128 || Sk % 128) return -2;
+  if (causal && Sq != Sk) return -2;
+  if (dtype != kF16 && dtype != kBF16) return -2;
+  if (!att_layout_ok(q, qs[0], qs[1], qs[2]) || !att_layout_ok(k, ks[0], ks[1], ks[2]) ||
+      !att_layout_ok(v, vs[0], vs[1], vs[2]) || !att_layout_ok(o, os[0], os[1], os[2]) ||
+      !att_layout_ok(dout, dos[0], dos[1], dos[2]) || !att_layout_ok(dq, dqs[0], dqs[1], dqs[2]) ||
+      !att_layout_ok(dk, dks[0], dks[1], dks[2]) || !att_layout_ok(dv, dvs[0], dvs[1], dvs[2]))
+    return -1;
+  if ((reinterpret_cast<uintptr_t>(lse) & 15) || (reinterpret_cast<uintptr_t>(delta) & 15)) return -1;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  CUtensorMap tq, tk, tv, tdo;
+  if (!att_tmap(&tq, q, dtype, B, Sq, H, qs[0], qs[1], qs[2]) ||
+      !att_tmap(&tk, k, dtype, B, Sk, H, ks[0], ks[1], ks[2]) ||
+      !att_tmap(&tv, v, dtype, B, Sk, H, vs[0], vs[1], vs[2]) ||
+      !att_tmap(&tdo, dout, dtype, B, Sq, H, dos[0], dos[1], dos[2])) return -1;
+  {
+    const long long rows = (long long)B * H * Sq;
+    const int blocks = (int)((rows * 32 + 255) / 256);
+    if (dtype == kBF16)
+      attn_delta_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(
+          (const __nv_bfloat16*)o, (const __nv_bfloat16*)dout, delta, B, H, Sq, os[0], os[1], os[2],
+          dos[0], dos[1], dos[2]);
+    else
+      attn_delta_kernel<__half><<<blocks, 256, 0, stream>>>((const __half*)o, (const __half*)dout, delta,
+                                                            B, H, Sq, os[0], os[1], os[2], dos[0],
+                                                            dos[1], dos[2]);
+  }
+  AttnParams p;
+  memset(&p, 0, sizeof(p));
+  p.B = B; p.H = H; p.Sq = Sq; p.Sk = Sk; p.causal = causal; p.in_dtype = dtype;
+  p.scale = scale; p.scale_log2 = scale * 1.4426950408889634f;
+  p.lse = const_cast<float*>(lse); p.delta = delta;
+  p.dq = dq; p.dq_sb = dqs[0]; p.dq_ss = dqs[1]; p.dq_sh = dqs[2];
+  p.dk = dk; p.dk_sb = dks[0]; p.dk_ss = dks[1]; p.dk_sh = dks[2];
+  p.dv = dv; p.dv_sb = dvs[0]; p.dv_ss = dvs[1]; p.dv_sh = dvs[2];
+  const int smem_kv = 6 * kAttTile + 1024, smem_q = 5 * kAttTile + 1024;
+  static bool configured = false;
+  if (!configured) {
+    cudaFuncSetAttribute(attn_bwd_kv_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_kv);
+    cudaFuncSetAttribute(attn_bwd_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_q);
+    configured = true;
+  }
+  attn_bwd_kv_kernel<<<dim3(Sk / 128, H, B), 192, smem_kv, stream>>>(tq, tk, tv, tdo, p,
+                                                                     lbhost::status_word());
+  attn_bwd_q_kernel<<<dim3(Sq / 128, H, B), 192, smem_q, stream>>>(tq, tk, tv, tdo, p,
+                                                                   lbhost::status_word());
+  return (int)cudaGetLastError();
+}
+
+}  // extern "C"

@@ -59,9 +59,10 @@ __device__ __forceinline__ bool block_rendezvous(const PeerPtrs& pp, int rank, i
     st_release_sys(remote, epoch);
     const uint32_t* mine = pp.pad[rank] + (size_t)row * kMaxRanks + peer;
     const uint64_t t0 = globaltimer_ns();
+    const uint64_t budget = peer_wait_budget_ns(status);
     uint32_t spins = 0;
     while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
-      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > LB_WAIT_BUDGET_NS) {
+      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > budget) {
         ok_flag = 0;
         if (status) atomicCAS(status, 0, kTimeoutPeerFlag);
         break;

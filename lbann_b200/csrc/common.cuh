@@ -102,6 +102,15 @@ __device__ __forceinline__ bool mbar_wait_budget_only(uint32_t bar, uint32_t par
   }
 }
 
+// Budget of the waits on OTHER RANKS (rendezvous flags, halo arrival counters).  It can be
+// changed at run time: the status allocation holds it as a 64-bit nanosecond count in bytes
+// 8..15 (0 = the compile-time default), set with lb_set_wait_budget_ns.
+__device__ __forceinline__ uint64_t peer_wait_budget_ns(const int* status) {
+  if (!status) return LB_WAIT_BUDGET_NS;
+  const uint64_t v = *reinterpret_cast<const volatile uint64_t*>(status + 2);
+  return v ? v : LB_WAIT_BUDGET_NS;
+}
+
 __device__ __forceinline__ void raise_status(int* status, volatile int* abort_flag, int code) {
   *abort_flag = 1;
   if (status) atomicCAS(status, 0, code);

@@ -83,11 +83,12 @@ __device__ __forceinline__ bool halo_wait(const uint32_t* flag, uint32_t target,
                                           volatile int* abort_flag) {
   if ((int32_t)(ld_acquire_sys_u32(flag) - target) < 0) {
     const uint64_t t0 = globaltimer_ns();
+    const uint64_t budget = peer_wait_budget_ns(status);
     uint32_t spins = 0;
     while ((int32_t)(ld_acquire_sys_u32(flag) - target) < 0) {
       if ((++spins & 0x3f) == 0) {
         if (*abort_flag) return false;
-        if (globaltimer_ns() - t0 > LB_WAIT_BUDGET_NS) {
+        if (globaltimer_ns() - t0 > budget) {
           raise_status(status, abort_flag, kTimeoutPeerFlag);
           return false;
         }

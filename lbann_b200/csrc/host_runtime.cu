@@ -105,6 +105,14 @@ int lb_consume_status(void* stream) {
   return lbhost::consume_status(reinterpret_cast<cudaStream_t>(stream));
 }
 
+// Budget, in nanoseconds, of every device-side wait on another rank (0 = the built-in 2 s).
+// Stored next to the status word on the current device; takes effect for kernels launched
+// after the call.
+int lb_set_wait_budget_ns(unsigned long long ns) {
+  int* w = lbhost::status_word();
+  return (int)cudaMemcpy(reinterpret_cast<char*>(w) + 8, &ns, sizeof(ns), cudaMemcpyHostToDevice);
+}
+
 // Device pointer of the status word (for kernels launched from other libraries/tests).
 void* lb_status_ptr() { return lbhost::status_word(); }
 

@@ -24,9 +24,10 @@ extern "C" {
 //
 //   dtype: 0 = fp16, 1 = bf16.  cols must be a multiple of 8 and x 16-byte aligned.
 //
-// Returns 0 on success; -1 for a bad pointer / dtype / cols % 8 != 0; -2 when cols exceeds
-// LB_COLUMN_SUMS_NOALLOC_MAX_COLS (a message naming the limit goes to stderr); a
-// positive cudaError_t if the set-up or a launch failed.
+// Returns 0 on success; -1 for a null pointer, an x that is not 16-byte aligned, rows < 0,
+// cols <= 0 or cols % 8 != 0, a dtype other than the two above, or a device index of 64 or
+// more; -2 when cols exceeds LB_COLUMN_SUMS_NOALLOC_MAX_COLS (a message naming the limit
+// goes to stderr); a positive cudaError_t if the set-up or a launch failed.
 //
 // Set-up: the FIRST call on each device looks the workspace's address up with
 // cudaGetSymbolAddress (checked), which may load the module; make that call once outside

@@ -177,9 +177,16 @@ class ExecModel:
         self._fuse_activations()
         self._fuse_softmax_cross_entropy()
         self._fuse_attention_scores()
+        self._fuse_attention()
         for mode in MODES:
             self.stats[mode] = ModeStats(self.device, len(self.metrics))
-        self._phase_timer = ExecModel._PhaseTimer(self.device) if os.environ.get("LBANN_PHASE_TIMING") else None
+        # LBANN_PHASE_TIMING=1: CUDA events between the phases of a step launched from the host;
+        # LBANN_PHASE_TIMING=graph: the step is replayed as THREE graphs (forward / backward +
+        # gradient reduction / update) with events between them, i.e. the phase times of the
+        # graph-launched step, free of host launch gaps
+        pt_mode = os.environ.get("LBANN_PHASE_TIMING")
+        self._phase_timer = ExecModel._PhaseTimer(self.device) if pt_mode else None
+        self._phase_graphs = pt_mode == "graph"
         self.is_setup = True
         return self
 
@@ -344,7 +351,8 @@ class ExecModel:
         element-wise passes over the [heads, S, S] tensor.  A mask qualifies when it is a
         constant (optimizer-less) weights layer holding 0 on and below the diagonal and a
         large negative number above it."""
-        if self.device.type != "cuda" or os.environ.get("LBANN_DISABLE_ATTENTION_FUSION"):
+        forced = os.environ.get("LBANN_FORCE_ATTENTION_FUSION")     # CPU tests of the graph rewrite
+        if (self.device.type != "cuda" and not forced) or os.environ.get("LBANN_DISABLE_ATTENTION_FUSION"):
             return
         protected = {n for n, _ in self.objective_terms} | {m.layer_name for m in self.metrics
                                                             if getattr(m, "layer_name", None)}
@@ -384,6 +392,123 @@ class ExecModel:
                 cur.fused_into_child = True
                 sm.fused_scale = scale
 
+    def _fuse_attention(self):
+        """The whole scaled-dot-product sub-graph that the front end emits for batched heads
+        (python/lbann/modules/transformer/attention.py:215-299)
+
+            q, k, v [S, E] -> Reshape [S, H, D] -> Permute [H, S, D]
+            MatMul(q, k^T) -> Scale -> (+ causal mask) -> ChannelwiseSoftmax -> MatMul(., v)
+            -> Permute [S, H, D] -> Reshape [S, E]
+
+        becomes one call of ``ops.attention`` placed in the last Reshape: the layers between
+        are not executed and the [H, S, S] scores are never formed.  When q, k and v are the
+        three slices of one projection the packed entry point is used (one gradient tensor
+        for the projection).  Dropout on the probabilities, extra biases, non-causal masks
+        and protected (objective / metric) layers keep the layer-by-layer path."""
+        if os.environ.get("LBANN_DISABLE_ATTENTION_FUSION"):
+            return
+        protected = {n for n, _ in self.objective_terms} | {m.layer_name for m in self.metrics
+                                                            if getattr(m, "layer_name", None)}
+
+        def only_child(l, kind=None):
+            if len(l.children) != 1 or l.name in protected:
+                return None
+            c = l.children[0]
+            return c if (kind is None or c.type == kind) else None
+
+        def heads_source(l):
+            """l = Permute([1,0,2]) of Reshape([S, H, D]) of x  ->  (x, H, D, [layers])"""
+            if l.type != "permute" or list(l.axes) != [1, 0, 2] or len(l.children) != 1 or l.name in protected:
+                return None
+            r = l.parents[0]
+            if r.type != "reshape" or len(r.out_dims[0]) != 3 or len(r.children) != 1 or r.name in protected:
+                return None
+            S, H, D = r.out_dims[0]
+            if tuple(r.in_dims[0]) != (S, H * D):
+                return None
+            return r.parents[0], H, D, [r, l]
+
+        for sm in self.layers:
+            if sm.type != "channelwise_softmax" or not sm.parents or sm.name in protected:
+                continue
+            scale = getattr(sm, "fused_scale", None)
+            causal = getattr(sm, "fused_causal", None)
+            cur = sm.parents[0]
+            between = []
+            ok = True
+            while cur.type == "operator_layer":
+                if not getattr(cur, "fused_into_child", False) or len(cur.children) != 1:
+                    ok = False
+                    break
+                between.append(cur)
+                cur = cur.parents[0]
+            scores = cur
+            if not ok or scores.type != "matmul" or scores.ta or not scores.tb or only_child(scores) is None:
+                continue
+            ctxl = only_child(sm, "matmul")
+            if ctxl is None or ctxl.ta or ctxl.tb or ctxl.parents[0] is not sm:
+                continue
+            merge = only_child(ctxl, "permute")
+            if merge is None or list(merge.axes) != [1, 0, 2]:
+                continue
+            out = only_child(merge, "reshape")
+            if out is None or len(out.out_dims[0]) != 2:
+                continue
+            qs, ks, vs = heads_source(scores.parents[0]), heads_source(scores.parents[1]), \
+                heads_source(ctxl.parents[1])
+            if qs is None or ks is None or vs is None:
+                continue
+            H, D = qs[1], qs[2]
+            if (ks[1], ks[2]) != (H, D) or (vs[1], vs[2]) != (H, D) or tuple(out.out_dims[0])[1] != H * D:
+                continue
+            Sq, Sk = scores.out_dims[0][-2], scores.out_dims[0][-1]
+            if causal is not None and (causal != Sk or Sq != Sk):
+                continue
+            # only shapes that the tcgen05 kernels cover are rerouted (csrc/attention_tc.cu)
+            if not os.environ.get("LBANN_FORCE_ATTENTION_FUSION") and (
+                    self.device.type != "cuda" or D != 128 or Sq % 128 or Sk % 128
+                    or self.default_dtype not in (torch.float16, torch.bfloat16)):
+                continue
+            mask_layers = [b for b in between if len(b.parents) == 2]
+            if causal is None and mask_layers:
+                continue            # an additive mask that is not the causal one
+            dead = between + [scores, sm, ctxl, merge] + qs[3] + ks[3] + vs[3]
+            for b in mask_layers:
+                # the constant mask tensor itself is not needed either when nobody else reads it
+                w = b.parents[1]
+                if len(w.children) == 1:
+                    dead.append(w)
+            srcs = [qs[0], ks[0], vs[0]]
+            packed = slice_layer = None
+            if all(x.type == "identity" and len(x.children) == 1 and x.name not in protected for x in srcs):
+                sl = srcs[0].parents[0]
+                if (sl.type == "slice" and all(x.parents[0] is sl for x in srcs)
+                        and [c.name for c in sl.children] == [x.name for x in srcs]
+                        and sl.points == [0, H * D, 2 * H * D, 3 * H * D] and sl.name not in protected
+                        and sl.axis == len(sl.in_dims[0]) - 1):
+                    packed, slice_layer = sl.parents[0], sl
+                    dead += srcs + [sl]
+            for l in dead:
+                l.dead = True
+            out.attention = {"packed": packed.name if packed is not None else None,
+                             "q": srcs[0].name, "k": srcs[1].name, "v": srcs[2].name,
+                             "heads": H, "scale": float(scale) if scale is not None else 1.0,
+                             "causal": causal is not None}
+            out.attention_sources = (packed, slice_layer) if packed is not None else tuple(srcs)
+
+    def _attention_forward(self, layer, acts):
+        from ..ops import attention as att
+        a = layer.attention
+        if a["packed"] is not None:
+            src, consumer = layer.attention_sources
+            qkv = acts[src.name][self._slot(src, consumer)]
+            y = att.attention_packed(layer.cast_in(qkv), a["heads"], a["scale"], a["causal"])
+        else:
+            q, k, v = (layer.cast_in(acts[s.name][self._slot(s, s.children[0])])
+                       for s in layer.attention_sources)
+            y = att.attention(q, k, v, a["heads"], a["scale"], a["causal"])
+        return [y.reshape(y.shape[0], *layer.out_dims[0])]
+
     # ------------------------------------------------------------------ execution
     def forward_prop(self, inputs: Dict[str, torch.Tensor], mode: str = "training",
                      global_mini_batch_size: Optional[int] = None, mini_batch_offset: int = 0):
@@ -400,6 +525,12 @@ class ExecModel:
         cbs = self.callbacks
         occurrence = defaultdict(int)
         for layer in self.layers:
+            if getattr(layer, "dead", False):        # folded into a fused consumer
+                acts[layer.name] = [None] * max(len(layer.out_dims), 1)
+                continue
+            if getattr(layer, "attention", None) is not None:
+                acts[layer.name] = self._attention_forward(layer, acts)
+                continue
             xs = []
             occ_local = defaultdict(int)
             for pn in layer.parent_names:
@@ -596,7 +727,7 @@ class ExecModel:
         if self.device.type != "cuda" or not (_opts.current().get_bool("use_cuda_graph")
                                               or os.environ.get("LBANN_CUDA_GRAPH") == "1"):
             return False
-        if self.layer_timing or self.sync_layers or self._phase_timer is not None:
+        if self.layer_timing or self.sync_layers or (self._phase_timer is not None and not self._phase_graphs):
             return False
         for cb in self.callbacks:
             for h in self._IN_STEP_HOOKS:
@@ -605,6 +736,9 @@ class ExecModel:
         # layers whose output depends on a host-side value that changes from step to step
         # (position in the epoch, host random streams, user code)
         if any(l.type in self._HOST_STATE_LAYERS for l in self.layers):
+            return False
+        # hypergradient Adam moves its learning rate on the host every step
+        if any(s.kind == "hypergradient_adam" for s in self.arena.slots):
             return False
         return True
 
@@ -639,8 +773,12 @@ class ExecModel:
             graph = torch.cuda.CUDAGraph()
             torch.cuda.synchronize(self.device)
             try:
-                with torch.cuda.graph(graph, capture_error_mode="thread_local"):
-                    out = self._train_step_eager(static, gmb, offset)
+                if self._phase_graphs:
+                    graph = self._capture_phase_graphs(static, gmb, offset)
+                    out = self.last_objective
+                else:
+                    with torch.cuda.graph(graph, capture_error_mode="thread_local"):
+                        out = self._train_step_eager(static, gmb, offset)
             except Exception as e:      # something in this model cannot be captured
                 self._graph_mode = False
                 self._graphs.clear()
@@ -676,6 +814,35 @@ class ExecModel:
         self.current_inputs = entry["static"]
         self.last_objective = entry["out"]
         return self.last_objective
+
+    def _capture_phase_graphs(self, static, gmb, offset):
+        """The step as three graphs in one memory pool; ``replay()`` of the returned object
+        runs them in order with timing events between (see LBANN_PHASE_TIMING=graph)."""
+        model = self
+        pool = torch.cuda.graph_pool_handle()
+        graphs = [torch.cuda.CUDAGraph() for _ in range(3)]
+        pt, self._phase_timer = self._phase_timer, None       # no event records inside a capture
+        try:
+            with torch.cuda.graph(graphs[0], pool=pool, capture_error_mode="thread_local"):
+                self.clear_gradients()
+                self.forward_prop(static, "training", gmb, offset)
+                obj = self.local_objective()
+                self.last_objective = obj.detach()
+                self.record_statistics("training", obj)
+            with torch.cuda.graph(graphs[1], pool=pool, capture_error_mode="thread_local"):
+                self.backward_prop(obj)
+            with torch.cuda.graph(graphs[2], pool=pool, capture_error_mode="thread_local"):
+                self.update_weights()
+        finally:
+            self._phase_timer = pt
+
+        class _Three:
+            def replay(self_inner):
+                pt.mark("start")
+                for g, name in zip(graphs, ("forward", "backward+sync", "update")):
+                    g.replay()
+                    pt.mark(name)
+        return _Three()
 
     def _train_step_eager(self, inputs, global_mini_batch_size=None, mini_batch_offset=0):
         pt = self._phase_timer

@@ -105,7 +105,7 @@ class ExecWeights:
             # autograd accumulates into the arena slice in place
             master.grad = grad if grad.dtype == master.dtype else None
         self.handle = WeightHandle(master, grad, compute)
-        self.slot.kind = "adam" if kind == "hypergradient_adam" else (kind or "none")
+        self.slot.kind = kind or "none"
         self.slot.hp = dict(hp)
         self.opt_kind, self.opt_hp = kind or "none", self.slot.hp
 
@@ -186,10 +186,14 @@ class ExecWeights:
         a = self.arena
         if self.slot.kind == "sgd":
             out["velocity"] = a.view(a.state0, self.slot)
-        elif self.slot.kind == "adam":
+        elif self.slot.kind in ("adam", "hypergradient_adam"):
             a.ensure_state1()
             out["moment1"] = a.view(a.state0, self.slot)
             out["moment2"] = a.view(a.state1, self.slot)
+            if self.slot.kind == "hypergradient_adam":
+                if "old_gradient" not in self.slot.extra:
+                    self.slot.extra["old_gradient"] = torch.zeros_like(a.view(a.master, self.slot))
+                out["old_gradient"] = self.slot.extra["old_gradient"]
         else:
             out["cache"] = a.view(a.state0, self.slot)
         return out

@@ -179,8 +179,12 @@ class AlexNet(Module):
         return self.fc8(x)
 
 
-def construct_classifier(net: Module, num_labels: int, num_epochs: int = 1, callbacks=()):
-    """images -> ``net`` -> softmax cross-entropy, top-1 / top-5 accuracy metrics."""
+def construct_classifier(net: Module, num_labels: int, num_epochs: int = 1, callbacks=(),
+                         l2_weight_decay: float = 0.0):
+    """images -> ``net`` -> softmax cross-entropy, top-1 / top-5 accuracy metrics.
+    ``l2_weight_decay``: L2 regularisation on the convolution and fully-connected matrices
+    (batch-norm parameters and biases excluded), as in the reference's ResNet script
+    (applications/vision/resnet.py:96-165)."""
     images = L.Input(data_field="samples", name="images")
     labels = L.Input(data_field="labels", name="labels")
     probs = L.Softmax(net(images), name="probs")
@@ -191,5 +195,13 @@ def construct_classifier(net: Module, num_labels: int, num_epochs: int = 1, call
         metrics.append(L.Metric(L.TopKCategoricalAccuracy(probs, labels, k=5, name="top5"),
                                 name="top-5 accuracy", unit="%"))
     layers = list(L.traverse_layer_graph([images, labels]))
-    return L.Model(num_epochs, layers=layers, objective_function=L.ObjectiveFunction([ce]),
+    terms = [ce]
+    if l2_weight_decay:
+        decayed = set()
+        for l in layers:
+            if type(l).__name__ in ("Convolution", "FullyConnected") and l.weights:
+                decayed.add(l.weights[0])
+        if decayed:
+            terms.append(L.L2WeightRegularization(weights=list(decayed), scale=l2_weight_decay))
+    return L.Model(num_epochs, layers=layers, objective_function=L.ObjectiveFunction(terms),
                    metrics=metrics, callbacks=list(callbacks))

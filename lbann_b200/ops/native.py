@@ -110,9 +110,28 @@ def check(rc: int, what: str) -> None:
         raise NativeError(f"{what} failed with code {rc}")
 
 
+_status_listeners = []
+
+
+def on_status(fn) -> None:
+    """``fn(code)`` is called whenever ``consume_status`` finds a non-zero device status."""
+    _status_listeners.append(fn)
+
+
+def set_wait_budget_ns(ns: int) -> None:
+    """Budget of the device-side waits on other ranks (0 restores the built-in 2 s)."""
+    lib = cuda_lib()
+    lib.lb_set_wait_budget_ns.restype = c_int
+    lib.lb_set_wait_budget_ns.argtypes = [ctypes.c_ulonglong]
+    check(lib.lb_set_wait_budget_ns(int(ns)), "lb_set_wait_budget_ns")
+
+
 def consume_status(raise_on_error: bool = True) -> int:
     """Synchronise the current stream and return (and clear) the device status word."""
     code = cuda_lib().lb_consume_status(stream_ptr())
+    if code:
+        for fn in list(_status_listeners):
+            fn(code)
     if code and raise_on_error:
         raise NativeError(f"device reported: {STATUS_TEXT.get(code, code)}")
     return code

@@ -18,7 +18,9 @@ import torch
 from . import native
 from .native import c_float, c_int, c_ll, c_void_p
 
-KIND = {"sgd": 0, "adam": 1, "adagrad": 2, "rmsprop": 3, "none": -1}
+# hypergradient Adam is applied tensor by tensor after the fused launch (``_step_hypergradient``):
+# the fused kernel sees those tensors as frozen
+KIND = {"sgd": 0, "adam": 1, "adagrad": 2, "rmsprop": 3, "none": -1, "hypergradient_adam": -1}
 _SEG_FMT = "<qqiiffffffffff"  # 64 bytes, mirrors OptSegment in csrc/optim.cu
 assert struct.calcsize(_SEG_FMT) == 64
 _configured = False
@@ -92,6 +94,7 @@ class Slot:
         self.hp: Dict[str, float] = {}
         self.step_count = 0
         self.l2 = 0.0
+        self.extra: Dict[str, torch.Tensor] = {}     # optimizer state beyond the two arenas
 
     def segment_bytes(self) -> bytes:
         hp = self.hp
@@ -225,8 +228,10 @@ class ParameterArena:
         for s in self.slots:
             if s.kind != "none":
                 s.step_count += 1
-        if any(s.kind == "adam" for s in self.slots):
+        if any(s.kind in ("adam", "hypergradient_adam") for s in self.slots):
             self.ensure_state1()
+        if any(s.kind == "hypergradient_adam" for s in self.slots):
+            self._step_hypergradient(inv_scale, skip_flag, inv_scale_dev)
         if self.master.is_cuda:
             segs = self._segments()
             if self.step_dev is None:
@@ -256,6 +261,41 @@ class ParameterArena:
                 self.refresh_compute()
             return
         self._step_cpu(inv_scale)
+
+    @torch.no_grad()
+    def _step_hypergradient(self, inv_scale, skip_flag, inv_scale_dev):
+        """Adam whose learning rate follows its own gradient
+        (src/optimizers/hypergradient_adam.cpp:137-185): lr += hyper_lr * <g, previous update
+        direction>, then a bias-corrected Adam step on g + eps whose direction is remembered."""
+        if skip_flag is not None and bool(int(skip_flag.item())):
+            return
+        scale = float(inv_scale) * (float(inv_scale_dev.item()) if inv_scale_dev is not None else 1.0)
+        for s in self.slots:
+            if s.kind != "hypergradient_adam":
+                continue
+            hp = s.hp
+            b1, b2 = float(hp.get("beta1", 0.9)), float(hp.get("beta2", 0.99))
+            eps = float(hp.get("eps", 1e-8))
+            x = self.view(self.master, s)
+            g = self.view(self.grad, s).float() * scale
+            if s.l2:
+                g = g + s.l2 * x
+            old = s.extra.get("old_gradient")
+            if old is None:
+                old = s.extra["old_gradient"] = torch.zeros_like(x)
+            lr = float(hp.get("learn_rate", 0.0)) + float(hp.get("hyper_learning_rate", 1e-7)) * \
+                float((g * old).sum())
+            hp["learn_rate"] = lr
+            t = s.step_count
+            corr = math.sqrt(1.0 - b2 ** t) / (1.0 - b1 ** t)
+            g = g + eps
+            m1, m2 = self.view(self.state0, s), self.view(self.state1, s)
+            m1.mul_(b1).add_(g, alpha=1 - b1)
+            m2.mul_(b2).addcmul_(g, g, value=1 - b2)
+            old.copy_(corr * m1 / (m2.sqrt() + eps))
+            x.sub_(lr * old)
+            if self.compute is not None:
+                self.view(self.compute, s).copy_(x)
 
     @torch.no_grad()
     def _step_cpu(self, inv_scale: float):

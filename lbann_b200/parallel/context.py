@@ -169,7 +169,8 @@ class ParallelContext:
         from ..ops.native import c_void_p
         arena = model.arena
         if (self.world_size == 1 or not self.group.native or self.tp_size > 1
-                or os.environ.get("LBANN_REPLICATED_OPTIMIZER")):
+                or os.environ.get("LBANN_REPLICATED_OPTIMIZER")
+                or any(s.kind == "hypergradient_adam" for s in arena.slots)):
             return
         mbuf = self._buffers.get(arena.master.data_ptr())
         gbuf = self._buffers.get(arena.grad.data_ptr())
@@ -191,6 +192,8 @@ class ParallelContext:
         stream already (``_install_early_reduce``); the rest follows here."""
         if self.world_size == 1:
             return
+        if os.environ.get("LBANN_DIAG_SKIP_GRAD_SYNC"):
+            return      # timing diagnostic only: the ranks then train on different gradients
         arena = model.arena
         buf = self._buffers.get(arena.grad.data_ptr())
         n = arena.total

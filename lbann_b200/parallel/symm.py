@@ -11,6 +11,7 @@ without GPUs.
 from __future__ import annotations
 
 import ctypes
+import weakref
 from typing import List, Optional, Sequence
 
 import torch
@@ -120,7 +121,27 @@ class SymmetricBuffer:
         return self.peer_ptrs[r] + offset_bytes
 
 
+_live_groups = weakref.WeakSet()
+
+
+def _poison_groups(code: int) -> None:
+    """A wait on another rank ran out somewhere on this device: the kernels involved left
+    before their closing rendezvous, so the use counters of the flag rows no longer agree
+    between the ranks and later rendezvous could pass on stale flags.  Every group of this
+    process refuses further collectives (restart from a checkpoint)."""
+    if code == 5:
+        for g in list(_live_groups):
+            g.poisoned = True
+
+
+native.on_status(_poison_groups)
+
+
 class SymmetricGroup:
+    """Collectives of one group launch on ONE stream at a time and in the same order on every
+    rank: the rendezvous rows (phases 0/1 all-reduce and reduce-scatter, 2/3 everything else)
+    are shared by all kernels of the group and count their uses on the device."""
+
     def __init__(self, device, ranks: Optional[Sequence[int]] = None, pg=None):
         self.device = torch.device(device)
         self.pg = pg
@@ -131,6 +152,8 @@ class SymmetricGroup:
         else:
             self.world, self.rank = 1, 0
         self.native = self.device.type == "cuda" and self.world > 1
+        self.poisoned = False
+        _live_groups.add(self)
         self.epoch = 0
         self.ctr = None          # use counters of the flag rows (this rank's own memory)
         self.ctr_ptr = None
@@ -143,6 +166,11 @@ class SymmetricGroup:
             self.ctr_ptr = self.ctr.data_ptr()
             self.staging = SymmetricBuffer(self, self.world * 4096 * 4)   # one-shot slots
             self.barrier_host()
+
+    def _guard(self):
+        if self.poisoned:
+            raise native.NativeError("this group saw a rendezvous time out: its ranks are no longer "
+                                     "in step; restart from the last checkpoint")
 
     def gather_object(self, obj):
         if not self.distributed:
@@ -170,6 +198,7 @@ class SymmetricGroup:
     def allreduce_(self, buf: SymmetricBuffer, dtype: torch.dtype, numel: int, scale: float = 1.0,
                    offset_bytes: int = 0, blocks: int = 32):
         """In-place sum over the group of ``numel`` elements at ``offset_bytes`` of ``buf``."""
+        self._guard()
         if self.world == 1:
             if scale != 1.0:
                 buf.view(dtype, numel, offset_bytes).mul_(scale)
@@ -195,6 +224,7 @@ class SymmetricGroup:
         owned by rank b % world) ends up summed over the group, times ``scale``, in its
         owner's buffer.  The other ranks' copies of the block keep their own contribution.
         No closing rendezvous: call a later collective before the buffers are overwritten."""
+        self._guard()
         if self.world == 1:
             if scale != 1.0:
                 buf.view(dtype)[e0:e1].mul_(scale)
@@ -215,6 +245,7 @@ class SymmetricGroup:
 
     def allreduce_small_(self, t: torch.Tensor, op: str = "sum"):
         """In-place all-reduce of a short fp32 tensor (<= 4096 elements) in one kernel."""
+        self._guard()
         if self.world == 1:
             return
         if not self.native or t.dtype != torch.float32 or t.numel() > 4096 or not t.is_contiguous():
@@ -237,6 +268,7 @@ class SymmetricGroup:
     def put_rows(self, src: torch.Tensor, dst_buf: SymmetricBuffer, dst_rank: int, dst_offset_bytes: int,
                  rows: int, row_bytes: int, src_pitch: int, dst_pitch: int):
         """Copy ``rows`` rows from a local tensor into rank ``dst_rank``'s buffer."""
+        self._guard()
         rc = _lib().lb_put_rows(src.data_ptr(), src_pitch, dst_buf.peer_ptr(dst_rank, dst_offset_bytes),
                                 dst_pitch, rows, row_bytes, native.stream_ptr())
         native.check(rc, "lb_put_rows")
@@ -248,6 +280,7 @@ class SymmetricGroup:
         """One kernel: ``x`` [n, dl, plane] -> interior of this rank's extended buffer, boundary
         planes -> the neighbours' halo planes, with the two rendezvous inside.  Returns False
         when the shape is not covered (the caller then uses separate puts and barriers)."""
+        self._guard()
         up = self.rank - 1 if self.rank > 0 else -1
         down = self.rank + 1 if self.rank < self.world - 1 else -1
         rc = _lib().lb_halo_exchange_fwd(ext._c_ptrs, self.pad._c_ptrs, self.rank, self.world, up, down,
@@ -265,6 +298,7 @@ class SymmetricGroup:
                       h: int, plane_bytes: int) -> bool:
         """One kernel: halo-plane gradients -> the neighbours' receive areas, and
         ``dx`` = interior of ``g`` + what the neighbours sent."""
+        self._guard()
         up = self.rank - 1 if self.rank > 0 else -1
         down = self.rank + 1 if self.rank < self.world - 1 else -1
         rc = _lib().lb_halo_exchange_bwd(recv._c_ptrs, self.pad._c_ptrs, self.rank, self.world, up, down,
@@ -282,6 +316,7 @@ class SymmetricGroup:
         """One kernel: slab i of ``src`` (``count`` contiguous slabs) -> rank i % world, slot
         (i // world) * world + rank of ``dst``; ends with a rendezvous of the group.  Returns
         False when the slabs are not multiples of 16 bytes (the caller falls back to puts)."""
+        self._guard()
         rc = _lib().lb_alltoall_slabs(dst._c_ptrs, self.pad._c_ptrs, self.rank, self.world,
                                       src.data_ptr(), count, slab_bytes, self.ctr_ptr,
                                       native.stream_ptr())
@@ -294,6 +329,7 @@ class SymmetricGroup:
 
     def barrier_device(self, phase: int = 3):
         """Stream-ordered rendezvous of the group (no host synchronisation)."""
+        self._guard()
         if self.world == 1:
             return
         if not self.native:

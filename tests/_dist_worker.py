@@ -411,6 +411,48 @@ def ltfb(strategy):
     return {"world": world, "weights": allw, "num_trainers": tr.comm.num_trainers}
 
 
+def abort_and_restart(ckpt_dir, fail_step, epochs):
+    """LeNet on the ranks of one trainer with a shared checkpoint after every epoch.  With
+    fail_step >= 0 rank 1 raises between two steps (after step ``fail_step``); the driver's
+    abort semantics then end this process with a non-zero code and the launcher tears the
+    other rank down.  A later run with the same checkpoint directory resumes."""
+    from lbann_b200 import driver
+    from lbann_b200.callbacks import ExecCallback
+    from test_lenet_cpu import build_lenet, make_reader
+    o = opts.reset()
+    o.set("disable_cuda", True)
+    images, labels, loss, acc = build_lenet()
+    cbs = [lbann.CallbackCheckpoint(checkpoint_dir=ckpt_dir, checkpoint_epochs=1)]
+    model = lbann.Model(epochs, layers=[images, labels], objective_function=loss,
+                        metrics=[lbann.Metric(acc, name="accuracy", unit="%")], callbacks=cbs)
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=64, random_seed=7), model=model,
+        data_reader=make_reader(256), optimizer=lbann.SGD(learn_rate=0.01, momentum=0.9))
+    rank = int(os.environ.get("RANK", "0"))
+
+    class FailAt(ExecCallback):
+        def on_batch_end(self, m):
+            if fail_step >= 0 and rank == 1 and m.ctx.step >= fail_step:
+                raise RuntimeError(f"injected failure on rank {rank} after step {m.ctx.step}")
+
+    orig = ExecTrainer.build_model
+
+    def build_with_failure(self, proto):
+        m = orig(self, proto)
+        m.callbacks.append(FailAt())
+        return m
+    ExecTrainer.build_model = build_with_failure
+    try:
+        tr, m = driver.run_experiment(exp, return_trainer=True)
+    finally:
+        ExecTrainer.build_model = orig
+    w = {x.name: float(x.values.detach().double().norm()) for x in m.weights}
+    res = {"world": int(os.environ.get("WORLD_SIZE", "1")), "weights": w, "epoch": m.ctx.epoch,
+           "step": m.ctx.step}
+    tr.shutdown()
+    return res
+
+
 if __name__ == "__main__":
     what, out = sys.argv[1], sys.argv[2]
     if what == "comm":
@@ -427,6 +469,8 @@ if __name__ == "__main__":
         res = data_store(sys.argv[3] == "preload")
     elif what == "mpfc":
         res = model_parallel_fc(int(sys.argv[3]), int(sys.argv[4]), len(sys.argv) > 5 and sys.argv[5] == "sharded")
+    elif what == "abort_restart":
+        res = abort_and_restart(sys.argv[3], int(sys.argv[4]), int(sys.argv[5]))
     elif what == "cosmoflow":
         res = cosmoflow(int(sys.argv[3]), int(sys.argv[4]), sys.argv[5] if len(sys.argv) > 5 else "float",
                         int(sys.argv[6]) if len(sys.argv) > 6 else 32,

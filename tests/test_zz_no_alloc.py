@@ -44,9 +44,28 @@ def test_two_calls_in_a_row_match_existing_entry_point(dtype):
     assert native.consume_status() == 0
 
 
+@pytest.mark.parametrize("rows,cols", [(130, 264), (5, 4096), (0, 64), (1, 8), (63, 520)])
+def test_edge_shapes_against_fp32_sums(rows, cols):
+    """Several vector blocks along the columns with a partly filled last one (264 and 520
+    columns), the widest matrix the workspace serves, no rows at all, a single row, fewer
+    rows than one block takes."""
+    fn, _ = _symbols()
+    torch.manual_seed(rows * 131 + cols)
+    x = torch.randn(rows, cols, device="cuda").to(torch.bfloat16)
+    out = torch.full((2 * cols,), float("nan"), dtype=torch.float32, device="cuda")
+    assert fn(x.data_ptr() if rows else out.data_ptr(), out.data_ptr(), rows, cols, native.DT_BF16,
+              native.stream_ptr()) == 0
+    torch.cuda.synchronize()
+    xf = x.float()
+    torch.testing.assert_close(out[:cols], xf.sum(0), rtol=1e-4, atol=1e-2)
+    torch.testing.assert_close(out[cols:], (xf * xf).sum(0), rtol=1e-4, atol=1e-2)
+
+
 def test_rejects_sizes_beyond_the_workspace():
     fn, _ = _symbols()
     x = torch.zeros(2, 8192, device="cuda", dtype=torch.float16)
     out = torch.zeros(2 * 8192, dtype=torch.float32, device="cuda")
     assert fn(x.data_ptr(), out.data_ptr(), 2, 8192, native.DT_F16, native.stream_ptr()) == -2
     assert fn(x.data_ptr(), out.data_ptr(), 2, 12, native.DT_F16, native.stream_ptr()) == -1
+    assert fn(x.data_ptr(), out.data_ptr(), -1, 64, native.DT_F16, native.stream_ptr()) == -1
+    assert fn(x.data_ptr() + 2, out.data_ptr(), 2, 64, native.DT_F16, native.stream_ptr()) == -1
