@@ -117,12 +117,38 @@ extern "C" {
 //   b_mn = 0: B stored [N][K] with row pitch ldb;  b_mn = 1: B stored [K][N] with row pitch ldb
 //   lda/ldb (elements) must be multiples of 8 and bases 16-byte aligned (TMA).
 //   in_dtype: 0 fp16, 1 bf16.  out_dtype: 0 fp16, 1 bf16, 2 fp32.
+int lb_gemm_bcast_tc(const void* A, const void* B, void* C, const float* bias, int M, int N, int K,
+                     int batch, long long lda, long long ldb, long long ldc, long long strideA,
+                     long long strideB, long long strideC, int a_mn, int b_mn, int in_dtype,
+                     int out_dtype, float alpha, float beta, int bias_mode, int act, float act_param,
+                     int bn_hint, void* const* bcast_ptrs, int bcast_ranks, void* stream_);
+
 int lb_gemm_tc(const void* A, const void* B, void* C, const float* bias, int M, int N, int K,
                int batch, long long lda, long long ldb, long long ldc, long long strideA,
                long long strideB, long long strideC, int a_mn, int b_mn, int in_dtype,
                int out_dtype, float alpha, float beta, int bias_mode, int act, float act_param,
                int bn_hint, void* stream_) {
+  return lb_gemm_bcast_tc(A, B, C, bias, M, N, K, batch, lda, ldb, ldc, strideA, strideB, strideC,
+                          a_mn, b_mn, in_dtype, out_dtype, alpha, beta, bias_mode, act, act_param,
+                          bn_hint, nullptr, 0, stream_);
+}
+
+// Same product with the all-gather epilogue: bcast_ptrs[q] is the (peer-mapped) address that
+// C has on rank q (entry of this rank = C); every finished tile is stored into all of them.
+// Needs a 16-bit output, beta == 0, N a multiple of 32 and 16-byte aligned rows; the caller
+// runs a rendezvous of the ranks before the outputs are read.
+int lb_gemm_bcast_tc(const void* A, const void* B, void* C, const float* bias, int M, int N, int K,
+                     int batch, long long lda, long long ldb, long long ldc, long long strideA,
+                     long long strideB, long long strideC, int a_mn, int b_mn, int in_dtype,
+                     int out_dtype, float alpha, float beta, int bias_mode, int act, float act_param,
+                     int bn_hint, void* const* bcast_ptrs, int bcast_ranks, void* stream_) {
   using namespace lb;
+  if (bcast_ranks < 0 || bcast_ranks > 8) return -1;
+  if (bcast_ranks > 0) {
+    if (!bcast_ptrs || out_dtype == kF32 || beta != 0.f || N % 32 || ldc % 8) return -1;
+    for (int q = 0; q < bcast_ranks; ++q)
+      if (!bcast_ptrs[q] || (reinterpret_cast<uintptr_t>(bcast_ptrs[q]) & 15)) return -1;
+  }
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
   if (M <= 0 || N <= 0 || K <= 0 || batch <= 0) return -1;
   if ((lda % 8) || (ldb % 8) || (strideA % 8) || (strideB % 8)) return -1;
@@ -163,6 +189,8 @@ int lb_gemm_tc(const void* A, const void* B, void* C, const float* bias, int M, 
   EpiParams e;
   e.C = C; e.bias = bias; e.alpha = alpha; e.beta = beta; e.out_dtype = out_dtype;
   e.bias_mode = bias ? bias_mode : 0; e.act = act; e.act_param = act_param; e.ldc = ldc;
+  e.bcast_ranks = bcast_ranks;
+  for (int q = 0; q < bcast_ranks; ++q) e.bcast_ptr[q] = bcast_ptrs[q];
 
 #define LB_LAUNCH(BN_)                                                        \
   {                                                                           \

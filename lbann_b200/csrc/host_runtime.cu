@@ -67,6 +67,13 @@ bool encode_tmap(CUtensorMap* out, int dtype, int rank, const void* base, const 
                  int swizzle_bytes) {
   EncodeTiledFn fn = get_encode();
   if (!fn) return false;
+  {
+    // The driver call needs a current context.  A host thread that has made no runtime call
+    // yet (an autograd worker thread entering a backward function) has none bound: selecting
+    // the device it already uses binds the primary context.
+    int dev = 0;
+    if (cudaGetDevice(&dev) == cudaSuccess) cudaSetDevice(dev);
+  }
   CUtensorMapDataType dt = CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   if (dtype == lb::kF16) dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
   if (dtype == lb::kF32) dt = CU_TENSOR_MAP_DATA_TYPE_FLOAT32;

@@ -40,6 +40,12 @@ struct EpiParams {
   int rs_rows = 0;
   int rs_store = 0;   // 1: plain stores (every source rank has its own slot at the owner)
   float* rs_ptr[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  // All-gather epilogue (fused GEMM -> all-gather): when bcast_ranks > 0 the finished tile is
+  // stored at the same offset into the output of EVERY rank (bcast_ptr[q], peer mapped; the
+  // entry of this rank is its own C), so each rank's column block of a model-parallel
+  // product lands in all replicas without a separate collective.  16-bit outputs, beta == 0.
+  int bcast_ranks = 0;
+  void* bcast_ptr[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
 };
 
 template <int BN>
@@ -170,7 +176,18 @@ __device__ __forceinline__ void tc_epilogue_rows(uint32_t taddr, bool row_ok, lo
 #pragma unroll
         for (int j = 0; j < 16; ++j) q[j] = pack2(v[2 * j], v[2 * j + 1], kF16);
       }
-      if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+      if (e.bcast_ranks > 0 && full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
+        // the same 64 bytes to every rank's copy of the output (peer stores over NVLink)
+#pragma unroll
+        for (int rk = 0; rk < 8; ++rk) {
+          if (rk >= e.bcast_ranks) break;
+          uint16_t* pd = reinterpret_cast<uint16_t*>(e.bcast_ptr[rk]) + off;
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4*>(pd + 8 * j) =
+                make_uint4(q[4 * j], q[4 * j + 1], q[4 * j + 2], q[4 * j + 3]);
+        }
+      } else if (full && ((reinterpret_cast<uintptr_t>(dst) & 15) == 0)) {
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           *reinterpret_cast<uint4*>(dst + 8 * j) =

@@ -64,8 +64,7 @@ class FullyConnected(ExecLayer):
         par = self.model.parallel
         if par is not None and self.data_layout == "model_parallel" and par.tp_size > 1:
             y = par.tp_linear(self, x)
-        elif (par is not None and self.w.sharded and par.world_size > 1 and not self.transpose
-              and self.out_size % (128 * par.world_size) == 0 and self.in_size % 8 == 0):
+        elif sharded_linear_ok(self, par):
             y = self._sharded_forward(par, x)
         elif self.transpose:
             w = self.w.handle.master.to(x.dtype).t()
@@ -76,25 +75,34 @@ class FullyConnected(ExecLayer):
         return [y.reshape(x.shape[0], *self.out_dims[0])]
 
     def _sharded_forward(self, par, x):
-        """Weights flagged ``sharded``: every rank multiplies by its own block of output rows
-        gathered tile by tile inside the GEMM (all-gather -> GEMM) and the weight gradient is
-        reduce-scattered by the GEMM epilogue into the owner's rows (parallel/
-        tensor_parallel.py::ShardedLinear).  The row block is a view of the arena's master
-        copy, so optimizer and checkpoints see ordinary weights."""
-        from ..parallel.tensor_parallel import ShardedLinear
-        P, r = par.world_size, par.comm.rank_in_trainer
-        rows = self.out_size // P
-        lin = getattr(self, "_sharded", None)
-        if lin is None:
-            lin = self._sharded = ShardedLinear(par.group, self.w.handle.master[r * rows:(r + 1) * rows])
-        lin.w_shard = self.w.handle.master[r * rows:(r + 1) * rows]
-        y = lin(x)
-        if self.b is not None:
-            y = y + self.b.handle.master.to(y.dtype)
-        if self.fused_act[0] != native.ACT_NONE:
-            from ..ops.gemm import _ACT_FN
-            y = _ACT_FN[self.fused_act[0]](y, self.fused_act[1])
-        return y
+        return sharded_linear_forward(self, par, x)
+
+
+def sharded_linear_forward(layer, par, x):
+    """Weights flagged ``sharded``: every rank multiplies by its own block of output rows
+    gathered tile by tile inside the GEMM (all-gather -> GEMM) and the weight gradient is
+    reduce-scattered by the GEMM epilogue into the owner's rows (parallel/
+    tensor_parallel.py::ShardedLinear).  The row block is a view of the arena's master
+    copy, so optimizer and checkpoints see ordinary weights.  ``x``: [rows, in_size]."""
+    from ..parallel.tensor_parallel import ShardedLinear
+    P, r = par.world_size, par.comm.rank_in_trainer
+    rows = layer.out_size // P
+    lin = getattr(layer, "_sharded", None)
+    if lin is None:
+        lin = layer._sharded = ShardedLinear(par.group, layer.w.handle.master[r * rows:(r + 1) * rows])
+    lin.w_shard = layer.w.handle.master[r * rows:(r + 1) * rows]
+    y = lin(x)
+    if layer.b is not None:
+        y = y + layer.b.handle.master.to(y.dtype)
+    if layer.fused_act[0] != native.ACT_NONE:
+        from ..ops.gemm import _ACT_FN
+        y = _ACT_FN[layer.fused_act[0]](y, layer.fused_act[1])
+    return y
+
+
+def sharded_linear_ok(layer, par) -> bool:
+    return (par is not None and layer.w.sharded and par.world_size > 1 and not layer.transpose
+            and layer.out_size % (128 * par.world_size) == 0 and layer.in_size % 8 == 0)
 
 
 class _ConvBase(ExecLayer):
@@ -205,6 +213,11 @@ class ChannelwiseFullyConnected(ExecLayer):
         par = self.model.parallel
         if par is not None and self.data_layout == "model_parallel" and par.tp_size > 1:
             y = par.tp_linear(self, x2)
+        elif sharded_linear_ok(self, par):
+            # FSDP-style weights (``Weights(sharded=True)``): all-gather -> GEMM forward,
+            # weight gradient reduce-scattered to the owners of the rows
+            y = sharded_linear_forward(self, par, x2.reshape(-1, self.in_size)).reshape(
+                n, self.channels, self.out_size)
         elif self.transpose:
             w = self.w.handle.cast(x.dtype) if x.is_cuda else self.w.handle.master.to(x.dtype)
             if x.is_cuda and x.dtype in (torch.float16, torch.bfloat16):

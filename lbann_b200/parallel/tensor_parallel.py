@@ -72,6 +72,80 @@ class _ModelParallelLinear(torch.autograd.Function):
         return dx.to(x.dtype), dw.to(w.dtype), db, None
 
 
+class _ModelParallelLinearFused(torch.autograd.Function):
+    """The same layer on this library's kernels (GPUs, 16-bit activations): the forward
+    product is ONE tcgen05 GEMM whose epilogue stores every finished tile of this rank's
+    column block into the output of all ranks of the column (peer stores over NVLink: GEMM
+    -> all-gather fused, ``lb_gemm_bcast_tc``); backward multiplies on the tensor cores,
+    sums the partial input gradients with the two-shot all-reduce kernel in symmetric
+    memory and writes the weight gradient of the own rows straight into the arena."""
+
+    @staticmethod
+    def forward(ctx, x, w_leaf, b_leaf, tp, layer):
+        import ctypes
+        from ..ops import native
+        from ..ops.gemm import _lib as gemm_lib
+        wh = layer.w.handle
+        bh = layer.b.handle if layer.b is not None else None
+        P = tp.size
+        n, k = wh.master.shape
+        lo, hi = tp.bounds(n)
+        tokens = x.shape[0]
+        dt = x.dtype
+        es = _esize(dt)
+        x = x.contiguous()
+        ybuf = tp.ws.get(("y", layer.name, tokens, n, dt), tokens * n * es)
+        y = ybuf.view(dt, tokens * n).view(tokens, n)
+        w_loc = wh.cast(dt)[lo:hi]
+        bias = bh.master.detach()[lo:hi].float().contiguous() if bh is not None else None
+        ptrs = (native.c_void_p * P)(*[ybuf.peer_ptr(q, lo * es) for q in range(P)])
+        lib = gemm_lib()
+        lib.lb_gemm_bcast_tc.restype = native.c_int
+        lib.lb_gemm_bcast_tc.argtypes = lib.lb_gemm_tc.argtypes[:-1] + [
+            ctypes.POINTER(native.c_void_p), native.c_int, native.c_void_p]
+        tp.sg.barrier_device(2)            # every rank is done reading the previous output
+        rc = lib.lb_gemm_bcast_tc(x.data_ptr(), w_loc.data_ptr(), ybuf.ptr + lo * es, native.ptr(bias),
+                                  tokens, hi - lo, k, 1, k, k, n, 0, 0, 0, 0, 0, native.dtype_code(dt),
+                                  native.dtype_code(dt), 1.0, 0.0, 1 if bias is not None else 0, 0, 0.0, 0,
+                                  ptrs, P, native.stream_ptr())
+        native.check(rc, "lb_gemm_bcast_tc")
+        native.count_launch()
+        tp.sg.barrier_device(3)            # all column blocks have landed everywhere
+        ctx.save_for_backward(x)
+        ctx.meta = (tp, layer, lo, hi, n, k)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.gemm import gemm
+        from ..ops.nn import column_sums
+        (x,) = ctx.saved_tensors
+        tp, layer, lo, hi, n, k = ctx.meta
+        wh = layer.w.handle
+        bh = layer.b.handle if layer.b is not None else None
+        dt = x.dtype
+        tokens = x.shape[0]
+        dy_loc = dy[:, lo:hi]
+        if dy_loc.stride(1) != 1 or dy_loc.stride(0) % 8 or dy_loc.data_ptr() % 16:
+            dy_loc = dy_loc.contiguous()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            dbuf = tp.ws.get(("dx", layer.name, tokens, k), tokens * k * 4)
+            part = dbuf.view(torch.float32, tokens * k).view(tokens, k)
+            gemm(dy_loc, wh.cast(dt)[lo:hi], out=part)                    # [tokens, k] partial sum
+            tp.sg.allreduce_(dbuf, torch.float32, tokens * k)
+            dx = part.to(dt)
+        if wh.grad is not None:
+            # rows of the other ranks stay zero here: the data-parallel reduction, which divides
+            # by the column size, completes them (hence the factor)
+            gemm(dy_loc, x, trans_a=True, out=wh.grad.view(n, k)[lo:hi], alpha=float(tp.size), beta=1.0)
+            wh.mark_ready()
+        if bh is not None and bh.grad is not None:
+            bh.grad.view(-1)[lo:hi].add_(column_sums(dy_loc.contiguous()) * float(tp.size))
+            bh.mark_ready()
+        return dx, None, None, None, None
+
+
 class TensorParallel:
     """Model-parallel fully-connected layers on a trainer's process grid (the reference's
     ``data_layout='model_parallel'`` over an MC,MR grid, src/layers/learning/
@@ -85,6 +159,10 @@ class TensorParallel:
         self.group = self.comm.grid_col_group
         self.size = self.comm.grid_height
         self.rank = dist.get_rank(self.group) if self.size > 1 else 0
+        # symmetric memory over the ranks of this grid column (GPUs only)
+        self.sg = SymmetricGroup(ctx.device, pg=self.group) if (
+            self.size > 1 and ctx.device.type == "cuda") else None
+        self.ws = _Workspace(self.sg) if self.sg is not None else None
 
     def bounds(self, n: int):
         per = (n + self.size - 1) // self.size
@@ -107,7 +185,24 @@ class TensorParallel:
         if self.size > 1:
             dist.all_reduce(t, group=self.group)
 
+    def _fused_ok(self, layer, x) -> bool:
+        if self.sg is None or not self.sg.native or layer.transpose or x.dim() != 2:
+            return False
+        n, k = layer.w.handle.master.shape
+        return (x.is_cuda and x.dtype in (torch.float16, torch.bfloat16) and n % (32 * self.size) == 0
+                and k % 8 == 0)
+
     def linear(self, layer, x: torch.Tensor) -> torch.Tensor:
+        if x.dim() == 3 and self._fused_ok(layer, x.reshape(-1, x.shape[-1])):
+            # per-token layers (channelwise fully connected): tokens are rows
+            y = _ModelParallelLinearFused.apply(
+                x.reshape(-1, x.shape[-1]), layer.w.handle.master,
+                layer.b.handle.master if layer.b is not None else None, self, layer)
+            return y.reshape(x.shape[0], x.shape[1], -1)
+        if self._fused_ok(layer, x):
+            return _ModelParallelLinearFused.apply(
+                x, layer.w.handle.master, layer.b.handle.master if layer.b is not None else None,
+                self, layer)
         w = layer.w.handle.master
         if layer.transpose:
             w = w.t()

@@ -243,10 +243,15 @@ def model_parallel_fc(grid_height, steps, sharded=False):
     """MLP whose hidden layers are model-parallel over a process-grid column (or, with
     ``sharded``, whose first layer has weights flagged sharded on a data-parallel trainer)."""
     o = opts.reset()
-    o.set("disable_cuda", True)
+    on_gpu = os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cuda"
+    if on_gpu:
+        o.set("default_dtype", "bf16")
+    else:
+        o.set("disable_cuda", True)
     if grid_height > 1:
         o.set("trainer_grid_height", grid_height)
     world = int(os.environ.get("WORLD_SIZE", "1"))
+    n1, n2, n3, nin = (128, 64, 64, 64) if on_gpu else (24, 10, 3, 12)
     x = lbann.Input(data_field="samples")
     t = lbann.Input(data_field="responses")
     layout = "model_parallel" if not sharded else "data_parallel"
@@ -254,17 +259,17 @@ def model_parallel_fc(grid_height, steps, sharded=False):
         w = lbann.Weights(initializer=lbann.HeNormalInitializer(), sharded=True, name="fc1_w")
         h = lbann.Relu(lbann.FullyConnected(x, num_neurons=256, has_bias=True, weights=[w], name="fc1"))
     else:
-        h = lbann.Relu(lbann.FullyConnected(x, num_neurons=24, has_bias=True, data_layout=layout, name="fc1"))
-    h = lbann.Relu(lbann.FullyConnected(h, num_neurons=10, has_bias=True, name="fc2"))
-    y = lbann.FullyConnected(h, num_neurons=3, has_bias=False, data_layout=layout, name="fc3")
+        h = lbann.Relu(lbann.FullyConnected(x, num_neurons=n1, has_bias=True, data_layout=layout, name="fc1"))
+    h = lbann.Relu(lbann.FullyConnected(h, num_neurons=n2, has_bias=True, name="fc2"))
+    y = lbann.FullyConnected(h, num_neurons=n3, has_bias=False, data_layout=layout, name="fc3")
     loss = lbann.MeanSquaredError(y, t, name="mse")
     model = lbann.Model(1, layers=list(lbann.traverse_layer_graph([x, t])),
                         objective_function=lbann.ObjectiveFunction([loss]))
     from test_models_cpu import _reader
     exp = lbann.proto.serialize.build_experiment(
         trainer=lbann.Trainer(mini_batch_size=8, random_seed=11), model=model,
-        data_reader=_reader(16, [12], "normal", response_dims=[3]),
-        optimizer=lbann.SGD(learn_rate=0.05, momentum=0.9))
+        data_reader=_reader(16, [nin], "normal", response_dims=[n3]),
+        optimizer=lbann.SGD(learn_rate=0.05 if not on_gpu else 0.01, momentum=0.9))
     tr = ExecTrainer(exp)
     m = tr.build_model(exp.model)
     dc = tr.data_coordinator

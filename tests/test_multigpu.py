@@ -89,6 +89,21 @@ def test_tensor_parallel_and_sharded_linear(tmp_path):
 
 
 @needs2
+def test_model_parallel_fc_on_fused_kernels(tmp_path):
+    """``data_layout='model_parallel'`` fully-connected layers on a 2 x 1 process grid: the
+    forward product stores its column block into both ranks' outputs from the GEMM epilogue
+    (GEMM -> all-gather in one kernel), backward sums the input gradients with the
+    all-reduce kernel.  Same losses and weights as one GPU."""
+    single = _run(1, ["mpfc", "1", "4"], str(tmp_path / "a.json"), ENV)
+    two = _run(2, ["mpfc", "2", "4"], str(tmp_path / "b.json"), ENV)
+    assert two["world"] == 2
+    for a, b in zip(single["losses"], two["losses"]):
+        assert abs(a - b) <= 2e-2 * max(1.0, abs(a)), (single["losses"], two["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - two["weight_norms"][k]) <= 1e-2 * max(1.0, abs(v)), k
+
+
+@needs2
 def test_partitioned_embedding_two_gpus(tmp_path):
     """The embedding table is split over two GPUs; rows are gathered from and gradients are
     added to their owners through peer memory.  Same losses and same trained table as the
