@@ -246,9 +246,50 @@ def case_optimizer(a, timer):
                    4.0 * n * (2 + 2 * states + 1) + 2.0 * n)
 
 
+def case_attention(a, timer):
+    """Fused causal attention (csrc/attention_tc.cu) on a packed [batch, seq, 3 * heads * 128]
+    projection; with --bwd the backward kernels (delta, key/value side, query side) are timed
+    as well, and --sdpa times torch's scaled_dot_product_attention on the same problem."""
+    import math
+    from lbann_b200.ops import attention as att
+    dt = _dtype(a.dtype)
+    B, H, S, D = a.batch, a.heads, a.seq, 128
+    E = H * D
+    qkv = (torch.randn(B, S, 3 * E, device="cuda") * 0.5).to(dt).requires_grad_(True)
+    scale = 1.0 / math.sqrt(D)
+    causal = not a.no_causal
+    flops_fwd = 4.0 * B * H * S * S * D * (0.5 if causal else 1.0)
+    io = 2.0 * B * S * E * 4
+    ms, mn = timer.run(lambda: att.attention_packed(qkv, H, scale, causal))
+    out = [_report("attention_fwd", [B, H, S, D], ms, mn, flops_fwd, io)]
+    if a.bwd:
+        y = att.attention_packed(qkv, H, scale, causal)
+        g = torch.randn_like(y)
+        ms, mn = timer.run(lambda: torch.autograd.grad(y, qkv, g, retain_graph=True))
+        # backward runs seven products where forward runs two (P is recomputed on both sides)
+        out.append(_report("attention_bwd", [B, H, S, D], ms, mn, 3.5 * flops_fwd, 2.5 * io))
+    if a.sdpa:
+        import torch.nn.functional as F
+        q, k, v = (qkv.detach()[:, :, i * E:(i + 1) * E].reshape(B, S, H, D).transpose(1, 2).contiguous()
+                   .requires_grad_(True) for i in range(3))
+        ms, mn = timer.run(lambda: F.scaled_dot_product_attention(q, k, v, is_causal=causal))
+        out.append(_report("sdpa_fwd", [B, H, S, D], ms, mn, flops_fwd, io))
+        if a.bwd:
+            y = F.scaled_dot_product_attention(q, k, v, is_causal=causal)
+            g = torch.randn_like(y)
+            ms, mn = timer.run(lambda: torch.autograd.grad(y, (q, k, v), g, retain_graph=True))
+            out.append(_report("sdpa_bwd", [B, H, S, D], ms, mn, 2.5 * flops_fwd, 2.5 * io))
+    return out
+
+
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("case", choices=["gemm", "gemm_comm", "conv", "pool", "optimizer", "linear_wgrad", "bn"])
+    ap.add_argument("case", choices=["gemm", "gemm_comm", "conv", "pool", "optimizer", "linear_wgrad", "bn",
+                                     "attention"])
+    ap.add_argument("--heads", type=int, default=16)
+    ap.add_argument("--seq", type=int, default=2048)
+    ap.add_argument("--no-causal", action="store_true")
+    ap.add_argument("--sdpa", action="store_true", help="also time torch's scaled_dot_product_attention")
     ap.add_argument("--dtype", default="bf16", choices=["fp16", "bf16"])
     ap.add_argument("--m", type=int, default=8192)
     ap.add_argument("--n", type=int, default=8192)
@@ -270,7 +311,8 @@ def main(argv=None):
         raise SystemExit("microbench needs a GPU")
     timer = _Timer(a.iters, a.warmup, flush=not a.no_flush)
     {"gemm": case_gemm, "gemm_comm": case_gemm_comm, "conv": case_conv, "pool": case_pool,
-     "optimizer": case_optimizer, "linear_wgrad": case_linear_wgrad, "bn": case_bn}[a.case](
+     "optimizer": case_optimizer, "linear_wgrad": case_linear_wgrad, "bn": case_bn,
+     "attention": case_attention}[a.case](
         a, timer)
     native.consume_status()
 

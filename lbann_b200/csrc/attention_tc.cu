@@ -13,10 +13,13 @@
 // head strides (so the three slices of a packed [B][S][3 H 128] projection are used in
 // place, and the output needs no permute).  Sequence lengths are multiples of 128.
 //
-// Warp roles (192 threads, one CTA per (batch, head, 128 query rows)):
+// Warp roles (320 threads, one CTA per (batch, head, 128 query rows)):
 //   warp 4  TMA producer (Q once, then a two-stage ring of K and V tiles)
 //   warp 5  TMEM allocation + MMA issue (one lane)
-//   warps 0-3  one query row per thread: softmax, rescaling of O, epilogue
+//   warps 0-3 and 6-9  softmax, rescaling of O, epilogue: two threads per query row, one for
+//              key columns 0-63 of a block and one for 64-127 (two warps per scheduler hide
+//              each other's TMEM and MUFU latency); the pair exchanges its row maxima
+//              through shared memory
 //
 // Backward is two kernels of the same shape, both recomputing P from Q, K and the saved
 // log-sum-exp: attn_bwd_kv_kernel (one CTA per 128 keys, loop over query blocks:
@@ -52,8 +55,10 @@ struct AttnShared {
   uint64_t k_full[2], v_full[2], k_empty[2], v_empty[2];
   uint64_t s_full[2], s_empty[2];
   uint64_t p_full, pv_done;
+  uint64_t x_full[2], l_full;  // the two threads of a row have published their partial values
   uint32_t tmem_base;
   int abort_flag;
+  float xch[3][2][128];      // [slot][column half][row]: partial row maxima (0, 1) / sums (2)
 };
 
 __device__ __forceinline__ void tmem_st_32x32(uint32_t taddr, const uint32_t (&r)[32]) {
@@ -124,6 +129,47 @@ __device__ __forceinline__ void att_store_row32(uint32_t tile, int row, int c0, 
   }
 }
 
+constexpr int kAttThreads = 320;
+
+// Role of a warp among the 8 that work on accumulator rows: `group` picks the column half,
+// `quarter` the 32 TMEM lanes (= rows) that the warp may access (warp index modulo 4).
+__device__ __forceinline__ bool att_row_role(int warp, int& group, int& quarter) {
+  if (warp == 4 || warp == 5) return false;
+  group = warp < 4 ? 0 : 1;
+  quarter = warp & 3;
+  return true;
+}
+
+// 64 fp32 values of one row -> 16-bit, columns [c0, c0 + 64) of a K-major tile.
+__device__ __forceinline__ void att_store_row64(uint32_t tile, int row, int c0, const uint32_t (&pk)[32]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+    sts128(tile + att_tile_off(row, c0 + 8 * j), make_uint4(pk[4 * j], pk[4 * j + 1], pk[4 * j + 2], pk[4 * j + 3]));
+}
+
+// 64 accumulator columns of one row, scaled, -> 16-bit global row (16-byte stores).
+__device__ __forceinline__ void att_store_out64(uint16_t* dst, const uint32_t (&a)[32], const uint32_t (&b)[32],
+                                                float mul, int dtype) {
+#pragma unroll
+  for (int k = 0; k < 32; k += 8) {
+    uint4 w;
+    w.x = pack2(__uint_as_float(a[k]) * mul, __uint_as_float(a[k + 1]) * mul, dtype);
+    w.y = pack2(__uint_as_float(a[k + 2]) * mul, __uint_as_float(a[k + 3]) * mul, dtype);
+    w.z = pack2(__uint_as_float(a[k + 4]) * mul, __uint_as_float(a[k + 5]) * mul, dtype);
+    w.w = pack2(__uint_as_float(a[k + 6]) * mul, __uint_as_float(a[k + 7]) * mul, dtype);
+    *reinterpret_cast<uint4*>(dst + k) = w;
+  }
+#pragma unroll
+  for (int k = 0; k < 32; k += 8) {
+    uint4 w;
+    w.x = pack2(__uint_as_float(b[k]) * mul, __uint_as_float(b[k + 1]) * mul, dtype);
+    w.y = pack2(__uint_as_float(b[k + 2]) * mul, __uint_as_float(b[k + 3]) * mul, dtype);
+    w.z = pack2(__uint_as_float(b[k + 4]) * mul, __uint_as_float(b[k + 5]) * mul, dtype);
+    w.w = pack2(__uint_as_float(b[k + 6]) * mul, __uint_as_float(b[k + 7]) * mul, dtype);
+    *reinterpret_cast<uint4*>(dst + 32 + k) = w;
+  }
+}
+
 __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -133,7 +179,7 @@ __device__ __forceinline__ float fast_exp2(float x) {
 // ------------------------------------------------------------------------------------
 // Forward
 // ------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kAttThreads, 1)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnParams p, int* status) {
   extern __shared__ uint8_t smem_raw[];
@@ -156,10 +202,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       mbar_init(smem_u32(&sh.k_empty[s]), 1);
       mbar_init(smem_u32(&sh.v_empty[s]), 1);
       mbar_init(smem_u32(&sh.s_full[s]), 1);
-      mbar_init(smem_u32(&sh.s_empty[s]), 128);
+      mbar_init(smem_u32(&sh.s_empty[s]), 256);
     }
-    mbar_init(smem_u32(&sh.p_full), 128);
+    mbar_init(smem_u32(&sh.p_full), 256);
     mbar_init(smem_u32(&sh.pv_done), 1);
+    mbar_init(smem_u32(&sh.x_full[0]), 256);
+    mbar_init(smem_u32(&sh.x_full[1]), 256);
+    mbar_init(smem_u32(&sh.l_full), 256);
     sh.abort_flag = 0;
     mbar_fence_init();
   }
@@ -251,8 +300,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
   } else {
     // ---------------------------------------------------------------- softmax / epilogue
-    const int row = threadIdx.x;                       // query row of this thread
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    int group = 0, quarter = 0;
+    att_row_role(warp, group, quarter);
+    const int row = quarter * 32 + lane;               // query row of this thread
+    const int col0 = group * 64;                       // its half of the key columns / head dim
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     float m = -1e30f, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nkv && ok; ++j) {
@@ -263,29 +315,58 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         break;
       }
       tc_fence_after();
-      const uint32_t tS = tS0 + s * 128 + lane_off;
+      const uint32_t tS = tS0 + s * 128 + lane_off + col0;
       const int limit = (p.causal && j == qb) ? row : 127;        // last visible key column
-      // pass 1: row maximum
+      uint32_t ra[32], rb[32];
+      tmem_ld_32x32(tS, ra);
+      tmem_ld_32x32(tS + 32, rb);
+      tmem_ld_wait();
       float mx = -1e30f;
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tS + c, r);
-        tmem_ld_wait();
 #pragma unroll
-        for (int i = 0; i < 32; ++i)
-          if (c + i <= limit) mx = fmaxf(mx, __uint_as_float(r[i]));
+      for (int i = 0; i < 32; ++i) {
+        if (col0 + i <= limit) mx = fmaxf(mx, __uint_as_float(ra[i]));
+        if (col0 + 32 + i <= limit) mx = fmaxf(mx, __uint_as_float(rb[i]));
       }
-      mx *= p.scale_log2;
+      // exchange with the thread that holds the other half of this row (bounded wait)
+      sh.xch[s][group][row] = mx;
+      mbar_arrive(smem_u32(&sh.x_full[s]));
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&sh.x_full[s]), (j >> 1) & 1, abort_flag));
+      if (!ok) {
+        if (lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
+        break;
+      }
+      mx = fmaxf(mx, sh.xch[s][group ^ 1][row]) * p.scale_log2;
       // the running maximum is only moved when it would grow by more than 2^8: until then
       // the probabilities stay below 256 and O needs no rescaling
       float alpha = 1.f;
-      float m_use = m;
       if (mx > m + 8.f) {
-        m_use = mx;
         alpha = fast_exp2(m - mx);
+        m = mx;
+      }
+      l *= alpha;
+      // probabilities, packed to 16 bits in registers (off the critical path: the tensor
+      // core is still busy with the previous block's P V)
+      uint32_t pk[32];
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float e0 = fast_exp2(__uint_as_float(ra[i]) * p.scale_log2 - m);
+        float e1 = fast_exp2(__uint_as_float(ra[i + 1]) * p.scale_log2 - m);
+        e0 = (col0 + i <= limit) ? e0 : 0.f;
+        e1 = (col0 + i + 1 <= limit) ? e1 : 0.f;
+        l += e0 + e1;
+        pk[i >> 1] = pack2(e0, e1, p.in_dtype);
+      }
+#pragma unroll
+      for (int i = 0; i < 32; i += 2) {
+        float e0 = fast_exp2(__uint_as_float(rb[i]) * p.scale_log2 - m);
+        float e1 = fast_exp2(__uint_as_float(rb[i + 1]) * p.scale_log2 - m);
+        e0 = (col0 + 32 + i <= limit) ? e0 : 0.f;
+        e1 = (col0 + 32 + i + 1 <= limit) ? e1 : 0.f;
+        l += e0 + e1;
+        pk[16 + (i >> 1)] = pack2(e0, e1, p.in_dtype);
       }
       if (j >= 1) {
+        // the previous P V has retired: the P buffer is free and O is consistent
         ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&sh.pv_done), (j - 1) & 1, abort_flag));
         if (!ok) {
           if (lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
@@ -293,35 +374,21 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         }
         tc_fence_after();
         if (__any_sync(0xffffffffu, alpha != 1.f)) {
-#pragma unroll 1
-          for (int c = 0; c < 128; c += 32) {
-            uint32_t r[32];
-            tmem_ld_32x32(tO + lane_off + c, r);
-            tmem_ld_wait();
+          uint32_t oa[32], ob[32];
+          tmem_ld_32x32(tO + lane_off + col0, oa);
+          tmem_ld_32x32(tO + lane_off + col0 + 32, ob);
+          tmem_ld_wait();
 #pragma unroll
-            for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * alpha);
-            tmem_st_32x32(tO + lane_off + c, r);
+          for (int i = 0; i < 32; ++i) {
+            oa[i] = __float_as_uint(__uint_as_float(oa[i]) * alpha);
+            ob[i] = __float_as_uint(__uint_as_float(ob[i]) * alpha);
           }
+          tmem_st_32x32(tO + lane_off + col0, oa);
+          tmem_st_32x32(tO + lane_off + col0 + 32, ob);
           tmem_st_wait();
         }
       }
-      l *= alpha;
-      m = m_use;
-      // pass 2: probabilities -> shared memory (A operand of P V)
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tS + c, r);
-        tmem_ld_wait();
-        float v[32];
-#pragma unroll
-        for (int i = 0; i < 32; ++i) {
-          const float e = fast_exp2(__uint_as_float(r[i]) * p.scale_log2 - m);
-          v[i] = (c + i <= limit) ? e : 0.f;
-          l += v[i];
-        }
-        att_store_row32(sP, row, c, v, p.in_dtype);
-      }
+      att_store_row64(sP, row, col0, pk);
       tc_fence_before();
       fence_async_smem();
       mbar_arrive(smem_u32(&sh.s_empty[s]));
@@ -332,26 +399,24 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       if (!ok && lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
     }
     if (ok) {
+      // the row sum is the sum of the two halves
+      sh.xch[2][group][row] = l;
+      mbar_arrive(smem_u32(&sh.l_full));
+      ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&sh.l_full), 0, abort_flag));
+      if (!ok && lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
+    }
+    if (ok) {
+      l += sh.xch[2][group ^ 1][row];
       tc_fence_after();
       const float inv = 1.f / l;
       const long long q = (long long)qb * 128 + row;
-      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + b * p.o_sb + q * p.o_ss + h * p.o_sh;
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tO + lane_off + c, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; i += 8) {
-          uint4 w;
-          w.x = pack2(__uint_as_float(r[i]) * inv, __uint_as_float(r[i + 1]) * inv, p.in_dtype);
-          w.y = pack2(__uint_as_float(r[i + 2]) * inv, __uint_as_float(r[i + 3]) * inv, p.in_dtype);
-          w.z = pack2(__uint_as_float(r[i + 4]) * inv, __uint_as_float(r[i + 5]) * inv, p.in_dtype);
-          w.w = pack2(__uint_as_float(r[i + 6]) * inv, __uint_as_float(r[i + 7]) * inv, p.in_dtype);
-          *reinterpret_cast<uint4*>(orow + c + i) = w;
-        }
-      }
-      if (p.lse) p.lse[((long long)b * p.H + h) * p.Sq + q] = m + log2f(l);
+      uint16_t* orow = reinterpret_cast<uint16_t*>(p.o) + b * p.o_sb + q * p.o_ss + h * p.o_sh + col0;
+      uint32_t oa[32], ob[32];
+      tmem_ld_32x32(tO + lane_off + col0, oa);
+      tmem_ld_32x32(tO + lane_off + col0 + 32, ob);
+      tmem_ld_wait();
+      att_store_out64(orow, oa, ob, inv, p.in_dtype);
+      if (p.lse && group == 0) p.lse[((long long)b * p.H + h) * p.Sq + q] = m + log2f(l);
     }
   }
   tc_fence_before();
@@ -408,7 +473,7 @@ struct __align__(128) AttnBwdShared {
   float delta[128];
 };
 
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kAttThreads, 1)
 attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                    const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                    const AttnParams p, int* status) {
@@ -429,7 +494,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     mbar_init(smem_u32(&sh.st_full), 1);
     mbar_init(smem_u32(&sh.st_empty), 1);
     mbar_init(smem_u32(&sh.s_full), 1);
-    mbar_init(smem_u32(&sh.p_full), 128);
+    mbar_init(smem_u32(&sh.p_full), 256);
     sh.abort_flag = 0;
     mbar_fence_init();
   }
@@ -499,8 +564,11 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       }
     }
   } else {
-    const int row = threadIdx.x;                       // key row of this thread
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    int group = 0, quarter = 0;
+    att_row_role(warp, group, quarter);
+    const int row = quarter * 32 + lane;               // key row of this thread
+    const int col0 = group * 64;                       // its half of the query columns / head dim
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = true;
     for (int it = 0; it < iters && ok; ++it) {
       const int i = i0 + it;
@@ -514,23 +582,28 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
       tc_fence_after();
       // causal, diagonal block: query column c sees key `row` only when c >= row
       const int first = (p.causal && i == kb) ? row : 0;
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
+      uint32_t pk[32], dk[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int c = col0 + half * 32;
         uint32_t rs[32], rd[32];
         tmem_ld_32x32(tS + lane_off + c, rs);
         tmem_ld_32x32(tDP + lane_off + c, rd);
         tmem_ld_wait();
-        float pv[32], dsv[32];
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const float e = fast_exp2(__uint_as_float(rs[k]) * p.scale_log2 - sh.lse[c + k]);
-          const float pr = (c + k >= first) ? e : 0.f;
-          pv[k] = pr;
-          dsv[k] = pr * (__uint_as_float(rd[k]) - sh.delta[c + k]) * p.scale;
+        for (int k = 0; k < 32; k += 2) {
+          float e0 = fast_exp2(__uint_as_float(rs[k]) * p.scale_log2 - sh.lse[c + k]);
+          float e1 = fast_exp2(__uint_as_float(rs[k + 1]) * p.scale_log2 - sh.lse[c + k + 1]);
+          e0 = (c + k >= first) ? e0 : 0.f;
+          e1 = (c + k + 1 >= first) ? e1 : 0.f;
+          const float d0 = e0 * (__uint_as_float(rd[k]) - sh.delta[c + k]) * p.scale;
+          const float d1 = e1 * (__uint_as_float(rd[k + 1]) - sh.delta[c + k + 1]) * p.scale;
+          pk[half * 16 + (k >> 1)] = pack2(e0, e1, p.in_dtype);
+          dk[half * 16 + (k >> 1)] = pack2(d0, d1, p.in_dtype);
         }
-        att_store_row32(sP, row, c, pv, p.in_dtype);
-        att_store_row32(sDS, row, c, dsv, p.in_dtype);
       }
+      att_store_row64(sP, row, col0, pk);
+      att_store_row64(sDS, row, col0, dk);
       tc_fence_before();
       fence_async_smem();
       mbar_arrive(smem_u32(&sh.p_full));
@@ -542,41 +615,17 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
     if (ok) {
       tc_fence_after();
       const long long key = (long long)kb * 128 + row;
-      uint16_t* dvrow = reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_sb + key * p.dv_ss + h * p.dv_sh;
-      uint16_t* dkrow = reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_sb + key * p.dk_ss + h * p.dk_sh;
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t r[32];
-        if (iters > 0) {
-          tmem_ld_32x32(tDV + lane_off + c, r);
-          tmem_ld_wait();
-        } else {
-#pragma unroll
-          for (int k = 0; k < 32; ++k) r[k] = 0u;
-        }
-#pragma unroll
-        for (int k = 0; k < 32; k += 8) {
-          uint4 w;
-          w.x = pack2(__uint_as_float(r[k]), __uint_as_float(r[k + 1]), p.in_dtype);
-          w.y = pack2(__uint_as_float(r[k + 2]), __uint_as_float(r[k + 3]), p.in_dtype);
-          w.z = pack2(__uint_as_float(r[k + 4]), __uint_as_float(r[k + 5]), p.in_dtype);
-          w.w = pack2(__uint_as_float(r[k + 6]), __uint_as_float(r[k + 7]), p.in_dtype);
-          *reinterpret_cast<uint4*>(dvrow + c + k) = w;
-        }
-        if (iters > 0) {
-          tmem_ld_32x32(tDK + lane_off + c, r);
-          tmem_ld_wait();
-        }
-#pragma unroll
-        for (int k = 0; k < 32; k += 8) {
-          uint4 w;
-          w.x = pack2(__uint_as_float(r[k]), __uint_as_float(r[k + 1]), p.in_dtype);
-          w.y = pack2(__uint_as_float(r[k + 2]), __uint_as_float(r[k + 3]), p.in_dtype);
-          w.z = pack2(__uint_as_float(r[k + 4]), __uint_as_float(r[k + 5]), p.in_dtype);
-          w.w = pack2(__uint_as_float(r[k + 6]), __uint_as_float(r[k + 7]), p.in_dtype);
-          *reinterpret_cast<uint4*>(dkrow + c + k) = w;
-        }
-      }
+      uint16_t* dvrow = reinterpret_cast<uint16_t*>(p.dv) + b * p.dv_sb + key * p.dv_ss + h * p.dv_sh + col0;
+      uint16_t* dkrow = reinterpret_cast<uint16_t*>(p.dk) + b * p.dk_sb + key * p.dk_ss + h * p.dk_sh + col0;
+      uint32_t ra[32], rb[32];
+      tmem_ld_32x32(tDV + lane_off + col0, ra);
+      tmem_ld_32x32(tDV + lane_off + col0 + 32, rb);
+      tmem_ld_wait();
+      att_store_out64(dvrow, ra, rb, 1.f, p.in_dtype);
+      tmem_ld_32x32(tDK + lane_off + col0, ra);
+      tmem_ld_32x32(tDK + lane_off + col0 + 32, rb);
+      tmem_ld_wait();
+      att_store_out64(dkrow, ra, rb, 1.f, p.in_dtype);
     }
   }
   tc_fence_before();
@@ -592,7 +641,7 @@ attn_bwd_kv_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constan
 //   per key block n:  S = Q K_n^T, dP = dO V_n^T  (TMEM);  dS = P * (dP - delta) * scale;
 //                     dQ += dS K_n
 // ------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kAttThreads, 1)
 attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                   const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmDO,
                   const AttnParams p, int* status) {
@@ -612,7 +661,7 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     mbar_init(smem_u32(&sh.st_full), 1);
     mbar_init(smem_u32(&sh.st_empty), 1);
     mbar_init(smem_u32(&sh.s_full), 1);
-    mbar_init(smem_u32(&sh.p_full), 128);
+    mbar_init(smem_u32(&sh.p_full), 256);
     sh.abort_flag = 0;
     mbar_fence_init();
   }
@@ -680,8 +729,11 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
     }
   } else {
-    const int row = threadIdx.x;                       // query row of this thread
-    const uint32_t lane_off = static_cast<uint32_t>(warp * 32) << 16;
+    int group = 0, quarter = 0;
+    att_row_role(warp, group, quarter);
+    const int row = quarter * 32 + lane;               // query row of this thread
+    const int col0 = group * 64;                       // its half of the key columns / head dim
+    const uint32_t lane_off = static_cast<uint32_t>(quarter * 32) << 16;
     bool ok = __all_sync(0xffffffffu, mbar_wait_bounded(smem_u32(&sh.kv_full), 0, abort_flag));
     if (!ok && lane == 0) raise_status(status, abort_flag, kTimeoutTmaFull);
     const float my_lse = ok ? sh.lse[row] : 0.f, my_delta = ok ? sh.delta[row] : 0.f;
@@ -693,21 +745,26 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
       }
       tc_fence_after();
       const int limit = (p.causal && it == qb) ? row : 127;
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
+      uint32_t dk[32];
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        const int c = col0 + half * 32;
         uint32_t rs[32], rd[32];
         tmem_ld_32x32(tS + lane_off + c, rs);
         tmem_ld_32x32(tDP + lane_off + c, rd);
         tmem_ld_wait();
-        float dsv[32];
 #pragma unroll
-        for (int k = 0; k < 32; ++k) {
-          const float e = fast_exp2(__uint_as_float(rs[k]) * p.scale_log2 - my_lse);
-          const float pr = (c + k <= limit) ? e : 0.f;
-          dsv[k] = pr * (__uint_as_float(rd[k]) - my_delta) * p.scale;
+        for (int k = 0; k < 32; k += 2) {
+          float e0 = fast_exp2(__uint_as_float(rs[k]) * p.scale_log2 - my_lse);
+          float e1 = fast_exp2(__uint_as_float(rs[k + 1]) * p.scale_log2 - my_lse);
+          e0 = (c + k <= limit) ? e0 : 0.f;
+          e1 = (c + k + 1 <= limit) ? e1 : 0.f;
+          dk[half * 16 + (k >> 1)] = pack2(e0 * (__uint_as_float(rd[k]) - my_delta) * p.scale,
+                                           e1 * (__uint_as_float(rd[k + 1]) - my_delta) * p.scale,
+                                           p.in_dtype);
         }
-        att_store_row32(sDS, row, c, dsv, p.in_dtype);
       }
+      att_store_row64(sDS, row, col0, dk);
       tc_fence_before();
       fence_async_smem();
       mbar_arrive(smem_u32(&sh.p_full));
@@ -719,22 +776,12 @@ attn_bwd_q_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant
     if (ok) {
       tc_fence_after();
       const long long q = (long long)qb * 128 + row;
-      uint16_t* dqrow = reinterpret_cast<uint16_t*>(p.dq) + b * p.dq_sb + q * p.dq_ss + h * p.dq_sh;
-#pragma unroll 1
-      for (int c = 0; c < 128; c += 32) {
-        uint32_t r[32];
-        tmem_ld_32x32(tDQ + lane_off + c, r);
-        tmem_ld_wait();
-#pragma unroll
-        for (int k = 0; k < 32; k += 8) {
-          uint4 w;
-          w.x = pack2(__uint_as_float(r[k]), __uint_as_float(r[k + 1]), p.in_dtype);
-          w.y = pack2(__uint_as_float(r[k + 2]), __uint_as_float(r[k + 3]), p.in_dtype);
-          w.z = pack2(__uint_as_float(r[k + 4]), __uint_as_float(r[k + 5]), p.in_dtype);
-          w.w = pack2(__uint_as_float(r[k + 6]), __uint_as_float(r[k + 7]), p.in_dtype);
-          *reinterpret_cast<uint4*>(dqrow + c + k) = w;
-        }
-      }
+      uint16_t* dqrow = reinterpret_cast<uint16_t*>(p.dq) + b * p.dq_sb + q * p.dq_ss + h * p.dq_sh + col0;
+      uint32_t ra[32], rb[32];
+      tmem_ld_32x32(tDQ + lane_off + col0, ra);
+      tmem_ld_32x32(tDQ + lane_off + col0 + 32, rb);
+      tmem_ld_wait();
+      att_store_out64(dqrow, ra, rb, 1.f, p.in_dtype);
     }
   }
   tc_fence_before();
@@ -792,7 +839,7 @@ int lb_attention_fwd(const void* q, const void* k, const void* v, void* o, float
     configured = true;
   }
   dim3 grid(Sq / 128, H, B);
-  attn_fwd_kernel<<<grid, 192, smem, stream>>>(tq, tk, tv, p, lbhost::status_word());
+  attn_fwd_kernel<<<grid, kAttThreads, smem, stream>>>(tq, tk, tv, p, lbhost::status_word());
   return (int)cudaGetLastError();
 }
 
@@ -847,9 +894,9 @@ int lb_attention_bwd(const void* q, const void* k, const void* v, const void* o,
     cudaFuncSetAttribute(attn_bwd_q_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_q);
     configured = true;
   }
-  attn_bwd_kv_kernel<<<dim3(Sk / 128, H, B), 192, smem_kv, stream>>>(tq, tk, tv, tdo, p,
+  attn_bwd_kv_kernel<<<dim3(Sk / 128, H, B), kAttThreads, smem_kv, stream>>>(tq, tk, tv, tdo, p,
                                                                      lbhost::status_word());
-  attn_bwd_q_kernel<<<dim3(Sq / 128, H, B), 192, smem_q, stream>>>(tq, tk, tv, tdo, p,
+  attn_bwd_q_kernel<<<dim3(Sq / 128, H, B), kAttThreads, smem_q, stream>>>(tq, tk, tv, tdo, p,
                                                                    lbhost::status_word());
   return (int)cudaGetLastError();
 }
