@@ -10,69 +10,9 @@
 // They take the place of the reference's Aluminum / NCCL calls (src/comm.cpp:440-625),
 // of DiHydrogen's halo exchange and tensor shufflers (src/utils/distconv.cpp:390-432), and
 // of the per-weight gradient allreduce (include/lbann/optimizers/optimizer_impl.hpp:101-143).
-#include "common.cuh"
+#include "comm_sync.cuh"
 
 namespace lb {
-
-constexpr int kMaxRanks = 8;
-constexpr int kCommBlocks = 64;          // upper bound on blocks of a collective kernel
-// signal pad layout (uint32): [phase 0..3][block][source rank]
-constexpr int kPadWords = 4 * kCommBlocks * kMaxRanks;
-
-struct PeerPtrs {
-  void* buf[kMaxRanks];        // data buffers (peer mapped), buf[my_rank] is local
-  uint32_t* pad[kMaxRanks];    // signal pads
-};
-
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-
-// Block-level rendezvous with the same block index on every rank of the group.
-// Threads 0..world-1 each handle one peer.  Returns false after the wait budget ran out.
-//
-// The epoch that the flags are compared with is not a launch argument: every flag row
-// (phase, block) has a use counter `ctr` in this rank's own memory, read at the start of the
-// rendezvous and advanced at its end.  All ranks run the same sequence of kernels, so their
-// counters agree, and a launch carries no per-step value - which is what lets a training
-// step be captured once as a CUDA graph and replayed.
-__device__ __forceinline__ bool block_rendezvous(const PeerPtrs& pp, int rank, int world,
-                                                 int phase, uint32_t* ctr, int* status) {
-  __shared__ int ok_flag;
-  __shared__ uint32_t epoch_sh;
-  const int row = phase * kCommBlocks + blockIdx.x;
-  if (threadIdx.x == 0) {
-    ok_flag = 1;
-    epoch_sh = ctr[row] + 1;
-  }
-  __syncthreads();          // all of this block's earlier writes are issued
-  const uint32_t epoch = epoch_sh;
-  if ((int)threadIdx.x < world) {
-    const int peer = threadIdx.x;
-    __threadfence_system();
-    uint32_t* remote = pp.pad[peer] + (size_t)row * kMaxRanks + rank;
-    st_release_sys(remote, epoch);
-    const uint32_t* mine = pp.pad[rank] + (size_t)row * kMaxRanks + peer;
-    const uint64_t t0 = globaltimer_ns();
-    const uint64_t budget = peer_wait_budget_ns(status);
-    uint32_t spins = 0;
-    while ((int32_t)(ld_acquire_sys(mine) - epoch) < 0) {
-      if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > budget) {
-        ok_flag = 0;
-        if (status) atomicCAS(status, 0, kTimeoutPeerFlag);
-        break;
-      }
-    }
-  }
-  __syncthreads();
-  if (threadIdx.x == 0) ctr[row] = epoch;
-  return ok_flag != 0;
-}
 
 // ---------------------------------------------------------------------------------
 // Two-shot all-reduce (sum) in place over fp32 / 16-bit buffers:
@@ -245,6 +185,30 @@ alltoall_slabs_kernel(PeerPtrs pp, int rank, int world, const uint4* __restrict_
   block_rendezvous(pp, rank, world, 3, ctr, status);
 }
 
+// Rows of a local matrix to arbitrary (rank, row) destinations: row j of `src` is stored as
+// row dst_row[j] of rank dst_rank[j]'s buffer (negative rank: the row goes nowhere).  One
+// kernel with the closing rendezvous inside: the data movement between two GPU subsets
+// ("grids") of a trainer, where every sample has one owner on either side
+// (what the reference does with El::copy::TranslateBetweenGrids,
+// include/lbann/layers/transform/split.hpp:135-243).
+__global__ void __launch_bounds__(512)
+scatter_rows_kernel(PeerPtrs pp, int rank, int world, const uint4* __restrict__ src,
+                    const int* __restrict__ dst_rank, const int* __restrict__ dst_row,
+                    long long rows, long long row_vec, uint32_t* ctr, int* status) {
+  __shared__ uint4* dst[kMaxRanks];
+  if ((int)threadIdx.x < world) dst[threadIdx.x] = reinterpret_cast<uint4*>(pp.buf[threadIdx.x]);
+  __syncthreads();
+  const long long total = rows * row_vec;
+  for (long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x; idx < total;
+       idx += (long long)gridDim.x * blockDim.x) {
+    const long long j = idx / row_vec, v = idx - j * row_vec;
+    const int q = dst_rank[j];
+    if (q < 0 || q >= world) continue;
+    dst[q][(long long)dst_row[j] * row_vec + v] = src[idx];
+  }
+  block_rendezvous(pp, rank, world, 3, ctr, status);
+}
+
 // Group barrier as its own (single block) kernel: orders "my puts are visible" with the
 // peers' consumers.  phase selects an independent flag row.
 __global__ void group_barrier_kernel(PeerPtrs pp, int rank, int world, int phase, uint32_t* ctr,
@@ -413,15 +377,6 @@ dist_embed_scatter_kernel(PeerPtrs pp, int rank, int world, const long long* __r
     const T* g = dy + s * dim;
     for (int k = lane; k < dim; k += 32) atomicAdd(row + k, scale * to_f32<T>(g[k]));
   }
-}
-
-static PeerPtrs make_ptrs(void* const* bufs, void* const* pads, int world) {
-  PeerPtrs pp;
-  for (int i = 0; i < kMaxRanks; ++i) {
-    pp.buf[i] = i < world ? bufs[i] : nullptr;
-    pp.pad[i] = i < world ? reinterpret_cast<uint32_t*>(pads[i]) : nullptr;
-  }
-  return pp;
 }
 
 }  // namespace lb
@@ -624,6 +579,24 @@ int lb_alltoall_slabs(void* const* bufs, void* const* pads, int rank, int world,
   // every rank launches the same number of blocks (they meet pairwise), whatever its count
   alltoall_slabs_kernel<<<kCommBlocks, 512, 0, s>>>(pp, rank, world, reinterpret_cast<const uint4*>(src),
                                                      count, slab_bytes / 16, ctr, lbhost::status_word());
+  return (int)cudaGetLastError();
+}
+
+// bufs: receive buffers of the group's ranks.  src: `rows` rows of row_bytes bytes (may be
+// null when rows == 0: a rank that only receives still takes part in the rendezvous).
+int lb_scatter_rows(void* const* bufs, void* const* pads, int rank, int world, const void* src,
+                    const int* dst_rank, const int* dst_row, long long rows, long long row_bytes,
+                    unsigned* ctr, void* stream_) {
+  using namespace lb;
+  if (world < 2 || world > kMaxRanks || rows < 0 || row_bytes <= 0) return -1;
+  if (row_bytes % 16 || (reinterpret_cast<uintptr_t>(src) & 15)) return -2;
+  for (int r = 0; r < world; ++r)
+    if (reinterpret_cast<uintptr_t>(bufs[r]) & 15) return -2;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  PeerPtrs pp = make_ptrs(bufs, pads, world);
+  scatter_rows_kernel<<<kCommBlocks, 512, 0, s>>>(pp, rank, world, reinterpret_cast<const uint4*>(src),
+                                                   dst_rank, dst_row, rows, row_bytes / 16, ctr,
+                                                   lbhost::status_word());
   return (int)cudaGetLastError();
 }
 

@@ -72,7 +72,12 @@ class ExecLayer:
         self.hint_layer = proto.hint_layer or None
         self.data_layout = proto.data_layout or "data_parallel"
         self.frozen = bool(proto.freeze)
-        self.grid_tag = proto.grid_tag.value if proto.HasField("grid_tag") else 0
+        if proto.HasField("grid_tag"):
+            self.grid_tag = int(proto.grid_tag.value)
+        elif proto.HasField("parallel_strategy") and proto.parallel_strategy.HasField("grid_tag"):
+            self.grid_tag = int(proto.parallel_strategy.grid_tag.value)
+        else:
+            self.grid_tag = -1     # inherit from the parents (src/models/model.cpp:1041-1090)
         self.parallel_strategy = proto.parallel_strategy if proto.HasField("parallel_strategy") else None
         self.dtype = _DTYPES.get(proto.datatype, None)   # None -> model default
         self.parents: List["ExecLayer"] = []

@@ -905,9 +905,9 @@ class CrossGridSum(ExecLayer):
         return [tuple(d) for d in in_dims]
 
     def forward(self, xs, training):
-        par = self.model.parallel
-        if par is not None and par.subgrids_active():
-            return [par.cross_grid_sum(self, x) for x in xs]
+        # With sub-grids the executor has brought every branch's tensor to this layer's grid
+        # (the whole trainer, since its parents sit on different grids) and sends the total
+        # back out to the branches; the layer itself is a plain sum.
         total = xs[0]
         for x in xs[1:]:
             total = total + x
@@ -926,9 +926,6 @@ class CrossGridSumSlice(ExecLayer):
         return [tuple(d[:-1]) + (d[-1] // k,) for d in in_dims]
 
     def forward(self, xs, training):
-        par = self.model.parallel
-        if par is not None and par.subgrids_active():
-            return [par.cross_grid_sum_slice(self, i, x) for i, x in enumerate(xs)]
         total = xs[0]
         for x in xs[1:]:
             total = total + x

@@ -160,6 +160,12 @@ class ExecModel:
         self._setup_execution_order()
         if self.parallel is not None:
             self.parallel.prepare_model(self)
+        self.subgrid = getattr(self.parallel, "subgrid", None) if self.parallel is not None else None
+        if self.subgrid is not None:
+            self.subgrid.resolve_tags(self)
+        else:
+            for l in self.layers:
+                l.grid_tag = 0
         if self.distconv is not None:
             self.distconv.prepare_model(self)
         for layer in self.layers:
@@ -524,6 +530,10 @@ class ExecModel:
         self._mean_cache = {}
         cbs = self.callbacks
         occurrence = defaultdict(int)
+        sg = self.subgrid
+        if sg is not None:
+            sg.dangling.clear()
+            base_mb = self.current_mini_batch_size
         for layer in self.layers:
             if getattr(layer, "dead", False):        # folded into a fused consumer
                 acts[layer.name] = [None] * max(len(layer.out_dims), 1)
@@ -540,6 +550,26 @@ class ExecModel:
                 xs.append(acts[pn][self._slot(parent, layer, k)])
             if self.distconv is not None:
                 xs = self.distconv.adapt_inputs(self, layer, xs)
+            if sg is not None:
+                # sub-graph parallelism: bring every input to this layer's grid (collective
+                # over the trainer), then only the grid's ranks compute
+                tag = layer.grid_tag
+                moved = []
+                for k, (pn, x) in enumerate(zip(layer.parent_names, xs)):
+                    parent = self.layers_by_name[pn]
+                    if parent.grid_tag != tag:
+                        slot = self._slot(parent, layer, 0)
+                        dims = parent.out_dims[slot] if slot < len(parent.out_dims) else parent.out_dims[0]
+                        dt = x.dtype if x is not None else self._act_dtype(parent)
+                        x = sg.transfer(x, parent.grid_tag, tag, self._global_mb, dims, dt,
+                                        f"{pn}>{layer.name}#{k}")
+                    moved.append(x)
+                xs = moved
+                if not sg.member(tag):
+                    acts[layer.name] = [None] * max(len(layer.out_dims), 1)
+                    continue
+                self.current_mini_batch_size = sg.local_count(tag, self._global_mb) if layer.type != "input" \
+                    else base_mb
             for cb in cbs:
                 cb.on_layer_forward_begin(self, layer, mode)
             if self.layer_timing:
@@ -562,6 +592,8 @@ class ExecModel:
                 self.distconv.note_outputs(self, layer)
             for cb in cbs:
                 cb.on_layer_forward_end(self, layer, mode)
+        if sg is not None:
+            self.current_mini_batch_size = base_mb
         self.acts = acts
         return acts
 
@@ -572,6 +604,10 @@ class ExecModel:
             return hit
         layer = self.layers_by_name[layer_name]
         y = self.acts[layer_name][0] if self.acts[layer_name] else self.acts[layer.parent_names[0]][0]
+        if y is None:        # computed on a sub-grid this rank does not belong to
+            val = torch.zeros((), device=self.device)
+            self._mean_cache[layer_name] = val
+            return val
         val = y.float().sum() / float(self._global_mb)
         self._mean_cache[layer_name] = val
         return val
@@ -583,7 +619,17 @@ class ExecModel:
             total = v if total is None else total + v
         if total is None:
             total = torch.zeros((), device=self.device)
+        if self.subgrid is not None:
+            # tensors that this rank handed to another grid and does not consume itself: a zero
+            # term keeps them in the autograd graph, so that this rank takes part in the
+            # exchanges of the backward pass
+            for d in self.subgrid.dangling:
+                total = total + d.float().sum() * 0.0
         return total
+
+    def _act_dtype(self, layer) -> torch.dtype:
+        dt = layer.dtype or self.default_dtype
+        return dt if isinstance(dt, torch.dtype) else self.default_dtype
 
     def l2_value(self) -> torch.Tensor:
         total = torch.zeros((), dtype=torch.float32, device=self.device)

@@ -110,7 +110,17 @@ class ExecTrainer:
         if self.comm.procs_per_trainer > 1:
             from ..parallel.context import ParallelContext
             self.parallel = ParallelContext(self.comm, self.device)
-        needs_dc = any(l.HasField("parallel_strategy") for l in model_pb.layer)
+        n_sub = opts.current().get_int("num_subgrids") or opts.current().get_int("num_subgrids_block_order")
+        if self.parallel is not None and n_sub > 1:
+            # branch (sub-graph) parallelism: layers tagged with a grid run on that GPU subset
+            from ..parallel.subgrid import SubgridContext
+            self.parallel.subgrid = SubgridContext(self.comm, self.device, n_sub, self.parallel.group)
+            self.parallel._subgrids = True
+        def partitions(l):      # a strategy that only names a grid is not a tensor partition
+            ps = l.parallel_strategy
+            return any(getattr(ps, f, 0) for f in ("sample_groups", "depth_groups", "height_groups",
+                                                   "width_groups", "channel_groups", "filter_groups"))
+        needs_dc = any(l.HasField("parallel_strategy") and partitions(l) for l in model_pb.layer)
         if needs_dc and not opts.current().get_bool("disable_distconv"):
             from ..parallel.distconv import DistconvContext
             self.distconv = DistconvContext(self.comm, self.device, self.parallel)

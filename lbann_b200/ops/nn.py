@@ -10,6 +10,7 @@ mirroring the reference's destination-scale / gradient-scale contract
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Callable, Optional
 
 import torch
@@ -38,6 +39,17 @@ def _lib():
         lib.lb_pool_bwd_tiled_strided.restype = c_int
         lib.lb_pool_bwd_tiled_strided.argtypes = [c_void_p, c_void_p, c_void_p, P(c_int), c_int, c_float,
                                                   c_ll, c_int, c_void_p]
+        VPP = P(c_void_p)
+        lib.lb_bn_fused_ws_floats.restype = c_int
+        lib.lb_bn_fused_ws_floats.argtypes = [c_int]
+        lib.lb_bn_fused_fwd.restype = c_int
+        lib.lb_bn_fused_fwd.argtypes = [c_void_p] * 8 + [c_ll, c_int, c_float, c_float, c_float, c_float,
+                                                       c_int, c_float, c_int, VPP, VPP, c_int, c_int, c_ll,
+                                                       c_void_p, c_void_p]
+        lib.lb_bn_fused_bwd.restype = c_int
+        lib.lb_bn_fused_bwd.argtypes = [c_void_p] * 9 + [c_ll, c_int, c_float, c_float, c_float, c_int,
+                                                       c_float, c_int, VPP, VPP, c_int, c_int, c_ll,
+                                                       c_void_p, c_void_p]
         lib.lb_pool_bwd.restype = c_int
         lib.lb_pool_bwd.argtypes = [c_void_p, c_void_p, c_void_p, P(c_int), P(c_ll), c_int, c_void_p]
         lib.lb_layer_norm_fwd.restype = c_int
@@ -643,6 +655,101 @@ def pooling(x, ksize, pad, stride, mode: str, bwd_act: int = native.ACT_NONE,
 
 
 # --------------------------------------------------------------------------- batch norm
+class GroupSum:
+    """In-place sum of an fp32 tensor over the ranks of a symmetric group, as a callable that
+    also names the group: the fused batch-norm kernels then do the reduction themselves."""
+
+    def __init__(self, group, fn):
+        self.group, self.fn = group, fn
+
+    def __call__(self, t):
+        return self.fn(t)
+
+
+_bn_workspaces = {}
+
+
+def _bn_ws(owner, tag, rows, C, device):
+    key = (id(owner), tag, rows, C)
+    ws = _bn_workspaces.get(key)
+    if ws is None:
+        ws = torch.zeros(_lib().lb_bn_fused_ws_floats(C), dtype=torch.float32, device=device)
+        _bn_workspaces[key] = ws
+    return ws
+
+
+def _bn_fused_peers(reduce_fn):
+    """(staging ptrs, pad ptrs, rank, world, slot stride, counters) for the fused kernels, or
+    None when the statistics group cannot be served by them."""
+    if reduce_fn is None:
+        return (None, None, 0, 1, 0, None)
+    g = getattr(reduce_fn, "group", None)
+    if g is None or not g.native or g.poisoned:
+        return None
+    return (g.staging._c_ptrs, g.pad._c_ptrs, g.rank, g.world, 4096, g.ctr_ptr)
+
+
+class _BatchNormFused(torch.autograd.Function):
+    """Training-mode batch norm as one cooperative kernel per direction, statistics over the
+    ranks of a symmetric group reduced inside the kernel (csrc/bn_fused.cu)."""
+
+    @staticmethod
+    def forward(ctx, x, s_leaf, b_leaf, sh, bh, run_mean, run_var, eps, decay, correction,
+                reduce_fn, count_scale, act, act_p, peers):
+        ndim = x.dim()
+        x_cl = _cl_view(x)
+        if not x_cl.is_contiguous():
+            x_cl = x_cl.contiguous()
+        C = x_cl.shape[-1]
+        rows = x_cl.numel() // C
+        staging, pads, rank, world, stride, ctr = peers
+        count = float(rows * count_scale)
+        y = torch.empty_like(x_cl)
+        stats = torch.empty(2 * C, dtype=torch.float32, device=x.device)
+        scale = sh.master.detach() if sh is not None else None
+        bias = bh.master.detach() if bh is not None else None
+        owner = sh if sh is not None else (bh if bh is not None else run_mean)
+        ws = _bn_ws(owner, "fwd", rows, C, x.device)
+        rc = _lib().lb_bn_fused_fwd(x_cl.data_ptr(), native.ptr(scale), native.ptr(bias), y.data_ptr(),
+                                    stats.data_ptr(), native.ptr(run_mean), native.ptr(run_var),
+                                    ws.data_ptr(), rows, C, count, float(correction), float(eps),
+                                    float(decay), act, float(act_p), native.dtype_code(x.dtype),
+                                    staging, pads, rank, world, stride, ctr, native.stream_ptr())
+        native.check(rc, "lb_bn_fused_fwd")
+        native.count_launch()
+        ctx.save_for_backward(x_cl, stats, y if act else None)
+        ctx.meta = (sh, bh, eps, correction, count, act, act_p, ndim, peers, owner)
+        return _from_cl(y, ndim)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_cl, stats, y = ctx.saved_tensors
+        sh, bh, eps, correction, count, act, act_p, ndim, peers, owner = ctx.meta
+        dy_cl = _cl_view(dy)
+        if not dy_cl.is_contiguous():
+            dy_cl = dy_cl.contiguous()
+        C = x_cl.shape[-1]
+        rows = x_cl.numel() // C
+        staging, pads, rank, world, stride, ctr = peers
+        scale = sh.master.detach() if sh is not None else None
+        dscale = sh.grad.view(-1) if (sh is not None and sh.grad is not None) else None
+        dbias = bh.grad.view(-1) if (bh is not None and bh.grad is not None) else None
+        dx = torch.empty_like(x_cl)
+        ws = _bn_ws(owner, "bwd", rows, C, x_cl.device)
+        rc = _lib().lb_bn_fused_bwd(x_cl.data_ptr(), dy_cl.data_ptr(), native.ptr(y), stats.data_ptr(),
+                                    native.ptr(scale), dx.data_ptr(), native.ptr(dscale),
+                                    native.ptr(dbias), ws.data_ptr(), rows, C, count, float(correction),
+                                    float(eps), act, float(act_p), native.dtype_code(x_cl.dtype),
+                                    staging, pads, rank, world, stride, ctr, native.stream_ptr())
+        native.check(rc, "lb_bn_fused_bwd")
+        native.count_launch()
+        if dscale is not None:
+            sh.mark_ready()
+        if dbias is not None:
+            bh.mark_ready()
+        return (_from_cl(dx, ndim),) + (None,) * 14
+
+
 class _BatchNorm(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, s_leaf, b_leaf, sh, bh, run_mean, run_var, eps, decay, correction,
@@ -725,6 +832,12 @@ def batch_norm(x, sh, bh, run_mean, run_var, training: bool, eps: float, decay: 
     correction = 1.0 if bessel else 0.0
     if _native_ok(x) and C % 8 == 0:
         if training:
+            peers = _bn_fused_peers(reduce_fn) if (2 * C <= 4096 and not os.environ.get(
+                "LBANN_BN_SEPARATE_KERNELS")) else None
+            if peers is not None:
+                return _BatchNormFused.apply(x, sh.master if sh else None, bh.master if bh else None,
+                                             sh, bh, run_mean, run_var, eps, decay, correction,
+                                             reduce_fn, count_scale, act, float(act_param), peers)
             return _BatchNorm.apply(x, sh.master if sh else None, bh.master if bh else None, sh, bh,
                                     run_mean, run_var, eps, decay, correction, reduce_fn,
                                     count_scale, act, float(act_param))

@@ -34,6 +34,21 @@ def bucket_elements(bucket_bytes: int, element_size: int) -> int:
     return max(bucket_bytes // element_size, 1 << 16) // v * v
 
 
+class _CrossGridSum(torch.autograd.Function):
+    """Sum over the sub-grid peers (ranks holding the same samples on the different grids);
+    the gradient of a sum is the sum of the gradients, over the same peers
+    (include/lbann/layers/transform/cross_grid_sum.hpp:113-148)."""
+
+    @staticmethod
+    def forward(ctx, x, sg):
+        ctx.sg = sg
+        return sg.cross_grid_sum(x)
+
+    @staticmethod
+    def backward(ctx, g):
+        return ctx.sg.cross_grid_sum(g), None
+
+
 class Bucket:
     """A range [start, end) of the gradient arena reduced by one kernel launch."""
 
@@ -74,6 +89,7 @@ class ParallelContext:
         self.comm_stream = torch.cuda.Stream(device=self.device) if self.device.type == "cuda" else None
         self.bucket_bytes = 64 << 20
         self._subgrids = False
+        self.subgrid = None                # SubgridContext when the trainer is split into grids
         self.tp = None
         self.fsdp = None
 
@@ -134,7 +150,8 @@ class ParallelContext:
         """(in-place sum over the statistics group, number of ranks in it) for batch norm:
         0 = all ranks of the trainer, k = groups of k consecutive ranks."""
         if stats_group == 0 or stats_group >= self.world_size:
-            return self.allreduce_sum_inplace, float(self.world_size)
+            from ..ops.nn import GroupSum
+            return GroupSum(self.group, self.allreduce_sum_inplace), float(self.world_size)
         if stats_group <= 1:
             return None, 1.0
         key = ("bn", stats_group)
@@ -285,6 +302,8 @@ class ParallelContext:
         return self._subgrids
 
     def cross_grid_sum(self, layer, x):
+        if self.subgrid is not None:
+            return _CrossGridSum.apply(x, self.subgrid)
         t = x.contiguous()
         self.comm.allreduce(t, getattr(self.comm, "subgrid_peer_group", "trainer"), "sum")
         return t

@@ -335,7 +335,8 @@ class DistconvContext:
                           out_alloc, dx_alloc)
 
     def bn_reduction(self, layer):
-        return self.parallel.allreduce_sum_inplace, float(self.world)
+        from ..ops.nn import GroupSum
+        return GroupSum(self.group, self.parallel.allreduce_sum_inplace), float(self.world)
 
     def sample_loss(self, layer, kind, a, b):
         """Per-sample loss of a spatially partitioned tensor: local partial sums, summed

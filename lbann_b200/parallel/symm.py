@@ -57,6 +57,9 @@ def _lib():
                                              c_ll, c_ll, c_ll, c_ll, c_int, c_void_p, c_void_p]
         lib.lb_alltoall_slabs.restype = c_int
         lib.lb_alltoall_slabs.argtypes = [vpp, vpp, c_int, c_int, c_void_p, c_ll, c_ll, c_void_p, c_void_p]
+        lib.lb_scatter_rows.restype = c_int
+        lib.lb_scatter_rows.argtypes = [vpp, vpp, c_int, c_int, c_void_p, c_void_p, c_void_p, c_ll, c_ll,
+                                        c_void_p, c_void_p]
         lib.lb_group_barrier.restype = c_int
         lib.lb_group_barrier.argtypes = [vpp, vpp, c_int, c_int, c_int, c_void_p, c_void_p]
         _configured = True
@@ -325,6 +328,24 @@ class SymmetricGroup:
         native.check(rc, "lb_alltoall_slabs")
         native.count_launch()
         self.bytes_moved += count * slab_bytes * (self.world - 1) // self.world
+        return True
+
+    def scatter_rows(self, src: Optional[torch.Tensor], dst: SymmetricBuffer, dst_rank: torch.Tensor,
+                     dst_row: torch.Tensor, rows: int, row_bytes: int) -> bool:
+        """One kernel: row j of ``src`` -> row ``dst_row[j]`` of rank ``dst_rank[j]``'s ``dst``
+        (int32 device tensors), closed by a rendezvous of the group.  Every rank of the group
+        calls it, also with ``rows == 0``.  False when rows are not multiples of 16 bytes."""
+        self._guard()
+        rc = _lib().lb_scatter_rows(dst._c_ptrs, self.pad._c_ptrs, self.rank, self.world,
+                                    src.data_ptr() if (src is not None and rows) else None,
+                                    dst_rank.data_ptr() if rows else None,
+                                    dst_row.data_ptr() if rows else None, rows, row_bytes,
+                                    self.ctr_ptr, native.stream_ptr())
+        if rc == -2:
+            return False
+        native.check(rc, "lb_scatter_rows")
+        native.count_launch()
+        self.bytes_moved += rows * row_bytes
         return True
 
     def barrier_device(self, phase: int = 3):

@@ -416,6 +416,56 @@ def ltfb(strategy):
     return {"world": world, "weights": allw, "num_trainers": tr.comm.num_trainers}
 
 
+def subgraph_branches(num_subgrids, steps):
+    """Two branches of a small network on two sub-grids (grid tags 1 and 2), joined by a sum on
+    the whole trainer; a third output goes through a sum across the grids."""
+    o = opts.reset()
+    on_gpu = os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cuda"
+    if not on_gpu:
+        o.set("disable_cuda", True)
+    if num_subgrids > 1:
+        o.set("num_subgrids", num_subgrids)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    x = lbann.Input(data_field="samples")
+    t = lbann.Input(data_field="responses")
+    a = lbann.Sin(x, grid_tag=1, name="branch1_sin")
+    a = lbann.FullyConnected(a, num_neurons=8, has_bias=True, name="branch1_fc")        # inherits grid 1
+    b = lbann.Cos(x, parallel_strategy={"grid_tag": 2}, name="branch2_cos")
+    b = lbann.FullyConnected(b, num_neurons=8, has_bias=True, name="branch2_fc")        # inherits grid 2
+    y = lbann.Sum(a, b, name="join")                                                       # parents differ: grid 0
+    y = lbann.FullyConnected(lbann.Tanh(y), num_neurons=4, has_bias=False, name="head")
+    loss = lbann.MeanSquaredError(y, t, name="mse")
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph([x, t])),
+                        objective_function=lbann.ObjectiveFunction([loss]),
+                        metrics=[lbann.Metric(loss, name="mse")])
+    from test_models_cpu import _reader
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=8, random_seed=13), model=model,
+        data_reader=_reader(32, [16], "normal", response_dims=[4]),
+        optimizer=lbann.SGD(learn_rate=0.05, momentum=0.9))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    tags = {l.name: l.grid_tag for l in m.layers if l.name in ("branch1_sin", "branch1_fc", "branch2_cos",
+                                                                "branch2_fc", "join", "head")}
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    losses = []
+    for _ in range(steps):
+        b_ = dc.next_batch("training")
+        if b_ is None:
+            dc.start_epoch("training")
+            b_ = dc.next_batch("training")
+        m.train_step(b_.tensors, b_.global_size)
+        v = m.last_objective.detach().float().reshape(1).clone()
+        if tr.parallel is not None:
+            tr.comm.allreduce(v, "trainer", "sum")
+        losses.append(float(v))
+    w = {x_.name: float(x_.values.detach().double().norm()) for x_ in m.weights}
+    moved = tr.parallel.subgrid.bytes_moved if (tr.parallel is not None and tr.parallel.subgrid) else 0
+    tr.shutdown()
+    return {"world": world, "losses": losses, "weight_norms": w, "tags": tags, "bytes_moved": moved}
+
+
 def abort_and_restart(ckpt_dir, fail_step, epochs):
     """LeNet on the ranks of one trainer with a shared checkpoint after every epoch.  With
     fail_step >= 0 rank 1 raises between two steps (after step ``fail_step``); the driver's
@@ -474,6 +524,8 @@ if __name__ == "__main__":
         res = data_store(sys.argv[3] == "preload")
     elif what == "mpfc":
         res = model_parallel_fc(int(sys.argv[3]), int(sys.argv[4]), len(sys.argv) > 5 and sys.argv[5] == "sharded")
+    elif what == "subgraph":
+        res = subgraph_branches(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "abort_restart":
         res = abort_and_restart(sys.argv[3], int(sys.argv[4]), int(sys.argv[5]))
     elif what == "cosmoflow":

@@ -8,6 +8,10 @@ from lbann_b200.ops.conv import conv_fwd, pack_filter
 
 pytestmark = pytest.mark.gpu
 
+# the oracle (cuDNN / cuBLAS through torch) must not round its inputs to TF32
+torch.backends.cudnn.allow_tf32 = False
+torch.backends.cuda.matmul.allow_tf32 = False
+
 CASES = [
     # N, C, D, H, W, K, k, pad, stride, dil
     (2, 16, 8, 8, 8, 32, 3, 1, 1, 1),

@@ -109,3 +109,19 @@ def test_partitioned_embedding_with_sparse_sgd_matches_single_rank(tmp_path):
         assert abs(a - b) <= 1e-4 * max(1.0, abs(a)), (single["losses"], two["losses"])
     assert max(abs(a - b) for a, b in zip(single["table"], two["table"])) < 1e-4
     assert single["losses"][-1] < single["losses"][0]
+
+
+def test_subgraph_parallel_branches_on_two_grids(tmp_path):
+    """Sub-graph parallelism on four CPU ranks split into two grids: the two branches run
+    on ranks {0, 1} and {2, 3}, untagged layers inherit their parents' grid, the join runs
+    on all ranks; tensors cross between the grids sample by sample.  Same training
+    trajectory as one process."""
+    single = _run(1, ["subgraph", "1", "4"], str(tmp_path / "a.json"))
+    four = _run(4, ["subgraph", "2", "4"], str(tmp_path / "b.json"), timeout=600)
+    assert four["world"] == 4
+    assert four["tags"] == {"branch1_sin": 1, "branch1_fc": 1, "branch2_cos": 2, "branch2_fc": 2,
+                            "join": 0, "head": 0}
+    for a, b in zip(single["losses"], four["losses"]):
+        assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], four["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - four["weight_norms"][k]) <= 1e-4 * max(1.0, abs(v)), k

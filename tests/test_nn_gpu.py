@@ -121,6 +121,81 @@ def test_batch_norm_matches_reference_formula():
     torch.testing.assert_close(bh.grad, b2.master.grad, rtol=3e-2, atol=2e-1)
 
 
+@pytest.mark.parametrize("fused", [True, False])
+@pytest.mark.parametrize("shape,act", [((4, 32, 6, 6, 6), 0), ((3, 64, 9, 7), 1), ((2, 8, 5, 5, 5), 2)])
+def test_batch_norm_against_fp64_restatement(monkeypatch, fused, shape, act):
+    """Both batch-norm implementations (one cooperative kernel per direction, and the
+    three-kernel sequence) against src/layers/regularizers/batch_normalization.cu:139-196
+    written out independently in fp64 on the CPU: mean, variance with Bessel correction
+    clamped from below by eps, eps added again inside the square root, running statistics,
+    optional fused (leaky) ReLU; gradients from autograd of that formula."""
+    if not fused:
+        monkeypatch.setenv("LBANN_BN_SEPARATE_KERNELS", "1")
+    torch.manual_seed(11)
+    C = shape[1]
+    x = (torch.randn(*shape, device="cuda") * 1.5 + 0.3).half()
+    if len(shape) == 4:
+        x = x.contiguous(memory_format=torch.channels_last)
+    x.requires_grad_(True)
+    sh, bh = _handle(torch.rand(C, device="cuda") + 0.5), _handle(torch.randn(C, device="cuda"))
+    rm, rv = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda")
+    eps, decay, slope = 1e-5, 0.9, 0.2
+    y = nn.batch_norm(x, sh, bh, rm, rv, True, eps, decay, True, act=act, act_param=slope)
+    g = torch.randn(*shape, device="cuda").half()
+    y.backward(g)
+    # ---- fp64 restatement
+    xd = x.detach().double().cpu().requires_grad_(True)
+    sd = sh.master.detach().double().cpu().requires_grad_(True)
+    bd = bh.master.detach().double().cpu().requires_grad_(True)
+    dims = [0] + list(range(2, len(shape)))
+    bshape = [1, C] + [1] * (len(shape) - 2)
+    n = xd.numel() / C
+    mean = xd.mean(dims)
+    sq = (xd * xd).mean(dims)
+    var = (sq - mean * mean) * n / (n - 1.0)
+    var = torch.clamp(var, min=eps)
+    yd = (xd - mean.view(bshape)) * torch.rsqrt(var + eps).view(bshape) * sd.view(bshape) + bd.view(bshape)
+    if act == 1:
+        yd = torch.relu(yd)
+    elif act == 2:
+        yd = torch.nn.functional.leaky_relu(yd, slope)
+    yd.backward(g.double().cpu())
+    torch.testing.assert_close(y.float().cpu(), yd.detach().float(), rtol=1e-2, atol=2e-2)
+    torch.testing.assert_close(rm.cpu(), ((1 - decay) * mean.detach()).float(), rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(rv.cpu(), (decay + (1 - decay) * var.detach()).float(), rtol=1e-3, atol=1e-3)
+    torch.testing.assert_close(x.grad.float().cpu(), xd.grad.float(), rtol=3e-2, atol=3e-2)
+    torch.testing.assert_close(sh.grad.cpu(), sd.grad.float(), rtol=3e-2, atol=2e-1)
+    torch.testing.assert_close(bh.grad.cpu(), bd.grad.float(), rtol=3e-2, atol=2e-1)
+    assert native.consume_status(False) == 0
+
+
+def test_fused_batch_norm_twice_in_a_row_and_changing_batch():
+    """The fused kernels keep their barrier counters and accumulators in a per-layer
+    workspace: a second call, and a call with another number of rows, still agree with the
+    three-kernel sequence."""
+    import os
+    torch.manual_seed(5)
+    C = 64
+    sh, bh = _handle(torch.rand(C, device="cuda") + 0.5), _handle(torch.randn(C, device="cuda"))
+    for n in (8, 8, 5, 8):
+        x = torch.randn(n, C, 14, 14, device="cuda").half().contiguous(memory_format=torch.channels_last)
+        outs = []
+        for sep in ("", "1"):
+            if sep:
+                os.environ["LBANN_BN_SEPARATE_KERNELS"] = "1"
+            else:
+                os.environ.pop("LBANN_BN_SEPARATE_KERNELS", None)
+            rm, rv = torch.zeros(C, device="cuda"), torch.ones(C, device="cuda")
+            xi = x.clone().requires_grad_(True)
+            y = nn.batch_norm(xi, sh, bh, rm, rv, True, 1e-5, 0.9, True, act=1)
+            y.backward(torch.ones_like(y))
+            outs.append((y.detach().float(), xi.grad.float(), rm, rv))
+        os.environ.pop("LBANN_BN_SEPARATE_KERNELS", None)
+        for a, b in zip(*outs):
+            torch.testing.assert_close(a, b, rtol=1e-2, atol=1e-2)
+    assert native.consume_status(False) == 0
+
+
 def test_fused_optimizer_matches_cpu_formulas():
     from lbann_b200.ops.optim import ParameterArena
     torch.manual_seed(4)
