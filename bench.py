@@ -105,9 +105,10 @@ def reference_arm(args):
 
 
 # ------------------------------------------------------------------------ experiments
-def cosmoflow_experiment(lbann, n_gpus, pool):
+def cosmoflow_experiment(lbann, n_gpus, pool, depth_groups=0):
     from lbann_b200.models.cosmoflow import construct_cosmoflow_model, synthetic_reader
-    ps = lbann.get_parallel_strategy_args(depth_groups=n_gpus) if n_gpus > 1 else None
+    depth = depth_groups if depth_groups > 0 else n_gpus      # left-over ranks become sample groups
+    ps = lbann.get_parallel_strategy_args(depth_groups=depth) if (n_gpus > 1 and depth > 1) else None
     model = construct_cosmoflow_model(WIDTH, 4, 4, num_epochs=1, channels=(32, 64, 128, 256, 256),
                                       pool_mode="max", parallel_strategy=ps, conv_bias=False)
     model.amp = lbann.AmpOptions(enabled=True, init_scale=128.0)
@@ -336,7 +337,7 @@ def ours(args):
     pool = 2 * GLOBAL_BATCH
     # the synthetic data set is two mini-batches long; epochs simply repeat, so the collated
     # pinned host batches are built once and every step pays only for its own transfers
-    exp = cosmoflow_experiment(lbann, world, pool)
+    exp = cosmoflow_experiment(lbann, world, pool, args.depth_groups)
     trainer = ExecTrainer(exp)
     model = trainer.build_model(exp.model)
     comm = trainer.comm
@@ -361,8 +362,11 @@ def ours(args):
                             "FC 2048-256-4, MSE, random init",
                    "optimizer": "Adam lr 1e-3 beta1 0.9 beta2 0.99 eps 1e-8, AMP initial loss scale 128",
                    "global_batch": GLOBAL_BATCH, "seq_len": None,
-                   "parallelism": (f"distconv depth x{world}, halo exchange inside the convolution "
-                                   f"kernels, optimizer sharded over the ranks") if world > 1 else "single GPU",
+                   "parallelism": (f"distconv depth x{args.depth_groups or world}"
+                                   + (f" x {world // args.depth_groups} sample groups"
+                                      if args.depth_groups and args.depth_groups < world else "")
+                                   + ", halo exchange inside the convolution kernels, optimizer "
+                                     "sharded over the ranks") if world > 1 else "single GPU",
                    "timing": f"CUDA events, max over ranks, median of {args.repeats} regions of {steps} "
                              "steps; two resident 134 MB fp16 mini-batches alternate so inputs exceed "
                              "the 126 MB L2",
@@ -438,6 +442,9 @@ if __name__ == "__main__":
     ap.add_argument("--workloads", default=os.environ.get("LBANN_BENCH_WORKLOADS", "cosmoflow,resnet50,gpt"),
                     help="comma list; cosmoflow is always the headline value")
     ap.add_argument("--no-torch-arm", action="store_true", help="skip the PyTorch comparison arms")
+    ap.add_argument("--depth-groups", type=int, default=int(os.environ.get("LBANN_BENCH_DEPTH_GROUPS", "0")),
+                    help="CosmoFlow: ranks per depth partition (default: all GPUs); the other ranks "
+                         "multiply the sample groups")
     ap.add_argument("--resnet-batch", type=int, default=256, help="per-GPU mini-batch of the ResNet-50 entry")
     ap.add_argument("--gpt-batch", type=int, default=8, help="sequences per GPU of the GPT entry")
     ap.add_argument("--gpt-layers", type=int, default=24)

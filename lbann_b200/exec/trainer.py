@@ -124,6 +124,7 @@ class ExecTrainer:
         if needs_dc and not opts.current().get_bool("disable_distconv"):
             from ..parallel.distconv import DistconvContext
             self.distconv = DistconvContext(self.comm, self.device, self.parallel)
+            self.distconv.plan(model_pb)
 
     def build_model(self, model_pb=None) -> ExecModel:
         model_pb = model_pb if model_pb is not None else self.proto.model

@@ -85,6 +85,21 @@ class DistconvContext:
                                           # the producing layer wrote there directly)
 
     # ------------------------------------------------------------------ set-up
+    def plan(self, model_pb) -> None:
+        """Depth / sample group sizes from the prototext alone (the data coordinator, which
+        deals samples to the sample groups, is built before the model is)."""
+        depth = 1
+        for l in model_pb.layer:
+            if l.HasField("parallel_strategy"):
+                st = Strategy(l.parallel_strategy, self.world)
+                if st.is_spatial():
+                    depth = max(depth, st.depth)
+        if depth > 1 and self.world % depth == 0:
+            self.depth_groups = depth
+            self.num_sample_groups = self.world // depth
+            self.sample_group_index = self.rank // depth
+            self.depth_rank = self.rank % depth
+
     def prepare_model(self, model):
         self._enabled.clear()
         depth = 1
@@ -109,9 +124,20 @@ class DistconvContext:
         # ranks of one sample group are consecutive: rank = sample_group * depth + depth_rank
         self.sample_group_index = self.rank // depth
         self.depth_rank = self.rank % depth
+        self.depth_pg = "trainer"
         if depth > 1 and self.num_sample_groups > 1:
-            raise NotImplementedError("mixed sample x depth partitions need one symmetric group "
-                                      "per sample group; use depth_groups == ranks per trainer")
+            # sample x depth partition (left-over ranks multiply the sample groups,
+            # src/layers/distconv_adapter.cpp:227-336): the mini-batch is dealt to the sample
+            # groups, every group splits its samples along depth over its own ranks and has
+            # its own symmetric memory; gradients and batch-norm statistics still span the
+            # whole trainer
+            base = self.comm.trainer_rank * self.world
+            for sgi in range(self.num_sample_groups):
+                ranks = [base + sgi * depth + i for i in range(depth)]
+                pg = self.comm.new_group(ranks)
+                if sgi == self.sample_group_index:
+                    self.depth_pg = pg
+            self.group = SymmetricGroup(self.device, pg=self.depth_pg)
         # inputs consumed only by distconv layers are sliced on the host before upload
         tr = getattr(model, "trainer", None)
         if depth > 1 and tr is not None and tr.data_coordinator is not None:
@@ -228,6 +254,15 @@ class DistconvContext:
         return b
 
     # ------------------------------------------------------------------ layer entry points
+    def allreduce_depth_(self, t: torch.Tensor):
+        """In-place sum over the ranks that share this rank's samples (its depth group)."""
+        if self.depth_groups == 1:
+            return
+        if self.group.native and t.dtype == torch.float32 and t.is_contiguous() and t.numel() <= 4096:
+            self.group.allreduce_small_(t, "sum")
+        else:
+            self.comm.allreduce(t, self.depth_pg, "sum")
+
     def step_barrier(self):
         """Stream-ordered rendezvous of the trainer's ranks (needed between two steps that
         have no other collective between them, see csrc/halo_sync.cuh)."""
@@ -336,7 +371,8 @@ class DistconvContext:
 
     def bn_reduction(self, layer):
         from ..ops.nn import GroupSum
-        return GroupSum(self.group, self.parallel.allreduce_sum_inplace), float(self.world)
+        # statistics span all samples and all slabs: the whole trainer, not only the depth group
+        return GroupSum(self.parallel.group, self.parallel.allreduce_sum_inplace), float(self.world)
 
     def sample_loss(self, layer, kind, a, b):
         """Per-sample loss of a spatially partitioned tensor: local partial sums, summed
@@ -494,7 +530,7 @@ class _AllReduceSum(torch.autograd.Function):
     def forward(ctx, t, dc):
         ctx.dc = dc
         out = t.float().contiguous().clone()
-        dc.parallel.allreduce_sum_inplace(out.view(-1))
+        dc.allreduce_depth_(out.view(-1))
         return out
 
     @staticmethod
@@ -535,7 +571,7 @@ class HaloExchange(torch.autograd.Function):
         if r == P - 1:
             xe[:, h + Dl:].fill_(fill)
         edges = torch.stack([xe[:, h:2 * h], xe[:, Dl:Dl + h]]).contiguous()
-        allp = dc.comm.all_gather(edges, "trainer")
+        allp = dc.comm.all_gather(edges, dc.depth_pg)
         if r > 0:
             xe[:, :h].copy_(allp[r - 1][1])
         if r < P - 1:
@@ -552,7 +588,7 @@ class HaloExchange(torch.autograd.Function):
         plane = H * W * C * g_cl.element_size()
         if not dc.group.native:
             edges = torch.stack([g_cl[:, :h], g_cl[:, h + Dl:]]).contiguous()
-            allp = dc.comm.all_gather(edges, "trainer")
+            allp = dc.comm.all_gather(edges, dc.depth_pg)
             dx = g_cl[:, h:h + Dl].clone()
             if r > 0:
                 dx[:, :h] += allp[r - 1][1]
@@ -591,7 +627,7 @@ def _redistribute(x, dc: DistconvContext, to_sample: bool, tag: str):
     es = x_cl.element_size()
     grp = dc.group
     if not grp.native:
-        parts = dc.comm.all_gather(x_cl, "trainer")
+        parts = dc.comm.all_gather(x_cl, dc.depth_pg)
         if to_sample:
             out = torch.cat([p[r::P] for p in parts], dim=1)
         else:

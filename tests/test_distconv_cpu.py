@@ -125,3 +125,15 @@ def test_subgraph_parallel_branches_on_two_grids(tmp_path):
         assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], four["losses"])
     for k, v in single["weight_norms"].items():
         assert abs(v - four["weight_norms"][k]) <= 1e-4 * max(1.0, abs(v)), k
+
+
+def test_sample_x_depth_partition_on_four_ranks(tmp_path):
+    """depth_groups = 2 on four ranks: two sample groups of two depth ranks each (the
+    left-over ranks multiply the sample groups).  Same results as one process."""
+    single = _run(1, ["cosmoflow", "1", "3"], str(tmp_path / "a.json"))
+    dist = _run(4, ["cosmoflow", "2", "3"], str(tmp_path / "b.json"), timeout=600)
+    assert dist["world"] == 4
+    for a, b in zip(single["losses"], dist["losses"]):
+        assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], dist["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - dist["weight_norms"][k]) <= 1e-3 * max(1.0, abs(v)), k
