@@ -380,4 +380,14 @@ bool encode_tmap(CUtensorMap* out, int dtype, int rank, const void* base, const 
 
 int sm_count();
 
+// Scratch memory that the caller lends to the NEXT tensor-core launch of this thread for a
+// split of the reduction (fp32 partial tiles).  plan_splitk takes the offer (it holds for one launch only) and returns the
+// number of splits: 1 when nothing was offered or the problem fills the GPU as it is.
+struct SplitKOffer {
+  float* ws = nullptr;
+  long long ws_bytes = 0;
+};
+SplitKOffer take_splitk_offer();
+int plan_splitk(const SplitKOffer& o, int num_tiles, int k_iters, int bn);
+
 }  // namespace lbhost

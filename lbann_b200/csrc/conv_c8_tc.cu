@@ -320,7 +320,7 @@ conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const C8FwdParams p,
         const int w = tw * 128 + row;
         const long long row_off = n * p.o_sn + d * p.o_sd + h * p.o_sh + (long long)w * p.o_sw;
         const uint32_t taddr = tmem_base + j * BN + (static_cast<uint32_t>(wq * 32) << 16);
-        tc_epilogue_rows<BN>(taddr, w < g.W, row_off, 0, g.Kout, row, e);
+        tc_epilogue_rows<BN>(TmemSrc{taddr}, w < g.W, row_off, 0, g.Kout, row, e);
         tc_fence_before();
         __syncwarp();
         if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[j]));

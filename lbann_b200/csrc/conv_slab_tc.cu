@@ -221,7 +221,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       const int h = q / p.Wp, w = q - h * p.Wp;
       const long long row_off = n * p.o_sn + d * p.o_sd + h * p.o_sh + (long long)w * p.o_sw;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(warp * 32) << 16);
-      tc_epilogue_rows<BN>(taddr, h < g.Ho && w < g.Wo, row_off, 0, g.Kout, row, e);
+      tc_epilogue_rows<BN>(TmemSrc{taddr}, h < g.Ho && w < g.Wo, row_off, 0, g.Kout, row, e);
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[acc]));

@@ -130,7 +130,8 @@ static int largest_tile(int extent, int limit) {
 
 template <int BN>
 static int launch_conv(const CUtensorMap& tmA, const CUtensorMap& tmB,
-                       typename ConvFwdPolicy<BN>::Params p, cudaStream_t stream) {
+                       typename ConvFwdPolicy<BN>::Params p, const lbhost::SplitKOffer& offer,
+                       cudaStream_t stream) {
   using P = ConvFwdPolicy<BN>;
   using G = StageGeom<BN>;
   static bool configured = false;
@@ -141,10 +142,16 @@ static int launch_conv(const CUtensorMap& tmA, const CUtensorMap& tmB,
   }
   p.tiles_col = (p.g.Kout + BN - 1) / BN;
   p.num_tiles = p.tiles_col * p.tiles_w * p.tiles_h * p.tiles_d * p.tiles_nb;
-  const int grid = p.num_tiles < lbhost::sm_count() ? p.num_tiles : lbhost::sm_count();
+  // few bricks, long reduction (the deep layers of a network on a small batch): split it
+  p.epi.k_splits = lbhost::plan_splitk(offer, p.num_tiles, p.k_iters, BN);
+  p.epi.sk_ws = offer.ws;
+  const int items = p.num_tiles * p.epi.k_splits;
+  const int grid = items < lbhost::sm_count() ? items : lbhost::sm_count();
   tc_persistent_kernel<P><<<grid, kTcThreads, G::kSmemBytes, stream>>>(tmA, tmB, p,
                                                                        lbhost::status_word());
-  return (int)cudaGetLastError();
+  int rc = (int)cudaGetLastError();
+  if (rc == 0 && p.epi.k_splits > 1) rc = launch_splitk_reduce<P>(p, stream);
+  return rc;
 }
 
 }  // namespace lb
@@ -178,6 +185,7 @@ int lb_conv_fwd_halo_tc(const void* x, const void* w, void* y, const float* bias
                         void* stream_) {
   using namespace lb;
   cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  const lbhost::SplitKOffer offer = lbhost::take_splitk_offer();   // holds for this call only
   ConvGeom g;
   static_assert(sizeof(ConvGeom) == 21 * sizeof(int), "geom layout");
   memcpy(&g, geom, sizeof(g));
@@ -242,7 +250,7 @@ int lb_conv_fwd_halo_tc(const void* x, const void* w, void* y, const float* bias
     p.epi.out_dtype = out_dtype; p.epi.bias_mode = bias ? 1 : 0; p.epi.act = act;        \
     p.epi.act_param = act_param; p.epi.ldc = ys[3];                                      \
     p.hs = hsync;                                                                        \
-    return launch_conv<BN_>(tmA, tmB, p, stream);                                        \
+    return launch_conv<BN_>(tmA, tmB, p, offer, stream);                                      \
   }
   if (BN == 256) LB_LAUNCH(256)
   if (BN == 128) LB_LAUNCH(128)

@@ -80,7 +80,7 @@ struct GemmCommPolicy {
   __device__ static void epilogue(uint32_t taddr, bool row_ok, long long row_off, int n0,
                                   int n_total, int row_index, const EpiParams& e, const Params& p) {
     if (e.rs_ranks == 0) {
-      tc_epilogue_rows<BN>(taddr, row_ok, row_off, n0, n_total, row_index, e);
+      tc_epilogue_rows<BN>(TmemSrc{taddr}, row_ok, row_off, n0, n_total, row_index, e);
       return;
     }
     __shared__ __align__(16) float stg[4][32][36];   // row pitch 144 B: 16-byte aligned rows

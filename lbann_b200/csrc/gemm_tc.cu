@@ -89,7 +89,8 @@ struct GemmPolicy {
 
 template <int BN>
 static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB,
-                       typename GemmPolicy<BN>::Params p, cudaStream_t stream) {
+                       typename GemmPolicy<BN>::Params p, const lbhost::SplitKOffer& offer,
+                       cudaStream_t stream) {
   using P = GemmPolicy<BN>;
   using G = StageGeom<BN>;
   static bool configured = false;
@@ -102,10 +103,19 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB,
   p.tiles_n = (p.N + BN - 1) / BN;
   p.num_tiles = p.tiles_m * p.tiles_n * p.batch;
   p.k_iters = (p.K + kBK - 1) / kBK;
-  const int grid = p.num_tiles < lbhost::sm_count() ? p.num_tiles : lbhost::sm_count();
+  // a skinny product (few tiles, long K, e.g. a wide fully-connected layer on a small
+  // mini-batch) is cut along K so that all SMs stream the weights
+  if (p.epi.rs_ranks == 0 && p.epi.bcast_ranks == 0) {
+    p.epi.k_splits = lbhost::plan_splitk(offer, p.num_tiles, p.k_iters, BN);
+    p.epi.sk_ws = offer.ws;
+  }
+  const int items = p.num_tiles * p.epi.k_splits;
+  const int grid = items < lbhost::sm_count() ? items : lbhost::sm_count();
   tc_persistent_kernel<P><<<grid, kTcThreads, G::kSmemBytes, stream>>>(tmA, tmB, p,
                                                                        lbhost::status_word());
-  return (int)cudaGetLastError();
+  int rc = (int)cudaGetLastError();
+  if (rc == 0 && p.epi.k_splits > 1) rc = launch_splitk_reduce<P>(p, stream);
+  return rc;
 }
 
 }  // namespace lb
@@ -143,6 +153,7 @@ int lb_gemm_bcast_tc(const void* A, const void* B, void* C, const float* bias, i
                      int out_dtype, float alpha, float beta, int bias_mode, int act, float act_param,
                      int bn_hint, void* const* bcast_ptrs, int bcast_ranks, void* stream_) {
   using namespace lb;
+  const lbhost::SplitKOffer offer = lbhost::take_splitk_offer();   // holds for this call only
   if (bcast_ranks < 0 || bcast_ranks > 8) return -1;
   if (bcast_ranks > 0) {
     if (!bcast_ptrs || out_dtype == kF32 || beta != 0.f || N % 32 || ldc % 8) return -1;
@@ -197,7 +208,7 @@ int lb_gemm_bcast_tc(const void* A, const void* B, void* C, const float* bias, i
     GemmPolicy<BN_>::Params p;                                                \
     p.M = M; p.N = N; p.K = K; p.batch = batch; p.a_mn = a_mn; p.b_mn = b_mn; \
     p.in_dtype = in_dtype; p.strideC = strideC; p.epi = e;                    \
-    return launch_gemm<BN_>(tmA, tmB, p, stream);                             \
+    return launch_gemm<BN_>(tmA, tmB, p, offer, stream);                          \
   }
   if (BN == 256) LB_LAUNCH(256)
   if (BN == 128) LB_LAUNCH(128)

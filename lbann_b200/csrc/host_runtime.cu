@@ -62,6 +62,26 @@ int sm_count() {
   return g_sm_count[dev];
 }
 
+static thread_local SplitKOffer g_splitk_offer;
+
+SplitKOffer take_splitk_offer() {
+  SplitKOffer o = g_splitk_offer;
+  g_splitk_offer = SplitKOffer();
+  return o;
+}
+
+int plan_splitk(const SplitKOffer& o, int num_tiles, int k_iters, int bn) {
+  if (!o.ws || num_tiles <= 0) return 1;
+  const int sms = sm_count();
+  if (num_tiles * 2 > sms || k_iters < 8) return 1;
+  int splits = sms / num_tiles;
+  if (splits > k_iters / 4) splits = k_iters / 4;     // at least four pipeline stages per item
+  if (splits > 32) splits = 32;
+  const long long tile_bytes = 128ll * bn * 4;
+  while (splits > 1 && (long long)num_tiles * splits * tile_bytes > o.ws_bytes) --splits;
+  return splits < 1 ? 1 : splits;
+}
+
 bool encode_tmap(CUtensorMap* out, int dtype, int rank, const void* base, const uint64_t* dims,
                  const uint64_t* strides_bytes, const uint32_t* box, const uint32_t* elem_strides,
                  int swizzle_bytes) {
@@ -124,6 +144,15 @@ int lb_set_wait_budget_ns(unsigned long long ns) {
 void* lb_status_ptr() { return lbhost::status_word(); }
 
 int lb_sm_count() { return lbhost::sm_count(); }
+
+// Lends scratch to the next GEMM / convolution launch of the calling thread (see
+// lbhost::SplitKOffer).  `ws` must be 16-byte aligned.
+int lb_splitk_offer(void* ws, long long ws_bytes) {
+  if ((reinterpret_cast<uintptr_t>(ws) & 15) || ws_bytes < 0) return -1;
+  lbhost::g_splitk_offer.ws = reinterpret_cast<float*>(ws);
+  lbhost::g_splitk_offer.ws_bytes = ws_bytes;
+  return 0;
+}
 
 int lb_abi_version() { return 1; }
 

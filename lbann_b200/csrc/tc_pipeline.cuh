@@ -46,6 +46,14 @@ struct EpiParams {
   // product lands in all replicas without a separate collective.  16-bit outputs, beta == 0.
   int bcast_ranks = 0;
   void* bcast_ptr[8] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};
+  // Split-K (k_splits > 1): the reduction of a tile is cut into k_splits ranges that run as
+  // separate work items, so a problem with few output tiles and a long reduction still fills
+  // the GPU.  Every item stores its fp32 accumulators into sk_ws[tile][split][128][BN] and is
+  // done; tc_splitk_reduce_kernel, launched behind it, sums the partials of every output
+  // element in split order (one warp per output row, lanes along the row), applies the
+  // epilogue and stores.
+  int k_splits = 1;
+  float* sk_ws = nullptr;
 };
 
 template <int BN>
@@ -93,8 +101,20 @@ __device__ __forceinline__ void tc_apply_act32(float (&v)[32], int act, float pr
   }
 }
 
-template <int BN>
-__device__ __forceinline__ void tc_epilogue_rows(uint32_t taddr, bool row_ok, long long row_off,
+// Where the epilogue takes a row's 32-column chunk of accumulators from.
+struct TmemSrc {                 // this warp's lanes of a TMEM accumulator
+  uint32_t taddr;
+  __device__ __forceinline__ void load(int c, float (&v)[32]) const {
+    uint32_t r[32];
+    __syncwarp();  // tcgen05.ld is warp-collective: rejoin lanes that skipped a masked row
+    tmem_ld_32x32(taddr + c, r);
+    tmem_ld_wait();
+#pragma unroll
+    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]);
+  }
+};
+template <int BN, class Src>
+__device__ __forceinline__ void tc_epilogue_rows(const Src& src, bool row_ok, long long row_off,
                                                  int n0, int n_total, int row_index,
                                                  const EpiParams& e) {
   const float alpha = e.alpha, beta = e.beta;
@@ -103,14 +123,11 @@ __device__ __forceinline__ void tc_epilogue_rows(uint32_t taddr, bool row_ok, lo
 #pragma unroll 1
   for (int c = 0; c < BN; c += 32) {
     if (n0 + c >= n_total) break;  // warp-uniform
-    uint32_t r[32];
-    __syncwarp();  // tcgen05.ld is warp-collective: rejoin lanes that skipped a masked row
-    tmem_ld_32x32(taddr + c, r);
-    tmem_ld_wait();
-    if (!row_ok) continue;
     float v[32];
+    src.load(c, v);
+    if (!row_ok) continue;
 #pragma unroll
-    for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(r[j]) * alpha + row_bias;
+    for (int j = 0; j < 32; ++j) v[j] = v[j] * alpha + row_bias;
     const long long off = row_off + n0 + c;
     const int ncol = min(32, n_total - (n0 + c));
     const bool full = ncol == 32;
@@ -201,6 +218,26 @@ __device__ __forceinline__ void tc_epilogue_rows(uint32_t taddr, bool row_ok, lo
   }
 }
 
+// Split-K: this warp's 32 rows of the accumulator go to the workspace as they are.
+template <int BN>
+__device__ __forceinline__ void tc_splitk_store(uint32_t taddr, float* row, bool row_ok, int n0,
+                                                int n_total) {
+#pragma unroll 1
+  for (int c = 0; c < BN; c += 32) {
+    if (n0 + c >= n_total) break;  // warp-uniform
+    uint32_t r[32];
+    __syncwarp();
+    tmem_ld_32x32(taddr + c, r);
+    tmem_ld_wait();
+    if (!row_ok) continue;
+    float4* dst = reinterpret_cast<float4*>(row + c);
+#pragma unroll
+    for (int j = 0; j < 8; ++j)
+      __stcg(dst + j, make_float4(__uint_as_float(r[4 * j]), __uint_as_float(r[4 * j + 1]),
+                                  __uint_as_float(r[4 * j + 2]), __uint_as_float(r[4 * j + 3])));
+  }
+}
+
 // A policy may reserve the LAST `Policy::helpers(p)` CTAs of the grid for work of its own
 // (e.g. copying a peer's operand shard into local memory while the other CTAs multiply):
 // such a CTA runs Policy::helper_cta and leaves before any tile machinery is set up.
@@ -242,13 +279,15 @@ struct TcHalo<Policy, typename Policy::HasHalo> {
 // `epilogue(...)`); the default is tc_epilogue_rows.
 template <class Policy, class = void>
 struct TcEpilogue {
+  static constexpr bool kSplitK = true;     // the default epilogue can finish a split-K tile
   __device__ static void run(uint32_t taddr, bool row_ok, long long row_off, int n0, int n_total,
                              int row_index, const EpiParams& e, const typename Policy::Params&) {
-    tc_epilogue_rows<Policy::BN>(taddr, row_ok, row_off, n0, n_total, row_index, e);
+    tc_epilogue_rows<Policy::BN>(TmemSrc{taddr}, row_ok, row_off, n0, n_total, row_index, e);
   }
 };
 template <class Policy>
 struct TcEpilogue<Policy, typename Policy::HasEpilogue> {
+  static constexpr bool kSplitK = false;
   __device__ static void run(uint32_t taddr, bool row_ok, long long row_off, int n0, int n_total,
                              int row_index, const EpiParams& e, const typename Policy::Params& p) {
     Policy::epilogue(taddr, row_ok, row_off, n0, n_total, row_index, e, p);
@@ -304,8 +343,10 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
   tc_fence_after();
   const uint32_t tmem_base = sh.tmem_base;
 
-  const int num_tiles = p.num_tiles;
+  // Work items: (tile, split) pairs, the splits of a tile next to one another.
   const int k_iters = p.k_iters;
+  const int splits = TcEpilogue<Policy>::kSplitK && p.epi.k_splits > 1 ? p.epi.k_splits : 1;
+  const int num_items = p.num_tiles * splits;
   const HaloSync* hs = TcHalo<Policy>::get(p);
   const bool halo_on = TcHalo<Policy>::kHas && hs->enabled;
 
@@ -326,7 +367,10 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     const uint32_t halo_target =
         halo_on ? (*reinterpret_cast<volatile uint32_t*>(hs->local) + 1u) * (uint32_t)n_workers : 0u;
     int halo_need = halo_on ? ((hs->top_flag ? 1 : 0) | (hs->bot_flag ? 2 : 0)) : 0;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += n_workers) {
+    for (int w = blockIdx.x; w < num_items && ok; w += n_workers) {
+      const int t = w / splits, sp = w - t * splits;
+      const int k_begin = (int)((long long)sp * k_iters / splits);
+      const int k_end = (int)((long long)(sp + 1) * k_iters / splits);
       const typename Policy::Tile tile = Policy::decode(p, t);
       if (halo_need) {
         // first tile of this CTA that reads planes a neighbour sends: wait for them (bounded)
@@ -343,7 +387,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         }
         halo_need &= ~touch;
       }
-      for (int k = 0; k < k_iters; ++k, ++it) {
+      for (int k = k_begin; k < k_end; ++k, ++it) {
         const uint32_t s = it % S;
         const uint32_t ph = (it / S) & 1;
         int good = 1;
@@ -380,7 +424,10 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       uint32_t it = 0;
       uint32_t local_tile = 0;
       bool ok = true;
-      for (int t = blockIdx.x; t < num_tiles && ok; t += n_workers, ++local_tile) {
+      for (int w = blockIdx.x; w < num_items && ok; w += n_workers, ++local_tile) {
+        const int sp = w % splits;
+        const int k_begin = (int)((long long)sp * k_iters / splits);
+        const int k_end = (int)((long long)(sp + 1) * k_iters / splits);
         const uint32_t acc = local_tile & 1;
         const uint32_t acc_ph = (local_tile >> 1) & 1;
         if (!mbar_wait_bounded(smem_u32(&sh.tmem_empty[acc]), acc_ph ^ 1, abort_flag)) {
@@ -390,7 +437,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         }
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * BN;
-        for (int k = 0; k < k_iters; ++k, ++it) {
+        for (int k = k_begin; k < k_end; ++k, ++it) {
           const uint32_t s = it % S;
           const uint32_t ph = (it / S) & 1;
           if (!mbar_wait_bounded(smem_u32(&sh.full[s]), ph, abort_flag)) {
@@ -401,7 +448,7 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
           tc_fence_after();
           const uint32_t sA = smem_base + s * G::kStageBytes;
           const uint32_t sB = sA + G::kABytes;
-          Policy::mma(p, k, sA, sB, tmem_acc, idesc, /*first=*/k == 0);
+          Policy::mma(p, k, sA, sB, tmem_acc, idesc, /*first=*/k == k_begin);
           umma_commit(smem_u32(&sh.empty[s]));  // frees the stage when the MMAs retire
         }
         if (ok) umma_commit(smem_u32(&sh.tmem_full[acc]));
@@ -411,7 +458,8 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     // ------------------------------- epilogue -------------------------------
     uint32_t local_tile = 0;
     bool ok = true;
-    for (int t = blockIdx.x; t < num_tiles && ok; t += n_workers, ++local_tile) {
+    for (int w = blockIdx.x; w < num_items && ok; w += n_workers, ++local_tile) {
+      const int t = w / splits;
       const typename Policy::Tile tile = Policy::decode(p, t);
       const uint32_t acc = local_tile & 1;
       const uint32_t acc_ph = (local_tile >> 1) & 1;
@@ -432,10 +480,17 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
       const int row_index = Policy::row_index(p, tile, row);
       const EpiParams& e = p.epi;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(warp * 32) << 16);
-      TcEpilogue<Policy>::run(taddr, row_ok, row_off, n0, n_total, row_index, e, p);
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[acc]));
+      if (splits == 1) {
+        TcEpilogue<Policy>::run(taddr, row_ok, row_off, n0, n_total, row_index, e, p);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[acc]));
+      } else {
+        tc_splitk_store<BN>(taddr, e.sk_ws + ((long long)w * kBM + row) * BN, row_ok, n0, n_total);
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[acc]));
+      }
     }
   }
 
@@ -446,6 +501,91 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     tc_fence_after();
     tmem_dealloc(tmem_base, G::kTmemCols);
   }
+}
+
+// Second half of a split-K product: one warp per output row of a tile, lanes along the row.
+// Sums the k_splits partials of every element in split order, so the result does not depend
+// on how the items were scheduled, then alpha / bias / beta / activation and the store.
+constexpr int kSplitReduceThreads = 256;
+
+template <class Policy>
+__global__ void __launch_bounds__(kSplitReduceThreads)
+tc_splitk_reduce_kernel(const __grid_constant__ typename Policy::Params p) {
+  constexpr int BN = Policy::BN;
+  const long long wg = (long long)blockIdx.x * (kSplitReduceThreads / 32) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int t = (int)(wg / kBM), row = (int)(wg % kBM);
+  if (t >= p.num_tiles) return;
+  const typename Policy::Tile tile = Policy::decode(p, t);
+  long long row_off = 0;
+  if (!Policy::row_addr(p, tile, row, row_off)) return;
+  const int n0 = Policy::col0(p, tile);
+  const int n_total = Policy::ncols(p);
+  const EpiParams& e = p.epi;
+  const int splits = e.k_splits;
+  const long long split_stride = (long long)kBM * BN;
+  const float* base = e.sk_ws + ((long long)t * splits * kBM + row) * BN;
+  const float row_bias = e.bias_mode == 2 ? e.bias[Policy::row_index(p, tile, row)] : 0.f;
+  for (int c = lane * 4; c < BN; c += 128) {
+    if (n0 + c >= n_total) break;
+    const float* src = base + c;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    int s = 0;
+    for (; s + 4 <= splits; s += 4) {
+      const float4 q0 = __ldcg(reinterpret_cast<const float4*>(src + (s + 0) * split_stride));
+      const float4 q1 = __ldcg(reinterpret_cast<const float4*>(src + (s + 1) * split_stride));
+      const float4 q2 = __ldcg(reinterpret_cast<const float4*>(src + (s + 2) * split_stride));
+      const float4 q3 = __ldcg(reinterpret_cast<const float4*>(src + (s + 3) * split_stride));
+      a.x += q0.x; a.y += q0.y; a.z += q0.z; a.w += q0.w;
+      a.x += q1.x; a.y += q1.y; a.z += q1.z; a.w += q1.w;
+      a.x += q2.x; a.y += q2.y; a.z += q2.z; a.w += q2.w;
+      a.x += q3.x; a.y += q3.y; a.z += q3.z; a.w += q3.w;
+    }
+    for (; s < splits; ++s) {
+      const float4 q = __ldcg(reinterpret_cast<const float4*>(src + s * split_stride));
+      a.x += q.x; a.y += q.y; a.z += q.z; a.w += q.w;
+    }
+    float v[4] = {a.x, a.y, a.z, a.w};
+    const int ncol = min(4, n_total - (n0 + c));
+    const long long off = row_off + n0 + c;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j >= ncol) break;
+      float x = v[j] * e.alpha + row_bias;
+      if (e.bias_mode == 1) x += __ldg(e.bias + n0 + c + j);
+      if (e.beta != 0.f) x += e.beta * load_as_f32(e.C, off + j, e.out_dtype);
+      v[j] = apply_act(x, e.act, e.act_param);
+    }
+    if (e.out_dtype == kF32) {
+      float* dst = reinterpret_cast<float*>(e.C) + off;
+      if (ncol == 4 && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+      } else {
+        for (int j = 0; j < ncol; ++j) dst[j] = v[j];
+      }
+    } else {
+      uint16_t* dst = reinterpret_cast<uint16_t*>(e.C) + off;
+      const uint32_t lo = pack2(v[0], v[1], e.out_dtype), hi = pack2(v[2], v[3], e.out_dtype);
+      if (ncol == 4 && (reinterpret_cast<uintptr_t>(dst) & 7) == 0) {
+        *reinterpret_cast<uint2*>(dst) = make_uint2(lo, hi);
+      } else {
+        for (int j = 0; j < ncol; ++j) {
+          const uint32_t q = j < 2 ? lo : hi;
+          dst[j] = static_cast<uint16_t>(j & 1 ? q >> 16 : q & 0xffffu);
+        }
+      }
+    }
+  }
+}
+
+// Host side: launches the reduction behind a split product.
+template <class Policy>
+static int launch_splitk_reduce(const typename Policy::Params& p, cudaStream_t stream) {
+  const long long rows = (long long)p.num_tiles * kBM;
+  const int per_block = kSplitReduceThreads / 32;
+  const int blocks = (int)((rows + per_block - 1) / per_block);
+  tc_splitk_reduce_kernel<Policy><<<blocks, kSplitReduceThreads, 0, stream>>>(p);
+  return (int)cudaGetLastError();
 }
 
 }  // namespace lb

@@ -659,6 +659,47 @@ class ExecModel:
         if self.parallel is not None and self.arena is not None:
             self.parallel.sync_optimizer_state(self)
 
+    def snapshot_state(self) -> dict:
+        """In-memory copy of everything a training step changes on this rank: weights (fp32
+        values and their 16-bit copies), optimizer state and step counters, the loss-scale
+        schedule.  ``restore_state`` writes it back into the same buffers, so a captured
+        graph stays valid.  The in-memory counterpart of a checkpoint; the reference keeps
+        such copies of a model's weights for tournaments (src/execution_algorithms/ltfb/
+        regularized_evolution.cpp) and for its check_* callbacks."""
+        a = self.arena
+        snap = {}
+        for k in ("master", "state0", "state1", "compute", "step_dev"):
+            v = getattr(a, k, None)
+            if v is not None:
+                snap[k] = v.detach().clone()
+        snap["slot_steps"] = [s.step_count for s in a.slots]
+        snap["slot_extra"] = [{k: v.clone() for k, v in s.extra.items()} for s in a.slots]
+        if self._amp_state is not None:
+            snap["amp_state"] = self._amp_state.clone()
+        snap["amp_host"] = (self._amp_scale_host, getattr(self, "_amp_good_steps", 0))
+        return snap
+
+    def restore_state(self, snap: dict) -> None:
+        a = self.arena
+        for k in ("master", "state0", "state1", "compute", "step_dev"):
+            v = getattr(a, k, None)
+            if k in snap and v is not None:
+                v.copy_(snap[k])
+            elif v is not None and k in ("state0", "state1"):
+                v.zero_()          # allocated after the snapshot was taken
+            elif v is not None and k == "step_dev":
+                v.zero_()
+        for s, n, e in zip(a.slots, snap["slot_steps"], snap["slot_extra"]):
+            s.step_count = n
+            for k in list(s.extra):
+                if k in e:
+                    s.extra[k].copy_(e[k])
+                else:
+                    del s.extra[k]
+        if "amp_state" in snap and self._amp_state is not None:
+            self._amp_state.copy_(snap["amp_state"])
+        self._amp_scale_host, self._amp_good_steps = snap["amp_host"]
+
     def backward_prop(self, local_obj: torch.Tensor):
         for cb in self.callbacks:
             cb.on_backward_prop_begin(self)

@@ -131,6 +131,7 @@ def conv_fwd(x: torch.Tensor, w_taps: torch.Tensor, ksize, *, pad=0, stride=1, d
     ys = (ctypes.c_longlong * 4)(out.stride(0), out.stride(1), out.stride(2), out.stride(3))
     if bias is not None and bias.dtype != torch.float32:
         bias = bias.float()
+    scratch = native.offer_splitk(N * Do * Ho * Wo, Kout, x.device) if C * kd * kh * kw >= 512 else None
     rc = _lib().lb_conv_fwd_halo_tc(x.data_ptr(), w_taps.data_ptr(), out.data_ptr(), native.ptr(bias),
                                     geom, xs, ys, native.dtype_code(x.dtype),
                                     native.dtype_code(out.dtype), float(alpha), float(beta), int(act),
@@ -139,6 +140,7 @@ def conv_fwd(x: torch.Tensor, w_taps: torch.Tensor, ksize, *, pad=0, stride=1, d
                                     native.stream_ptr())
     native.check(rc, "lb_conv_fwd_halo_tc")
     native.count_launch()
+    del scratch
     return out
 
 

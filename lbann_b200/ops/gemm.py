@@ -101,6 +101,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         raise ValueError("gemm: output must have unit stride in its last dimension")
     if bias is not None and bias.dtype != torch.float32:
         bias = bias.float()
+    scratch = native.offer_splitk(M * nb, N, a.device) if K >= 512 else None
     rc = _lib().lb_gemm_tc(
         a.data_ptr(), b.data_ptr(), out.data_ptr(), native.ptr(bias), M, N, K, nb,
         a.stride(-2), b.stride(-2), out.stride(-2),
@@ -112,4 +113,5 @@ def gemm(a: torch.Tensor, b: torch.Tensor, *, trans_a: bool = False, trans_b: bo
         int(bn_hint), native.stream_ptr())
     native.check(rc, "lb_gemm_tc")
     native.count_launch()
+    del scratch         # enqueued: the allocator may hand the workspace to later work of this stream
     return out

@@ -148,3 +148,32 @@ def count_launch(n: int = 1) -> None:
 
 def launches() -> int:
     return _launch_count
+
+
+# --------------------------------------------------------------------------- split-K scratch
+_splitk_sms: dict = {}      # device index -> SM count
+splitk_offers = 0           # how many launches were lent scratch (tests read it)
+
+
+def offer_splitk(rows: int, cols: int, device) -> "torch.Tensor | None":
+    """Lends scratch memory to the GEMM / convolution launch that the calling thread makes
+    NEXT, so that a product with few output tiles and a long reduction can be cut along the
+    reduction (``csrc/tc_pipeline.cuh``).  Offered only where that can pay: an output of at
+    most half a wave of 128 x 256 tiles.  Returns the workspace tensor; the caller holds it
+    until the launch is enqueued."""
+    global splitk_offers
+    if rows * cols > 74 * 128 * 256 or os.environ.get("LBANN_DISABLE_SPLITK", "") not in ("", "0"):
+        return None
+    device = torch.device(device)
+    idx = device.index if device.index is not None else torch.cuda.current_device()
+    lib = cuda_lib()
+    sms = _splitk_sms.get(idx)
+    if sms is None:
+        lib.lb_splitk_offer.restype = c_int
+        lib.lb_splitk_offer.argtypes = [c_void_p, ctypes.c_longlong]
+        sms = _splitk_sms[idx] = int(lib.lb_sm_count())
+    bn = 256 if cols > 128 else 128
+    ws = torch.empty(sms * 128 * bn, dtype=torch.float32, device=device)
+    check(lib.lb_splitk_offer(ws.data_ptr(), ws.numel() * 4), "lb_splitk_offer")
+    splitk_offers += 1
+    return ws

@@ -100,3 +100,30 @@ def test_conv_wgrad(case):
     assert native.consume_status() == 0
     ref = prev + 0.5 * w.grad
     torch.testing.assert_close(got, ref, rtol=2e-3, atol=2e-2 * (N * D * H * W) ** 0.5 / 8)
+
+
+@pytest.mark.parametrize("case", [(2, 256, 8, 8, 8, 256), (1, 128, 4, 16, 16, 200), (3, 64, 1, 12, 12, 96)])
+def test_conv_deep_layers_split_the_reduction(case, monkeypatch):
+    """The deep layers of a network on a small batch: a handful of output bricks, thousands of
+    reduction steps.  The split result equals the unsplit one up to fp32 summation order."""
+    N, C, D, H, W, K = case
+    torch.manual_seed(4)
+    ks = (1 if D == 1 else 3, 3, 3)
+    pd = (0 if D == 1 else 1, 1, 1)
+    x = torch.randn(N, C, D, H, W, device="cuda").half()
+    w = (torch.randn(K, C, *ks, device="cuda") / (C * 27) ** 0.5).half()
+    bias = torch.randn(K, device="cuda")
+    xl = x.permute(0, 2, 3, 4, 1).contiguous()
+    wp = pack_filter(w, torch.float16)
+    before = native.splitk_offers
+    ys = [conv_fwd(xl, wp, ks, pad=pd, bias=bias, act=native.ACT_LEAKY, act_param=0.01,
+                   out_dtype=torch.float32) for _ in range(2)]
+    assert native.consume_status() == 0
+    assert native.splitk_offers == before + 2
+    assert torch.equal(ys[0], ys[1])
+    ref = F.leaky_relu(F.conv3d(x.float(), w.float(), bias, 1, pd), 0.01).permute(0, 2, 3, 4, 1)
+    torch.testing.assert_close(ys[0], ref, rtol=2e-3, atol=2e-2)
+    monkeypatch.setenv("LBANN_DISABLE_SPLITK", "1")
+    plain = conv_fwd(xl, wp, ks, pad=pd, bias=bias, act=native.ACT_LEAKY, act_param=0.01,
+                     out_dtype=torch.float32)
+    torch.testing.assert_close(ys[0], plain, rtol=1e-4, atol=1e-4)

@@ -63,3 +63,33 @@ def test_gemm_unaligned_operands_are_repacked():
     out = gemm(a, w, trans_b=True, out_dtype=torch.float32)
     assert native.consume_status() == 0
     torch.testing.assert_close(out, a.float() @ w.float().t(), rtol=2e-3, atol=3e-2)
+
+
+@pytest.mark.parametrize("M,N,K,dtype", [(8, 2048, 16384, torch.float16), (130, 300, 4096, torch.bfloat16),
+                                         (2, 256, 2048, torch.float16)])
+def test_gemm_skinny_products_split_the_reduction(M, N, K, dtype, monkeypatch):
+    """Few output tiles and a long K: the reduction is cut into ranges that run on different
+    SMs and are summed by the warp that arrives last.  Twice in a row (the arrival counters
+    must be back at zero), with bias, beta and activation applied once, against fp32 and
+    against the same product without the split."""
+    torch.manual_seed(5)
+    a = (torch.randn(M, K, device="cuda") / K ** 0.25).to(dtype)
+    w = (torch.randn(N, K, device="cuda") / K ** 0.25).to(dtype)
+    bias = torch.randn(N, device="cuda")
+    prev = torch.randn(M, N, device="cuda").to(dtype)
+    ref = torch.relu(a.float() @ w.float().t() + bias + 0.5 * prev.float())
+    before = native.splitk_offers
+    outs = []
+    for _ in range(2):
+        out = prev.clone()
+        gemm(a, w, trans_b=True, out=out, beta=0.5, bias=bias, act=native.ACT_RELU)
+        assert native.consume_status() == 0
+        outs.append(out)
+    assert native.splitk_offers == before + 2
+    assert torch.equal(outs[0], outs[1])          # summed in split order: bitwise repeatable
+    torch.testing.assert_close(outs[0].float(), ref, rtol=1e-2, atol=3e-2)
+    monkeypatch.setenv("LBANN_DISABLE_SPLITK", "1")
+    plain = prev.clone()
+    gemm(a, w, trans_b=True, out=plain, beta=0.5, bias=bias, act=native.ACT_RELU)
+    assert native.splitk_offers == before + 2
+    torch.testing.assert_close(outs[0].float(), plain.float(), rtol=1e-2, atol=2e-2)

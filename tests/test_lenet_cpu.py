@@ -92,3 +92,34 @@ def test_cuda_graph_option_is_ignored_without_a_gpu():
     opts.reset()
     assert m._graph_mode is False and not m._graphs
     assert last < first
+
+
+def test_snapshot_and_restore_replay_the_same_steps():
+    """``snapshot_state`` / ``restore_state``: weights, Adam moments and step counters go back
+    to where they were, so the same mini-batches give the same losses again."""
+    from lbann_b200.exec.trainer import ExecTrainer
+    from lbann_b200.utils import options as opts
+    from test_models_cpu import _reader
+    o = opts.reset()
+    o.set("disable_cuda", True)
+    x = lbann.Input(data_field="samples")
+    y = lbann.FullyConnected(lbann.Relu(lbann.FullyConnected(x, num_neurons=7)), num_neurons=3)
+    loss = lbann.MeanSquaredError(y, lbann.Input(data_field="responses"))
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph([x])),
+                        objective_function=lbann.ObjectiveFunction([loss]))
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=4), model=model,
+        data_reader=_reader(8, [5], "normal", response_dims=[3]), optimizer=lbann.Adam(learn_rate=0.05))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    b = dc.next_batch("training")
+    snap = m.snapshot_state()
+    first = [float(m.train_step(b.tensors, b.global_size)) for _ in range(4)]
+    m.restore_state(snap)
+    again = [float(m.train_step(b.tensors, b.global_size)) for _ in range(4)]
+    tr.shutdown()
+    opts.reset()
+    assert first[-1] < first[0]
+    assert again == first

@@ -126,3 +126,48 @@ def test_ltfb_two_trainers_on_gpus(tmp_path, strategy):
     a, b = res["weights"]
     for k in a:
         assert abs(a[k] - b[k]) <= 1e-4 * max(1.0, abs(a[k])), (strategy, k, a, b)
+
+
+needs4 = pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
+
+
+def _same_run(single, dist, loss_tol=1e-2, w_tol=5e-3):
+    for a, b in zip(single["losses"], dist["losses"]):
+        assert abs(a - b) <= loss_tol * max(1.0, abs(a)), (single["losses"], dist["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - dist["weight_norms"][k]) <= w_tol * max(1.0, abs(v)), k
+
+
+@needs4
+@pytest.mark.parametrize("width,channels,graph", [("64", "16,32,32", ""),
+                                                  ("128", "16,32,32,64,64", "graph")])
+def test_distconv_four_gpus_matches_one(tmp_path, width, channels, graph):
+    """Depth split over four GPUs: the two middle ranks exchange halo planes with a
+    neighbour on either side.  Same losses and weights as one GPU."""
+    steps = "8" if graph else "5"
+    tail = [width, channels] + ([graph] if graph else [])
+    single = _run(1, ["cosmoflow", "1", steps, "fp16"] + tail, str(tmp_path / "a.json"), STABLE)
+    dist = _run(4, ["cosmoflow", "4", steps, "fp16"] + tail, str(tmp_path / "b.json"), STABLE)
+    assert dist["status"] == 0 and dist["world"] == 4
+    assert dist["interior_copies"] == 0, dist
+    _same_run(single, dist)
+
+
+@needs4
+def test_sample_x_depth_partition_on_four_gpus(tmp_path):
+    """Two sample groups of two depth ranks each, every group with its own symmetric
+    memory for the halo exchange; the weight gradients are summed over all four."""
+    tail = ["64", "16,32,32"]
+    single = _run(1, ["cosmoflow", "1", "5", "fp16"] + tail, str(tmp_path / "a.json"), STABLE)
+    dist = _run(4, ["cosmoflow", "2", "5", "fp16"] + tail, str(tmp_path / "b.json"), STABLE)
+    assert dist["status"] == 0 and dist["world"] == 4
+    _same_run(single, dist)
+
+
+@needs4
+def test_subgraph_parallel_branches_on_four_gpus(tmp_path):
+    """Two sub-grids of two GPUs; tensors change grids through the row-scatter kernel."""
+    single = _run(1, ["subgraph", "1", "4"], str(tmp_path / "a.json"), ENV)
+    four = _run(4, ["subgraph", "2", "4"], str(tmp_path / "b.json"), ENV)
+    assert four["world"] == 4
+    _same_run(single, four, 2e-2, 1e-2)
