@@ -813,7 +813,7 @@ class CheckSmall(ExecCallback):
             self._chk(w.values, f"weights '{w.name}'")
 
 
-@register("check_init")
+@register("check_init", "init")
 class CheckInit(ExecCallback):
     """All ranks of a trainer start from identical weights (src/callbacks/check_init.cpp)."""
 

@@ -90,3 +90,72 @@ def test_torch_module_lowering_matches_pytorch():
     outs = lt.compile(net, input=x)
     got = lbann.evaluate(outs[0], x.numpy())
     torch.testing.assert_close(torch.from_numpy(got), net(x).detach(), rtol=1e-4, atol=1e-5)
+
+
+def test_model_surgery_keeps_weights_and_changes_the_graph():
+    """insert / replace / remove / swap on a set-up model: the graph changes, weights whose
+    name and shape survive keep values and optimizer state, and training carries on."""
+    import torch
+    import lbann_b200 as lbann
+    from lbann_b200.exec import surgery
+    from lbann_b200.exec.trainer import ExecTrainer
+    from lbann_b200.proto import lbann_pb2 as pb
+    from lbann_b200.utils import options as opts
+    from test_models_cpu import _reader
+    o = opts.reset()
+    o.set("disable_cuda", True)
+    x = lbann.Input(data_field="samples")
+    h = lbann.FullyConnected(x, num_neurons=6, name="fc1", weights=[lbann.Weights(name="w1"), lbann.Weights(name="b1")],
+                             has_bias=True)
+    a = lbann.Relu(h, name="act1")
+    y = lbann.FullyConnected(a, num_neurons=3, name="fc2", weights=[lbann.Weights(name="w2")])
+    loss = lbann.MeanSquaredError(y, lbann.Input(data_field="responses"), name="mse")
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph([x])),
+                        objective_function=lbann.ObjectiveFunction([loss]))
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=4), model=model,
+        data_reader=_reader(8, [5], "normal", response_dims=[3]), optimizer=lbann.Adam(learn_rate=0.01))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    b = dc.next_batch("training")
+    for _ in range(3):
+        m.train_step(b.tensors, b.global_size)
+    w1 = m.weights_by_name["w1"].values.detach().clone()
+    mom = {k: v.clone() for k, v in m.weights_by_name["w1"].optimizer_state().items()}
+
+    # replace the activation
+    new = pb.Layer(name="act1")
+    new.leaky_relu.negative_slope = 0.2
+    m2 = surgery.replace_layer(tr, m, "act1", new)
+    assert m2.layer("act1").type == "leaky_relu" and m2 in tr.models and m not in tr.models
+    assert torch.equal(m2.weights_by_name["w1"].values, w1)
+    for k, v in m2.weights_by_name["w1"].optimizer_state().items():
+        assert torch.equal(v, mom[k]), k
+    # insert a layer behind it, then take it out again
+    ins = pb.Layer(name="drop_in")
+    ins.identity.SetInParent()
+    m3 = surgery.insert_layer(tr, m2, ins, after="act1")
+    assert [p.name for p in m3.layer("fc2").parents] == ["drop_in"]
+    assert [p.name for p in m3.layer("drop_in").parents] == ["act1"]
+    m4 = surgery.remove_layer(tr, m3, "drop_in")
+    assert [p.name for p in m4.layer("fc2").parents] == ["act1"]
+    assert "drop_in" not in m4.layers_by_name
+    assert torch.equal(m4.weights_by_name["w2"].values, m2.weights_by_name["w2"].values)
+    before = float(m4.train_step(b.tensors, b.global_size))
+    for _ in range(5):
+        after = float(m4.train_step(b.tensors, b.global_size))
+    assert after < before
+    # swap two neighbouring activations: fc1 -> act1 -> act2 -> fc2 becomes fc1 -> act2 -> act1 -> fc2
+    t = pb.Layer(name="act2")
+    t.elu.alpha = 1.0
+    m5 = surgery.insert_layer(tr, m4, t, after="act1")
+    m6 = surgery.swap_layers(tr, m5, "act1", "act2")
+    assert [p.name for p in m6.layer("act2").parents] == ["fc1"]
+    assert [p.name for p in m6.layer("act1").parents] == ["act2"]
+    assert [p.name for p in m6.layer("fc2").parents] == ["act1"]
+    assert len(tr.models) == 1
+    float(m6.train_step(b.tensors, b.global_size))
+    tr.shutdown()
+    opts.reset()
