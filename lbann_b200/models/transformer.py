@@ -67,7 +67,7 @@ class TransformerEncoderLayer(Module):
 
     def __init__(self, embed_dim=512, num_heads=8, feedforward_dim=2048, dropout=0.1,
                  attn_dropout=0.0, pre_layernorm=False, activation=L.Relu, name=None,
-                 attention_bias=None, positional_encoding=None):
+                 attention_bias=None, positional_encoding=None, branches=0):
         super().__init__()
         TransformerEncoderLayer.global_count += 1
         self.name = name or f"transformerencoderlayer{TransformerEncoderLayer.global_count}"
@@ -75,6 +75,7 @@ class TransformerEncoderLayer(Module):
         self.attention = MultiheadAttention(embed_dim, num_heads, self_attention=True,
                                             dropout=attn_dropout, bias=attention_bias,
                                             positional_encoding=positional_encoding,
+                                            subgraph_branches=branches,
                                             name=f"{self.name}_attention")
         self.norm1 = LayerNorm(embed_dim, name=f"{self.name}_norm1")
         self.norm2 = LayerNorm(embed_dim, name=f"{self.name}_norm2")
@@ -103,7 +104,7 @@ class TransformerDecoderLayer(Module):
 
     def __init__(self, embed_dim=512, num_heads=8, feedforward_dim=2048, dropout=0.1,
                  attn_dropout=0.0, pre_layernorm=False, activation=L.Relu, name=None,
-                 attention_bias=None, positional_encoding=None):
+                 attention_bias=None, positional_encoding=None, branches=0):
         super().__init__()
         TransformerDecoderLayer.global_count += 1
         self.name = name or f"transformerdecoderlayer{TransformerDecoderLayer.global_count}"
@@ -111,9 +112,11 @@ class TransformerDecoderLayer(Module):
         self.attention1 = MultiheadAttention(embed_dim, num_heads, self_attention=True,
                                              dropout=attn_dropout, bias=attention_bias,
                                              positional_encoding=positional_encoding,
+                                             subgraph_branches=branches,
                                              name=f"{self.name}_attention1")
         self.attention2 = MultiheadAttention(embed_dim, num_heads, dropout=attn_dropout,
                                              positional_encoding=positional_encoding,
+                                             subgraph_branches=branches,
                                              name=f"{self.name}_attention2")
         self.norm1 = LayerNorm(embed_dim, name=f"{self.name}_norm1")
         self.norm2 = LayerNorm(embed_dim, name=f"{self.name}_norm2")
@@ -148,13 +151,15 @@ def causal_mask(seq_len: int, name: str = "causal_mask"):
 
 
 class Transformer(Module):
-    """Encoder-decoder stack; ``forward(source, target)`` returns the decoder output."""
+    """Encoder-decoder stack; ``forward(source, target)`` returns the decoder output.
+    ``branches`` = B > 0: the attention heads of every layer run on B sub-grids of the trainer
+    (sub-graph parallelism; run with ``--num-subgrids B``)."""
 
     global_count = 0
 
     def __init__(self, hidden_size=512, num_heads=8, num_encoder_layers=6, num_decoder_layers=6,
                  feedforward_size=None, dropout=0.1, attn_dropout=0.0, pre_layernorm=False,
-                 activation=L.Relu, name=None, positional_encoding=None):
+                 activation=L.Relu, name=None, positional_encoding=None, branches=0):
         super().__init__()
         Transformer.global_count += 1
         self.name = name or f"transformer{Transformer.global_count}"
@@ -162,7 +167,7 @@ class Transformer(Module):
         ff = feedforward_size or 4 * hidden_size
         kw = dict(embed_dim=hidden_size, num_heads=num_heads, feedforward_dim=ff, dropout=dropout,
                   attn_dropout=attn_dropout, pre_layernorm=pre_layernorm, activation=activation,
-                  positional_encoding=positional_encoding)
+                  positional_encoding=positional_encoding, branches=branches)
         self.encoder = [TransformerEncoderLayer(name=f"{self.name}_encoder{i}", **kw)
                         for i in range(num_encoder_layers)]
         self.decoder = [TransformerDecoderLayer(name=f"{self.name}_decoder{i}", **kw)

@@ -101,8 +101,13 @@ class MultiheadAttention(Module):
                                            output_channel_dims=[self.embed_dim], name=name)
 
     def _separate(self, q, k, v, mask, name):
-        """One small attention per head (the reference's non-batched / sub-graph mode)."""
+        """One small attention per head (the reference's non-batched mode).  With
+        ``subgraph_branches`` = B > 0 the heads are dealt in blocks onto the sub-grids 1..B
+        (grid tags; python/lbann/modules/attention_allsubgraph.py does the same with its
+        branch tags): each sub-grid computes its heads for the whole mini-batch, the slices
+        and the concatenation run on the whole trainer and move the tensors between grids."""
         H, D = self.num_heads, self.head_dim
+        B = self.subgraph_branches
         pts = [i * D for i in range(H + 1)]
         qs = L.Slice(q, axis=1, slice_points=pts, name=f"{name}_queries_slice")
         ks = L.Slice(k, axis=1, slice_points=pts, name=f"{name}_keys_slice")
@@ -110,16 +115,17 @@ class MultiheadAttention(Module):
         outs = []
         for h in range(H):
             hn = f"{name}_head{h}"
-            qh, kh, vh = (L.Identity(s, name=f"{hn}_{t}") for s, t in ((qs, "q"), (ks, "k"), (vs, "v")))
-            y = L.MatMul(qh, kh, transpose_b=True, name=f"{hn}_matmul")
-            y = L.Scale(y, constant=1.0 / math.sqrt(D), name=f"{hn}_scale")
+            kw = {"grid_tag": 1 + h // (H // B)} if B > 0 else {}
+            qh, kh, vh = (L.Identity(s, name=f"{hn}_{t}", **kw) for s, t in ((qs, "q"), (ks, "k"), (vs, "v")))
+            y = L.MatMul(qh, kh, transpose_b=True, name=f"{hn}_matmul", **kw)
+            y = L.Scale(y, constant=1.0 / math.sqrt(D), name=f"{hn}_scale", **kw)
             if mask is not None:       # a [seq_q, seq_k] mask shared by the heads in this mode
-                y = L.Add(y, mask, name=f"{hn}_mask")
-            y = L.ChannelwiseSoftmax(y, name=f"{hn}_softmax")
+                y = L.Add(y, mask, name=f"{hn}_mask", **kw)
+            y = L.ChannelwiseSoftmax(y, name=f"{hn}_softmax", **kw)
             if self.dropout > 0:
-                y = L.Dropout(y, keep_prob=1 - self.dropout, name=f"{hn}_drop")
-            outs.append(L.MatMul(y, vh, name=f"{hn}_context"))
-        return L.Concatenation(outs, axis=1, name=f"{name}_heads_concat")
+                y = L.Dropout(y, keep_prob=1 - self.dropout, name=f"{hn}_drop", **kw)
+            outs.append(L.MatMul(y, vh, name=f"{hn}_context", **kw))
+        return L.Concatenation(outs, axis=1, name=f"{name}_heads_concat", **({"grid_tag": 0} if B > 0 else {}))
 
 
 class SequenceEncoding:

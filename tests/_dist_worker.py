@@ -416,6 +416,55 @@ def ltfb(strategy):
     return {"world": world, "weights": allw, "num_trainers": tr.comm.num_trainers}
 
 
+def subgraph_transformer(num_subgrids, steps):
+    """Encoder whose attention heads sit on two sub-grids (two heads each)."""
+    from lbann_b200.models.subgraph import TransformerAllSubgraph
+    o = opts.reset()
+    on_gpu = os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cuda"
+    if not on_gpu:
+        o.set("disable_cuda", True)
+    if num_subgrids > 1:
+        o.set("num_subgrids", num_subgrids)
+    S, E = 6, 16
+    x = lbann.Input(data_field="samples")
+    t = lbann.Input(data_field="responses")
+    seq = lbann.Reshape(x, dims=[S, E])
+    enc = TransformerAllSubgraph(2, hidden_size=E, num_heads=4, num_encoder_layers=2, num_decoder_layers=0,
+                                 feedforward_size=32, dropout=0.0, name="sgt")
+    y = enc(seq, None)
+    y = lbann.FullyConnected(lbann.Reshape(y, dims=[S * E]), num_neurons=4, has_bias=False, name="head")
+    loss = lbann.MeanSquaredError(y, t, name="mse")
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph([x, t])),
+                        objective_function=lbann.ObjectiveFunction([loss]))
+    from test_models_cpu import _reader
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=8, random_seed=17), model=model,
+        data_reader=_reader(16, [S * E], "normal", response_dims=[4]),
+        optimizer=lbann.SGD(learn_rate=0.05, momentum=0.9))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    tags = sorted({l.grid_tag for l in m.layers})
+    head_tags = {l.name: l.grid_tag for l in m.layers if l.name.endswith("_matmul") and "encoder0" in l.name}
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    losses = []
+    for _ in range(steps):
+        b_ = dc.next_batch("training")
+        if b_ is None:
+            dc.start_epoch("training")
+            b_ = dc.next_batch("training")
+        m.train_step(b_.tensors, b_.global_size)
+        v = m.last_objective.detach().float().reshape(1).clone()
+        if tr.parallel is not None:
+            tr.comm.allreduce(v, "trainer", "sum")
+        losses.append(float(v))
+    w = {x_.name: float(x_.values.detach().double().norm()) for x_ in m.weights}
+    res = {"losses": losses, "weight_norms": w, "world": int(os.environ.get("WORLD_SIZE", "1")),
+           "tags": tags, "head_tags": head_tags}
+    tr.shutdown()
+    return res
+
+
 def subgraph_branches(num_subgrids, steps):
     """Two branches of a small network on two sub-grids (grid tags 1 and 2), joined by a sum on
     the whole trainer; a third output goes through a sum across the grids."""
@@ -526,6 +575,8 @@ if __name__ == "__main__":
         res = model_parallel_fc(int(sys.argv[3]), int(sys.argv[4]), len(sys.argv) > 5 and sys.argv[5] == "sharded")
     elif what == "subgraph":
         res = subgraph_branches(int(sys.argv[3]), int(sys.argv[4]))
+    elif what == "subgraph_transformer":
+        res = subgraph_transformer(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "abort_restart":
         res = abort_and_restart(sys.argv[3], int(sys.argv[4]), int(sys.argv[5]))
     elif what == "cosmoflow":

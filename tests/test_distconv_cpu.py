@@ -127,6 +127,19 @@ def test_subgraph_parallel_branches_on_two_grids(tmp_path):
         assert abs(v - four["weight_norms"][k]) <= 1e-4 * max(1.0, abs(v)), k
 
 
+def test_subgraph_transformer_heads_on_two_grids(tmp_path):
+    """Attention heads of an encoder dealt onto two sub-grids of two ranks each: same
+    trajectory as one process running all heads."""
+    single = _run(1, ["subgraph_transformer", "1", "3"], str(tmp_path / "a.json"))
+    four = _run(4, ["subgraph_transformer", "2", "3"], str(tmp_path / "b.json"), timeout=900)
+    assert four["world"] == 4 and four["tags"] == [0, 1, 2]
+    assert sorted(set(four["head_tags"].values())) == [1, 2] and len(four["head_tags"]) == 4
+    for a, b in zip(single["losses"], four["losses"]):
+        assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], four["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - four["weight_norms"][k]) <= 1e-4 * max(1.0, abs(v)), k
+
+
 def test_sample_x_depth_partition_on_four_ranks(tmp_path):
     """depth_groups = 2 on four ranks: two sample groups of two depth ranks each (the
     left-over ranks multiply the sample groups).  Same results as one process."""

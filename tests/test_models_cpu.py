@@ -178,3 +178,169 @@ def test_transformer_parallelism_switches_mark_the_graph():
     layouts = {l.name: l.data_layout for l in msg.layer}
     assert layouts[head.name] == "model_parallel"
     assert any(l.grid_tag.value == 2 for l in msg.layer)
+
+
+def _graph_forward(build, n_nodes, feat, n_edges, extra=0, seed=0):
+    """Builds a model whose input sample is [node features | source | target | extra],
+    runs one forward pass and returns (model, input tensors, activation getter)."""
+    o = opts.reset()
+    o.set("disable_cuda", True)
+    width = n_nodes * feat + 2 * n_edges + extra
+    x = lbann.Input(data_field="samples")
+    parts = lbann.Slice(x, axis=0, slice_points=[0, n_nodes * feat, n_nodes * feat + n_edges,
+                                                 n_nodes * feat + 2 * n_edges] + ([width] if extra else []))
+    nodes = lbann.Reshape(lbann.Identity(parts), dims=[n_nodes, feat])
+    src = lbann.Identity(parts)
+    dst = lbann.Identity(parts)
+    rest = lbann.Identity(parts) if extra else None
+    out = build(nodes, src, dst, rest)
+    out = lbann.Identity(out, name="graph_out")
+    loss = lbann.L2Norm2(lbann.Reshape(out, dims=[-1]))
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph([x])),
+                        objective_function=lbann.ObjectiveFunction([loss]))
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=2, random_seed=seed + 1), model=model,
+        data_reader=_reader(2, [width], "normal"), optimizer=lbann.SGD(learn_rate=0.01))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    g = torch.Generator().manual_seed(seed)
+    feats = torch.randn(2, n_nodes, feat, generator=g)
+    s = torch.randint(0, n_nodes, (2, n_edges), generator=g).float()
+    t = torch.randint(0, n_nodes, (2, n_edges), generator=g).float()
+    s[:, -1] = -1                   # a padding edge
+    t[:, -1] = -1
+    ex = torch.randn(2, extra, generator=g) if extra else torch.zeros(2, 0)
+    sample = torch.cat([feats.reshape(2, -1), s, t, ex], 1)
+    m.forward_prop({"samples": sample}, "validation")
+    return tr, m, feats, s.long(), t.long(), ex
+
+
+def _propagate(msg, s, t, n_nodes):
+    """out[b, s[e]] += msg[b, t[e]] for edges with valid indices."""
+    out = torch.zeros(msg.shape[0], n_nodes, msg.shape[2])
+    for b in range(msg.shape[0]):
+        for e in range(s.shape[1]):
+            if s[b, e] >= 0 and t[b, e] >= 0:
+                out[b, s[b, e]] += msg[b, t[b, e]]
+    return out
+
+
+def test_sparse_graph_convolutions_match_their_formulas():
+    from lbann_b200 import modules
+    N, F, E, C = 5, 4, 9, 3
+    # GCN: sum over neighbours of relu(W x_j + b)
+    tr, m, x, s, t, _ = _graph_forward(
+        lambda nodes, src, dst, _: modules.GCNConv(F, C, N, name="gcn")(nodes, src, dst), N, F, E)
+    W = m.weights_by_name["gcn_weights"].values.detach().reshape(C, F)
+    b = m.weights_by_name["gcn_bias_weights"].values.detach().reshape(C)
+    ref = _propagate(torch.relu(x @ W.t() + b), s, t, N)
+    torch.testing.assert_close(m.activation("graph_out").float(), ref, rtol=1e-5, atol=1e-5)
+    tr.shutdown()
+    # GraphConv: relu(W1 x_i) + sum relu(W2 x_j + b)
+    tr, m, x, s, t, _ = _graph_forward(
+        lambda nodes, src, dst, _: modules.GraphConv(F, C, N, name="gc")(nodes, src, dst), N, F, E, seed=1)
+    wn = {w.name: w.values.detach() for w in m.weights}
+    W1 = wn["gc_ID_FC_layer_matrix"].reshape(C, F)
+    W2 = wn["gc_Message_FC_layer_matrix"].reshape(C, F)
+    b2 = wn["gc_Message_FC_layer_bias"].reshape(C)
+    ref = torch.relu(x @ W1.t()) + _propagate(torch.relu(x @ W2.t() + b2), s, t, N)
+    torch.testing.assert_close(m.activation("graph_out").float(), ref, rtol=1e-5, atol=1e-5)
+    tr.shutdown()
+    # GIN on an edge list with a one-layer network
+    tr, m, x, s, t, _ = _graph_forward(
+        lambda nodes, src, dst, _: modules.SparseGINConv(
+            [modules.ChannelwiseFullyConnectedModule(C, bias=False, name="gin_fc")], F, C, N, eps=0.5,
+            name="gin")(nodes, src, dst), N, F, E, seed=2)
+    Wg = m.weights_by_name["gin_fc_matrix"].values.detach().reshape(C, F)
+    ref = (1.5 * x + _propagate(x, s, t, N)) @ Wg.t()
+    torch.testing.assert_close(m.activation("graph_out").float(), ref, rtol=1e-5, atol=1e-5)
+    tr.shutdown()
+    opts.reset()
+
+
+def test_gated_graph_and_edge_conditioned_convolutions():
+    from lbann_b200 import modules
+    N, F, E, C, EF = 4, 3, 6, 5, 2
+    # GatedGraphConv: padded input, one round: h' = GRU(sum_j W h_j, h)
+    tr, m, x, s, t, _ = _graph_forward(
+        lambda nodes, src, dst, _: modules.GatedGraphConv(F, C, N, num_layers=1, name="ggc")(nodes, src, dst),
+        N, F, E, seed=3)
+    wn = {w.name: w.values.detach() for w in m.weights}
+    h = torch.cat([x, torch.zeros(2, N, C - F)], 2)
+    Wm = wn["ggc_message_0_matrix"].reshape(C, C)
+    msg = _propagate(h @ Wm.t(), s, t, N)
+    Wih, bih = wn["ggc_gru_ih_fc_matrix"].reshape(3 * C, C), wn["ggc_gru_ih_fc_bias"].reshape(3 * C)
+    Whh, bhh = wn["ggc_gru_hh_fc_matrix"].reshape(3 * C, C), wn["ggc_gru_hh_fc_bias"].reshape(3 * C)
+    gi, gh = msg @ Wih.t() + bih, h @ Whh.t() + bhh
+    r = torch.sigmoid(gi[..., :C] + gh[..., :C])
+    z = torch.sigmoid(gi[..., C:2 * C] + gh[..., C:2 * C])
+    n = torch.tanh(gi[..., 2 * C:] + r * gh[..., 2 * C:])
+    ref = (1 - z) * n + z * h
+    torch.testing.assert_close(m.activation("graph_out").float(), ref, rtol=1e-5, atol=1e-5)
+    tr.shutdown()
+
+    # NNConv: relu(Theta x_i) + sum_{e: s[e] = i} x_{t[e]} . reshape(W_e edge_feat[e])
+    def build(nodes, src, dst, rest):
+        edge_feats = lbann.Reshape(rest, dims=[E, EF])
+        nbr = lbann.Reshape(modules.GraphExpand(nodes, dst), dims=[E, 1, F])
+        nn = [modules.ChannelwiseFullyConnectedModule(F * C, bias=False, name="edge_fc")]
+        return modules.NNConv(nn, N, E, F, C, EF, name="nnc")(nodes, nbr, edge_feats, src)
+    tr, m, x, s, t, ex = _graph_forward(build, N, F, E, extra=E * EF, seed=4)
+    wn = {w.name: w.values.detach() for w in m.weights}
+    We = wn["edge_fc_matrix"].reshape(F * C, EF)
+    Wn = wn["nnc_node_weights_matrix"].reshape(C, F)
+    ef = ex.reshape(2, E, EF)
+    ref = torch.relu(x @ Wn.t())
+    for b in range(2):
+        for e in range(E):
+            if s[b, e] >= 0 and t[b, e] >= 0:
+                theta = (We @ ef[b, e]).reshape(F, C)
+                ref[b, s[b, e]] += x[b, t[b, e]] @ theta
+    torch.testing.assert_close(m.activation("graph_out").float(), ref, rtol=1e-5, atol=1e-5)
+    tr.shutdown()
+    opts.reset()
+
+
+def test_roberta_matches_the_transformers_implementation(tmp_path):
+    """A small RoBERTa with its parameters exported to ``.npy``: last hidden states and the
+    pooled output equal those of ``transformers.RobertaModel`` on ids with padding."""
+    transformers = pytest.importorskip("transformers")
+    from lbann_b200.models.roberta import RoBERTa, RobertaConfig
+    torch.manual_seed(0)
+    S = 10
+    kw = dict(vocab_size=40, hidden_size=16, num_hidden_layers=2, num_attention_heads=4, intermediate_size=32,
+              max_position_embeddings=S + 2, type_vocab_size=1, pad_token_id=1, layer_norm_eps=1e-5,
+              hidden_dropout_prob=0.0, attention_probs_dropout_prob=0.0)
+    hf = transformers.RobertaModel(transformers.RobertaConfig(**kw)).eval()
+    for name, p in hf.state_dict().items():
+        if p.dtype.is_floating_point:
+            np.save(tmp_path / f"{name}.npy", p.detach().numpy())
+    o = opts.reset()
+    o.set("disable_cuda", True)
+    ids_in = lbann.Input(data_field="samples")
+    sl = lbann.Slice(ids_in, axis=0, slice_points=[0, S, 2 * S])
+    ids, amask = lbann.Identity(sl), lbann.Identity(sl)
+    hidden, pooled = RoBERTa(RobertaConfig(**kw), S, load_weights=str(tmp_path))(ids, attention_mask=amask)
+    hidden = lbann.Identity(hidden, name="hidden_out")
+    pooled = lbann.Identity(pooled, name="pooled_out")
+    loss = lbann.Add(lbann.L2Norm2(lbann.Reshape(hidden, dims=[-1])), lbann.L2Norm2(pooled))
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph([ids_in])),
+                        objective_function=lbann.ObjectiveFunction([loss]))
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=3), model=model, data_reader=_reader(3, [2 * S], "normal"),
+        optimizer=lbann.SGD(learn_rate=0.0))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    tok = torch.randint(2, 40, (3, S))
+    tok[0, 7:] = 1                      # padding at the end of the first sequence
+    tok[2, 4:] = 1
+    att = (tok != 1).long()
+    m.forward_prop({"samples": torch.cat([tok, att], 1).float()}, "validation")
+    with torch.no_grad():
+        ref = hf(input_ids=tok, attention_mask=att)
+    got_h, got_p = m.activation("hidden_out").float(), m.activation("pooled_out").float()
+    keep = att.bool()
+    torch.testing.assert_close(got_h[keep], ref.last_hidden_state[keep], rtol=2e-4, atol=2e-4)
+    torch.testing.assert_close(got_p, ref.pooler_output, rtol=2e-4, atol=2e-4)
+    tr.shutdown()
+    opts.reset()
