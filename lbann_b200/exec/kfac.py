@@ -11,8 +11,17 @@ and replaces the weight gradient dW by  (G + pi^-1 sqrt(damping_err) I)^-1 dW
 Grosse 2015; the reference: src/execution_algorithms/kfac.cpp:122-860 and
 src/execution_algorithms/kfac/kfac_block_fc_conv.cpp).  Factors are averaged over the
 data-parallel ranks; inverses are recomputed every ``update_interval`` steps with a
-Cholesky solve (``torch.linalg``; not a hot path).  Batch-norm and GRU blocks of the
-reference are not preconditioned here.
+Cholesky solve (``torch.linalg``; not a hot path) or, with ``use_eigen_decomposition``,
+from the eigen-decompositions of both factors.
+
+Batch-norm layers get the reference's dense block (kfac_block_bn.cpp): the Fisher matrix of
+the stacked (scale, bias) gradient, F = E_n[g_n g_n^T] with g_n = [sum_x dy x_hat ; sum_x dy]
+per sample, damped with ``damping_bn_err`` and inverted like the other factors.
+
+With ``distribute_precondition_compute`` (or ``inverse_strategy: "each"``) block i is
+inverted by data-parallel rank i mod P only and the inverses travel to the others (the
+reference spreads inverses over ranks the same way, kfac.cpp:480-620; its asynchronous
+secondary grid is replaced by this round-robin).  GRU blocks are not preconditioned.
 """
 from __future__ import annotations
 
@@ -59,6 +68,20 @@ class _Block:
             a = torch.cat([a, torch.ones(a.shape[0], 1, device=a.device)], 1)
         return a
 
+    def bn_sample_gradients(self, batch: int) -> torch.Tensor:
+        """[samples, 2C]: every sample's gradient of (scale, bias)."""
+        l = self.layer
+        x, g = self.inp.detach().float(), self.grad_out.detach().float() * batch
+        dims = [0] + list(range(2, x.dim()))
+        mean = x.mean(dims, keepdim=True)
+        count = x.numel() // x.shape[1]
+        var = x.var(dims, unbiased=bool(getattr(l, "bessel", False)) and count > 1, keepdim=True)
+        xhat = (x - mean) / torch.sqrt(var + l.eps)
+        sp = list(range(2, x.dim()))
+        d_scale = (g * xhat).sum(sp) if sp else g * xhat
+        d_bias = g.sum(sp) if sp else g
+        return torch.cat([d_scale, d_bias], 1)
+
     def errors(self, batch: int) -> torch.Tensor:
         l, g = self.layer, self.grad_out.detach().float()
         if l.type == "convolution":
@@ -84,6 +107,13 @@ class KFAC(SGDTrainingAlgorithm):
         self.compute_interval = int(msg.compute_interval) or 1
         self.disable_layers = set(str(msg.disable_layers).split()) if msg.disable_layers else set()
         self.lr_factor = float(msg.learning_rate_factor) or 1.0
+        self.damping_bn_act = _floats(msg.damping_bn_act, self.damping_act[0])
+        self.damping_bn_err = _floats(msg.damping_bn_err, self.damping_err[0])
+        self.use_eigen = bool(msg.use_eigen_decomposition)
+        self.distribute = bool(msg.distribute_precondition_compute) or \
+            str(msg.inverse_strategy).lower() in ("each", "root")
+        self.root_only = str(msg.inverse_strategy).lower() == "root"
+        self.inverses_computed = 0          # on this rank (tests read it)
         self.blocks: Dict[str, _Block] = {}
 
     # ---------------------------------------------------------------- schedules
@@ -102,6 +132,11 @@ class KFAC(SGDTrainingAlgorithm):
     # ---------------------------------------------------------------- set-up
     def _setup(self, model):
         for l in model.layers:
+            if l.type == "batch_normalization":
+                if l.name not in self.disable_layers and l.scale.has_optimizer() and l.bias.has_optimizer() \
+                        and not getattr(l, "fused_into_parent", False):
+                    self.blocks[l.name] = _Block(l)
+                continue
             if l.type not in ("fully_connected", "channelwise_fully_connected", "convolution"):
                 continue
             if l.name in self.disable_layers or not l.w.has_optimizer():
@@ -145,24 +180,69 @@ class KFAC(SGDTrainingAlgorithm):
             if (ctx.step - 1) % cb.batch_interval == 0:
                 cb.on_batch_end(model)
 
+    def _invert(self, M: torch.Tensor, damping: float) -> torch.Tensor:
+        eye = torch.eye(M.shape[0], device=M.device)
+        self.inverses_computed += 1
+        if self.use_eigen:
+            w, V = torch.linalg.eigh(M)
+            return (V / (w.clamp_min(0.0) + damping)) @ V.t()
+        return torch.cholesky_inverse(torch.linalg.cholesky(M + damping * eye))
+
+    def _inverses(self, par, index: int, mats, dampings):
+        """Inverses of ``mats``; with the distributed strategy one rank computes them and the
+        others receive (a sum over the ranks in which only the owner's term is non-zero)."""
+        if not self.distribute or par is None or par.dp_size <= 1:
+            return [self._invert(M, d) for M, d in zip(mats, dampings)]
+        owner = 0 if self.root_only else index % par.dp_size
+        mine = par.dp_rank == owner
+        out = []
+        for M, d in zip(mats, dampings):
+            inv = self._invert(M, d) if mine else torch.zeros_like(M)
+            par.allreduce_sum_inplace(inv)
+            out.append(inv)
+        return out
+
     @torch.no_grad()
     def _precondition(self, model, step: int, global_batch: int):
         d_act = self._damping(self.damping_act, step)
         d_err = self._damping(self.damping_err, step)
+        d_bn = self._damping(self.damping_bn_err, step)
         refresh = step % self._update_interval(step) == 0
         par = model.parallel
-        for blk in self.blocks.values():
-            if blk.grad_out is None or blk.layer.w.handle.grad is None:
+        dp = par.dp_size if par is not None else 1
+        for index, blk in enumerate(self.blocks.values()):
+            l = blk.layer
+            if blk.grad_out is None:
+                continue
+            if l.type == "batch_normalization":
+                if l.scale.handle.grad is None or l.bias.handle.grad is None:
+                    continue
+                gs = blk.bn_sample_gradients(global_batch)
+                Fm = gs.t() @ gs / gs.shape[0]
+                if dp > 1:
+                    par.allreduce_sum_inplace(Fm)
+                    Fm /= dp
+                blk.G = Fm if blk.G is None else self.decay * blk.G + (1 - self.decay) * Fm
+                if refresh or blk.Ginv is None:
+                    (blk.Ginv,) = self._inverses(par, index, [blk.G], [d_bn])
+                c = l.scale.handle.grad.numel()
+                g = torch.cat([l.scale.handle.grad.float().reshape(-1), l.bias.handle.grad.float().reshape(-1)])
+                nat = blk.Ginv @ g * self.lr_factor
+                l.scale.handle.grad.copy_(nat[:c].reshape(l.scale.handle.grad.shape))
+                l.bias.handle.grad.copy_(nat[c:].reshape(l.bias.handle.grad.shape))
+                blk.grad_out = None
+                continue
+            if l.w.handle.grad is None:
                 continue
             a = blk.activations()
             g = blk.errors(global_batch)
             A = a.t() @ a / a.shape[0]
             G = g.t() @ g / g.shape[0]
-            if par is not None and par.dp_size > 1:
+            if dp > 1:
                 par.allreduce_sum_inplace(A)
                 par.allreduce_sum_inplace(G)
-                A /= par.dp_size
-                G /= par.dp_size
+                A /= dp
+                G /= dp
             blk.A = A if blk.A is None else self.decay * blk.A + (1 - self.decay) * A
             blk.G = G if blk.G is None else self.decay * blk.G + (1 - self.decay) * G
             if refresh or blk.Ainv is None:
@@ -170,11 +250,8 @@ class KFAC(SGDTrainingAlgorithm):
                 if self.use_pi:
                     pi = float(torch.sqrt((blk.A.trace() / blk.A.shape[0]) /
                                           (blk.G.trace() / blk.G.shape[0]).clamp_min(1e-30)).clamp(1e-3, 1e3))
-                eye_a = torch.eye(blk.A.shape[0], device=A.device)
-                eye_g = torch.eye(blk.G.shape[0], device=G.device)
-                blk.Ainv = torch.cholesky_inverse(torch.linalg.cholesky(blk.A + pi * d_act ** 0.5 * eye_a))
-                blk.Ginv = torch.cholesky_inverse(torch.linalg.cholesky(blk.G + d_err ** 0.5 / pi * eye_g))
-            l = blk.layer
+                blk.Ainv, blk.Ginv = self._inverses(par, index, [blk.A, blk.G],
+                                                    [pi * d_act ** 0.5, d_err ** 0.5 / pi])
             gw = l.w.handle.grad.float().reshape(blk.G.shape[0], -1)
             if l.b is not None and l.b.handle.grad is not None:
                 gw = torch.cat([gw, l.b.handle.grad.float().reshape(-1, 1)], 1)

@@ -416,6 +416,40 @@ def ltfb(strategy):
     return {"world": world, "weights": allw, "num_trainers": tr.comm.num_trainers}
 
 
+def kfac_job(distribute, steps):
+    """K-FAC on a small MLP with batch norm; optionally the inverses are spread over the ranks."""
+    o = opts.reset()
+    o.set("disable_cuda", True)
+    x = lbann.Input(data_field="samples")
+    t = lbann.Input(data_field="responses")
+    h = lbann.FullyConnected(x, num_neurons=12, has_bias=True, name="fc1")
+    h = lbann.BatchNormalization(h, name="bn1", epsilon=1e-5, statistics_group_size=0)
+    y = lbann.FullyConnected(lbann.Tanh(h), num_neurons=3, has_bias=True, name="fc2")
+    loss = lbann.MeanSquaredError(y, t, name="mse")
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph([x, t])),
+                        objective_function=lbann.ObjectiveFunction([loss]))
+    sgd = lbann.BatchedIterativeOptimizer("sgd", epoch_count=1)
+    algo = lbann.KFAC("kfac", sgd, damping_act="1e-2", damping_err="1e-2", damping_bn_err="3e-2",
+                      kronecker_decay=0.9, update_intervals="1", compute_interval=1,
+                      distribute_precondition_compute=bool(distribute))
+    from test_models_cpu import _reader
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=16, random_seed=9, training_algo=algo), model=model,
+        data_reader=_reader(64, [8], "normal", response_dims=[3]),
+        optimizer=lbann.SGD(learn_rate=0.05, momentum=0.0))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    tr.train(m, num_batches=steps)
+    w = {x_.name: float(x_.values.detach().double().norm()) for x_ in m.weights}
+    counts = torch.tensor([float(tr.algorithm.inverses_computed)])
+    per_rank = [float(counts)]
+    if tr.parallel is not None:
+        per_rank = [float(v) for v in tr.comm.all_gather(counts, "trainer")]
+    res = {"weight_norms": w, "world": int(os.environ.get("WORLD_SIZE", "1")), "inverses": per_rank}
+    tr.shutdown()
+    return res
+
+
 def subgraph_transformer(num_subgrids, steps):
     """Encoder whose attention heads sit on two sub-grids (two heads each)."""
     from lbann_b200.models.subgraph import TransformerAllSubgraph
@@ -575,6 +609,8 @@ if __name__ == "__main__":
         res = model_parallel_fc(int(sys.argv[3]), int(sys.argv[4]), len(sys.argv) > 5 and sys.argv[5] == "sharded")
     elif what == "subgraph":
         res = subgraph_branches(int(sys.argv[3]), int(sys.argv[4]))
+    elif what == "kfac":
+        res = kfac_job(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "subgraph_transformer":
         res = subgraph_transformer(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "abort_restart":

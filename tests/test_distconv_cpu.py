@@ -127,6 +127,18 @@ def test_subgraph_parallel_branches_on_two_grids(tmp_path):
         assert abs(v - four["weight_norms"][k]) <= 1e-4 * max(1.0, abs(v)), k
 
 
+def test_kfac_inverses_spread_over_the_ranks(tmp_path):
+    """distribute_precondition_compute: every factor is inverted by one rank only and the
+    others receive it; the training trajectory is the one of the replicated computation."""
+    rep = _run(2, ["kfac", "0", "4"], str(tmp_path / "a.json"))
+    dist = _run(2, ["kfac", "1", "4"], str(tmp_path / "b.json"))
+    # 3 blocks: fc1 and fc2 have two factors, bn1 one -> 5 inverses per step
+    assert rep["inverses"] == [20.0, 20.0]
+    assert sorted(dist["inverses"]) == [4.0, 16.0] and sum(dist["inverses"]) == 20.0
+    for k, v in rep["weight_norms"].items():
+        assert abs(v - dist["weight_norms"][k]) <= 1e-5 * max(1.0, abs(v)), k
+
+
 def test_subgraph_transformer_heads_on_two_grids(tmp_path):
     """Attention heads of an encoder dealt onto two sub-grids of two ranks each: same
     trajectory as one process running all heads."""
