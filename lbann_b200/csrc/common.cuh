@@ -284,6 +284,49 @@ constexpr uint32_t kLayoutSw128 = 2;
 constexpr uint32_t kLayoutSw64 = 4;
 constexpr uint32_t kLayoutSw32 = 6;
 
+// ---------------------------------------------------------------------------------------
+// Helpers for the single threads that drive a pipeline (TMA producer, MMA issuer).  One
+// thread issues everything, so every instruction between two tcgen05.mma or two TMA boxes
+// is on the critical path: an integer division by a run-time value costs it 100-150 cycles
+// and a multiply-add chain per descriptor about as much as the MMA itself takes to execute
+// (48 cycles at N = 64, 64 at N = 128, 128 at N = 256 for M = 128, K = 16).
+
+// Division by a run-time constant as multiply-high: exact for n * d < 2^32.
+struct FastDiv {
+  uint32_t d, m;
+  __host__ __device__ FastDiv() : d(1), m(0) {}
+  __host__ explicit FastDiv(uint32_t divisor)
+      : d(divisor ? divisor : 1u), m(divisor > 1 ? (uint32_t)(0x100000000ull / divisor) + 1u : 0u) {}
+  __device__ __forceinline__ uint32_t div(uint32_t n) const { return d == 1 ? n : __umulhi(n, m); }
+  __device__ __forceinline__ void divmod(uint32_t n, uint32_t& q, uint32_t& r) const {
+    q = div(n);
+    r = n - q * d;
+  }
+};
+
+// Position in a ring of `S` pipeline stages: stage index and the parity of its barrier.
+struct RingPos {
+  uint32_t s = 0, ph = 0;
+  __device__ __forceinline__ void advance(uint32_t S) {
+    if (++s == S) { s = 0; ph ^= 1u; }
+  }
+};
+
+// tcgen05.mma without a memory clobber: for runs of MMAs between two barrier operations
+// (which carry the clobber), so that the compiler keeps descriptors in registers.  The
+// start-address field of a descriptor is its low 14 bits (address >> 4): operands of one
+// shared-memory window differ in the low word only.
+__device__ __forceinline__ void umma_f16_lo(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi,
+                                            uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                            uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\t"
+      "mov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}" ::"r"(tmem_d),
+      "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate));
+}
+
 // Instruction descriptor for tcgen05.mma kind::f16 with fp32 accumulation.
 //   fmt: 0 = fp16 inputs, 1 = bf16 inputs.  M is 128 here; N a multiple of 16.
 __host__ __device__ __forceinline__ uint32_t make_idesc_f16(uint32_t fmt, uint32_t a_mn,

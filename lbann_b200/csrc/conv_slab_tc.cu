@@ -34,6 +34,7 @@ struct SlabParams {
   int slab_bytes, stage_bytes, stages, filter_bytes;
   int in_dtype;
   long long o_sn, o_sd, o_sh, o_sw;
+  FastDiv fd_tiles_plane, fd_Do, fd_Wp;   // tile decode without run-time divisions
   EpiParams epi;
   HaloSync hs;                // halo exchange with the depth neighbours inside this kernel
 };
@@ -48,6 +49,29 @@ struct SlabShared {
   int abort_flag;
 };
 
+// The MMAs of one filter plane on one slab, straight-line: with loops over run-time tap counts
+// the issuing thread spent ~90-120 cycles per tcgen05.mma on counters and branches, twice what
+// the instruction takes to execute at N <= 64 (48 cycles); unrolled it issues at that rate.
+template <int KSTEPS, int KH, int KW>
+__device__ __forceinline__ void slab_issue_plane(uint32_t tmem_acc, uint32_t a_line, uint32_t bd,
+                                                 uint32_t line_step, uint32_t pix_step,
+                                                 uint32_t tap_step, uint32_t d_hi, uint32_t idesc,
+                                                 uint32_t& accum) {
+#pragma unroll
+  for (int b = 0; b < KH; ++b) {
+#pragma unroll
+    for (int c = 0; c < KW; ++c) {
+      const uint32_t ad = a_line + b * line_step + c * pix_step;
+      const uint32_t bt = bd + (b * KW + c) * tap_step;
+#pragma unroll
+      for (int kk = 0; kk < KSTEPS; ++kk) {
+        umma_f16_lo(tmem_acc, ad + 2 * kk, d_hi, bt + 2 * kk, d_hi, idesc, accum);
+        accum = 1u;
+      }
+    }
+  }
+}
+
 template <int BN>
 __global__ void __launch_bounds__(192, 1)
 conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
@@ -61,7 +85,6 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
   volatile int* abort_flag = &sh.abort_flag;
   const int S = p.stages;
   const ConvGeom& g = p.g;
-  const int stages_per_tile = g.kd * p.cblocks;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < S; ++s) {
@@ -112,11 +135,13 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
           hs.enabled ? (*reinterpret_cast<volatile uint32_t*>(hs.local) + 1u) * gridDim.x : 0u;
       bool top_ok = !hs.enabled || hs.top_flag == nullptr;
       bool bot_ok = !hs.enabled || hs.bot_flag == nullptr;
+      RingPos rp;
       for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x) {
-        int r = t;
-        const int ti = r % p.tiles_plane; r /= p.tiles_plane;
-        const int d = hs.enabled ? halo_rotate(r % g.Do, g.Do) : r % g.Do, n = r / g.Do;
-        const int l0 = (ti * 128) / p.Wp;
+        uint32_t ti, r, dd, nn;
+        p.fd_tiles_plane.divmod((uint32_t)t, r, ti);
+        p.fd_Do.divmod(r, nn, dd);
+        const int d = hs.enabled ? halo_rotate((int)dd, g.Do) : (int)dd, n = (int)nn;
+        const int l0 = (int)p.fd_Wp.div(ti * 128u);
         for (int a = 0; a < g.kd && ok; ++a) {
           const int plane_in = d - g.pd + a;
           if (!top_ok && plane_in < hs.h) {
@@ -128,8 +153,8 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             if (!bot_ok) { ok = false; break; }
           }
           for (int j = 0; j < p.cblocks; ++j, ++it) {
-            const uint32_t s = it % S, ph = (it / S) & 1;
-            if (!mbar_wait_bounded(smem_u32(&sh.empty[s]), ph ^ 1, abort_flag)) {
+            const uint32_t s = rp.s;
+            if (!mbar_wait_bounded(smem_u32(&sh.empty[s]), rp.ph ^ 1, abort_flag)) {
               raise_status(status, abort_flag, kTimeoutStageEmpty);
               ok = false;
               break;
@@ -138,6 +163,7 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
             mbar_expect_tx(bar, (uint32_t)p.slab_bytes);
             tma_load_5d(s_stage0 + s * p.stage_bytes, &tmX, bar, j * p.Cb, -g.pw, l0 - g.ph,
                         d - g.pd + a, n);
+            rp.advance((uint32_t)S);
           }
         }
       }
@@ -152,19 +178,32 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     }
   } else if (warp == 5) {
     if (lane == 0) {
+      // Everything between two tcgen05.mma of this loop is on the critical path of the CTA
+      // (one thread issues all of them): descriptors differ in the start-address field of
+      // their low word only, and the tap offsets are running sums.
       const uint32_t idesc = make_idesc_f16(p.in_dtype == kBF16 ? 1u : 0u, 0, 0, 128, BN);
       const uint32_t row_bytes = p.Cb * 2;
       const uint64_t desc0 = make_smem_desc(0, 16, 8 * row_bytes, p.layout_type);
-      const uint32_t tap_bytes = BN * row_bytes;                 // one tap of the filter
-      const uint32_t fblock = p.filter_bytes / p.cblocks;
-      const int ksteps = p.Cb / 16;
+      const uint32_t d_lo = (uint32_t)desc0, d_hi = (uint32_t)(desc0 >> 32);
+      const uint32_t tap_step = (BN * row_bytes) >> 4;            // one tap of the filter
+      const uint32_t pix_step = row_bytes >> 4;                   // one pixel along a row
+      const uint32_t line_step = ((uint32_t)p.Wp * row_bytes) >> 4;   // one image row in the slab
+      const uint32_t fblock = ((uint32_t)p.filter_bytes / (uint32_t)p.cblocks) >> 4;
+      const uint32_t plane_step = (uint32_t)(g.kh * g.kw) * tap_step;
+      const uint32_t stage_step = (uint32_t)p.stage_bytes >> 4;
+      const uint32_t ksteps = (uint32_t)p.Cb / 16u;
+      const uint32_t kh = (uint32_t)g.kh, kw = (uint32_t)g.kw, kd = (uint32_t)g.kd;
+      const uint32_t cblocks = (uint32_t)p.cblocks;
+      const bool plane33 = kh == 3 && kw == 3;
       bool ok = mbar_wait_bounded(smem_u32(&sh.filter_ready), 0, abort_flag);
       if (!ok) raise_status(status, abort_flag, kTimeoutTmaFull);
-      uint32_t it = 0, lt = 0;
+      uint32_t lt = 0;
+      RingPos rp;
       for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, ++lt) {
-        const int ti = t % p.tiles_plane;
-        const int q0 = ti * 128;
-        const uint32_t row0 = q0 - (q0 / p.Wp) * p.Wp;           // first operand row in the slab
+        uint32_t ti, r;
+        p.fd_tiles_plane.divmod((uint32_t)t, r, ti);
+        const uint32_t q0 = ti * 128u;
+        const uint32_t row0 = q0 - p.fd_Wp.div(q0) * (uint32_t)p.Wp;   // first operand row in the slab
         const uint32_t acc = lt & 1, acc_ph = (lt >> 1) & 1;
         if (!mbar_wait_bounded(smem_u32(&sh.tmem_empty[acc]), acc_ph ^ 1, abort_flag)) {
           raise_status(status, abort_flag, kTimeoutTmemEmpty);
@@ -173,29 +212,39 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         }
         tc_fence_after();
         const uint32_t tmem_acc = tmem_base + acc * BN;
+        const uint32_t a_tile = d_lo + ((s_stage0 + row0 * row_bytes) >> 4);
         uint32_t accum = 0;
-        for (int a = 0; a < g.kd && ok; ++a) {
-          for (int j = 0; j < p.cblocks; ++j, ++it) {
-            const uint32_t s = it % S, ph = (it / S) & 1;
-            if (!mbar_wait_bounded(smem_u32(&sh.full[s]), ph, abort_flag)) {
+        uint32_t b_plane = d_lo + (s_filter >> 4);
+        for (uint32_t a = 0; a < kd && ok; ++a, b_plane += plane_step) {
+          uint32_t b_blk = b_plane;
+          for (uint32_t j = 0; j < cblocks; ++j, b_blk += fblock) {
+            if (!mbar_wait_bounded(smem_u32(&sh.full[rp.s]), rp.ph, abort_flag)) {
               raise_status(status, abort_flag, kTimeoutTmaFull);
               ok = false;
               break;
             }
             tc_fence_after();
-            const uint32_t slab = s_stage0 + s * p.stage_bytes + row0 * row_bytes;
-            const uint32_t fil = s_filter + j * fblock + a * (g.kh * g.kw) * tap_bytes;
-            for (int b = 0; b < g.kh; ++b) {
-              for (int c = 0; c < g.kw; ++c) {
-                const uint64_t ad = desc0 + ((slab + (b * p.Wp + c) * row_bytes) >> 4);
-                const uint64_t bd = desc0 + ((fil + (b * g.kw + c) * tap_bytes) >> 4);
-                for (int kk = 0; kk < ksteps; ++kk) {
-                  umma_f16(tmem_acc, ad + 2 * kk, bd + 2 * kk, idesc, accum);
-                  accum = 1u;
+            uint32_t a_line = a_tile + rp.s * stage_step;
+            uint32_t bd = b_blk;
+            if (plane33 && ksteps == 2) {
+              slab_issue_plane<2, 3, 3>(tmem_acc, a_line, bd, line_step, pix_step, tap_step, d_hi, idesc, accum);
+            } else if (plane33 && ksteps == 4) {
+              slab_issue_plane<4, 3, 3>(tmem_acc, a_line, bd, line_step, pix_step, tap_step, d_hi, idesc, accum);
+            } else if (plane33 && ksteps == 1) {
+              slab_issue_plane<1, 3, 3>(tmem_acc, a_line, bd, line_step, pix_step, tap_step, d_hi, idesc, accum);
+            } else {
+              for (uint32_t b = 0; b < kh; ++b, a_line += line_step) {
+                uint32_t ad = a_line;
+                for (uint32_t c = 0; c < kw; ++c, ad += pix_step, bd += tap_step) {
+                  for (uint32_t kk = 0; kk < ksteps; ++kk) {
+                    umma_f16_lo(tmem_acc, ad + 2 * kk, d_hi, bd + 2 * kk, d_hi, idesc, accum);
+                    accum = 1u;
+                  }
                 }
               }
             }
-            umma_commit(smem_u32(&sh.empty[s]));
+            umma_commit(smem_u32(&sh.empty[rp.s]));
+            rp.advance((uint32_t)S);
           }
         }
         if (ok) umma_commit(smem_u32(&sh.tmem_full[acc]));
@@ -205,9 +254,10 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
     uint32_t lt = 0;
     const EpiParams& e = p.epi;
     for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++lt) {
-      int r = t;
-      const int ti = r % p.tiles_plane; r /= p.tiles_plane;
-      const int d = hs.enabled ? halo_rotate(r % g.Do, g.Do) : r % g.Do, n = r / g.Do;
+      uint32_t ti, r, dd, nn;
+      p.fd_tiles_plane.divmod((uint32_t)t, r, ti);
+      p.fd_Do.divmod(r, nn, dd);
+      const int d = hs.enabled ? halo_rotate((int)dd, g.Do) : (int)dd, n = (int)nn;
       const uint32_t acc = lt & 1, acc_ph = (lt >> 1) & 1;
       const bool landed = __all_sync(
           0xffffffffu, mbar_wait_bounded(smem_u32(&sh.tmem_full[acc]), acc_ph, abort_flag));
@@ -217,8 +267,8 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       }
       tc_fence_after();
       const int row = warp * 32 + lane;
-      const int q = ti * 128 + row;
-      const int h = q / p.Wp, w = q - h * p.Wp;
+      const uint32_t q = ti * 128u + (uint32_t)row;
+      const int h = (int)p.fd_Wp.div(q), w = (int)q - h * p.Wp;
       const long long row_off = n * p.o_sn + d * p.o_sd + h * p.o_sh + (long long)w * p.o_sw;
       const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(warp * 32) << 16);
       tc_epilogue_rows<BN>(TmemSrc{taddr}, h < g.Ho && w < g.Wo, row_off, 0, g.Kout, row, e);
@@ -284,6 +334,11 @@ extern "C" int lb_conv_slab_fwd(const void* x, const void* w, void* y, const flo
   if (p.stages > kSlabMaxStages) p.stages = kSlabMaxStages;
   p.tiles_plane = (g.Ho * p.Wp + 127) / 128;
   p.num_tiles = p.tiles_plane * g.Do * g.N;
+  if ((long long)p.num_tiles * p.tiles_plane >= (1ll << 32) || (long long)p.num_tiles * g.Do >= (1ll << 32))
+    return -2;                      // beyond the exact range of the multiply-high divisions
+  p.fd_tiles_plane = FastDiv((uint32_t)p.tiles_plane);
+  p.fd_Do = FastDiv((uint32_t)g.Do);
+  p.fd_Wp = FastDiv((uint32_t)p.Wp);
   p.in_dtype = in_dtype;
   p.o_sn = ys[0]; p.o_sd = ys[1]; p.o_sh = ys[2]; p.o_sw = ys[3];
   p.epi.C = y; p.epi.bias = bias; p.epi.alpha = alpha; p.epi.beta = beta;
