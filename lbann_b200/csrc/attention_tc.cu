@@ -82,23 +82,29 @@ __device__ __forceinline__ void fence_async_smem() {
 // acc (+)= A . B^T over K = 128 with both operands K-major tiles [2][128 rows][64 k].
 __device__ __forceinline__ void att_mma_kk(uint32_t acc, uint32_t a, uint32_t b, uint32_t idesc,
                                            bool accumulate) {
+  // the eight descriptors differ in the start-address field of the low word only
+  const uint64_t d0 = make_smem_desc(0, 16, 1024, kLayoutSw128);
+  const uint32_t hi = (uint32_t)(d0 >> 32);
+  const uint32_t alo = (uint32_t)d0 + (a >> 4), blo = (uint32_t)d0 + (b >> 4);
 #pragma unroll
   for (int kk = 0; kk < 8; ++kk) {
-    const uint32_t off = (kk >> 2) * kAttHalf + (kk & 3) * 32;
-    umma_f16(acc, make_smem_desc(a + off, 16, 1024, kLayoutSw128),
-             make_smem_desc(b + off, 16, 1024, kLayoutSw128), idesc, (accumulate || kk) ? 1u : 0u);
+    const uint32_t off = ((kk >> 2) * kAttHalf + (kk & 3) * 32) >> 4;
+    umma_f16_lo(acc, alo + off, hi, blo + off, hi, idesc, (accumulate || kk) ? 1u : 0u);
   }
 }
 // acc (+)= A . B with A a K-major tile [2][128 rows][64 k] and B given as rows of K:
 // [2 halves of N][128 k rows][64 n] ("MN-major"; the layout of a token-major tile as loaded).
 __device__ __forceinline__ void att_mma_kn(uint32_t acc, uint32_t a, uint32_t b, uint32_t idesc,
                                            bool accumulate) {
+  const uint64_t da = make_smem_desc(0, 16, 1024, kLayoutSw128);
+  const uint64_t db = make_smem_desc(0, kAttHalf, 1024, kLayoutSw128);
+  const uint32_t ahi = (uint32_t)(da >> 32), bhi = (uint32_t)(db >> 32);
+  const uint32_t alo = (uint32_t)da + (a >> 4), blo = (uint32_t)db + (b >> 4);
 #pragma unroll
   for (int kk = 0; kk < 8; ++kk) {
-    const uint32_t aoff = (kk >> 2) * kAttHalf + (kk & 3) * 32;
-    umma_f16(acc, make_smem_desc(a + aoff, 16, 1024, kLayoutSw128),
-             make_smem_desc(b + kk * 2048, kAttHalf, 1024, kLayoutSw128), idesc,
-             (accumulate || kk) ? 1u : 0u);
+    const uint32_t aoff = ((kk >> 2) * kAttHalf + (kk & 3) * 32) >> 4;
+    umma_f16_lo(acc, alo + aoff, ahi, blo + ((kk * 2048) >> 4), bhi, idesc,
+                (accumulate || kk) ? 1u : 0u);
   }
 }
 

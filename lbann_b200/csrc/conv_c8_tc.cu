@@ -16,6 +16,7 @@
 // The reference relies on cuDNN for this layer
 // (src/layers/learning/base_convolution.cpp:462-814).
 #include "tc_pipeline.cuh"
+#include <algorithm>
 
 namespace lb {
 
@@ -125,6 +126,7 @@ struct C8FwdParams {
   int in_dtype;
   const void* w;               // packed filter in global memory
   long long o_sn, o_sd, o_sh, o_sw;
+  FastDiv fd_tiles_w, fd_H, fd_Do;   // tile decode without run-time divisions
   EpiParams epi;
 };
 
@@ -204,13 +206,15 @@ conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const C8FwdParams p,
       const int step_tw = gridDim.x % p.tiles_w, step_r = gridDim.x / p.tiles_w;
       const int step_h = step_r % g.H, step_r2 = step_r / g.H;
       const int step_d = step_r2 % g.Do, step_n = step_r2 / g.Do;
+      RingPos rp;
       for (; t < p.num_tiles; t += gridDim.x, ++it) {
-        const uint32_t s = it % S, ph = (it / S) & 1;
-        if (!mbar_wait_bounded(smem_u32(&sh.empty[s]), ph ^ 1, abort_flag)) {
+        const uint32_t s = rp.s;
+        if (!mbar_wait_bounded(smem_u32(&sh.empty[s]), rp.ph ^ 1, abort_flag)) {
           raise_status(status, abort_flag, kTimeoutStageEmpty);
           ok = false;
           break;
         }
+        rp.advance((uint32_t)S);
         const uint32_t bar = smem_u32(&sh.full[s]);
         mbar_expect_tx(bar, (uint32_t)(p.taps2 * p.slab_row_bytes));
         tma_load_5d(s_stage0 + s * p.stage_bytes, &tmX, bar, 0, tw * (128 / chunk_px) - 1,
@@ -241,10 +245,14 @@ conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const C8FwdParams p,
       // BN * 16 B apart (LBO), 8-row groups 128 B apart (SBO).  One UMMA = 2 K chunks.
       const uint64_t a_desc0 = make_smem_desc(0, 128, p.mb_pad * 128, kLayoutNone);
       const uint64_t b_desc0 = make_smem_desc(s_filter, BN * 16, 128, kLayoutNone);
-      uint32_t it = 0;
+      const uint32_t a_hi = (uint32_t)(a_desc0 >> 32), b_hi = (uint32_t)(b_desc0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)a_desc0 + (s_a0 >> 4), b_lo0 = (uint32_t)b_desc0;
+      const uint32_t a_buf_step = a_bytes >> 4;
+      const int ksteps = p.ksteps;
       bool ok = true;
-      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, ++it) {
-        const uint32_t j = it % G, jph = (it / G) & 1;
+      RingPos gp;                                   // which worker group's buffers: (j, parity)
+      for (int t = blockIdx.x; t < p.num_tiles && ok; t += gridDim.x, gp.advance((uint32_t)G)) {
+        const uint32_t j = gp.s, jph = gp.ph;
         if (!mbar_wait_bounded(smem_u32(&sh.tmem_empty[j]), jph ^ 1, abort_flag)) {
           raise_status(status, abort_flag, kTimeoutTmemEmpty);
           ok = false;
@@ -256,14 +264,17 @@ conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const C8FwdParams p,
           break;
         }
         tc_fence_after();
-        uint64_t ad = a_desc0 + ((s_a0 + j * a_bytes) >> 4);
-        uint64_t bd = b_desc0;
+        uint32_t ad = a_lo0 + j * a_buf_step;
+        uint32_t bd = b_lo0;
         const uint32_t tmem_acc = tmem_base + j * BN;
-        for (int kk = 0; kk < p.ksteps; ++kk) {
-          umma_f16(tmem_acc, ad, bd, idesc, kk == 0 ? 0u : 1u);
-          ad += (2 * 128) >> 4;
-          bd += (2 * BN * 16) >> 4;
+        constexpr uint32_t kAStep = (2 * 128) >> 4, kBStep = (2 * BN * 16) >> 4;
+        umma_f16_lo(tmem_acc, ad, a_hi, bd, b_hi, idesc, 0u);
+        int kk = 1;
+        for (; kk + 1 < ksteps; kk += 2) {          // two per round: half the loop overhead
+          umma_f16_lo(tmem_acc, ad + kk * kAStep, a_hi, bd + kk * kBStep, b_hi, idesc, 1u);
+          umma_f16_lo(tmem_acc, ad + (kk + 1) * kAStep, a_hi, bd + (kk + 1) * kBStep, b_hi, idesc, 1u);
         }
+        if (kk < ksteps) umma_f16_lo(tmem_acc, ad + kk * kAStep, a_hi, bd + kk * kBStep, b_hi, idesc, 1u);
         umma_commit(smem_u32(&sh.a_free[j]));
         umma_commit(smem_u32(&sh.tmem_full[j]));
       }
@@ -277,13 +288,17 @@ conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const C8FwdParams p,
     const uint32_t j = group;
     int t_prev = -1;
     uint32_t use = 0;                               // how often this group used its buffers
+    // ring position of tile `it` = group, group + G, ...: advanced by G stages per round
+    uint32_t rs = (uint32_t)group % (uint32_t)S, rph = ((uint32_t)group / (uint32_t)S) & 1u;
     for (uint32_t it = group;; it += G, ++use) {
       const long long tl = (long long)blockIdx.x + (long long)it * gridDim.x;
       const bool have = tl < p.num_tiles;
       const int t = (int)tl;
       if (have) {
         // ---- unfold tile `it` ---------------------------------------------------------
-        const uint32_t s = it % S, ph = (it / S) & 1;
+        const uint32_t s = rs, ph = rph;
+        rs += (uint32_t)G;
+        if (rs >= (uint32_t)S) { rs -= (uint32_t)S; rph ^= 1u; }
         const uint32_t jph = use & 1;
         bool good = mbar_wait_bounded(smem_u32(&sh.full[s]), ph, abort_flag);
         good = good && mbar_wait_bounded(smem_u32(&sh.a_free[j]), jph ^ 1, abort_flag);
@@ -305,10 +320,11 @@ conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const C8FwdParams p,
       // ---- epilogue of this group's previous tile (its UMMAs ran meanwhile) ------------
       if (t_prev >= 0) {
         const uint32_t acc_ph = (use - 1) & 1;
-        int r = t_prev;
-        const int tw = r % p.tiles_w; r /= p.tiles_w;
-        const int h = r % g.H; r /= g.H;
-        const int d = r % g.Do, n = r / g.Do;
+        uint32_t r, utw, uh, ud, un;
+        p.fd_tiles_w.divmod((uint32_t)t_prev, r, utw);
+        p.fd_H.divmod(r, r, uh);
+        p.fd_Do.divmod(r, un, ud);
+        const int tw = (int)utw, h = (int)uh, d = (int)ud, n = (int)un;
         const bool landed = __all_sync(
             0xffffffffu, mbar_wait_bounded(smem_u32(&sh.tmem_full[j]), acc_ph, abort_flag));
         if (!landed) {
@@ -367,6 +383,7 @@ struct C8WgradParams {
   float alpha;
   float* dW;
   long long s_tap, s_k, s_c;   // tap = (a*kh + b)*3 + kw
+  FastDiv fd_bricks_w, fd_H, fd_Do;  // brick decode without run-time divisions
 };
 
 constexpr int kWgMaxStages = 8;
@@ -431,18 +448,20 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     if (lane == 0) {
       uint32_t it = 0;
       bool ok = true;
+      RingPos rp;
       for (int b = split; b < p.bricks_total && ok; b += p.splits, ++it) {
-        int r = b;
-        const int bw = r % p.bricks_w; r /= p.bricks_w;
-        const int h = r % g.H; r /= g.H;
-        const int d = r % g.Do; r /= g.Do;
-        const int n = r;
-        const uint32_t s = it % S, ph = (it / S) & 1;
-        if (!mbar_wait_bounded(smem_u32(&sh.empty[s]), ph ^ 1, abort_flag)) {
+        uint32_t r, ubw, uh, ud, un;
+        p.fd_bricks_w.divmod((uint32_t)b, r, ubw);
+        p.fd_H.divmod(r, r, uh);
+        p.fd_Do.divmod(r, un, ud);
+        const int bw = (int)ubw, h = (int)uh, d = (int)ud, n = (int)un;
+        const uint32_t s = rp.s;
+        if (!mbar_wait_bounded(smem_u32(&sh.empty[s]), rp.ph ^ 1, abort_flag)) {
           raise_status(status, abort_flag, kTimeoutStageEmpty);
           ok = false;
           break;
         }
+        rp.advance((uint32_t)S);
         const uint32_t sX = s_stage0 + s * p.stage_bytes;
         const uint32_t sDy = sX + p.slab_bytes;
         const uint32_t bar = smem_u32(&sh.full[s]);
@@ -469,32 +488,44 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
       const uint32_t b_row = p.BN == 32 ? 64u : 128u;
       const uint64_t b_desc0 =
           make_smem_desc(0, 8192, 8 * b_row, p.BN == 32 ? kLayoutSw64 : kLayoutSw128);
-      uint32_t it = 0;
+      const uint32_t a_hi = (uint32_t)(a_desc0 >> 32), b_hi = (uint32_t)(b_desc0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)a_desc0 + (s_a0 >> 4);
+      const uint32_t b_lo0 = (uint32_t)b_desc0 + ((s_stage0 + (uint32_t)p.slab_bytes) >> 4);
+      const uint32_t a_buf_step = a_bytes >> 4, stage_step = (uint32_t)p.stage_bytes >> 4;
+      const uint32_t a_kstep = (2u * p.mb_pad * 128u) >> 4;     // two pixel groups
+      const uint32_t b_kstep = (16u * b_row) >> 4;              // sixteen pixel rows
+      const uint32_t BNu = (uint32_t)p.BN;
+      const int m_tiles = p.m_tiles;
+      uint32_t first = 0;                           // 0 for the MMAs that start an accumulator
       bool ok = true;
-      for (int b = split; b < p.bricks_total && ok; b += p.splits, ++it) {
-        const uint32_t s = it % S, ph = (it / S) & 1;
-        const uint32_t j = it % G, jph = (it / G) & 1;
-        if (!mbar_wait_bounded(smem_u32(&sh.full[s]), ph, abort_flag) ||
-            !mbar_wait_bounded(smem_u32(&sh.a_ready[j]), jph, abort_flag)) {
+      RingPos rp, gp;
+      for (int b = split; b < p.bricks_total && ok; b += p.splits) {
+        const uint32_t s = rp.s, j = gp.s;
+        if (!mbar_wait_bounded(smem_u32(&sh.full[s]), rp.ph, abort_flag) ||
+            !mbar_wait_bounded(smem_u32(&sh.a_ready[j]), gp.ph, abort_flag)) {
           raise_status(status, abort_flag, kTimeoutTmaFull);
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t sDy = s_stage0 + s * p.stage_bytes + p.slab_bytes;
-        const uint64_t ad0 = a_desc0 + ((s_a0 + j * a_bytes) >> 4);
-        const uint64_t bd0 = b_desc0 + (sDy >> 4);
-        for (int mt = 0; mt < p.m_tiles; ++mt) {
-          uint64_t ad = ad0 + ((mt * 16 * 128) >> 4);
-          uint64_t bd = bd0;
-          for (int kk = 0; kk < k_steps; ++kk) {
-            umma_f16(tmem_base + mt * p.BN, ad, bd, idesc, (it == 0 && kk == 0) ? 0u : 1u);
-            ad += (2 * p.mb_pad * 128) >> 4;     // two pixel groups
-            bd += (16 * b_row) >> 4;             // sixteen pixel rows
+        const uint32_t ad0 = a_lo0 + j * a_buf_step;
+        const uint32_t bd0 = b_lo0 + s * stage_step;
+        for (int mt = 0; mt < m_tiles; ++mt) {
+          const uint32_t ad = ad0 + (uint32_t)mt * ((16u * 128u) >> 4);
+          const uint32_t acc = tmem_base + (uint32_t)mt * BNu;
+          umma_f16_lo(acc, ad, a_hi, bd0, b_hi, idesc, first);
+          int kk = 1;
+          for (; kk + 1 < k_steps; kk += 2) {
+            umma_f16_lo(acc, ad + kk * a_kstep, a_hi, bd0 + kk * b_kstep, b_hi, idesc, 1u);
+            umma_f16_lo(acc, ad + (kk + 1) * a_kstep, a_hi, bd0 + (kk + 1) * b_kstep, b_hi, idesc, 1u);
           }
+          if (kk < k_steps) umma_f16_lo(acc, ad + kk * a_kstep, a_hi, bd0 + kk * b_kstep, b_hi, idesc, 1u);
         }
+        first = 1u;
         umma_commit(smem_u32(&sh.empty[s]));
         umma_commit(smem_u32(&sh.a_free[j]));
+        rp.advance((uint32_t)S);
+        gp.advance((uint32_t)G);
       }
       if (ok) umma_commit(smem_u32(&sh.done));
     }
@@ -506,9 +537,12 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
     const uint32_t j = group;
     bool ok = true;
     uint32_t use = 0;
+    uint32_t rs = (uint32_t)group % (uint32_t)S, rph = ((uint32_t)group / (uint32_t)S) & 1u;
     for (uint32_t it = group; (long long)split + (long long)it * p.splits < p.bricks_total;
          it += G, ++use) {
-      const uint32_t s = it % S, ph = (it / S) & 1;
+      const uint32_t s = rs, ph = rph;
+      rs += (uint32_t)G;
+      if (rs >= (uint32_t)S) { rs -= (uint32_t)S; rph ^= 1u; }
       const uint32_t jph = use & 1;
       bool good = mbar_wait_bounded(smem_u32(&sh.full[s]), ph, abort_flag);
       good = good && mbar_wait_bounded(smem_u32(&sh.a_free[j]), jph ^ 1, abort_flag);
@@ -608,6 +642,13 @@ int lb_conv_c8_fwd(const void* x, const void* w, void* y, const float* bias, con
   if (p.stages < 2) return -1;
   p.tiles_w = (g.W + 127) / 128;
   p.num_tiles = p.tiles_w * g.H * g.Do * g.N;
+  {   // exact range of the multiply-high divisions
+    const long long dmax = std::max(std::max(p.tiles_w, g.H), g.Do);
+    if ((long long)p.num_tiles * dmax >= (1ll << 32)) return -1;
+  }
+  p.fd_tiles_w = FastDiv((uint32_t)p.tiles_w);
+  p.fd_H = FastDiv((uint32_t)g.H);
+  p.fd_Do = FastDiv((uint32_t)g.Do);
   p.in_dtype = in_dtype;
   p.w = w;
   p.o_sn = ys[0]; p.o_sd = ys[1]; p.o_sh = ys[2]; p.o_sw = ys[3];
@@ -675,6 +716,13 @@ int lb_conv_c8_wgrad(const void* x, const void* dy, float* dW, const int* geom,
   if (p.stages < 2) return -1;
   p.bricks_w = (g.W + kWgBrick - 1) / kWgBrick;
   p.bricks_total = p.bricks_w * g.H * g.Do * g.N;
+  {
+    const long long dmax = std::max(std::max(p.bricks_w, g.H), g.Do);
+    if ((long long)p.bricks_total * dmax >= (1ll << 32)) return -1;
+  }
+  p.fd_bricks_w = FastDiv((uint32_t)p.bricks_w);
+  p.fd_H = FastDiv((uint32_t)g.H);
+  p.fd_Do = FastDiv((uint32_t)g.Do);
   int splits = lbhost::sm_count();
   if (splits > p.bricks_total) splits = p.bricks_total;
   p.splits = splits;

@@ -14,6 +14,7 @@
 // (src/layers/learning/base_convolution.cpp:462-814).
 #include "conv_geom.cuh"
 #include "tc_pipeline.cuh"
+#include <algorithm>
 
 namespace lb {
 
@@ -29,6 +30,10 @@ struct ConvFwdPolicy {
     int Cb, cblocks, slices, slices_per_stage, layout_type;
     int num_tiles, k_iters, in_dtype;
     long long o_sn, o_sd, o_sh, o_sw;  // output strides in elements
+    // divisions by run-time values as multiply-high (the producer and the MMA issuer are
+    // single threads: a plain division costs them 100+ cycles)
+    FastDiv fd_tiles_col, fd_tiles_w, fd_tiles_h, fd_tiles_d, fd_cblocks, fd_khw, fd_kw;
+    FastDiv fd_TW, fd_TH, fd_TD;
     EpiParams epi;
     HaloSync hs;                       // halo exchange with the depth neighbours (distconv)
   };
@@ -46,14 +51,16 @@ struct ConvFwdPolicy {
 
   __device__ static Tile decode(const Params& p, int t) {
     Tile tl;
-    int r = t;
-    const int cb = r % p.tiles_col; r /= p.tiles_col;
-    const int tw = r % p.tiles_w;   r /= p.tiles_w;
-    const int th = r % p.tiles_h;   r /= p.tiles_h;
-    int td = r % p.tiles_d;         r /= p.tiles_d;
+    uint32_t r = (uint32_t)t, ucb, utw, uth, utd;
+    p.fd_tiles_col.divmod(r, r, ucb);
+    p.fd_tiles_w.divmod(r, r, utw);
+    p.fd_tiles_h.divmod(r, r, uth);
+    p.fd_tiles_d.divmod(r, r, utd);
+    const int cb = (int)ucb, tw = (int)utw, th = (int)uth;
+    int td = (int)utd;
     if (p.hs.enabled) td = halo_rotate(td, p.tiles_d);   // the brick that needs the top halo goes last
     tl.col0 = cb * BN;
-    tl.w0 = tw * p.TW; tl.h0 = th * p.TH; tl.d0 = td * p.TD; tl.n0 = r * p.TN;
+    tl.w0 = tw * p.TW; tl.h0 = th * p.TH; tl.d0 = td * p.TD; tl.n0 = (int)r * p.TN;
     return tl;
   }
   __device__ static int slices_in(const Params& p, int k) {
@@ -72,12 +79,13 @@ struct ConvFwdPolicy {
     const int j = lane >> 1;
     if (j >= ns) return;
     const int sl = k * p.slices_per_stage + j;
-    const int tap = sl / p.cblocks;
+    const int tap = (int)p.fd_cblocks.div((uint32_t)sl);
     const int c0 = (sl - tap * p.cblocks) * p.Cb;
     if ((lane & 1) == 0) {
-      const int a = tap / (g.kh * g.kw);
-      const int b = (tap / g.kw) % g.kh;
-      const int c = tap % g.kw;
+      uint32_t ua, rem, ub, uc;
+      p.fd_khw.divmod((uint32_t)tap, ua, rem);
+      p.fd_kw.divmod(rem, ub, uc);
+      const int a = (int)ua, b = (int)ub, c = (int)uc;
       tma_load_5d(sA + j * (kBM * p.Cb * 2), tmA, bar, c0,
                   tl.w0 * g.sw - g.pw + c * g.dw,
                   tl.h0 * g.sh - g.ph + b * g.dh,
@@ -91,25 +99,33 @@ struct ConvFwdPolicy {
   }
   __device__ static void mma(const Params& p, int k, uint32_t sA, uint32_t sB, uint32_t tmem_acc,
                              uint32_t idesc, bool first) {
+    // A stage holds 64 / Cb slices of Cb channels: four MMAs of K = 16 whatever Cb is.  MMA i
+    // reads slice i / (Cb / 16), K step i % (Cb / 16); descriptors differ in the low word.
     const int ns = slices_in(p, k);
-    const uint32_t sbo = 8u * p.Cb * 2u;  // 8 rows of Cb elements
+    const uint64_t d0 = make_smem_desc(0, 16, 8u * p.Cb * 2u, p.layout_type);
+    const uint32_t hi = (uint32_t)(d0 >> 32);
+    const uint32_t a_lo = (uint32_t)d0 + (sA >> 4), b_lo = (uint32_t)d0 + (sB >> 4);
+    const uint32_t a_slice = (uint32_t)(kBM * p.Cb * 2) >> 4, b_slice = (uint32_t)(BN * p.Cb * 2) >> 4;
+    const int per = p.Cb >> 4;                    // MMAs per slice: 4, 2 or 1
+    const int sh = per == 4 ? 2 : (per == 2 ? 1 : 0);
+    const int count = ns * per;
     uint32_t acc = first ? 0u : 1u;
-    for (int j = 0; j < ns; ++j) {
-      const uint32_t a0 = sA + j * (kBM * p.Cb * 2);
-      const uint32_t b0 = sB + j * (BN * p.Cb * 2);
-      for (int kk = 0; kk < p.Cb / 16; ++kk) {
-        umma_f16(tmem_acc, make_smem_desc(a0 + kk * 32, 16, sbo, p.layout_type),
-                 make_smem_desc(b0 + kk * 32, 16, sbo, p.layout_type), idesc, acc);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      if (i < count) {
+        const uint32_t j = (uint32_t)i >> sh, kk = (uint32_t)i & (uint32_t)(per - 1);
+        umma_f16_lo(tmem_acc, a_lo + j * a_slice + 2 * kk, hi, b_lo + j * b_slice + 2 * kk, hi, idesc, acc);
         acc = 1u;
       }
     }
   }
   __device__ static bool row_addr(const Params& p, const Tile& tl, int row, long long& off) {
-    int r = row;
-    const int tw = r % p.TW; r /= p.TW;
-    const int th = r % p.TH; r /= p.TH;
-    const int td = r % p.TD; r /= p.TD;
-    const int n = tl.n0 + r, d = tl.d0 + td, h = tl.h0 + th, w = tl.w0 + tw;
+    uint32_t r = (uint32_t)row, utw, uth, utd;
+    p.fd_TW.divmod(r, r, utw);
+    p.fd_TH.divmod(r, r, uth);
+    p.fd_TD.divmod(r, r, utd);
+    const int tw = (int)utw, th = (int)uth, td = (int)utd;
+    const int n = tl.n0 + (int)r, d = tl.d0 + td, h = tl.h0 + th, w = tl.w0 + tw;
     off = n * p.o_sn + d * p.o_sd + h * p.o_sh + w * p.o_sw;
     return row < p.rows_used && n < p.g.N && d < p.g.Do && h < p.g.Ho && w < p.g.Wo;
   }
@@ -142,6 +158,20 @@ static int launch_conv(const CUtensorMap& tmA, const CUtensorMap& tmB,
   }
   p.tiles_col = (p.g.Kout + BN - 1) / BN;
   p.num_tiles = p.tiles_col * p.tiles_w * p.tiles_h * p.tiles_d * p.tiles_nb;
+  {
+    const long long dmax = std::max({p.tiles_col, p.tiles_w, p.tiles_h, p.tiles_d, 128});
+    if ((long long)p.num_tiles * dmax >= (1ll << 32)) return -1;   // range of the fast divisions
+  }
+  p.fd_tiles_col = FastDiv((uint32_t)p.tiles_col);
+  p.fd_tiles_w = FastDiv((uint32_t)p.tiles_w);
+  p.fd_tiles_h = FastDiv((uint32_t)p.tiles_h);
+  p.fd_tiles_d = FastDiv((uint32_t)p.tiles_d);
+  p.fd_cblocks = FastDiv((uint32_t)p.cblocks);
+  p.fd_khw = FastDiv((uint32_t)(p.g.kh * p.g.kw));
+  p.fd_kw = FastDiv((uint32_t)p.g.kw);
+  p.fd_TW = FastDiv((uint32_t)p.TW);
+  p.fd_TH = FastDiv((uint32_t)p.TH);
+  p.fd_TD = FastDiv((uint32_t)p.TD);
   // few bricks, long reduction (the deep layers of a network on a small batch): split it
   p.epi.k_splits = lbhost::plan_splitk(offer, p.num_tiles, p.k_iters, BN);
   p.epi.sk_ws = offer.ws;

@@ -38,6 +38,7 @@ struct WgradParams {
   float alpha;
   float* dW;
   long long s_tap, s_k, s_c;            // output strides in elements
+  FastDiv fd_bw, fd_bh, fd_bd;          // brick decode without run-time divisions
 };
 
 struct WgradShared {
@@ -99,7 +100,9 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
   if (warp == 4) {
     // The whole warp walks the bricks: lane 0 owns the barrier protocol, and the
     // boxes of one stage go out from different lanes so that they enter the
-    // copy engine side by side instead of one after another.
+    // copy engine side by side instead of one after another.  What a lane loads is
+    // the same for every brick (which box, which tap, which channel block), so it is
+    // worked out once; per brick only the brick origin changes.
     uint32_t it = 0;
     bool ok = true;
     // slices this CTA loads per brick (the same for every brick)
@@ -107,24 +110,47 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     for (int gi = 0; gi < g_count; ++gi)
       nsl += min(p.spg, p.slices_total - (g_first + gi) * p.spg);
     const int ndy = p.BN == 32 ? 1 : p.BN / 64;
+    const int njobs = ndy + g_count * p.spg;
+    // this lane's jobs q = lane, lane + 32 (at most two: njobs <= 4 + 4 * 8)
+    struct Job { int kind; uint32_t dst; int c0, ow, oh, od; };   // kind 0 none, 1 dy box, 2 x slice
+    Job jobs[2];
+#pragma unroll
+    for (int jj = 0; jj < 2; ++jj) {
+      const int q = lane + 32 * jj;
+      Job jb = {0, 0u, 0, 0, 0, 0};
+      if (q < ndy) {
+        jb.kind = 1; jb.dst = (uint32_t)p.a_bytes + q * 8192u; jb.c0 = n0 + q * 64;
+      } else if (q < njobs) {
+        const int gi = (q - ndy) / p.spg, j = (q - ndy) - gi * p.spg;
+        const int sl = (g_first + gi) * p.spg + j;
+        if (sl < p.slices_total) {
+          const int tap = sl / p.cblocks;
+          const int ta = tap / (g.kh * g.kw), tb = (tap / g.kw) % g.kh, tc = tap % g.kw;
+          jb.kind = 2; jb.dst = gi * 16384u + j * (64u * p.Cb * 2u);
+          jb.c0 = (sl - tap * p.cblocks) * p.Cb;
+          jb.ow = tc * g.dw - g.pw; jb.oh = tb * g.dh - g.ph; jb.od = ta * g.dd - g.pd;
+        }
+      }
+      jobs[jj] = jb;
+    }
+    const uint32_t tx_bytes = (uint32_t)(p.rows_used * 2 * (nsl * p.Cb + p.BN));
+    RingPos rp;
     for (int b = split; b < p.bricks_total && ok; b += p.splits, ++it) {
-      int r = b;
-      const int bw = r % p.bricks_w; r /= p.bricks_w;
-      const int bh = r % p.bricks_h; r /= p.bricks_h;
-      const int bd = r % p.bricks_d; r /= p.bricks_d;
-      const int w0 = bw * p.TW, h0 = bh * p.TH, d0 = bd * p.TD, nn0 = r * p.TN;
-      const uint32_t s = it % S, ph = (it / S) & 1;
-      const uint32_t sA = smem_base + s * p.stage_bytes;
-      const uint32_t sB = sA + p.a_bytes;
-      const uint32_t bar = smem_u32(&sh.full[s]);
+      uint32_t r, bw, bh, bd, nb;
+      p.fd_bw.divmod((uint32_t)b, r, bw);
+      p.fd_bh.divmod(r, r, bh);
+      p.fd_bd.divmod(r, nb, bd);
+      const int w0 = bw * p.TW, h0 = bh * p.TH, d0 = bd * p.TD, nn0 = nb * p.TN;
+      const uint32_t sA = smem_base + rp.s * p.stage_bytes;
+      const uint32_t bar = smem_u32(&sh.full[rp.s]);
       int go = 1;
       if (lane == 0) {
-        if (!mbar_wait_bounded(smem_u32(&sh.empty[s]), ph ^ 1, abort_flag)) {
+        if (!mbar_wait_bounded(smem_u32(&sh.empty[rp.s]), rp.ph ^ 1, abort_flag)) {
           raise_status(status, abort_flag, kTimeoutStageEmpty);
           go = 0;
         } else {
           // every slice brings rows_used * Cb * 2 bytes, dy brings rows_used * BN * 2
-          mbar_expect_tx(bar, (uint32_t)(p.rows_used * 2 * (nsl * p.Cb + p.BN)));
+          mbar_expect_tx(bar, tx_bytes);
         }
       }
       go = __shfl_sync(0xffffffffu, go, 0);
@@ -132,23 +158,18 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
         ok = false;
         break;
       }
-      // job q < ndy: a box of dy; job q >= ndy: slice (q - ndy) of this CTA's groups
-      for (int q = lane; q < ndy + g_count * p.spg; q += 32) {
-        if (q < ndy) {
-          tma_load_5d(sB + q * 8192, &tmDy, bar, n0 + q * 64, w0, h0, d0, nn0);
-          continue;
+#pragma unroll
+      for (int jj = 0; jj < 2; ++jj) {
+        const Job& jb = jobs[jj];
+        if (jb.kind == 1) {
+          tma_load_5d(sA + jb.dst, &tmDy, bar, jb.c0, w0, h0, d0, nn0);
+        } else if (jb.kind == 2) {
+          tma_load_5d(sA + jb.dst, &tmX, bar, jb.c0, w0 * g.sw + jb.ow, h0 * g.sh + jb.oh,
+                      d0 * g.sd + jb.od, nn0);
         }
-        const int gi = (q - ndy) / p.spg, j = (q - ndy) - gi * p.spg;
-        const int sl = (g_first + gi) * p.spg + j;
-        if (sl >= p.slices_total) continue;
-        const int tap = sl / p.cblocks;
-        const int c0 = (sl - tap * p.cblocks) * p.Cb;
-        const int ta = tap / (g.kh * g.kw), tb = (tap / g.kw) % g.kh, tc = tap % g.kw;
-        tma_load_5d(sA + gi * 16384 + j * (64 * p.Cb * 2), &tmX, bar, c0,
-                    w0 * g.sw - g.pw + tc * g.dw, h0 * g.sh - g.ph + tb * g.dh,
-                    d0 * g.sd - g.pd + ta * g.dd, nn0);
       }
       __syncwarp();
+      rp.advance((uint32_t)S);
     }
     if (lane == 0) {
       if (!ok || *abort_flag) {
@@ -161,33 +182,44 @@ conv_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant
     }
   } else if (warp == 5) {
     if (lane == 0) {
+      // descriptors differ in the start-address field of the low word only; four MMAs per
+      // accumulator and stage, issued straight-line (see slab_issue_plane for why)
       const uint32_t idesc =
           make_idesc_f16(p.in_dtype == kBF16 ? 1u : 0u, 1, 1, 128, (uint32_t)p.BN);
-      const uint32_t a_lbo = 64u * p.Cb * 2u, a_sbo = 8u * p.Cb * 2u, a_adv = 16u * p.Cb * 2u;
+      const uint32_t a_lbo = 64u * p.Cb * 2u, a_sbo = 8u * p.Cb * 2u, a_adv = (16u * p.Cb * 2u) >> 4;
       const uint32_t b_row = (p.BN == 32) ? 64u : 128u;
-      const uint32_t b_lbo = 8192u, b_sbo = 8u * b_row, b_adv = 16u * b_row;
-      uint32_t it = 0;
+      const uint32_t b_lbo = 8192u, b_sbo = 8u * b_row, b_adv = (16u * b_row) >> 4;
+      const uint64_t a_desc = make_smem_desc(0, a_lbo, a_sbo, p.a_layout);
+      const uint64_t b_desc = make_smem_desc(0, b_lbo, b_sbo, p.b_layout);
+      const uint32_t a_lo0 = (uint32_t)a_desc, a_hi = (uint32_t)(a_desc >> 32);
+      const uint32_t b_lo0 = (uint32_t)b_desc, b_hi = (uint32_t)(b_desc >> 32);
+      const uint32_t stage_step = (uint32_t)p.stage_bytes >> 4;
+      const uint32_t a_base = a_lo0 + (smem_base >> 4);
+      const uint32_t b_base = b_lo0 + ((smem_base + (uint32_t)p.a_bytes) >> 4);
+      const uint32_t BNu = (uint32_t)p.BN;
+      uint32_t accum = 0;
       bool ok = true;
-      for (int b = split; b < p.bricks_total && ok; b += p.splits, ++it) {
-        const uint32_t s = it % S, ph = (it / S) & 1;
-        if (!mbar_wait_bounded(smem_u32(&sh.full[s]), ph, abort_flag)) {
+      RingPos rp;
+      for (int b = split; b < p.bricks_total && ok; b += p.splits) {
+        if (!mbar_wait_bounded(smem_u32(&sh.full[rp.s]), rp.ph, abort_flag)) {
           raise_status(status, abort_flag, kTimeoutTmaFull);
           ok = false;
           break;
         }
         tc_fence_after();
-        const uint32_t sA = smem_base + s * p.stage_bytes;
-        const uint32_t sB = sA + p.a_bytes;
-        for (int gi = 0; gi < g_count; ++gi) {
+        const uint32_t sa = a_base + rp.s * stage_step, sb = b_base + rp.s * stage_step;
 #pragma unroll
-          for (int kk = 0; kk < 4; ++kk) {
-            umma_f16(tmem_base + gi * p.BN,
-                     make_smem_desc(sA + gi * 16384 + kk * a_adv, a_lbo, a_sbo, p.a_layout),
-                     make_smem_desc(sB + kk * b_adv, b_lbo, b_sbo, p.b_layout), idesc,
-                     (it == 0 && kk == 0) ? 0u : 1u);
+        for (int gi = 0; gi < 4; ++gi) {
+          if (gi < g_count) {
+#pragma unroll
+            for (int kk = 0; kk < 4; ++kk)
+              umma_f16_lo(tmem_base + gi * BNu, sa + gi * 1024u + kk * a_adv, a_hi, sb + kk * b_adv,
+                          b_hi, idesc, kk == 0 ? accum : 1u);   // the first MMA of an accumulator overwrites
           }
         }
-        umma_commit(smem_u32(&sh.empty[s]));
+        accum = 1u;
+        umma_commit(smem_u32(&sh.empty[rp.s]));
+        rp.advance((uint32_t)S);
       }
       if (ok) umma_commit(smem_u32(&sh.done));
     }
@@ -291,6 +323,10 @@ int lb_conv_wgrad_tc(const void* x, const void* dy, float* dW, const int* geom,
   p.bricks_d = (g.Do + p.TD - 1) / p.TD;
   p.bricks_n = (g.N + p.TN - 1) / p.TN;
   p.bricks_total = p.bricks_w * p.bricks_h * p.bricks_d * p.bricks_n;
+  if ((long long)p.bricks_total * 256 >= (1ll << 32)) return -1;
+  p.fd_bw = FastDiv((uint32_t)p.bricks_w);
+  p.fd_bh = FastDiv((uint32_t)p.bricks_h);
+  p.fd_bd = FastDiv((uint32_t)p.bricks_d);
 
   const int base_ctas = p.group_sets * p.n_tiles;
   int splits = (2 * lbhost::sm_count() + base_ctas - 1) / base_ctas;

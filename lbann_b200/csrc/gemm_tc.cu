@@ -66,16 +66,21 @@ struct GemmPolicy {
   }
   __device__ static void mma(const Params& p, int, uint32_t sA, uint32_t sB, uint32_t tmem_acc,
                              uint32_t idesc, bool first) {
+    // K-major: 16 elements = 32 bytes along the swizzled row.
+    // MN-major: 16 k-rows of 128 bytes.
+    // The four descriptors of a stage differ in the start-address field of the low word.
+    const uint64_t a0 = p.a_mn ? make_smem_desc(0, 8192, 1024, kLayoutSw128)
+                               : make_smem_desc(0, 16, 1024, kLayoutSw128);
+    const uint64_t b0 = p.b_mn ? make_smem_desc(0, 8192, 1024, kLayoutSw128)
+                               : make_smem_desc(0, 16, 1024, kLayoutSw128);
+    const uint32_t a_hi = (uint32_t)(a0 >> 32), b_hi = (uint32_t)(b0 >> 32);
+    const uint32_t a_lo = (uint32_t)a0 + (sA >> 4), b_lo = (uint32_t)b0 + (sB >> 4);
+    const uint32_t a_step = p.a_mn ? (2048u >> 4) : (32u >> 4);
+    const uint32_t b_step = p.b_mn ? (2048u >> 4) : (32u >> 4);
 #pragma unroll
-    for (int kk = 0; kk < kBK / 16; ++kk) {
-      // K-major: 16 elements = 32 bytes along the swizzled row.
-      // MN-major: 16 k-rows of 128 bytes.
-      const uint64_t ad = p.a_mn ? make_smem_desc(sA + kk * 2048, 8192, 1024, kLayoutSw128)
-                                 : make_smem_desc(sA + kk * 32, 16, 1024, kLayoutSw128);
-      const uint64_t bd = p.b_mn ? make_smem_desc(sB + kk * 2048, 8192, 1024, kLayoutSw128)
-                                 : make_smem_desc(sB + kk * 32, 16, 1024, kLayoutSw128);
-      umma_f16(tmem_acc, ad, bd, idesc, (first && kk == 0) ? 0u : 1u);
-    }
+    for (int kk = 0; kk < kBK / 16; ++kk)
+      umma_f16_lo(tmem_acc, a_lo + kk * a_step, a_hi, b_lo + kk * b_step, b_hi, idesc,
+                  (first && kk == 0) ? 0u : 1u);
   }
   __device__ static bool row_addr(const Params& p, const Tile& tl, int row, long long& off) {
     const int m = tl.m0 + row;
