@@ -107,6 +107,31 @@ __device__ __forceinline__ void c8_unfold(int cr, int taps2, uint32_t slab, int 
 // back; the chunk left of the tile and chunks beyond W are zero-filled and supply the
 // padding along W, rows outside H / D likewise.  Pixels are 8 bytes (4 channels) or 16.
 // The filter, packed on the host as [K chunk of 8][32 rows][8], stays in shared memory.
+// A run of MMAs along K into one accumulator, straight-line for the step counts the first-layer
+// shapes have (a rolled loop costs the issuing thread ~100 cycles per MMA, the MMA itself 44).
+template <int KSTEPS>
+__device__ __forceinline__ void c8_issue_run(uint32_t acc, uint32_t ad, uint32_t a_hi, uint32_t bd,
+                                             uint32_t b_hi, uint32_t idesc, uint32_t a_step,
+                                             uint32_t b_step, uint32_t first) {
+#pragma unroll
+  for (int kk = 0; kk < KSTEPS; ++kk)
+    umma_f16_lo(acc, ad + kk * a_step, a_hi, bd + kk * b_step, b_hi, idesc, kk ? 1u : first);
+}
+__device__ __forceinline__ void c8_issue(int ksteps, uint32_t acc, uint32_t ad, uint32_t a_hi,
+                                         uint32_t bd, uint32_t b_hi, uint32_t idesc, uint32_t a_step,
+                                         uint32_t b_step, uint32_t first) {
+  switch (ksteps) {
+    case 3: c8_issue_run<3>(acc, ad, a_hi, bd, b_hi, idesc, a_step, b_step, first); break;
+    case 5: c8_issue_run<5>(acc, ad, a_hi, bd, b_hi, idesc, a_step, b_step, first); break;
+    case 7: c8_issue_run<7>(acc, ad, a_hi, bd, b_hi, idesc, a_step, b_step, first); break;
+    case 8: c8_issue_run<8>(acc, ad, a_hi, bd, b_hi, idesc, a_step, b_step, first); break;
+    case 14: c8_issue_run<14>(acc, ad, a_hi, bd, b_hi, idesc, a_step, b_step, first); break;
+    default:
+      for (int kk = 0; kk < ksteps; ++kk)
+        umma_f16_lo(acc, ad + kk * a_step, a_hi, bd + kk * b_step, b_hi, idesc, kk ? 1u : first);
+  }
+}
+
 constexpr int kC8MaxStages = 12;
 // Worker groups of four warps.  A group unfolds a tile and later runs its epilogue; with a
 // single warp per scheduler every dependent instruction shows its full latency, so the
@@ -134,7 +159,6 @@ struct C8FwdShared {
   uint64_t full[kC8MaxStages];
   uint64_t empty[kC8MaxStages];
   uint64_t a_ready[kC8Groups];
-  uint64_t a_free[kC8Groups];
   uint64_t tmem_full[kC8Groups];
   uint64_t tmem_empty[kC8Groups];
   uint32_t tmem_base;
@@ -166,7 +190,6 @@ conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const C8FwdParams p,
     }
     for (int a = 0; a < kC8Groups; ++a) {
       mbar_init(smem_u32(&sh.a_ready[a]), 4);
-      mbar_init(smem_u32(&sh.a_free[a]), 1);
       mbar_init(smem_u32(&sh.tmem_full[a]), 1);
       mbar_init(smem_u32(&sh.tmem_empty[a]), 4);
     }
@@ -268,14 +291,9 @@ conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const C8FwdParams p,
         uint32_t bd = b_lo0;
         const uint32_t tmem_acc = tmem_base + j * BN;
         constexpr uint32_t kAStep = (2 * 128) >> 4, kBStep = (2 * BN * 16) >> 4;
-        umma_f16_lo(tmem_acc, ad, a_hi, bd, b_hi, idesc, 0u);
-        int kk = 1;
-        for (; kk + 1 < ksteps; kk += 2) {          // two per round: half the loop overhead
-          umma_f16_lo(tmem_acc, ad + kk * kAStep, a_hi, bd + kk * kBStep, b_hi, idesc, 1u);
-          umma_f16_lo(tmem_acc, ad + (kk + 1) * kAStep, a_hi, bd + (kk + 1) * kBStep, b_hi, idesc, 1u);
-        }
-        if (kk < ksteps) umma_f16_lo(tmem_acc, ad + kk * kAStep, a_hi, bd + kk * kBStep, b_hi, idesc, 1u);
-        umma_commit(smem_u32(&sh.a_free[j]));
+        c8_issue(ksteps, tmem_acc, ad, a_hi, bd, b_hi, idesc, kAStep, kBStep, 0u);
+        // one commit tells the group both that its accumulator is complete and that its
+        // operand buffer may be overwritten (every barrier operation costs this thread ~80 cycles)
         umma_commit(smem_u32(&sh.tmem_full[j]));
       }
     }
@@ -299,9 +317,10 @@ conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const C8FwdParams p,
         const uint32_t s = rs, ph = rph;
         rs += (uint32_t)G;
         if (rs >= (uint32_t)S) { rs -= (uint32_t)S; rph ^= 1u; }
-        const uint32_t jph = use & 1;
         bool good = mbar_wait_bounded(smem_u32(&sh.full[s]), ph, abort_flag);
-        good = good && mbar_wait_bounded(smem_u32(&sh.a_free[j]), jph ^ 1, abort_flag);
+        // the MMAs of this group's previous tile have read the operand buffer
+        good = good && (use == 0 ||
+                        mbar_wait_bounded(smem_u32(&sh.tmem_full[j]), (use - 1) & 1, abort_flag));
         if (!__all_sync(0xffffffffu, good)) {
           if (lane == 0) raise_status(status, abort_flag, kTimeoutTmaFull);
           break;
@@ -513,13 +532,7 @@ conv_c8_wgrad_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_const
         for (int mt = 0; mt < m_tiles; ++mt) {
           const uint32_t ad = ad0 + (uint32_t)mt * ((16u * 128u) >> 4);
           const uint32_t acc = tmem_base + (uint32_t)mt * BNu;
-          umma_f16_lo(acc, ad, a_hi, bd0, b_hi, idesc, first);
-          int kk = 1;
-          for (; kk + 1 < k_steps; kk += 2) {
-            umma_f16_lo(acc, ad + kk * a_kstep, a_hi, bd0 + kk * b_kstep, b_hi, idesc, 1u);
-            umma_f16_lo(acc, ad + (kk + 1) * a_kstep, a_hi, bd0 + (kk + 1) * b_kstep, b_hi, idesc, 1u);
-          }
-          if (kk < k_steps) umma_f16_lo(acc, ad + kk * a_kstep, a_hi, bd0 + kk * b_kstep, b_hi, idesc, 1u);
+          c8_issue(k_steps, acc, ad, a_hi, bd0, b_hi, idesc, a_kstep, b_kstep, first);
         }
         first = 1u;
         umma_commit(smem_u32(&sh.empty[s]));
