@@ -232,3 +232,61 @@ def test_strided_and_dilated_convolution_gradients(case):
     scale = (ref.numel() / K) ** 0.5
     torch.testing.assert_close(wh.grad, wr.grad, rtol=2e-2, atol=4e-3 * scale)
     torch.testing.assert_close(bh.grad, br.grad, rtol=2e-2, atol=4e-3 * scale)
+
+
+# ------------------------------------------------------------- long rows, vector kernels
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("rows,cols", [(37, 4096), (300, 50304 // 8), (5, 2048 + 8)])
+def test_softmax_cross_entropy_long_rows(rows, cols, dtype):
+    """Vocabulary-sized rows take the one-pass 16-byte-load kernels."""
+    torch.manual_seed(7)
+    logits = (torch.randn(rows, cols, device="cuda") * 3).to(dtype).requires_grad_(True)
+    labels = torch.randint(0, cols, (rows,), device="cuda")
+    labels[1] = cols + 5                       # out of range: contributes nothing
+    loss = nn.softmax_cross_entropy(logits, labels)
+    lr = logits.detach().float().requires_grad_(True)
+    ok = labels < cols
+    ref = F.cross_entropy(lr, labels.clamp(max=cols - 1), reduction="none") * ok
+    torch.testing.assert_close(loss, ref, rtol=1e-3, atol=2e-3)
+    w = torch.rand(rows, device="cuda") + 0.5
+    (loss * w).sum().backward()
+    (ref * w).sum().backward()
+    assert native.consume_status() == 0
+    torch.testing.assert_close(logits.grad.float(), lr.grad, rtol=2e-2, atol=2e-3)
+
+
+@pytest.mark.parametrize("rows,cols", [(4096, 2048), (1000, 520), (33, 64), (7, 8)])
+def test_layer_norm_parameter_gradients_vector_kernel(rows, cols):
+    torch.manual_seed(8)
+    z = torch.randn(rows, cols, device="cuda").bfloat16().requires_grad_(True)
+    sh, bh = _handle(torch.rand(cols, device="cuda") + 0.5), _handle(torch.randn(cols, device="cuda"))
+    out = nn.layer_norm(z, cols, sh, bh, 1e-5)
+    zr = z.detach().float().requires_grad_(True)
+    sr, br = sh.master.detach().clone().requires_grad_(True), bh.master.detach().clone().requires_grad_(True)
+    ref = F.layer_norm(zr, (cols,), sr, br, 1e-5)
+    g = torch.randn_like(ref).bfloat16()
+    out.backward(g)
+    ref.backward(g.float())
+    assert native.consume_status() == 0
+    scale = rows ** 0.5
+    torch.testing.assert_close(sh.grad, sr.grad, rtol=3e-2, atol=2e-2 * scale)
+    torch.testing.assert_close(bh.grad, br.grad, rtol=3e-2, atol=2e-2 * scale)
+    torch.testing.assert_close(z.grad.float(), zr.grad, rtol=3e-2, atol=3e-2)
+
+
+@pytest.mark.parametrize("name", ["gelu", "gelu_tanh", "sigmoid", "tanh", "leaky_relu", "exp"])
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_unary_operators_on_16_bit_tensors(name, dtype):
+    torch.manual_seed(9)
+    x = (torch.randn(1 << 20, device="cuda")).to(dtype)
+    p0 = 0.1 if name == "leaky_relu" else 0.0
+    xa = x.clone().requires_grad_(True)
+    xr = x.float().requires_grad_(True)
+    y = ew.unary(name, xa, p0, 0.0)
+    ref = ew._CPU_UNARY[name](xr, p0, 0.0)
+    torch.testing.assert_close(y.float(), ref, rtol=1e-2, atol=1e-2)
+    g = torch.randn_like(ref).to(dtype)
+    y.backward(g)
+    ref.backward(g.float())
+    assert native.consume_status() == 0
+    torch.testing.assert_close(xa.grad.float(), xr.grad, rtol=2e-2, atol=2e-2)
