@@ -34,10 +34,15 @@ __device__ __forceinline__ void st8(T* p, const float (&f)[8]) {
   *reinterpret_cast<uint4*>(p) = q;
 }
 
+// `idx` (optional, max pooling): one byte per output element, dense [N][Do][Ho][Wo][C]: the
+// position of the first maximum in the window's scan order (kd, kh, kw nested) in bits 0-6
+// and "the maximum is positive" in bit 7.  The backward kernel of non-overlapping windows
+// then needs neither x nor y: it reads dy and these bytes (0.2 GB instead of 1.2 GB for
+// the first pooling layer of CosmoFlow).
 template <typename T>
 __global__ void pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, PoolGeom g,
                                 long long xs_n, long long xs_d, long long xs_h, long long xs_w,
-                                long long y_sn, long long total) {
+                                long long y_sn, long long total, uint8_t* __restrict__ idx) {
   const int cv = g.C / 8;
   const long long per_sample = (long long)g.Do * g.Ho * g.Wo * g.C;   // dense part of a sample
   for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
@@ -49,8 +54,9 @@ __global__ void pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, Pool
     const int od = r % g.Do; r /= g.Do;
     const int n = (int)r;
     float acc[8];
+    int arg[8];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) acc[j] = g.mode == 0 ? -INFINITY : 0.f;
+    for (int j = 0; j < 8; ++j) { acc[j] = g.mode == 0 ? -INFINITY : 0.f; arg[j] = 0; }
     int count = 0;
     for (int a = 0; a < g.kd; ++a) {
       const int id = od * g.sd - g.pd + a;
@@ -63,11 +69,27 @@ __global__ void pool_fwd_kernel(const T* __restrict__ x, T* __restrict__ y, Pool
           if (iw < 0 || iw >= g.W) continue;
           float f[8];
           ld8<T>(x + n * xs_n + id * xs_d + ih * xs_h + iw * xs_w + c8 * 8, f);
+          if (idx) {
+            const int pos = (a * g.kh + b) * g.kw + c;
 #pragma unroll
-          for (int j = 0; j < 8; ++j) acc[j] = g.mode == 0 ? fmaxf(acc[j], f[j]) : acc[j] + f[j];
+            for (int j = 0; j < 8; ++j)
+              if (f[j] > acc[j]) { acc[j] = f[j]; arg[j] = pos; }
+          } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) acc[j] = g.mode == 0 ? fmaxf(acc[j], f[j]) : acc[j] + f[j];
+          }
           ++count;
         }
       }
+    }
+    if (idx) {
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        lo |= (uint32_t)((arg[j] & 0x7f) | (acc[j] > 0.f ? 0x80 : 0)) << (8 * j);
+        hi |= (uint32_t)((arg[j + 4] & 0x7f) | (acc[j + 4] > 0.f ? 0x80 : 0)) << (8 * j);
+      }
+      *reinterpret_cast<uint2*>(idx + i * 8) = make_uint2(lo, hi);
     }
     if (g.mode == 1) {
       const float inv = 1.f / (g.kd * g.kh * g.kw);
@@ -169,6 +191,8 @@ extern "C" {
 // y and dx are dense NDHWC; x may be strided (xs = n, d, h, w strides in elements).
 int lb_pool_fwd_strided(const void* x, void* y, const int* geom, const long long* xs,
                         long long y_sn, int dtype, void* stream_);
+int lb_pool_fwd_idx(const void* x, void* y, void* idx, const int* geom, const long long* xs,
+                    long long y_sn, int dtype, void* stream_);
 int lb_pool_fwd(const void* x, void* y, const int* geom, const long long* xs, int dtype,
                 void* stream_) {
   return lb_pool_fwd_strided(x, y, geom, xs, 0, dtype, stream_);
@@ -177,20 +201,31 @@ int lb_pool_fwd(const void* x, void* y, const int* geom, const long long* xs, in
 // y_sn: elements between consecutive samples of y (0 = dense); a sample itself is dense.
 int lb_pool_fwd_strided(const void* x, void* y, const int* geom, const long long* xs,
                         long long y_sn, int dtype, void* stream_) {
+  return lb_pool_fwd_idx(x, y, nullptr, geom, xs, y_sn, dtype, stream_);
+}
+
+// Max pooling that also records where each maximum sits (see pool_fwd_kernel); idx: dense
+// bytes [N][Do][Ho][Wo][C], 8-byte aligned, windows of at most 128 positions.
+int lb_pool_fwd_idx(const void* x, void* y, void* idx, const int* geom, const long long* xs,
+                    long long y_sn, int dtype, void* stream_) {
   using namespace lb;
   PoolGeom g;
   memcpy(&g, geom, sizeof(g));
   if (g.C % 8) return -1;
+  if (idx && (g.mode != 0 || g.kd * g.kh * g.kw > 128 || (reinterpret_cast<uintptr_t>(idx) & 7)))
+    return -1;
   if (y_sn == 0) y_sn = (long long)g.Do * g.Ho * g.Wo * g.C;
   if (y_sn % 8 || (reinterpret_cast<uintptr_t>(y) & 15)) return -1;
   const long long total = (long long)g.N * g.Do * g.Ho * g.Wo * (g.C / 8);
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
   if (dtype == kBF16)
     pool_fwd_kernel<__nv_bfloat16><<<pool_grid(total), 256, 0, s>>>(
-        (const __nv_bfloat16*)x, (__nv_bfloat16*)y, g, xs[0], xs[1], xs[2], xs[3], y_sn, total);
+        (const __nv_bfloat16*)x, (__nv_bfloat16*)y, g, xs[0], xs[1], xs[2], xs[3], y_sn, total,
+        (uint8_t*)idx);
   else if (dtype == kF16)
     pool_fwd_kernel<__half><<<pool_grid(total), 256, 0, s>>>((const __half*)x, (__half*)y, g,
-                                                             xs[0], xs[1], xs[2], xs[3], y_sn, total);
+                                                             xs[0], xs[1], xs[2], xs[3], y_sn, total,
+                                                             (uint8_t*)idx);
   else
     return -1;
   return (int)cudaGetLastError();

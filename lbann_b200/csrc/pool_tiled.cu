@@ -81,6 +81,55 @@ __global__ void pool_bwd_tiled_kernel(const T* __restrict__ x, const T* __restri
   }
 }
 
+// The same from the positions recorded by the forward kernel (pool.cu: one byte per output
+// element, bits 0-6 the arg-max in scan order, bit 7 "maximum positive"): reads dy and the
+// bytes, writes dx once.
+template <typename T>
+__global__ void pool_bwd_tiled_idx_kernel(const uint8_t* __restrict__ idx, const T* __restrict__ dy,
+                                          T* __restrict__ dx, TiledPoolGeom g, int act,
+                                          float act_param, long long dx_sn, long long total) {
+  const int cv = g.C / 8;
+  const int Do = g.D / g.kd, Ho = g.H / g.kh, Wo = g.W / g.kw;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long r = i;
+    const int c8 = r % cv; r /= cv;
+    const int ow = r % Wo; r /= Wo;
+    const int oh = r % Ho; r /= Ho;
+    const int od = r % Do; r /= Do;
+    const long long n = r;
+    float gy[8];
+    int arg[8];
+    {
+      const uint4 q = *reinterpret_cast<const uint4*>(dy + i * 8);
+      const T* e = reinterpret_cast<const T*>(&q);
+      const uint2 b = *reinterpret_cast<const uint2*>(idx + i * 8);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const uint32_t v = ((j < 4 ? b.x : b.y) >> (8 * (j & 3))) & 0xffu;
+        arg[j] = (int)(v & 0x7fu);
+        float f = 1.f;
+        if (act == kActRelu) f = (v & 0x80u) ? 1.f : 0.f;
+        else if (act == kActLeaky) f = (v & 0x80u) ? 1.f : act_param;
+        gy[j] = to_f32<T>(e[j]) * f;
+      }
+    }
+    const long long base = n * dx_sn + ((((long long)od * g.kd) * g.H + (long long)oh * g.kh) * g.W +
+                                        (long long)ow * g.kw) * g.C + c8 * 8;
+    int pos = 0;
+    for (int a = 0; a < g.kd; ++a)
+      for (int b = 0; b < g.kh; ++b)
+        for (int c = 0; c < g.kw; ++c, ++pos) {
+          const long long off = base + (((long long)a * g.H + b) * g.W + c) * g.C;
+          uint4 q;
+          T* e = reinterpret_cast<T*>(&q);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) e[j] = from_f32<T>(arg[j] == pos ? gy[j] : 0.f);
+          *reinterpret_cast<uint4*>(dx + off) = q;
+        }
+  }
+}
+
 }  // namespace lb
 
 extern "C" {
@@ -115,6 +164,32 @@ int lb_pool_bwd_tiled_strided(const void* x, const void* dy, void* dx, const int
   else if (dtype == kF16)
     pool_bwd_tiled_kernel<__half><<<grid, 256, 0, s>>>((const __half*)x, (const __half*)dy,
                                                        (__half*)dx, g, act, act_param, dx_sn, total);
+  else
+    return -1;
+  return (int)cudaGetLastError();
+}
+
+// idx: the bytes written by lb_pool_fwd_idx for the same geometry.
+int lb_pool_bwd_tiled_idx(const void* idx, const void* dy, void* dx, const int* geom, int act,
+                          float act_param, long long dx_sn, int dtype, void* stream_) {
+  using namespace lb;
+  TiledPoolGeom g;
+  memcpy(&g, geom, sizeof(g));
+  if (g.C % 8 || g.D % g.kd || g.H % g.kh || g.W % g.kw || g.kd * g.kh * g.kw > 128) return -1;
+  if (dx_sn == 0) dx_sn = (long long)g.D * g.H * g.W * g.C;
+  if (dx_sn % 8 || (reinterpret_cast<uintptr_t>(dx) & 15) || (reinterpret_cast<uintptr_t>(idx) & 7)) return -1;
+  const long long total = (long long)g.N * (g.D / g.kd) * (g.H / g.kh) * (g.W / g.kw) * (g.C / 8);
+  if (total <= 0) return 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  const long long blocks = (total + 255) / 256;
+  const long long cap = (long long)lbhost::sm_count() * 32;
+  const int grid = (int)(blocks < cap ? blocks : cap);
+  if (dtype == kBF16)
+    pool_bwd_tiled_idx_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
+        (const uint8_t*)idx, (const __nv_bfloat16*)dy, (__nv_bfloat16*)dx, g, act, act_param, dx_sn, total);
+  else if (dtype == kF16)
+    pool_bwd_tiled_idx_kernel<__half><<<grid, 256, 0, s>>>((const uint8_t*)idx, (const __half*)dy,
+                                                           (__half*)dx, g, act, act_param, dx_sn, total);
   else
     return -1;
   return (int)cudaGetLastError();

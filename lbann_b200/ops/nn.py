@@ -36,6 +36,11 @@ def _lib():
         lib.lb_pool_fwd.argtypes = [c_void_p, c_void_p, P(c_int), P(c_ll), c_int, c_void_p]
         lib.lb_pool_fwd_strided.restype = c_int
         lib.lb_pool_fwd_strided.argtypes = [c_void_p, c_void_p, P(c_int), P(c_ll), c_ll, c_int, c_void_p]
+        lib.lb_pool_fwd_idx.restype = c_int
+        lib.lb_pool_fwd_idx.argtypes = [c_void_p, c_void_p, c_void_p, P(c_int), P(c_ll), c_ll, c_int, c_void_p]
+        lib.lb_pool_bwd_tiled_idx.restype = c_int
+        lib.lb_pool_bwd_tiled_idx.argtypes = [c_void_p, c_void_p, c_void_p, P(c_int), c_int, c_float,
+                                              c_ll, c_int, c_void_p]
         lib.lb_pool_bwd_tiled_strided.restype = c_int
         lib.lb_pool_bwd_tiled_strided.argtypes = [c_void_p, c_void_p, c_void_p, P(c_int), c_int, c_float,
                                                   c_ll, c_int, c_void_p]
@@ -593,26 +598,52 @@ class _Pool(torch.autograd.Function):
             y = torch.empty((N, Do, Ho, Wo, C), dtype=x.dtype, device=x.device)
         geom = (c_int * 18)(N, D, H, W, C, Do, Ho, Wo, *ksize, *pad, *stride, mode)
         xs = (c_ll * 4)(x_cl.stride(0), x_cl.stride(1), x_cl.stride(2), x_cl.stride(3))
-        rc = _lib().lb_pool_fwd_strided(x_cl.data_ptr(), y.data_ptr(), geom, xs, y.stride(0),
-                                        native.dtype_code(x.dtype), native.stream_ptr())
-        native.check(rc, "lb_pool_fwd_strided")
+        # non-overlapping max pooling: record where the maxima sit (a byte per output), so
+        # that backward reads dy and those bytes instead of scanning x again
+        tiled = (mode == 0 and ksize == stride and pad == (0, 0, 0) and D % ksize[0] == 0
+                 and H % ksize[1] == 0 and W % ksize[2] == 0 and ksize[0] * ksize[1] * ksize[2] <= 128)
+        idx = None
+        if tiled and x.requires_grad and os.environ.get("LBANN_POOL_RESCAN", "") in ("", "0"):
+            idx = torch.empty((N, Do, Ho, Wo, C), dtype=torch.uint8, device=x.device)
+        rc = _lib().lb_pool_fwd_idx(x_cl.data_ptr(), y.data_ptr(), native.ptr(idx), geom, xs, y.stride(0),
+                                    native.dtype_code(x.dtype), native.stream_ptr())
+        native.check(rc, "lb_pool_fwd_idx")
         native.count_launch()
-        ctx.save_for_backward(x_cl)
+        if idx is not None:
+            ctx.save_for_backward(idx)
+            ctx.x_shape = tuple(x_cl.shape)
+        else:
+            ctx.save_for_backward(x_cl)
+            ctx.x_shape = None
+        ctx.x_dtype = x.dtype
         ctx.meta = (geom, ndim)
         return _from_cl(y, ndim)
 
     @staticmethod
     def backward(ctx, dy):
-        (x_cl,) = ctx.saved_tensors
         geom, ndim = ctx.meta
         dy_cl = _cl_view(dy)
         if not dy_cl.is_contiguous():
             dy_cl = dy_cl.contiguous()
         ksize, pad, stride, mode = ctx.win
+        nothing = (None,) * 8
+        if ctx.x_shape is not None:
+            (idx,) = ctx.saved_tensors
+            N, D, H, W, C = ctx.x_shape
+            dx = ctx.dx_alloc(ctx.x_shape, ctx.x_dtype) if ctx.dx_alloc is not None else None
+            if dx is None or not _sample_dense(dx):
+                dx = torch.empty(ctx.x_shape, dtype=ctx.x_dtype, device=dy.device)
+            tg = (c_int * 8)(N, D, H, W, C, *ksize)
+            rc = _lib().lb_pool_bwd_tiled_idx(idx.data_ptr(), dy_cl.data_ptr(), dx.data_ptr(), tg,
+                                              int(ctx.bwd_act[0]), float(ctx.bwd_act[1]), dx.stride(0),
+                                              native.dtype_code(ctx.x_dtype), native.stream_ptr())
+            native.check(rc, "lb_pool_bwd_tiled_idx")
+            native.count_launch()
+            return (_from_cl(dx, ndim),) + nothing
+        (x_cl,) = ctx.saved_tensors
         N, D, H, W, C = x_cl.shape
         tiled = (mode == 0 and ksize == stride and pad == (0, 0, 0) and x_cl.is_contiguous()
                  and D % ksize[0] == 0 and H % ksize[1] == 0 and W % ksize[2] == 0)
-        nothing = (None,) * 8
         if tiled:
             dx = ctx.dx_alloc(tuple(x_cl.shape), x_cl.dtype) if ctx.dx_alloc is not None else None
             if dx is None or not _sample_dense(dx):
