@@ -137,7 +137,7 @@ constexpr int kC8MaxStages = 12;
 // single warp per scheduler every dependent instruction shows its full latency, so the
 // groups take tiles in turn (tile i belongs to group i % G, with its own operand buffer
 // and accumulator) and overlap one another's latencies.
-constexpr int kC8Groups = 3;
+constexpr int kC8Groups = 4;
 constexpr int kC8Threads = 64 + 128 * kC8Groups;
 
 struct C8FwdParams {
@@ -168,7 +168,7 @@ struct C8FwdShared {
 __global__ void __launch_bounds__(kC8Threads, 1)
 conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const C8FwdParams p, int* status) {
   constexpr int BN = 32;
-  const int G = p.groups;                        // worker groups in this launch: 2 or 3
+  const int G = p.groups;                        // worker groups in this launch: 2 to 4
   const int kProducerWarp = 4 * G, kMmaWarp = 4 * G + 1;
   constexpr int kTmemCols = 128;
   extern __shared__ uint8_t smem_raw[];
@@ -643,11 +643,11 @@ int lb_conv_c8_fwd(const void* x, const void* w, void* y, const float* bias, con
   const int nchunks = (p.slab_lead + 128 + 2 + chunk_px - 1) / chunk_px;
   p.slab_row_bytes = nchunks * 128;
   p.stage_bytes = p.taps2 * p.slab_row_bytes;
-  // three worker groups when their operand buffers leave room for a few slab stages
+  // as many worker groups as leave room for a few slab stages beside their operand buffers
   p.groups = kC8Groups;
   int fixed = p.groups * 16 * p.mb_pad * 128 + p.filter_bytes;
-  if ((224 * 1024 - fixed) / p.stage_bytes < 3) {
-    p.groups = 2;
+  while (p.groups > 2 && (224 * 1024 - fixed) / p.stage_bytes < 3) {
+    --p.groups;
     fixed = p.groups * 16 * p.mb_pad * 128 + p.filter_bytes;
   }
   p.stages = (224 * 1024 - fixed) / p.stage_bytes;
@@ -720,8 +720,8 @@ int lb_conv_c8_wgrad(const void* x, const void* dy, float* dW, const int* geom,
   p.stage_bytes = p.slab_bytes + kWgBrick * p.BN * 2;
   p.groups = kC8Groups;
   int a_total = p.groups * 16 * p.mb_pad * 128;
-  if ((224 * 1024 - a_total) / p.stage_bytes < 3) {
-    p.groups = 2;
+  while (p.groups > 2 && (224 * 1024 - a_total) / p.stage_bytes < 3) {
+    --p.groups;
     a_total = p.groups * 16 * p.mb_pad * 128;
   }
   p.stages = (224 * 1024 - a_total) / p.stage_bytes;
