@@ -301,9 +301,6 @@ int lb_conv_wgrad_tc(const void* x, const void* dy, float* dW, const int* geom,
   p.n_tiles = (g.Kout + p.BN - 1) / p.BN;
   p.G = 512 / p.BN < 4 ? 512 / p.BN : 4;
   if (p.G > p.groups_total) p.G = p.groups_total;
-  // at least three stages in flight: with two, every brick waits out a full TMA round trip
-  // (~2 us) while a brick's MMAs take a few hundred cycles
-  while (p.G > 1 && 200 * 1024 / (p.G * 16384 + 64 * p.BN * 2) < 3) --p.G;
   p.group_sets = (p.groups_total + p.G - 1) / p.G;
   p.a_layout = p.Cb == 64 ? kLayoutSw128 : (p.Cb == 32 ? kLayoutSw64 : kLayoutSw32);
   p.b_layout = p.BN == 32 ? kLayoutSw64 : kLayoutSw128;

@@ -81,6 +81,68 @@ __global__ void pool_bwd_tiled_kernel(const T* __restrict__ x, const T* __restri
   }
 }
 
+// Forward of the same windows: a thread owns one window and 8 channels, issues all of the
+// window's 16-byte loads before the first comparison (a 2x2x2 window keeps eight loads in
+// flight per thread) and records the position of the first maximum (bits 0-6) and whether it
+// is positive (bit 7) in one byte per output element.  y may leave a gap between samples.
+template <typename T, int KD, int KH, int KW>
+__global__ void pool_fwd_tiled_kernel(const T* __restrict__ x, T* __restrict__ y,
+                                      uint8_t* __restrict__ idx, TiledPoolGeom g, long long xs_n,
+                                      long long xs_d, long long xs_h, long long xs_w,
+                                      long long y_sn, long long total) {
+  const int cv = g.C / 8;
+  const int Do = g.D / KD, Ho = g.H / KH, Wo = g.W / KW;
+  const long long per_sample = (long long)Do * Ho * Wo * g.C;
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+       i += (long long)gridDim.x * blockDim.x) {
+    long long r = i;
+    const int c8 = r % cv; r /= cv;
+    const int ow = r % Wo; r /= Wo;
+    const int oh = r % Ho; r /= Ho;
+    const int od = r % Do; r /= Do;
+    const long long n = r;
+    const T* base = x + n * xs_n + (long long)od * KD * xs_d + (long long)oh * KH * xs_h +
+                    (long long)ow * KW * xs_w + c8 * 8;
+    uint4 q[KD * KH * KW];
+#pragma unroll
+    for (int a = 0; a < KD; ++a)
+#pragma unroll
+      for (int b = 0; b < KH; ++b)
+#pragma unroll
+        for (int c = 0; c < KW; ++c)
+          q[(a * KH + b) * KW + c] = *reinterpret_cast<const uint4*>(base + a * xs_d + b * xs_h + c * xs_w);
+    float best[8];
+    int arg[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { best[j] = -INFINITY; arg[j] = 0; }
+#pragma unroll
+    for (int pos = 0; pos < KD * KH * KW; ++pos) {
+      const T* e = reinterpret_cast<const T*>(&q[pos]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float v = to_f32<T>(e[j]);
+        const bool gt = v > best[j];
+        best[j] = gt ? v : best[j];
+        arg[j] = gt ? pos : arg[j];
+      }
+    }
+    uint4 o;
+    T* oe = reinterpret_cast<T*>(&o);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) oe[j] = from_f32<T>(best[j]);
+    *reinterpret_cast<uint4*>(y + n * y_sn + (i * 8 - n * per_sample)) = o;
+    if (idx) {
+      uint32_t lo = 0, hi = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        lo |= (uint32_t)(arg[j] | (best[j] > 0.f ? 0x80 : 0)) << (8 * j);
+        hi |= (uint32_t)(arg[j + 4] | (best[j + 4] > 0.f ? 0x80 : 0)) << (8 * j);
+      }
+      *reinterpret_cast<uint2*>(idx + i * 8) = make_uint2(lo, hi);
+    }
+  }
+}
+
 // The same from the positions recorded by the forward kernel (pool.cu: one byte per output
 // element, bits 0-6 the arg-max in scan order, bit 7 "maximum positive"): reads dy and the
 // bytes, writes dx once.
@@ -169,7 +231,39 @@ int lb_pool_bwd_tiled_strided(const void* x, const void* dy, void* dx, const int
   return (int)cudaGetLastError();
 }
 
-// idx: the bytes written by lb_pool_fwd_idx for the same geometry.
+// Forward max pooling over non-overlapping 2x2x2 / 1x2x2 / 2x2 windows (the shapes of every
+// pooling layer of CosmoFlow, U-Net and the ResNet stem are covered by 2 and 3).  Returns -2
+// for other windows: the caller then uses the general kernel.  x strided (xs: n, d, h, w in
+// elements), y dense per sample with y_sn elements between samples, idx optional.
+int lb_pool_fwd_tiled(const void* x, void* y, void* idx, const int* geom, const long long* xs,
+                      long long y_sn, int dtype, void* stream_) {
+  using namespace lb;
+  TiledPoolGeom g;
+  memcpy(&g, geom, sizeof(g));
+  if (g.C % 8 || g.D % g.kd || g.H % g.kh || g.W % g.kw) return -2;
+  const bool k222 = g.kd == 2 && g.kh == 2 && g.kw == 2, k122 = g.kd == 1 && g.kh == 2 && g.kw == 2;
+  if (!k222 && !k122) return -2;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || xs[0] % 8 || xs[1] % 8 || xs[2] % 8 || xs[3] % 8) return -2;
+  const long long per_sample = (long long)(g.D / g.kd) * (g.H / g.kh) * (g.W / g.kw) * g.C;
+  if (y_sn == 0) y_sn = per_sample;
+  if (y_sn % 8 || (reinterpret_cast<uintptr_t>(y) & 15) || (reinterpret_cast<uintptr_t>(idx) & 7)) return -1;
+  const long long total = (long long)g.N * per_sample / 8;
+  if (total <= 0) return 0;
+  cudaStream_t s = reinterpret_cast<cudaStream_t>(stream_);
+  const long long blocks = (total + 255) / 256;
+  const long long cap = (long long)lbhost::sm_count() * 32;
+  const int grid = (int)(blocks < cap ? blocks : cap);
+#define LB_POOL_FWD(T, KD)                                                                         \
+  pool_fwd_tiled_kernel<T, KD, 2, 2><<<grid, 256, 0, s>>>((const T*)x, (T*)y, (uint8_t*)idx, g, xs[0], \
+                                                          xs[1], xs[2], xs[3], y_sn, total)
+  if (dtype == kBF16) { if (k222) LB_POOL_FWD(__nv_bfloat16, 2); else LB_POOL_FWD(__nv_bfloat16, 1); }
+  else if (dtype == kF16) { if (k222) LB_POOL_FWD(__half, 2); else LB_POOL_FWD(__half, 1); }
+  else return -2;
+#undef LB_POOL_FWD
+  return (int)cudaGetLastError();
+}
+
+// idx: the bytes written by lb_pool_fwd_idx / lb_pool_fwd_tiled for the same geometry.
 int lb_pool_bwd_tiled_idx(const void* idx, const void* dy, void* dx, const int* geom, int act,
                           float act_param, long long dx_sn, int dtype, void* stream_) {
   using namespace lb;

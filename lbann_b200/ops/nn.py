@@ -38,6 +38,8 @@ def _lib():
         lib.lb_pool_fwd_strided.argtypes = [c_void_p, c_void_p, P(c_int), P(c_ll), c_ll, c_int, c_void_p]
         lib.lb_pool_fwd_idx.restype = c_int
         lib.lb_pool_fwd_idx.argtypes = [c_void_p, c_void_p, c_void_p, P(c_int), P(c_ll), c_ll, c_int, c_void_p]
+        lib.lb_pool_fwd_tiled.restype = c_int
+        lib.lb_pool_fwd_tiled.argtypes = [c_void_p, c_void_p, c_void_p, P(c_int), P(c_ll), c_ll, c_int, c_void_p]
         lib.lb_pool_bwd_tiled_idx.restype = c_int
         lib.lb_pool_bwd_tiled_idx.argtypes = [c_void_p, c_void_p, c_void_p, P(c_int), c_int, c_float,
                                               c_ll, c_int, c_void_p]
@@ -605,9 +607,15 @@ class _Pool(torch.autograd.Function):
         idx = None
         if tiled and x.requires_grad and os.environ.get("LBANN_POOL_RESCAN", "") in ("", "0"):
             idx = torch.empty((N, Do, Ho, Wo, C), dtype=torch.uint8, device=x.device)
-        rc = _lib().lb_pool_fwd_idx(x_cl.data_ptr(), y.data_ptr(), native.ptr(idx), geom, xs, y.stride(0),
-                                    native.dtype_code(x.dtype), native.stream_ptr())
-        native.check(rc, "lb_pool_fwd_idx")
+        rc = -2
+        if tiled:       # the window-per-thread kernel (2x2x2 and 2x2 windows); -2: not one of those
+            tg = (c_int * 8)(N, D, H, W, C, *ksize)
+            rc = _lib().lb_pool_fwd_tiled(x_cl.data_ptr(), y.data_ptr(), native.ptr(idx), tg, xs, y.stride(0),
+                                          native.dtype_code(x.dtype), native.stream_ptr())
+        if rc == -2:
+            rc = _lib().lb_pool_fwd_idx(x_cl.data_ptr(), y.data_ptr(), native.ptr(idx), geom, xs, y.stride(0),
+                                        native.dtype_code(x.dtype), native.stream_ptr())
+        native.check(rc, "lb_pool_fwd")
         native.count_launch()
         if idx is not None:
             ctx.save_for_backward(idx)
