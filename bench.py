@@ -431,6 +431,7 @@ def ours(args):
         "region_ms": [round(v, 3) for v in m["region_ms"]],
         "device_status": m["device_status"], "clocks": clocks,
         "distconv": halo, "sharded_optimizer": sharded,
+        "cpu_cores_bound": len(getattr(trainer, "cpu_binding", None) or ()) or None,
     }
     if phase is not None and rank == 0:
         # LBANN_PHASE_TIMING=1: (device ms, host ms) per phase of the step, on stderr

@@ -48,6 +48,9 @@ class ExecTrainer:
         self.device = torch.device(device) if device is not None else pick_device(local_rank, disable_cuda)
         if self.device.type == "cuda":
             torch.cuda.set_device(self.device)
+            # run (and first-touch pinned buffers) on the cores next to this GPU
+            from ..utils.affinity import bind_to_gpu
+            self.cpu_binding = bind_to_gpu(self.device.index if self.device.index is not None else 0)
         self.comm = comm or LbannComm(procs_per_trainer or o.get_int("procs_per_trainer"),
                                       grid_height or o.get_int("trainer_grid_height") or 1,
                                       device=self.device)

@@ -116,3 +116,21 @@ def test_saved_model_is_loaded_for_inference(tmp_path):
     opts.reset()
     np.testing.assert_allclose(got, want, rtol=1e-5, atol=1e-6)
     assert labels.tolist() == want.argmax(1).tolist()
+
+
+def test_cpu_binding_helpers(tmp_path, monkeypatch):
+    """The core list of a GPU's NUMA node is parsed from sysfs; binding is skipped when the
+    information is missing or disabled."""
+    from lbann_b200.utils import affinity
+    assert affinity.parse_cpulist("0-3,8,10-11\n") == {0, 1, 2, 3, 8, 10, 11}
+    assert affinity.parse_cpulist("") == set()
+    dev = tmp_path / "0000:1b:00.0"
+    dev.mkdir()
+    (dev / "local_cpulist").write_text("0-1,4\n")
+    assert affinity.local_cpus_of("0000:1b:00.0", str(tmp_path)) == {0, 1, 4}
+    assert affinity.local_cpus_of("0000:ff:00.0", str(tmp_path)) == set()
+    monkeypatch.setattr(affinity, "gpu_pci_address", lambda i: "0000:1b:00.0")
+    # fewer than four usable cores: nothing is changed
+    assert affinity.bind_to_gpu(0, str(tmp_path)) is None
+    monkeypatch.setenv("LBANN_DISABLE_NUMA_BIND", "1")
+    assert affinity.bind_to_gpu(0, str(tmp_path)) is None
