@@ -837,7 +837,15 @@ class ExecModel:
         """Copy a step's input into the graph's input buffer with a copy KERNEL (a device
         memcpy would queue behind the next mini-batch's upload on the copy engines: measured
         +1.4 ms per step end to end)."""
-        if v.data_ptr() != static.data_ptr():
+        if v.data_ptr() == static.data_ptr():
+            return
+        if (v.dtype == static.dtype and v.is_contiguous() and static.is_contiguous()
+                and v.is_cuda and v.element_size() in (2, 4) and v.shape == static.shape):
+            # ``copy_`` between dense tensors of one dtype is a device memcpy; an element-wise
+            # kernel on the bit pattern is the same copy on the SMs (25 us for 69 MB)
+            bits = torch.int16 if v.element_size() == 2 else torch.int32
+            torch.bitwise_or(v.view(bits), 0, out=static.view(bits))
+        else:
             static.copy_(v)
 
     def _train_step_graph(self, inputs, gmb, offset):
