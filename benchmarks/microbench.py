@@ -97,12 +97,23 @@ def case_conv(a, timer):
     fwd_bytes = 2.0 * px * (max(C, 8) + K)
     out = []
 
+    act = native.ACT_LEAKY if a.act else native.ACT_NONE
+
     def fwd():
-        return nn.convolution(x, wh, None, (ks,) * 3, (pad,) * 3, (1,) * 3, (1,) * 3,
-                              act=native.ACT_LEAKY if a.act else native.ACT_NONE, act_param=0.3)
+        # --pool: the 2x2x2 max pooling behind a first-layer convolution, as a second kernel
+        # ("separate") or inside the convolution kernel ("fused")
+        fuse = nn.PoolFusion() if a.pool == "fused" else None
+        y = nn.convolution(x, wh, None, (ks,) * 3, (pad,) * 3, (1,) * 3, (1,) * 3, act=act, act_param=0.3,
+                           skip_act_grad=a.pool != "none", fuse_pool=fuse)
+        if a.pool == "separate" or (fuse is not None and not fuse.done):
+            y = nn.pooling(y, 2, 0, 2, "max", act, 0.3)
+        return y
 
     ms, mn = timer.run(fwd)
-    out.append(_report("conv_fwd", [N, C, K, S, ks], ms, mn, flops, fwd_bytes))
+    if a.pool != "none":
+        fwd_bytes = 2.0 * px * (max(C, 8) + K / 8) + px * K / 8
+    out.append(_report("conv_fwd" if a.pool == "none" else f"conv_fwd+pool({a.pool})",
+                       [N, C, K, S, ks], ms, mn, flops, fwd_bytes))
     if a.bwd:
         y = fwd()
         dy = torch.randn_like(y)
@@ -300,6 +311,7 @@ def main(argv=None):
     ap.add_argument("--size", type=int, default=64)
     ap.add_argument("--ksize", type=int, default=3)
     ap.add_argument("--act", action="store_true")
+    ap.add_argument("--pool", default="none", choices=["none", "separate", "fused"])
     ap.add_argument("--bwd", action="store_true")
     ap.add_argument("--opt", default="adam")
     ap.add_argument("--helpers", type=int, default=6, help="copying CTAs of the staged all-gather")

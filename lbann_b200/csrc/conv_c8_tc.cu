@@ -34,15 +34,18 @@ struct C8Geom {
 // kd * kh slab rows) and store them as 16-byte K chunks, 128 B apart, of the operand row.
 // All loads of a pixel are issued before the first store so that their latencies overlap;
 // TAPS2 > 0 fixes kd * kh at compile time (full unrolling), TAPS2 = 0 is the generic loop.
-template <int CR, int TAPS2>
+// RPITCH > 0 (with TAPS2 = 9, a 3 x 3 tap plane): the slab has RPITCH rows per depth plane
+// instead of 3, i.e. it is a window of a larger slab shared by several tiles.
+template <int CR, int TAPS2, int RPITCH = 0>
 __device__ __forceinline__ void c8_unfold_pixel(uint32_t src_px, uint32_t dst, int taps2,
                                                 int row_bytes) {
   if constexpr (TAPS2 > 0 && CR == 4) {
     uint2 v[TAPS2 * 3 + 1];
 #pragma unroll
     for (int r = 0; r < TAPS2; ++r) {
+      const int row = RPITCH > 0 ? (r / 3) * RPITCH + (r % 3) : r;
 #pragma unroll
-      for (int c = 0; c < 3; ++c) v[r * 3 + c] = lds64(src_px + r * row_bytes + c * 8);
+      for (int c = 0; c < 3; ++c) v[r * 3 + c] = lds64(src_px + row * row_bytes + c * 8);
     }
     v[TAPS2 * 3] = make_uint2(0u, 0u);
 #pragma unroll
@@ -372,6 +375,316 @@ conv_c8_fwd_kernel(const __grid_constant__ CUtensorMap tmX, const C8FwdParams p,
   }
 }
 
+// ------------------------------------------------- forward + 2 x 2 x 2 max pooling in one pass
+// The first layer's output is the largest tensor of the network (128^3 x 32 channels per
+// sample in CosmoFlow) and its only reader is the pooling layer behind the activation.
+// This kernel never writes it: a CTA takes SUPER-TILES of four row tiles, (plane 2dp or
+// 2dp + 1) x (row 2hp or 2hp + 1), one per worker group.  One TMA box brings the 4 x 4-row
+// slab that the four tiles share; each group unfolds its own 3 x 3-row window of it, the
+// MMA thread fills four accumulators, and every group then pools 8 of the 32 channels over
+// all four accumulators (the 2 x 2 window in depth and height comes from the four tiles,
+// the one along W from the neighbouring TMEM lane through a shuffle).  Written: the pooled
+// tensor, and one byte per pooled element with the arg-max position in scan order
+// (bits 0-6) and "maximum positive" (bit 7) - the layout pool_bwd_tiled_idx_kernel reads,
+// so the backward pass is the same as for the separate pooling kernel.  Two sets of
+// accumulators alternate between super-tiles.
+// 4-channel pixels, 3 x 3 x 3 filter only.
+struct C8PoolParams {
+  C8Geom g;
+  int tiles_w, num_super, Hp, Dp, Wp;
+  int mb_pad, ksteps;
+  int slab_row_bytes, slab_lead, stage_bytes, stages, filter_bytes;
+  int in_dtype, out_dtype, act;
+  float act_param;
+  const void* w;
+  const float* bias;
+  void* y;
+  uint8_t* idx;
+  long long o_sn, o_sd, o_sh, o_sw;   // strides of the pooled output, in elements
+  FastDiv fd_tiles_w, fd_Hp, fd_Dp;
+};
+
+struct C8PoolShared {
+  uint64_t full[kC8MaxStages];
+  uint64_t empty[kC8MaxStages];
+  uint64_t a_ready[4];
+  uint64_t tmem_full[2][4];
+  uint64_t tmem_empty[2];
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ void tmem_ld_32x8(uint32_t taddr, uint32_t (&r)[8]) {
+  asm volatile("tcgen05.ld.sync.aligned.32x32b.x8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]),
+                 "=r"(r[7])
+               : "r"(taddr));
+}
+
+// The maximum is taken on the fp32 accumulators (3 instructions per value); bias,
+// activation and the rounding to 16 bits are monotonic (leaky slope >= 0), so they are applied
+// to the eight winners only and give the same pooled values as pooling the rounded tensor.
+// Where two values of a window differ only below the 16-bit rounding, the arg-max recorded is
+// the larger fp32 value rather than the first in scan order.
+template <typename T, int ACT>
+__device__ __forceinline__ void c8_pool_epilogue(const C8PoolParams& p, uint32_t taddr, int col0,
+                                                 int lane, bool in_range, long long y_off,
+                                                 long long idx_off) {
+  uint32_t r[4][8];
+#pragma unroll
+  for (int a = 0; a < 4; ++a) tmem_ld_32x8(taddr + a * 32, r[a]);
+  tmem_ld_wait();
+  const int par = lane & 1;
+  float best[8];
+  int pos[8];
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    best[c] = -INFINITY;
+    pos[c] = 0;
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const float v = __uint_as_float(r[a][c]);
+      const bool gt = v > best[c];
+      best[c] = gt ? v : best[c];
+      pos[c] = gt ? 2 * a + par : pos[c];
+    }
+  }
+  // the neighbouring pixel along W: the larger value wins, on equal values the earlier
+  // position in scan order
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    const float ov = __shfl_xor_sync(0xffffffffu, best[c], 1);
+    const int op = __shfl_xor_sync(0xffffffffu, pos[c], 1);
+    const bool take = ov > best[c] || (ov == best[c] && op < pos[c]);
+    best[c] = take ? ov : best[c];
+    pos[c] = take ? op : pos[c];
+  }
+  if (!in_range) return;
+  if (p.bias) {
+    const float4 b0 = __ldg(reinterpret_cast<const float4*>(p.bias + col0));
+    const float4 b1 = __ldg(reinterpret_cast<const float4*>(p.bias + col0 + 4));
+    best[0] += b0.x; best[1] += b0.y; best[2] += b0.z; best[3] += b0.w;
+    best[4] += b1.x; best[5] += b1.y; best[6] += b1.z; best[7] += b1.w;
+  }
+  uint4 o;
+  T* oe = reinterpret_cast<T*>(&o);
+  uint32_t lo = 0, hi = 0;
+#pragma unroll
+  for (int c = 0; c < 8; ++c) {
+    float v = best[c];
+    if (ACT == kActRelu) v = fmaxf(v, 0.f);
+    else if (ACT == kActLeaky) v = v > 0.f ? v : v * p.act_param;
+    oe[c] = from_f32<T>(v);
+    const uint32_t byte = (uint32_t)pos[c] | (to_f32<T>(oe[c]) > 0.f ? 0x80u : 0u);
+    if (c < 4) lo |= byte << (8 * c);
+    else hi |= byte << (8 * (c - 4));
+  }
+  if (par == 0) *reinterpret_cast<uint4*>(reinterpret_cast<T*>(p.y) + y_off) = o;
+  else *reinterpret_cast<uint2*>(p.idx + idx_off) = make_uint2(lo, hi);
+}
+
+template <typename T>
+__device__ __forceinline__ void c8_pool_epilogue_act(const C8PoolParams& p, uint32_t taddr, int col0,
+                                                     int lane, bool in_range, long long y_off,
+                                                     long long idx_off) {
+  if (p.act == kActLeaky) c8_pool_epilogue<T, kActLeaky>(p, taddr, col0, lane, in_range, y_off, idx_off);
+  else if (p.act == kActRelu) c8_pool_epilogue<T, kActRelu>(p, taddr, col0, lane, in_range, y_off, idx_off);
+  else c8_pool_epilogue<T, kActNone>(p, taddr, col0, lane, in_range, y_off, idx_off);
+}
+
+constexpr int kC8PoolThreads = 64 + 128 * 4;
+
+__global__ void __launch_bounds__(kC8PoolThreads, 1)
+conv_c8_fwd_pool_kernel(const __grid_constant__ CUtensorMap tmX, const C8PoolParams p, int* status) {
+  constexpr int BN = 32;
+  constexpr int G = 4;
+  constexpr int kProducerWarp = 4 * G, kMmaWarp = 4 * G + 1;
+  constexpr int kTmemCols = 256;                 // two sets of four 32-column accumulators
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ C8PoolShared sh;
+  const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+  const uint32_t a_bytes = 16u * p.mb_pad * 128u;
+  const uint32_t s_a0 = smem_base;
+  const uint32_t s_filter = smem_base + G * a_bytes;
+  const uint32_t s_stage0 = s_filter + p.filter_bytes;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  volatile int* abort_flag = &sh.abort_flag;
+  const int S = p.stages;
+  const C8Geom& g = p.g;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < S; ++s) {
+      mbar_init(smem_u32(&sh.full[s]), 1);
+      mbar_init(smem_u32(&sh.empty[s]), 4 * G);   // one arrive per unfolding warp
+    }
+    for (int a = 0; a < G; ++a) {
+      mbar_init(smem_u32(&sh.a_ready[a]), 4);
+      mbar_init(smem_u32(&sh.tmem_full[0][a]), 1);
+      mbar_init(smem_u32(&sh.tmem_full[1][a]), 1);
+    }
+    mbar_init(smem_u32(&sh.tmem_empty[0]), 4 * G);
+    mbar_init(smem_u32(&sh.tmem_empty[1]), 4 * G);
+    sh.abort_flag = 0;
+    mbar_fence_init();
+  }
+  if (warp == kProducerWarp && lane == 0) tma_prefetch_desc(&tmX);
+  if (warp == kMmaWarp) {
+    tmem_alloc(smem_u32(&sh.tmem_base), kTmemCols);
+    tmem_relinquish();
+  }
+  if (warp < 4 * G) {
+    uint4* az = reinterpret_cast<uint4*>(smem_raw + (s_a0 - smem_u32(smem_raw)));
+    for (uint32_t i = threadIdx.x; i < G * a_bytes / 16; i += 128 * G) az[i] = make_uint4(0, 0, 0, 0);
+    uint4* fz = reinterpret_cast<uint4*>(smem_raw + (s_filter - smem_u32(smem_raw)));
+    const uint4* fw = reinterpret_cast<const uint4*>(p.w);
+    for (uint32_t i = threadIdx.x; i < (uint32_t)p.filter_bytes / 16; i += 128 * G) fz[i] = fw[i];
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = sh.tmem_base;
+
+  if (warp == kProducerWarp) {
+    if (lane == 0) {
+      uint32_t it = 0;
+      bool ok = true;
+      RingPos rp;
+      for (int q = blockIdx.x; q < p.num_super; q += gridDim.x, ++it) {
+        const uint32_t s = rp.s;
+        if (!mbar_wait_bounded(smem_u32(&sh.empty[s]), rp.ph ^ 1, abort_flag)) {
+          raise_status(status, abort_flag, kTimeoutStageEmpty);
+          ok = false;
+          break;
+        }
+        rp.advance((uint32_t)S);
+        uint32_t r, tw, hp, dp, n;
+        p.fd_tiles_w.divmod((uint32_t)q, r, tw);
+        p.fd_Hp.divmod(r, r, hp);
+        p.fd_Dp.divmod(r, n, dp);
+        const uint32_t bar = smem_u32(&sh.full[s]);
+        mbar_expect_tx(bar, (uint32_t)p.stage_bytes);
+        // 16 pixels of 8 bytes per 128-byte chunk; the chunk left of the tile carries the
+        // padding along W, rows / planes outside the tensor are zero-filled
+        tma_load_5d(s_stage0 + s * p.stage_bytes, &tmX, bar, 0, (int)tw * 8 - 1,
+                    2 * (int)hp - g.ph, 2 * (int)dp - g.pd, (int)n);
+      }
+      if (!ok || *abort_flag) {
+        const uint32_t pending = it < (uint32_t)S ? it : (uint32_t)S;
+        for (uint32_t j = 0; j < pending; ++j) {
+          const uint32_t qq = it - 1 - j;
+          mbar_wait_budget_only(smem_u32(&sh.full[qq % S]), (qq / S) & 1);
+        }
+      }
+    }
+  } else if (warp == kMmaWarp) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc_f16(p.in_dtype == kBF16 ? 1u : 0u, 0, 0, 128, BN);
+      const uint64_t a_desc0 = make_smem_desc(0, 128, p.mb_pad * 128, kLayoutNone);
+      const uint64_t b_desc0 = make_smem_desc(s_filter, BN * 16, 128, kLayoutNone);
+      const uint32_t a_hi = (uint32_t)(a_desc0 >> 32), b_hi = (uint32_t)(b_desc0 >> 32);
+      const uint32_t a_lo0 = (uint32_t)a_desc0 + (s_a0 >> 4), b_lo0 = (uint32_t)b_desc0;
+      const uint32_t a_buf_step = a_bytes >> 4;
+      constexpr uint32_t kAStep = (2 * 128) >> 4, kBStep = (2 * BN * 16) >> 4;
+      const int ksteps = p.ksteps;
+      bool ok = true;
+      uint32_t k = 0;
+      for (int q = blockIdx.x; q < p.num_super && ok; q += gridDim.x, ++k) {
+        const uint32_t set = k & 1u, u = k >> 1;
+        if (!mbar_wait_bounded(smem_u32(&sh.tmem_empty[set]), (u & 1u) ^ 1u, abort_flag)) {
+          raise_status(status, abort_flag, kTimeoutTmemEmpty);
+          break;
+        }
+#pragma unroll
+        for (int j = 0; j < G; ++j) {
+          if (!mbar_wait_bounded(smem_u32(&sh.a_ready[j]), k & 1u, abort_flag)) {
+            raise_status(status, abort_flag, kTimeoutTmaFull);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          c8_issue(ksteps, tmem_base + set * (G * BN) + j * BN, a_lo0 + j * a_buf_step, a_hi, b_lo0,
+                   b_hi, idesc, kAStep, kBStep, 0u);
+          umma_commit(smem_u32(&sh.tmem_full[set][j]));
+        }
+      }
+    }
+  } else {
+    const int group = warp >> 2;                    // sub-tile: plane offset group >> 1, row offset group & 1
+    const int wq = warp & 3;
+    const int px = wq * 32 + lane;
+    const uint32_t dst = s_a0 + group * a_bytes + (px >> 3) * (p.mb_pad * 128) + (px & 7) * 16;
+    const uint32_t sub_off = (uint32_t)(((group >> 1) * 4 + (group & 1)) * p.slab_row_bytes) +
+                             (uint32_t)(p.slab_lead + px) * 8u;
+    const int col0 = group * 8;
+    RingPos rp;
+    for (uint32_t k = 0;; ++k) {
+      const long long ql = (long long)blockIdx.x + (long long)k * gridDim.x;
+      const bool have = ql < p.num_super;
+      if (have) {
+        const uint32_t s = rp.s, ph = rp.ph;
+        rp.advance((uint32_t)S);
+        bool good = mbar_wait_bounded(smem_u32(&sh.full[s]), ph, abort_flag);
+        // the MMAs of this group's previous tile have read its operand buffer
+        good = good && (k == 0 || mbar_wait_bounded(smem_u32(&sh.tmem_full[(k - 1) & 1u][group]),
+                                                    ((k - 1) >> 1) & 1u, abort_flag));
+        if (!__all_sync(0xffffffffu, good)) {
+          if (lane == 0) raise_status(status, abort_flag, kTimeoutTmaFull);
+          break;
+        }
+        c8_unfold_pixel<4, 9, 4>(s_stage0 + s * p.stage_bytes + sub_off, dst, 9, p.slab_row_bytes);
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) {
+          mbar_arrive(smem_u32(&sh.a_ready[group]));
+          mbar_arrive(smem_u32(&sh.empty[s]));
+        }
+      }
+      if (k >= 1) {
+        // ---- pool the previous super-tile: 8 channels of all four accumulators -----------
+        const uint32_t kp = k - 1, set = kp & 1u, par = (kp >> 1) & 1u;
+        bool landed = true;
+#pragma unroll
+        for (int a = 0; a < G; ++a)
+          landed = landed && mbar_wait_bounded(smem_u32(&sh.tmem_full[set][a]), par, abort_flag);
+        if (!__all_sync(0xffffffffu, landed)) {
+          if (lane == 0) raise_status(status, abort_flag, kTimeoutTmemFull);
+          break;
+        }
+        tc_fence_after();
+        if (col0 < g.Kout) {
+          const uint32_t qp = (uint32_t)(ql - gridDim.x);
+          uint32_t r, tw, hp, dp, n;
+          p.fd_tiles_w.divmod(qp, r, tw);
+          p.fd_Hp.divmod(r, r, hp);
+          p.fd_Dp.divmod(r, n, dp);
+          const int w = (int)tw * 128 + px;
+          const int wp = w >> 1;
+          const long long y_off = (long long)n * p.o_sn + (long long)dp * p.o_sd +
+                                  (long long)hp * p.o_sh + (long long)wp * p.o_sw + col0;
+          const long long idx_off =
+              ((((long long)n * p.Dp + dp) * p.Hp + hp) * p.Wp + wp) * g.Kout + col0;
+          const uint32_t taddr = tmem_base + set * (G * BN) + col0 + (static_cast<uint32_t>(wq * 32) << 16);
+          if (p.out_dtype == kBF16)
+            c8_pool_epilogue_act<__nv_bfloat16>(p, taddr, col0, lane, w < g.W, y_off, idx_off);
+          else
+            c8_pool_epilogue_act<__half>(p, taddr, col0, lane, w < g.W, y_off, idx_off);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(smem_u32(&sh.tmem_empty[set]));
+      }
+      if (!have) break;
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == kMmaWarp) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
 // ------------------------------------------------------------------------- wgrad
 // dW[tap][k][c] = sum over pixels of x[pixel + tap][c] * dy[pixel][k], as a GEMM with
 // M = (tap, channel), N = output channel, K = pixel.  A tcgen05.mma costs ~104 cycles for any
@@ -685,6 +998,76 @@ int lb_conv_c8_fwd(const void* x, const void* w, void* y, const float* bias, con
   }
   const int grid = p.num_tiles < lbhost::sm_count() ? p.num_tiles : lbhost::sm_count();
   conv_c8_fwd_kernel<<<grid, 64 + 128 * p.groups, smem, stream>>>(tmX, p, lbhost::status_word());
+  return (int)cudaGetLastError();
+}
+
+// Convolution (3 x 3 x 3, 4-channel pixels) + bias + activation + 2 x 2 x 2 max pooling,
+// stride 2, in one kernel.  x, w, geom, xs as for lb_conv_c8_fwd (xs[3] must be 4).
+// y: pooled output [N][Do/2][H/2][W/2][Kout] with element strides ys; idx: one byte per
+// pooled element, contiguous, in the layout of lb_pool_fwd_tiled.  Returns -2 when the
+// shape is not covered (the caller then runs the two kernels separately).
+int lb_conv_c8_fwd_pool(const void* x, const void* w, void* y, void* idx, const float* bias,
+                        const int* geom, const long long* xs, const long long* ys, int in_dtype,
+                        int out_dtype, int act, float act_param, void* stream_) {
+  using namespace lb;
+  cudaStream_t stream = reinterpret_cast<cudaStream_t>(stream_);
+  C8PoolParams p;
+  memcpy(&p.g, geom, sizeof(C8Geom));
+  const C8Geom& g = p.g;
+  if (g.Kout > 32 || g.Kout % 8) return -2;
+  if (xs[3] != 4 || g.kd != 3 || g.kh != 3 || g.ph != 1) return -2;
+  if (g.W % 16 || g.H % 2 || g.Do % 2) return -2;
+  if (out_dtype != kF16 && out_dtype != kBF16) return -2;
+  if (act != kActNone && act != kActRelu && !(act == kActLeaky && act_param >= 0.f)) return -2;
+  if (bias && (reinterpret_cast<uintptr_t>(bias) & 15)) return -2;
+  if ((reinterpret_cast<uintptr_t>(x) & 15) || (reinterpret_cast<uintptr_t>(w) & 15) ||
+      (reinterpret_cast<uintptr_t>(y) & 15) || (reinterpret_cast<uintptr_t>(idx) & 7))
+    return -1;
+  if (ys[0] % 8 || ys[1] % 8 || ys[2] % 8 || ys[3] % 8) return -2;
+  const int chunk_px = 16;
+  const int kchunks = (27 * 4 + 7) / 8;
+  p.ksteps = (kchunks + 1) / 2;                      // 7
+  p.mb_pad = 16;
+  p.filter_bytes = (2 * p.ksteps * 32 * 16 + 1023) & ~1023;
+  p.slab_lead = chunk_px - 1;
+  const int nchunks = (p.slab_lead + 128 + 2 + chunk_px - 1) / chunk_px;
+  p.slab_row_bytes = nchunks * 128;
+  p.stage_bytes = 16 * p.slab_row_bytes;             // 4 planes x 4 rows
+  const int fixed = 4 * 16 * p.mb_pad * 128 + p.filter_bytes;
+  p.stages = (224 * 1024 - fixed) / p.stage_bytes;
+  if (p.stages > kC8MaxStages) p.stages = kC8MaxStages;
+  if (p.stages < 2) return -2;
+  p.tiles_w = (g.W + 127) / 128;
+  p.Hp = g.H / 2; p.Dp = g.Do / 2; p.Wp = g.W / 2;
+  const long long num_super = (long long)p.tiles_w * p.Hp * p.Dp * g.N;
+  {
+    const long long dmax = std::max(std::max(p.tiles_w, p.Hp), p.Dp);
+    if (num_super * dmax >= (1ll << 32) || num_super >= (1ll << 31)) return -2;
+  }
+  p.num_super = (int)num_super;
+  if (p.num_super <= 0) return 0;
+  p.fd_tiles_w = FastDiv((uint32_t)p.tiles_w);
+  p.fd_Hp = FastDiv((uint32_t)p.Hp);
+  p.fd_Dp = FastDiv((uint32_t)p.Dp);
+  p.in_dtype = in_dtype; p.out_dtype = out_dtype; p.act = act; p.act_param = act_param;
+  p.w = w; p.bias = bias; p.y = y; p.idx = static_cast<uint8_t*>(idx);
+  p.o_sn = ys[0]; p.o_sd = ys[1]; p.o_sh = ys[2]; p.o_sw = ys[3];
+  CUtensorMap tmX;
+  {
+    uint64_t dims[5] = {16, (uint64_t)(g.W / chunk_px), (uint64_t)g.H, (uint64_t)g.D,
+                        (uint64_t)g.N};
+    uint64_t strides[4] = {128, (uint64_t)xs[2] * 2, (uint64_t)xs[1] * 2, (uint64_t)xs[0] * 2};
+    uint32_t box[5] = {16, (uint32_t)nchunks, 4, 4, 1};
+    if (!lbhost::encode_tmap(&tmX, kI64, 5, x, dims, strides, box, nullptr, 0)) return -1;
+  }
+  const int smem = fixed + p.stages * p.stage_bytes + 1024;
+  static int configured = 0;
+  if (configured < smem) {
+    cudaFuncSetAttribute(conv_c8_fwd_pool_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    configured = smem;
+  }
+  const int grid = p.num_super < lbhost::sm_count() ? p.num_super : lbhost::sm_count();
+  conv_c8_fwd_pool_kernel<<<grid, kC8PoolThreads, smem, stream>>>(tmX, p, lbhost::status_word());
   return (int)cudaGetLastError();
 }
 

@@ -132,6 +132,7 @@ class KFAC(SGDTrainingAlgorithm):
     # ---------------------------------------------------------------- set-up
     def _setup(self, model):
         for l in model.layers:
+            l.fuse_pool_layer = None          # the blocks need every layer's own output
             if l.type == "batch_normalization":
                 if l.name not in self.disable_layers and l.scale.has_optimizer() and l.bias.has_optimizer() \
                         and not getattr(l, "fused_into_parent", False):

@@ -144,11 +144,18 @@ class Convolution(_ConvBase):
     def forward(self, xs, training):
         x = self.cast_in(xs[0])
         dc = self.model.distconv
+        pool = getattr(self, "fuse_pool_layer", None)
+        fuse = None
+        if pool is not None and (dc is None or dc.enabled(self) == dc.enabled(pool)):
+            fuse = nn.PoolFusion()
         if dc is not None and dc.enabled(self):
-            return [dc.convolution(self, x)]
-        y = nn.convolution(x, self.w.handle, None if self.b is None else self.b.handle, self.ksize,
-                           self.pad, self.stride, self.dil, self.groups, self.fused_act[0],
-                           self.fused_act[1], getattr(self, "skip_act_grad", False))
+            y = dc.convolution(self, x, fuse, pool)
+        else:
+            y = nn.convolution(x, self.w.handle, None if self.b is None else self.b.handle, self.ksize,
+                               self.pad, self.stride, self.dil, self.groups, self.fused_act[0],
+                               self.fused_act[1], getattr(self, "skip_act_grad", False), fuse)
+        if pool is not None:
+            pool.input_is_pooled = bool(fuse is not None and fuse.done)
         return [y]
 
 

@@ -243,6 +243,10 @@ class Pooling(ExecLayer):
         return [(d[0],) + sp]
 
     def forward(self, xs, training):
+        if getattr(self, "input_is_pooled", False):
+            # the producing first-layer convolution ran this pooling inside its own kernel
+            self.input_is_pooled = False
+            return [xs[0]]
         x = self.cast_in(xs[0])
         dc = self.model.distconv
         if dc is not None and dc.enabled(self):

@@ -328,8 +328,18 @@ class ExecModel:
             if (l.type == "convolution" and len(c.children) == 1 and c.name not in protected
                     and c.children[0].type == "pooling" and c.children[0].mode == "max"
                     and l.cout % 8 == 0):
-                c.children[0].bwd_act = act
+                pool = c.children[0]
+                pool.bwd_act = act
                 l.skip_act_grad = True
+                # a first-layer convolution (<= 4 channels, 3^3 filter) followed by 2^3 / stride-2
+                # max pooling runs both in one kernel where the shapes allow (ops/nn.py)
+                hinted = {getattr(x, "hint_layer", None) for x in self.layers}
+                if (l.nd == 3 and l.cin <= 4 and tuple(l.ksize) == (3, 3, 3)
+                        and tuple(l.stride) == (1, 1, 1) and tuple(l.dil) == (1, 1, 1)
+                        and tuple(pool.k) == (2, 2, 2) and tuple(pool.stride) == (2, 2, 2)
+                        and tuple(pool.pad) == (0, 0, 0) and pool.name not in protected
+                        and pool.name not in hinted):
+                    l.fuse_pool_layer = pool
 
     def _fuse_softmax_cross_entropy(self):
         """softmax over channels -> cross-entropy with integer labels: the softmax layer

@@ -115,6 +115,9 @@ def _lib():
         lib.lb_conv_c8_fwd.restype = c_int
         lib.lb_conv_c8_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, P(c_int), P(c_ll),
                                        P(c_ll), c_int, c_int, c_int, c_float, c_void_p]
+        lib.lb_conv_c8_fwd_pool.restype = c_int
+        lib.lb_conv_c8_fwd_pool.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, P(c_int),
+                                            P(c_ll), P(c_ll), c_int, c_int, c_int, c_float, c_void_p]
         lib.lb_conv_c8_wgrad.restype = c_int
         lib.lb_conv_c8_wgrad.argtypes = [c_void_p, c_void_p, c_void_p, P(c_int), P(c_ll), P(c_ll),
                                          c_ll, c_ll, c_ll, c_int, c_int, c_float, c_void_p]
@@ -492,11 +495,122 @@ class _ConvC8(torch.autograd.Function):
         return (dx,) + (None,) * 9
 
 
+class PoolFusion:
+    """A request to run the 2 x 2 x 2 max pooling that follows a first-layer convolution (and
+    its folded activation) inside the convolution kernel.  ``out_alloc`` as for ``_Pool``;
+    ``done`` tells the caller whether the returned tensor is already pooled."""
+
+    def __init__(self, out_alloc=None):
+        self.out_alloc = out_alloc
+        self.done = False
+
+
+class _ConvC8Pool(torch.autograd.Function):
+    """First-layer convolution + activation + 2 x 2 x 2 max pooling (stride 2) in one kernel
+    (csrc/conv_c8_tc.cu, conv_c8_fwd_pool_kernel): the full-resolution activation is never
+    written.  Backward expands the pooled gradient with the recorded arg-max bytes (the
+    separate pooling layer's kernel) and feeds the first-layer filter-gradient kernel."""
+
+    @staticmethod
+    def forward(ctx, x, w_leaf, b_leaf, wh, bh, pad, act, act_p, out_alloc):
+        ndim = x.dim()
+        x_in = _cl_view(x)
+        Cin = x_in.shape[-1]
+        x_cl = F.pad(x_in, (0, 4 - Cin)) if Cin != 4 else x_in
+        if not x_cl.is_contiguous():
+            x_cl = x_cl.contiguous()
+        Kout = wh.master.shape[0]
+
+        def pack():
+            w = wh.master.detach().reshape(Kout, Cin, 27).permute(0, 2, 1)
+            w = F.pad(w, (0, 4 - Cin)).reshape(Kout, -1)
+            kpad = (w.shape[1] + 15) // 16 * 16
+            w = F.pad(w, (0, kpad - w.shape[1], 0, 32 - Kout))
+            return w.reshape(32, kpad // 8, 8).permute(1, 0, 2).contiguous().to(x.dtype)
+
+        wt = wh.packed("c8fwd", x.dtype, pack)
+        N, D, H, W, _ = x_cl.shape
+        Do = D + 2 * pad[0] - 2
+        shape = (N, Do // 2, H // 2, W // 2, Kout)
+        y = out_alloc(shape, x.dtype) if out_alloc is not None else None
+        if y is None or not _sample_dense(y):
+            y = torch.empty(shape, dtype=x.dtype, device=x.device)
+        idx = torch.empty(shape, dtype=torch.uint8, device=x.device)
+        geom = (c_int * 10)(N, D, H, W, Kout, 3, 3, pad[0], pad[1], Do)
+        xs = (c_ll * 4)(x_cl.stride(0), x_cl.stride(1), x_cl.stride(2), x_cl.stride(3))
+        ys = (c_ll * 4)(y.stride(0), y.stride(1), y.stride(2), y.stride(3))
+        bias = bh.master.detach() if bh is not None else None
+        native.check(_lib().lb_conv_c8_fwd_pool(x_cl.data_ptr(), wt.data_ptr(), y.data_ptr(),
+                                                idx.data_ptr(), native.ptr(bias), geom, xs, ys,
+                                                native.dtype_code(x.dtype), native.dtype_code(x.dtype),
+                                                int(act), float(act_p), native.stream_ptr()),
+                     "lb_conv_c8_fwd_pool")
+        native.count_launch()
+        ctx.save_for_backward(x_cl, idx)
+        ctx.meta = (wh, bh, pad, act, act_p, ndim, Kout, Cin, geom, xs, (N, Do, H, W, Kout))
+        return _from_cl(y, ndim)
+
+    @staticmethod
+    def backward(ctx, dy):
+        x_cl, idx = ctx.saved_tensors
+        wh, bh, pad, act, act_p, ndim, Kout, Cin, geom, xs, full = ctx.meta
+        dyp = _cl_view(dy)
+        if not dyp.is_contiguous():
+            dyp = dyp.contiguous()
+        N, Do, H, W, _ = full
+        # gradient of pooling and activation at full resolution
+        dy_cl = torch.empty(full, dtype=dy.dtype, device=dy.device)
+        tg = (c_int * 8)(N, Do, H, W, Kout, 2, 2, 2)
+        native.check(_lib().lb_pool_bwd_tiled_idx(idx.data_ptr(), dyp.data_ptr(), dy_cl.data_ptr(), tg,
+                                                  int(act), float(act_p), dy_cl.stride(0),
+                                                  native.dtype_code(dy.dtype), native.stream_ptr()),
+                     "lb_pool_bwd_tiled_idx")
+        native.count_launch()
+        dx = None
+        if ctx.needs_input_grad[0]:
+            ksize = (3, 3, 3)
+
+            def pack_bwd():
+                w = F.pad(wh.master.detach().reshape(Kout, Cin, -1), (0, 0, 0, 8 - Cin))
+                return pack_filter(w.reshape(Kout, 8, *ksize), dy.dtype, for_dgrad=True)
+            wt = wh.packed("dgrad", dy.dtype, pack_bwd)
+            bpad = tuple(k - 1 - p for k, p in zip(ksize, pad))
+            D = x_cl.shape[1]
+            dx_cl = conv_fwd(dy_cl, wt, ksize, pad=bpad, stride=1, out_dims=(D, H, W))
+            dx = _from_cl(dx_cl[..., :Cin], ndim)
+        if wh.grad is not None:
+            ys = (c_ll * 4)(dy_cl.stride(0), dy_cl.stride(1), dy_cl.stride(2), dy_cl.stride(3))
+            native.check(_lib().lb_conv_c8_wgrad(x_cl.data_ptr(), dy_cl.data_ptr(),
+                                                 wh.grad.data_ptr(), geom, xs, ys, 1, Cin * 27,
+                                                 27, Cin, native.dtype_code(x_cl.dtype), 1.0,
+                                                 native.stream_ptr()), "lb_conv_c8_wgrad")
+            native.count_launch()
+            wh.mark_ready()
+        if bh is not None and bh.grad is not None:
+            bh.grad.add_(column_sums(dy_cl.reshape(-1, Kout)))
+            bh.mark_ready()
+        return (dx,) + (None,) * 8
+
+
+def _c8_pool_ok(x, Cin, Kout, k3, p3) -> bool:
+    """Shapes the fused convolution + pooling kernel covers: 4-channel pixels, 3 x 3 x 3
+    filter, even output extents."""
+    if os.environ.get("LBANN_DISABLE_CONV_POOL_FUSION", "") not in ("", "0"):
+        return False
+    D, H, W = x.shape[2:]
+    Do = D + 2 * p3[0] - 2
+    return (Cin <= 4 and tuple(k3) == (3, 3, 3) and p3[1] == 1 and W % 16 == 0 and H % 2 == 0
+            and Do % 2 == 0 and Do > 0 and x.dtype in (torch.float16, torch.bfloat16))
+
+
 def convolution(x, wh: WeightHandle, bh: Optional[WeightHandle], ksize, pad, stride, dilation,
                 groups: int = 1, act: int = native.ACT_NONE, act_param: float = 0.0,
-                skip_act_grad: bool = False):
+                skip_act_grad: bool = False, fuse_pool: Optional["PoolFusion"] = None):
     """N-d convolution on a logical [N, C, spatial...] tensor; kernel Kout x C/groups x k...
-    ``skip_act_grad``: the consumer applies the fused activation's gradient itself."""
+    ``skip_act_grad``: the consumer applies the fused activation's gradient itself.
+    ``fuse_pool``: the consumer is a 2 x 2 x 2 max pooling with stride 2; where the
+    first-layer kernel covers the shape the pooled tensor is returned and
+    ``fuse_pool.done`` is set."""
     nsp = x.dim() - 2
     if _native_ok(x) and groups == 1 and act in (native.ACT_NONE, native.ACT_RELU, native.ACT_LEAKY):
         k3, p3, s3, d3 = norm3(ksize, 1), norm3(pad, 0), norm3(stride, 1), norm3(dilation, 1)
@@ -506,6 +620,10 @@ def convolution(x, wh: WeightHandle, bh: Optional[WeightHandle], ksize, pad, str
                 and x.shape[-1] % 8 == 0
                 and p3[0] in (0, (k3[0] - 1) // 2) and k3[0] % 2 == 1 and 2 * p3[1] == k3[1] - 1
                 and wh.grad is not None and wh.grad.is_contiguous()):
+            if fuse_pool is not None and x.dim() == 5 and _c8_pool_ok(x, Cin, Kout, k3, p3):
+                fuse_pool.done = True
+                return _ConvC8Pool.apply(x, wh.master, bh.master if bh is not None else None, wh, bh,
+                                         p3, act, float(act_param), fuse_pool.out_alloc)
             return _ConvC8.apply(x, wh.master, bh.master if bh is not None else None, wh, bh, k3,
                                  p3, act, float(act_param), bool(skip_act_grad))
         return _Conv.apply(x, wh.master, bh.master if bh is not None else None, wh, bh, k3, p3, s3,

@@ -296,7 +296,9 @@ class DistconvContext:
                 and (x.shape[3] * x.shape[4] * Cin * 2) % 16 == 0
                 and self.depth_groups == self.group.world)
 
-    def convolution(self, layer, x):
+    def convolution(self, layer, x, fuse_pool=None, pool_layer=None):
+        """``fuse_pool`` / ``pool_layer``: the 2^3 max pooling behind this convolution may run
+        inside its kernel (ops/nn.py, PoolFusion); only the path without an exchange takes it."""
         from ..ops import nn
         halo = tuple((k - 1) // 2 * d for k, d in zip(layer.ksize, layer.dil))
         hd = halo[0] if layer.nd == 3 else 0
@@ -305,10 +307,12 @@ class DistconvContext:
         if hd > 0 and pre == hd:
             # the input was uploaded with its halo planes: an ordinary convolution, no exchange
             pad = (0,) + tuple(layer.pad[1:])
+            if fuse_pool is not None and pool_layer is not None:
+                fuse_pool.out_alloc = self._pool_allocs(pool_layer, x)[0]
             return nn.convolution(x, layer.w.handle, None if layer.b is None else layer.b.handle,
                                   layer.ksize, pad, layer.stride, layer.dil, layer.groups,
                                   layer.fused_act[0], layer.fused_act[1],
-                                  getattr(layer, "skip_act_grad", False))
+                                  getattr(layer, "skip_act_grad", False), fuse_pool)
         if self._fused_halo_ok(layer, x, hd):
             return _DistConv.apply(x, layer.w.handle.master,
                                    None if layer.b is None else layer.b.handle.master, self, layer, hd)
@@ -338,6 +342,13 @@ class DistconvContext:
             pad = (0,) + tuple(layer.pad[1:])
             return nn.pooling(x, layer.k, pad, layer.stride, layer.mode)
         act = getattr(layer, "bwd_act", (0, 0.0))
+        out_alloc, dx_alloc = self._pool_allocs(layer, x)
+        return nn.pooling(x, layer.k, layer.pad, layer.stride, layer.mode, act[0], act[1],
+                          out_alloc, dx_alloc)
+
+    def _pool_allocs(self, layer, x):
+        """Where a pooling layer's output and input gradient go: straight into the next
+        convolution's tensor with halo planes and into the producing convolution's."""
         out_alloc = dx_alloc = None
         if self.group.native and x.is_cuda:
             # write the output straight into the next convolution's tensor with halo planes,
@@ -366,8 +377,7 @@ class DistconvContext:
                     if not getattr(par, "_fused_halo", False) or not getattr(par, "_needs_dx", False):
                         return None
                     return self.halo_tensor(("dy", par.name), N, D, hp, H, W, C, dtype).interior
-        return nn.pooling(x, layer.k, layer.pad, layer.stride, layer.mode, act[0], act[1],
-                          out_alloc, dx_alloc)
+        return out_alloc, dx_alloc
 
     def bn_reduction(self, layer):
         from ..ops.nn import GroupSum

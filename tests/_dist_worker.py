@@ -26,8 +26,8 @@ def cosmoflow(depth_groups, steps, dtype, width=32, channels=(8, 16, 16), graph=
     model = construct_cosmoflow_model(width, 4, 4, num_epochs=1, channels=tuple(channels), pool_mode="max",
                                       conv_bias=False, fc_sizes=(32, 16), parallel_strategy=ps)
     exp = lbann.proto.serialize.build_experiment(
-        trainer=lbann.Trainer(mini_batch_size=4, random_seed=5), model=model,
-        data_reader=synthetic_reader(16, width, 4, 4),
+        trainer=lbann.Trainer(mini_batch_size=int(os.environ.get("LBANN_TEST_MINI_BATCH", "4")), random_seed=5),
+        model=model, data_reader=synthetic_reader(16, width, 4, 4),
         optimizer=lbann.SGD(learn_rate=float(os.environ.get("LBANN_TEST_LR", "0.01")), momentum=0.9))
     tr = ExecTrainer(exp)
     m = tr.build_model(exp.model)
@@ -54,6 +54,7 @@ def cosmoflow(depth_groups, steps, dtype, width=32, channels=(8, 16, 16), graph=
         from lbann_b200.ops import native
         torch.cuda.synchronize()
         res["status"] = native.consume_status(False)
+        res["launches"] = native.launches()
         res["sharded_update"] = m.arena.shard is not None
         res["graph"] = bool(getattr(m, "_graph_mode", False))
     tr.shutdown()

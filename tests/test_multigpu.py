@@ -15,6 +15,21 @@ ENV = {"LBANN_TEST_DEVICE": "cuda", "NCCL_NVLS_ENABLE": "0"}
 STABLE = dict(ENV, LBANN_TEST_LR="0.0005")
 
 
+def test_first_layer_pooling_fusion_in_the_model(tmp_path):
+    """The small CosmoFlow on one GPU with the first pooling layer computed inside the
+    first convolution's kernel (the default) and with the two separate kernels: same
+    losses and weights; the fused run launches fewer kernels."""
+    args = ["cosmoflow", "1", "6", "fp16", "32", "8,16,16"]
+    fused = _run(1, args, str(tmp_path / "a.json"), STABLE)
+    plain = _run(1, args, str(tmp_path / "b.json"), dict(STABLE, LBANN_DISABLE_CONV_POOL_FUSION="1"))
+    assert fused["status"] == 0 and plain["status"] == 0
+    assert fused["launches"] < plain["launches"], (fused["launches"], plain["launches"])
+    for a, b in zip(fused["losses"], plain["losses"]):
+        assert abs(a - b) <= 2e-3 * max(1.0, abs(a)), (fused["losses"], plain["losses"])
+    for k, v in plain["weight_norms"].items():
+        assert abs(v - fused["weight_norms"][k]) <= 1e-3 * max(1.0, abs(v)), k
+
+
 @needs2
 def test_symmetric_memory_collectives(tmp_path):
     n = min(torch.cuda.device_count(), 4)
@@ -25,11 +40,13 @@ def test_symmetric_memory_collectives(tmp_path):
 
 @needs2
 @pytest.mark.parametrize("width,channels,graph", [("32", "8,16,16", ""), ("64", "16,32,32", ""),
-                                                  ("32", "8,16,16", "graph")])
+                                                  ("32", "8,16,16", "graph"),
+                                                  ("32", "8,16,16,16,16", "")])
 def test_distconv_two_gpus_matches_one(tmp_path, width, channels, graph):
     """Depth split over two GPUs with the halo exchange inside the convolution kernels
     (generic implicit-GEMM kernel at width 32, halo-slab kernel at width 64; eager launches
-    and graph replay): same losses and weights as one GPU, no interior copies (every
+    and graph replay; five blocks at width 32 leave the last convolution ONE plane per rank,
+    as eight ranks do on a 128^3 volume): same losses and weights as one GPU, no interior copies (every
     producer wrote straight into its consumer's tensor with halo planes), clean status."""
     steps = "8" if graph else "5"
     tail = [width, channels] + ([graph] if graph else [])

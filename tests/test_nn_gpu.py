@@ -38,6 +38,62 @@ def test_conv_c8_first_layer(shape, kout):
     torch.testing.assert_close(wh.grad, wr.grad, rtol=2e-2, atol=3e-2 * scale / 8)
 
 
+@pytest.mark.parametrize("shape,pad_d,bias,dtype", [
+    ((2, 4, 8, 16, 64), 1, False, torch.float16),      # one row tile, padding along depth
+    ((1, 3, 6, 10, 144), 1, True, torch.float16),      # three channels, two row tiles, ragged second tile
+    ((2, 4, 6, 4, 128), 0, True, torch.bfloat16),      # halo planes come with the input (no depth padding)
+    ((3, 4, 4, 6, 272), 1, False, torch.bfloat16),
+])
+@pytest.mark.parametrize("kout", [32, 16])
+def test_conv_c8_with_pooling_inside_the_kernel(shape, pad_d, bias, dtype, kout):
+    """First-layer convolution + leaky ReLU + 2x2x2 max pooling in one kernel: the pooled
+    tensor equals that of the two separate kernels bit for bit, the gradients agree with
+    them up to the choice between values that round to the same 16-bit number, and both
+    agree with PyTorch fp32."""
+    N, C, D, H, W = shape
+    torch.manual_seed(3)
+    pad = (pad_d, 1, 1)
+    x = torch.randn(N, C, D, H, W, device="cuda").to(dtype)
+    w = (torch.randn(kout, C, 3, 3, 3, device="cuda") / 6).to(dtype).float()
+    b = torch.randn(kout, device="cuda") / 4 if bias else None
+    outs = []
+    for fused in (True, False):
+        wh = _handle(w)
+        bh = _handle(b) if bias else None
+        fuse = nn.PoolFusion() if fused else None
+        y = nn.convolution(x, wh, bh, (3, 3, 3), pad, (1, 1, 1), (1, 1, 1), act=native.ACT_LEAKY,
+                           act_param=0.3, skip_act_grad=True, fuse_pool=fuse)
+        if fused:
+            assert fuse.done
+        else:
+            y = nn.pooling(y, (2, 2, 2), (0, 0, 0), (2, 2, 2), "max", native.ACT_LEAKY, 0.3)
+        assert native.consume_status() == 0
+        torch.manual_seed(4)
+        dy = torch.randn(y.shape, device="cuda").to(dtype)
+        y.backward(dy)
+        assert native.consume_status() == 0
+        outs.append((y.detach(), wh.grad.clone(), bh.grad.clone() if bias else None, dy))
+    (yf, gwf, gbf, dy), (yu, gwu, gbu, _) = outs
+    assert torch.equal(yf, yu)
+    # the fused kernel picks the arg-max on the fp32 accumulators, the pooling kernel on the
+    # rounded tensor: where two values of a window round to the same number the gradient may
+    # go to the other one
+    assert (gwf - gwu).norm() <= (0.1 if dtype == torch.float16 else 0.3) * gwu.norm() + 1e-3
+    if bias:
+        torch.testing.assert_close(gbf, gbu, rtol=1e-3, atol=1e-2)
+    wr = w.clone().requires_grad_(True)
+    br = b.clone().requires_grad_(True) if bias else None
+    ref = F.max_pool3d(F.leaky_relu(F.conv3d(x.float(), wr, br, 1, pad), 0.3), 2, 2)
+    tol = dict(rtol=1e-2, atol=2e-2) if dtype == torch.float16 else dict(rtol=3e-2, atol=6e-2)
+    torch.testing.assert_close(yf.float(), ref, **tol)
+    ref.backward(dy.float())
+    # like PyTorch in fp32, the fused kernel takes the arg-max before rounding: it follows the
+    # reference closely, the separate kernels only up to their near-ties
+    scale = (N * D * H * W) ** 0.5
+    assert (gwf - wr.grad).norm() <= 0.02 * wr.grad.norm() + 1e-3 * scale
+    assert (gwu - wr.grad).norm() <= (0.1 if dtype == torch.float16 else 0.3) * wr.grad.norm() + 1e-3 * scale
+
+
 def test_pool_bwd_tiled_with_fused_activation():
     torch.manual_seed(1)
     x = torch.randn(2, 16, 8, 8, 8, device="cuda").half()
