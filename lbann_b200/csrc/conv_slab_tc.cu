@@ -72,8 +72,10 @@ __device__ __forceinline__ void slab_issue_plane(uint32_t tmem_acc, uint32_t a_l
   }
 }
 
+constexpr int kSlabThreads = 64 + 2 * 128;     // 8 epilogue warps, producer, MMA issuer
+
 template <int BN>
-__global__ void __launch_bounds__(192, 1)
+__global__ void __launch_bounds__(kSlabThreads, 1)
 conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant__ CUtensorMap tmW,
                  const SlabParams p, int* status) {
   extern __shared__ uint8_t smem_raw[];
@@ -251,14 +253,22 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
       }
     }
   } else {
-    uint32_t lt = 0;
+    // Two epilogue groups of four warps (warps 0-3 and 6-9), one per accumulator: group eg
+    // drains this CTA's tiles eg, eg + 2, ...  With a single warp per scheduler the epilogue
+    // of a tile (TMEM load, conversion, row stores) shows its full latency and outlasts the
+    // tile's MMAs for layers with few input channels; two tiles in flight hide it.
+    const int eg = warp >= 6 ? 1 : 0;
+    const int quarter = warp & 3;                   // TMEM lane quarter this warp may read
+    uint32_t use = 0;
     const EpiParams& e = p.epi;
-    for (int t = blockIdx.x; t < p.num_tiles; t += gridDim.x, ++lt) {
+    for (long long tl = (long long)blockIdx.x + (long long)eg * gridDim.x; tl < p.num_tiles;
+         tl += 2ll * gridDim.x, ++use) {
+      const int t = (int)tl;
       uint32_t ti, r, dd, nn;
       p.fd_tiles_plane.divmod((uint32_t)t, r, ti);
       p.fd_Do.divmod(r, nn, dd);
       const int d = hs.enabled ? halo_rotate((int)dd, g.Do) : (int)dd, n = (int)nn;
-      const uint32_t acc = lt & 1, acc_ph = (lt >> 1) & 1;
+      const uint32_t acc = (uint32_t)eg, acc_ph = use & 1u;
       const bool landed = __all_sync(
           0xffffffffu, mbar_wait_bounded(smem_u32(&sh.tmem_full[acc]), acc_ph, abort_flag));
       if (!landed) {
@@ -266,11 +276,11 @@ conv_slab_kernel(const __grid_constant__ CUtensorMap tmX, const __grid_constant_
         break;
       }
       tc_fence_after();
-      const int row = warp * 32 + lane;
+      const int row = quarter * 32 + lane;
       const uint32_t q = ti * 128u + (uint32_t)row;
       const int h = (int)p.fd_Wp.div(q), w = (int)q - h * p.Wp;
       const long long row_off = n * p.o_sn + d * p.o_sd + h * p.o_sh + (long long)w * p.o_sw;
-      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(warp * 32) << 16);
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
       tc_epilogue_rows<BN>(TmemSrc{taddr}, h < g.Ho && w < g.Wo, row_off, 0, g.Kout, row, e);
       tc_fence_before();
       __syncwarp();
@@ -295,7 +305,7 @@ static int launch_slab(const CUtensorMap& tmX, const CUtensorMap& tmW, const Sla
     configured = smem;
   }
   const int grid = p.num_tiles < lbhost::sm_count() ? p.num_tiles : lbhost::sm_count();
-  conv_slab_kernel<BN><<<grid, 192, smem, stream>>>(tmX, tmW, p, lbhost::status_word());
+  conv_slab_kernel<BN><<<grid, kSlabThreads, smem, stream>>>(tmX, tmW, p, lbhost::status_word());
   return (int)cudaGetLastError();
 }
 

@@ -21,6 +21,7 @@ namespace lb {
 template <int BN_>
 struct ConvFwdPolicy {
   static constexpr int BN = BN_;
+  static constexpr int kEpiGroups = 2;       // two tiles' epilogues in flight (tc_pipeline.cuh)
   using G = StageGeom<BN>;
 
   struct Params {
@@ -177,7 +178,7 @@ static int launch_conv(const CUtensorMap& tmA, const CUtensorMap& tmB,
   p.epi.sk_ws = offer.ws;
   const int items = p.num_tiles * p.epi.k_splits;
   const int grid = items < lbhost::sm_count() ? items : lbhost::sm_count();
-  tc_persistent_kernel<P><<<grid, kTcThreads, G::kSmemBytes, stream>>>(tmA, tmB, p,
+  tc_persistent_kernel<P><<<grid, tc_threads<P>(), G::kSmemBytes, stream>>>(tmA, tmB, p,
                                                                        lbhost::status_word());
   int rc = (int)cudaGetLastError();
   if (rc == 0 && p.epi.k_splits > 1) rc = launch_splitk_reduce<P>(p, stream);

@@ -313,7 +313,7 @@ static int launch_gemm_comm(const CUtensorMap& tmA, const CUtensorMap& tmB,
     if (p.st.helpers >= grid) return -1;
   }
   p.status = lbhost::status_word();
-  tc_persistent_kernel<P><<<grid, kTcThreads, G::kSmemBytes, stream>>>(tmA, tmB, p,
+  tc_persistent_kernel<P><<<grid, tc_threads<P>(), G::kSmemBytes, stream>>>(tmA, tmB, p,
                                                                        lbhost::status_word());
   return (int)cudaGetLastError();
 }

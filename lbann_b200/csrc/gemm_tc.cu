@@ -17,6 +17,7 @@ namespace lb {
 template <int BN_>
 struct GemmPolicy {
   static constexpr int BN = BN_;
+  static constexpr int kEpiGroups = 2;       // two tiles' epilogues in flight (tc_pipeline.cuh)
   using G = StageGeom<BN>;
 
   struct Params {
@@ -116,7 +117,7 @@ static int launch_gemm(const CUtensorMap& tmA, const CUtensorMap& tmB,
   }
   const int items = p.num_tiles * p.epi.k_splits;
   const int grid = items < lbhost::sm_count() ? items : lbhost::sm_count();
-  tc_persistent_kernel<P><<<grid, kTcThreads, G::kSmemBytes, stream>>>(tmA, tmB, p,
+  tc_persistent_kernel<P><<<grid, tc_threads<P>(), G::kSmemBytes, stream>>>(tmA, tmB, p,
                                                                        lbhost::status_word());
   int rc = (int)cudaGetLastError();
   if (rc == 0 && p.epi.k_splits > 1) rc = launch_splitk_reduce<P>(p, stream);

@@ -13,6 +13,7 @@
 // issue and the row -> output address map.
 #pragma once
 #include "common.cuh"
+#include <type_traits>
 #include "halo_sync.cuh"
 
 namespace lb {
@@ -294,8 +295,23 @@ struct TcEpilogue<Policy, typename Policy::HasEpilogue> {
   }
 };
 
+// Epilogue groups of a policy: four warps each (0-3, and 6-9 for the second).  With two
+// groups each owns one of the two accumulators and drains every other tile of the CTA, so
+// that two tiles' epilogues are in flight: with a single warp per scheduler the TMEM load,
+// conversion and row stores of a tile show their full latency, which outlasts the MMAs of
+// tiles with a short reduction (convolutions with few channels, 1x1 convolutions).
+// A policy opts in with `static constexpr int kEpiGroups = 2`.
+template <class Policy, class = void>
+struct TcEpiGroups { static constexpr int value = 1; };
 template <class Policy>
-__global__ void __launch_bounds__(kTcThreads, 1)
+struct TcEpiGroups<Policy, std::void_t<decltype(Policy::kEpiGroups)>> {
+  static constexpr int value = Policy::kEpiGroups;
+};
+template <class Policy>
+constexpr int tc_threads() { return 64 + 128 * TcEpiGroups<Policy>::value; }
+
+template <class Policy>
+__global__ void __launch_bounds__(tc_threads<Policy>(), 1)
 tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
                      const __grid_constant__ CUtensorMap tmB,
                      const __grid_constant__ typename Policy::Params p, int* status) {
@@ -456,9 +472,14 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
     }
   } else {
     // ------------------------------- epilogue -------------------------------
-    uint32_t local_tile = 0;
+    constexpr int EG = TcEpiGroups<Policy>::value;
+    const int eg = (EG > 1 && warp >= 6) ? 1 : 0;
+    const int quarter = warp & 3;                    // TMEM lane quarter this warp may read
+    uint32_t local_tile = (uint32_t)eg;
     bool ok = true;
-    for (int w = blockIdx.x; w < num_items && ok; w += n_workers, ++local_tile) {
+    for (long long wl = (long long)blockIdx.x + (long long)eg * n_workers; wl < num_items && ok;
+         wl += (long long)EG * n_workers, local_tile += EG) {
+      const int w = (int)wl;
       const int t = w / splits;
       const typename Policy::Tile tile = Policy::decode(p, t);
       const uint32_t acc = local_tile & 1;
@@ -472,14 +493,14 @@ tc_persistent_kernel(const __grid_constant__ CUtensorMap tmA,
         break;
       }
       tc_fence_after();
-      const int row = warp * 32 + lane;
+      const int row = quarter * 32 + lane;
       long long row_off = 0;
       const bool row_ok = Policy::row_addr(p, tile, row, row_off);
       const int n0 = Policy::col0(p, tile);
       const int n_total = Policy::ncols(p);
       const int row_index = Policy::row_index(p, tile, row);
       const EpiParams& e = p.epi;
-      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(warp * 32) << 16);
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
       if (splits == 1) {
         TcEpilogue<Policy>::run(taddr, row_ok, row_off, n0, n_total, row_index, e, p);
         tc_fence_before();
