@@ -115,6 +115,8 @@ def _lib():
         lib.lb_conv_c8_fwd.restype = c_int
         lib.lb_conv_c8_fwd.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, P(c_int), P(c_ll),
                                        P(c_ll), c_int, c_int, c_int, c_float, c_void_p]
+        lib.lb_planar_to_pixels.restype = c_int
+        lib.lb_planar_to_pixels.argtypes = [c_void_p, c_void_p, c_int, c_int, c_ll, c_ll, c_int, c_void_p]
         lib.lb_conv_c8_fwd_pool.restype = c_int
         lib.lb_conv_c8_fwd_pool.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, P(c_int),
                                             P(c_ll), P(c_ll), c_int, c_int, c_int, c_float, c_void_p]
@@ -412,6 +414,27 @@ class _Conv(torch.autograd.Function):
         return (dx,) + (None,) * 11
 
 
+def _first_layer_pixels(x, cr: int):
+    """The [N, D, H, W, cr] pixel layout the first-layer kernels read (cr = 4 or 8 channels
+    per pixel, zero beyond the tensor's own).  A planar [N, C, D, H, W] tensor is
+    interleaved by one vectorised kernel (csrc/layout.cu)."""
+    N, C = x.shape[0], x.shape[1]
+    sp = tuple(x.shape[2:])
+    S = 1
+    for v in sp:
+        S *= v
+    if (x.dim() == 5 and x.dtype in (torch.float16, torch.bfloat16) and S % 8 == 0 and x.stride(1) == S
+            and x[0].is_contiguous() and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0):
+        y = torch.empty((N,) + sp + (cr,), dtype=x.dtype, device=x.device)
+        native.check(_lib().lb_planar_to_pixels(x.data_ptr(), y.data_ptr(), N, C, S, x.stride(0), cr,
+                                                native.stream_ptr()), "lb_planar_to_pixels")
+        native.count_launch()
+        return y
+    x_in = _cl_view(x)
+    x_cl = F.pad(x_in, (0, cr - C)) if C != cr else x_in
+    return x_cl if x_cl.is_contiguous() else x_cl.contiguous()
+
+
 class _ConvC8(torch.autograd.Function):
     """First-layer convolution: at most 8 input channels, kernel (kd, kh, 3), stride 1, no
     dilation, "same" padding along W.  Forward and filter gradient use the dedicated
@@ -421,14 +444,11 @@ class _ConvC8(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w_leaf, b_leaf, wh, bh, ksize, pad, act, act_p, skip_act_grad):
         ndim = x.dim()
-        x_in = _cl_view(x)
-        Cin = x_in.shape[-1]
+        Cin = x.shape[1]
         # pixels are 8 bytes (<= 4 channels, W a multiple of 16) or 16 bytes; an input that
-        # already has 4 or 8 channels is used as it is
-        cr = 4 if (Cin <= 4 and x_in.shape[-2] % 16 == 0) else 8
-        x_cl = F.pad(x_in, (0, cr - Cin)) if Cin != cr else x_in
-        if not x_cl.is_contiguous():
-            x_cl = x_cl.contiguous()
+        # already has 4 or 8 channels in that layout is used as it is
+        cr = 4 if (Cin <= 4 and x.shape[-1] % 16 == 0) else 8
+        x_cl = _first_layer_pixels(x, cr)
         x_bwd = x_cl
         Kout = wh.master.shape[0]
         kd, kh, _ = ksize
@@ -514,11 +534,8 @@ class _ConvC8Pool(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w_leaf, b_leaf, wh, bh, pad, act, act_p, out_alloc):
         ndim = x.dim()
-        x_in = _cl_view(x)
-        Cin = x_in.shape[-1]
-        x_cl = F.pad(x_in, (0, 4 - Cin)) if Cin != 4 else x_in
-        if not x_cl.is_contiguous():
-            x_cl = x_cl.contiguous()
+        Cin = x.shape[1]
+        x_cl = _first_layer_pixels(x, 4)
         Kout = wh.master.shape[0]
 
         def pack():
