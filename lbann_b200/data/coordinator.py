@@ -204,7 +204,10 @@ class DataCoordinator:
         nbytes = 0
         for f, t in host.items():
             sl = getattr(self, "field_slices", {}).get(f)
-            if sl is not None:      # this rank only needs a slab of the sample (distconv)
+            if isinstance(sl, list):    # a brick of the sample: one slice per partitioned dimension
+                for one in sl:
+                    t = slice_with_halo(t, one[0], one[1], one[2], one[3] if len(one) > 3 else 0)
+            elif sl is not None:    # this rank only needs a slab of the sample (distconv)
                 t = slice_with_halo(t, sl[0], sl[1], sl[2], sl[3] if len(sl) > 3 else 0)
             dt = self.field_dtypes.get(f)
             if dt is not None and t.dtype != dt:

@@ -70,10 +70,13 @@ class DistconvContext:
             SymmetricGroup(self.device, pg=comm.trainer_group)
         self.strategies: Dict[str, Strategy] = {}
         self.depth_groups = 1
+        self.height_groups = 1                    # second partitioned dimension (depth x height)
         self.input_halo: Dict[str, int] = {}      # input layer -> halo planes uploaded with it
         self.num_sample_groups = 1
         self.sample_group_index = 0
         self.depth_rank = 0
+        self.height_rank = 0
+        self.line_pg = {}                         # tensor dim (2 depth, 3 height) -> process group of that line
         self.dist: Dict[Tuple[str, int], str] = {}
         self._enabled: Dict[str, bool] = {}
         self._bufs: Dict[tuple, SymmetricBuffer] = {}
@@ -88,21 +91,44 @@ class DistconvContext:
     def plan(self, model_pb) -> None:
         """Depth / sample group sizes from the prototext alone (the data coordinator, which
         deals samples to the sample groups, is built before the model is)."""
-        depth = 1
+        depth = height = 1
         for l in model_pb.layer:
             if l.HasField("parallel_strategy"):
                 st = Strategy(l.parallel_strategy, self.world)
                 if st.is_spatial():
-                    depth = max(depth, st.depth)
-        if depth > 1 and self.world % depth == 0:
-            self.depth_groups = depth
-            self.num_sample_groups = self.world // depth
-            self.sample_group_index = self.rank // depth
-            self.depth_rank = self.rank % depth
+                    depth, height = max(depth, st.depth), max(height, st.height)
+        if depth * height > 1 and self.world % (depth * height) == 0:
+            self._set_grid(depth, height)
+
+    def _set_grid(self, depth: int, height: int) -> None:
+        """Ranks of one sample group are consecutive and form a depth x height grid, height
+        fastest: rank = (sample_group * depth + depth_rank) * height + height_rank."""
+        spatial = depth * height
+        self.depth_groups, self.height_groups = depth, height
+        self.num_sample_groups = self.world // spatial
+        self.sample_group_index = self.rank // spatial
+        self.depth_rank = (self.rank % spatial) // height
+        self.height_rank = self.rank % height
+
+    @property
+    def spatial_size(self) -> int:
+        """Ranks that share one sample (depth_groups x height_groups)."""
+        return self.depth_groups * self.height_groups
+
+    @property
+    def spatial_rank(self) -> int:
+        return self.depth_rank * self.height_groups + self.height_rank
+
+    @property
+    def fused(self) -> bool:
+        """The peer-memory kernels (halo exchange inside the convolutions, all-to-all
+        redistribution, small all-reduce) serve the depth-only partition; a depth x height
+        grid exchanges its halos with library collectives over the grid's lines."""
+        return self.group.native and self.height_groups == 1
 
     def prepare_model(self, model):
         self._enabled.clear()
-        depth = 1
+        depth = height = 1
         for l in model.layers:
             if l.parallel_strategy is None:
                 continue
@@ -110,22 +136,22 @@ class DistconvContext:
             if l.type in ("convolution", "deconvolution") and (st.channel > 1 or st.filter > 1):
                 raise ValueError(f"layer '{l.name}': channel / filter parallelism is not "
                                  f"supported for convolutions")
-            if st.height > 1 or st.width > 1:
+            if st.width > 1:
                 raise NotImplementedError(
-                    f"layer '{l.name}': this build partitions the depth dimension only "
-                    f"(height_groups / width_groups > 1 requested)")
+                    f"layer '{l.name}': depth and height can be partitioned, width cannot "
+                    f"(width_groups > 1 requested)")
             self.strategies[l.name] = st
             if st.is_spatial():
-                if depth not in (1, st.depth):
-                    raise ValueError("all distconv layers of a model must use the same depth_groups")
-                depth = st.depth
-        self.depth_groups = depth
-        self.num_sample_groups = self.world // depth
-        # ranks of one sample group are consecutive: rank = sample_group * depth + depth_rank
-        self.sample_group_index = self.rank // depth
-        self.depth_rank = self.rank % depth
+                if (depth, height) not in ((1, 1), (st.depth, st.height)):
+                    raise ValueError("all distconv layers of a model must use the same "
+                                     "depth_groups and height_groups")
+                depth, height = st.depth, st.height
+        self._set_grid(depth, height)
         self.depth_pg = "trainer"
-        if depth > 1 and self.num_sample_groups > 1:
+        self.line_pg = {2: "trainer", 3: "trainer"}
+        if height > 1:
+            self._build_grid_groups(depth, height)
+        elif depth > 1 and self.num_sample_groups > 1:
             # sample x depth partition (left-over ranks multiply the sample groups,
             # src/layers/distconv_adapter.cpp:227-336): the mini-batch is dealt to the sample
             # groups, every group splits its samples along depth over its own ranks and has
@@ -140,7 +166,23 @@ class DistconvContext:
             self.group = SymmetricGroup(self.device, pg=self.depth_pg)
         # inputs consumed only by distconv layers are sliced on the host before upload
         tr = getattr(model, "trainer", None)
-        if depth > 1 and tr is not None and tr.data_coordinator is not None:
+        if height > 1 and tr is not None and tr.data_coordinator is not None:
+            slicers = {}
+            for l in model.layers:
+                if l.type != "input":
+                    continue
+                kids = [model.layers_by_name[c] for c in l.child_names]
+                f = l.params.data_field or "samples"
+                dims = tr.data_coordinator.dims(f)
+                if (kids and all(self.enabled(k) for k in kids) and len(dims) == 4
+                        and dims[1] % depth == 0 and dims[2] % height == 0):
+                    dl, hl = dims[1] // depth, dims[2] // height
+                    slicers[f] = [(2, self.depth_rank * dl, (self.depth_rank + 1) * dl, 0),
+                                  (3, self.height_rank * hl, (self.height_rank + 1) * hl, 0)]
+                    self.input_halo[l.name] = 0
+            tr.data_coordinator.field_slices = slicers
+            self.sliced_fields = set(slicers)
+        elif depth > 1 and tr is not None and tr.data_coordinator is not None:
             slicers = {}
             for l in model.layers:
                 if l.type != "input":
@@ -153,7 +195,7 @@ class DistconvContext:
                         # an input read by one convolution only is uploaded WITH its halo
                         # planes (zeros beyond the volume): the first layer then needs no
                         # exchange at all
-                        h = self._input_halo(kids) if self.group.native else 0
+                        h = self._input_halo(kids) if self.fused else 0
                         slicers[l.params.data_field or "samples"] = (2, self.depth_rank * dl,
                                                                      (self.depth_rank + 1) * dl, h)
                         self.input_halo[l.name] = h
@@ -161,6 +203,30 @@ class DistconvContext:
             self.sliced_fields = set(slicers)
         else:
             self.sliced_fields = set()
+
+    def _build_grid_groups(self, depth: int, height: int) -> None:
+        """Process groups of a depth x height grid: the ranks of this sample group (sums of
+        partial losses, redistribution) and the two lines through this rank (halo exchange
+        along depth and along height; src/layers/distconv_adapter.cpp:227-336 sets up the
+        same locale shapes).  Every rank creates every group, in the same order."""
+        spatial = depth * height
+        base = self.comm.trainer_rank * self.world
+        for sgi in range(self.num_sample_groups):
+            first = base + sgi * spatial
+            mine = sgi == self.sample_group_index
+            if self.num_sample_groups > 1:
+                pg = self.comm.new_group([first + i for i in range(spatial)])
+                if mine:
+                    self.depth_pg = pg
+            for hr in range(height):                  # lines along depth: fixed height rank
+                pg = self.comm.new_group([first + d * height + hr for d in range(depth)]) \
+                    if depth > 1 else None
+                if mine and hr == self.height_rank and pg is not None:
+                    self.line_pg[2] = pg
+            for dr in range(depth):                   # lines along height: fixed depth rank
+                pg = self.comm.new_group([first + dr * height + i for i in range(height)])
+                if mine and dr == self.depth_rank:
+                    self.line_pg[3] = pg
 
     def _input_halo(self, kids) -> int:
         """Halo planes to upload with an input: what its only consumer, a stride-1 3-D
@@ -186,7 +252,7 @@ class DistconvContext:
             return hit
         st = self.strategies.get(layer.name)
         val = bool(st is not None and st.is_spatial() and layer.supports_distconv
-                   and self.depth_groups > 1 and self._feasible(layer))
+                   and self.spatial_size > 1 and self._feasible(layer))
         if getattr(layer, "in_dims", None):
             self._enabled[layer.name] = val
         return val
@@ -199,21 +265,28 @@ class DistconvContext:
         dims = layer.in_dims[0] if getattr(layer, "in_dims", None) else None
         if not dims or len(dims) != 4:
             return True
-        D, P = int(dims[1]), self.depth_groups
-        if D % P:
-            return False
-        local = D // P
-        if layer.type in ("convolution", "deconvolution"):
-            k, s, d = layer.ksize[0], layer.stride[0], layer.dil[0]
-            return local % s == 0 and local >= (k - 1) // 2 * d and local >= 1
-        if layer.type == "pooling":
-            return local % layer.stride[0] == 0 and local >= layer.k[0] // 2
-        return local >= 1
+        for axis, P in ((0, self.depth_groups), (1, self.height_groups)):
+            if P == 1:
+                continue
+            D = int(dims[1 + axis])
+            if D % P:
+                return False
+            local = D // P
+            if layer.type in ("convolution", "deconvolution"):
+                k, s, d = layer.ksize[axis], layer.stride[axis], layer.dil[axis]
+                if not (local % s == 0 and local >= (k - 1) // 2 * d and local >= 1):
+                    return False
+            elif layer.type == "pooling":
+                if not (local % layer.stride[axis] == 0 and local >= layer.k[axis] // 2):
+                    return False
+            elif local < 1:
+                return False
+        return True
 
     # ------------------------------------------------------------------ distribution bookkeeping
     def adapt_inputs(self, model, layer, xs):
         """Redistribute the inputs of ``layer`` to the layout it computes in."""
-        if self.depth_groups == 1:
+        if self.spatial_size == 1:
             return xs
         want = SPATIAL if self.enabled(layer) else SAMPLE
         out = []
@@ -222,10 +295,14 @@ class DistconvContext:
             if have == want or x.dim() < 1:
                 out.append(x)
             elif have == REPLICATED and want == SAMPLE:
-                out.append(x[self.depth_rank::self.depth_groups])
+                out.append(x[self.spatial_rank::self.spatial_size])
             elif have == REPLICATED and want == SPATIAL:
                 dl = x.shape[2] // self.depth_groups
-                out.append(x[:, :, self.depth_rank * dl:(self.depth_rank + 1) * dl])
+                x = x[:, :, self.depth_rank * dl:(self.depth_rank + 1) * dl]
+                if self.height_groups > 1:
+                    hl = x.shape[3] // self.height_groups
+                    x = x[:, :, :, self.height_rank * hl:(self.height_rank + 1) * hl]
+                out.append(x)
             elif have == SPATIAL and want == SAMPLE:
                 out.append(_Redistribute.apply(x, self, True, pn))
             elif have == SAMPLE and want == SPATIAL:
@@ -235,7 +312,7 @@ class DistconvContext:
         return out
 
     def note_outputs(self, model, layer):
-        if self.depth_groups == 1:
+        if self.spatial_size == 1:
             return
         if layer.type == "input":
             f = layer.params.data_field or "samples"
@@ -256,9 +333,9 @@ class DistconvContext:
     # ------------------------------------------------------------------ layer entry points
     def allreduce_depth_(self, t: torch.Tensor):
         """In-place sum over the ranks that share this rank's samples (its depth group)."""
-        if self.depth_groups == 1:
+        if self.spatial_size == 1:
             return
-        if self.group.native and t.dtype == torch.float32 and t.is_contiguous() and t.numel() <= 4096:
+        if self.fused and t.dtype == torch.float32 and t.is_contiguous() and t.numel() <= 4096:
             self.group.allreduce_small_(t, "sum")
         else:
             self.comm.allreduce(t, self.depth_pg, "sum")
@@ -266,7 +343,7 @@ class DistconvContext:
     def step_barrier(self):
         """Stream-ordered rendezvous of the trainer's ranks (needed between two steps that
         have no other collective between them, see csrc/halo_sync.cuh)."""
-        if self.depth_groups > 1 and self.group.native:
+        if self.depth_groups > 1 and self.fused:
             self.group.barrier_device(3)
 
     def halo_tensor(self, key: tuple, N, Dl, h, H, W, C, dtype) -> "HaloTensor":
@@ -285,7 +362,7 @@ class DistconvContext:
         return t
 
     def _fused_halo_ok(self, layer, x, hd: int) -> bool:
-        if not (self.group.native and hd > 0 and x.is_cuda and layer.nd == 3 and layer.groups == 1):
+        if not (self.fused and hd > 0 and x.is_cuda and layer.nd == 3 and layer.groups == 1):
             return False
         if os.environ.get("LBANN_DISTCONV_HALO_EXCHANGE", "").upper() == "SEPARATE":
             return False
@@ -301,6 +378,8 @@ class DistconvContext:
         inside its kernel (ops/nn.py, PoolFusion); only the path without an exchange takes it."""
         from ..ops import nn
         halo = tuple((k - 1) // 2 * d for k, d in zip(layer.ksize, layer.dil))
+        if self.height_groups > 1:
+            return self._grid_convolution(layer, x, halo)
         hd = halo[0] if layer.nd == 3 else 0
         parent = layer.parent_names[0] if layer.parent_names else None
         pre = self.input_halo.get(parent, 0)
@@ -323,6 +402,31 @@ class DistconvContext:
                               layer.fused_act[0], layer.fused_act[1],
                               getattr(layer, "skip_act_grad", False))
 
+    def _grid_convolution(self, layer, x, halo):
+        """Convolution on a depth x height grid: the halo planes along depth are exchanged
+        first, then the halo rows along height of the depth-extended tensor, which brings the
+        corner regions from the diagonal neighbours in two hops
+        (src/layers/learning/base_convolution.cpp:1355-1445 exchanges per dimension likewise)."""
+        from ..ops import nn
+        if layer.nd != 3:
+            raise NotImplementedError("a depth x height partition needs 3-D convolutions")
+        parts = (self.depth_groups, self.height_groups, 1)
+        pad = list(layer.pad)
+        xe = x
+        for axis in (0, 1):
+            if parts[axis] == 1:
+                continue
+            if layer.pad[axis] != halo[axis]:
+                raise NotImplementedError(
+                    f"layer '{layer.name}': a partitioned dimension needs padding (k - 1) / 2 * dilation")
+            if halo[axis] > 0:
+                xe = LineHaloExchange.apply(xe, self, halo[axis], 2 + axis, 0.0)
+            pad[axis] = 0
+        return nn.convolution(xe, layer.w.handle, None if layer.b is None else layer.b.handle,
+                              layer.ksize, tuple(pad), layer.stride, layer.dil, layer.groups,
+                              layer.fused_act[0], layer.fused_act[1],
+                              getattr(layer, "skip_act_grad", False))
+
     def deconvolution(self, layer, x):
         from ..ops import nn
         if any(k != s for k, s in zip(layer.ksize, layer.stride)):
@@ -333,6 +437,12 @@ class DistconvContext:
 
     def pooling(self, layer, x):
         from ..ops import nn
+        if self.height_groups > 1:
+            if any(layer.k[a] != layer.stride[a] or layer.pad[a] != 0 for a in (0, 1)):
+                raise NotImplementedError("pooling on a depth x height grid needs windows that "
+                                          "do not overlap (kernel == stride, no padding)")
+            act = getattr(layer, "bwd_act", (0, 0.0))
+            return nn.pooling(x, layer.k, layer.pad, layer.stride, layer.mode, act[0], act[1])
         if layer.k[0] != layer.stride[0] or layer.pad[0] != 0:
             hd = (layer.k[0] - 1) // 2
             if layer.k[0] % 2 == 0 or layer.stride[0] != 1:
@@ -350,7 +460,7 @@ class DistconvContext:
         """Where a pooling layer's output and input gradient go: straight into the next
         convolution's tensor with halo planes and into the producing convolution's."""
         out_alloc = dx_alloc = None
-        if self.group.native and x.is_cuda:
+        if self.fused and x.is_cuda:
             # write the output straight into the next convolution's tensor with halo planes,
             # and the input gradient into the producing convolution's (no interior copies)
             model = getattr(layer, "model", None)
@@ -390,7 +500,7 @@ class DistconvContext:
         from ..ops import nn
         part = nn.sample_loss(kind, a, b.reshape(a.shape))
         if kind in ("mean_squared_error", "mean_absolute_error"):
-            part = part / self.depth_groups
+            part = part / self.spatial_size
         return _AllReduceSum.apply(part.reshape(-1, 1), self)
 
     def cross_entropy(self, layer, p, labels):
@@ -550,6 +660,51 @@ class _AllReduceSum(torch.autograd.Function):
         return g, None
 
 
+class LineHaloExchange(torch.autograd.Function):
+    """Halo exchange along one dimension of a depth x height grid.  x: logical
+    [N, C, D, H, W]; ``dim`` = 2 (depth) or 3 (height); the result is 2h longer along it,
+    with the neighbours' boundary slices at either end (``fill`` beyond the global
+    boundary).  The ranks of the line through this rank trade their boundary slices with a
+    library all-gather; backward sends the gradients of the received slices back and adds
+    them to the owners' boundary."""
+
+    @staticmethod
+    def forward(ctx, x, dc: "DistconvContext", h: int, dim: int, fill: float = 0.0):
+        P = dc.depth_groups if dim == 2 else dc.height_groups
+        r = dc.depth_rank if dim == 2 else dc.height_rank
+        L = x.shape[dim]
+        ctx.meta = (dc, h, dim, P, r, L)
+        lo, hi = x.narrow(dim, 0, h), x.narrow(dim, L - h, h)
+        edges = torch.stack([lo, hi]).contiguous()
+        allp = dc.comm.all_gather(edges, dc.line_pg[dim])
+        shape = list(x.shape)
+        shape[dim] = L + 2 * h
+        xe = x.new_empty(shape)
+        xe.narrow(dim, h, L).copy_(x)
+        if r > 0:
+            xe.narrow(dim, 0, h).copy_(allp[r - 1][1])
+        else:
+            xe.narrow(dim, 0, h).fill_(fill)
+        if r < P - 1:
+            xe.narrow(dim, h + L, h).copy_(allp[r + 1][0])
+        else:
+            xe.narrow(dim, h + L, h).fill_(fill)
+        dc.halo_bytes += 2 * lo.numel() * lo.element_size()
+        return xe
+
+    @staticmethod
+    def backward(ctx, gxe):
+        dc, h, dim, P, r, L = ctx.meta
+        edges = torch.stack([gxe.narrow(dim, 0, h), gxe.narrow(dim, h + L, h)]).contiguous()
+        allp = dc.comm.all_gather(edges, dc.line_pg[dim])
+        dx = gxe.narrow(dim, h, L).clone()
+        if r > 0:             # what the rank before me computed for my first slices
+            dx.narrow(dim, 0, h).add_(allp[r - 1][1])
+        if r < P - 1:
+            dx.narrow(dim, L - h, h).add_(allp[r + 1][0])
+        return dx, None, None, None, None
+
+
 class HaloExchange(torch.autograd.Function):
     """x: logical [N, C, Dl, H, W] (channels-last memory) -> [N, C, Dl + 2h, H, W] whose outer
     planes hold the neighbours' boundary planes (``fill`` beyond the global boundary)."""
@@ -565,13 +720,13 @@ class HaloExchange(torch.autograd.Function):
         x_cl = x.permute(0, 2, 3, 4, 1)
         g = dc.group
         ctx.meta = (dc, h, tag, (N, C, Dl, H, W))
-        if g.native and P == g.world and r == g.rank:
+        if dc.fused and P == g.world and r == g.rank:
             # interior copy, boundary fill, peer stores and both rendezvous in one launch
             xs = x_cl if x_cl.is_contiguous() else x_cl.contiguous()
             if g.halo_forward(xs, buf, N, Dl, h, plane, fill):
                 dc.halo_bytes += 2 * N * h * plane
                 return xe.permute(0, 4, 1, 2, 3)
-        if g.native:
+        if dc.fused:
             raise native.NativeError("halo exchange: the tensor's planes are not multiples of "
                                      "16 bytes or it has fewer planes than the halo is wide")
         # host-side ranks (gloo): same data movement with a library all-gather
@@ -596,7 +751,7 @@ class HaloExchange(torch.autograd.Function):
         if not g_cl.is_contiguous():
             g_cl = g_cl.contiguous()
         plane = H * W * C * g_cl.element_size()
-        if not dc.group.native:
+        if not dc.fused:
             edges = torch.stack([g_cl[:, :h], g_cl[:, h + Dl:]]).contiguous()
             allp = dc.comm.all_gather(edges, dc.depth_pg)
             dx = g_cl[:, h:h + Dl].clone()
@@ -636,7 +791,22 @@ def _redistribute(x, dc: DistconvContext, to_sample: bool, tag: str):
     x_cl = x.permute(0, 2, 3, 4, 1).contiguous()        # N, D, H, W, C
     es = x_cl.element_size()
     grp = dc.group
-    if not grp.native:
+    if dc.height_groups > 1:
+        # depth x height grid: every rank of the sample group contributes its brick
+        Hg, S, sr = dc.height_groups, dc.spatial_size, dc.spatial_rank
+        parts = dc.comm.all_gather(x_cl, dc.depth_pg)
+        if to_sample:       # my samples (sr, sr + S, ...) of every brick, bricks put together
+            out = torch.cat([torch.cat([parts[d * Hg + i][sr::S] for i in range(Hg)], dim=2)
+                             for d in range(P)], dim=1)
+        else:               # my brick of every rank's samples, samples interleaved again
+            ns, D, H = x_cl.shape[0], x_cl.shape[1], x_cl.shape[2]
+            Dl, Hl = D // P, H // Hg
+            out = torch.empty((sum(q.shape[0] for q in parts), Dl, Hl) + tuple(x_cl.shape[3:]),
+                              dtype=x_cl.dtype, device=x_cl.device)
+            for q, part in enumerate(parts):
+                out[q::S] = part[:, r * Dl:(r + 1) * Dl, dc.height_rank * Hl:(dc.height_rank + 1) * Hl]
+        return out.permute(0, 4, 1, 2, 3)
+    if not dc.fused:
         parts = dc.comm.all_gather(x_cl, dc.depth_pg)
         if to_sample:
             out = torch.cat([p[r::P] for p in parts], dim=1)

@@ -22,7 +22,9 @@ def cosmoflow(depth_groups, steps, dtype, width=32, channels=(8, 16, 16), graph=
     if graph:
         o.set("use_cuda_graph", True)
     world = int(os.environ.get("WORLD_SIZE", "1"))
-    ps = lbann.get_parallel_strategy_args(depth_groups=depth_groups) if depth_groups > 1 else None
+    height_groups = int(os.environ.get("LBANN_TEST_HEIGHT_GROUPS", "1"))
+    ps = lbann.get_parallel_strategy_args(depth_groups=depth_groups, height_groups=height_groups) \
+        if depth_groups * height_groups > 1 else None
     model = construct_cosmoflow_model(width, 4, 4, num_epochs=1, channels=tuple(channels), pool_mode="max",
                                       conv_bias=False, fc_sizes=(32, 16), parallel_strategy=ps)
     exp = lbann.proto.serialize.build_experiment(
@@ -57,6 +59,50 @@ def cosmoflow(depth_groups, steps, dtype, width=32, channels=(8, 16, 16), graph=
         res["launches"] = native.launches()
         res["sharded_update"] = m.arena.shard is not None
         res["graph"] = bool(getattr(m, "_graph_mode", False))
+    tr.shutdown()
+    return res
+
+
+def unet(depth_groups, height_groups, steps, volume=16, base=4, levels=2):
+    """Small 3-D U-Net (convolution + batch norm + ReLU, max pooling, 2x up-convolutions,
+    skip concatenations, per-voxel softmax cross-entropy) on a depth x height grid."""
+    from lbann_b200.models import construct_unet3d_model
+    o = opts.reset()
+    o.set("default_dtype", "float")
+    if os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cpu":
+        o.set("disable_cuda", True)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    ps = lbann.get_parallel_strategy_args(depth_groups=depth_groups, height_groups=height_groups) \
+        if depth_groups * height_groups > 1 else None
+    model = construct_unet3d_model(num_classes=3, base_channels=base, levels=levels, parallel_strategy=ps)
+    v = volume
+    r = lbann.reader_pb2.Reader()
+    r.name, r.role, r.shuffle, r.fraction_of_data_to_use = "synthetic", "train", False, 1.0
+    r.synth_dimensions = f"1 {v} {v} {v}"
+    r.synth_response_dimensions = f"{v} {v} {v}"
+    r.synth_distribution = "samples:normal responses:randint:3"
+    r.num_samples = 4
+    r.synth_pool_size = 4
+    dr = lbann.reader_pb2.DataReader()
+    dr.reader.append(r)
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=2, random_seed=3), model=model, data_reader=dr,
+        optimizer=lbann.SGD(learn_rate=0.01, momentum=0.9))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    losses = []
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    for _ in range(steps):
+        b = dc.next_batch("training")
+        if b is None:
+            dc.start_epoch("training")
+            b = dc.next_batch("training")
+        m.train_step(b.tensors, b.global_size)
+        losses.append(float(m.last_objective.detach().float()))
+    w = {x.name: float(x.values.detach().float().norm()) for x in m.weights}
+    res = {"losses": losses, "weight_norms": w, "world": world,
+           "halo_bytes": tr.distconv.halo_bytes if tr.distconv is not None else 0}
     tr.shutdown()
     return res
 
@@ -616,6 +662,8 @@ if __name__ == "__main__":
         res = subgraph_transformer(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "abort_restart":
         res = abort_and_restart(sys.argv[3], int(sys.argv[4]), int(sys.argv[5]))
+    elif what == "unet":
+        res = unet(int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]))
     elif what == "cosmoflow":
         res = cosmoflow(int(sys.argv[3]), int(sys.argv[4]), sys.argv[5] if len(sys.argv) > 5 else "float",
                         int(sys.argv[6]) if len(sys.argv) > 6 else 32,
