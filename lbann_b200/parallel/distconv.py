@@ -174,11 +174,13 @@ class DistconvContext:
                 kids = [model.layers_by_name[c] for c in l.child_names]
                 f = l.params.data_field or "samples"
                 dims = tr.data_coordinator.dims(f)
-                if (kids and all(self.enabled(k) for k in kids) and len(dims) == 4
-                        and dims[1] % depth == 0 and dims[2] % height == 0):
-                    dl, hl = dims[1] // depth, dims[2] // height
-                    slicers[f] = [(2, self.depth_rank * dl, (self.depth_rank + 1) * dl, 0),
-                                  (3, self.height_rank * hl, (self.height_rank + 1) * hl, 0)]
+                # [C, D, H, W] volumes and [D, H, W] per-voxel labels: depth is third from last
+                if (kids and all(self.enabled(k) for k in kids) and len(dims) in (3, 4)
+                        and dims[-3] % depth == 0 and dims[-2] % height == 0):
+                    dl, hl = dims[-3] // depth, dims[-2] // height
+                    ax = len(dims) - 2            # depth axis of the mini-batch tensor
+                    slicers[f] = [(ax, self.depth_rank * dl, (self.depth_rank + 1) * dl, 0),
+                                  (ax + 1, self.height_rank * hl, (self.height_rank + 1) * hl, 0)]
                     self.input_halo[l.name] = 0
             tr.data_coordinator.field_slices = slicers
             self.sliced_fields = set(slicers)
@@ -190,13 +192,14 @@ class DistconvContext:
                 kids = [model.layers_by_name[c] for c in l.child_names]
                 if kids and all(self.enabled(k) for k in kids):
                     dims = tr.data_coordinator.dims(l.params.data_field or "samples")
-                    if len(dims) == 4 and dims[1] % depth == 0:
-                        dl = dims[1] // depth
+                    # [C, D, H, W] volumes and [D, H, W] per-voxel labels: depth is third from last
+                    if len(dims) in (3, 4) and dims[-3] % depth == 0:
+                        dl = dims[-3] // depth
                         # an input read by one convolution only is uploaded WITH its halo
                         # planes (zeros beyond the volume): the first layer then needs no
                         # exchange at all
-                        h = self._input_halo(kids) if self.fused else 0
-                        slicers[l.params.data_field or "samples"] = (2, self.depth_rank * dl,
+                        h = self._input_halo(kids) if (self.fused and len(dims) == 4) else 0
+                        slicers[l.params.data_field or "samples"] = (len(dims) - 2, self.depth_rank * dl,
                                                                      (self.depth_rank + 1) * dl, h)
                         self.input_halo[l.name] = h
             tr.data_coordinator.field_slices = slicers
@@ -297,11 +300,13 @@ class DistconvContext:
             elif have == REPLICATED and want == SAMPLE:
                 out.append(x[self.spatial_rank::self.spatial_size])
             elif have == REPLICATED and want == SPATIAL:
-                dl = x.shape[2] // self.depth_groups
-                x = x[:, :, self.depth_rank * dl:(self.depth_rank + 1) * dl]
+                # depth is the third dimension from the last ([N, C, D, H, W] and [N, D, H, W])
+                ax = x.dim() - 3
+                dl = x.shape[ax] // self.depth_groups
+                x = x.narrow(ax, self.depth_rank * dl, dl)
                 if self.height_groups > 1:
-                    hl = x.shape[3] // self.height_groups
-                    x = x[:, :, :, self.height_rank * hl:(self.height_rank + 1) * hl]
+                    hl = x.shape[ax + 1] // self.height_groups
+                    x = x.narrow(ax + 1, self.height_rank * hl, hl)
                 out.append(x)
             elif have == SPATIAL and want == SAMPLE:
                 out.append(_Redistribute.apply(x, self, True, pn))

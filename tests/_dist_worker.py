@@ -87,7 +87,7 @@ def unet(depth_groups, height_groups, steps, volume=16, base=4, levels=2):
     dr.reader.append(r)
     exp = lbann.proto.serialize.build_experiment(
         trainer=lbann.Trainer(mini_batch_size=2, random_seed=3), model=model, data_reader=dr,
-        optimizer=lbann.SGD(learn_rate=0.01, momentum=0.9))
+        optimizer=lbann.SGD(learn_rate=float(os.environ.get("LBANN_TEST_LR", "1e-5")), momentum=0.9))
     tr = ExecTrainer(exp)
     m = tr.build_model(exp.model)
     losses = []

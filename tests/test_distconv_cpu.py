@@ -162,3 +162,32 @@ def test_sample_x_depth_partition_on_four_ranks(tmp_path):
         assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], dist["losses"])
     for k, v in single["weight_norms"].items():
         assert abs(v - dist["weight_norms"][k]) <= 1e-3 * max(1.0, abs(v)), k
+
+
+def test_distconv_depth_x_height_grid_matches_single(tmp_path):
+    """Four ranks as a 2 x 2 grid over depth and height: halo planes are exchanged along
+    depth, then halo rows (with the corners) along height; where the extents run out the
+    bricks are gathered to sample-parallel.  Same losses and weights as one process."""
+    single = _run(1, ["cosmoflow", "1", "3"], str(tmp_path / "a.json"))
+    grid = _run(4, ["cosmoflow", "2", "3"], str(tmp_path / "b.json"), {"LBANN_TEST_HEIGHT_GROUPS": "2"},
+                timeout=600)
+    assert grid["world"] == 4 and grid["halo_bytes"] > 0
+    for a, b in zip(single["losses"], grid["losses"]):
+        assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], grid["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - grid["weight_norms"][k]) <= 1e-3 * max(1.0, abs(v)), k
+
+
+@pytest.mark.parametrize("ranks,depth,height", [(2, 2, 1), (2, 1, 2), (4, 2, 2)])
+def test_unet_on_spatial_partitions_matches_single(tmp_path, ranks, depth, height):
+    """A small 3-D U-Net (convolution + batch norm over all ranks + ReLU, max pooling, 2x
+    up-convolutions, skip concatenations, per-voxel labels sliced like the volume, softmax
+    cross-entropy summed over the bricks) split along depth, along height, and on a grid."""
+    single = _run(1, ["unet", "1", "1", "4"], str(tmp_path / "a.json"))
+    dist = _run(ranks, ["unet", str(depth), str(height), "4"], str(tmp_path / "b.json"), timeout=900)
+    assert dist["world"] == ranks
+    for a, b in zip(single["losses"], dist["losses"]):
+        assert abs(a - b) <= 1e-4 * max(1.0, abs(a)), (single["losses"], dist["losses"])
+    assert dist["losses"][-1] < dist["losses"][0]
+    for k, v in single["weight_norms"].items():
+        assert abs(v - dist["weight_norms"][k]) <= 1e-4 * max(1.0, abs(v)), k
