@@ -664,25 +664,17 @@ class SampleListReader(DataReader):
         return np.asarray(a, dtype=np.float32).reshape(self._fields[field])
 
 
-_UNAVAILABLE = {
-    "jag_conduit": "needs the Conduit library",
-    "ras_lipid": "needs the Conduit library",
-    "pilot2_molecular_reader": "reads the Pilot-2 molecular data set format",
-    "mesh": "reads the LLNL mesh data set format",
-    "nci": "reads the NCI data set format",
-}
-
-
-def build_reader(reader_pb) -> DataReader:
+def build_reader(reader_pb, metadata=None) -> DataReader:
+    """``metadata``: the experiment's ``DataSetMetaData`` message (key selection and
+    normalisation of the JAG reader)."""
+    from . import readers_science  # noqa: F401  (registers the application readers)
     name = reader_pb.name
     role = {"validation": "validate", "validate": "validate", "test": "test", "train": "train",
             "tournament": "tournament"}.get(reader_pb.role or "train", reader_pb.role)
-    if name in _UNAVAILABLE and name not in READER_REGISTRY:
-        raise NotImplementedError(f"data reader '{name}' is not available in this build: "
-                                  f"{_UNAVAILABLE[name]}")
     if name not in READER_REGISTRY:
         raise ValueError(f"unknown data reader '{name}'")
-    r = READER_REGISTRY[name](reader_pb, role=role)
+    cls = READER_REGISTRY[name]
+    r = cls(reader_pb, role=role, metadata=metadata) if getattr(cls, "KINDS", None) else cls(reader_pb, role=role)
     if len(reader_pb.transforms):
         from .transforms import build_pipeline
         r.transforms = build_pipeline(reader_pb.transforms)

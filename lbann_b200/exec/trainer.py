@@ -91,7 +91,8 @@ class ExecTrainer:
             return readers
         readers = {}
         for rp in self.proto.data_reader.reader:
-            r = build_reader(rp)
+            md = self.proto.data_set_metadata if self.proto.HasField("data_set_metadata") else None
+            r = build_reader(rp, md)
             r.setup(self.data_seed)
             readers[r.role] = r
         tr = readers.get("train")

@@ -198,3 +198,129 @@ def test_trainer_runs_with_the_data_store_option():
     tr.shutdown()
     opts.reset()
     assert store.stats["file_reads"] == 12 and store.stats["cache_hits"] >= 12
+
+
+def test_nci_reader_skips_metadata_columns_and_maps_classes(tmp_path):
+    lines = ["broken header line"]
+    rows = [("a", "b", 0.5, "rs", "e", 1.0, 2.0, 3.0), ("a", "b", 1.5, "xx", "e", 4.0, 5.0, 6.0)]
+    lines += [" ".join(str(v) for v in r) for r in rows]
+    (tmp_path / "nci.txt").write_text("\n".join(lines) + "\n")
+    r = build_reader(_proto("nci", data_filedir=str(tmp_path), data_filename="nci.txt")).setup(0)
+    assert r.num_samples() == 2 and r.dims("samples") == (3,)
+    b = r.fetch_batch([0, 1], ["samples", "labels", "responses"])
+    assert b["samples"].tolist() == [[1.0, 2.0, 3.0], [4.0, 5.0, 6.0]]
+    assert b["labels"].tolist() == [[1.0, 0.0], [0.0, 1.0]]            # "rs" -> class 0
+    assert b["responses"].reshape(-1).tolist() == [0.5, 1.5]
+
+
+def test_mesh_reader_channels_target_and_flips(tmp_path):
+    h, w, chans = 4, 6, ("Density", "Pressure")
+    rng = np.random.RandomState(0)
+    ref = {}
+    for c in chans + ("mask",):
+        os.makedirs(tmp_path / f"{c}16")
+        for i in range(3):
+            a = rng.rand(h, w).astype(np.float32)
+            ref[(c, i)] = a
+            a.tofile(tmp_path / f"{c}16" / f"{c}{i:03d}.bin")
+    fmt = f"suffix=16 height={h} width={w} index_length=3 channels={','.join(chans)}"
+    r = build_reader(_proto("mesh", data_filedir=str(tmp_path), format=fmt)).setup(0)
+    assert r.num_samples() == 3 and r.dims("samples") == (2, h, w) and r.dims("responses") == (h, w)
+    b = r.fetch_batch([2], ["samples", "responses"])
+    np.testing.assert_array_equal(b["samples"][0, 1].numpy(), ref[("Pressure", 2)])
+    np.testing.assert_array_equal(b["responses"][0].numpy(), ref[("mask", 2)])
+    # flips: the target of a sample is flipped like its channels
+    r2 = build_reader(_proto("mesh", data_filedir=str(tmp_path), format=fmt + " flips")).setup(0)
+    for _ in range(6):
+        b = r2.fetch_batch([1], ["samples", "responses"])
+        fh, fv = r2._flips[1]
+        want = ref[("mask", 1)][::-1 if fv else 1, ::-1 if fh else 1]
+        np.testing.assert_array_equal(b["responses"][0].numpy(), want)
+        np.testing.assert_array_equal(b["samples"][0, 0].numpy(), ref[("Density", 1)][::-1 if fv else 1, ::-1 if fh else 1])
+    with pytest.raises(ValueError, match="index length"):
+        build_reader(_proto("mesh", data_filedir=str(tmp_path),
+                            format=f"suffix=16 height={h} width={w} index_length=0")).setup(0)
+
+
+def test_pilot2_molecular_reader_neighbours_and_scaling(tmp_path):
+    frames, mols, beads, nv, hood = 2, 5, 3, 20, 2
+    rng = np.random.RandomState(1)
+    feats = rng.rand(frames, mols, beads, nv).astype(np.float32) * 100
+    nbrs = np.full((frames, mols, 2 * hood), -1, dtype=np.float32)
+    nbrs[1, 3] = [3, 0, -1, 4]                       # entry 0 is the molecule itself
+    np.savez(tmp_path / "p2.npz", features=feats, neighbors=nbrs)
+    r = build_reader(_proto("pilot2_molecular_reader", data_filedir=str(tmp_path), data_filename="p2.npz",
+                            num_neighbors=3, max_neighborhood=hood)).setup(0)
+    assert r.num_samples() == frames * mols and r.dims("samples") == (4, beads, nv)
+    x = r.fetch_batch([1 * mols + 3], ["samples"])["samples"][0].numpy()
+    scale = np.ones(nv, dtype=np.float32)
+    scale[:3] = 1 / 320.0
+    scale[8:] = 1 / 10.0
+    np.testing.assert_allclose(x[0], feats[1, 3] * scale, rtol=1e-6)
+    np.testing.assert_allclose(x[1], feats[1, 0] * scale, rtol=1e-6)      # neighbour 0 of the same frame
+    assert not x[2].any()                                                 # id -1: left at zero
+    np.testing.assert_allclose(x[3], feats[1, 4] * scale, rtol=1e-6)
+
+
+def test_ras_lipid_reader_sequences_and_normalisation(tmp_path):
+    rng = np.random.RandomState(2)
+    for f, n in (("a.npz", 5), ("b.npz", 4)):
+        np.savez(tmp_path / f, density_sig1=rng.rand(n, 13, 13, 14).astype(np.float64),
+                 states=rng.randint(0, 3, n).astype(np.float64), bbs=rng.rand(n, 184, 3).astype(np.float32),
+                 probs=rng.rand(n, 3))
+    table = np.stack([np.full(14, 2.0), np.full(14, -1.0), np.full(14, 0.5), np.full(14, 0.25)], axis=1)
+    np.savetxt(tmp_path / "norm.txt", table)
+    rp = _proto("ras_lipid", data_filedir=str(tmp_path), data_file_pattern="*.npz", metadata_filename="norm.txt",
+                format="seq_len=2")
+    r = build_reader(rp).setup(0)
+    assert r.num_samples() == 2 + 2                   # whole sequences only: 5 // 2 + 4 // 2
+    assert r.dims("samples") == (2, 13, 13, 14) and r.dims("labels") == (3,)
+    za = np.load(tmp_path / "a.npz")
+    b = r.fetch_batch([1], ["samples", "labels", "bbs"])
+    np.testing.assert_allclose(b["samples"][0].numpy(), (za["density_sig1"][2:4] + 1.0) / 3.0, rtol=1e-5, atol=1e-6)
+    assert int(b["labels"][0].argmax()) == int(za["states"][3])            # state of the last frame
+    np.testing.assert_allclose(b["bbs"][0].numpy(), za["bbs"][2:4], rtol=1e-6)
+    rp.format = "seq_len=1 z_score=1"
+    rz = build_reader(rp).setup(0)
+    assert rz.num_samples() == 9
+    x = rz.fetch_batch([0], ["samples"])["samples"][0].numpy()
+    np.testing.assert_allclose(x[0], (za["density_sig1"][0] - 0.5) / 0.25, rtol=1e-5, atol=1e-6)
+
+
+def test_jag_reader_key_selection_slices_and_normalisation(tmp_path):
+    rng = np.random.RandomState(3)
+    data = {}
+    for s in ("run0", "run1", "run2"):
+        for k in ("p0", "p1", "p2"):
+            data[f"{s}/inputs/{k}"] = rng.rand(1).astype(np.float32)
+        for k in ("yield", "tion", "bang"):
+            data[f"{s}/scalars/{k}"] = rng.rand(1).astype(np.float32)
+        data[f"{s}/images/view0"] = rng.rand(4, 4).astype(np.float32)
+    np.savez(tmp_path / "jag0.npz", **data)
+    (tmp_path / "list.txt").write_text(f"MULTI-SAMPLE_INCLUSION\n3 0 1\n{tmp_path}\njag0.npz 3 0 run0 run1 run2\n")
+    md = lbann.lbann_pb2.DataSetMetaData() if hasattr(lbann, "lbann_pb2") else None
+    if md is None:
+        from lbann_b200.proto import lbann_pb2
+        md = lbann_pb2.DataSetMetaData()
+    md.schema.jag_scalar_keys.extend(["tion", "yield"])
+    md.schema.jag_input_keys.extend(["p2", "p0"])
+    ind = md.schema.independent.add()
+    ind.pieces.extend([2, 1])                           # scalars, then images
+    dep = md.schema.dependent.add()
+    dep.pieces.append(3)                                # inputs
+    for scale, bias in ((2.0, 1.0), (3.0, -1.0)):
+        q = md.normalization.jag_scalar_normalization_params.add()
+        q.scale, q.bias = scale, bias
+    rp = _proto("jag_conduit", sample_list=str(tmp_path / "list.txt"))
+    r = build_reader(rp, md).setup(0)
+    assert r.num_samples() == 3 and r.dims("samples") == (2 + 16,) and r.dims("responses") == (2,)
+    assert r.slice_points("independent") == [0, 2, 18] and r.slice_points("dependent") == [0, 2]
+    b = r.fetch_batch([1], ["samples", "responses"])
+    want = np.concatenate([data["run1/scalars/tion"] * 2.0 + 1.0, data["run1/scalars/yield"] * 3.0 - 1.0,
+                           data["run1/images/view0"].reshape(-1)])
+    np.testing.assert_allclose(b["samples"][0].numpy(), want, rtol=1e-6)
+    np.testing.assert_allclose(b["responses"][0].numpy(),
+                               np.concatenate([data["run1/inputs/p2"], data["run1/inputs/p0"]]), rtol=1e-6)
+    md.schema.jag_input_keys.append("nope")
+    with pytest.raises(ValueError, match="not in the bundles"):
+        build_reader(rp, md).setup(0)
