@@ -649,6 +649,7 @@ class AlternateUpdates(ExecCallback):
 
     def _freeze(self, model, layers, frozen):
         for l in layers:
+            l.frozen = frozen              # layers without weights (identity_zero) switch on this
             for w in l.weights:
                 if w is None or w.slot is None:
                     continue

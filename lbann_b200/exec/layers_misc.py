@@ -734,7 +734,13 @@ class Evaluation(ExecLayer):
 
 @register("identity_zero")
 class IdentityZero(ExecLayer):
+    """The input while the layer is unfrozen, zeros (and no gradient) while it is frozen: the
+    switch on each side's loss in alternating GAN updates
+    (src/layers/transform/identity_zero.cpp:66-90)."""
+
     def forward(self, xs, training):
+        if self.frozen:
+            return [torch.zeros_like(xs[0])]
         return [xs[0]]
 
 

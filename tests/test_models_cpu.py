@@ -344,3 +344,94 @@ def test_roberta_matches_the_transformers_implementation(tmp_path):
     torch.testing.assert_close(got_p, ref.pooler_output, rtol=2e-4, atol=2e-4)
     tr.shutdown()
     opts.reset()
+
+
+# ------------------------------------------------------------------ application models
+def test_autoencoders_reduce_the_reconstruction_error():
+    from lbann_b200.models.applications import construct_autoencoder
+    torch.manual_seed(0)
+    dense = construct_autoencoder((1, 12, 12), "dense", hidden=(64, 32, 8))
+    losses = _train(dense, _reader(8, [1, 12, 12], "uniform"), steps=25, mb=8)
+    assert losses[-1] < 0.9 * losses[0], losses
+    conv = construct_autoencoder((1, 12, 12), "conv")
+    losses = _train(conv, _reader(8, [1, 12, 12], "uniform"), steps=25, mb=8)
+    assert losses[-1] < 0.95 * losses[0], losses
+
+
+def test_vae_objective_is_reconstruction_plus_kl():
+    from lbann_b200.models.applications import construct_vae
+    torch.manual_seed(0)
+    model = construct_vae(input_size=36, hidden=(32, 16), latent=4)
+    losses = _train(model, _reader(8, [36], "uniform"), steps=30, mb=8)
+    assert losses[0] > 0.8 * 36 * math.log(2)       # at least ~log 2 per pixel at the start, plus the KL term
+    assert losses[-1] < 0.9 * losses[0], losses
+
+
+def test_gan_alternates_discriminator_and_generator_updates():
+    from lbann_b200.models.applications import construct_gan
+    torch.manual_seed(0)
+    model = construct_gan(sample_size=36, noise_size=4, hidden=(16, 16))
+    o = opts.reset()
+    o.set("disable_cuda", True)
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=8, random_seed=3), model=model,
+        data_reader=_reader(8, [36], "uniform"), optimizer=lbann.Adam(learn_rate=1e-3, beta1=0.5, beta2=0.99, eps=1e-8))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    b = dc.next_batch("training")
+
+    def snap(prefix):
+        return {w.name: w.values.detach().clone() for w in m.weights if w.name.startswith(prefix)}
+    moved = []
+    for step in range(4):
+        g0, d0 = snap("gen_"), snap("disc_")
+        for cb in m.callbacks:
+            cb.on_batch_begin(m)
+        m.train_step(b.tensors, b.global_size)
+        m.ctx.step += 1
+        g1, d1 = snap("gen_"), snap("disc_")
+        moved.append((any(not torch.equal(g0[k], g1[k]) for k in g0), any(not torch.equal(d0[k], d1[k]) for k in d0)))
+    tr.shutdown()
+    # step 0: discriminator only; step 1: generator only; and so on
+    assert moved == [(False, True), (True, False), (False, True), (True, False)], moved
+
+
+def test_densenet_small_builds_and_trains():
+    from lbann_b200.models.applications import construct_densenet
+    torch.manual_seed(0)
+    model = construct_densenet(num_classes=5, growth=4, blocks=(2, 2), init_features=8, small_input=True)
+    losses = _train(model, _reader(8, [3, 8, 8], "normal", label_classes=5), steps=15, mb=8)
+    assert losses[-1] < losses[0], losses
+    full = construct_densenet()            # DenseNet-121: 58 dense layers x 2 convs + stem + 3 transitions
+    convs = [l for l in lbann.traverse_layer_graph(full.layers) if type(l).__name__ == "Convolution"]
+    assert len(convs) == 2 * (6 + 12 + 24 + 16) + 1 + 3
+
+
+def test_char_rnn_learns_a_repeating_sequence():
+    from lbann_b200.models.applications import construct_char_rnn
+    torch.manual_seed(0)
+    model = construct_char_rnn(vocab_size=11, sequence_length=9, embedding_size=8, hidden_size=16)
+    losses = _train(model, _reader(4, [9], "randint:11"), steps=40, mb=4,
+                    optimizer=lbann.Adam(learn_rate=2e-2, beta1=0.9, beta2=0.99, eps=1e-8))
+    assert losses[0] == pytest.approx(math.log(11), rel=0.3)
+    assert losses[-1] < 0.7 * losses[0], losses
+
+
+def test_dense_gcn_siamese_candle_and_jag_models_train():
+    from lbann_b200.models.applications import (construct_candle_combo, construct_dense_gcn,
+                                                construct_jag_wae, construct_siamese)
+    torch.manual_seed(0)
+    gcn = construct_dense_gcn(num_nodes=6, num_features=3, num_classes=2, hidden=(8, 8))
+    losses = _train(gcn, _reader(8, [6 * 3 + 36], "uniform", label_classes=2), steps=20, mb=8)
+    assert losses[-1] < losses[0], losses
+    siam = construct_siamese(num_patches=3, patch_dims=(1, 8, 8), num_classes=6, embed=8)
+    losses = _train(siam, _reader(8, [3, 8, 8], "normal", label_classes=6), steps=20, mb=8)
+    assert losses[-1] < losses[0], losses
+    combo = construct_candle_combo(cell_features=5, drug_features=7, hidden=(16, 16))
+    losses = _train(combo, _reader(8, [19], "normal", response_dims=[1]), steps=20, mb=8)
+    assert losses[-1] < losses[0], losses
+    wae = construct_jag_wae(sample_size=24, latent=3, enc_hidden=(16, 8), disc_hidden=(8,))
+    losses = _train(wae, _reader(8, [24], "normal"), steps=20, mb=8)
+    assert losses[-1] < losses[0], losses
