@@ -64,14 +64,15 @@ class BottleneckBlock(Module):
     """1x1 reduce -> 3x3 -> 1x1 expand (x4) with shortcut."""
 
     def __init__(self, in_channels, mid_channels, downsample, zero_init_residual,
-                 bn_statistics_group_size, name):
+                 bn_statistics_group_size, name, width=1):
         super().__init__()
         self.name, self.instance = name, 0
         self.out_channels = 4 * mid_channels
         stride = 2 if downsample else 1
         g = bn_statistics_group_size
-        self.conv1 = ConvBNRelu(mid_channels, 1, 1, 0, False, g, True, name + "_branch2a")
-        self.conv2 = ConvBNRelu(mid_channels, 3, stride, 1, False, g, True, name + "_branch2b")
+        inner = mid_channels * width            # wide ResNets widen the inner convolutions only
+        self.conv1 = ConvBNRelu(inner, 1, 1, 0, False, g, True, name + "_branch2a")
+        self.conv2 = ConvBNRelu(inner, 3, stride, 1, False, g, True, name + "_branch2b")
         self.conv3 = ConvBNRelu(self.out_channels, 1, 1, 0, zero_init_residual, g, False, name + "_branch2c")
         self.shortcut = None
         if downsample or in_channels != self.out_channels:
@@ -89,7 +90,7 @@ class ResNet(Module):
     global_count = 0
 
     def __init__(self, block, output_size, layer_sizes, layer_channels, zero_init_residual=True,
-                 bn_statistics_group_size=1, name=None):
+                 bn_statistics_group_size=1, name=None, width=1):
         super().__init__()
         ResNet.global_count += 1
         self.name = name or f"resnet_module{ResNet.global_count}"
@@ -100,8 +101,9 @@ class ResNet(Module):
         cin = layer_channels[0]
         for stage, (count, ch) in enumerate(zip(layer_sizes, layer_channels)):
             for i in range(count):
+                extra = {"width": width} if width != 1 else {}
                 b = block(cin, ch, downsample=(i == 0 and stage > 0), zero_init_residual=zero_init_residual,
-                          bn_statistics_group_size=g, name=f"{self.name}_layer{stage + 1}_block{i}")
+                          bn_statistics_group_size=g, name=f"{self.name}_layer{stage + 1}_block{i}", **extra)
                 self.blocks.append(b)
                 cin = b.out_channels
         self.fc = FullyConnectedModule(output_size, bias=False, name=self.name + "_fc")
