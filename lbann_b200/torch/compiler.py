@@ -191,6 +191,168 @@ def _f_flatten(name, ctx, x, *a, **k):
     return L.Reshape(x, dims=[-1], name=name)
 
 
+@register_module(nn.ConvTranspose1d, nn.ConvTranspose2d, nn.ConvTranspose3d)
+def _deconv(m, name, ctx, x):
+    ws = None
+    if ctx.with_weights:
+        ws = [_weights(m.weight, name + "_kernel")] + ([_weights(m.bias, name + "_bias")] if m.bias is not None else [])
+    return L.Deconvolution(x, weights=ws, num_dims=len(m.kernel_size), out_channels=m.out_channels,
+                           kernel_size=list(m.kernel_size), stride=list(m.stride), padding=list(m.padding),
+                           output_padding=list(m.output_padding), dilation=list(m.dilation), groups=m.groups,
+                           has_bias=m.bias is not None, name=name)
+
+
+@register_module(nn.Embedding)
+def _embedding(m, name, ctx, x):
+    ws = [_weights(m.weight, name + "_table")] if ctx.with_weights else None
+    return L.Embedding(x, weights=ws, num_embeddings=m.num_embeddings, embedding_dim=m.embedding_dim,
+                       padding_idx=-1 if m.padding_idx is None else m.padding_idx, name=name)
+
+
+@register_module(nn.AdaptiveAvgPool2d, nn.AdaptiveAvgPool3d)
+def _global_pool(m, name, ctx, x):
+    size = m.output_size if isinstance(m.output_size, (tuple, list)) else (m.output_size,)
+    if any(v not in (1, None) for v in size):
+        raise NotImplementedError("lbann.torch: adaptive pooling is lowered for output size 1 only")
+    shape = ctx.shapes.get(x)
+    y = L.ChannelwiseMean(x, name=name)
+    return L.Reshape(y, dims=[shape[0]] + [1] * (len(shape) - 1), name=name + "_shape") if shape else y
+
+
+@register_module(nn.ELU)
+def _elu(m, name, ctx, x):
+    return L.Elu(x, alpha=m.alpha, name=name)
+
+
+@register_module(nn.SiLU)
+def _silu(m, name, ctx, x):
+    return L.Multiply(x, L.Sigmoid(x, name=name + "_gate"), name=name)
+
+
+@register_module(nn.LogSoftmax)
+def _logsoftmax(m, name, ctx, x):
+    return L.LogSoftmax(x, name=name)
+
+
+def _sample_dim(ctx, x, dim):
+    """A tensor dimension (mini-batch first, negative allowed) as a sample dimension."""
+    rank = len(ctx.shapes[x]) + 1
+    d = dim % rank
+    if d == 0:
+        raise NotImplementedError("lbann.torch: operations along the mini-batch dimension are not lowered")
+    return d - 1
+
+
+@register_function(torch.cat, torch.concat)
+def _f_cat(name, ctx, tensors, dim=0):
+    tensors = list(tensors)
+    return L.Concatenation(tensors, axis=_sample_dim(ctx, tensors[0], dim), name=name)
+
+
+@register_function(torch.matmul, operator.matmul)
+def _f_matmul(name, ctx, a, b):
+    return L.MatMul(a, b, name=name)
+
+
+@register_function(torch.reshape, torch.Tensor.reshape, torch.Tensor.view)
+def _f_reshape(name, ctx, x, *shape):
+    shape = list(shape[0]) if len(shape) == 1 and isinstance(shape[0], (tuple, list, torch.Size)) else list(shape)
+    return L.Reshape(x, dims=[int(v) for v in shape[1:]], name=name)       # the first entry is the mini-batch
+
+
+@register_function(torch.permute, torch.Tensor.permute)
+def _f_permute(name, ctx, x, *dims):
+    dims = list(dims[0]) if len(dims) == 1 and isinstance(dims[0], (tuple, list)) else list(dims)
+    if dims[0] != 0:
+        raise NotImplementedError("lbann.torch: the mini-batch dimension must stay first in a permutation")
+    return L.TensorPermute(x, axes=[d - 1 for d in dims[1:]], name=name)
+
+
+@register_function(torch.transpose, torch.Tensor.transpose)
+def _f_transpose(name, ctx, x, d0, d1):
+    rank = len(ctx.shapes[x])
+    axes = list(range(rank))
+    a, b = _sample_dim(ctx, x, d0), _sample_dim(ctx, x, d1)
+    axes[a], axes[b] = axes[b], axes[a]
+    return L.TensorPermute(x, axes=axes, name=name)
+
+
+@register_function(torch.mean, torch.Tensor.mean)
+def _f_mean(name, ctx, x, dim=None, keepdim=False):
+    shape = ctx.shapes[x]
+    dims = list(range(1, len(shape) + 1)) if dim is None else ([dim] if isinstance(dim, int) else list(dim))
+    dims = sorted(_sample_dim(ctx, x, d) for d in dims)
+    if dims == list(range(len(shape))):
+        return L.Reduction(x, mode="mean", name=name)
+    if dims == list(range(1, len(shape))):
+        y = L.ChannelwiseMean(x, name=name)
+        return L.Reshape(y, dims=[shape[0]] + [1] * (len(shape) - 1), name=name + "_keep") if keepdim else y
+    if len(dims) == 1:
+        # one dimension: bring it to the front and multiply by a constant row of 1 / extent
+        d = dims[0]
+        axes = [d] + [a for a in range(len(shape)) if a != d]
+        rest = [shape[a] for a in axes[1:]]
+        n_rest = 1
+        for v in rest:
+            n_rest *= v
+        y = x if d == 0 else L.TensorPermute(x, axes=axes, name=name + "_front")
+        y = L.Reshape(y, dims=[shape[d], n_rest], name=name + "_2d")
+        row = L.Constant(value=1.0 / shape[d], num_neurons=[1, shape[d]], name=name + "_row")
+        y = L.MatMul(row, y, name=name + "_sum")
+        out = list(shape)
+        if keepdim:
+            out[d] = 1
+        else:
+            del out[d]
+        return L.Reshape(y, dims=out, name=name)
+    raise NotImplementedError("lbann.torch: mean over one sample dimension, over all, or over all but the first")
+
+
+@register_function(F.softmax, torch.softmax, torch.Tensor.softmax)
+def _f_softmax(name, ctx, x, dim=-1, **k):
+    shape = ctx.shapes[x]
+    d = _sample_dim(ctx, x, dim)
+    if len(shape) == 1:
+        return L.Softmax(x, name=name)
+    if d == len(shape) - 1:
+        return L.ChannelwiseSoftmax(x, dim=-1, name=name) if len(shape) > 2 else L.ChannelwiseSoftmax(x, name=name)
+    if d == 0:
+        return L.Softmax(x, softmax_mode="channel", name=name)
+    raise NotImplementedError("lbann.torch: softmax over the first or the last sample dimension only")
+
+
+@register_function(operator.truediv, torch.div)
+def _f_div(name, ctx, a, b):
+    if isinstance(b, (int, float)):
+        return L.Scale(a, constant=1.0 / float(b), name=name)
+    return L.Divide(a, b, name=name)
+
+
+@register_function(operator.neg, torch.neg)
+def _f_neg(name, ctx, x):
+    return L.Negative(x, name=name)
+
+
+@register_function(torch.exp)
+def _f_exp(name, ctx, x):
+    return L.Exp(x, name=name)
+
+
+@register_function(torch.sqrt)
+def _f_sqrt(name, ctx, x):
+    return L.Sqrt(x, name=name)
+
+
+@register_function(F.silu)
+def _f_silu(name, ctx, x, **k):
+    return L.Multiply(x, L.Sigmoid(x, name=name + "_gate"), name=name)
+
+
+@register_function(F.leaky_relu)
+def _f_leaky(name, ctx, x, negative_slope=0.01, **k):
+    return L.LeakyRelu(x, negative_slope=negative_slope, name=name)
+
+
 def compile(module: nn.Module, with_weights: bool = True, **example_inputs) -> List[L.Layer]:
     """Lower ``module`` to LBANN layers.  ``example_inputs`` maps the module's argument names
     to example tensors WITH the mini-batch dimension (used for shape propagation); every
@@ -224,13 +386,32 @@ def compile(module: nn.Module, with_weights: bool = True, **example_inputs) -> L
             layer = conv(m, lname, ctx, *args)
         elif node.op == "call_function" or node.op == "call_method":
             key = node.target if node.op == "call_function" else getattr(torch.Tensor, node.target, None)
+            if node.op == "call_method" and key not in _FUNCTIONS and node.target in ("size", "contiguous"):
+                if node.target == "contiguous":
+                    env[node.name] = env[node.args[0].name]
+                    ctx.shapes.setdefault(env[node.name], ctx.shapes.get(env[node.args[0].name]))
+                    continue
+                raise NotImplementedError("lbann.torch: shapes must be static (x.size() in forward)")
             conv = _FUNCTIONS.get(key) or _FUNCTIONS.get(getattr(torch, str(node.target), None))
             if conv is None:
                 raise NotImplementedError(f"lbann.torch: no converter for function {node.target} "
                                           f"(node '{node.name}')")
-            args = [env[a.name] if isinstance(a, fx.Node) else a for a in node.args]
-            kwargs = {k: (env[v.name] if isinstance(v, fx.Node) else v) for k, v in node.kwargs.items()}
+            args = fx.node.map_arg(node.args, lambda n: env[n.name])          # also inside lists / tuples
+            kwargs = fx.node.map_arg(node.kwargs, lambda n: env[n.name])
             layer = conv(lname, ctx, *args, **kwargs)
+        elif node.op == "get_attr":
+            t = gm
+            for part in str(node.target).split("."):
+                t = getattr(t, part)
+            if not isinstance(t, torch.Tensor):
+                raise NotImplementedError(f"lbann.torch: attribute '{node.target}' is not a tensor")
+            trainable = isinstance(t, nn.Parameter) and t.requires_grad
+            w = _weights(t, lname + "_values", trainable) if with_weights else \
+                L.Weights(name=lname + "_values", optimizer=None if trainable else L.NoOptimizer())
+            layer = L.WeightsLayer(weights=w, dims=list(t.shape), name=lname)
+            env[node.name] = layer
+            ctx.shapes[layer] = tuple(t.shape)           # a parameter has no mini-batch dimension
+            continue
         elif node.op == "output":
             outs = node.args[0]
             outs = outs if isinstance(outs, (tuple, list)) else [outs]

@@ -232,3 +232,50 @@ def _fit_model(make, algo, epochs=2):
     obj, _, _ = m.reduce_statistics("training")
     tr.shutdown()
     return obj
+
+
+def test_torch_lowering_of_functions_parameters_and_token_models():
+    """fx lowering beyond Sequential stacks: residual adds, concatenation, a parameter used
+    directly in forward(), mean / transpose / matmul / softmax over sample dimensions, and an
+    embedding + transposed convolution model; outputs equal PyTorch's."""
+    import torch.nn as nn
+    import torch.nn.functional as F
+    import lbann_b200.torch as lt
+    opts.reset().set("disable_cuda", True)
+    torch.manual_seed(0)
+
+    class Block(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.q, self.k, self.v = nn.Linear(8, 8), nn.Linear(8, 8), nn.Linear(8, 8)
+            self.gate = nn.Parameter(torch.randn(5, 8) * 0.1)
+            self.norm = nn.LayerNorm(8)
+            self.head = nn.Linear(16, 3)
+
+        def forward(self, input):                      # [N, 5, 8]
+            q, k, v = self.q(input), self.k(input), self.v(input)
+            att = torch.softmax(torch.matmul(q, k.transpose(1, 2)) / 8 ** 0.5, dim=-1)
+            h = self.norm(input + torch.matmul(att, v) * self.gate)
+            pooled = torch.cat([h.mean(dim=1), F.silu(h).mean(dim=1)], dim=1)
+            return self.head(pooled)
+
+    net = Block()
+    x = torch.randn(4, 5, 8)
+    got = lbann.evaluate(lt.compile(net, input=x)[0], x.numpy())
+    torch.testing.assert_close(torch.from_numpy(got).reshape(4, 3), net(x).detach(), rtol=1e-4, atol=1e-5)
+
+    class Tokens(nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.emb = nn.Embedding(11, 6)
+            self.up = nn.ConvTranspose1d(6, 4, 2, stride=2)
+            self.pool = nn.AdaptiveAvgPool2d(1)
+
+        def forward(self, input):                      # [N, 7] token ids
+            h = self.emb(input).permute(0, 2, 1)       # [N, 6, 7]
+            return torch.exp(-self.up(h)).reshape(-1, 4, 14)
+
+    net = Tokens()
+    ids = torch.randint(0, 11, (3, 7))
+    got = lbann.evaluate(lt.compile(net, input=ids)[0], ids.float().numpy())
+    torch.testing.assert_close(torch.from_numpy(got).reshape(3, 4, 14), net(ids).detach(), rtol=1e-4, atol=1e-5)
