@@ -502,32 +502,24 @@ class SaveTopKModels(ExecCallback):
 
 @register("export_onnx")
 class ExportOnnx(ExecCallback):
-    """Model graph export.  The ``onnx`` package is not part of this environment, so the
-    graph (nodes, attributes, initialiser shapes) is written as JSON with ONNX operator
-    names; ``debug_string_filename`` receives the human-readable form
-    (src/callbacks/export_onnx.cpp)."""
-    _OPS = {"fully_connected": "Gemm", "convolution": "Conv", "deconvolution": "ConvTranspose",
-            "relu": "Relu", "leaky_relu": "LeakyRelu", "softmax": "Softmax", "pooling": "MaxPool",
-            "batch_normalization": "BatchNormalization", "sum": "Sum", "concatenation": "Concat",
-            "reshape": "Reshape", "identity": "Identity", "dropout": "Dropout", "elu": "Elu",
-            "log_softmax": "LogSoftmax", "layer_norm": "LayerNormalization", "matmul": "MatMul",
-            "embedding": "Gather", "slice": "Split", "permute": "Transpose"}
+    """Writes the trained model as an ONNX file (binary ``ModelProto``, opset 11) to
+    ``output_filename`` (default ``lbann.onnx``); ``debug_string_filename`` receives the text
+    form of the same message (src/callbacks/export_onnx.cpp).  The graph is built by
+    ``io/onnx_export.py``; the ``onnx`` package is not needed."""
 
     def on_train_end(self, model):
         if not is_master(model):
             return
-        import json
-        nodes = [{"name": l.name, "op_type": self._OPS.get(l.type, l.type), "input": l.parent_names + [
-            w.name for w in l.weights if w is not None], "output": [f"{l.name}_out{k}" for k in range(len(l.out_dims))],
-            "output_dims": [list(d) for d in l.out_dims]} for l in model.layers]
-        graph = {"ir_version": 7, "producer_name": "lbann_b200", "graph": {
-            "name": model.name, "node": nodes,
-            "initializer": [{"name": w.name, "dims": list(w.shape)} for w in model.weights]}}
-        with open(self.params.output_filename or "lbann.onnx.json", "w") as f:
-            json.dump(graph, f)
+        from google.protobuf import text_format
+        from ..io.onnx_export import export_model
+        mp = export_model(model)
+        with open(self.params.output_filename or "lbann.onnx", "wb") as f:
+            f.write(mp.SerializeToString())
         if self.params.debug_string_filename:
+            for t in mp.graph.initializer:          # values are in the binary file; keep the text readable
+                t.raw_data = b""
             with open(self.params.debug_string_filename, "w") as f:
-                json.dump(graph, f, indent=1)
+                f.write(text_format.MessageToString(mp))
 
 
 # =============================================================================== weights manipulation
