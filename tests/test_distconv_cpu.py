@@ -164,6 +164,20 @@ def test_sample_x_depth_partition_on_four_ranks(tmp_path):
         assert abs(v - dist["weight_norms"][k]) <= 1e-3 * max(1.0, abs(v)), k
 
 
+def test_distconv_eight_ranks_match_single(tmp_path):
+    """Depth split over eight ranks, mini-batch 8: the layout of the 8-GPU CosmoFlow run in
+    small (local depth 4 -> 2 -> 1, the last convolution sees ONE plane per rank with both
+    neighbours' halos, then the tensor is gathered to one sample per rank)."""
+    env = {"LBANN_TEST_MINI_BATCH": "8", "OMP_NUM_THREADS": "2"}
+    single = _run(1, ["cosmoflow", "1", "2"], str(tmp_path / "a.json"), env)
+    dist = _run(8, ["cosmoflow", "8", "2"], str(tmp_path / "b.json"), env, timeout=900)
+    assert dist["world"] == 8
+    for a, b in zip(single["losses"], dist["losses"]):
+        assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], dist["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - dist["weight_norms"][k]) <= 1e-3 * max(1.0, abs(v)), k
+
+
 def test_distconv_depth_x_height_grid_matches_single(tmp_path):
     """Four ranks as a 2 x 2 grid over depth and height: halo planes are exchanged along
     depth, then halo rows (with the corners) along height; where the extents run out the
