@@ -136,8 +136,8 @@ class DataCoordinator:
         r = st.reader
         st.order = r.indices.copy()
         if r.shuffle and mode in ("training", "tournament"):
-            rng = np.random.RandomState((self.seed * 7907 + st.epoch * 31 + 11) % (2 ** 31 - 1))
-            rng.shuffle(st.order)
+            from ..utils.random import data_order
+            st.order = data_order(self.seed, st.order, st.epoch)
 
     def start_epoch(self, mode: str):
         st = self.modes[mode]

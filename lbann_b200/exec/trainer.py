@@ -71,6 +71,9 @@ class ExecTrainer:
         self.timer_sync = False
         self.models = []
         self.io_threads = io_threads if io_threads is not None else (o.get_int("num_io_threads") or 2)
+        from ..utils.random import init_random
+        init_random(self.data_seed, self.comm.rank_in_world, self.comm.rank_in_trainer,
+                    self.comm.trainer_rank, self.io_threads)
         self.background_io = (not bool(tp.serialize_io)) if background_io is None else background_io
         self.parallel = None
         self.distconv = None

@@ -147,9 +147,12 @@ def _save_rng(dirpath: str, rank: int, model):
     t = {"torch_cpu": torch.get_rng_state()}
     if model._gen is not None:
         t["model_generator"] = model._gen.get_state().cpu()
+    from ..utils.random import banks
     container.save(os.path.join(dirpath, "rng_state", f"rng_generator_{rank}"), t,
                    {"numpy": [str(x) if not isinstance(x, np.ndarray) else x.tolist()
-                              for x in np.random.get_state()]})
+                              for x in np.random.get_state()],
+                    # model / fast / data-sequence / LTFB / per-thread I/O generators of this rank
+                    "banks": banks().dumps()})
 
 
 def _load_rng(dirpath: str, rank: int, model):
@@ -163,6 +166,9 @@ def _load_rng(dirpath: str, rank: int, model):
     torch.set_rng_state(t["torch_cpu"])
     if "model_generator" in t:
         model.generator().set_state(t["model_generator"])
+    if meta.get("banks"):
+        from ..utils.random import banks
+        banks().loads(meta["banks"])
     st = meta.get("numpy")
     if st:
         np.random.set_state((st[0], np.asarray(st[1], dtype=np.uint32), int(st[2]), int(st[3]), float(st[4])))

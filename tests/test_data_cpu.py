@@ -324,3 +324,25 @@ def test_jag_reader_key_selection_slices_and_normalisation(tmp_path):
     md.schema.jag_input_keys.append("nope")
     with pytest.raises(ValueError, match="not in the bundles"):
         build_reader(rp, md).setup(0)
+
+
+def test_generator_banks_streams_and_checkpoint_state():
+    """Named generators: the data-sequence and LTFB streams agree across ranks and trainers,
+    model / fast / I/O streams differ per rank (I/O also per thread); the state survives a
+    round trip; an epoch's visiting order depends on (seed, epoch) only."""
+    from lbann_b200.utils.random import GeneratorBanks, data_order
+    a, b = GeneratorBanks(), GeneratorBanks()
+    a.init(7, rank_in_world=0, rank_in_trainer=0, trainer=0, num_io_threads=2)
+    b.init(7, rank_in_world=3, rank_in_trainer=1, trainer=1, num_io_threads=2)
+    assert a.data_seq_generator.integers(1 << 30, size=4).tolist() == b.data_seq_generator.integers(1 << 30, size=4).tolist()
+    assert a.ltfb_generator.integers(1 << 30, size=4).tolist() == b.ltfb_generator.integers(1 << 30, size=4).tolist()
+    assert a.generator.integers(1 << 30, size=4).tolist() != b.generator.integers(1 << 30, size=4).tolist()
+    assert a.io_generator(0).integers(1 << 30, size=4).tolist() != a.io_generator(1).integers(1 << 30, size=4).tolist()
+    saved = a.dumps()
+    want = [a.generator.random(), a.io_generator(1).random(), a.fast_generator.random()]
+    c = GeneratorBanks()
+    c.loads(saved)
+    assert [c.generator.random(), c.io_generator(1).random(), c.fast_generator.random()] == want
+    idx = np.arange(20)
+    assert data_order(5, idx, 2).tolist() == data_order(5, idx, 2).tolist() != data_order(5, idx, 3).tolist()
+    assert sorted(data_order(5, idx, 2).tolist()) == idx.tolist()
