@@ -11,8 +11,10 @@ request round.
 
 Takes the place of the reference's Conduit data store
 (src/data_ingestion/data_store_conduit.cpp: preload 1003-1100, exchange_data_by_sample
-1274-1400, owner maps 470-600); spilling to disk and checkpointing of the cache are not
-carried over: a lost cache is rebuilt from the files.
+1274-1400, owner maps 470-600).  ``spill`` / ``load_spilled`` write a rank's share of the
+cache with its ownership table to node-local storage and read it back
+(data_store_conduit.cpp:1600-1800, the ``--data_store_spill`` / checkpoint options): a restarted
+job, or the next job on the same nodes, starts with a warm cache and reads no sample file.
 """
 from __future__ import annotations
 
@@ -112,6 +114,51 @@ class DataStore:
     def fetch_batch(self, idx, fields):
         """Single-rank use: a plain cache in front of the reader."""
         return self.fetch_batch_global(idx, 0, 1, fields)
+
+
+    # ------------------------------------------------------------------ spill / restore
+    def spill(self, directory: str) -> str:
+        """Write this rank's cached samples and the ownership table to
+        ``<directory>/data_store_rank<r>.npz``; returns the file name.  Every rank writes its
+        own file (node-local storage is fine: only the owner ever reads it back)."""
+        import os
+        os.makedirs(directory, exist_ok=True)
+        path = os.path.join(directory, f"data_store_rank{self.rank}.npz")
+        with self.lock:
+            arrays = {"__owner_ids": np.asarray(sorted(self.owner_of), dtype=np.int64),
+                      "__owner_ranks": np.asarray([self.owner_of[i] for i in sorted(self.owner_of)], dtype=np.int64),
+                      "__meta": np.asarray([self.rank, self.world, int(self.preloaded)], dtype=np.int64)}
+            for i, sample in self.cache.items():
+                for f, a in sample.items():
+                    arrays[f"{i}/{f}"] = a
+        tmp = path + ".tmp.npz"
+        np.savez(tmp, **arrays)
+        os.replace(tmp, path)
+        return path
+
+    def load_spilled(self, directory: str) -> int:
+        """Restore what ``spill`` wrote for this rank; returns the number of samples now in
+        the cache.  The file must come from a run with the same number of ranks (ownership is
+        by rank)."""
+        import os
+        path = os.path.join(directory, f"data_store_rank{self.rank}.npz")
+        if not os.path.exists(path):
+            raise FileNotFoundError(f"data store: no spilled cache for rank {self.rank} in {directory}")
+        with np.load(path) as z:
+            rank, world, preloaded = (int(v) for v in z["__meta"])
+            if rank != self.rank or world != self.world:
+                raise ValueError(f"data store: {path} was written by rank {rank} of {world}, "
+                                 f"this is rank {self.rank} of {self.world}")
+            with self.lock:
+                self.owner_of = {int(i): int(r) for i, r in zip(z["__owner_ids"], z["__owner_ranks"])}
+                self.cache = {}
+                for key in z.files:
+                    if key.startswith("__"):
+                        continue
+                    i, _, f = key.partition("/")
+                    self.cache.setdefault(int(i), {})[f] = np.asarray(z[key], dtype=np.float32)
+                self.preloaded = bool(preloaded)
+        return len(self.cache)
 
     # ------------------------------------------------------------------ exchange
     def _sample_len(self, fields) -> int:

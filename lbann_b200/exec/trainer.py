@@ -148,8 +148,15 @@ class ExecTrainer:
                 pg = DataStore.make_group() if dp_size == self.comm.world_size and dp_size > 1 else None
                 world = dp_size if (pg is not None or dp_size == 1) else 1
                 for k, role in enumerate(sorted(readers)):
-                    readers[role] = DataStore(readers[role], dp_rank if world > 1 else 0, world, pg,
-                                              preload=o.get_bool("preload_data_store"), tag=k)
+                    spill = str(o.get("data_store_spill", "") or "")
+                    sdir = os.path.join(spill, role) if spill else ""
+                    warm = bool(sdir) and os.path.exists(os.path.join(sdir, f"data_store_rank{dp_rank if world > 1 else 0}.npz"))
+                    st = DataStore(readers[role], dp_rank if world > 1 else 0, world, pg,
+                                   preload=o.get_bool("preload_data_store") and not warm, tag=k)
+                    if warm:
+                        st.load_spilled(sdir)        # warm cache from an earlier run: no file is read
+                    st.spill_dir = sdir
+                    readers[role] = st
             self.data_coordinator = DataCoordinator(
                 readers, self.max_mini_batch_size, device=self.device, dp_rank=dp_rank,
                 dp_size=dp_size, seed=self.data_seed, io_threads=self.io_threads,
@@ -205,4 +212,8 @@ class ExecTrainer:
 
     def shutdown(self):
         if self.data_coordinator is not None:
+            for st in self.data_coordinator.modes.values():
+                r = getattr(st, "reader", None)
+                if getattr(r, "spill_dir", "") and hasattr(r, "spill"):
+                    r.spill(r.spill_dir)
             self.data_coordinator.shutdown()

@@ -23,6 +23,7 @@ _FLAGS = [
 _OPTIONS = {
     # name: (type, default)
     "ckpt_dir": (str, ""), "restart_dir": (str, ""), "load_model_weights_dir": (str, ""),
+    "data_store_spill": (str, ""),      # directory: stores load their spilled cache from it and write it back at the end
     "load_model_weights_dir_is_complete": (int, 0), "hydrogen_block_size": (int, 0),
     "metadata": (str, ""), "mini_batch_size": (int, 0), "model": (str, ""), "num_epochs": (int, -1),
     "num_io_threads": (int, 0), "max_rng_seeds": (int, 0), "optimizer": (str, ""),

@@ -346,3 +346,51 @@ def test_generator_banks_streams_and_checkpoint_state():
     idx = np.arange(20)
     assert data_order(5, idx, 2).tolist() == data_order(5, idx, 2).tolist() != data_order(5, idx, 3).tolist()
     assert sorted(data_order(5, idx, 2).tolist()) == idx.tolist()
+
+
+def test_data_store_spill_and_warm_restart(tmp_path):
+    """A store writes its cache and ownership table to disk; a new store over the same
+    reader restores it and serves every sample without touching the reader again.  Through
+    the trainer: --data_store_spill=<dir> makes the second run start warm."""
+    from lbann_b200.data.store import DataStore
+    _write_bundles(tmp_path)
+    (tmp_path / "list.txt").write_text(
+        f"MULTI-SAMPLE_INCLUSION\n4 8 2\n{tmp_path}\nbundle0.npz 2 2 s0_1 s0_2\nbundle2.npz 2 2 s2_0 s2_3\n")
+    rp = lbann.reader_pb2.Reader(name="npz_bundle", role="train", sample_list=str(tmp_path / "list.txt"),
+                                 fraction_of_data_to_use=1.0)
+    first = DataStore(build_reader(rp).setup(0), preload=True)
+    want = first.fetch_batch([0, 1, 2, 3], ["samples", "responses"])
+    path = first.spill(str(tmp_path / "spill"))
+    assert os.path.exists(path)
+    again = DataStore(build_reader(rp).setup(0))
+    assert again.load_spilled(str(tmp_path / "spill")) == 4 and again.preloaded
+    got = again.fetch_batch([3, 2, 1, 0], ["samples", "responses"])
+    assert again.stats["file_reads"] == 0
+    torch.testing.assert_close(got["samples"], want["samples"].flip(0))
+    other = DataStore(build_reader(rp).setup(0), rank=1, world=2)
+    with pytest.raises(FileNotFoundError):
+        other.load_spilled(str(tmp_path / "spill"))
+
+    from lbann_b200.exec.trainer import ExecTrainer
+    from lbann_b200.utils import options as opts
+    x = lbann.Input(data_field="samples")
+    y = lbann.FullyConnected(lbann.Reshape(x, dims=[4]), num_neurons=1, has_bias=False, name="fc")
+    loss = lbann.MeanSquaredError(y, lbann.Input(data_field="responses"))
+    reads = []
+    for _ in range(2):
+        o = opts.reset()
+        o.set("disable_cuda", True)
+        o.set("use_data_store", True)
+        o.set("data_store_spill", str(tmp_path / "spill2"))
+        model = lbann.Model(1, layers=list(lbann.traverse_layer_graph(x)), objective_function=lbann.ObjectiveFunction([loss]))
+        dr = lbann.reader_pb2.DataReader()
+        dr.reader.append(rp)
+        exp = lbann.proto.serialize.build_experiment(trainer=lbann.Trainer(mini_batch_size=2), model=model,
+                                                     data_reader=dr, optimizer=lbann.SGD(learn_rate=0.01))
+        tr = ExecTrainer(exp)
+        m = tr.build_model(exp.model)
+        tr.train(m)
+        reads.append(tr.data_coordinator.modes["training"].reader.stats["file_reads"])
+        tr.shutdown()
+    opts.reset()
+    assert reads[0] == 4 and reads[1] == 0, reads
