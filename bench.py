@@ -431,6 +431,7 @@ def ours(args):
         "region_ms": [round(v, 3) for v in m["region_ms"]],
         "device_status": m["device_status"], "clocks": clocks,
         "distconv": halo, "sharded_optimizer": sharded,
+        "optimizer_state_bytes_per_rank": int(model.arena.state_bytes()),
         "cpu_cores_bound": len(getattr(trainer, "cpu_binding", None) or ()) or None,
     }
     if phase is not None and rank == 0:

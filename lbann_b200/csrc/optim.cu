@@ -175,7 +175,7 @@ fused_optimizer_vec_kernel(float* __restrict__ w, const G* __restrict__ grad,
                            const int* __restrict__ step_ptr,
                            const float* __restrict__ lr_scale_ptr,
                            const float* __restrict__ inv_scale_dev, int rank, int world,
-                           int own_chunks, OptPeers peers) {
+                           int own_chunks, OptPeers peers, int compact_state) {
   if (skip_flag && *skip_flag) return;
   if (inv_scale_dev) inv_scale *= *inv_scale_dev;
   const float step_t = step_ptr ? (float)(*step_ptr) : 1.f;
@@ -201,6 +201,9 @@ fused_optimizer_vec_kernel(float* __restrict__ w, const G* __restrict__ grad,
     const long long i = base + 4 * (long long)threadIdx.x;
     if (i >= end) continue;
     const int nv = end - i >= 4 ? 4 : (int)(end - i);
+    // optimizer state: at the element's arena offset, or - when only the owned blocks have
+    // state storage - at its position in the dense enumeration of this rank's chunks
+    const long long is = compact_state ? k * kOptChunk + 4 * (long long)threadIdx.x : i;
     float x[4], g[4], a0[4], a1[4];
     if (nv == 4) {
       const float4 xv = *reinterpret_cast<const float4*>(w + i);
@@ -220,33 +223,33 @@ fused_optimizer_vec_kernel(float* __restrict__ w, const G* __restrict__ grad,
 #pragma unroll
           for (int j = 0; j < 4; ++j) g[j] = to_f32<G>(e[j]);
         }
-        const float4 v0 = *reinterpret_cast<const float4*>(s0 + i);
+        const float4 v0 = *reinterpret_cast<const float4*>(s0 + is);
         a0[0] = v0.x; a0[1] = v0.y; a0[2] = v0.z; a0[3] = v0.w;
         if (has_s1) {
-          const float4 v1 = *reinterpret_cast<const float4*>(s1 + i);
+          const float4 v1 = *reinterpret_cast<const float4*>(s1 + is);
           a1[0] = v1.x; a1[1] = v1.y; a1[2] = v1.z; a1[3] = v1.w;
         }
       } else {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           g[j] = j < nv ? to_f32<G>(grad[i + j]) : 0.f;
-          a0[j] = j < nv ? s0[i + j] : 0.f;
-          a1[j] = (j < nv && has_s1) ? s1[i + j] : 0.f;
+          a0[j] = j < nv ? s0[is + j] : 0.f;
+          a1[j] = (j < nv && has_s1) ? s1[is + j] : 0.f;
         }
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) x[j] = opt_update_one(sg, x[j], g[j] * inv_scale, a0[j], a1[j]);
       if (nv == 4) {
-        *reinterpret_cast<float4*>(s0 + i) = make_float4(a0[0], a0[1], a0[2], a0[3]);
+        *reinterpret_cast<float4*>(s0 + is) = make_float4(a0[0], a0[1], a0[2], a0[3]);
         if (has_s1 && sg.kind == kOptAdam)
-          *reinterpret_cast<float4*>(s1 + i) = make_float4(a1[0], a1[1], a1[2], a1[3]);
+          *reinterpret_cast<float4*>(s1 + is) = make_float4(a1[0], a1[1], a1[2], a1[3]);
         *reinterpret_cast<float4*>(w + i) = make_float4(x[0], x[1], x[2], x[3]);
       } else {
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           if (j >= nv) continue;
-          s0[i + j] = a0[j];
-          if (has_s1 && sg.kind == kOptAdam) s1[i + j] = a1[j];
+          s0[is + j] = a0[j];
+          if (has_s1 && sg.kind == kOptAdam) s1[is + j] = a1[j];
           w[i + j] = x[j];
         }
       }
@@ -434,12 +437,14 @@ int lb_unscale_check(void* grad, long long n, float inv_scale, const float* inv_
 // peer-mapped; entry `rank` is ignored).  With world == 1 it is the whole update and also
 // refreshes the 16-bit copy; with world > 1 the 16-bit copy is left to a cast of the arena
 // once every rank's stores have landed.
-int lb_fused_optimizer_sharded(float* w, const void* grad, float* s0, float* s1, void* w16,
-                               const void* segs, int nseg, long long total, float inv_scale,
-                               const int* skip_flag, const int* step_ptr,
-                               const float* lr_scale_ptr, const float* inv_scale_dev,
-                               int grad_dtype, int w16_dtype, int rank, int world, int own_chunks,
-                               void* const* peer_w, void* stream_) {
+// compact_state != 0: s0 / s1 hold state for the owned blocks only, densely, in block order
+// (owned block j = arena block j * world + rank): ceil-divided share of the arena per rank.
+int lb_fused_optimizer_sharded2(float* w, const void* grad, float* s0, float* s1, void* w16,
+                                const void* segs, int nseg, long long total, float inv_scale,
+                                const int* skip_flag, const int* step_ptr,
+                                const float* lr_scale_ptr, const float* inv_scale_dev,
+                                int grad_dtype, int w16_dtype, int rank, int world, int own_chunks,
+                                void* const* peer_w, int compact_state, void* stream_) {
   using namespace lb;
   if (total <= 0 || nseg <= 0) return 0;
   if (world < 1 || world > 8 || rank < 0 || rank >= world || own_chunks < 1) return -1;
@@ -457,13 +462,24 @@ int lb_fused_optimizer_sharded(float* w, const void* grad, float* s0, float* s1,
 #define LB_OPTV(G, W)                                                                        \
   fused_optimizer_vec_kernel<G, W><<<grid, 256, 0, s>>>(                                     \
       w, (const G*)grad, s0, s1, (W*)w16, sg, nseg, total, inv_scale, skip_flag, step_ptr,   \
-      lr_scale_ptr, inv_scale_dev, rank, world, own_chunks, peers)
+      lr_scale_ptr, inv_scale_dev, rank, world, own_chunks, peers, compact_state)
   const bool wb = (w16_dtype == kBF16);
   if (grad_dtype == kF32) { if (wb) LB_OPTV(float, __nv_bfloat16); else LB_OPTV(float, __half); }
   else if (grad_dtype == kBF16) { if (wb) LB_OPTV(__nv_bfloat16, __nv_bfloat16); else LB_OPTV(__nv_bfloat16, __half); }
   else { if (wb) LB_OPTV(__half, __nv_bfloat16); else LB_OPTV(__half, __half); }
 #undef LB_OPTV
   return (int)cudaGetLastError();
+}
+
+int lb_fused_optimizer_sharded(float* w, const void* grad, float* s0, float* s1, void* w16,
+                               const void* segs, int nseg, long long total, float inv_scale,
+                               const int* skip_flag, const int* step_ptr,
+                               const float* lr_scale_ptr, const float* inv_scale_dev,
+                               int grad_dtype, int w16_dtype, int rank, int world, int own_chunks,
+                               void* const* peer_w, void* stream_) {
+  return lb_fused_optimizer_sharded2(w, grad, s0, s1, w16, segs, nseg, total, inv_scale, skip_flag,
+                                     step_ptr, lr_scale_ptr, inv_scale_dev, grad_dtype, w16_dtype,
+                                     rank, world, own_chunks, peer_w, 0, stream_);
 }
 
 int lb_sqnorm(const void* x, long long n, float* out, int dtype, void* stream_) {

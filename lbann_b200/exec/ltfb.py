@@ -62,6 +62,7 @@ def unpack_model(model, state: Dict[str, torch.Tensor], with_optimizer=True):
                 for k, v in zip(("learn_rate", "momentum", "beta1", "beta2", "eps"), hp.tolist()):
                     if k in w.slot.hp:
                         w.slot.hp[k] = v
+    model.arena.commit_state()           # state kept for the owned blocks only: take this rank's share
     model.arena.refresh_compute()
 
 

@@ -185,17 +185,17 @@ class ExecWeights:
             return out
         a = self.arena
         if self.slot.kind == "sgd":
-            out["velocity"] = a.view(a.state0, self.slot)
+            out["velocity"] = a.state_view(0, self.slot)
         elif self.slot.kind in ("adam", "hypergradient_adam"):
             a.ensure_state1()
-            out["moment1"] = a.view(a.state0, self.slot)
-            out["moment2"] = a.view(a.state1, self.slot)
+            out["moment1"] = a.state_view(0, self.slot)
+            out["moment2"] = a.state_view(1, self.slot)
             if self.slot.kind == "hypergradient_adam":
                 if "old_gradient" not in self.slot.extra:
                     self.slot.extra["old_gradient"] = torch.zeros_like(a.view(a.master, self.slot))
                 out["old_gradient"] = self.slot.extra["old_gradient"]
         else:
-            out["cache"] = a.view(a.state0, self.slot)
+            out["cache"] = a.state_view(0, self.slot)
         return out
 
 

@@ -113,6 +113,8 @@ def load_model_state(model, tensors, meta, strict: bool = True):
             tk = f"weights/{w.name}/{k}"
             if tk in tensors:
                 t.copy_(tensors[tk].to(t.device).reshape(t.shape))
+    if getattr(model, "arena", None) is not None:
+        model.arena.commit_state()       # state kept for the owned blocks only: take this rank's share
     if "optimizer_step" in meta and model.device.type == "cuda":
         a = model.arena
         if a.step_dev is None:

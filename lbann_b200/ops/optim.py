@@ -44,6 +44,11 @@ def _lib():
                                                    c_void_p, c_int, c_ll, c_float, c_void_p, c_void_p,
                                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
                                                    c_void_p, c_void_p]
+        lib.lb_fused_optimizer_sharded2.restype = c_int
+        lib.lb_fused_optimizer_sharded2.argtypes = [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                                    c_void_p, c_int, c_ll, c_float, c_void_p, c_void_p,
+                                                    c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                                    c_void_p, c_int, c_void_p]
         lib.lb_amp_update.restype = c_int
         lib.lb_amp_update.argtypes = [c_void_p, c_void_p, c_void_p, c_float, c_float, c_float, c_void_p]
         lib.lb_sqnorm.restype = c_int
@@ -134,6 +139,8 @@ class ParameterArena:
         self.step_dev = None      # int32[1] on the device: optimizer step number
         self.lr_scale_dev = None  # float32[1] on the device: global learning-rate multiplier
         self.shard: Optional[ArenaShard] = None   # set when the update is sharded over ranks
+        self.state_compact = False    # optimizer state stored for the owned blocks only
+        self._full_state = None       # [state0, state1] at full size while a gathered copy is in use
 
     # ---- layout
     def reserve(self, name: str, shape) -> Slot:
@@ -164,7 +171,74 @@ class ParameterArena:
 
     def ensure_state1(self):
         if self.state1 is None:
-            self.state1 = torch.zeros_like(self.master)
+            self.state1 = torch.zeros_like(self.state0)       # full size, or the owned share when compact
+
+    # ---- optimizer state for the owned blocks only (memory sharded over the ranks)
+    def _block_counts(self):
+        sh = self.shard
+        nchunks = (self.total + CHUNK - 1) // CHUNK
+        nblocks = (nchunks + sh.own_chunks - 1) // sh.own_chunks
+        mine = (nblocks - sh.rank + sh.world - 1) // sh.world
+        return nblocks, mine
+
+    def _pack_state(self, full: torch.Tensor) -> torch.Tensor:
+        """Owned blocks of a full-size state tensor, densely, in block order."""
+        sh = self.shard
+        nblocks, mine = self._block_counts()
+        padded = torch.zeros(nblocks * sh.own_elems, dtype=full.dtype, device=full.device)
+        padded[:min(full.numel(), padded.numel())] = full.reshape(-1)[:padded.numel()]
+        return padded.view(nblocks, sh.own_elems)[sh.rank::sh.world].reshape(-1).clone()
+
+    def _unpack_state(self, compact: torch.Tensor) -> torch.Tensor:
+        """Full-size tensor with this rank's blocks filled in and zeros elsewhere."""
+        sh = self.shard
+        nblocks, mine = self._block_counts()
+        padded = torch.zeros(nblocks * sh.own_elems, dtype=compact.dtype, device=compact.device)
+        padded.view(nblocks, sh.own_elems)[sh.rank::sh.world] = compact.view(mine, sh.own_elems)
+        return padded[:self.master.numel()] if padded.numel() >= self.master.numel() else \
+            torch.cat([padded, padded.new_zeros(self.master.numel() - padded.numel())])
+
+    def compact_state(self) -> None:
+        """Keep optimizer state for the blocks this rank owns only: the moments of a sharded
+        update are never read elsewhere, so 8 of Adam's 18 bytes per parameter shrink to 8 / world
+        (what the reference's sharded weights do for their optimizer state,
+        src/weights/data_type_weights.cpp:244-283).  Call once, after the shard is installed and
+        before the first step (the storage must not move once a step has been captured)."""
+        if self.shard is None or self.shard.world <= 1 or self.state_compact or self.state0 is None:
+            return
+        old0, old1 = self.state0, self.state1
+        self.state0 = self._pack_state(old0)
+        self.state1 = self._pack_state(old1) if old1 is not None else None
+        self.state_compact = True
+        self._full_state = None
+
+    def state_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in (self.state0, self.state1) if t is not None)
+
+    def state_view(self, which: int, slot: Slot) -> torch.Tensor:
+        """A weight tensor's slice of optimizer state ``which`` (0 / 1).  With compact state this
+        is a view of the gathered full-size copy (``gather_sharded_state`` makes it whole across
+        the ranks; ``commit_state`` writes changes back into the owned share)."""
+        if not self.state_compact:
+            return self.view(self.state0 if which == 0 else self.state1, slot)
+        if self._full_state is None:
+            self._full_state = [self._unpack_state(self.state0),
+                                self._unpack_state(self.state1) if self.state1 is not None else None]
+        if which == 1 and self._full_state[1] is None:
+            self.ensure_state1()
+            self._full_state[1] = self._unpack_state(self.state1)
+        return self.view(self._full_state[which], slot)
+
+    def commit_state(self) -> None:
+        """Write a gathered full-size copy that was modified (checkpoint restart, model
+        exchange) back into the owned share, in place, and drop the copy."""
+        if not self.state_compact or self._full_state is None:
+            return
+        self.state0.copy_(self._pack_state(self._full_state[0]))
+        if self._full_state[1] is not None:
+            self.ensure_state1()
+            self.state1.copy_(self._pack_state(self._full_state[1]))
+        self._full_state = None
 
     def view(self, buf: torch.Tensor, slot: Slot) -> torch.Tensor:
         return buf[slot.offset:slot.offset + slot.count].view(slot.shape if slot.shape else (1,))
@@ -190,7 +264,17 @@ class ParameterArena:
         model exchange): each rank clears the blocks it does not own and the ranks sum.
         ``allreduce_sum(tensor)`` sums in place over the group.  Collective."""
         sh = self.shard
-        if sh is None or sh.state_whole:
+        if self.state_compact:
+            # every rank contributes its blocks to a full-size copy; the sum is the whole state
+            self._full_state = [self._unpack_state(self.state0),
+                                self._unpack_state(self.state1) if self.state1 is not None else None]
+            for st in self._full_state:
+                if st is not None:
+                    allreduce_sum(st)
+            sh.state_whole = True
+            return
+        # (no short cut on ``state_whole``: a replayed graph steps without passing through here)
+        if sh is None:
             return
         mask = sh.owner_mask(self.state0.numel(), self.state0.device)
         for st in (self.state0, self.state1):
@@ -242,14 +326,16 @@ class ParameterArena:
                 self.step_dev.sub_(skip_flag.to(torch.int32))   # a skipped step is not counted
             s1 = self.state1 if self.state1 is not None else self.state0
             sh = self.shard
-            rc = _lib().lb_fused_optimizer_sharded(
+            if self._full_state is not None and not torch.cuda.is_current_stream_capturing():
+                self.commit_state()      # a gathered copy may have been written to (restart, exchange)
+            rc = _lib().lb_fused_optimizer_sharded2(
                 self.master.data_ptr(), self.grad.data_ptr(), self.state0.data_ptr(),
                 s1.data_ptr(), native.ptr(self.compute), segs.data_ptr(), len(self.slots),
                 self.total, float(inv_scale), native.ptr(skip_flag), self.step_dev.data_ptr(),
                 self.lr_scale_dev.data_ptr(), native.ptr(inv_scale_dev), native.dtype_code(self.grad.dtype),
                 native.dtype_code(self.compute.dtype) if self.compute is not None else native.DT_BF16,
                 sh.rank if sh else 0, sh.world if sh else 1, sh.own_chunks if sh else 1,
-                sh.peer_master if sh else None, native.stream_ptr())
+                sh.peer_master if sh else None, 1 if self.state_compact else 0, native.stream_ptr())
             native.check(rc, "lb_fused_optimizer_sharded")
             native.count_launch()
             if sh is not None:

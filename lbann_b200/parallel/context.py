@@ -196,6 +196,8 @@ class ParallelContext:
         peers = (c_void_p * self.world_size)(*mbuf.peer_ptrs)
         arena.shard = ArenaShard(self.rank, self.world_size, peers,
                                  after_step=lambda: self.group.barrier_device(3))
+        if not os.environ.get("LBANN_REPLICATED_OPTIMIZER_STATE"):
+            arena.compact_state()        # moments for the owned blocks only: 1 / world of the memory
 
     def sync_optimizer_state(self, model):
         """Collective: optimizer state sharded by ``_setup_sharded_update`` becomes whole on

@@ -341,3 +341,47 @@ def test_add_relu_fused_kernel():
     assert native.launches() == n1 and n1 == n0 + 1
     torch.testing.assert_close(c.grad, g)
     assert native.consume_status() == 0
+
+
+def test_sharded_update_with_state_for_owned_blocks_only():
+    """Two ranks emulated on one GPU (each its own arena; the 'peer' master is the other
+    arena's): every rank keeps Adam moments for its own blocks only (half the bytes), updates
+    them and stores the new values into both masters.  Masters and the gathered moments equal
+    an unsharded arena's after three steps."""
+    from lbann_b200.ops.native import c_void_p
+    from lbann_b200.ops.optim import ArenaShard, CHUNK, OWN_CHUNKS, ParameterArena
+    torch.manual_seed(5)
+    n1, n2 = 3 * OWN_CHUNKS * CHUNK + 777, 2 * OWN_CHUNKS * CHUNK - 55
+
+    def make():
+        a = ParameterArena("cuda", compute_dtype=torch.bfloat16)
+        s1, s2 = a.reserve("a", (n1,)), a.reserve("b", (n2,))
+        a.materialise()
+        s1.kind, s1.hp = "adam", {"learn_rate": 1e-2, "beta1": 0.9, "beta2": 0.95, "eps": 1e-8}
+        s2.kind, s2.hp = "sgd", {"learn_rate": 0.1, "momentum": 0.9}
+        return a
+    ref, ranks = make(), [make(), make()]
+    init = torch.randn(ref.master.numel(), device="cuda")
+    for a in [ref] + ranks:
+        a.master.copy_(init)
+        a.ensure_state1()
+    peers = (c_void_p * 2)(ranks[0].master.data_ptr(), ranks[1].master.data_ptr())
+    for r, a in enumerate(ranks):
+        a.shard = ArenaShard(r, 2, peers)
+        full_bytes = a.state_bytes()
+        a.compact_state()
+        assert a.state_bytes() <= 0.62 * full_bytes
+    for step in range(3):
+        grad = torch.randn(ref.master.numel(), device="cuda")
+        for a in [ref] + ranks:
+            a.grad.copy_(grad)
+            a.step()
+        torch.cuda.synchronize()
+    assert native.consume_status(False) == 0
+    for a in ranks:
+        torch.testing.assert_close(a.master, ref.master, rtol=1e-6, atol=1e-7)
+    for which, want in ((0, ref.state0), (1, ref.state1)):
+        got = sum(a._unpack_state(a.state0 if which == 0 else a.state1) for a in ranks)
+        if which == 1:      # the second moment exists for the Adam tensor only
+            got, want = got[:n1], want[:n1]
+        torch.testing.assert_close(got[:want.numel()], want, rtol=1e-6, atol=1e-7)

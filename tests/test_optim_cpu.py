@@ -104,3 +104,53 @@ def test_sharded_state_gather_restores_whole_state():
         assert torch.equal(a.state0, torch.arange(n, dtype=torch.float32))
         assert torch.equal(a.state1, torch.ones(n))
         assert a.shard.state_whole
+
+
+def test_compact_state_pack_gather_and_commit():
+    """Optimizer state kept for the owned blocks only: packing takes a rank's blocks in
+    block order, the gather (unpack + sum over ranks) restores the whole tensor, views of the
+    gathered copy can be written and committed back into the owned share."""
+    n = 5 * OWN_CHUNKS * CHUNK - 1234                  # a ragged last block
+    world = 2
+    arenas = []
+    for r in range(world):
+        a = ParameterArena(torch.device("cpu"))
+        a.reserve("w", (n // 2,))
+        a.reserve("v", (n - n // 2 - 64,))
+        a.materialise()
+        a.ensure_state1()
+        full0 = torch.arange(a.master.numel(), dtype=torch.float32)
+        full1 = -full0
+        a.state0.copy_(full0)
+        a.state1.copy_(full1)
+        a.shard = ArenaShard(r, world, None)
+        before = a.state_bytes()
+        a.compact_state()
+        assert a.state_compact
+        nblocks, mine = a._block_counts()
+        assert nblocks == 5 and mine == (3 if r == 0 else 2)
+        assert a.state_bytes() == 2 * 4 * mine * OWN_CHUNKS * CHUNK < 0.65 * before
+        arenas.append(a)
+    blk = OWN_CHUNKS * CHUNK
+    assert torch.equal(arenas[1].state0[:blk], full0[blk:2 * blk])          # rank 1's first block is block 1
+    pending = {}
+    for i, a in enumerate(arenas):
+        a.gather_sharded_state(lambda t, i=i: pending.setdefault(i, []).append(t))
+    for k in range(2):
+        total = pending[0][k] + pending[1][k]
+        for i in range(world):
+            pending[i][k].copy_(total)
+    for a in arenas:
+        for slot in a.slots:
+            assert torch.equal(a.state_view(0, slot), a.view(full0, slot))
+            assert torch.equal(a.state_view(1, slot), a.view(full1, slot))
+    # a restart writes new values into the views; the commit keeps this rank's blocks of them
+    a = arenas[0]
+    a.state_view(0, a.slots[1]).fill_(5.0)
+    want = full0.clone()
+    a.view(want, a.slots[1]).fill_(5.0)
+    a.commit_state()
+    assert a._full_state is None
+    back = a._unpack_state(a.state0)
+    own = a.shard.owner_mask(want.numel(), "cpu")
+    assert torch.equal(back[:a.total], torch.where(own, want, torch.zeros_like(want))[:a.total])
