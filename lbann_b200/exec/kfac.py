@@ -21,7 +21,11 @@ per sample, damped with ``damping_bn_err`` and inverted like the other factors.
 With ``distribute_precondition_compute`` (or ``inverse_strategy: "each"``) block i is
 inverted by data-parallel rank i mod P only and the inverses travel to the others (the
 reference spreads inverses over ranks the same way, kfac.cpp:480-620; its asynchronous
-secondary grid is replaced by this round-robin).  GRU blocks are not preconditioned.
+secondary grid is replaced by this round-robin).
+
+GRU layers (kfac_block_gru.cpp): per stacked layer and per product (input -> gates, hidden ->
+gates) one activation factor over samples x time steps and one error factor per gate; see
+``_precondition_gru``.
 """
 from __future__ import annotations
 
@@ -138,6 +142,11 @@ class KFAC(SGDTrainingAlgorithm):
                         and not getattr(l, "fused_into_parent", False):
                     self.blocks[l.name] = _Block(l)
                 continue
+            if l.type == "gru":
+                if l.name not in self.disable_layers and all(w.has_optimizer() for grp in l.ws for w in grp):
+                    l.kfac_capture = True
+                    self.blocks[l.name] = _Block(l)
+                continue
             if l.type not in ("fully_connected", "channelwise_fully_connected", "convolution"):
                 continue
             if l.name in self.disable_layers or not l.w.has_optimizer():
@@ -203,6 +212,55 @@ class KFAC(SGDTrainingAlgorithm):
             out.append(inv)
         return out
 
+    def _precondition_gru(self, blk, par, dp, index, global_batch, refresh, d_act, d_err):
+        """GRU block (src/execution_algorithms/kfac/kfac_block_gru.cpp): for every stacked
+        layer and each of its two products (input -> gates, hidden -> gates) one activation
+        factor A over (samples x time steps) of [input | 1] resp. [previous hidden | 1], and one
+        error factor G per gate (reset, update, new) from the gradient at that gate's
+        pre-activation; the gate's rows of the matrix and bias become G^-1 [dW | db] A^-1."""
+        l = blk.layer
+        H = l.hidden
+        caches = getattr(l, "kfac_cache", None) or []
+        if blk.A is None:
+            blk.A, blk.G, blk.Ainv, blk.Ginv = {}, {}, {}, {}
+        for li, (cap, (wih, whh, bih, bhh)) in enumerate(zip(caches, l.ws)):
+            if cap["g_gi"] is None or any(g is None for g in cap["g_gh"]):
+                continue
+            ones = lambda a: torch.cat([a, torch.ones(a.shape[0], 1, device=a.device)], 1)   # noqa: E731
+            prods = (("ih", ones(cap["x"].float().reshape(-1, cap["x"].shape[-1])),
+                      cap["g_gi"].float().reshape(-1, 3 * H), wih, bih),
+                     ("hh", ones(torch.stack(cap["h_prev"], 1).float().reshape(-1, H)),
+                      torch.stack(cap["g_gh"], 1).float().reshape(-1, 3 * H), whh, bhh))
+            for tag, a, g, W, b in prods:
+                if W.handle.grad is None:
+                    continue
+                g = g * global_batch                       # the objective is a mean over the mini-batch
+                key = (li, tag)
+                A = a.t() @ a / a.shape[0]
+                Gs = [g[:, k * H:(k + 1) * H].t() @ g[:, k * H:(k + 1) * H] / g.shape[0] for k in range(3)]
+                if dp > 1:
+                    for M in [A] + Gs:
+                        par.allreduce_sum_inplace(M)
+                        M /= dp
+                if key not in blk.A:
+                    blk.A[key], blk.G[key] = A, Gs
+                else:
+                    blk.A[key] = self.decay * blk.A[key] + (1 - self.decay) * A
+                    blk.G[key] = [self.decay * o + (1 - self.decay) * n for o, n in zip(blk.G[key], Gs)]
+                if refresh or key not in blk.Ainv:
+                    invs = self._inverses(par, index, [blk.A[key]] + blk.G[key],
+                                          [d_act ** 0.5] + [d_err ** 0.5] * 3)
+                    blk.Ainv[key], blk.Ginv[key] = invs[0], invs[1:]
+                gw = W.handle.grad.float().reshape(3 * H, -1)
+                gb = b.handle.grad.float().reshape(3 * H, 1) if b.handle.grad is not None else \
+                    torch.zeros(3 * H, 1, device=gw.device)
+                full = torch.cat([gw, gb], 1)
+                nat = torch.cat([blk.Ginv[key][k] @ full[k * H:(k + 1) * H] @ blk.Ainv[key] for k in range(3)], 0)
+                nat = nat * self.lr_factor
+                W.handle.grad.copy_(nat[:, :-1].reshape(W.handle.grad.shape))
+                if b.handle.grad is not None:
+                    b.handle.grad.copy_(nat[:, -1].reshape(b.handle.grad.shape))
+
     @torch.no_grad()
     def _precondition(self, model, step: int, global_batch: int):
         d_act = self._damping(self.damping_act, step)
@@ -214,6 +272,10 @@ class KFAC(SGDTrainingAlgorithm):
         for index, blk in enumerate(self.blocks.values()):
             l = blk.layer
             if blk.grad_out is None:
+                continue
+            if l.type == "gru":
+                self._precondition_gru(blk, par, dp, index, global_batch, refresh, d_act, d_err)
+                blk.grad_out = None
                 continue
             if l.type == "batch_normalization":
                 if l.scale.handle.grad is None or l.bias.handle.grad is None:

@@ -380,9 +380,21 @@ class GRU(ExecLayer):
             gi_all = F.linear(out, wih, bih)
             steps = []
             H = self.hidden
+            # K-FAC (exec/kfac.py) needs, per stacked layer, the inputs of both products and
+            # the error signals at their outputs: kept when it sets ``kfac_capture``
+            cap = None
+            if getattr(self, "kfac_capture", False) and gi_all.requires_grad:
+                cap = {"x": out.detach(), "h_prev": [], "g_gi": None, "g_gh": [None] * self.seq}
+                gi_all.register_hook(lambda g, c=cap: c.__setitem__("g_gi", g.detach()))
+                if l == 0:
+                    self.kfac_cache = []
+                self.kfac_cache.append(cap)
             for t in range(self.seq):
                 gi = gi_all[:, t]
                 gh = F.linear(h, whh, bhh)
+                if cap is not None:
+                    cap["h_prev"].append(h.detach())
+                    gh.register_hook(lambda g, c=cap, t=t: c["g_gh"].__setitem__(t, g.detach()))
                 r = torch.sigmoid(gi[:, :H] + gh[:, :H])
                 z = torch.sigmoid(gi[:, H:2 * H] + gh[:, H:2 * H])
                 n = torch.tanh(gi[:, 2 * H:] + r * gh[:, 2 * H:])

@@ -279,3 +279,84 @@ def test_torch_lowering_of_functions_parameters_and_token_models():
     ids = torch.randint(0, 11, (3, 7))
     got = lbann.evaluate(lt.compile(net, input=ids)[0], ids.float().numpy())
     torch.testing.assert_close(torch.from_numpy(got).reshape(3, 4, 14), net(ids).detach(), rtol=1e-4, atol=1e-5)
+
+
+def test_kfac_gru_block_preconditions_every_gate():
+    """The GRU block: factors from the captured inputs / previous hidden states and the
+    per-gate error signals; the preconditioned gradient of gate k is G_k^-1 [dW_k | db_k] A^-1
+    with the damped factors, and a K-FAC run on a GRU regression stays finite and improves."""
+    from lbann_b200.exec.kfac import KFAC
+    from lbann_b200.modules.rnn import GRU
+    o = opts.reset()
+    o.set("disable_cuda", True)
+    T, I, H = 5, 3, 4
+
+    def model():
+        x = lbann.Reshape(lbann.Input(data_field="samples"), dims=[T, I])
+        h0 = lbann.Constant(value=0.0, num_neurons=[1, H])
+        y = GRU(H, name="g")(x, h0)
+        pred = lbann.FullyConnected(lbann.Reshape(y, dims=[T * H]), num_neurons=2, has_bias=True, name="head")
+        loss = lbann.MeanSquaredError(pred, lbann.Input(data_field="responses"))
+        return lbann.Model(2, layers=list(lbann.traverse_layer_graph(x)), objective_function=lbann.ObjectiveFunction([loss]))
+
+    sgd = lbann.BatchedIterativeOptimizer("sgd", epoch_count=2)
+    algo = lbann.KFAC("kfac", sgd, damping_act="1e-2", damping_err="1e-2", kronecker_decay=0.9,
+                      update_intervals="1", compute_interval=1)
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=8, random_seed=11, training_algo=algo), model=model(),
+        data_reader=_reader(32, [T * I], "normal", response_dims=[2]), optimizer=lbann.SGD(learn_rate=0.05))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    k = tr.algorithm
+    assert isinstance(k, KFAC)
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    b = dc.next_batch("training")
+    k._setup(m)
+    k._ready = True
+    gru = next(l for l in m.layers if l.type == "gru")
+    assert gru.name in k.blocks and gru.kfac_capture
+    m.clear_gradients()
+    m.forward_prop(b.tensors, "training", b.global_size, 0)
+    k._capture(m)
+    obj = m.local_objective()
+    m.backward_prop(obj)
+    cap = gru.kfac_cache[0]
+    wih, whh, bih, bhh = gru.ws[0]
+    # captured error signals reproduce the layer's own gradients: dW_ih = sum_t g_gi^T x
+    g_gi, x = cap["g_gi"].reshape(-1, 3 * H), cap["x"].reshape(-1, I)
+    torch.testing.assert_close(g_gi.t() @ x, wih.handle.grad.reshape(3 * H, I), rtol=1e-4, atol=1e-6)
+    g_gh, hp = torch.stack(cap["g_gh"], 1).reshape(-1, 3 * H), torch.stack(cap["h_prev"], 1).reshape(-1, H)
+    torch.testing.assert_close(g_gh.t() @ hp, whh.handle.grad.reshape(3 * H, H), rtol=1e-4, atol=1e-6)
+    raw_w, raw_b = wih.handle.grad.clone().reshape(3 * H, I), bih.handle.grad.clone().reshape(3 * H, 1)
+    k._precondition(m, 0, b.global_size)
+    a = torch.cat([x, torch.ones(x.shape[0], 1)], 1)
+    A = a.t() @ a / a.shape[0]
+    Ainv = torch.linalg.inv(A + 0.1 * torch.eye(I + 1))
+    g = g_gi * b.global_size
+    for gate in range(3):
+        gk = g[:, gate * H:(gate + 1) * H]
+        Ginv = torch.linalg.inv(gk.t() @ gk / gk.shape[0] + 0.1 * torch.eye(H))
+        want = Ginv @ torch.cat([raw_w, raw_b], 1)[gate * H:(gate + 1) * H] @ Ainv
+        got = torch.cat([wih.handle.grad.reshape(3 * H, I), bih.handle.grad.reshape(3 * H, 1)], 1)[gate * H:(gate + 1) * H]
+        torch.testing.assert_close(got, want, rtol=1e-3, atol=1e-5)
+    tr.shutdown()
+    # and a whole run
+    exp2 = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=8, random_seed=11, training_algo=algo), model=model(),
+        data_reader=_reader(32, [T * I], "normal", response_dims=[2]), optimizer=lbann.SGD(learn_rate=0.02))
+    tr = ExecTrainer(exp2)
+    m = tr.build_model(exp2.model)
+    first = None
+    dc = tr.data_coordinator
+    losses = []
+    for epoch in range(3):
+        dc.start_epoch("training")
+        while True:
+            bb = dc.next_batch("training")
+            if bb is None:
+                break
+            tr.algorithm.train_mini_batch(tr, m, tr.context(m, "training"), bb, [])
+            losses.append(float(m.last_objective))
+    tr.shutdown()
+    assert all(math.isfinite(v) for v in losses) and sum(losses[-4:]) < sum(losses[:4]), losses
