@@ -605,7 +605,8 @@ def abort_and_restart(ckpt_dir, fail_step, epochs):
     from lbann_b200.callbacks import ExecCallback
     from test_lenet_cpu import build_lenet, make_reader
     o = opts.reset()
-    o.set("disable_cuda", True)
+    if os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cpu":
+        o.set("disable_cuda", True)
     images, labels, loss, acc = build_lenet()
     cbs = [lbann.CallbackCheckpoint(checkpoint_dir=ckpt_dir, checkpoint_epochs=1)]
     model = lbann.Model(epochs, layers=[images, labels], objective_function=loss,
@@ -633,7 +634,8 @@ def abort_and_restart(ckpt_dir, fail_step, epochs):
         ExecTrainer.build_model = orig
     w = {x.name: float(x.values.detach().double().norm()) for x in m.weights}
     res = {"world": int(os.environ.get("WORLD_SIZE", "1")), "weights": w, "epoch": m.ctx.epoch,
-           "step": m.ctx.step}
+           "step": m.ctx.step, "state_compact": bool(getattr(m.arena, "state_compact", False)),
+           "state_bytes": int(m.arena.state_bytes()), "master_bytes": int(m.arena.master.numel() * 4)}
     tr.shutdown()
     return res
 

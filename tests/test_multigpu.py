@@ -145,6 +145,23 @@ def test_ltfb_two_trainers_on_gpus(tmp_path, strategy):
         assert abs(a[k] - b[k]) <= 1e-4 * max(1.0, abs(a[k])), (strategy, k, a, b)
 
 
+@needs2
+def test_checkpoint_restart_with_optimizer_state_for_owned_blocks(tmp_path):
+    """Two GPUs, sharded update with momentum kept for the owned blocks only: a run that stops
+    after two epochs and a second process that resumes from its checkpoint for the third end
+    with the weights of an uninterrupted three-epoch run (the checkpoint gathers the state over
+    the ranks, the restart takes every rank's share of it back)."""
+    ref = _run(2, ["abort_restart", str(tmp_path / "ref"), "-1", "3"], str(tmp_path / "ref.json"), ENV, timeout=600)
+    ck = str(tmp_path / "ck")
+    first = _run(2, ["abort_restart", ck, "-1", "2"], str(tmp_path / "first.json"), ENV, timeout=600)
+    again = _run(2, ["abort_restart", ck, "-1", "3"], str(tmp_path / "again.json"), ENV, timeout=600)
+    assert first["epoch"] == 2 and again["epoch"] == 3 and again["step"] == ref["step"]
+    assert ref["state_compact"] and ref["state_bytes"] <= 0.6 * ref["master_bytes"] + 2 * 65536
+    for k, v in ref["weights"].items():
+        assert abs(v - again["weights"][k]) <= 1e-4 * max(1.0, abs(v)), (k, v, again["weights"][k])
+        assert abs(v - first["weights"][k]) > 0 or v == 0.0
+
+
 needs4 = pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
 
 
