@@ -1,0 +1,8 @@
+"""The openmpi flavour of the batch script (python/lbann/launcher/openmpi.py): header directives,
+parallel launch prefix and submit command of that scheduler; the class lives in
+``batch_script.py`` with the others."""
+from .batch_script import OpenMPIBatchScript  # noqa: F401
+
+
+def make_batch_script(**kwargs) -> OpenMPIBatchScript:
+    return OpenMPIBatchScript(**kwargs)

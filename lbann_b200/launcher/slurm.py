@@ -1,0 +1,8 @@
+"""The slurm flavour of the batch script (python/lbann/launcher/slurm.py): header directives,
+parallel launch prefix and submit command of that scheduler; the class lives in
+``batch_script.py`` with the others."""
+from .batch_script import SlurmBatchScript  # noqa: F401
+
+
+def make_batch_script(**kwargs) -> SlurmBatchScript:
+    return SlurmBatchScript(**kwargs)

@@ -3,8 +3,8 @@
 adjacency matrix ``[nodes, nodes]``; both products run on the batched tensor-core GEMM."""
 from __future__ import annotations
 
-from ..frontend import core as L
-from .base import ChannelwiseFullyConnectedModule, Module
+from ...frontend import core as L
+from ..base import ChannelwiseFullyConnectedModule, Module
 
 
 class DenseGCNConv(Module):

@@ -7,3 +7,4 @@ converters.py:64-193).  Unknown modules / functions raise with the node's name;
 ``register_module`` / ``register_function`` add converters.
 """
 from .compiler import compile, register_function, register_module  # noqa: F401
+from .opaque import register_opaque  # noqa: F401

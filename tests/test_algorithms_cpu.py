@@ -360,3 +360,26 @@ def test_kfac_gru_block_preconditions_every_gate():
             losses.append(float(m.last_objective))
     tr.shutdown()
     assert all(math.isfinite(v) for v in losses) and sum(losses[-4:]) < sum(losses[:4]), losses
+
+
+def test_torch_lowering_keeps_registered_user_modules_whole():
+    """A user module whose forward cannot be traced (data-dependent branch) is lowered through
+    a converter registered for its class; the tracer does not look inside it."""
+    import torch.nn as nn
+    import lbann_b200.torch as lt
+    opts.reset().set("disable_cuda", True)
+
+    class Gate(nn.Module):
+        def forward(self, x):
+            if float(x.sum()) > 1e30:            # not traceable
+                return x
+            return torch.relu(x) * 2.0
+
+    @lt.register_opaque(Gate)
+    def _gate(m, name, ctx, x):
+        return lbann.Scale(lbann.Relu(x, name=name + "_relu"), constant=2.0, name=name)
+
+    net = nn.Sequential(nn.Linear(6, 5), Gate(), nn.Linear(5, 2))
+    x = torch.randn(3, 6)
+    got = lbann.evaluate(lt.compile(net, input=x)[0], x.numpy())
+    torch.testing.assert_close(torch.from_numpy(got), net(x).detach(), rtol=1e-4, atol=1e-5)

@@ -140,3 +140,78 @@ def test_single_tensor_reader_functions(tmp_path, monkeypatch):
     mod = importlib.reload(importlib.import_module("lbann_b200.contrib.single_tensor_data_reader"))
     assert mod.num_samples() == 4 and mod.sample_dims() == (3,)
     np.testing.assert_array_equal(mod.get_sample(2), data[2])
+
+
+def test_smiles_tokenizer_and_masked_molecule_dataset(tmp_path):
+    from lbann_b200.contrib.data.chem_tokenizers import ChemTokenizer, ChemTokenType, SMILESTokenizer, TOKENIZERS
+    from lbann_b200.contrib.data.molecule_dataset import ChemTextDataset, IGNORE, TextDatasetWithOffsets
+    mols = ["CC(=O)Oc1ccccc1C(=O)O", "zinc42|C[C@H](N)C(=O)O", "BrCCCl", "[Na+].[Cl-]", "C%12CC%12"]
+    tok = SMILESTokenizer(vocab=ChemTokenizer.build_vocab(mols, SMILESTokenizer(vocab=list(
+        ("[PAD]", "[UNK]", "[CLS]", "[SEP]", "[MASK]"))).tokenize))
+    assert tok.tokenize(mols[2]) == ["Br", "C", "C", "Cl"]                       # two-letter elements stay whole
+    assert tok.tokenize(mols[1])[:2] == ["C", "[C@H]"]                           # name before "|" dropped, bracket atom whole
+    assert tok.tokenize(mols[4]) == ["C", "%12", "C", "C", "%12"]
+    ids = tok.encode(mols[3], max_length=12)
+    assert len(ids) == 12 and ids[0] == tok.cls_token_id and ids.count(tok.pad_token_id) == 12 - 5
+    assert tok.decode(ids) == "[Na+].[Cl-]"
+    assert tok.encode("CSC")[2] == tok.unk_token_id                                  # an element the vocabulary lacks
+    with pytest.raises(ModuleNotFoundError):
+        TOKENIZERS[ChemTokenType.SELFIES]("x")
+    vocab_file, data_file = tmp_path / "vocab.txt", tmp_path / "mols.txt"
+    vocab_file.write_text("\n".join(tok.ids_to_tokens[i] for i in range(len(tok))) + "\n")
+    data_file.write_text("\n".join(mols) + "\n")
+    assert TextDatasetWithOffsets.write_offsets(str(data_file)) == 5
+    for offsets in (False, True):
+        ds = ChemTextDataset(str(data_file), str(vocab_file), seqlen=16, mlm_probability=0.5, attn_mask=True,
+                             use_offsets=offsets, seed=3)
+        assert len(ds) == 5 and ds.get_sample_dims().sample == [48]
+        s = ds[0].sample
+        inp, lab, att = s[:16].astype(int), s[16:32].astype(int), s[32:].astype(int)
+        clean = np.asarray(tok.encode(mols[0], max_length=16))
+        picked = lab != IGNORE
+        assert picked.any() and (lab[picked] == clean[picked]).all()
+        assert (inp[~picked] == clean[~picked]).all()                            # untouched positions keep their ids
+        assert not picked[0] and att.tolist() == (clean != tok.pad_token_id).astype(int).tolist()
+        np.testing.assert_array_equal(ds[0].sample, s)                           # deterministic per (seed, index)
+    import pickle
+    assert pickle.loads(pickle.dumps(ds))[1].sample.shape == (48,)
+
+
+def test_reference_import_paths_resolve():
+    """Module paths of the reference's Python package that scripts import directly."""
+    import importlib
+    for name in ("launcher.slurm", "launcher.lsf", "launcher.flux", "launcher.pjm", "launcher.openmpi",
+                 "models.alexnet", "modules.attention_allsubgraph", "modules.pytorch", "modules.graph.dense",
+                 "modules.graph.sparse", "modules.graph.utils", "proto.text2bin", "proto.bin2text",
+                 "torch.converters", "torch.helpers", "torch.lowering", "torch.opaque", "contrib.data.chem_tokenizers",
+                 "contrib.data.molecule_dataset", "contrib.lc.launcher", "contrib.nersc.systems"):
+        importlib.import_module("lbann_b200." + name)
+    from lbann_b200.modules.pytorch import PytorchLinear, PytorchMatmul
+    x = lbann.Input(data_field="samples")
+    y, shape = PytorchLinear(lbann.Reshape(x, dims=[2, 3, 4]), (2, 3, 4), 5, return_dims=True)
+    assert shape == (2, 3, 5)
+    (out,) = _evaluate(lambda inp: PytorchMatmul(lbann.Reshape(inp, dims=[2, 2, 3, 2]), (2, 2, 3, 2),
+                                                 lbann.Reshape(lbann.Slice(inp, axis=0, slice_points=[0, 16]),
+                                                               dims=[2, 2, 2, 2]), (2, 2, 2, 2)),
+                       np.arange(2 * 24, dtype=np.float32).reshape(2, 24))
+    a = np.arange(48, dtype=np.float32).reshape(2, 2, 2, 3, 2)
+    b = a.reshape(2, 24)[:, :16].reshape(2, 2, 2, 2, 2)
+    np.testing.assert_allclose(out.reshape(2, 2, 2, 3, 2), a @ b, rtol=1e-6)
+
+
+def test_prototext_binary_round_trip_tools(tmp_path):
+    from lbann_b200.proto.bin2text import bin2text
+    from lbann_b200.proto.text2bin import text2bin
+    x = lbann.Input(data_field="samples")
+    y = lbann.FullyConnected(x, num_neurons=3, name="fc")
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph(x)))
+    lbann.proto.serialize.save_prototext(str(tmp_path / "a.prototext"), trainer=lbann.Trainer(mini_batch_size=2),
+                                         model=model, data_reader=None, optimizer=lbann.SGD(learn_rate=0.1))
+    text2bin(str(tmp_path / "a.prototext"), str(tmp_path / "a.protobin"))
+    bin2text(str(tmp_path / "a.protobin"), str(tmp_path / "b.prototext"))
+    from google.protobuf import text_format
+    from lbann_b200.proto import lbann_pb2
+    m1, m2 = lbann_pb2.LbannPB(), lbann_pb2.LbannPB()
+    text_format.Parse(open(tmp_path / "a.prototext").read(), m1)
+    text_format.Parse(open(tmp_path / "b.prototext").read(), m2)
+    assert m1 == m2 and m1.model.layer[1].name == "fc" and y is not None
