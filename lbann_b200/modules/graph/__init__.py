@@ -198,7 +198,7 @@ class GatedGraphConv(_SparseConv):
 
     def __init__(self, input_channels, output_channels, num_nodes, num_layers=1, name=None):
         super().__init__()
-        from .rnn import ChannelwiseGRU
+        from ..rnn import ChannelwiseGRU
         if input_channels > output_channels:
             raise ValueError(f"node features ({input_channels}) cannot be wider than the output "
                              f"({output_channels})")
