@@ -27,6 +27,19 @@ _DTYPES = {
 }
 
 
+
+def rows2d(x):
+    """[N, ...] -> [N, features]; also for a rank that holds no sample of the mini-batch
+    (PyTorch cannot infer a -1 extent of an empty tensor)."""
+    n = x.shape[0]
+    if x.numel():
+        return x.reshape(n, -1)
+    f = 1
+    for d in x.shape[1:]:
+        f *= int(d)
+    return x.reshape(n, f)
+
+
 def register(*names):
     def deco(cls):
         for n in names:

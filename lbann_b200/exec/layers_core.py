@@ -14,7 +14,7 @@ import torch.nn.functional as F
 from ..ops import native, nn
 from ..ops import elementwise as ew
 from ..proto import lbann_pb2 as pb
-from .layer_base import ExecLayer, broadcast_list, prod, register
+from .layer_base import ExecLayer, broadcast_list, prod, register, rows2d
 from .weights import constant_default, he_normal_default
 
 _FUSABLE_ACT = {"relu": (native.ACT_RELU, 0.0)}
@@ -60,7 +60,7 @@ class FullyConnected(ExecLayer):
         return [out_dims]
 
     def forward(self, xs, training):
-        x = self.cast_in(xs[0]).reshape(xs[0].shape[0], -1)
+        x = rows2d(self.cast_in(xs[0]))
         par = self.model.parallel
         if par is not None and self.data_layout == "model_parallel" and par.tp_size > 1:
             y = par.tp_linear(self, x)
@@ -469,8 +469,8 @@ class Softmax(ExecLayer):
         n = x.shape[0]
         par = self.model.parallel
         if par is not None and self.data_layout == "model_parallel" and par.tp_size > 1:
-            return [par.tp_softmax(x.reshape(n, -1), self.log).reshape(x.shape)]
-        return [nn.softmax_lastdim(x.reshape(n, -1), self.log).reshape(x.shape)]
+            return [par.tp_softmax(rows2d(x), self.log).reshape(x.shape)]
+        return [nn.softmax_lastdim(rows2d(x), self.log).reshape(x.shape)]
 
 
 @register("log_softmax")
@@ -529,7 +529,7 @@ class CrossEntropy(ExecLayer):
         fused = getattr(self, "fused_logits", None)
         if self.params.use_labels:
             C = p.shape[1]
-            lab = xs[1].reshape(n, -1).long()
+            lab = rows2d(xs[1]).long()
             pm = p.reshape(n, C, -1).movedim(1, -1)            # n, positions, C
             if fused is not None:
                 loss = nn.softmax_cross_entropy(pm.contiguous(), lab)
@@ -541,8 +541,8 @@ class CrossEntropy(ExecLayer):
         t = self.cast_in(xs[1]).to(p.dtype).reshape(p.shape)
         if fused is not None:
             # parent softmax was folded away: p holds logits
-            lp = nn.softmax_lastdim(p.reshape(n, -1), log=True)
-            return [-(t.reshape(n, -1).float() * lp.float()).sum(1, keepdim=True)]
+            lp = nn.softmax_lastdim(rows2d(p), log=True)
+            return [-(rows2d(t).float() * lp.float()).sum(1, keepdim=True)]
         return [nn.sample_loss("cross_entropy", p, t).reshape(-1, 1)]
 
 
@@ -558,8 +558,8 @@ class CategoricalAccuracy(ExecLayer):
     def forward(self, xs, training):
         n = xs[0].shape[0]
         with torch.no_grad():
-            pred = xs[0].reshape(n, -1)
-            lab = xs[1].reshape(n, -1)
+            pred = rows2d(xs[0])
+            lab = rows2d(xs[1])
             if lab.shape[1] == pred.shape[1]:
                 lab = lab.argmax(1)
             else:
@@ -656,7 +656,7 @@ class EntrywiseBatchNormalization(ExecLayer):
     def forward(self, xs, training):
         x = self.cast_in(xs[0])
         n = x.shape[0]
-        xf = x.reshape(n, -1).float()
+        xf = rows2d(x).float()
         rm, rv = self.run_mean.handle.master.detach(), self.run_var.handle.master.detach()
         if training:
             par = self.model.parallel
@@ -823,7 +823,7 @@ class OperatorLayer(ExecLayer):
             return self._select(msg, xs)
         if short == "log_softmax":
             n = xs[0].shape[0]
-            return nn.softmax_lastdim(xs[0].reshape(n, -1), True).reshape(xs[0].shape)
+            return nn.softmax_lastdim(rows2d(xs[0]), True).reshape(xs[0].shape)
         if short in ew.UNARY_CODE:
             c = float(getattr(msg, "constant", 0.0)) if hasattr(msg, "constant") else 0.0
             return ew.unary(short, xs[0], c, 0.0)

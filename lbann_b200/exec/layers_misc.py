@@ -18,7 +18,7 @@ import torch.nn.functional as F
 from ..ops import native, nn
 from ..ops import elementwise as ew
 from ..ops.gemm import gemm
-from .layer_base import ExecLayer, broadcast_list, prod, register
+from .layer_base import ExecLayer, broadcast_list, prod, register, rows2d
 
 
 # =============================================================================== shape / routing
@@ -167,7 +167,7 @@ class Crop(ExecLayer):
         return [tuple(int(d) for d in self.params.dims)]
 
     def forward(self, xs, training):
-        x, pos = xs[0], xs[1].reshape(xs[1].shape[0], -1).float()
+        x, pos = xs[0], rows2d(xs[1]).float()
         out_d, in_d = self.out_dims[0], self.in_dims[0]
         outs = []
         for n in range(x.shape[0]):
@@ -344,7 +344,7 @@ class CategoricalRandom(ExecLayer):
     """One-hot sample from the input probabilities during training, arg-max otherwise."""
 
     def forward(self, xs, training):
-        p = xs[0].reshape(xs[0].shape[0], -1).float()
+        p = rows2d(xs[0]).float()
         idx = torch.multinomial(p.clamp(min=0) + 1e-30, 1).squeeze(1) if training else p.argmax(1)
         return [F.one_hot(idx, p.shape[1]).to(xs[0].dtype).reshape(xs[0].shape)]
 
@@ -356,7 +356,7 @@ class DiscreteRandom(ExecLayer):
         return [tuple(int(d) for d in self.params.dims) or (1,)]
 
     def forward(self, xs, training):
-        p = xs[0].reshape(xs[0].shape[0], -1).float()
+        p = rows2d(xs[0]).float()
         n = prod(self.out_dims[0])
         if training:
             idx = torch.multinomial(p.clamp(min=0) + 1e-30, n, replacement=True)
@@ -416,7 +416,7 @@ class Reduction(ExecLayer):
         return [(1,)]
 
     def forward(self, xs, training):
-        x = self.cast_in(xs[0]).reshape(xs[0].shape[0], -1)
+        x = rows2d(self.cast_in(xs[0]))
         mode = (self.params.mode or "sum").lower()
         r = x.float().sum(1, keepdim=True)
         if mode in ("mean", "average"):
@@ -468,7 +468,7 @@ class Variance(ExecLayer):
         return [(1,)]
 
     def forward(self, xs, training):
-        x = self.cast_in(xs[0]).reshape(xs[0].shape[0], -1).float()
+        x = rows2d(self.cast_in(xs[0])).float()
         n = x.shape[1]
         v = ((x - x.mean(1, keepdim=True)) ** 2).sum(1, keepdim=True)
         return [(v / (n if self.params.biased else max(n - 1, 1))).to(xs[0].dtype)]
@@ -482,8 +482,8 @@ class Covariance(ExecLayer):
         return [(1,)]
 
     def forward(self, xs, training):
-        a = self.cast_in(xs[0]).reshape(xs[0].shape[0], -1).float()
-        b = self.cast_in(xs[1]).reshape(xs[1].shape[0], -1).float()
+        a = rows2d(self.cast_in(xs[0])).float()
+        b = rows2d(self.cast_in(xs[1])).float()
         n = a.shape[1]
         c = ((a - a.mean(1, keepdim=True)) * (b - b.mean(1, keepdim=True))).sum(1, keepdim=True)
         return [(c / (n if self.params.biased else max(n - 1, 1))).to(xs[0].dtype)]
@@ -495,7 +495,7 @@ class Argmax(ExecLayer):
         return [(1,)]
 
     def forward(self, xs, training):
-        x = xs[0].reshape(xs[0].shape[0], -1)
+        x = rows2d(xs[0])
         return [x.argmax(1, keepdim=True).to(xs[0].dtype)]
 
 
@@ -505,7 +505,7 @@ class Argmin(ExecLayer):
         return [(1,)]
 
     def forward(self, xs, training):
-        x = xs[0].reshape(xs[0].shape[0], -1)
+        x = rows2d(xs[0])
         return [x.argmin(1, keepdim=True).to(xs[0].dtype)]
 
 
@@ -529,7 +529,7 @@ class InTopK(ExecLayer):
     """1 for the k largest entries of each sample, else 0 (src/layers/transform/in_top_k.cu)."""
 
     def forward(self, xs, training):
-        x = xs[0].reshape(xs[0].shape[0], -1)
+        x = rows2d(xs[0])
         k = min(int(self.params.k), x.shape[1])
         out = torch.zeros_like(x)
         if k > 0:
@@ -541,7 +541,7 @@ class InTopK(ExecLayer):
 @register("sort")
 class Sort(ExecLayer):
     def forward(self, xs, training):
-        x = xs[0].reshape(xs[0].shape[0], -1)
+        x = rows2d(xs[0])
         y, _ = torch.sort(x, dim=1, descending=bool(self.params.descending))
         return [y.reshape(xs[0].shape)]
 
@@ -566,7 +566,7 @@ class Gather(ExecLayer):
     def forward(self, xs, training):
         v = self.cast_in(xs[0])
         n = v.shape[0]
-        ind = xs[1].reshape(n, -1).long()
+        ind = rows2d(xs[1]).long()
         if v.dim() == 2:
             ok = (ind >= 0) & (ind < v.shape[1])
             out = v.gather(1, ind.clamp(0, v.shape[1] - 1)) * ok.to(v.dtype)
@@ -596,13 +596,13 @@ class Scatter(ExecLayer):
     def forward(self, xs, training):
         v = self.cast_in(xs[0])
         n = v.shape[0]
-        ind = xs[1].reshape(n, -1).long()
+        ind = rows2d(xs[1]).long()
         outd = self.out_dims[0]
         if len(outd) == 1:
             size = outd[0]
             ok = (ind >= 0) & (ind < size)
             out = torch.zeros(n, size, dtype=v.dtype, device=v.device)
-            out = out.scatter_add(1, ind.clamp(0, size - 1), v.reshape(n, -1) * ok.to(v.dtype))
+            out = out.scatter_add(1, ind.clamp(0, size - 1), rows2d(v) * ok.to(v.dtype))
             return [out]
         ax = self.axis + 1
         size = outd[self.axis]
@@ -771,7 +771,7 @@ class RowwiseWeightsNorms(ExecLayer):
 
     def forward(self, xs, training):
         w = self.w.handle.master
-        norms = w.reshape(w.shape[0], -1).float().norm(dim=1)
+        norms = rows2d(w).float().norm(dim=1)
         return [norms.unsqueeze(0).expand(self.model.current_mini_batch_size, -1)]
 
 

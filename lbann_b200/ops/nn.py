@@ -1269,8 +1269,9 @@ def sample_loss(kind: str, a, b=None):
             (b is None or (b.dtype == a.dtype and b.shape == a.shape)):
         return _SampleLoss.apply(a, b, _LOSS_KIND[kind])
     n = a.shape[0]
-    af = a.float().reshape(n, -1)
-    bf = b.float().reshape(n, -1) if b is not None else None
+    from ..exec.layer_base import rows2d
+    af = rows2d(a.float())
+    bf = rows2d(b.float()) if b is not None else None
     if kind == "cross_entropy":
         return torch.where(bf > 0, -bf * torch.log(af), torch.zeros_like(af)).sum(1)
     if kind == "mean_squared_error":

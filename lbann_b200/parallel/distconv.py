@@ -511,7 +511,8 @@ class DistconvContext:
     def cross_entropy(self, layer, p, labels):
         n, C = p.shape[0], p.shape[1]
         if layer.params.use_labels:
-            lab = labels.reshape(n, -1).long()
+            from ..exec.layer_base import rows2d
+            lab = rows2d(labels).long()
             pm = p.reshape(n, C, -1).movedim(1, -1)
             ok = (lab >= 0) & (lab < C)
             picked = pm.float().gather(2, lab.clamp(0, C - 1).unsqueeze(-1)).squeeze(-1)
@@ -782,20 +783,42 @@ class _Redistribute(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, dc: DistconvContext, to_sample: bool, tag: str):
-        ctx.meta = (dc, to_sample, tag)
-        return _redistribute(x, dc, to_sample, tag + ("/s" if to_sample else "/p"))
+        out, total = _redistribute(x, dc, to_sample, tag + ("/s" if to_sample else "/p"))
+        ctx.meta = (dc, to_sample, tag, total)
+        return out
 
     @staticmethod
     def backward(ctx, g):
-        dc, to_sample, tag = ctx.meta
-        return _redistribute(g, dc, not to_sample, tag + ("/bs" if to_sample else "/bp")), None, None, None
+        dc, to_sample, tag, total = ctx.meta
+        out, _ = _redistribute(g, dc, not to_sample, tag + ("/bs" if to_sample else "/bp"), total)
+        return out, None, None, None
 
 
-def _redistribute(x, dc: DistconvContext, to_sample: bool, tag: str):
+def _redistribute(x, dc: DistconvContext, to_sample: bool, tag: str, total=None):
+    """Returns (tensor, number of samples of the sample group).  The samples of a group are
+    dealt round-robin, so the last mini-batch of an epoch may leave the ranks with unequal
+    (even zero) counts: towards the spatial layout every rank pads its share to the common
+    maximum, and the padding is dropped where the bricks are put together."""
     P, r = dc.depth_groups, dc.depth_rank
     x_cl = x.permute(0, 2, 3, 4, 1).contiguous()        # N, D, H, W, C
     es = x_cl.element_size()
     grp = dc.group
+    S = dc.spatial_size
+    if to_sample:
+        total = x_cl.shape[0]
+    else:
+        if total is None:        # not known from a matching forward: ask the group
+            cnt = torch.tensor([x_cl.shape[0]], dtype=torch.int64, device=x_cl.device)
+            total = int(sum(int(c.item()) for c in dc.comm.all_gather(cnt, dc.depth_pg)))
+        ns_max = (total + S - 1) // S
+        if x_cl.shape[0] < ns_max:
+            pad = x_cl.new_zeros((ns_max - x_cl.shape[0],) + tuple(x_cl.shape[1:]))
+            x_cl = torch.cat([x_cl, pad], 0)
+    out = _redistribute_cl(x_cl, dc, to_sample, tag, total, P, r, es, grp, S)
+    return out, total
+
+
+def _redistribute_cl(x_cl, dc, to_sample, tag, total, P, r, es, grp, S):
     if dc.height_groups > 1:
         # depth x height grid: every rank of the sample group contributes its brick
         Hg, S, sr = dc.height_groups, dc.spatial_size, dc.spatial_rank
@@ -806,10 +829,10 @@ def _redistribute(x, dc: DistconvContext, to_sample: bool, tag: str):
         else:               # my brick of every rank's samples, samples interleaved again
             ns, D, H = x_cl.shape[0], x_cl.shape[1], x_cl.shape[2]
             Dl, Hl = D // P, H // Hg
-            out = torch.empty((sum(q.shape[0] for q in parts), Dl, Hl) + tuple(x_cl.shape[3:]),
-                              dtype=x_cl.dtype, device=x_cl.device)
+            out = torch.empty((total, Dl, Hl) + tuple(x_cl.shape[3:]), dtype=x_cl.dtype, device=x_cl.device)
             for q, part in enumerate(parts):
-                out[q::S] = part[:, r * Dl:(r + 1) * Dl, dc.height_rank * Hl:(dc.height_rank + 1) * Hl]
+                cq = len(range(q, total, S))
+                out[q::S] = part[:cq, r * Dl:(r + 1) * Dl, dc.height_rank * Hl:(dc.height_rank + 1) * Hl]
         return out.permute(0, 4, 1, 2, 3)
     if not dc.fused:
         parts = dc.comm.all_gather(x_cl, dc.depth_pg)
@@ -818,9 +841,9 @@ def _redistribute(x, dc: DistconvContext, to_sample: bool, tag: str):
         else:
             ns, D = x_cl.shape[0], x_cl.shape[1]
             Dl = D // P
-            out = torch.empty((ns * P, Dl) + tuple(x_cl.shape[2:]), dtype=x_cl.dtype, device=x_cl.device)
+            out = torch.empty((total, Dl) + tuple(x_cl.shape[2:]), dtype=x_cl.dtype, device=x_cl.device)
             for q, p in enumerate(parts):
-                out[q::P] = p[:, r * Dl:(r + 1) * Dl]
+                out[q::P] = p[:len(range(q, total, P)), r * Dl:(r + 1) * Dl]
         return out.permute(0, 4, 1, 2, 3)
     if to_sample:
         N, Dl, H, W, C = x_cl.shape
@@ -845,17 +868,18 @@ def _redistribute(x, dc: DistconvContext, to_sample: bool, tag: str):
     ns, D, H, W, C = x_cl.shape
     Dl = D // P
     slab = Dl * H * W * C * es
-    # every rank owns ns samples (equal counts are required for the inverse map)
+    # every rank brings ns samples (shares padded to the common maximum by the caller); rows
+    # beyond ``total`` are that padding
     N = ns * P
     buf = dc.buffer(("redist", tag), N * slab)
     view = buf.view(x_cl.dtype, N * Dl * H * W * C).view(N, Dl, H, W, C)
     # my sample j (global index j * P + r), depth slab q -> row j * P + r of rank q's buffer
     if grp.alltoall_slabs(x_cl, buf, ns * P, slab):
-        return view.permute(0, 4, 1, 2, 3)
+        return view[:total].permute(0, 4, 1, 2, 3)
     for q in range(P):
         src = x_cl[:, q * Dl:(q + 1) * Dl]
         grp.put_rows(src, buf, q, r * slab, ns, slab, D * H * W * C * es, P * slab)
     grp.barrier_device(3)
-    out = view.clone()
+    out = view[:total].clone()
     grp.barrier_device(2)
     return out.permute(0, 4, 1, 2, 3)

@@ -205,3 +205,18 @@ def test_unet_on_spatial_partitions_matches_single(tmp_path, ranks, depth, heigh
     assert dist["losses"][-1] < dist["losses"][0]
     for k, v in single["weight_norms"].items():
         assert abs(v - dist["weight_norms"][k]) <= 1e-4 * max(1.0, abs(v)), k
+
+
+@pytest.mark.parametrize("mini_batch", ["6", "2"])
+def test_distconv_uneven_and_empty_sample_shares(tmp_path, mini_batch):
+    """Four ranks whose sample-parallel tail gets unequal shares of a mini-batch (6 samples:
+    2, 2, 1, 1) or none at all on some ranks (2 samples): shares are padded to a common
+    size for the way back to the spatial layout, and layers run on empty shares."""
+    env = {"LBANN_TEST_MINI_BATCH": mini_batch, "LBANN_TEST_LR": "0.001"}
+    single = _run(1, ["cosmoflow", "1", "3", "float", "16"], str(tmp_path / "a.json"), env)
+    dist = _run(4, ["cosmoflow", "4", "3", "float", "16"], str(tmp_path / "b.json"), env, timeout=600)
+    assert dist["world"] == 4
+    for a, b in zip(single["losses"], dist["losses"]):
+        assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], dist["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - dist["weight_norms"][k]) <= 1e-3 * max(1.0, abs(v)), k
