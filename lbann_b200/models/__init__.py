@@ -13,4 +13,5 @@ from . import subgraph  # noqa: F401
 from . import applications  # noqa: F401
 from .applications import (construct_autoencoder, construct_candle_combo, construct_char_rnn,  # noqa: F401
                            construct_dense_gcn, construct_densenet, construct_gan, construct_jag_wae,
-                           construct_siamese, construct_vae)
+                           construct_image_regressor, construct_node2vec, construct_siamese, construct_vae,
+                           construct_voxel_autoencoder)

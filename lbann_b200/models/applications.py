@@ -3,7 +3,9 @@ auto-encoders and a variational auto-encoder (autoencoders/, ATOM), a hinge GAN 
 alternating updates (gan/mnist), DenseNet (vision/densenet.py), a character GRU language
 model (ATOM/train_atom_char_rnn.py), a dense-graph GCN classifier (graph/GNN), a siamese patch
 network with shared towers (selfsupervised/), the CANDLE Pilot-1 combo regressor
-(CANDLE/pilot1/combo.py) and the JAG Wasserstein auto-encoder (physics/ICF/jag_models.py).
+(CANDLE/pilot1/combo.py), the JAG Wasserstein auto-encoder (physics/ICF/jag_models.py), node2vec
+skip-gram with negative sampling (graph/node2vec), a 3-D voxel auto-encoder (MOF/) and an
+image regressor (physics/HRRL).
 Every builder returns an ``lbann.Model`` reading the data fields named in its docstring.
 """
 from __future__ import annotations
@@ -323,3 +325,91 @@ def construct_jag_wae(sample_size=16399, latent=20, enc_hidden=(32, 256, 128), d
                    metrics=[L.Metric(mse, name="reconstruction"), L.Metric(d_real, name="disc real"),
                             L.Metric(d_fake, name="disc fake"), L.Metric(g_adv, name="adversarial")],
                    callbacks=[copy])
+
+
+# ------------------------------------------------------------------------ node2vec skip-gram
+def construct_node2vec(num_vertices, walk_length, num_negative_samples, latent_dim=128, learning_rate=0.025,
+                       embeddings="replicated", scale_decay=0.8, num_epochs=1):
+    """Skip-gram with negative sampling over random walks (applications/graph/node2vec): a
+    sample is ``[negative vertex ids | walk vertex ids]`` as the ``node2vec`` reader writes
+    it.  Vertices of a walk attract one another with a weight that decays with their distance
+    along the walk (``scale_decay`` per step), and repel the negative samples:
+    positive loss = - sum_{i<j} decay^(j-i-1) log sigmoid(w_i . w_j) / normaliser,
+    negative loss = - mean_{i,k} log sigmoid(-w_i . n_k).  ``embeddings="distributed"`` keeps the
+    table partitioned over the ranks with sparse SGD at the owners (``DistEmbedding``)."""
+    ids = L.Input(data_field="samples", name="vertex_ids")
+    w = L.Weights(initializer=L.NormalInitializer(mean=0.0, standard_deviation=1.0 / latent_dim), name="embeddings")
+    if embeddings == "distributed":
+        emb = L.DistEmbedding(ids, weights=w, num_embeddings=num_vertices, embedding_dim=latent_dim,
+                              sparse_sgd=True, learning_rate=learning_rate, name="vertex_embeddings")
+    elif embeddings == "replicated":
+        emb = L.Embedding(ids, weights=w, num_embeddings=num_vertices, embedding_dim=latent_dim,
+                          name="vertex_embeddings")
+    else:
+        raise RuntimeError(f"unknown method to get embedding vectors ({embeddings})")
+    sl = L.Slice(emb, axis=0, slice_points=[0, num_negative_samples, num_negative_samples + walk_length],
+                 name="embedding_slice")
+    neg, walk = L.Identity(sl, name="negative_embeddings"), L.Identity(sl, name="walk_embeddings")
+    # all pairwise dot products of the walk: [walk, walk]; softplus(-x) = -log sigmoid(x)
+    pos_dots = L.MatMul(walk, walk, transpose_b=True, name="walk_dots")
+    pos_nll = L.Softplus(L.Negative(pos_dots), name="walk_nll")
+    mask, norm = [], 0.0
+    for i in range(walk_length):
+        for j in range(walk_length):
+            wgt = scale_decay ** (j - i - 1) if j > i else 0.0
+            mask.append(wgt)
+            norm += wgt
+    pair_w = L.WeightsLayer(weights=L.Weights(initializer=L.ValueInitializer(values=[m / norm for m in mask]),
+                                              optimizer=L.NoOptimizer(), name="pair_weights"),
+                            dims=[walk_length, walk_length], name="pair_weight_matrix")
+    pos_loss = L.Reduction(L.Multiply(pos_nll, pair_w), mode="sum", name="positive_loss")
+    neg_dots = L.MatMul(walk, neg, transpose_b=True, name="negative_dots")          # [walk, negatives]
+    neg_loss = L.Reduction(L.Softplus(neg_dots), mode="mean", name="negative_loss")
+    return L.Model(num_epochs, layers=list(L.traverse_layer_graph(ids)),
+                   objective_function=L.ObjectiveFunction([L.LayerTerm(pos_loss), L.LayerTerm(neg_loss, scale=2.0)]),
+                   metrics=[L.Metric(pos_loss, name="positive loss"), L.Metric(neg_loss, name="negative loss")])
+
+
+# ------------------------------------------------------------- 3-D voxel auto-encoder (MOF)
+def construct_voxel_autoencoder(channels=11, size=32, base=16, latent=64, num_epochs=1):
+    """Convolutional auto-encoder of voxelised crystals (metal-organic frameworks as
+    ``channels`` x size^3 grids; applications/MOF/MOFae.py): three stride-2 3-D convolutions with
+    batch norm down to (4 base) x (size/8)^3, a dense bottleneck, three transposed convolutions
+    back; mean squared error of the reconstruction."""
+    x = L.Input(data_field="samples", name="voxels")
+    h = x
+    for i, c in enumerate((base, 2 * base, 4 * base)):
+        h = ConvolutionModule(3, c, 4, stride=2, padding=1, bias=False, name=f"mof_enc{i}")(h)
+        h = L.Relu(L.BatchNormalization(h, decay=0.9, epsilon=1e-5, name=f"mof_enc{i}_bn"), name=f"mof_enc{i}_relu")
+    low = size // 8
+    z = FullyConnectedModule(latent, name="mof_latent")(h)
+    h = L.Reshape(FullyConnectedModule(4 * base * low ** 3, activation=L.Relu, name="mof_expand")(z),
+                  dims=[4 * base, low, low, low], name="mof_expand_shape")
+    for i, c in enumerate((2 * base, base, channels)):
+        h = ConvolutionModule(3, c, 4, stride=2, padding=1, bias=(i == 2), transpose=True, name=f"mof_dec{i}")(h)
+        if i < 2:
+            h = L.Relu(L.BatchNormalization(h, decay=0.9, epsilon=1e-5, name=f"mof_dec{i}_bn"), name=f"mof_dec{i}_relu")
+    recon = L.Sigmoid(h, name="mof_reconstruction")
+    mse = L.MeanSquaredError(recon, x, name="mof_mse")
+    return L.Model(num_epochs, layers=list(L.traverse_layer_graph(x)), objective_function=L.ObjectiveFunction([mse]),
+                   metrics=[L.Metric(mse, name="reconstruction error")])
+
+
+# ------------------------------------------------------- image regression (HRRL ProbiesNet)
+def construct_image_regressor(input_dims=(1, 300, 300), num_outputs=5, num_epochs=1):
+    """Regression from single-channel images to a few physical quantities
+    (applications/physics/HRRL: spectrometer images -> beam parameters): four convolution +
+    pooling blocks, two dense layers; mean squared error, R^2 reported through the variance."""
+    x = L.Input(data_field="samples", name="image")
+    y = L.Input(data_field="responses", name="targets")
+    h = x
+    for i, (c, k) in enumerate(((36, 11), (64, 5), (128, 3), (128, 3))):
+        h = Convolution2dModule(c, k, padding=k // 2, activation=L.Relu, name=f"reg_conv{i}")(h)
+        h = L.Pooling(h, num_dims=2, has_vectors=False, pool_dims_i=2, pool_pads_i=0, pool_strides_i=2,
+                      pool_mode="max", name=f"reg_pool{i}")
+    h = FullyConnectedModule(480, activation=L.Relu, name="reg_fc1")(h)
+    h = FullyConnectedModule(240, activation=L.Relu, name="reg_fc2")(h)
+    pred = FullyConnectedModule(num_outputs, name="reg_out")(h)
+    mse = L.MeanSquaredError(pred, y, name="reg_mse")
+    return L.Model(num_epochs, layers=list(L.traverse_layer_graph([x, y])),
+                   objective_function=L.ObjectiveFunction([mse]), metrics=[L.Metric(mse, name="mse")])

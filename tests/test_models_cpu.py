@@ -435,3 +435,28 @@ def test_dense_gcn_siamese_candle_and_jag_models_train():
     wae = construct_jag_wae(sample_size=24, latent=3, enc_hidden=(16, 8), disc_hidden=(8,))
     losses = _train(wae, _reader(8, [24], "normal"), steps=20, mb=8)
     assert losses[-1] < losses[0], losses
+
+
+def test_node2vec_voxel_autoencoder_and_image_regressor_train(tmp_path):
+    from lbann_b200.models.applications import (construct_image_regressor, construct_node2vec,
+                                                construct_voxel_autoencoder)
+    torch.manual_seed(0)
+    # a ring graph: walks visit neighbours, so neighbours' embeddings align
+    n = 12
+    (tmp_path / "ring.txt").write_text("".join(f"{i} {(i + 1) % n}\n" for i in range(n)))
+    r = lbann.reader_pb2.Reader()
+    r.name, r.role, r.shuffle, r.fraction_of_data_to_use = "node2vec", "train", False, 1.0
+    r.node2vec.graph_file, r.node2vec.epoch_size, r.node2vec.walk_length = str(tmp_path / "ring.txt"), 16, 5
+    r.node2vec.return_param = r.node2vec.inout_param = 1.0
+    r.node2vec.num_negative_samples = 3
+    dr = lbann.reader_pb2.DataReader()
+    dr.reader.append(r)
+    model = construct_node2vec(num_vertices=n, walk_length=5, num_negative_samples=3, latent_dim=8)
+    losses = _train(model, dr, steps=40, mb=8, optimizer=lbann.SGD(learn_rate=0.5))
+    assert losses[-1] < 0.9 * losses[0], losses
+    ae = construct_voxel_autoencoder(channels=2, size=8, base=4, latent=8)
+    losses = _train(ae, _reader(8, [2, 8, 8, 8], "uniform"), steps=20, mb=8)
+    assert losses[-1] < losses[0], losses
+    reg = construct_image_regressor(input_dims=(1, 32, 32), num_outputs=3)
+    losses = _train(reg, _reader(8, [1, 32, 32], "normal", response_dims=[3]), steps=15, mb=8)
+    assert losses[-1] < losses[0], losses
