@@ -546,6 +546,47 @@ def subgraph_transformer(num_subgrids, steps):
     return res
 
 
+def layer_parallel_gpt(num_subgrids, steps):
+    """A small GPT whose blocks are placed on sub-grids in order (blocks 0-1 on grid 1,
+    blocks 2-3 on grid 2): layer parallelism as placement, the grids run one after the other."""
+    from types import SimpleNamespace
+    from lbann_b200.models.parallelism import apply_layer_parallelism
+    from lbann_b200.models.transformer import construct_gpt_model
+    o = opts.reset()
+    if os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cpu":
+        o.set("disable_cuda", True)
+    model = construct_gpt_model(vocab_size=24, seq_len=8, d_model=16, num_heads=2, num_layers=4, ffn_dim=32)
+    grids = 0
+    if num_subgrids > 1:
+        grids = apply_layer_parallelism(model, SimpleNamespace(layer_parallel=True, lp_count=num_subgrids))
+        o.set("num_subgrids", grids)
+    from test_models_cpu import _reader
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=8, random_seed=23), model=model,
+        data_reader=_reader(16, [9], "randint:24"), optimizer=lbann.SGD(learn_rate=0.05, momentum=0.9))
+    tr = ExecTrainer(exp)
+    m = tr.build_model(exp.model)
+    tags = sorted({l.grid_tag for l in m.layers})
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    losses = []
+    for _ in range(steps):
+        b_ = dc.next_batch("training")
+        if b_ is None:
+            dc.start_epoch("training")
+            b_ = dc.next_batch("training")
+        m.train_step(b_.tensors, b_.global_size)
+        v = m.last_objective.detach().float().reshape(1).clone()
+        if tr.parallel is not None:
+            tr.comm.allreduce(v, "trainer", "sum")
+        losses.append(float(v))
+    w = {x_.name: float(x_.values.detach().double().norm()) for x_ in m.weights}
+    res = {"losses": losses, "weight_norms": w, "world": int(os.environ.get("WORLD_SIZE", "1")),
+           "tags": tags, "grids": grids}
+    tr.shutdown()
+    return res
+
+
 def subgraph_branches(num_subgrids, steps):
     """Two branches of a small network on two sub-grids (grid tags 1 and 2), joined by a sum on
     the whole trainer; a third output goes through a sum across the grids."""
@@ -660,6 +701,8 @@ if __name__ == "__main__":
         res = subgraph_branches(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "kfac":
         res = kfac_job(int(sys.argv[3]), int(sys.argv[4]))
+    elif what == "layer_parallel":
+        res = layer_parallel_gpt(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "subgraph_transformer":
         res = subgraph_transformer(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "abort_restart":

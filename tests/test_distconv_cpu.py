@@ -220,3 +220,16 @@ def test_distconv_uneven_and_empty_sample_shares(tmp_path, mini_batch):
         assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], dist["losses"])
     for k, v in single["weight_norms"].items():
         assert abs(v - dist["weight_norms"][k]) <= 1e-3 * max(1.0, abs(v)), k
+
+
+def test_layer_parallel_placement_on_two_subgrids(tmp_path):
+    """GPT blocks 0-1 on sub-grid 1 and blocks 2-3 on sub-grid 2 (four ranks, two per grid;
+    activations move between the rank subsets at the block boundary): same losses and
+    weights as one process."""
+    single = _run(1, ["layer_parallel", "1", "3"], str(tmp_path / "a.json"))
+    four = _run(4, ["layer_parallel", "2", "3"], str(tmp_path / "b.json"), timeout=600)
+    assert four["world"] == 4 and four["tags"] == [0, 1, 2] and four["grids"] == 2
+    for a, b in zip(single["losses"], four["losses"]):
+        assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], four["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - four["weight_norms"][k]) <= 1e-4 * max(1.0, abs(v)), k
