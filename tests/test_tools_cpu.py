@@ -78,3 +78,42 @@ def test_mnist_idx_conversion(tmp_path):
     assert np.array_equal(comb[:, :784], keep[0].reshape(9, -1)) and np.array_equal(comb[:, 784], keep[1])
     z = np.load(tmp_path / "out" / "test.npz")
     assert z["data"].shape == (4, 784) and z["labels"].shape == (4,)
+
+
+def test_viz_writes_a_dot_graph_with_subgrid_colours(tmp_path):
+    import lbann_b200 as lbann
+    from lbann_b200.tools import viz
+    x = lbann.Input(data_field="samples", name="in")
+    a = lbann.FullyConnected(x, num_neurons=4, name="left", grid_tag=1)
+    b = lbann.FullyConnected(x, num_neurons=4, name="right", grid_tag=2)
+    y = lbann.Sum([a, b], name="join")
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph(x)))
+    lbann.proto.serialize.save_prototext(str(tmp_path / "m.prototext"), trainer=lbann.Trainer(mini_batch_size=2),
+                                         model=model, data_reader=None, optimizer=lbann.SGD(learn_rate=0.1))
+    assert viz.main([str(tmp_path / "m.prototext"), str(tmp_path / "g.dot"), "--label-format", "type-and-name",
+                     "--color-cross-grid"]) == 0
+    dot = open(tmp_path / "g.dot").read()
+    assert dot.startswith("digraph model {") and '"in" -> "left" [color="red"' in dot
+    assert '"left" [label="fully_connected\\nleft", fillcolor="#a0c4ff"]' in dot
+    assert '"right" -> "join"' in dot and y is not None
+
+
+def test_print_times_reads_the_statistics_lines(tmp_path, capsys):
+    from lbann_b200.tools import print_times
+    log = """\
+some other output
+model0 (instance 0) training epoch 0 objective function : 2.30412
+model0 (instance 0) training epoch 0 accuracy : 11.5%
+model0 (instance 0) training epoch 0 run time : 3.25s
+model0 (instance 0) training epoch 0 mini-batch time statistics : 0.0125s mean, 0.012s median, 0.02s max, 0.011s min, 0.001s stdev
+model0 (instance 0) validation objective function : 2.1
+model0 (instance 0) training epoch 1 objective function : 1.5
+"""
+    (tmp_path / "run.log").write_text(log)
+    rows = print_times.parse(log.splitlines())
+    assert ("model0", "training", 0, "accuracy", 11.5) in rows and ("model0", "validation", -1, "objective function", 2.1) in rows
+    assert print_times.main([str(tmp_path / "run.log"), "--csv", str(tmp_path / "t.csv")]) == 0
+    out = capsys.readouterr().out.splitlines()
+    assert out[0].split()[:3] == ["model", "mode", "epoch"] and "mini-batch time statistics" in out[0]
+    csv_rows = open(tmp_path / "t.csv").read().splitlines()
+    assert csv_rows[1].startswith("model0,training,0,2.30412,11.5,3.25,0.0125")
