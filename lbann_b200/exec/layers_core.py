@@ -191,6 +191,7 @@ class Deconvolution(_ConvBase):
 
 @register("channelwise_fully_connected")
 class ChannelwiseFullyConnected(ExecLayer):
+    supports_channel_parallel = True
     """The same fully-connected map applied to every channel (row) of the input
     (src/layers/learning/channelwise_fully_connected.cpp).  Weights ``<name>_matrix`` /
     ``<name>_bias`` in the front-end modules; default names ``_linearity_weights`` /
@@ -216,7 +217,7 @@ class ChannelwiseFullyConnected(ExecLayer):
     def forward(self, xs, training):
         x = self.cast_in(xs[0])
         n = x.shape[0]
-        x2 = x.reshape(n, self.channels, self.in_size)
+        x2 = x.reshape(n, x.shape[1] if x.dim() > 1 else self.channels, self.in_size)   # a channel partition holds a slice
         par = self.model.parallel
         if par is not None and self.data_layout == "model_parallel" and par.tp_size > 1:
             y = par.tp_linear(self, x2)
@@ -224,7 +225,7 @@ class ChannelwiseFullyConnected(ExecLayer):
             # FSDP-style weights (``Weights(sharded=True)``): all-gather -> GEMM forward,
             # weight gradient reduce-scattered to the owners of the rows
             y = sharded_linear_forward(self, par, x2.reshape(-1, self.in_size)).reshape(
-                n, self.channels, self.out_size)
+                n, x2.shape[1], self.out_size)
         elif self.transpose:
             w = self.w.handle.cast(x.dtype) if x.is_cuda else self.w.handle.master.to(x.dtype)
             if x.is_cuda and x.dtype in (torch.float16, torch.bfloat16):
@@ -236,7 +237,7 @@ class ChannelwiseFullyConnected(ExecLayer):
         else:
             y = nn.linear(x2, self.w.handle, None if self.b is None else self.b.handle,
                           self.fused_act[0], self.fused_act[1])
-        return [y.reshape(n, self.channels, *self.out_cdims)]
+        return [y.reshape(n, x2.shape[1], *self.out_cdims)]
 
 
 class _TransposedLinear(torch.autograd.Function):
@@ -406,6 +407,7 @@ class GRU(ExecLayer):
 
 # =============================================================================== activations
 class _Unary(ExecLayer):
+    supports_channel_parallel = True
     op = "identity"
     supports_distconv = True
 
@@ -444,6 +446,7 @@ class Elu(_Unary):
 
 @register("identity")
 class Identity(ExecLayer):
+    supports_channel_parallel = True
     supports_distconv = True
 
     def forward(self, xs, training):
@@ -718,6 +721,7 @@ class InstanceNorm(ExecLayer):
 
 @register("dropout")
 class Dropout(ExecLayer):
+    supports_channel_parallel = True
     """Inverted dropout with keep probability ``keep_prob`` (default 0.5)
     (src/layers/regularizers/dropout.cpp)."""
 
@@ -774,6 +778,7 @@ def _snake(name: str) -> str:
 
 @register("operator_layer")
 class OperatorLayer(ExecLayer):
+    supports_channel_parallel = True
     """A chain of entrywise operators (include/lbann/layers/operator_layer_impl.hpp,
     src/proto/operators.proto).  A single operator is the common case."""
     max_parents = -1

@@ -57,6 +57,7 @@ class Split(ExecLayer):
 
 @register("sum")
 class Sum(ExecLayer):
+    supports_channel_parallel = True
     """Entrywise sum of all inputs (include/lbann/layers/transform/sum.hpp)."""
     max_parents = -1
     supports_distconv = True
@@ -78,6 +79,7 @@ class Sum(ExecLayer):
 
 @register("weighted_sum")
 class WeightedSum(ExecLayer):
+    supports_channel_parallel = True
     max_parents = -1
 
     def forward(self, xs, training):
@@ -91,6 +93,7 @@ class WeightedSum(ExecLayer):
 
 @register("hadamard")
 class Hadamard(ExecLayer):
+    supports_channel_parallel = True
     max_parents = -1
 
     def forward(self, xs, training):
@@ -618,6 +621,7 @@ class Scatter(ExecLayer):
 # =============================================================================== math
 @register("matmul")
 class MatMul(ExecLayer):
+    supports_channel_parallel = True
     """Per-sample matrix product of two (batched) 2-D inputs with optional transposes
     (src/layers/math/matmul.cpp:419-584)."""
     min_parents = max_parents = 2
@@ -632,6 +636,12 @@ class MatMul(ExecLayer):
 
     def forward(self, xs, training):
         a, b = self.cast_in(xs[0]), self.cast_in(xs[1])
+        dc = self.model.distconv
+        if dc is not None and dc.channel_groups > 1 and dc.enabled(self):
+            # rows of the first operand stay with their rank; the second operand is needed whole
+            if self.ta:
+                raise NotImplementedError("a channel-partitioned matrix product cannot transpose its first operand")
+            b = dc.gather_channels(b)
         if a.is_cuda and a.dtype in (torch.float16, torch.bfloat16):
             return [_BatchedMatMul.apply(a, b.to(a.dtype), self.ta, self.tb)]
         A = a.transpose(-1, -2) if self.ta else a
@@ -683,6 +693,7 @@ class DFTAbs(ExecLayer):
 # =============================================================================== misc
 @register("channelwise_softmax")
 class ChannelwiseSoftmax(ExecLayer):
+    supports_channel_parallel = True
     """Softmax within each channel (row) of the sample; with ``single_dim_mode`` only along
     ``dim`` (src/layers/misc/channelwise_softmax.cu:238-319)."""
 

@@ -367,6 +367,8 @@ class ExecModel:
         element-wise passes over the [heads, S, S] tensor.  A mask qualifies when it is a
         constant (optimizer-less) weights layer holding 0 on and below the diagonal and a
         large negative number above it."""
+        if self.distconv is not None and getattr(self.distconv, "channel_groups", 1) > 1:
+            return          # the attention chain is partitioned over tokens: keep its layers apart
         forced = os.environ.get("LBANN_FORCE_ATTENTION_FUSION")     # CPU tests of the graph rewrite
         if (self.device.type != "cuda" and not forced) or os.environ.get("LBANN_DISABLE_ATTENTION_FUSION"):
             return
@@ -421,6 +423,8 @@ class ExecModel:
         three slices of one projection the packed entry point is used (one gradient tensor
         for the projection).  Dropout on the probabilities, extra biases, non-causal masks
         and protected (objective / metric) layers keep the layer-by-layer path."""
+        if self.distconv is not None and getattr(self.distconv, "channel_groups", 1) > 1:
+            return          # the attention chain is partitioned over tokens: keep its layers apart
         if os.environ.get("LBANN_DISABLE_ATTENTION_FUSION"):
             return
         protected = {n for n, _ in self.objective_terms} | {m.layer_name for m in self.metrics

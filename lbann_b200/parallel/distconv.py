@@ -58,6 +58,11 @@ class Strategy:
     def is_spatial(self) -> bool:
         return self.depth * self.height * self.width > 1
 
+    def is_channel(self) -> bool:
+        """Partition along the first sample dimension (the "channel" dimension of [N, C, ...]
+        tensors: tokens of a sequence) without any spatial split."""
+        return self.channel > 1 and not self.is_spatial()
+
 
 class DistconvContext:
     def __init__(self, comm, device, parallel):
@@ -71,6 +76,8 @@ class DistconvContext:
         self.strategies: Dict[str, Strategy] = {}
         self.depth_groups = 1
         self.height_groups = 1                    # second partitioned dimension (depth x height)
+        self.channel_groups = 1                   # partition of the channel (token) dimension of [N, C, F] tensors
+        self.channel_rank = 0
         self.input_halo: Dict[str, int] = {}      # input layer -> halo planes uploaded with it
         self.num_sample_groups = 1
         self.sample_group_index = 0
@@ -91,44 +98,50 @@ class DistconvContext:
     def plan(self, model_pb) -> None:
         """Depth / sample group sizes from the prototext alone (the data coordinator, which
         deals samples to the sample groups, is built before the model is)."""
-        depth = height = 1
+        depth = height = channel = 1
         for l in model_pb.layer:
             if l.HasField("parallel_strategy"):
                 st = Strategy(l.parallel_strategy, self.world)
                 if st.is_spatial():
                     depth, height = max(depth, st.depth), max(height, st.height)
+                elif st.is_channel() and not (l.HasField("convolution") or l.HasField("deconvolution")):
+                    channel = max(channel, st.channel)
         if depth * height > 1 and self.world % (depth * height) == 0:
             self._set_grid(depth, height)
+        elif channel > 1 and self.world % channel == 0:
+            self._set_grid(1, 1, channel)
 
-    def _set_grid(self, depth: int, height: int) -> None:
+    def _set_grid(self, depth: int, height: int, channel: int = 1) -> None:
         """Ranks of one sample group are consecutive and form a depth x height grid, height
-        fastest: rank = (sample_group * depth + depth_rank) * height + height_rank."""
-        spatial = depth * height
-        self.depth_groups, self.height_groups = depth, height
+        fastest: rank = (sample_group * depth + depth_rank) * height + height_rank.  A channel
+        partition (no spatial split) uses the same consecutive ranks along the channel dimension."""
+        spatial = depth * height * channel
+        self.depth_groups, self.height_groups, self.channel_groups = depth, height, channel
         self.num_sample_groups = self.world // spatial
         self.sample_group_index = self.rank // spatial
-        self.depth_rank = (self.rank % spatial) // height
-        self.height_rank = self.rank % height
+        self.depth_rank = (self.rank % spatial) // (height * channel)
+        self.height_rank = (self.rank // channel) % height
+        self.channel_rank = self.rank % channel
 
     @property
     def spatial_size(self) -> int:
-        """Ranks that share one sample (depth_groups x height_groups)."""
-        return self.depth_groups * self.height_groups
+        """Ranks that share one sample (depth_groups x height_groups, or channel_groups)."""
+        return self.depth_groups * self.height_groups * self.channel_groups
 
     @property
     def spatial_rank(self) -> int:
-        return self.depth_rank * self.height_groups + self.height_rank
+        return (self.depth_rank * self.height_groups + self.height_rank) * self.channel_groups + self.channel_rank
 
     @property
     def fused(self) -> bool:
         """The peer-memory kernels (halo exchange inside the convolutions, all-to-all
         redistribution, small all-reduce) serve the depth-only partition; a depth x height
         grid exchanges its halos with library collectives over the grid's lines."""
-        return self.group.native and self.height_groups == 1
+        return self.group.native and self.height_groups == 1 and self.channel_groups == 1
 
     def prepare_model(self, model):
         self._enabled.clear()
-        depth = height = 1
+        depth = height = channel = 1
         for l in model.layers:
             if l.parallel_strategy is None:
                 continue
@@ -146,10 +159,24 @@ class DistconvContext:
                     raise ValueError("all distconv layers of a model must use the same "
                                      "depth_groups and height_groups")
                 depth, height = st.depth, st.height
-        self._set_grid(depth, height)
+            elif st.is_channel() and l.type not in ("convolution", "deconvolution"):
+                if channel not in (1, st.channel):
+                    raise ValueError("all channel-partitioned layers of a model must use the same channel_groups")
+                channel = st.channel
+        if channel > 1 and depth * height > 1:
+            raise ValueError("channel_groups cannot be combined with depth / height partitions in one model")
+        self._set_grid(depth, height, channel)
         self.depth_pg = "trainer"
         self.line_pg = {2: "trainer", 3: "trainer"}
-        if height > 1:
+        if channel > 1:
+            # ranks that share a sample: consecutive groups of `channel` ranks
+            if self.num_sample_groups > 1:
+                base = self.comm.trainer_rank * self.world
+                for sgi in range(self.num_sample_groups):
+                    pg = self.comm.new_group([base + sgi * channel + i for i in range(channel)])
+                    if sgi == self.sample_group_index:
+                        self.depth_pg = pg
+        elif height > 1:
             self._build_grid_groups(depth, height)
         elif depth > 1 and self.num_sample_groups > 1:
             # sample x depth partition (left-over ranks multiply the sample groups,
@@ -254,11 +281,23 @@ class DistconvContext:
         if hit is not None:
             return hit
         st = self.strategies.get(layer.name)
-        val = bool(st is not None and st.is_spatial() and layer.supports_distconv
-                   and self.spatial_size > 1 and self._feasible(layer))
+        if self.channel_groups > 1:
+            val = bool(st is not None and st.is_channel() and getattr(layer, "supports_channel_parallel", False)
+                       and self._feasible_channel(layer))
+        else:
+            val = bool(st is not None and st.is_spatial() and layer.supports_distconv
+                       and self.spatial_size > 1 and self._feasible(layer))
         if getattr(layer, "in_dims", None):
             self._enabled[layer.name] = val
         return val
+
+    def _feasible_channel(self, layer) -> bool:
+        """Channel (token) partition: every input is [C, ...] with at least two dimensions and C
+        divisible by the number of ranks."""
+        dims = getattr(layer, "in_dims", None)
+        if not dims:
+            return True
+        return all(len(d) >= 2 and int(d[0]) % self.channel_groups == 0 for d in dims)
 
     def _feasible(self, layer) -> bool:
         """Can this layer still be computed on depth slabs?  Deep in a network the depth
@@ -299,6 +338,9 @@ class DistconvContext:
                 out.append(x)
             elif have == REPLICATED and want == SAMPLE:
                 out.append(x[self.spatial_rank::self.spatial_size])
+            elif have == REPLICATED and want == SPATIAL and self.channel_groups > 1:
+                cl = x.shape[1] // self.channel_groups
+                out.append(x.narrow(1, self.channel_rank * cl, cl))
             elif have == REPLICATED and want == SPATIAL:
                 # depth is the third dimension from the last ([N, C, D, H, W] and [N, D, H, W])
                 ax = x.dim() - 3
@@ -493,6 +535,13 @@ class DistconvContext:
                         return None
                     return self.halo_tensor(("dy", par.name), N, D, hp, H, W, C, dtype).interior
         return out_alloc, dx_alloc
+
+    def gather_channels(self, x):
+        """The whole channel (token) extent of a channel-partitioned tensor on every rank of the
+        group: the second operand of a matrix product whose first operand stays partitioned
+        (scores = Q_local K^T need all keys; src/layers/math/matmul.cpp:82-130 partitions the
+        same way)."""
+        return _GatherChannels.apply(x, self)
 
     def bn_reduction(self, layer):
         from ..ops.nn import GroupSum
@@ -799,6 +848,8 @@ def _redistribute(x, dc: DistconvContext, to_sample: bool, tag: str, total=None)
     dealt round-robin, so the last mini-batch of an epoch may leave the ranks with unequal
     (even zero) counts: towards the spatial layout every rank pads its share to the common
     maximum, and the padding is dropped where the bricks are put together."""
+    if dc.channel_groups > 1:
+        return _redistribute_channel(x, dc, to_sample, total)
     P, r = dc.depth_groups, dc.depth_rank
     x_cl = x.permute(0, 2, 3, 4, 1).contiguous()        # N, D, H, W, C
     es = x_cl.element_size()
@@ -816,6 +867,46 @@ def _redistribute(x, dc: DistconvContext, to_sample: bool, tag: str, total=None)
             x_cl = torch.cat([x_cl, pad], 0)
     out = _redistribute_cl(x_cl, dc, to_sample, tag, total, P, r, es, grp, S)
     return out, total
+
+
+def _redistribute_channel(x, dc, to_sample: bool, total=None):
+    """Channel (token) partition <-> sample-parallel for tensors [N, C, ...] of any rank."""
+    S, sr = dc.channel_groups, dc.channel_rank
+    x = x.contiguous()
+    if to_sample:           # every rank's channel slice of all samples -> my samples, all channels
+        total = x.shape[0]
+        parts = dc.comm.all_gather(x, dc.depth_pg)
+        return torch.cat([p[sr::S] for p in parts], dim=1), total
+    if total is None:
+        cnt = torch.tensor([x.shape[0]], dtype=torch.int64, device=x.device)
+        total = int(sum(int(c.item()) for c in dc.comm.all_gather(cnt, dc.depth_pg)))
+    ns_max = (total + S - 1) // S
+    if x.shape[0] < ns_max:
+        x = torch.cat([x, x.new_zeros((ns_max - x.shape[0],) + tuple(x.shape[1:]))], 0)
+    parts = dc.comm.all_gather(x, dc.depth_pg)
+    cl = x.shape[1] // S
+    out = x.new_empty((total, cl) + tuple(x.shape[2:]))
+    for q, part in enumerate(parts):
+        out[q::S] = part[:len(range(q, total, S)), sr * cl:(sr + 1) * cl]
+    return out, total
+
+
+class _GatherChannels(torch.autograd.Function):
+    """All ranks' channel slices of a [N, Cl, ...] tensor put together along dimension 1; the
+    gradient of the local slice is the sum over the ranks of their gradients of it."""
+
+    @staticmethod
+    def forward(ctx, x, dc):
+        ctx.dc = dc
+        return torch.cat(dc.comm.all_gather(x.contiguous(), dc.depth_pg), dim=1)
+
+    @staticmethod
+    def backward(ctx, g):
+        dc = ctx.dc
+        g = g.contiguous().clone()
+        dc.comm.allreduce(g, dc.depth_pg, "sum")
+        cl = g.shape[1] // dc.channel_groups
+        return g.narrow(1, dc.channel_rank * cl, cl).contiguous(), None
 
 
 def _redistribute_cl(x_cl, dc, to_sample, tag, total, P, r, es, grp, S):

@@ -587,6 +587,62 @@ def layer_parallel_gpt(num_subgrids, steps):
     return res
 
 
+def token_parallel(channel_groups, steps):
+    """One attention + MLP block over [S, E] token tensors with the tokens split over the
+    ranks (channel_groups): projections and the MLP are channel-wise and stay local, the
+    score and context products gather keys and values, everything after the block runs
+    sample-parallel."""
+    o = opts.reset()
+    if os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cpu":
+        o.set("disable_cuda", True)
+    S, E = 8, 16
+    ps = lbann.get_parallel_strategy_args(channel_groups=channel_groups) if channel_groups > 1 else {}
+    x = lbann.Input(data_field="samples")
+    t = lbann.Input(data_field="responses")
+    seq = lbann.Identity(lbann.Reshape(x, dims=[S, E]), name="tokens", parallel_strategy=ps)
+
+    def cfc(h, n, name):
+        return lbann.ChannelwiseFullyConnected(h, output_channel_dims=[n], name=name, parallel_strategy=ps)
+    q, k, v = cfc(seq, E, "q"), cfc(seq, E, "k"), cfc(seq, E, "v")
+    scores = lbann.MatMul(q, k, transpose_b=True, name="scores", parallel_strategy=ps)
+    probs = lbann.ChannelwiseSoftmax(lbann.Scale(scores, constant=E ** -0.5, name="scaled", parallel_strategy=ps),
+                                     name="probs", parallel_strategy=ps)
+    ctx = lbann.MatMul(probs, v, name="context", parallel_strategy=ps)
+    h = lbann.Add(seq, ctx, name="res1", parallel_strategy=ps)
+    m = cfc(lbann.Relu(cfc(h, 32, "up"), name="act", parallel_strategy=ps), E, "down")
+    h = lbann.Add(h, m, name="res2", parallel_strategy=ps)
+    y = lbann.FullyConnected(lbann.Reshape(h, dims=[S * E]), num_neurons=4, has_bias=False, name="head")
+    loss = lbann.MeanSquaredError(y, t, name="mse")
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph([x, t])),
+                        objective_function=lbann.ObjectiveFunction([loss]))
+    from test_models_cpu import _reader
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=6, random_seed=29), model=model,
+        data_reader=_reader(12, [S * E], "normal", response_dims=[4]),
+        optimizer=lbann.SGD(learn_rate=0.005, momentum=0.9))
+    tr = ExecTrainer(exp)
+    mdl = tr.build_model(exp.model)
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    losses = []
+    for _ in range(steps):
+        b_ = dc.next_batch("training")
+        if b_ is None:
+            dc.start_epoch("training")
+            b_ = dc.next_batch("training")
+        mdl.train_step(b_.tensors, b_.global_size)
+        vv = mdl.last_objective.detach().float().reshape(1).clone()
+        if tr.parallel is not None:
+            tr.comm.allreduce(vv, "trainer", "sum")
+        losses.append(float(vv))
+    w = {x_.name: float(x_.values.detach().double().norm()) for x_ in mdl.weights}
+    spatial = sorted(n for n, d in (tr.distconv.dist.items() if tr.distconv is not None else []) if d == "spatial")
+    res = {"losses": losses, "weight_norms": w, "world": int(os.environ.get("WORLD_SIZE", "1")),
+           "partitioned": spatial, "sample_groups": tr.distconv.num_sample_groups if tr.distconv is not None else 1}
+    tr.shutdown()
+    return res
+
+
 def subgraph_branches(num_subgrids, steps):
     """Two branches of a small network on two sub-grids (grid tags 1 and 2), joined by a sum on
     the whole trainer; a third output goes through a sum across the grids."""
@@ -701,6 +757,8 @@ if __name__ == "__main__":
         res = subgraph_branches(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "kfac":
         res = kfac_job(int(sys.argv[3]), int(sys.argv[4]))
+    elif what == "token_parallel":
+        res = token_parallel(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "layer_parallel":
         res = layer_parallel_gpt(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "subgraph_transformer":

@@ -233,3 +233,20 @@ def test_layer_parallel_placement_on_two_subgrids(tmp_path):
         assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], four["losses"])
     for k, v in single["weight_norms"].items():
         assert abs(v - four["weight_norms"][k]) <= 1e-4 * max(1.0, abs(v)), k
+
+
+@pytest.mark.parametrize("ranks", [2, 4])
+def test_token_parallel_attention_block_matches_single(tmp_path, ranks):
+    """channel_groups = 2 on the layers of an attention + MLP block over [tokens, features]
+    tensors: tokens are split over two ranks, channel-wise products / activations / softmax stay
+    local, the score and context products gather keys and values, the head runs
+    sample-parallel.  With four ranks there are two sample groups (and uneven shares)."""
+    single = _run(1, ["token_parallel", "1", "4"], str(tmp_path / "a.json"))
+    dist = _run(ranks, ["token_parallel", "2", "4"], str(tmp_path / "b.json"), timeout=600)
+    assert dist["world"] == ranks and dist["sample_groups"] == ranks // 2
+    assert {"q", "k", "v", "scores", "probs", "context", "up", "down"} <= set(dist["partitioned"])
+    assert dist["losses"][-1] < dist["losses"][0]
+    for a, b in zip(single["losses"], dist["losses"]):
+        assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], dist["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - dist["weight_norms"][k]) <= 1e-4 * max(1.0, abs(v)), k
