@@ -217,7 +217,11 @@ class ChannelwiseFullyConnected(ExecLayer):
     def forward(self, xs, training):
         x = self.cast_in(xs[0])
         n = x.shape[0]
-        x2 = x.reshape(n, x.shape[1] if x.dim() > 1 else self.channels, self.in_size)   # a channel partition holds a slice
+        dc = self.model.distconv
+        c = self.channels
+        if dc is not None and dc.channel_groups > 1 and dc.enabled(self):
+            c //= dc.channel_groups                  # a channel partition holds a slice of the rows
+        x2 = x.reshape(n, c, self.in_size)
         par = self.model.parallel
         if par is not None and self.data_layout == "model_parallel" and par.tp_size > 1:
             y = par.tp_linear(self, x2)
@@ -225,7 +229,7 @@ class ChannelwiseFullyConnected(ExecLayer):
             # FSDP-style weights (``Weights(sharded=True)``): all-gather -> GEMM forward,
             # weight gradient reduce-scattered to the owners of the rows
             y = sharded_linear_forward(self, par, x2.reshape(-1, self.in_size)).reshape(
-                n, x2.shape[1], self.out_size)
+                n, c, self.out_size)
         elif self.transpose:
             w = self.w.handle.cast(x.dtype) if x.is_cuda else self.w.handle.master.to(x.dtype)
             if x.is_cuda and x.dtype in (torch.float16, torch.bfloat16):
@@ -237,7 +241,7 @@ class ChannelwiseFullyConnected(ExecLayer):
         else:
             y = nn.linear(x2, self.w.handle, None if self.b is None else self.b.handle,
                           self.fused_act[0], self.fused_act[1])
-        return [y.reshape(n, x2.shape[1], *self.out_cdims)]
+        return [y.reshape(n, c, *self.out_cdims)]
 
 
 class _TransposedLinear(torch.autograd.Function):
