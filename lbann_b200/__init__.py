@@ -51,6 +51,11 @@ def evaluate(*args, **kwargs):
 
 def __getattr__(name):
     # lazily loaded sub-packages: lbann.modules, lbann.models, lbann.contrib, lbann.util, ...
+    if name == "ops":                      # operator classes, as `import lbann.core.operators as ops`
+        import importlib
+        mod = importlib.import_module(f"{__name__}.core.operators")
+        globals()[name] = mod
+        return mod
     if name in ("modules", "models", "contrib", "util", "launcher", "torch"):
         import importlib
         mod = importlib.import_module(f"{__name__}.{name}")

@@ -1,8 +1,10 @@
-"""Operator classes (element-wise operators used by operator layers)."""
-from ..frontend import core as _C
+"""Operator classes (``lbann.ops``): the entry-wise operators that an ``OperatorLayer`` chains,
+one class per operator message of the schema, e.g.
 
-for _n in dir(_C):
-    _o = getattr(_C, _n)
-    if not _n.startswith('_') and (lambda n, o: isinstance(o, type) and issubclass(o, _C.Operator))(_n, _o):
-        globals()[_n] = _o
-del _n, _o
+    lbann.OperatorLayer(x, ops=[lbann.ops.Clamp(min=0.0, max=1.0)])
+
+(python/lbann/core/operators.py generates the same classes from operators.proto)."""
+from ..frontend.core import Operator, operator_classes as _classes
+
+globals().update(_classes)
+__all__ = ["Operator"] + sorted(_classes)

@@ -134,3 +134,19 @@ def test_cpu_binding_helpers(tmp_path, monkeypatch):
     assert affinity.bind_to_gpu(0, str(tmp_path)) is None
     monkeypatch.setenv("LBANN_DISABLE_NUMA_BIND", "1")
     assert affinity.bind_to_gpu(0, str(tmp_path)) is None
+
+
+def test_operator_classes_through_lbann_ops():
+    """``lbann.ops`` holds one class per operator message; an operator layer chains them."""
+    import numpy as np
+    import lbann_b200 as lbann
+    assert {"Add", "Clamp", "Exp", "Scale", "Tanh"} <= set(lbann.ops.__all__)
+    x = lbann.Input(data_field="samples")
+    y = lbann.OperatorLayer(x, ops=[lbann.ops.Clamp(min=-1.0, max=0.5)], name="clamped")
+    z = lbann.OperatorLayer(y, ops=[lbann.ops.Scale(constant=2.0)], name="scaled")
+    data = np.linspace(-2, 2, 12, dtype=np.float32).reshape(3, 4)
+    got = lbann.evaluate(z, data)
+    np.testing.assert_allclose(got, 2.0 * np.clip(data, -1.0, 0.5), rtol=1e-6)
+    import pytest
+    with pytest.raises(ValueError, match="unknown argument"):
+        lbann.ops.Clamp(minimum=0.0)
