@@ -51,11 +51,9 @@ def evaluate(*args, **kwargs):
 
 def __getattr__(name):
     # lazily loaded sub-packages: lbann.modules, lbann.models, lbann.contrib, lbann.util, ...
-    if name == "ops":                      # operator classes, as `import lbann.core.operators as ops`
+    if name == "ops":                      # operator classes (lbann.ops.Clamp, ...): served by the ops package
         import importlib
-        mod = importlib.import_module(f"{__name__}.core.operators")
-        globals()[name] = mod
-        return mod
+        return importlib.import_module(f"{__name__}.ops")
     if name in ("modules", "models", "contrib", "util", "launcher", "torch"):
         import importlib
         mod = importlib.import_module(f"{__name__}.{name}")
