@@ -161,3 +161,20 @@ def apply_layer_parallelism(model, args, world_size: int = 1) -> int:
     for i, relay in reversed(inserts):
         model.layers.insert(i, relay)
     return max(tag_of.values())
+
+
+def apply_all(model, args, world_size: int = 1) -> List[str]:
+    """Applies every switch that ``args`` carries and returns the extra driver arguments the
+    choice needs (``--num_subgrids`` for layer parallelism, ``--trainer_grid_height`` when the
+    sharded weights are shared by ``--fsdp-ranks`` ranks or layers are model-parallel)."""
+    extra: List[str] = []
+    apply_fsdp_mlp(model, args)
+    apply_fsdp_allweights(model, args)
+    changed = apply_ffn_model_parallelism(model, args)
+    grids = apply_layer_parallelism(model, args, world_size)
+    if grids:
+        extra.append(f"--num_subgrids={grids}")
+    height = getattr(args, "fsdp_ranks", 0) or (world_size if changed else 0)
+    if height and height > 1:
+        extra.append(f"--trainer_grid_height={height}")
+    return extra
