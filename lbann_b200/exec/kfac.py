@@ -20,8 +20,16 @@ per sample, damped with ``damping_bn_err`` and inverted like the other factors.
 
 With ``distribute_precondition_compute`` (or ``inverse_strategy: "each"``) block i is
 inverted by data-parallel rank i mod P only and the inverses travel to the others (the
-reference spreads inverses over ranks the same way, kfac.cpp:480-620; its asynchronous
-secondary grid is replaced by this round-robin).
+reference spreads inverses over ranks the same way, kfac.cpp:480-620).
+
+Asynchronous inverses (``--trainer_enable_subgrid_async_comm``, the reference's switch for its
+secondary grid, kfac.cpp:283-390,1109-1180: ranks set aside for the inversions hand their
+results to the training ranks one step late).  Here no GPU is set aside: at a refresh step the
+owner of a block starts the inversion of the current factors beside the training step (a side
+CUDA stream on a GPU, a worker thread on the host), the step itself preconditions with the
+inverses it already has, and the NEXT K-FAC step waits for the job, exchanges the result and
+installs it.  Every rank installs at the same step, so the ranks stay identical; only a
+block's very first inversion is synchronous.
 
 GRU layers (kfac_block_gru.cpp): per stacked layer and per product (input -> gates, hidden ->
 gates) one activation factor over samples x time steps and one error factor per gate; see
@@ -29,6 +37,7 @@ gates) one activation factor over samples x time steps and one error factor per 
 """
 from __future__ import annotations
 
+from concurrent.futures import ThreadPoolExecutor
 from typing import Dict, List
 
 import torch
@@ -119,6 +128,12 @@ class KFAC(SGDTrainingAlgorithm):
         self.root_only = str(msg.inverse_strategy).lower() == "root"
         self.inverses_computed = 0          # on this rank (tests read it)
         self.blocks: Dict[str, _Block] = {}
+        from ..utils import options as _opts
+        self.async_inverses = _opts.current().get_bool("trainer_enable_subgrid_async_comm")
+        self._pending: Dict[object, tuple] = {}     # block key -> job started at the last refresh
+        self._pool = None
+        self._side = None
+        self.async_installs = 0             # inverses that arrived one step late (tests read it)
 
     # ---------------------------------------------------------------- schedules
     def _damping(self, vals: List[float], step: int) -> float:
@@ -212,6 +227,70 @@ class KFAC(SGDTrainingAlgorithm):
             out.append(inv)
         return out
 
+    # ---------------------------------------------------------------- asynchronous inverses
+    def _start_job(self, par, index: int, mats, dampings):
+        """Start the inversion of ``mats`` beside the training step; returns the job."""
+        distributed = self.distribute and par is not None and par.dp_size > 1
+        owner = 0 if (self.root_only or not distributed) else index % par.dp_size
+        mine = (not distributed) or par.dp_rank == owner
+        mats = [M.clone() for M in mats]
+        if not mine:
+            return ("none", mats, None, distributed)
+        if mats[0].is_cuda:
+            if self._side is None:
+                self._side = torch.cuda.Stream()
+            side, cur = self._side, torch.cuda.current_stream()
+            side.wait_stream(cur)
+            with torch.cuda.stream(side):
+                out = [self._invert(M, d) for M, d in zip(mats, dampings)]
+                for t in mats + out:
+                    t.record_stream(side)
+            ev = torch.cuda.Event()
+            ev.record(side)
+            return ("stream", mats, (out, ev), distributed)
+        if self._pool is None:
+            self._pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix="kfac-inverse")
+        fut = self._pool.submit(lambda: [self._invert(M, d) for M, d in zip(mats, dampings)])
+        return ("thread", mats, fut, distributed)
+
+    def _finish_job(self, par, job):
+        kind, mats, handle, distributed = job
+        if kind == "none":
+            out = [torch.zeros_like(M) for M in mats]
+        elif kind == "stream":
+            out, ev = handle
+            torch.cuda.current_stream().wait_event(ev)
+        else:
+            out = handle.result()
+        if distributed:
+            for inv in out:
+                par.allreduce_sum_inplace(inv)
+        self.async_installs += len(out)
+        return out
+
+    def _refresh(self, key, have, refresh: bool, par, index: int, mats, dampings):
+        """The inverses to precondition with at this step.  ``have``: the installed ones (None
+        before the first inversion)."""
+        if not self.async_inverses:
+            return self._inverses(par, index, mats, dampings) if (refresh or have is None) else have
+        job = self._pending.pop(key, None)
+        if job is not None:
+            have = self._finish_job(par, job)
+        if have is None:
+            return self._inverses(par, index, mats, dampings)
+        if refresh:
+            self._pending[key] = self._start_job(par, index, mats, dampings)
+        return have
+
+    def shutdown(self):
+        for job in self._pending.values():
+            if job[0] == "thread":
+                job[2].result()
+        self._pending.clear()
+        if self._pool is not None:
+            self._pool.shutdown(wait=True)
+            self._pool = None
+
     def _precondition_gru(self, blk, par, dp, index, global_batch, refresh, d_act, d_err):
         """GRU block (src/execution_algorithms/kfac/kfac_block_gru.cpp): for every stacked
         layer and each of its two products (input -> gates, hidden -> gates) one activation
@@ -247,10 +326,10 @@ class KFAC(SGDTrainingAlgorithm):
                 else:
                     blk.A[key] = self.decay * blk.A[key] + (1 - self.decay) * A
                     blk.G[key] = [self.decay * o + (1 - self.decay) * n for o, n in zip(blk.G[key], Gs)]
-                if refresh or key not in blk.Ainv:
-                    invs = self._inverses(par, index, [blk.A[key]] + blk.G[key],
-                                          [d_act ** 0.5] + [d_err ** 0.5] * 3)
-                    blk.Ainv[key], blk.Ginv[key] = invs[0], invs[1:]
+                have = [blk.Ainv[key]] + list(blk.Ginv[key]) if key in blk.Ainv else None
+                invs = self._refresh((l.name, key), have, refresh, par, index, [blk.A[key]] + blk.G[key],
+                                     [d_act ** 0.5] + [d_err ** 0.5] * 3)
+                blk.Ainv[key], blk.Ginv[key] = invs[0], invs[1:]
                 gw = W.handle.grad.float().reshape(3 * H, -1)
                 gb = b.handle.grad.float().reshape(3 * H, 1) if b.handle.grad is not None else \
                     torch.zeros(3 * H, 1, device=gw.device)
@@ -286,8 +365,8 @@ class KFAC(SGDTrainingAlgorithm):
                     par.allreduce_sum_inplace(Fm)
                     Fm /= dp
                 blk.G = Fm if blk.G is None else self.decay * blk.G + (1 - self.decay) * Fm
-                if refresh or blk.Ginv is None:
-                    (blk.Ginv,) = self._inverses(par, index, [blk.G], [d_bn])
+                (blk.Ginv,) = self._refresh(l.name, None if blk.Ginv is None else [blk.Ginv], refresh, par,
+                                            index, [blk.G], [d_bn])
                 c = l.scale.handle.grad.numel()
                 g = torch.cat([l.scale.handle.grad.float().reshape(-1), l.bias.handle.grad.float().reshape(-1)])
                 nat = blk.Ginv @ g * self.lr_factor
@@ -308,13 +387,13 @@ class KFAC(SGDTrainingAlgorithm):
                 G /= dp
             blk.A = A if blk.A is None else self.decay * blk.A + (1 - self.decay) * A
             blk.G = G if blk.G is None else self.decay * blk.G + (1 - self.decay) * G
-            if refresh or blk.Ainv is None:
-                pi = 1.0
-                if self.use_pi:
-                    pi = float(torch.sqrt((blk.A.trace() / blk.A.shape[0]) /
-                                          (blk.G.trace() / blk.G.shape[0]).clamp_min(1e-30)).clamp(1e-3, 1e3))
-                blk.Ainv, blk.Ginv = self._inverses(par, index, [blk.A, blk.G],
-                                                    [pi * d_act ** 0.5, d_err ** 0.5 / pi])
+            pi = 1.0
+            if self.use_pi and (refresh or blk.Ainv is None):
+                pi = float(torch.sqrt((blk.A.trace() / blk.A.shape[0]) /
+                                      (blk.G.trace() / blk.G.shape[0]).clamp_min(1e-30)).clamp(1e-3, 1e3))
+            blk.Ainv, blk.Ginv = self._refresh(l.name, None if blk.Ainv is None else [blk.Ainv, blk.Ginv],
+                                               refresh, par, index, [blk.A, blk.G],
+                                               [pi * d_act ** 0.5, d_err ** 0.5 / pi])
             gw = l.w.handle.grad.float().reshape(blk.G.shape[0], -1)
             if l.b is not None and l.b.handle.grad is not None:
                 gw = torch.cat([gw, l.b.handle.grad.float().reshape(-1, 1)], 1)

@@ -211,6 +211,8 @@ class ExecTrainer:
         algo.evaluate(self, model, mode, report, max_batches)
 
     def shutdown(self):
+        if hasattr(self.algorithm, "shutdown"):
+            self.algorithm.shutdown()
         if self.data_coordinator is not None:
             for st in self.data_coordinator.modes.values():
                 r = getattr(st, "reader", None)

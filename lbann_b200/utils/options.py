@@ -19,6 +19,7 @@ _FLAGS = [
     "data_store_cache", "data_store_debug", "data_store_fail", "data_store_profile",
     "check_data", "keep_sample_order", "quiet", "write_sample_list", "z_score", "use_cuda_graph",
     "allow_multitrainer_global_statistics", "hang", "use_caliper", "deterministic",
+    "trainer_enable_subgrid_async_comm",       # K-FAC: factor inversions run beside the next step
 ]
 _OPTIONS = {
     # name: (type, default)

@@ -463,10 +463,13 @@ def ltfb(strategy):
     return {"world": world, "weights": allw, "num_trainers": tr.comm.num_trainers}
 
 
-def kfac_job(distribute, steps):
-    """K-FAC on a small MLP with batch norm; optionally the inverses are spread over the ranks."""
+def kfac_job(distribute, steps, asynchronous=0):
+    """K-FAC on a small MLP with batch norm; optionally the inverses are spread over the ranks
+    and computed beside the next step."""
     o = opts.reset()
     o.set("disable_cuda", True)
+    if asynchronous:
+        o.set("trainer_enable_subgrid_async_comm", True)
     x = lbann.Input(data_field="samples")
     t = lbann.Input(data_field="responses")
     h = lbann.FullyConnected(x, num_neurons=12, has_bias=True, name="fc1")
@@ -488,11 +491,16 @@ def kfac_job(distribute, steps):
     m = tr.build_model(exp.model)
     tr.train(m, num_batches=steps)
     w = {x_.name: float(x_.values.detach().double().norm()) for x_ in m.weights}
+    tr.algorithm.shutdown()                       # asynchronous jobs still running are counted too
     counts = torch.tensor([float(tr.algorithm.inverses_computed)])
     per_rank = [float(counts)]
+    all_w = [w]
     if tr.parallel is not None:
         per_rank = [float(v) for v in tr.comm.all_gather(counts, "trainer")]
-    res = {"weight_norms": w, "world": int(os.environ.get("WORLD_SIZE", "1")), "inverses": per_rank}
+        all_w = tr.comm.world_gather_object(w)
+    obj, _, _ = m.reduce_statistics("training")
+    res = {"weight_norms": w, "world": int(os.environ.get("WORLD_SIZE", "1")), "inverses": per_rank,
+           "all_weight_norms": all_w, "installs": tr.algorithm.async_installs, "objective": float(obj)}
     tr.shutdown()
     return res
 
@@ -756,7 +764,7 @@ if __name__ == "__main__":
     elif what == "subgraph":
         res = subgraph_branches(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "kfac":
-        res = kfac_job(int(sys.argv[3]), int(sys.argv[4]))
+        res = kfac_job(int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]) if len(sys.argv) > 5 else 0)
     elif what == "token_parallel":
         res = token_parallel(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "layer_parallel":

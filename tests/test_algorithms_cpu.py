@@ -383,3 +383,50 @@ def test_torch_lowering_keeps_registered_user_modules_whole():
     x = torch.randn(3, 6)
     got = lbann.evaluate(lt.compile(net, input=x)[0], x.numpy())
     torch.testing.assert_close(torch.from_numpy(got), net(x).detach(), rtol=1e-4, atol=1e-5)
+
+
+def test_kfac_asynchronous_inverses_arrive_one_step_late():
+    """With the asynchronous switch an inversion started at step t runs beside the step and is
+    installed at step t + 1: after two steps the installed inverses are those of the factors
+    after ONE step of the synchronous run (both runs are identical up to there)."""
+    from lbann_b200.exec.kfac import KFAC
+
+    def run(steps, asynchronous):
+        o = opts.reset()
+        o.set("disable_cuda", True)
+        if asynchronous:
+            o.set("trainer_enable_subgrid_async_comm", True)
+        torch.manual_seed(0)
+        sgd = lbann.BatchedIterativeOptimizer("sgd", epoch_count=1)
+        algo = lbann.KFAC("kfac", sgd, damping_act="1e-2", damping_err="1e-2", kronecker_decay=0.9,
+                          update_intervals="1", compute_interval=1)
+        exp = lbann.proto.serialize.build_experiment(
+            trainer=lbann.Trainer(mini_batch_size=16, random_seed=9, training_algo=algo), model=_mlp(),
+            data_reader=_reader(64, [8], "normal", response_dims=[3]),
+            optimizer=lbann.SGD(learn_rate=0.05, momentum=0.0))
+        tr = ExecTrainer(exp)
+        m = tr.build_model(exp.model)
+        tr.train(m, num_batches=steps)
+        k = tr.algorithm
+        assert isinstance(k, KFAC) and k.async_inverses == asynchronous
+        inv = {n: (b.Ainv.clone(), b.Ginv.clone()) for n, b in k.blocks.items()}
+        obj, _, _ = m.reduce_statistics("training")
+        installs, pending = k.async_installs, len(k._pending)
+        tr.shutdown()                              # waits for the jobs still running
+        assert not k._pending
+        return inv, (k.inverses_computed, installs, pending), obj
+
+    sync1, s1, _ = run(1, False)
+    async2, a2, _ = run(2, True)
+    assert s1 == (4, 0, 0)                         # two blocks, two factors each
+    # step 0 inverts in place (nothing to precondition with yet), step 1 starts jobs for both blocks
+    assert a2[1] == 0 and a2[2] == 2
+    for n in sync1:
+        assert torch.allclose(sync1[n][0], async2[n][0], rtol=1e-5, atol=1e-6), n
+        assert torch.allclose(sync1[n][1], async2[n][1], rtol=1e-5, atol=1e-6), n
+    # longer runs: the late inverses are installed and training still beats plain SGD
+    _, a12, obj_async = run(12, True)
+    assert a12[1] == 4 * 10 and a12[2] == 2 and a12[0] == 4 * 12
+    sgd = lbann.BatchedIterativeOptimizer("sgd", epoch_count=3)
+    plain = _fit(sgd)
+    assert math.isfinite(obj_async) and obj_async < plain, (plain, obj_async)

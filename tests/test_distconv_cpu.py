@@ -139,6 +139,21 @@ def test_kfac_inverses_spread_over_the_ranks(tmp_path):
         assert abs(v - dist["weight_norms"][k]) <= 1e-5 * max(1.0, abs(v)), k
 
 
+def test_kfac_asynchronous_inverses_keep_the_ranks_identical(tmp_path):
+    """Distributed and asynchronous: the owner inverts beside the next step, every rank installs
+    the result at the same (following) step, so the replicas never drift apart."""
+    res = _run(2, ["kfac", "1", "6", "1"], str(tmp_path / "a.json"))
+    sync = _run(2, ["kfac", "1", "6", "0"], str(tmp_path / "b.json"))
+    assert res["world"] == 2 and sum(res["inverses"]) == 30.0 and sorted(res["inverses"]) == [6.0, 24.0]
+    assert res["installs"] == 5 * 4                # steps 1..4 started jobs that a later step installed
+    a, b = res["all_weight_norms"]
+    for k, v in a.items():
+        if "running" not in k:                     # batch-norm statistics are local to a rank here
+            assert abs(v - b[k]) <= 1e-9 * max(1.0, abs(v)), k
+    # stale-by-one inverses give a slightly different, equally good trajectory
+    assert res["objective"] < 1.5 * sync["objective"], (res["objective"], sync["objective"])
+
+
 def test_subgraph_transformer_heads_on_two_grids(tmp_path):
     """Attention heads of an encoder dealt onto two sub-grids of two ranks each: same
     trajectory as one process running all heads."""
