@@ -75,7 +75,9 @@ class DistconvContext:
             SymmetricGroup(self.device, pg=comm.trainer_group)
         self.strategies: Dict[str, Strategy] = {}
         self.depth_groups = 1
-        self.height_groups = 1                    # second partitioned dimension (depth x height)
+        self.height_groups = 1                    # second and third partitioned dimensions
+        self.width_groups = 1                     # (depth x height x width grid)
+        self.width_rank = 0
         self.channel_groups = 1                   # partition of the channel (token) dimension of [N, C, F] tensors
         self.channel_rank = 0
         self.input_halo: Dict[str, int] = {}      # input layer -> halo planes uploaded with it
@@ -83,7 +85,7 @@ class DistconvContext:
         self.sample_group_index = 0
         self.depth_rank = 0
         self.height_rank = 0
-        self.line_pg = {}                         # tensor dim (2 depth, 3 height) -> process group of that line
+        self.line_pg = {}                         # tensor dim (2 depth, 3 height, 4 width) -> process group of that line
         self.dist: Dict[Tuple[str, int], str] = {}
         self._enabled: Dict[str, bool] = {}
         self._bufs: Dict[tuple, SymmetricBuffer] = {}
@@ -98,50 +100,59 @@ class DistconvContext:
     def plan(self, model_pb) -> None:
         """Depth / sample group sizes from the prototext alone (the data coordinator, which
         deals samples to the sample groups, is built before the model is)."""
-        depth = height = channel = 1
+        depth = height = width = channel = 1
         for l in model_pb.layer:
             if l.HasField("parallel_strategy"):
                 st = Strategy(l.parallel_strategy, self.world)
                 if st.is_spatial():
-                    depth, height = max(depth, st.depth), max(height, st.height)
+                    depth, height, width = max(depth, st.depth), max(height, st.height), max(width, st.width)
                 elif st.is_channel() and not (l.HasField("convolution") or l.HasField("deconvolution")):
                     channel = max(channel, st.channel)
-        if depth * height > 1 and self.world % (depth * height) == 0:
-            self._set_grid(depth, height)
+        if depth * height * width > 1 and self.world % (depth * height * width) == 0:
+            self._set_grid(depth, height, 1, width)
         elif channel > 1 and self.world % channel == 0:
             self._set_grid(1, 1, channel)
 
-    def _set_grid(self, depth: int, height: int, channel: int = 1) -> None:
-        """Ranks of one sample group are consecutive and form a depth x height grid, height
-        fastest: rank = (sample_group * depth + depth_rank) * height + height_rank.  A channel
-        partition (no spatial split) uses the same consecutive ranks along the channel dimension."""
-        spatial = depth * height * channel
+    def _set_grid(self, depth: int, height: int, channel: int = 1, width: int = 1) -> None:
+        """Ranks of one sample group are consecutive and form a depth x height x width grid,
+        width fastest: rank = ((sample_group * depth + depth_rank) * height + height_rank) * width
+        + width_rank.  A channel partition (no spatial split) uses the same consecutive ranks
+        along the channel dimension."""
+        spatial = depth * height * width * channel
         self.depth_groups, self.height_groups, self.channel_groups = depth, height, channel
+        self.width_groups = width
         self.num_sample_groups = self.world // spatial
         self.sample_group_index = self.rank // spatial
-        self.depth_rank = (self.rank % spatial) // (height * channel)
-        self.height_rank = (self.rank // channel) % height
+        self.depth_rank = (self.rank % spatial) // (height * width * channel)
+        self.height_rank = (self.rank // (width * channel)) % height
+        self.width_rank = (self.rank // channel) % width
         self.channel_rank = self.rank % channel
 
     @property
     def spatial_size(self) -> int:
-        """Ranks that share one sample (depth_groups x height_groups, or channel_groups)."""
-        return self.depth_groups * self.height_groups * self.channel_groups
+        """Ranks that share one sample (depth x height x width groups, or channel_groups)."""
+        return self.depth_groups * self.height_groups * self.width_groups * self.channel_groups
+
+    @property
+    def grid_mode(self) -> bool:
+        """More than the depth dimension is partitioned."""
+        return self.height_groups * self.width_groups > 1
 
     @property
     def spatial_rank(self) -> int:
-        return (self.depth_rank * self.height_groups + self.height_rank) * self.channel_groups + self.channel_rank
+        return (((self.depth_rank * self.height_groups + self.height_rank) * self.width_groups
+                 + self.width_rank) * self.channel_groups + self.channel_rank)
 
     @property
     def fused(self) -> bool:
         """The peer-memory kernels (halo exchange inside the convolutions, all-to-all
         redistribution, small all-reduce) serve the depth-only partition; a depth x height
         grid exchanges its halos with library collectives over the grid's lines."""
-        return self.group.native and self.height_groups == 1 and self.channel_groups == 1
+        return self.group.native and not self.grid_mode and self.channel_groups == 1
 
     def prepare_model(self, model):
         self._enabled.clear()
-        depth = height = channel = 1
+        depth = height = width = channel = 1
         for l in model.layers:
             if l.parallel_strategy is None:
                 continue
@@ -149,25 +160,21 @@ class DistconvContext:
             if l.type in ("convolution", "deconvolution") and (st.channel > 1 or st.filter > 1):
                 raise ValueError(f"layer '{l.name}': channel / filter parallelism is not "
                                  f"supported for convolutions")
-            if st.width > 1:
-                raise NotImplementedError(
-                    f"layer '{l.name}': depth and height can be partitioned, width cannot "
-                    f"(width_groups > 1 requested)")
             self.strategies[l.name] = st
             if st.is_spatial():
-                if (depth, height) not in ((1, 1), (st.depth, st.height)):
+                if (depth, height, width) not in ((1, 1, 1), (st.depth, st.height, st.width)):
                     raise ValueError("all distconv layers of a model must use the same "
-                                     "depth_groups and height_groups")
-                depth, height = st.depth, st.height
+                                     "depth_groups, height_groups and width_groups")
+                depth, height, width = st.depth, st.height, st.width
             elif st.is_channel() and l.type not in ("convolution", "deconvolution"):
                 if channel not in (1, st.channel):
                     raise ValueError("all channel-partitioned layers of a model must use the same channel_groups")
                 channel = st.channel
-        if channel > 1 and depth * height > 1:
-            raise ValueError("channel_groups cannot be combined with depth / height partitions in one model")
-        self._set_grid(depth, height, channel)
+        if channel > 1 and depth * height * width > 1:
+            raise ValueError("channel_groups cannot be combined with spatial partitions in one model")
+        self._set_grid(depth, height, channel, width)
         self.depth_pg = "trainer"
-        self.line_pg = {2: "trainer", 3: "trainer"}
+        self.line_pg = {2: "trainer", 3: "trainer", 4: "trainer"}
         if channel > 1:
             # ranks that share a sample: consecutive groups of `channel` ranks
             if self.num_sample_groups > 1:
@@ -176,8 +183,8 @@ class DistconvContext:
                     pg = self.comm.new_group([base + sgi * channel + i for i in range(channel)])
                     if sgi == self.sample_group_index:
                         self.depth_pg = pg
-        elif height > 1:
-            self._build_grid_groups(depth, height)
+        elif height * width > 1:
+            self._build_grid_groups(depth, height, width)
         elif depth > 1 and self.num_sample_groups > 1:
             # sample x depth partition (left-over ranks multiply the sample groups,
             # src/layers/distconv_adapter.cpp:227-336): the mini-batch is dealt to the sample
@@ -193,7 +200,7 @@ class DistconvContext:
             self.group = SymmetricGroup(self.device, pg=self.depth_pg)
         # inputs consumed only by distconv layers are sliced on the host before upload
         tr = getattr(model, "trainer", None)
-        if height > 1 and tr is not None and tr.data_coordinator is not None:
+        if height * width > 1 and tr is not None and tr.data_coordinator is not None:
             slicers = {}
             for l in model.layers:
                 if l.type != "input":
@@ -203,11 +210,13 @@ class DistconvContext:
                 dims = tr.data_coordinator.dims(f)
                 # [C, D, H, W] volumes and [D, H, W] per-voxel labels: depth is third from last
                 if (kids and all(self.enabled(k) for k in kids) and len(dims) in (3, 4)
-                        and dims[-3] % depth == 0 and dims[-2] % height == 0):
-                    dl, hl = dims[-3] // depth, dims[-2] // height
+                        and dims[-3] % depth == 0 and dims[-2] % height == 0 and dims[-1] % width == 0):
+                    dl, hl, wl = dims[-3] // depth, dims[-2] // height, dims[-1] // width
                     ax = len(dims) - 2            # depth axis of the mini-batch tensor
                     slicers[f] = [(ax, self.depth_rank * dl, (self.depth_rank + 1) * dl, 0),
                                   (ax + 1, self.height_rank * hl, (self.height_rank + 1) * hl, 0)]
+                    if width > 1:
+                        slicers[f].append((ax + 2, self.width_rank * wl, (self.width_rank + 1) * wl, 0))
                     self.input_halo[l.name] = 0
             tr.data_coordinator.field_slices = slicers
             self.sliced_fields = set(slicers)
@@ -234,13 +243,19 @@ class DistconvContext:
         else:
             self.sliced_fields = set()
 
-    def _build_grid_groups(self, depth: int, height: int) -> None:
-        """Process groups of a depth x height grid: the ranks of this sample group (sums of
-        partial losses, redistribution) and the two lines through this rank (halo exchange
-        along depth and along height; src/layers/distconv_adapter.cpp:227-336 sets up the
-        same locale shapes).  Every rank creates every group, in the same order."""
-        spatial = depth * height
+    def _build_grid_groups(self, depth: int, height: int, width: int = 1) -> None:
+        """Process groups of a depth x height x width grid: the ranks of this sample group (sums
+        of partial losses, redistribution) and the lines through this rank (halo exchange along
+        depth, height and width; src/layers/distconv_adapter.cpp:227-336 sets up the same
+        locale shapes).  Every rank creates every group, in the same order."""
+        spatial = depth * height * width
         base = self.comm.trainer_rank * self.world
+        extent = (depth, height, width)
+        me = (self.depth_rank, self.height_rank, self.width_rank)
+
+        def rank_of(c):
+            return (c[0] * height + c[1]) * width + c[2]
+
         for sgi in range(self.num_sample_groups):
             first = base + sgi * spatial
             mine = sgi == self.sample_group_index
@@ -248,15 +263,20 @@ class DistconvContext:
                 pg = self.comm.new_group([first + i for i in range(spatial)])
                 if mine:
                     self.depth_pg = pg
-            for hr in range(height):                  # lines along depth: fixed height rank
-                pg = self.comm.new_group([first + d * height + hr for d in range(depth)]) \
-                    if depth > 1 else None
-                if mine and hr == self.height_rank and pg is not None:
-                    self.line_pg[2] = pg
-            for dr in range(depth):                   # lines along height: fixed depth rank
-                pg = self.comm.new_group([first + dr * height + i for i in range(height)])
-                if mine and dr == self.depth_rank:
-                    self.line_pg[3] = pg
+            for axis in range(3):                     # lines along `axis`: the other two coordinates fixed
+                if extent[axis] == 1:
+                    continue
+                o1, o2 = [a for a in range(3) if a != axis]
+                for c1 in range(extent[o1]):
+                    for c2 in range(extent[o2]):
+                        coords = []
+                        for i in range(extent[axis]):
+                            c = [0, 0, 0]
+                            c[axis], c[o1], c[o2] = i, c1, c2
+                            coords.append(first + rank_of(c))
+                        pg = self.comm.new_group(coords)
+                        if mine and me[o1] == c1 and me[o2] == c2:
+                            self.line_pg[2 + axis] = pg
 
     def _input_halo(self, kids) -> int:
         """Halo planes to upload with an input: what its only consumer, a stride-1 3-D
@@ -307,7 +327,7 @@ class DistconvContext:
         dims = layer.in_dims[0] if getattr(layer, "in_dims", None) else None
         if not dims or len(dims) != 4:
             return True
-        for axis, P in ((0, self.depth_groups), (1, self.height_groups)):
+        for axis, P in ((0, self.depth_groups), (1, self.height_groups), (2, self.width_groups)):
             if P == 1:
                 continue
             D = int(dims[1 + axis])
@@ -349,6 +369,9 @@ class DistconvContext:
                 if self.height_groups > 1:
                     hl = x.shape[ax + 1] // self.height_groups
                     x = x.narrow(ax + 1, self.height_rank * hl, hl)
+                if self.width_groups > 1:
+                    wl = x.shape[ax + 2] // self.width_groups
+                    x = x.narrow(ax + 2, self.width_rank * wl, wl)
                 out.append(x)
             elif have == SPATIAL and want == SAMPLE:
                 out.append(_Redistribute.apply(x, self, True, pn))
@@ -425,7 +448,7 @@ class DistconvContext:
         inside its kernel (ops/nn.py, PoolFusion); only the path without an exchange takes it."""
         from ..ops import nn
         halo = tuple((k - 1) // 2 * d for k, d in zip(layer.ksize, layer.dil))
-        if self.height_groups > 1:
+        if self.grid_mode:
             return self._grid_convolution(layer, x, halo)
         hd = halo[0] if layer.nd == 3 else 0
         parent = layer.parent_names[0] if layer.parent_names else None
@@ -450,17 +473,18 @@ class DistconvContext:
                               getattr(layer, "skip_act_grad", False))
 
     def _grid_convolution(self, layer, x, halo):
-        """Convolution on a depth x height grid: the halo planes along depth are exchanged
-        first, then the halo rows along height of the depth-extended tensor, which brings the
-        corner regions from the diagonal neighbours in two hops
+        """Convolution on a depth x height (x width) grid: the halo planes along depth are
+        exchanged first, then the halo rows along height of the depth-extended tensor, then the
+        halo columns along width, which brings the edge and corner regions from the diagonal
+        neighbours in two or three hops
         (src/layers/learning/base_convolution.cpp:1355-1445 exchanges per dimension likewise)."""
         from ..ops import nn
         if layer.nd != 3:
-            raise NotImplementedError("a depth x height partition needs 3-D convolutions")
-        parts = (self.depth_groups, self.height_groups, 1)
+            raise NotImplementedError("a grid partition needs 3-D convolutions")
+        parts = (self.depth_groups, self.height_groups, self.width_groups)
         pad = list(layer.pad)
         xe = x
-        for axis in (0, 1):
+        for axis in (0, 1, 2):
             if parts[axis] == 1:
                 continue
             if layer.pad[axis] != halo[axis]:
@@ -484,9 +508,10 @@ class DistconvContext:
 
     def pooling(self, layer, x):
         from ..ops import nn
-        if self.height_groups > 1:
-            if any(layer.k[a] != layer.stride[a] or layer.pad[a] != 0 for a in (0, 1)):
-                raise NotImplementedError("pooling on a depth x height grid needs windows that "
+        if self.grid_mode:
+            parts = (self.depth_groups, self.height_groups, self.width_groups)
+            if any(layer.k[a] != layer.stride[a] or layer.pad[a] != 0 for a in range(3) if parts[a] > 1):
+                raise NotImplementedError("pooling on a grid partition needs windows that "
                                           "do not overlap (kernel == stride, no padding)")
             act = getattr(layer, "bwd_act", (0, 0.0))
             return nn.pooling(x, layer.k, layer.pad, layer.stride, layer.mode, act[0], act[1])
@@ -716,8 +741,8 @@ class _AllReduceSum(torch.autograd.Function):
 
 
 class LineHaloExchange(torch.autograd.Function):
-    """Halo exchange along one dimension of a depth x height grid.  x: logical
-    [N, C, D, H, W]; ``dim`` = 2 (depth) or 3 (height); the result is 2h longer along it,
+    """Halo exchange along one dimension of a depth x height x width grid.  x: logical
+    [N, C, D, H, W]; ``dim`` = 2 (depth), 3 (height) or 4 (width); the result is 2h longer along it,
     with the neighbours' boundary slices at either end (``fill`` beyond the global
     boundary).  The ranks of the line through this rank trade their boundary slices with a
     library all-gather; backward sends the gradients of the received slices back and adds
@@ -725,8 +750,8 @@ class LineHaloExchange(torch.autograd.Function):
 
     @staticmethod
     def forward(ctx, x, dc: "DistconvContext", h: int, dim: int, fill: float = 0.0):
-        P = dc.depth_groups if dim == 2 else dc.height_groups
-        r = dc.depth_rank if dim == 2 else dc.height_rank
+        P = (dc.depth_groups, dc.height_groups, dc.width_groups)[dim - 2]
+        r = (dc.depth_rank, dc.height_rank, dc.width_rank)[dim - 2]
         L = x.shape[dim]
         ctx.meta = (dc, h, dim, P, r, L)
         lo, hi = x.narrow(dim, 0, h), x.narrow(dim, L - h, h)
@@ -910,20 +935,22 @@ class _GatherChannels(torch.autograd.Function):
 
 
 def _redistribute_cl(x_cl, dc, to_sample, tag, total, P, r, es, grp, S):
-    if dc.height_groups > 1:
-        # depth x height grid: every rank of the sample group contributes its brick
-        Hg, S, sr = dc.height_groups, dc.spatial_size, dc.spatial_rank
+    if dc.grid_mode:
+        # grid partition: every rank of the sample group contributes its brick
+        Hg, Wg, S, sr = dc.height_groups, dc.width_groups, dc.spatial_size, dc.spatial_rank
         parts = dc.comm.all_gather(x_cl, dc.depth_pg)
         if to_sample:       # my samples (sr, sr + S, ...) of every brick, bricks put together
-            out = torch.cat([torch.cat([parts[d * Hg + i][sr::S] for i in range(Hg)], dim=2)
+            out = torch.cat([torch.cat([torch.cat([parts[(d * Hg + i) * Wg + j][sr::S] for j in range(Wg)], dim=3)
+                                        for i in range(Hg)], dim=2)
                              for d in range(P)], dim=1)
         else:               # my brick of every rank's samples, samples interleaved again
-            ns, D, H = x_cl.shape[0], x_cl.shape[1], x_cl.shape[2]
-            Dl, Hl = D // P, H // Hg
-            out = torch.empty((total, Dl, Hl) + tuple(x_cl.shape[3:]), dtype=x_cl.dtype, device=x_cl.device)
+            ns, D, H, W = x_cl.shape[:4]
+            Dl, Hl, Wl = D // P, H // Hg, W // Wg
+            out = torch.empty((total, Dl, Hl, Wl) + tuple(x_cl.shape[4:]), dtype=x_cl.dtype, device=x_cl.device)
             for q, part in enumerate(parts):
                 cq = len(range(q, total, S))
-                out[q::S] = part[:cq, r * Dl:(r + 1) * Dl, dc.height_rank * Hl:(dc.height_rank + 1) * Hl]
+                out[q::S] = part[:cq, r * Dl:(r + 1) * Dl, dc.height_rank * Hl:(dc.height_rank + 1) * Hl,
+                                 dc.width_rank * Wl:(dc.width_rank + 1) * Wl]
         return out.permute(0, 4, 1, 2, 3)
     if not dc.fused:
         parts = dc.comm.all_gather(x_cl, dc.depth_pg)

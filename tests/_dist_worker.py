@@ -23,8 +23,10 @@ def cosmoflow(depth_groups, steps, dtype, width=32, channels=(8, 16, 16), graph=
         o.set("use_cuda_graph", True)
     world = int(os.environ.get("WORLD_SIZE", "1"))
     height_groups = int(os.environ.get("LBANN_TEST_HEIGHT_GROUPS", "1"))
-    ps = lbann.get_parallel_strategy_args(depth_groups=depth_groups, height_groups=height_groups) \
-        if depth_groups * height_groups > 1 else None
+    width_groups = int(os.environ.get("LBANN_TEST_WIDTH_GROUPS", "1"))
+    ps = lbann.get_parallel_strategy_args(depth_groups=depth_groups, height_groups=height_groups,
+                                          width_groups=width_groups) \
+        if depth_groups * height_groups * width_groups > 1 else None
     model = construct_cosmoflow_model(width, 4, 4, num_epochs=1, channels=tuple(channels), pool_mode="max",
                                       conv_bias=False, fc_sizes=(32, 16), parallel_strategy=ps)
     exp = lbann.proto.serialize.build_experiment(

@@ -207,6 +207,20 @@ def test_distconv_depth_x_height_grid_matches_single(tmp_path):
         assert abs(v - grid["weight_norms"][k]) <= 1e-3 * max(1.0, abs(v)), k
 
 
+@pytest.mark.parametrize("ranks,depth,height,width", [(2, 1, 1, 2), (4, 1, 2, 2), (8, 2, 2, 2)])
+def test_distconv_width_partitions_match_single(tmp_path, ranks, depth, height, width):
+    """Width alone, a height x width grid and a 2 x 2 x 2 grid over all three dimensions (edge and
+    corner regions arrive over two and three hops): same losses and weights as one process."""
+    single = _run(1, ["cosmoflow", "1", "3"], str(tmp_path / "a.json"))
+    grid = _run(ranks, ["cosmoflow", str(depth), "3"], str(tmp_path / "b.json"),
+                {"LBANN_TEST_HEIGHT_GROUPS": str(height), "LBANN_TEST_WIDTH_GROUPS": str(width)}, timeout=900)
+    assert grid["world"] == ranks and grid["halo_bytes"] > 0
+    for a, b in zip(single["losses"], grid["losses"]):
+        assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], grid["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - grid["weight_norms"][k]) <= 1e-3 * max(1.0, abs(v)), k
+
+
 @pytest.mark.parametrize("ranks,depth,height", [(2, 2, 1), (2, 1, 2), (4, 2, 2)])
 def test_unet_on_spatial_partitions_matches_single(tmp_path, ranks, depth, height):
     """A small 3-D U-Net (convolution + batch norm over all ranks + ReLU, max pooling, 2x
