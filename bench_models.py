@@ -39,8 +39,9 @@ def _build(lbann, args, world):
         # depth dimension is split over them (strong scaling of one global mini-batch)
         from lbann_b200.models import construct_unet3d_model
         # --height-groups H: a (world / H) x H grid over depth and height instead of depth only
-        hg = max(1, args.height_groups)
-        ps = lbann.get_parallel_strategy_args(depth_groups=world // hg, height_groups=hg) if world > 1 else None
+        hg, wg = max(1, args.height_groups), max(1, args.width_groups)
+        ps = lbann.get_parallel_strategy_args(depth_groups=world // (hg * wg), height_groups=hg,
+                                              width_groups=wg) if world > 1 else None
         model = construct_unet3d_model(num_classes=3, base_channels=32, levels=4, parallel_strategy=ps)
         v = args.volume
         r = lbann.reader_pb2.Reader()
@@ -119,8 +120,9 @@ def ours(args):
                "gpu_launches": native.launches() - n0, "loss": loss, "device_status": status,
                "cuda_graph": bool(getattr(m, "_graph_mode", False))}
         if args.model == "unet3d" and world > 1:
-            hg = max(1, args.height_groups)
-            out["parallelism"] = f"distconv depth x{world // hg}" + (f" height x{hg}" if hg > 1 else "")
+            hg, wg = max(1, args.height_groups), max(1, args.width_groups)
+            out["parallelism"] = f"distconv depth x{world // (hg * wg)}" + (f" height x{hg}" if hg > 1 else "") + \
+                (f" width x{wg}" if wg > 1 else "")
         if args.model == "gpt":
             out["tokens_per_s"] = round(gb * args.seq / ms * 1e3, 1)
             out["config"] = {"layers": args.layers, "d_model": args.d_model, "heads": args.heads,
@@ -237,6 +239,7 @@ def main():
     ap.add_argument("--volume", type=int, default=128, help="edge of the U-Net input volume")
     ap.add_argument("--height-groups", type=int, default=1,
                     help="U-Net: ranks along height (the rest of the ranks split depth)")
+    ap.add_argument("--width-groups", type=int, default=1, help="U-Net: ranks along width")
     ap.add_argument("--layers", type=int, default=4)
     ap.add_argument("--d-model", type=int, default=2048)
     ap.add_argument("--heads", type=int, default=16)
