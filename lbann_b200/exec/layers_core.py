@@ -107,6 +107,7 @@ def sharded_linear_ok(layer, par) -> bool:
 
 class _ConvBase(ExecLayer):
     supports_distconv = True
+    supports_channel_parallel = True        # channel / filter partition (convolution only)
 
     def _common(self, in_dims):
         p = self.params
@@ -163,6 +164,7 @@ class Convolution(_ConvBase):
 class Deconvolution(_ConvBase):
     """Transposed convolution, kernel Cin x Cout/groups x k...
     (src/layers/learning/deconvolution.cpp)."""
+    supports_channel_parallel = False
 
     def setup(self, in_dims):
         self._common(in_dims)

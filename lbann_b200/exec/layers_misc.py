@@ -228,6 +228,7 @@ class Upsample(ExecLayer):
 class Pooling(ExecLayer):
     """Max / average pooling (src/layers/transform/pooling.cpp:111-176)."""
     supports_distconv = True
+    supports_channel_parallel = True
 
     def setup(self, in_dims):
         p = self.params

@@ -321,6 +321,9 @@ class ExecModel:
                 continue
             if l.data_layout == "model_parallel":
                 continue
+            if (l.type == "convolution" and self.distconv is not None and self.distconv.channel_groups > 1
+                    and self.distconv.enabled(l)):
+                continue          # channel / filter partition: the general path, nothing folded in
             l.fused_act = act
             c.fused_into_parent = True
             # conv -> (fused act) -> max pooling: the pooling backward kernel also applies the

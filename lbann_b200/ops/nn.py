@@ -1035,10 +1035,15 @@ def batch_norm(x, sh, bh, run_mean, run_var, training: bool, eps: float, decay: 
         n = x.numel() / C
         s = torch.stack([xf.sum(dims), (xf * xf).sum(dims)])
         if reduce_fn is not None:
-            s = _ReduceSum.apply(s, reduce_fn)
-            n = n * count_scale
+            # the entry count travels with the sums: the ranks' shares of a mini-batch may differ
+            # (the last mini-batch of an epoch, a sample-parallel tail behind a partitioned part)
+            s = _ReduceSum.apply(torch.cat([s, s.new_full((1, C), n)]), reduce_fn)
+            n = s[2].detach()
+            var_scale = n / (n - correction).clamp_min(1.0)
+        else:
+            var_scale = n / (n - correction)
         mean = s[0] / n
-        var = (s[1] / n - mean * mean) * (n / (n - correction))
+        var = (s[1] / n - mean * mean) * var_scale
         var = torch.clamp(var, min=eps)
         with torch.no_grad():
             if run_mean is not None:

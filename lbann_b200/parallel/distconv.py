@@ -50,7 +50,8 @@ class Strategy:
         self.channel, self.filter = g("channel_groups"), g("filter_groups")
         if world == 1:
             self.sample = self.depth = self.height = self.width = self.channel = self.filter = 1
-        spatial = self.depth * self.height * self.width * self.channel * self.filter
+        # channel and filter groups name the SAME ranks (input channels in, output filters out)
+        spatial = self.depth * self.height * self.width * max(self.channel, self.filter)
         if world % spatial:
             raise ValueError(f"parallel strategy uses {spatial} ranks, trainer has {world}")
         self.sample = world // spatial            # left-over ranks become sample groups
@@ -106,7 +107,7 @@ class DistconvContext:
                 st = Strategy(l.parallel_strategy, self.world)
                 if st.is_spatial():
                     depth, height, width = max(depth, st.depth), max(height, st.height), max(width, st.width)
-                elif st.is_channel() and not (l.HasField("convolution") or l.HasField("deconvolution")):
+                elif st.is_channel() and not l.HasField("deconvolution"):
                     channel = max(channel, st.channel)
         if depth * height * width > 1 and self.world % (depth * height * width) == 0:
             self._set_grid(depth, height, 1, width)
@@ -157,16 +158,23 @@ class DistconvContext:
             if l.parallel_strategy is None:
                 continue
             st = Strategy(l.parallel_strategy, self.world)
-            if l.type in ("convolution", "deconvolution") and (st.channel > 1 or st.filter > 1):
+            if l.type == "deconvolution" and (st.channel > 1 or st.filter > 1):
                 raise ValueError(f"layer '{l.name}': channel / filter parallelism is not "
-                                 f"supported for convolutions")
+                                 f"supported for transposed convolutions")
+            if l.type == "convolution" and (st.channel > 1 or st.filter > 1):
+                if st.is_spatial():
+                    raise ValueError(f"layer '{l.name}': channel / filter parallelism cannot be "
+                                     f"combined with a spatial partition")
+                if st.filter not in (1, st.channel) or st.channel == 1:
+                    raise ValueError(f"layer '{l.name}': a channel / filter partition needs "
+                                     f"channel_groups == filter_groups")
             self.strategies[l.name] = st
             if st.is_spatial():
                 if (depth, height, width) not in ((1, 1, 1), (st.depth, st.height, st.width)):
                     raise ValueError("all distconv layers of a model must use the same "
                                      "depth_groups, height_groups and width_groups")
                 depth, height, width = st.depth, st.height, st.width
-            elif st.is_channel() and l.type not in ("convolution", "deconvolution"):
+            elif st.is_channel() and l.type != "deconvolution":
                 if channel not in (1, st.channel):
                     raise ValueError("all channel-partitioned layers of a model must use the same channel_groups")
                 channel = st.channel
@@ -317,6 +325,8 @@ class DistconvContext:
         dims = getattr(layer, "in_dims", None)
         if not dims:
             return True
+        if layer.type == "convolution" and (layer.groups != 1 or layer.cout % self.channel_groups):
+            return False
         return all(len(d) >= 2 and int(d[0]) % self.channel_groups == 0 for d in dims)
 
     def _feasible(self, layer) -> bool:
@@ -447,6 +457,8 @@ class DistconvContext:
         """``fuse_pool`` / ``pool_layer``: the 2^3 max pooling behind this convolution may run
         inside its kernel (ops/nn.py, PoolFusion); only the path without an exchange takes it."""
         from ..ops import nn
+        if self.channel_groups > 1:
+            return self._channel_convolution(layer, x)
         halo = tuple((k - 1) // 2 * d for k, d in zip(layer.ksize, layer.dil))
         if self.grid_mode:
             return self._grid_convolution(layer, x, halo)
@@ -471,6 +483,25 @@ class DistconvContext:
                               layer.ksize, pad, layer.stride, layer.dil, layer.groups,
                               layer.fused_act[0], layer.fused_act[1],
                               getattr(layer, "skip_act_grad", False))
+
+    def _channel_convolution(self, layer, x):
+        """Channel / filter partition (src/layers/learning/base_convolution.cpp with
+        channel_groups == filter_groups): the input arrives split along its channels, every rank
+        gathers it, applies ITS block of filters and leaves the output split along the filters.
+        The kernel stays whole on every rank; a rank's gradient is non-zero in its filter rows
+        only and the sum over the ranks puts the rows together."""
+        import torch.nn.functional as F
+        from ..ops.gemm import _ACT_FN
+        P, r = self.channel_groups, self.channel_rank
+        xg = _GatherChannels.apply(x, self)
+        kl = layer.cout // P
+        w = layer.w.handle.master[r * kl:(r + 1) * kl]
+        b = None if layer.b is None else layer.b.handle.master[r * kl:(r + 1) * kl]
+        if w.dtype != xg.dtype:
+            w, b = w.to(xg.dtype), (None if b is None else b.to(xg.dtype))
+        fn = {1: F.conv1d, 2: F.conv2d, 3: F.conv3d}[layer.nd]
+        y = fn(xg, w, b, tuple(layer.stride), tuple(layer.pad), tuple(layer.dil), 1)
+        return _ACT_FN[layer.fused_act[0]](y, layer.fused_act[1])
 
     def _grid_convolution(self, layer, x, halo):
         """Convolution on a depth x height (x width) grid: the halo planes along depth are
@@ -508,6 +539,9 @@ class DistconvContext:
 
     def pooling(self, layer, x):
         from ..ops import nn
+        if self.channel_groups > 1:            # every channel is pooled by itself
+            act = getattr(layer, "bwd_act", (0, 0.0))
+            return nn.pooling(x, layer.k, layer.pad, layer.stride, layer.mode, act[0], act[1])
         if self.grid_mode:
             parts = (self.depth_groups, self.height_groups, self.width_groups)
             if any(layer.k[a] != layer.stride[a] or layer.pad[a] != 0 for a in range(3) if parts[a] > 1):

@@ -653,6 +653,61 @@ def token_parallel(channel_groups, steps):
     return res
 
 
+def filter_parallel(channel_groups, steps):
+    """Two 3-D convolutions with bias, leaky ReLU and max pooling whose channels / filters are
+    split over the ranks (channel_groups == filter_groups), a batch norm (not partitioned: runs
+    sample-parallel after a redistribution) and a fully-connected head."""
+    o = opts.reset()
+    if os.environ.get("LBANN_TEST_DEVICE", "cpu") == "cpu":
+        o.set("disable_cuda", True)
+    ps = lbann.get_parallel_strategy_args(channel_groups=channel_groups, filter_groups=channel_groups) \
+        if channel_groups > 1 else {}
+    x = lbann.Input(data_field="samples")
+    t = lbann.Input(data_field="responses")
+    vol = lbann.Identity(lbann.Reshape(x, dims=[4, 8, 8, 8]), name="volume", parallel_strategy=ps)
+
+    def conv(h, n, name):
+        return lbann.Convolution(h, num_dims=3, out_channels=n, kernel_size=3, padding=1, stride=1, has_bias=True,
+                                 name=name, parallel_strategy=ps)
+
+    def pool(h, name):
+        return lbann.Pooling(h, num_dims=3, pool_dims_i=2, pool_strides_i=2, pool_pads_i=0, pool_mode="max",
+                             name=name, parallel_strategy=ps)
+    h = pool(lbann.LeakyRelu(conv(vol, 8, "conv1"), negative_slope=0.1, name="act1", parallel_strategy=ps), "pool1")
+    h = lbann.BatchNormalization(h, name="bn", epsilon=1e-5, statistics_group_size=-1)
+    h = pool(lbann.LeakyRelu(conv(h, 12, "conv2"), negative_slope=0.1, name="act2", parallel_strategy=ps), "pool2")
+    y = lbann.FullyConnected(h, num_neurons=4, has_bias=True, name="head")
+    loss = lbann.MeanSquaredError(y, t, name="mse")
+    model = lbann.Model(1, layers=list(lbann.traverse_layer_graph([x, t])),
+                        objective_function=lbann.ObjectiveFunction([loss]))
+    from test_models_cpu import _reader
+    exp = lbann.proto.serialize.build_experiment(
+        trainer=lbann.Trainer(mini_batch_size=6, random_seed=31), model=model,
+        data_reader=_reader(12, [4 * 8 * 8 * 8], "normal", response_dims=[4]),
+        optimizer=lbann.SGD(learn_rate=0.01, momentum=0.9))
+    tr = ExecTrainer(exp)
+    mdl = tr.build_model(exp.model)
+    dc = tr.data_coordinator
+    dc.start_epoch("training")
+    losses = []
+    for _ in range(steps):
+        b_ = dc.next_batch("training")
+        if b_ is None:
+            dc.start_epoch("training")
+            b_ = dc.next_batch("training")
+        mdl.train_step(b_.tensors, b_.global_size)
+        vv = mdl.last_objective.detach().float().reshape(1).clone()
+        if tr.parallel is not None:
+            tr.comm.allreduce(vv, "trainer", "sum")
+        losses.append(float(vv))
+    w = {x_.name: float(x_.values.detach().double().norm()) for x_ in mdl.weights if "running" not in x_.name}
+    spatial = sorted(n for n, d in (tr.distconv.dist.items() if tr.distconv is not None else []) if d == "spatial")
+    res = {"losses": losses, "weight_norms": w, "world": int(os.environ.get("WORLD_SIZE", "1")),
+           "partitioned": spatial, "sample_groups": tr.distconv.num_sample_groups if tr.distconv is not None else 1}
+    tr.shutdown()
+    return res
+
+
 def subgraph_branches(num_subgrids, steps):
     """Two branches of a small network on two sub-grids (grid tags 1 and 2), joined by a sum on
     the whole trainer; a third output goes through a sum across the grids."""
@@ -767,6 +822,8 @@ if __name__ == "__main__":
         res = subgraph_branches(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "kfac":
         res = kfac_job(int(sys.argv[3]), int(sys.argv[4]), int(sys.argv[5]) if len(sys.argv) > 5 else 0)
+    elif what == "filter_parallel":
+        res = filter_parallel(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "token_parallel":
         res = token_parallel(int(sys.argv[3]), int(sys.argv[4]))
     elif what == "layer_parallel":

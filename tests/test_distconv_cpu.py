@@ -279,3 +279,20 @@ def test_token_parallel_attention_block_matches_single(tmp_path, ranks):
         assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], dist["losses"])
     for k, v in single["weight_norms"].items():
         assert abs(v - dist["weight_norms"][k]) <= 1e-4 * max(1.0, abs(v)), k
+
+
+@pytest.mark.parametrize("ranks,groups", [(2, 2), (4, 4), (4, 2)])
+def test_channel_filter_parallel_convolutions_match_single(tmp_path, ranks, groups):
+    """channel_groups == filter_groups on convolutions, activations and poolings: every rank
+    gathers the input channels, applies its block of filters and keeps its block of output
+    channels; the batch norm between them runs sample-parallel.  Same losses and weights as one
+    process (4 ranks with 2 groups: two sample groups)."""
+    single = _run(1, ["filter_parallel", "1", "4"], str(tmp_path / "a.json"))
+    dist = _run(ranks, ["filter_parallel", str(groups), "4"], str(tmp_path / "b.json"), timeout=600)
+    assert dist["world"] == ranks and dist["sample_groups"] == ranks // groups
+    assert {"conv1", "act1", "pool1", "conv2", "act2", "pool2"} <= set(dist["partitioned"])
+    assert "bn" not in dist["partitioned"]
+    for a, b in zip(single["losses"], dist["losses"]):
+        assert abs(a - b) <= 2e-4 * max(1.0, abs(a)), (single["losses"], dist["losses"])
+    for k, v in single["weight_norms"].items():
+        assert abs(v - dist["weight_norms"][k]) <= 1e-4 * max(1.0, abs(v)), k
