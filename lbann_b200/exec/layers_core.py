@@ -637,6 +637,8 @@ class BatchNormalization(ExecLayer):
             reduce_fn, count_scale = dc.bn_reduction(self)
         elif par is not None and self.stats_group != 1 and par.dp_size > 1:
             reduce_fn, count_scale = par.bn_reduction(self.stats_group)
+        if reduce_fn is not None and training:
+            count_scale = self.exact_count_scale(x, count_scale)
         squeeze = False
         if x.dim() == 2:
             x = x.unsqueeze(-1)
@@ -646,6 +648,21 @@ class BatchNormalization(ExecLayer):
                           training, self.eps, self.decay, self.bessel, reduce_fn, count_scale,
                           self.fused_act[0], self.fused_act[1])
         return [y.squeeze(-1) if squeeze else y]
+
+
+    def exact_count_scale(self, x, count_scale: float) -> float:
+        """Statistics over the whole trainer: entries per channel of the whole mini-batch divided
+        by this rank's, which is the number of ranks only while every rank holds the same share
+        (the last mini-batch of an epoch, or a sample-parallel stretch behind a partitioned one,
+        may deal 2 + 1 samples).  The reference counts the global mini-batch the same way
+        (src/layers/regularizers/batch_normalization.cu:139-153)."""
+        m, par = self.model, self.model.parallel
+        if (par is None or count_scale != float(par.world_size) or par.tp_size != 1
+                or getattr(m, "subgrid", None) is not None or not getattr(m, "_global_mb_given", False)):
+            return count_scale
+        local = x.numel() // max(int(x.shape[1]), 1)
+        total = int(m._global_mb) * prod(self.in_dims[0][1:])
+        return total / local if local > 0 else count_scale
 
 
 @register("entrywise_batch_normalization")

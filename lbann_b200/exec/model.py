@@ -541,6 +541,7 @@ class ExecModel:
         self.current_mini_batch_size = int(first.shape[0]) if first is not None else 0
         dp = self.parallel.dp_size if self.parallel is not None else 1
         self._global_mb = global_mini_batch_size or self.current_mini_batch_size * dp
+        self._global_mb_given = bool(global_mini_batch_size)
         self._mb_offset = mini_batch_offset
         acts = {}
         self.acts = acts          # visible to callbacks while it fills up

@@ -141,3 +141,25 @@ def test_every_frontend_layer_class_exports_a_message():
         msg = cls().export_proto()
         assert msg.WhichOneof("layer_type") == f.name, cls_name
     assert not missing, missing
+
+
+def test_batch_norm_counts_the_whole_mini_batch_when_shares_differ():
+    """Whole-trainer statistics: the count is global mini-batch x entries per sample, not this
+    rank's entries x ranks (a last mini-batch of 3 samples leaves 2 + 1 on two ranks)."""
+    from types import SimpleNamespace
+    from lbann_b200.exec.layers_core import BatchNormalization
+    bn = BatchNormalization.__new__(BatchNormalization)
+    bn.in_dims = [(8, 4, 4)]
+    par = SimpleNamespace(world_size=2, tp_size=1)
+    bn.model = SimpleNamespace(parallel=par, subgrid=None, _global_mb=3, _global_mb_given=True)
+    two, one = torch.zeros(2, 8, 4, 4), torch.zeros(1, 8, 4, 4)
+    assert bn.exact_count_scale(two, 2.0) == 3 * 16 / (2 * 16)
+    assert bn.exact_count_scale(one, 2.0) == 3.0
+    bn.model._global_mb = 4                          # equal shares: exactly the number of ranks
+    assert bn.exact_count_scale(two, 2.0) == 2.0
+    bn.model._global_mb_given = False                # size not passed by the caller: unchanged
+    assert bn.exact_count_scale(one, 2.0) == 2.0
+    bn.model._global_mb_given = True
+    assert bn.exact_count_scale(one, 4.0) == 4.0     # statistics of a sub-group of ranks: unchanged
+    bn.in_dims = [(8,)]
+    assert bn.exact_count_scale(torch.zeros(1, 8), 2.0) == 4.0
