@@ -37,6 +37,7 @@ gates) one activation factor over samples x time steps and one error factor per 
 """
 from __future__ import annotations
 
+import time
 from concurrent.futures import ThreadPoolExecutor
 from typing import Dict, List
 
@@ -120,6 +121,12 @@ class KFAC(SGDTrainingAlgorithm):
         self.compute_interval = int(msg.compute_interval) or 1
         self.disable_layers = set(str(msg.disable_layers).split()) if msg.disable_layers else set()
         self.lr_factor = float(msg.learning_rate_factor) or 1.0
+        self.lr_factor_gru = float(msg.learning_rate_factor_gru) or self.lr_factor
+        # "a b c": plain SGD in epochs [0, a), K-FAC in [a, b), SGD in [b, c), K-FAC afterwards
+        # (factors keep being updated; only the preconditioned gradient is not applied)
+        self.use_epochs = self._parse_use_interval(str(msg.kfac_use_interval or ""))
+        self.print_time = bool(msg.print_time)
+        self.print_matrix_summary = bool(msg.print_matrix_summary) or bool(msg.print_matrix)
         self.damping_bn_act = _floats(msg.damping_bn_act, self.damping_act[0])
         self.damping_bn_err = _floats(msg.damping_bn_err, self.damping_err[0])
         self.use_eigen = bool(msg.use_eigen_decomposition)
@@ -136,6 +143,19 @@ class KFAC(SGDTrainingAlgorithm):
         self.async_installs = 0             # inverses that arrived one step late (tests read it)
 
     # ---------------------------------------------------------------- schedules
+    @staticmethod
+    def _parse_use_interval(s: str) -> List[bool]:
+        marks = [int(v) for v in s.split()]
+        flags, use = [], False
+        for epoch in range(marks[-1] if marks else 0):
+            if epoch in marks:
+                use = not use
+            flags.append(use)
+        return flags
+
+    def _applies(self, epoch: int) -> bool:
+        return self.use_epochs[epoch] if epoch < len(self.use_epochs) else True
+
     def _damping(self, vals: List[float], step: int) -> float:
         if len(vals) == 1 or self.damping_warmup_steps <= 0:
             return vals[0]
@@ -197,7 +217,14 @@ class KFAC(SGDTrainingAlgorithm):
         model.record_statistics("training", obj)
         model.backward_prop(obj)
         if ctx.step % self.compute_interval == 0:
+            self._apply = self._applies(ctx.epoch)
+            t0 = time.perf_counter() if self.print_time else 0.0
             self._precondition(model, ctx.step, batch.global_size)
+            if self.print_time and trainer.comm.rank_in_trainer == 0:
+                if model.device.type == "cuda":
+                    torch.cuda.synchronize()
+                print(f"K-FAC step {ctx.step}: preconditioning {1e3 * (time.perf_counter() - t0):.3f} ms"
+                      f"{'' if self._apply else ' (factors only)'}", flush=True)
         model.update_weights()
         ctx.step += 1
         ctx.step_in_epoch += 1
@@ -335,10 +362,21 @@ class KFAC(SGDTrainingAlgorithm):
                     torch.zeros(3 * H, 1, device=gw.device)
                 full = torch.cat([gw, gb], 1)
                 nat = torch.cat([blk.Ginv[key][k] @ full[k * H:(k + 1) * H] @ blk.Ainv[key] for k in range(3)], 0)
-                nat = nat * self.lr_factor
+                nat = nat * self.lr_factor_gru
+                if not getattr(self, "_apply", True):
+                    continue
                 W.handle.grad.copy_(nat[:, :-1].reshape(W.handle.grad.shape))
                 if b.handle.grad is not None:
                     b.handle.grad.copy_(nat[:, -1].reshape(b.handle.grad.shape))
+
+    def _summary(self, name: str, **mats):
+        """``print_matrix_summary``: size, mean and extreme values of a block's factors and
+        inverses (kfac_util.cpp prints the same figures)."""
+        if not self.print_matrix_summary:
+            return
+        parts = [f"{k} {tuple(M.shape)} mean {float(M.mean()):.3e} min {float(M.min()):.3e} "
+                 f"max {float(M.max()):.3e}" for k, M in mats.items() if M is not None]
+        print(f"K-FAC {name}: " + "; ".join(parts), flush=True)
 
     @torch.no_grad()
     def _precondition(self, model, step: int, global_batch: int):
@@ -370,8 +408,10 @@ class KFAC(SGDTrainingAlgorithm):
                 c = l.scale.handle.grad.numel()
                 g = torch.cat([l.scale.handle.grad.float().reshape(-1), l.bias.handle.grad.float().reshape(-1)])
                 nat = blk.Ginv @ g * self.lr_factor
-                l.scale.handle.grad.copy_(nat[:c].reshape(l.scale.handle.grad.shape))
-                l.bias.handle.grad.copy_(nat[c:].reshape(l.bias.handle.grad.shape))
+                if getattr(self, "_apply", True):
+                    l.scale.handle.grad.copy_(nat[:c].reshape(l.scale.handle.grad.shape))
+                    l.bias.handle.grad.copy_(nat[c:].reshape(l.bias.handle.grad.shape))
+                self._summary(l.name, G=blk.G, Ginv=blk.Ginv)
                 blk.grad_out = None
                 continue
             if l.w.handle.grad is None:
@@ -399,8 +439,11 @@ class KFAC(SGDTrainingAlgorithm):
                 gw = torch.cat([gw, l.b.handle.grad.float().reshape(-1, 1)], 1)
             # (the patch matrix is ordered (channel, kernel...) like the kernel's trailing dims)
             nat = blk.Ginv @ gw @ blk.Ainv * self.lr_factor
+            self._summary(l.name, A=blk.A, G=blk.G, Ainv=blk.Ainv, Ginv=blk.Ginv)
+            blk.grad_out = None
+            if not getattr(self, "_apply", True):
+                continue
             if l.b is not None and l.b.handle.grad is not None:
                 l.b.handle.grad.copy_(nat[:, -1].reshape(l.b.handle.grad.shape))
                 nat = nat[:, :-1]
             l.w.handle.grad.copy_(nat.reshape(l.w.handle.grad.shape))
-            blk.grad_out = None

@@ -430,3 +430,25 @@ def test_kfac_asynchronous_inverses_arrive_one_step_late():
     sgd = lbann.BatchedIterativeOptimizer("sgd", epoch_count=3)
     plain = _fit(sgd)
     assert math.isfinite(obj_async) and obj_async < plain, (plain, obj_async)
+
+
+def test_kfac_use_interval_switches_between_sgd_and_kfac_by_epoch(capsys):
+    """kfac_use_interval "1 2": epoch 0 applies plain SGD gradients (factors are still gathered),
+    epoch 1 preconditions, from epoch 2 on K-FAC again (beyond the listed range)."""
+    from lbann_b200.exec.kfac import KFAC
+    assert KFAC._parse_use_interval("1 2") == [False, True]
+    assert KFAC._parse_use_interval("2 4 6") == [False, False, True, True, False, False]
+    assert KFAC._parse_use_interval("") == []
+
+    def run(**kw):
+        sgd = lbann.BatchedIterativeOptimizer("sgd", epoch_count=1)
+        return _fit(lbann.KFAC("kfac", sgd, damping_act="1e-2", damping_err="1e-2", kronecker_decay=0.9,
+                               update_intervals="1", compute_interval=1, **kw), epochs=1)
+
+    plain = _fit(lbann.BatchedIterativeOptimizer("sgd", epoch_count=1), epochs=1)
+    off = run(kfac_use_interval="1 2", print_time=True, print_matrix_summary=True)   # one epoch: SGD only
+    on = run()
+    out = capsys.readouterr().out
+    assert abs(off - plain) <= 1e-6 * max(1.0, abs(plain)), (off, plain)
+    assert on < plain
+    assert "(factors only)" in out and "K-FAC fc1: A (9, 9)" in out
