@@ -57,7 +57,7 @@ def apply_overrides(msg, o: opts.Options):
             r.fraction_of_data_to_use = float(o.get("data_reader_fraction"))
         if o.get_int("absolute_sample_count"):
             r.absolute_sample_count = o.get_int("absolute_sample_count")
-    ck = o.get("ckpt_dir")
+    ck = o.get("ckpt_dir") or o.get("checkpoint_dir")
     rs = o.get("restart_dir")
     if ck or rs:
         for cb in list(msg.trainer.callback) + list(msg.model.callback):

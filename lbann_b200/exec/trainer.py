@@ -75,6 +75,10 @@ class ExecTrainer:
         init_random(self.data_seed, self.comm.rank_in_world, self.comm.rank_in_trainer,
                     self.comm.trainer_rank, self.io_threads)
         self.background_io = (not bool(tp.serialize_io)) if background_io is None else background_io
+        if o.get_bool("serialize_io") or o.get_bool("disable_background_io_activity"):
+            self.background_io = False
+        if "omp_num_threads" in o._values or o._env("omp_num_threads"):   # only when asked for
+            torch.set_num_threads(max(1, o.get_int("omp_num_threads")))
         self.parallel = None
         self.distconv = None
         self._readers_override = readers

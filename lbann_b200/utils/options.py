@@ -20,6 +20,14 @@ _FLAGS = [
     "check_data", "keep_sample_order", "quiet", "write_sample_list", "z_score", "use_cuda_graph",
     "allow_multitrainer_global_statistics", "hang", "use_caliper", "deterministic",
     "trainer_enable_subgrid_async_comm",       # K-FAC: factor inversions run beside the next step
+    # accepted for command lines written for the reference; what they switch (its data-store
+    # test modes, SHMEM / NVSHMEM start-up, GPU-direct forward prop, the second model of its
+    # sub-grid scheme) has no counterpart here
+    "disable_background_io_activity", "ltfb_allow_global_statistics", "ltfb_global_multitrainer_statistics",
+    "use_gpu_direct_memory_in_forward_prop", "init_shmem", "init_nvshmem", "caliper",
+    "data_store_min_max_timing", "data_store_no_thread", "data_store_test_cache", "node_sizes_vary",
+    "keep_packed_fields", "load_full_sample_list_once", "write_sample_label_list", "jag",
+    "trainer_create_two_models", "trainer_enable_topo_aware_subgrid",
 ]
 _OPTIONS = {
     # name: (type, default)
@@ -40,6 +48,16 @@ _OPTIONS = {
     "sample_list_train": (str, ""), "sample_list_validate": (str, ""),
     "sequence_length": (int, 0), "vocab": (str, ""), "default_dtype": (str, ""),
     "num_train_samples": (int, 0), "num_validate_samples": (int, 0), "num_test_samples": (int, 0),
+    "checkpoint_dir": (str, ""), "rng_seeds_per_trainer_to_display": (int, 2), "max_io_thread_rngs": (int, 128),
+    "omp_num_threads": (int, 4), "data_store_test_checkpoint": (str, ""), "normalization": (str, ""),
+    "pilot2_read_file_sizes": (str, ""), "pilot2_save_file_sizes": (str, ""),
+    "smiles_buffer_size": (int, 16 * 1024 * 1024),
+    # options of the reference's data-preparation tools that share its parser
+    "base_dir": (str, ""), "filelist": (str, ""), "filename": (str, ""), "format": (str, ""),
+    "index_fn": (str, ""), "mapping_fn": (str, ""), "num_lists": (int, -1), "num_samples": (int, -1),
+    "num_samples_per_file": (int, 1000), "num_samples_per_list": (int, -1), "num_subdirs": (int, -1),
+    "output_base_dir": (str, ""), "output_base_fn": (str, ""), "output_dir": (str, ""), "output_fn": (str, ""),
+    "samples_per_file": (int, -1),
 }
 
 

@@ -117,3 +117,18 @@ model0 (instance 0) training epoch 1 objective function : 1.5
     assert out[0].split()[:3] == ["model", "mode", "epoch"] and "mini-batch time statistics" in out[0]
     csv_rows = open(tmp_path / "t.csv").read().splitlines()
     assert csv_rows[1].startswith("model0,training,0,2.30412,11.5,3.25,0.0125")
+
+
+def test_every_command_line_option_of_the_reference_is_accepted():
+    """Option names are the reference's (src/utils/options.cpp); a command line written for it
+    parses here, including the switches that have no counterpart."""
+    from lbann_b200.utils import options as opts
+    o = opts.reset()
+    rest = o.parse(["--omp_num_threads=8", "--init_nvshmem", "--checkpoint_dir", "ck", "--num_lists=3",
+                    "--trainer_enable_subgrid_async_comm", "--data_store_test_cache", "--not_an_option"])
+    assert rest == ["--not_an_option"]
+    assert o.get_int("omp_num_threads") == 8 and o.get_bool("init_nvshmem") and o.get("checkpoint_dir") == "ck"
+    assert o.get_int("num_lists") == 3 and o.get_bool("trainer_enable_subgrid_async_comm")
+    assert o.get("smiles_buffer_size") == 16 * 1024 * 1024 and not o.get_bool("caliper")
+    assert "--omp_num_threads" in o.describe()
+    opts.reset()
