@@ -286,7 +286,10 @@ class KFAC(SGDTrainingAlgorithm):
             out = [torch.zeros_like(M) for M in mats]
         elif kind == "stream":
             out, ev = handle
-            torch.cuda.current_stream().wait_event(ev)
+            cur = torch.cuda.current_stream()
+            cur.wait_event(ev)
+            for t in out:                  # allocated on the side stream, used on this one from now on
+                t.record_stream(cur)
         else:
             out = handle.result()
         if distributed:
